@@ -1,0 +1,173 @@
+/*
+ * titan_kv.h — C ABI of the B200 (sm_100a) paged KV-cache hot path.
+ *
+ * The reference (titan-engine) has no FFI seam for this path: callers link
+ * straight against class titan::KVCache (src/inference/kv_cache.h:15-81) and the
+ * free function titan::cuda::attention_decode (src/compute/dispatch.h:73-75).
+ * Every entry point below names the reference interface it stands in for.  The
+ * C++ classes with the reference's own names that sit on top of this ABI are in
+ * titan_engine_b200/csrc/compat/.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; `stream` is a cudaStream_t passed as void*
+ *    (NULL = default stream, as the reference passes nullptr: src/inference/engine.cpp:191)
+ *  - every call returns a tk_status and never throws; tk_kv_last_error() gives text
+ *  - one caller thread per handle (the reference serialises the path under one
+ *    mutex, src/api/server.cpp:33); all device work is stream-ordered and no entry
+ *    point other than create/destroy and the *_host variants synchronises the device
+ *  - no device allocation after tk_kv_create* (reference invariant: no cudaMalloc
+ *    during generation, src/model/moe.cpp:49-108)
+ *  - there is no CPU fallback: without a CUDA device every compute call fails.
+ */
+#ifndef TITAN_KV_H
+#define TITAN_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum tk_status {
+    TK_OK = 0,
+    TK_INVALID_ARG = 1,
+    TK_OUT_OF_PAGES = 2,
+    TK_CUDA_ERROR = 3,
+    TK_TIMEOUT = 4,
+    TK_OUT_OF_SEQS = 5,
+    TK_UNSUPPORTED = 6
+} tk_status;
+
+/* dtype numbering = titan::DType (src/core/types.h:17-21) */
+enum { TK_FP32 = 0, TK_FP16 = 1, TK_BF16 = 2, TK_FP8_E4M3 = 3 };
+
+/* which decode kernel tk_kv_decode launches */
+enum { TK_DECODE_AUTO = 0, TK_DECODE_SIMT = 1, TK_DECODE_MMA = 2 };
+
+/* Stands in for the (L, Hkv, D, max_seq_len, dtype) argument list of
+ * KVCache::initialize (src/inference/kv_cache.h:21-23) plus the fields of
+ * RuntimeConfig the reference declares for this path but never reads
+ * (max_context_len, kv_cache_dtype: src/core/types.h:243-248). */
+typedef struct tk_kv_config {
+    int32_t num_layers;
+    int32_t num_heads;          /* query heads */
+    int32_t num_kv_heads;
+    int32_t head_dim;           /* 64 or 128 */
+    int32_t page_size;          /* tokens per page: 16 */
+    int32_t dtype;              /* storage: TK_FP16 / TK_BF16 / TK_FP8_E4M3 */
+    int32_t io_dtype;           /* type of q, k, v, out and of FP8 open pages: TK_FP16 / TK_BF16; 0 = dtype */
+    int32_t num_pages;          /* physical pages per layer */
+    int32_t max_seqs;           /* sequence slots */
+    int32_t max_pages_per_seq;  /* page-table row length */
+    int32_t max_step_tokens;    /* most tokens one step may append (all sequences together) */
+    int32_t chunk_tokens;       /* split-KV chunk, multiple of page_size; 0 = choose per step */
+    int32_t decode_impl;        /* TK_DECODE_* */
+    int32_t device;             /* CUDA ordinal, -1 = current, -2 = none: page bookkeeping only,
+                                   every compute call fails (there is no CPU compute path) */
+    int32_t hot_window;         /* tokens kept in HBM per sequence; 0 = everything (no cold tier) */
+    int32_t reserved[5];
+} tk_kv_config;
+
+typedef struct tk_kv_stats {    /* in the style of CacheStats, src/memory/memory_manager.h:211-220 */
+    int64_t pages_total, pages_free, pages_cold;
+    int64_t page_allocs, page_frees, seq_allocs, seq_frees;
+    int64_t evictions, prefetch_hits, prefetch_misses;
+    int64_t bytes_h2d, bytes_d2h;
+    int64_t steps, tokens_appended, pages_sealed;
+} tk_kv_stats;
+
+typedef struct tk_kv tk_kv;
+
+const char* tk_status_str(int status);
+const char* tk_kv_last_error(const tk_kv* h);          /* h may be NULL: last create error */
+
+/* ---- lifetime: KVCache::initialize / initialize_external / ~KVCache ----------
+ * (src/inference/kv_cache.cpp:16-57, :59-81, :9-14).  The pool is zero-filled like
+ * the reference's slabs (:49-50). */
+void   tk_kv_config_default(tk_kv_config* cfg);
+size_t tk_kv_arena_bytes(const tk_kv_config* cfg);     /* device bytes create_external needs */
+int    tk_kv_create(const tk_kv_config* cfg, tk_kv** out);
+/* Adopts caller-owned device memory (e.g. carved from the reference's VramPool,
+ * src/model/moe.cpp:549-595); it is never freed by the handle (kv_cache.cpp:71). */
+int    tk_kv_create_external(const tk_kv_config* cfg, void* arena, size_t arena_bytes, tk_kv** out);
+int    tk_kv_destroy(tk_kv* h);
+int    tk_kv_get_config(const tk_kv* h, tk_kv_config* out);
+/* KVCache::memory_bytes (kv_cache.cpp:153-156) */
+size_t tk_kv_memory_bytes(const tk_kv* h);
+/* Device address of layer `layer`'s pool: [num_pages][Hkv][2][page_size][D] (parity dumps).
+ * FP8: `codes`, plus scales f32 [num_pages][Hkv][2] and open pages [max_seqs][Hkv][2][page_size][D]. */
+int    tk_kv_layer_ptrs(const tk_kv* h, int layer, void** pool, float** scales, void** open_pages);
+
+/* ---- sequences and pages ------------------------------------------------------
+ * The reference's closest analogues: BatchScheduler::allocate_slot / free_slot
+ * (src/inference/batch.cpp:86-101; lowest free index) and KVCache::clear /
+ * set_seq_len (kv_cache.cpp:158-167, kv_cache.h:51).  Host-only; no device work. */
+int tk_kv_seq_alloc(tk_kv* h, int32_t* seq_out);
+int tk_kv_seq_free(tk_kv* h, int32_t seq);
+/* Grow `seq` by n_tokens, taking pages from the LIFO free list (pops 0,1,2,... on a
+ * fresh pool).  TK_OUT_OF_PAGES leaves all state unchanged. */
+int tk_kv_reserve(tk_kv* h, int32_t seq, int32_t n_tokens);
+/* Drop tokens past new_len (speculative rollback; the reference has none:
+ * src/inference/speculative.cpp:306-307). */
+int tk_kv_truncate(tk_kv* h, int32_t seq, int32_t new_len);
+/* Install a caller-chosen page list (e.g. a shuffled pool) as the table of `seq`;
+ * the pages must be free. */
+int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t seq_len);
+/* KVCache::seq_len (kv_cache.h:50), per sequence here; -1 if the slot is free */
+int tk_kv_seq_len(const tk_kv* h, int32_t seq);
+int tk_kv_num_free_pages(const tk_kv* h);
+/* Copies the page-table row of `seq` (n_out pages). */
+int tk_kv_page_table(const tk_kv* h, int32_t seq, int32_t* out, int32_t cap, int32_t* n_out);
+/* Slot index page*page_size + pos%page_size of token `pos`, or -1. */
+int64_t  tk_kv_slot(const tk_kv* h, int32_t seq, int32_t pos);
+/* FNV-1a over (sequence lengths, page tables, free stack). */
+uint64_t tk_kv_state_digest(const tk_kv* h);
+int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out);
+
+/* ---- one decode/prefill step ---------------------------------------------------
+ * tk_kv_step_begin reserves n_new[i] tokens for seq_ids[i] (all or nothing), lays
+ * out this step's token list (sequence order of the call, then position) and the
+ * split-KV work list, and uploads the page-table delta: one pinned-buffer copy and
+ * one small kernel on `stream`.  n_new may be NULL (decode without append).
+ * Sequence lengths advance once per step, not once per layer as the reference's
+ * single counter does (kv_cache.cpp:148-150). */
+int tk_kv_step_begin(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new,
+                     void* stream);
+int tk_kv_step_num_tokens(const tk_kv* h);
+int tk_kv_step_num_work_items(const tk_kv* h);
+int tk_kv_step_chunk_tokens(const tk_kv* h);
+
+/* KVCache::update (src/inference/kv_cache.cpp:121-151) for every token of the step:
+ * k, v device [n_tokens][Hkv][D] in io_dtype.  Page-table scatter; with FP8 storage,
+ * pages completed by this step are sealed (absmax scale + E4M3 codes).
+ * slots_out (device int64[n_tokens], may be NULL) receives each token's slot index. */
+int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t* slots_out,
+                 void* stream);
+/* cuda::attention_decode (src/compute/cuda/attention.cu:315-330) for every sequence
+ * of the step: q, out device [n_seqs][H][D] in io_dtype.  Paged GQA attention,
+ * online softmax, split-KV partials and log-sum-exp combine. */
+int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream);
+/* Same, but stops before normalisation: partial[n_seqs][H][D+2] f32 =
+ * (o unnormalised [D], m, l), for a cross-GPU combine. */
+int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial, void* stream);
+/* Log-sum-exp merge of n_parts partial sets: parts [n_parts][n_rows][D+2] f32 ->
+ * out [n_rows][D] in out_dtype (TK_FP16 / TK_BF16 / TK_FP32). */
+int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int32_t head_dim,
+                        void* out, int32_t out_dtype, void* stream);
+/* update + attention_decode of one layer with HOST buffers (pageable or pinned):
+ * copies k, v, q in, runs append and decode, copies out back, and waits for it. */
+int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
+                             const void* q_host, void* out_host, void* stream);
+
+/* Reads the device status word after draining `stream`: TK_OK, or TK_TIMEOUT when a
+ * bounded device-side wait gave up (the word is cleared). */
+int tk_kv_device_status(tk_kv* h, void* stream);
+
+/* Number of kernels this library has launched on this handle so far. */
+int64_t tk_kv_launch_count(const tk_kv* h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TITAN_KV_H */

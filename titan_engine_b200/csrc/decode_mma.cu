@@ -1,0 +1,501 @@
+// decode_mma.cu — paged GQA decode attention for sm_100a: TMA-staged pages,
+// tensor-core QK^T / PV tiles, online softmax, split-KV partials.
+//
+// Arithmetic contract: that of attention_decode_kernel (reference:
+// src/compute/cuda/attention.cu:58-157) — score = (q.k)/sqrtf(D), running max from
+// -1e30f, FP32 accumulation, GQA map kv_head = head/(H/Hkv) — evaluated as an online
+// softmax whose (o, m, l) partials are merged by the LSE combine (decode_simt.cu).
+//
+// Schedule.  One CTA per work item (sequence, kv head, chunk of pages).  A pool tile
+// (page, kv head) is [K: 16 tokens x D][V: 16 tokens x D], contiguous in HBM, so one
+// TMA box of 32 rows x 128 bytes (two boxes when a row is 256 bytes) brings K and V of a
+// page into shared memory with the 128-byte swizzle that makes ldmatrix conflict-free.
+// Each of the 4 warps owns every 4th page of the chunk and runs a private ring of
+// kStages TMA stages (own mbarriers, no CTA-wide barrier in the loop), so a CTA keeps up
+// to 4*kStages page tiles in flight.  The G query heads of the group are the M rows of
+// m16n8k16 MMAs (rows >= G are zero padding): S = Q K^T over one page (2 n-tiles x D/16
+// k-steps), softmax in registers, O += P V (D/8 n-tiles).  FP8 pools are expanded to
+// fp16 in registers (cvt.rn.f16x2.e4m3x2, exact) with the per-page K scale folded into
+// the score scale and the V scale folded into P.
+//
+// The path is HBM-bound: 4 flop/B (bf16, G=4) to 16 flop/B (fp8, G=8); the tensor pipe
+// is used because FP32 SIMT FMAs cannot keep up with 6.5 TB/s at those intensities, not
+// because the op is a large contraction.  tcgen05 needs M >= 64 rows; with 4-16 query
+// rows mma.sync is the fitting instruction.
+#include "tk_kernels.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cudaTypedefs.h>
+
+namespace tk {
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+constexpr int kPage = 16;               // tokens per page on this path
+constexpr int kBoxBytes = 32 * 128;     // one TMA box: 32 rows (K 0-15, V 16-31) x 128 B
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // bounded mbarrier wait
+
+enum Kind { K_F16 = 0, K_BF16 = 1, K_FP8 = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Wait with a wall-clock bound: on expiry record it and give up instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (!mbar_try_wait(bar, parity)) {
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (status) atomicExch(status, 4 /* TK_TIMEOUT */);
+            return false;
+        }
+    }
+    return true;
+}
+// 2-D tiled TMA load, global -> this CTA's shared memory, completion on an mbarrier.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+template <bool BF16>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if (BF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    if (BF16) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v); }
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// two E4M3 codes (low byte first) -> f16x2, exact
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_codes) {
+    uint32_t r;
+    const unsigned short a = (unsigned short)two_codes;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(a));
+    return r;
+}
+// swizzled byte offset of 16-byte chunk `c` of row `r` inside a 32x128-byte box
+__device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int KIND, int D>
+struct Cfg {
+    static constexpr int ESIZE = KIND == K_FP8 ? 1 : 2;
+    static constexpr int ROW_BYTES = D * ESIZE;
+    static constexpr int NBOX = ROW_BYTES / 128;            // TMA boxes per (page, kv head) tile
+    static constexpr int STAGE_BYTES = NBOX * kBoxBytes;
+    static constexpr int BOX_W = 128 / ESIZE;               // box width in elements
+    static constexpr bool MMA_BF16 = KIND == K_BF16;        // FP8 computes in fp16
+    static constexpr int SMEM_BYTES = kWarps * kStages * STAGE_BYTES + 1024 + 128;
+};
+
+// IO_BF16: type of q (relevant for FP8, where the MMA type is fp16 regardless).
+// GHI: group has more than 8 query heads (rows 8..15 of the M tile carry data).
+template <int KIND, int D, bool IO_BF16, bool GHI>
+__global__ void __launch_bounds__(kWarps * 32)
+decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtrs lp, StepDev st,
+                  const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q,
+                  float* __restrict__ partials, int* __restrict__ status) {
+    using C = Cfg<KIND, D>;
+    constexpr bool BF = C::MMA_BF16;
+    constexpr int KS = D / 16;                              // k-steps of QK^T
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + kWarps * kStages * C::STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gr = lane >> 2, j = lane & 3;                 // fragment row / column-pair index
+    const int G = g.H / g.Hkv;
+
+    const int4 it = st.items[blockIdx.x];
+    const int b = it.x, chunk = it.y, kvh = it.z;
+    const int seq = st.seq[b], len = st.len[b];
+    const int pool_tokens = KIND == K_FP8 ? (len / kPage) * kPage : len;
+    const int t0 = chunk * st.chunk_tokens;
+    const int t1 = min(pool_tokens, t0 + st.chunk_tokens);
+    const int n_pages = (t1 - t0 + kPage - 1) / kPage;
+    const int lp0 = t0 / kPage;
+    const int n_w = n_pages > warp ? (n_pages - warp + kWarps - 1) / kWarps : 0;   // pages of this warp (<= 32)
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kWarps * kStages; i++) mbar_init(smem_u32(&bars[i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    // lane i keeps the physical page (and FP8 scales) of this warp's i-th page
+    int my_page = 0;
+    float my_ks = 1.0f, my_vs = 1.0f;
+    if (lane < n_w) {
+        my_page = page_table[(size_t)seq * g.max_pages_per_seq + lp0 + warp + kWarps * lane];
+        if (KIND == K_FP8) {
+            const float2 sc = *reinterpret_cast<const float2*>(lp.scales + ((size_t)my_page * g.Hkv + kvh) * 2);
+            my_ks = sc.x; my_vs = sc.y;
+        }
+    }
+
+    uint8_t* wstage = smem + (size_t)warp * kStages * C::STAGE_BYTES;
+    auto issue = [&](int i) {                               // called by lane 0 only
+        const int page = __shfl_sync(0xFFFFFFFFu, my_page, i);
+        if (lane == 0) {
+            const int s = i % kStages;
+            const uint32_t bar = smem_u32(&bars[warp * kStages + s]);
+            const uint32_t dst = smem_u32(wstage + (size_t)s * C::STAGE_BYTES);
+            mbar_expect_tx(bar, C::STAGE_BYTES);
+            const int row = (page * g.Hkv + kvh) * 32;
+#pragma unroll
+            for (int h = 0; h < C::NBOX; h++) tma_load_2d(dst + h * kBoxBytes, &tmap, h * C::BOX_W, row, bar);
+        }
+    };
+    for (int i = 0; i < kStages && i < n_w; i++) issue(i);
+
+    // ---- Q fragments (A operand), rows >= G are zero -------------------------------
+    uint32_t qa[KS][4];
+    {
+        const uint16_t* qrow0 = q + ((size_t)b * g.H + (size_t)kvh * G + gr) * D;
+        const uint16_t* qrow1 = qrow0 + (size_t)8 * D;
+        const bool v0 = gr < G, v1 = GHI && (gr + 8 < G);
+#pragma unroll
+        for (int kk = 0; kk < KS; kk++) {
+            uint32_t w[4];
+            if (KIND == K_FP8) {
+                // k index (2j,2j+1) <-> dims 16kk+4j,+1 ; (2j+8,2j+9) <-> dims 16kk+4j+2,+3
+                const uint2 x0 = v0 ? *reinterpret_cast<const uint2*>(qrow0 + 16 * kk + 4 * j) : make_uint2(0, 0);
+                const uint2 x1 = v1 ? *reinterpret_cast<const uint2*>(qrow1 + 16 * kk + 4 * j) : make_uint2(0, 0);
+                w[0] = x0.x; w[2] = x0.y; w[1] = x1.x; w[3] = x1.y;
+                if (IO_BF16) {                              // bf16 -> fp16 (exact in fp16's normal range)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+                        w[i] = pack2<false>(lo, hi);
+                    }
+                }
+            } else {
+                w[0] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + 16 * kk + 2 * j) : 0u;
+                w[2] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + 16 * kk + 8 + 2 * j) : 0u;
+                w[1] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 2 * j) : 0u;
+                w[3] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 8 + 2 * j) : 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) qa[kk][i] = w[i];
+        }
+    }
+
+    // ---- running state -------------------------------------------------------------
+    // 16-bit: o[nt] is the C fragment of n-tile nt (dims 8nt..8nt+7).
+    // FP8:    o[2c] / o[2c+1] are the even-dim / odd-dim tiles of 16-dim chunk c.
+    constexpr int NT = D / 8;
+    float o[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f; }
+    float m0 = -1e30f, m1 = -1e30f, l0 = 0.0f, l1 = 0.0f;  // rows gr and gr+8
+    const float sm_scale = 1.0f / sqrtf((float)D);
+    bool alive = true;
+
+    for (int i = 0; i < n_w; i++) {
+        const int s = i % kStages;
+        const uint32_t bar = smem_u32(&bars[warp * kStages + s]);
+        // warp-uniform verdict, so that a give-up never splits the warp before a shuffle
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(bar, (uint32_t)((i / kStages) & 1), status))) { alive = false; break; }
+        uint8_t* stg = wstage + (size_t)s * C::STAGE_BYTES;
+        const uint32_t stg_u = smem_u32(stg);
+        const int tok_base = (lp0 + warp + kWarps * i) * kPage;
+        const int n_valid = min(kPage, t1 - tok_base);     // < 16 only on a sequence's last page
+
+        float sc_k = sm_scale, sc_v = 1.0f;
+        if (KIND == K_FP8) {
+            sc_k *= __shfl_sync(0xFFFFFFFFu, my_ks, i);
+            sc_v = __shfl_sync(0xFFFFFFFFu, my_vs, i);
+        }
+
+        if (KIND != K_FP8 && n_valid < kPage) {
+            // stale rows of a partly filled page: zero the V rows so 0 * garbage cannot make NaN
+            for (int idx = lane; idx < (kPage - n_valid) * 8 * C::NBOX; idx += 32) {
+                const int h = idx / ((kPage - n_valid) * 8), rem = idx % ((kPage - n_valid) * 8);
+                const int r = 16 + n_valid + rem / 8, c = rem % 8;
+                *reinterpret_cast<uint4*>(stg + h * kBoxBytes + r * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+
+        // ---- S = Q K^T over the page's 16 tokens ----
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        if (KIND == K_FP8) {
+            const int row = ((lane >> 4) << 3) + (lane & 7);
+#pragma unroll
+            for (int cp = 0; cp < D / 32; cp++) {
+                uint32_t r0, r1, r2, r3;
+                ldsm_x4(stg_u + swz(row, 2 * cp + ((lane >> 3) & 1)), r0, r1, r2, r3);
+                mma16816<BF>(s0, qa[2 * cp],     e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r0 >> 16));
+                mma16816<BF>(s1, qa[2 * cp],     e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r2 >> 16));
+                mma16816<BF>(s0, qa[2 * cp + 1], e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
+                mma16816<BF>(s1, qa[2 * cp + 1], e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
+            }
+        } else {
+            const int row = ((lane >> 4) << 3) + (lane & 7);
+#pragma unroll
+            for (int kk = 0; kk < KS; kk++) {
+                const int cc = 2 * kk + ((lane >> 3) & 1);
+                uint32_t r0, r1, r2, r3;
+                ldsm_x4(stg_u + (cc >> 3) * kBoxBytes + swz(row, cc & 7), r0, r1, r2, r3);
+                mma16816<BF>(s0, qa[kk], r0, r1);
+                mma16816<BF>(s1, qa[kk], r2, r3);
+            }
+        }
+
+        // ---- online softmax (row gr in [0],[1]; row gr+8 in [2],[3]) ----
+        float p0[4], p1[4];
+        {
+            const int c0 = 2 * j;                           // token columns of this thread: c0, c0+1, c0+8, c0+9
+            float a0 = s0[0] * sc_k, a1 = s0[1] * sc_k, a2 = s1[0] * sc_k, a3 = s1[1] * sc_k;
+            if (c0 >= n_valid) a0 = -1e30f;
+            if (c0 + 1 >= n_valid) a1 = -1e30f;
+            if (c0 + 8 >= n_valid) a2 = -1e30f;
+            if (c0 + 9 >= n_valid) a3 = -1e30f;
+            float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+            const float mn = fmaxf(m0, mx);
+            const float alpha = ex2((m0 - mn) * kLog2e);
+            const float nb = -mn * kLog2e;
+            p0[0] = ex2(fmaf(a0, kLog2e, nb)); p0[1] = ex2(fmaf(a1, kLog2e, nb));
+            p1[0] = ex2(fmaf(a2, kLog2e, nb)); p1[1] = ex2(fmaf(a3, kLog2e, nb));
+            l0 = l0 * alpha + (p0[0] + p0[1] + p1[0] + p1[1]);
+            m0 = mn;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) { o[nt][0] *= alpha; o[nt][1] *= alpha; }
+        }
+        if (GHI) {
+            const int c0 = 2 * j;
+            float a0 = s0[2] * sc_k, a1 = s0[3] * sc_k, a2 = s1[2] * sc_k, a3 = s1[3] * sc_k;
+            if (c0 >= n_valid) a0 = -1e30f;
+            if (c0 + 1 >= n_valid) a1 = -1e30f;
+            if (c0 + 8 >= n_valid) a2 = -1e30f;
+            if (c0 + 9 >= n_valid) a3 = -1e30f;
+            float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+            const float mn = fmaxf(m1, mx);
+            const float alpha = ex2((m1 - mn) * kLog2e);
+            const float nb = -mn * kLog2e;
+            p0[2] = ex2(fmaf(a0, kLog2e, nb)); p0[3] = ex2(fmaf(a1, kLog2e, nb));
+            p1[2] = ex2(fmaf(a2, kLog2e, nb)); p1[3] = ex2(fmaf(a3, kLog2e, nb));
+            l1 = l1 * alpha + (p0[2] + p0[3] + p1[2] + p1[3]);
+            m1 = mn;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) { o[nt][2] *= alpha; o[nt][3] *= alpha; }
+        } else {
+            p0[2] = p0[3] = p1[2] = p1[3] = 0.0f;
+        }
+
+        // ---- O += P V ----
+        uint32_t pa[4];
+        pa[0] = pack2<BF>(p0[0] * sc_v, p0[1] * sc_v);
+        pa[1] = pack2<BF>(p0[2] * sc_v, p0[3] * sc_v);
+        pa[2] = pack2<BF>(p1[0] * sc_v, p1[1] * sc_v);
+        pa[3] = pack2<BF>(p1[2] * sc_v, p1[3] * sc_v);
+        if (KIND == K_FP8) {
+            const int row = 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+            for (int cp = 0; cp < D / 32; cp++) {
+                uint32_t r0, r1, r2, r3;
+                ldsm_x4_t(stg_u + swz(row, 2 * cp + (lane >> 4)), r0, r1, r2, r3);
+                const uint32_t e0 = __byte_perm(r0, r1, 0x6420), d0 = __byte_perm(r0, r1, 0x7531);
+                const uint32_t e1 = __byte_perm(r2, r3, 0x6420), d1 = __byte_perm(r2, r3, 0x7531);
+                mma16816<BF>(o[4 * cp + 0], pa, e4m3x2_to_f16x2(e0), e4m3x2_to_f16x2(e0 >> 16));
+                mma16816<BF>(o[4 * cp + 1], pa, e4m3x2_to_f16x2(d0), e4m3x2_to_f16x2(d0 >> 16));
+                mma16816<BF>(o[4 * cp + 2], pa, e4m3x2_to_f16x2(e1), e4m3x2_to_f16x2(e1 >> 16));
+                mma16816<BF>(o[4 * cp + 3], pa, e4m3x2_to_f16x2(d1), e4m3x2_to_f16x2(d1 >> 16));
+            }
+        } else {
+            const int row = 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+#pragma unroll
+            for (int np = 0; np < NT / 2; np++) {
+                const int cc = 2 * np + (lane >> 4);
+                uint32_t r0, r1, r2, r3;
+                ldsm_x4_t(stg_u + (cc >> 3) * kBoxBytes + swz(row, cc & 7), r0, r1, r2, r3);
+                mma16816<BF>(o[2 * np], pa, r0, r1);
+                mma16816<BF>(o[2 * np + 1], pa, r2, r3);
+            }
+        }
+
+        // ---- refill this stage ----
+        __syncwarp();
+        if (i + kStages < n_w) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue(i + kStages);
+        }
+    }
+    (void)alive;
+
+    // ---- merge the 4 warps through shared memory (stage memory is idle now) ----------
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+    __syncthreads();
+    float* red = reinterpret_cast<float*>(smem);            // [kWarps][G][D+2]
+    auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * G + row) * (D + 2) + d]; };
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const int row = gr + 8 * half;
+        if (row < G && (half == 0 || GHI)) {
+            if (KIND == K_FP8) {
+#pragma unroll
+                for (int c = 0; c < D / 16; c++) {
+                    red_at(warp, row, 16 * c + 4 * j + 0) = o[2 * c][2 * half + 0];
+                    red_at(warp, row, 16 * c + 4 * j + 1) = o[2 * c + 1][2 * half + 0];
+                    red_at(warp, row, 16 * c + 4 * j + 2) = o[2 * c][2 * half + 1];
+                    red_at(warp, row, 16 * c + 4 * j + 3) = o[2 * c + 1][2 * half + 1];
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    red_at(warp, row, 8 * nt + 2 * j + 0) = o[nt][2 * half + 0];
+                    red_at(warp, row, 8 * nt + 2 * j + 1) = o[nt][2 * half + 1];
+                }
+            }
+            if (j == 0) {
+                red_at(warp, row, D) = half ? m1 : m0;
+                red_at(warp, row, D + 1) = half ? l1 : l0;
+            }
+        }
+    }
+    __syncthreads();
+    const int prow = st.chunk_base[b] + chunk;
+    for (int idx = threadIdx.x; idx < G * (D + 2); idx += blockDim.x) {
+        const int row = idx / (D + 2), d = idx % (D + 2);
+        float M = -1e30f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, red_at(w, row, D));
+        float val;
+        if (d == D) {
+            val = M;
+        } else {
+            val = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarps; w++) val += red_at(w, row, d) * ex2((red_at(w, row, D) - M) * kLog2e);
+        }
+        partials[partial_off(prow, kvh * G + row, g.H, D) + d] = val;
+    }
+}
+
+template <int KIND, int D, bool IO_BF16, bool GHI>
+cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
+                       const int32_t* page_table, const void* q, float* partials, int* status,
+                       cudaStream_t s) {
+    using C = Cfg<KIND, D>;
+    auto kern = decode_mma_kernel<KIND, D, IO_BF16, GHI>;
+    static bool attr_done[64] = {};                         // per instantiation and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    kern<<<st.n_items, kWarps * 32, C::SMEM_BYTES, s>>>(*map, g, lp, st, page_table, (const uint16_t*)q,
+                                                        partials, status);
+    return cudaGetLastError();
+}
+
+template <int KIND, int D>
+cudaError_t launch_kd(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
+                      const int32_t* page_table, const void* q, float* partials, int* status,
+                      cudaStream_t s) {
+    const bool io_bf16 = g.io_dtype == DT_BF16, ghi = g.H / g.Hkv > 8;
+    if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, st, page_table, q, partials, status, s);
+    if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, st, page_table, q, partials, status, s);
+    if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, st, page_table, q, partials, status, s);
+    return launch_one<KIND, D, false, false>(g, lp, map, st, page_table, q, partials, status, s);
+}
+
+}  // namespace
+
+bool decode_mma_supported(const Geometry& g) {
+    if (g.ps != kPage || g.Hkv <= 0 || g.H % g.Hkv != 0 || g.H / g.Hkv > 16) return false;
+    if (g.dtype == DT_FP8) return g.D == 128;
+    if (g.dtype == DT_FP16 || g.dtype == DT_BF16) return (g.D == 64 || g.D == 128) && g.io_dtype == g.dtype;
+    return false;
+}
+
+// The layer's pool as a 2-D tensor: rows = num_pages*Hkv*2*16 token rows of D elements.
+// Box = 32 rows (one tile: K rows then V rows) x 128 bytes, 128-byte swizzle.
+cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out) {
+    static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return e;
+        if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+        encode = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+    }
+    const int esize = g.dtype == DT_FP8 ? 1 : 2;
+    cuuint64_t dims[2] = {(cuuint64_t)g.D, (cuuint64_t)g.num_pages * g.Hkv * 2 * g.ps};
+    cuuint64_t strides[1] = {(cuuint64_t)g.D * esize};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(out, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
+                        layer_pool, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
+                              const StepDev& st, const int32_t* page_table, const void* q,
+                              float* partials, int* status, cudaStream_t s) {
+    if (st.n_items <= 0) return cudaSuccess;
+    if (!decode_mma_supported(g) || st.chunk_tokens > kPage * kWarps * 32) return cudaErrorNotSupported;
+    if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, st, page_table, q, partials, status, s);
+    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd<K_BF16, 128>(g, lp, map, st, page_table, q, partials, status, s)
+                                              : launch_kd<K_BF16, 64>(g, lp, map, st, page_table, q, partials, status, s);
+    return g.D == 128 ? launch_kd<K_F16, 128>(g, lp, map, st, page_table, q, partials, status, s)
+                      : launch_kd<K_F16, 64>(g, lp, map, st, page_table, q, partials, status, s);
+}
+
+}  // namespace tk

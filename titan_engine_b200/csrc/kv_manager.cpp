@@ -1,0 +1,222 @@
+// kv_manager.cpp — host-side page manager (see kv_manager.h).  No CUDA.
+#include "kv_manager.h"
+
+#include <algorithm>
+#include <cstring>
+
+namespace tk {
+
+PageManager::PageManager(int num_pages, int max_seqs, int max_pages_per_seq, int page_size)
+    : num_pages_(num_pages), max_seqs_(max_seqs), max_pages_per_seq_(max_pages_per_seq),
+      page_size_(page_size) {
+    free_stack_.resize(num_pages);
+    for (int i = 0; i < num_pages; i++) free_stack_[i] = num_pages - 1 - i;  // pops give 0,1,2,...
+    table_.assign((size_t)max_seqs * max_pages_per_seq, -1);
+    seq_len_.assign(max_seqs, -1);
+    seq_pages_.assign(max_seqs, 0);
+}
+
+void PageManager::set_entry(int seq, int idx, int32_t value) {
+    int32_t flat = seq * max_pages_per_seq_ + idx;
+    table_[flat] = value;
+    delta_.emplace_back(flat, value);
+}
+
+// Lowest free index, like BatchScheduler::allocate_slot (src/inference/batch.cpp:86-96).
+int PageManager::seq_alloc() {
+    for (int i = 0; i < max_seqs_; i++)
+        if (seq_len_[i] < 0) { seq_len_[i] = 0; seq_pages_[i] = 0; counters.seq_allocs++; return i; }
+    return -1;
+}
+
+int PageManager::seq_free(int seq) {
+    if (!live(seq)) return ST_INVALID_ARG;
+    const int32_t* r = row(seq);
+    for (int i = 0; i < seq_pages_[seq]; i++) {
+        free_stack_.push_back(r[i]);
+        set_entry(seq, i, -1);
+    }
+    counters.page_frees += seq_pages_[seq];
+    counters.seq_frees++;
+    seq_pages_[seq] = 0;
+    seq_len_[seq] = -1;
+    return ST_OK;
+}
+
+int PageManager::reserve(int seq, int n_tokens) {
+    if (!live(seq) || n_tokens < 0) return ST_INVALID_ARG;
+    int64_t new_len = (int64_t)seq_len_[seq] + n_tokens;
+    int64_t need = (new_len + page_size_ - 1) / page_size_;
+    if (need > max_pages_per_seq_) return ST_INVALID_ARG;
+    int extra = (int)need - seq_pages_[seq];
+    if (extra > (int)free_stack_.size()) return ST_OUT_OF_PAGES;
+    for (int i = 0; i < extra; i++) {
+        int32_t page = free_stack_.back();
+        free_stack_.pop_back();
+        set_entry(seq, seq_pages_[seq]++, page);
+    }
+    counters.page_allocs += extra > 0 ? extra : 0;
+    seq_len_[seq] = (int32_t)new_len;
+    return ST_OK;
+}
+
+int PageManager::truncate(int seq, int new_len) {
+    if (!live(seq) || new_len < 0 || new_len > seq_len_[seq]) return ST_INVALID_ARG;
+    int keep = (new_len + page_size_ - 1) / page_size_;
+    const int32_t* r = row(seq);
+    for (int i = keep; i < seq_pages_[seq]; i++) {
+        free_stack_.push_back(r[i]);
+        set_entry(seq, i, -1);
+        counters.page_frees++;
+    }
+    seq_pages_[seq] = keep;
+    seq_len_[seq] = new_len;
+    return ST_OK;
+}
+
+int PageManager::adopt(int seq, const int32_t* pages, int n_pages, int seq_len) {
+    if (!live(seq) || seq_pages_[seq] != 0 || n_pages < 0 || n_pages > max_pages_per_seq_) return ST_INVALID_ARG;
+    if (seq_len < 0 || (seq_len + page_size_ - 1) / page_size_ != n_pages) return ST_INVALID_ARG;
+    std::vector<uint8_t> want(num_pages_, 0);
+    for (int i = 0; i < n_pages; i++) {
+        if (pages[i] < 0 || pages[i] >= num_pages_ || want[pages[i]]) return ST_INVALID_ARG;
+        want[pages[i]] = 1;
+    }
+    int found = 0;
+    for (int32_t p : free_stack_) found += want[p];
+    if (found != n_pages) return ST_INVALID_ARG;                 // some page is not free
+    free_stack_.erase(std::remove_if(free_stack_.begin(), free_stack_.end(),
+                                     [&](int32_t p) { return want[p] != 0; }),
+                      free_stack_.end());
+    for (int i = 0; i < n_pages; i++) set_entry(seq, i, pages[i]);
+    seq_pages_[seq] = n_pages;
+    seq_len_[seq] = seq_len;
+    counters.page_allocs += n_pages;
+    return ST_OK;
+}
+
+int64_t PageManager::slot(int seq, int pos) const {
+    if (!live(seq) || pos < 0 || pos >= seq_len_[seq]) return -1;
+    return (int64_t)row(seq)[pos / page_size_] * page_size_ + pos % page_size_;
+}
+
+static uint64_t fnv(uint64_t h, const void* p, size_t n) {
+    const uint8_t* b = (const uint8_t*)p;
+    for (size_t i = 0; i < n; i++) { h ^= b[i]; h *= 0x100000001B3ull; }
+    return h;
+}
+
+uint64_t PageManager::digest() const {
+    uint64_t h = 0xCBF29CE484222325ull;
+    h = fnv(h, seq_len_.data(), sizeof(int32_t) * seq_len_.size());
+    h = fnv(h, table_.data(), sizeof(int32_t) * table_.size());
+    int32_t top = (int32_t)free_stack_.size();
+    h = fnv(h, &top, sizeof(top));
+    h = fnv(h, free_stack_.data(), sizeof(int32_t) * free_stack_.size());
+    return h;
+}
+
+int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
+                           bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
+                           int max_partial_rows, StepPlan* plan) {
+    if (n_seqs < 0 || (n_seqs > 0 && !seqs) || !plan) return ST_INVALID_ARG;
+    const int ps = page_size_;
+    if (chunk_tokens < 0 || chunk_tokens % ps != 0) return ST_INVALID_ARG;
+
+    // validate; count pages needed (all or nothing)
+    std::vector<uint8_t> seen(max_seqs_, 0);
+    int64_t total_new = 0, extra_pages = 0;
+    for (int i = 0; i < n_seqs; i++) {
+        int s = seqs[i];
+        if (!live(s) || seen[s]) return ST_INVALID_ARG;
+        seen[s] = 1;
+        int add = n_new ? n_new[i] : 0;
+        if (add < 0) return ST_INVALID_ARG;
+        int64_t new_len = (int64_t)seq_len_[s] + add;
+        int64_t need = (new_len + ps - 1) / ps;
+        if (need > max_pages_per_seq_) return ST_INVALID_ARG;
+        extra_pages += need - seq_pages_[s];
+        total_new += add;
+    }
+    if (total_new > max_step_tokens) return ST_INVALID_ARG;
+    if (extra_pages > (int64_t)free_stack_.size()) return ST_OUT_OF_PAGES;
+
+    // pick the split-KV chunk before touching state (rows must fit the workspace)
+    auto rows_for = [&](int chunk, int64_t* items_out) {
+        int64_t rows = 0, items = 0;
+        for (int i = 0; i < n_seqs; i++) {
+            int64_t len = (int64_t)seq_len_[seqs[i]] + (n_new ? n_new[i] : 0);
+            int64_t pool_tokens = fp8 ? (len / ps) * ps : len;
+            int64_t r = (pool_tokens + chunk - 1) / chunk + ((fp8 && len > pool_tokens) ? 1 : 0);
+            rows += r;
+            items += r * num_kv_heads;
+        }
+        if (items_out) *items_out = items;
+        return rows;
+    };
+    int chunk = chunk_tokens;
+    if (chunk == 0) {
+        static const int cands[] = {2048, 1024, 512, 256, 128};
+        chunk = 0;
+        for (int c : cands) {
+            if (c % ps != 0) continue;
+            int64_t items = 0;
+            int64_t rows = rows_for(c, &items);
+            if (rows > max_partial_rows) break;        // smaller chunks only need more rows
+            chunk = c;
+            if (items >= target_items) break;
+        }
+        if (chunk == 0) return ST_INVALID_ARG;
+    } else if (rows_for(chunk, nullptr) > max_partial_rows) {
+        return ST_INVALID_ARG;
+    }
+
+    plan->chunk_tokens = chunk;
+    plan->seq.assign(seqs, seqs + n_seqs);
+    plan->len.resize(n_seqs);
+    plan->chunk_base.assign(n_seqs + 1, 0);
+    plan->tok_b.clear(); plan->tok_pos.clear(); plan->items.clear(); plan->seals.clear();
+
+    std::vector<int32_t> item_tokens;
+    for (int i = 0; i < n_seqs; i++) {
+        int s = seqs[i];
+        int add = n_new ? n_new[i] : 0;
+        int old_len = seq_len_[s];
+        int st = reserve(s, add);
+        if (st != ST_OK) return st;                     // cannot happen after the checks above
+        int len = seq_len_[s];
+        plan->len[i] = len;
+        int tok_base = (int)plan->tok_b.size();
+        for (int p = old_len; p < len; p++) { plan->tok_b.push_back(i); plan->tok_pos.push_back(p); }
+        if (fp8)
+            for (int lp = old_len / ps; (lp + 1) * ps <= len; lp++)
+                plan->seals.push_back({i, lp, old_len, tok_base});
+        int pool_tokens = fp8 ? (len / ps) * ps : len;
+        int n_chunks = (pool_tokens + chunk - 1) / chunk;
+        for (int c = 0; c < n_chunks; c++)
+            for (int h = 0; h < num_kv_heads; h++) {
+                plan->items.push_back({i, c, h, 0});
+                item_tokens.push_back(std::min(chunk, pool_tokens - c * chunk));
+            }
+        int rows = n_chunks;
+        if (fp8 && len > pool_tokens) {
+            for (int h = 0; h < num_kv_heads; h++) {
+                plan->items.push_back({i, n_chunks, h, 1});
+                item_tokens.push_back(len - pool_tokens);
+            }
+            rows++;
+        }
+        plan->chunk_base[i + 1] = plan->chunk_base[i] + rows;
+    }
+    // biggest items first, so the short tails fill the end of the schedule
+    std::vector<int32_t> order(plan->items.size());
+    for (size_t i = 0; i < order.size(); i++) order[i] = (int32_t)i;
+    std::stable_sort(order.begin(), order.end(),
+                     [&](int32_t a, int32_t b) { return item_tokens[a] > item_tokens[b]; });
+    std::vector<WorkItem> sorted(order.size());
+    for (size_t i = 0; i < order.size(); i++) sorted[i] = plan->items[order[i]];
+    plan->items.swap(sorted);
+    return ST_OK;
+}
+
+}  // namespace tk

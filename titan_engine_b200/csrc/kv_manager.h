@@ -1,0 +1,96 @@
+// kv_manager.h — host-side page manager of the paged KV cache (no CUDA here).
+//
+// Stands where the reference keeps its per-request KV bookkeeping: whole-sequence
+// slots handed out lowest-index-first (BatchScheduler::allocate_slot/free_slot,
+// src/inference/batch.cpp:86-101) and one length counter (KVCache::seq_len,
+// src/inference/kv_cache.h:50-51).  The reference has no pages; the page rules are:
+//   * free list = LIFO stack of page ids, a fresh pool pops 0,1,2,...
+//   * reserve() takes pages one at a time as ceil(len/page_size) grows and
+//     changes nothing when the pool cannot cover the request
+//   * free() returns a sequence's pages in logical order 0..n-1 (the last
+//     logical page is reused first)
+// Every change to a page-table entry is also logged as an (index, value) pair so
+// the device copy can be patched with one small upload per step.
+#pragma once
+
+#include <cstdint>
+#include <utility>
+#include <vector>
+
+namespace tk {
+
+struct WorkItem {      // one CTA's worth of decode work; mirrors the device int4
+    int32_t b;         // index into the step's sequence list
+    int32_t chunk;     // split-KV chunk index inside the sequence
+    int32_t kvh;       // kv head
+    int32_t kind;      // 0 = pool pages, 1 = FP8 open page (16-bit tail)
+};
+
+struct SealItem {      // FP8: one logical page completed by this step
+    int32_t b;         // index into the step's sequence list
+    int32_t lpage;     // logical page
+    int32_t old_len;   // sequence length before the step
+    int32_t tok_base;  // index of the sequence's first new token in the step's token list
+};
+
+struct StepPlan {
+    int32_t chunk_tokens = 0;
+    std::vector<int32_t> seq;        // [n_seqs] sequence slot ids
+    std::vector<int32_t> len;        // [n_seqs] lengths after the step's appends
+    std::vector<int32_t> chunk_base; // [n_seqs+1] prefix sum of partial rows per sequence
+    std::vector<int32_t> tok_b;      // [n_tokens] index into seq[]
+    std::vector<int32_t> tok_pos;    // [n_tokens] position inside the sequence
+    std::vector<WorkItem> items;
+    std::vector<SealItem> seals;
+};
+
+class PageManager {
+public:
+    PageManager(int num_pages, int max_seqs, int max_pages_per_seq, int page_size);
+
+    int  seq_alloc();                              // lowest free slot or -1
+    int  seq_free(int seq);                        // status
+    int  reserve(int seq, int n_tokens);           // status
+    int  truncate(int seq, int new_len);           // status
+    int  adopt(int seq, const int32_t* pages, int n_pages, int seq_len);  // status
+    bool live(int seq) const { return seq >= 0 && seq < max_seqs_ && seq_len_[seq] >= 0; }
+    int  seq_len(int seq) const { return live(seq) ? seq_len_[seq] : -1; }
+    int  seq_pages(int seq) const { return live(seq) ? seq_pages_[seq] : -1; }
+    int  num_free_pages() const { return (int)free_stack_.size(); }
+    int64_t slot(int seq, int pos) const;
+    uint64_t digest() const;
+
+    const int32_t* page_table() const { return table_.data(); }
+    const int32_t* row(int seq) const { return table_.data() + (size_t)seq * max_pages_per_seq_; }
+    int num_pages() const { return num_pages_; }
+    int max_seqs() const { return max_seqs_; }
+    int max_pages_per_seq() const { return max_pages_per_seq_; }
+    int page_size() const { return page_size_; }
+
+    // (flat index into the table, new value) pairs since the last take_delta()
+    std::vector<std::pair<int32_t, int32_t>>& delta() { return delta_; }
+
+    // Reserve n_new[i] tokens for seqs[i] (all or nothing), then lay out the step:
+    // token list in call order then position, FP8 seal list, split-KV work list.
+    // chunk_tokens == 0 picks a chunk so that about `target_items` items exist.
+    int plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
+                  bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
+                  int max_partial_rows, StepPlan* plan);
+
+    struct Counters { int64_t page_allocs = 0, page_frees = 0, seq_allocs = 0, seq_frees = 0; } counters;
+
+private:
+    void set_entry(int seq, int idx, int32_t value);
+    int num_pages_, max_seqs_, max_pages_per_seq_, page_size_;
+    std::vector<int32_t> free_stack_;   // back() is the next page handed out
+    std::vector<int32_t> table_;        // [max_seqs][max_pages_per_seq], -1 = unmapped
+    std::vector<int32_t> seq_len_;      // -1 = slot free
+    std::vector<int32_t> seq_pages_;
+    std::vector<std::pair<int32_t, int32_t>> delta_;
+};
+
+// status codes shared with include/titan_kv.h
+enum { ST_OK = 0, ST_INVALID_ARG = 1, ST_OUT_OF_PAGES = 2, ST_CUDA_ERROR = 3, ST_TIMEOUT = 4,
+       ST_OUT_OF_SEQS = 5, ST_UNSUPPORTED = 6 };
+
+}  // namespace tk

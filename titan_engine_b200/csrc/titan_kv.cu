@@ -1,0 +1,585 @@
+// titan_kv.cu — the C ABI (include/titan_kv.h): handle, device memory, per-step
+// metadata upload and kernel launches.  Host bookkeeping lives in kv_manager.cpp.
+#include "../../include/titan_kv.h"
+
+#include "kv_manager.h"
+#include "tk_kernels.cuh"
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+namespace {
+
+constexpr int kRing = 4;                 // pinned staging buffers in rotation
+constexpr int kMaxDelta = 1 << 16;       // page-table patches per upload; more -> full table copy
+constexpr int TK_DEVICE_NONE = -2;       // bookkeeping only: no device memory, compute calls fail
+
+std::string g_create_error;
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct ArenaLayout {
+    size_t pool_layer, scales_layer, open_layer;   // bytes per layer
+    size_t pool_off, scales_off, open_off, total;
+};
+
+ArenaLayout arena_layout(const tk_kv_config& c) {
+    ArenaLayout a{};
+    const size_t esize = c.dtype == TK_FP8_E4M3 ? 1 : 2;
+    const size_t tile = (size_t)c.num_kv_heads * 2 * c.page_size * c.head_dim;
+    a.pool_layer = align_up((size_t)c.num_pages * tile * esize, 1024);
+    if (c.dtype == TK_FP8_E4M3) {
+        a.scales_layer = align_up((size_t)c.num_pages * c.num_kv_heads * 2 * sizeof(float), 1024);
+        a.open_layer = align_up((size_t)c.max_seqs * tile * 2, 1024);
+    }
+    a.pool_off = 0;
+    a.scales_off = a.pool_off + a.pool_layer * c.num_layers;
+    a.open_off = a.scales_off + a.scales_layer * c.num_layers;
+    a.total = a.open_off + a.open_layer * c.num_layers;
+    return a;
+}
+
+const char* validate(const tk_kv_config& c) {
+    if (c.num_layers <= 0 || c.num_heads <= 0 || c.num_kv_heads <= 0) return "layers/heads must be positive";
+    if (c.num_heads % c.num_kv_heads != 0) return "num_heads must be a multiple of num_kv_heads";
+    const int G = c.num_heads / c.num_kv_heads;
+    if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return "heads per kv head must be 1, 2, 4, 8 or 16";
+    if (c.head_dim != 64 && c.head_dim != 128) return "head_dim must be 64 or 128";
+    if (c.page_size <= 0 || c.page_size % 8 != 0) return "page_size must be a positive multiple of 8";
+    if (c.dtype != TK_FP16 && c.dtype != TK_BF16 && c.dtype != TK_FP8_E4M3) return "dtype must be FP16, BF16 or FP8_E4M3";
+    if (c.io_dtype != TK_FP16 && c.io_dtype != TK_BF16) return "io_dtype must be FP16 or BF16";
+    if (c.dtype != TK_FP8_E4M3 && c.io_dtype != c.dtype) return "io_dtype must equal dtype for 16-bit storage";
+    if (c.num_pages <= 0 || c.max_seqs <= 0 || c.max_pages_per_seq <= 0) return "num_pages/max_seqs/max_pages_per_seq must be positive";
+    if ((int64_t)c.max_seqs * c.max_pages_per_seq > (int64_t)1 << 30) return "page table too large";
+    if (c.max_step_tokens <= 0) return "max_step_tokens must be positive";
+    if (c.chunk_tokens < 0 || c.chunk_tokens % c.page_size != 0) return "chunk_tokens must be a multiple of page_size";
+    if (c.decode_impl < TK_DECODE_AUTO || c.decode_impl > TK_DECODE_MMA) return "bad decode_impl";
+    return nullptr;
+}
+
+}  // namespace
+
+struct tk_kv {
+    tk_kv_config cfg{};
+    tk::Geometry geo{};
+    tk::PageManager* mgr = nullptr;
+    bool host_only = false;
+    int device = 0, num_sms = 148;
+    bool use_mma = false;
+
+    uint8_t* arena = nullptr;
+    bool owns_arena = false;
+    ArenaLayout lay{};
+
+    int32_t* d_table = nullptr;
+    float* d_partials = nullptr;
+    int max_partial_rows = 0, max_items = 0, max_seals = 0;
+    int* d_status = nullptr;
+
+    size_t step_bytes = 0;
+    uint8_t* d_step = nullptr;
+    uint8_t* h_step[kRing] = {};
+    cudaEvent_t ev[kRing] = {};
+    bool ev_pending[kRing] = {};
+    int ring_pos = 0;
+
+    // staging for the *_host entry point
+    void *d_k = nullptr, *d_v = nullptr, *d_q = nullptr, *d_out = nullptr;
+
+    std::vector<CUtensorMap> maps;       // one per layer (MMA path)
+
+    tk::StepPlan plan;
+    tk::StepDev dev{};
+    bool have_step = false;
+    int n_pool_items = 0;                // items of kind 0 come first
+
+    tk_kv_stats stats{};
+    int64_t launches = 0;
+    std::string err;
+
+    tk::LayerPtrs layer(int l) const {
+        tk::LayerPtrs p{};
+        p.pool = arena + lay.pool_off + lay.pool_layer * l;
+        p.scales = lay.scales_layer ? (float*)(arena + lay.scales_off + lay.scales_layer * l) : nullptr;
+        p.open_pages = lay.open_layer ? (void*)(arena + lay.open_off + lay.open_layer * l) : nullptr;
+        return p;
+    }
+};
+
+namespace {
+
+int fail(tk_kv* h, int status, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (h) h->err = buf; else g_create_error = buf;
+    return status;
+}
+
+#define TK_CUDA(h, call)                                                                         \
+    do {                                                                                         \
+        cudaError_t e_ = (call);                                                                 \
+        if (e_ != cudaSuccess)                                                                   \
+            return fail(h, TK_CUDA_ERROR, "%s failed: %s", #call, cudaGetErrorString(e_));       \
+    } while (0)
+
+void release(tk_kv* h) {
+    if (!h) return;
+    if (!h->host_only) {
+        cudaSetDevice(h->device);
+        if (h->owns_arena && h->arena) cudaFree(h->arena);
+        if (h->d_table) cudaFree(h->d_table);
+        if (h->d_partials) cudaFree(h->d_partials);
+        if (h->d_status) cudaFree(h->d_status);
+        if (h->d_step) cudaFree(h->d_step);
+        if (h->d_k) cudaFree(h->d_k);
+        if (h->d_v) cudaFree(h->d_v);
+        if (h->d_q) cudaFree(h->d_q);
+        if (h->d_out) cudaFree(h->d_out);
+        for (int i = 0; i < kRing; i++) {
+            if (h->h_step[i]) cudaFreeHost(h->h_step[i]);
+            if (h->ev[i]) cudaEventDestroy(h->ev[i]);
+        }
+    }
+    delete h->mgr;
+    delete h;
+}
+
+int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, bool external, tk_kv** out) {
+    if (!cfg_in || !out) return fail(nullptr, TK_INVALID_ARG, "null argument");
+    *out = nullptr;
+    tk_kv_config c = *cfg_in;
+    if (c.io_dtype == 0) c.io_dtype = c.dtype == TK_FP8_E4M3 ? TK_BF16 : c.dtype;
+    if (c.max_step_tokens == 0) c.max_step_tokens = c.max_seqs;
+    if (const char* why = validate(c)) return fail(nullptr, TK_INVALID_ARG, "config: %s", why);
+
+    tk_kv* h = new (std::nothrow) tk_kv();
+    if (!h) return fail(nullptr, TK_INVALID_ARG, "out of host memory");
+    h->cfg = c;
+    h->geo = tk::Geometry{c.num_heads, c.num_kv_heads, c.head_dim, c.page_size, c.dtype, c.io_dtype,
+                          c.num_pages, c.max_seqs, c.max_pages_per_seq};
+    h->mgr = new tk::PageManager(c.num_pages, c.max_seqs, c.max_pages_per_seq, c.page_size);
+    h->lay = arena_layout(c);
+    h->host_only = c.device == TK_DEVICE_NONE;
+    h->stats.pages_total = c.num_pages;
+
+    const int min_chunk = c.chunk_tokens ? c.chunk_tokens : 128;
+    int64_t rows = ((int64_t)c.num_pages * c.page_size + min_chunk - 1) / min_chunk + 2 * (int64_t)c.max_seqs;
+    if (rows > (1 << 24)) rows = 1 << 24;
+    h->max_partial_rows = (int)rows;
+    h->max_items = h->max_partial_rows * c.num_kv_heads;
+    h->max_seals = c.max_step_tokens / c.page_size + c.max_seqs;
+
+    // one buffer holds every per-step array; sections are 16-byte aligned
+    size_t ints = 3 * (size_t)c.max_seqs + 4 + 8 + 2 * (size_t)c.max_step_tokens + 8 +
+                  4 * (size_t)h->max_items + 4 * (size_t)h->max_seals + 2 * (size_t)kMaxDelta + 32;
+    h->step_bytes = align_up(ints * 4, 256);
+
+    if (h->host_only) { *out = h; return TK_OK; }
+
+    if (c.device >= 0) h->device = c.device;
+    else if (cudaGetDevice(&h->device) != cudaSuccess) { release(h); return fail(nullptr, TK_CUDA_ERROR, "no CUDA device"); }
+#define CREATE_CUDA(call)                                                                        \
+    do {                                                                                         \
+        cudaError_t e_ = (call);                                                                 \
+        if (e_ != cudaSuccess) {                                                                 \
+            release(h);                                                                          \
+            return fail(nullptr, TK_CUDA_ERROR, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+        }                                                                                        \
+    } while (0)
+    CREATE_CUDA(cudaSetDevice(h->device));
+    cudaDeviceProp prop;
+    CREATE_CUDA(cudaGetDeviceProperties(&prop, h->device));
+    h->num_sms = prop.multiProcessorCount;
+    if (prop.major != 10) {
+        release(h);
+        return fail(nullptr, TK_UNSUPPORTED, "built for sm_100a only; device is sm_%d%d", prop.major, prop.minor);
+    }
+    if (external) {
+        if (!arena || arena_bytes < h->lay.total || ((uintptr_t)arena & 1023)) {
+            release(h);
+            return fail(nullptr, TK_INVALID_ARG, "external arena must be 1024-byte aligned and >= %zu bytes", h->lay.total);
+        }
+        h->arena = (uint8_t*)arena;
+    } else {
+        CREATE_CUDA(cudaMalloc((void**)&h->arena, h->lay.total));
+        h->owns_arena = true;
+    }
+    CREATE_CUDA(cudaMemset(h->arena, 0, h->lay.total));     // like KVCache::initialize, kv_cache.cpp:49-50
+    const size_t table_bytes = (size_t)c.max_seqs * c.max_pages_per_seq * sizeof(int32_t);
+    CREATE_CUDA(cudaMalloc((void**)&h->d_table, table_bytes));
+    CREATE_CUDA(cudaMemset(h->d_table, 0xFF, table_bytes));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_partials,
+                           (size_t)h->max_partial_rows * c.num_heads * (c.head_dim + 2) * sizeof(float)));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_status, 256));
+    CREATE_CUDA(cudaMemset(h->d_status, 0, 256));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_step, h->step_bytes));
+    for (int i = 0; i < kRing; i++) {
+        CREATE_CUDA(cudaHostAlloc((void**)&h->h_step[i], h->step_bytes, cudaHostAllocDefault));
+        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev[i], cudaEventDisableTiming));
+    }
+    const size_t kv_bytes = (size_t)c.max_step_tokens * c.num_kv_heads * c.head_dim * 2;
+    const size_t q_bytes = (size_t)c.max_seqs * c.num_heads * c.head_dim * 2;
+    CREATE_CUDA(cudaMalloc(&h->d_k, kv_bytes));
+    CREATE_CUDA(cudaMalloc(&h->d_v, kv_bytes));
+    CREATE_CUDA(cudaMalloc(&h->d_q, q_bytes));
+    CREATE_CUDA(cudaMalloc(&h->d_out, q_bytes));
+
+    const bool mma_ok = tk::decode_mma_supported(h->geo);
+    if (c.decode_impl == TK_DECODE_MMA && !mma_ok) {
+        release(h);
+        return fail(nullptr, TK_UNSUPPORTED, "decode_impl=MMA needs page_size 16 and head_dim 64/128 (128 for FP8)");
+    }
+    h->use_mma = mma_ok && c.decode_impl != TK_DECODE_SIMT;
+    if (h->use_mma) {
+        h->maps.resize(c.num_layers);
+        for (int l = 0; l < c.num_layers; l++) CREATE_CUDA(tk::make_pool_tensor_map(h->geo, h->layer(l).pool, &h->maps[l]));
+    }
+    CREATE_CUDA(cudaDeviceSynchronize());
+#undef CREATE_CUDA
+    *out = h;
+    return TK_OK;
+}
+
+struct Sections {       // offsets (in int32 units) of the arrays inside a step buffer
+    size_t seq, len, chunk_base, tok_b, tok_pos, items, seals, delta, end;
+};
+Sections sections(int n_seqs, int n_tokens, int n_items, int n_seals, int n_delta) {
+    auto a4 = [](size_t x) { return (x + 3) / 4 * 4; };
+    Sections s{};
+    size_t o = 0;
+    s.seq = o;        o = a4(o + n_seqs);
+    s.len = o;        o = a4(o + n_seqs);
+    s.chunk_base = o; o = a4(o + n_seqs + 1);
+    s.tok_b = o;      o = a4(o + n_tokens);
+    s.tok_pos = o;    o = a4(o + n_tokens);
+    s.items = o;      o = a4(o + 4 * (size_t)n_items);
+    s.seals = o;      o = a4(o + 4 * (size_t)n_seals);
+    s.delta = o;      o = a4(o + 2 * (size_t)n_delta);
+    s.end = o;
+    return s;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* tk_status_str(int s) {
+    switch (s) {
+        case TK_OK: return "ok";
+        case TK_INVALID_ARG: return "invalid argument";
+        case TK_OUT_OF_PAGES: return "out of pages";
+        case TK_CUDA_ERROR: return "CUDA error";
+        case TK_TIMEOUT: return "device wait timed out";
+        case TK_OUT_OF_SEQS: return "out of sequence slots";
+        case TK_UNSUPPORTED: return "unsupported";
+        default: return "unknown status";
+    }
+}
+
+const char* tk_kv_last_error(const tk_kv* h) { return h ? h->err.c_str() : g_create_error.c_str(); }
+
+void tk_kv_config_default(tk_kv_config* c) {
+    if (!c) return;
+    memset(c, 0, sizeof(*c));
+    c->page_size = 16;
+    c->dtype = TK_BF16;
+    c->device = -1;
+}
+
+size_t tk_kv_arena_bytes(const tk_kv_config* cfg) {
+    if (!cfg) return 0;
+    tk_kv_config c = *cfg;
+    if (c.io_dtype == 0) c.io_dtype = c.dtype == TK_FP8_E4M3 ? TK_BF16 : c.dtype;
+    if (c.max_step_tokens == 0) c.max_step_tokens = c.max_seqs;
+    if (validate(c)) return 0;
+    return arena_layout(c).total;
+}
+
+int tk_kv_create(const tk_kv_config* cfg, tk_kv** out) { return create_impl(cfg, nullptr, 0, false, out); }
+int tk_kv_create_external(const tk_kv_config* cfg, void* arena, size_t bytes, tk_kv** out) {
+    return create_impl(cfg, arena, bytes, true, out);
+}
+int tk_kv_destroy(tk_kv* h) {
+    if (!h) return TK_INVALID_ARG;
+    if (!h->host_only) { cudaSetDevice(h->device); cudaDeviceSynchronize(); }
+    release(h);
+    return TK_OK;
+}
+int tk_kv_get_config(const tk_kv* h, tk_kv_config* out) {
+    if (!h || !out) return TK_INVALID_ARG;
+    *out = h->cfg;
+    return TK_OK;
+}
+size_t tk_kv_memory_bytes(const tk_kv* h) { return h ? h->lay.total : 0; }
+
+int tk_kv_layer_ptrs(const tk_kv* h, int layer, void** pool, float** scales, void** open_pages) {
+    if (!h || layer < 0 || layer >= h->cfg.num_layers || h->host_only) return TK_INVALID_ARG;
+    tk::LayerPtrs p = h->layer(layer);
+    if (pool) *pool = p.pool;
+    if (scales) *scales = p.scales;
+    if (open_pages) *open_pages = p.open_pages;
+    return TK_OK;
+}
+
+// ---- sequences and pages -------------------------------------------------------------
+int tk_kv_seq_alloc(tk_kv* h, int32_t* seq_out) {
+    if (!h || !seq_out) return TK_INVALID_ARG;
+    int s = h->mgr->seq_alloc();
+    if (s < 0) return fail(h, TK_OUT_OF_SEQS, "all %d sequence slots are in use", h->cfg.max_seqs);
+    *seq_out = s;
+    return TK_OK;
+}
+int tk_kv_seq_free(tk_kv* h, int32_t seq) {
+    if (!h) return TK_INVALID_ARG;
+    int st = h->mgr->seq_free(seq);
+    return st == TK_OK ? TK_OK : fail(h, st, "seq_free(%d): sequence is not live", seq);
+}
+int tk_kv_reserve(tk_kv* h, int32_t seq, int32_t n) {
+    if (!h) return TK_INVALID_ARG;
+    int st = h->mgr->reserve(seq, n);
+    return st == TK_OK ? TK_OK : fail(h, st, "reserve(%d, %d): %s", seq, n, tk_status_str(st));
+}
+int tk_kv_truncate(tk_kv* h, int32_t seq, int32_t new_len) {
+    if (!h) return TK_INVALID_ARG;
+    if (h->cfg.dtype == TK_FP8_E4M3 && h->mgr->live(seq) && new_len % h->cfg.page_size != 0 &&
+        new_len / h->cfg.page_size < h->mgr->seq_len(seq) / h->cfg.page_size)
+        return fail(h, TK_UNSUPPORTED, "FP8: cannot truncate into a sealed page (length must stay page-aligned there)");
+    int st = h->mgr->truncate(seq, new_len);
+    return st == TK_OK ? TK_OK : fail(h, st, "truncate(%d, %d): %s", seq, new_len, tk_status_str(st));
+}
+int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t seq_len) {
+    if (!h || (n_pages > 0 && !pages)) return TK_INVALID_ARG;
+    if (h->cfg.dtype == TK_FP8_E4M3 && seq_len % h->cfg.page_size != 0)
+        return fail(h, TK_UNSUPPORTED, "FP8: adopted length must be page-aligned (no open page to adopt)");
+    int st = h->mgr->adopt(seq, pages, n_pages, seq_len);
+    return st == TK_OK ? TK_OK : fail(h, st, "seq_adopt(%d): pages must be distinct, in range and free", seq);
+}
+int tk_kv_seq_len(const tk_kv* h, int32_t seq) { return h ? h->mgr->seq_len(seq) : -1; }
+int tk_kv_num_free_pages(const tk_kv* h) { return h ? h->mgr->num_free_pages() : -1; }
+int tk_kv_page_table(const tk_kv* h, int32_t seq, int32_t* out, int32_t cap, int32_t* n_out) {
+    if (!h || !h->mgr->live(seq)) return TK_INVALID_ARG;
+    int n = h->mgr->seq_pages(seq);
+    if (n_out) *n_out = n;
+    if (out) {
+        if (cap < n) return TK_INVALID_ARG;
+        memcpy(out, h->mgr->row(seq), sizeof(int32_t) * (size_t)n);
+    }
+    return TK_OK;
+}
+int64_t tk_kv_slot(const tk_kv* h, int32_t seq, int32_t pos) { return h ? h->mgr->slot(seq, pos) : -1; }
+uint64_t tk_kv_state_digest(const tk_kv* h) { return h ? h->mgr->digest() : 0; }
+int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out) {
+    if (!h || !out) return TK_INVALID_ARG;
+    *out = h->stats;
+    out->pages_free = h->mgr->num_free_pages();
+    out->page_allocs = h->mgr->counters.page_allocs;
+    out->page_frees = h->mgr->counters.page_frees;
+    out->seq_allocs = h->mgr->counters.seq_allocs;
+    out->seq_frees = h->mgr->counters.seq_frees;
+    return TK_OK;
+}
+
+// ---- step ----------------------------------------------------------------------------------
+int tk_kv_step_begin(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new, void* stream) {
+    if (!h) return TK_INVALID_ARG;
+    h->have_step = false;
+    const char* env_chunk = getenv("TK_CHUNK_TOKENS");
+    int chunk = h->cfg.chunk_tokens;
+    if (chunk == 0 && env_chunk) chunk = atoi(env_chunk);
+    const char* env_target = getenv("TK_TARGET_ITEMS");
+    int target = env_target ? atoi(env_target) : 24 * h->num_sms;
+    // the tensor-core kernel keeps one page id per lane per warp: chunk <= 16*4*32 tokens
+    int st = h->mgr->plan_step(n_seqs, seq_ids, n_new, h->cfg.num_kv_heads, h->cfg.dtype == TK_FP8_E4M3,
+                               chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan);
+    if (st != TK_OK) return fail(h, st, "step_begin: %s", tk_status_str(st));
+    tk::StepPlan& p = h->plan;
+    if (chunk == 0 && p.chunk_tokens > 2048) {
+        return fail(h, TK_INVALID_ARG, "internal: chunk %d too large", p.chunk_tokens);
+    }
+    // kind-0 items first (already size-sorted), FP8 open-page items after them
+    std::stable_partition(p.items.begin(), p.items.end(), [](const tk::WorkItem& w) { return w.kind == 0; });
+    h->n_pool_items = 0;
+    for (const auto& w : p.items) h->n_pool_items += w.kind == 0;
+
+    h->stats.steps++;
+    h->stats.tokens_appended += (int64_t)p.tok_b.size();
+    h->stats.pages_sealed += (int64_t)p.seals.size();
+    if (h->host_only) { h->mgr->delta().clear(); h->have_step = true; return TK_OK; }
+
+    cudaStream_t s = (cudaStream_t)stream;
+    TK_CUDA(h, cudaSetDevice(h->device));
+    auto& delta = h->mgr->delta();
+    int n_delta = (int)delta.size();
+    if (n_delta > kMaxDelta) {
+        // rare (bulk adopt / huge prefill): copy the whole table from pageable memory
+        TK_CUDA(h, cudaMemcpyAsync(h->d_table, h->mgr->page_table(),
+                                   (size_t)h->cfg.max_seqs * h->cfg.max_pages_per_seq * sizeof(int32_t),
+                                   cudaMemcpyHostToDevice, s));
+        TK_CUDA(h, cudaStreamSynchronize(s));
+        h->stats.bytes_h2d += (int64_t)h->cfg.max_seqs * h->cfg.max_pages_per_seq * 4;
+        delta.clear();
+        n_delta = 0;
+    }
+    const int n_tok = (int)p.tok_b.size(), n_items = (int)p.items.size(), n_seals = (int)p.seals.size();
+    if (n_items > h->max_items || n_seals > h->max_seals)
+        return fail(h, TK_INVALID_ARG, "step_begin: work list exceeds the workspace (%d items, %d seals)", n_items, n_seals);
+    Sections sec = sections(n_seqs, n_tok, n_items, n_seals, n_delta);
+    if (sec.end * 4 > h->step_bytes) return fail(h, TK_INVALID_ARG, "step_begin: step metadata exceeds its buffer");
+
+    const int r = h->ring_pos;
+    h->ring_pos = (r + 1) % kRing;
+    if (h->ev_pending[r]) { TK_CUDA(h, cudaEventSynchronize(h->ev[r])); h->ev_pending[r] = false; }
+    int32_t* w = (int32_t*)h->h_step[r];
+    if (n_seqs) {
+        memcpy(w + sec.seq, p.seq.data(), 4 * (size_t)n_seqs);
+        memcpy(w + sec.len, p.len.data(), 4 * (size_t)n_seqs);
+    }
+    memcpy(w + sec.chunk_base, p.chunk_base.data(), 4 * (size_t)(n_seqs + 1));
+    if (n_tok) {
+        memcpy(w + sec.tok_b, p.tok_b.data(), 4 * (size_t)n_tok);
+        memcpy(w + sec.tok_pos, p.tok_pos.data(), 4 * (size_t)n_tok);
+    }
+    if (n_items) memcpy(w + sec.items, p.items.data(), 16 * (size_t)n_items);
+    if (n_seals) memcpy(w + sec.seals, p.seals.data(), 16 * (size_t)n_seals);
+    for (int i = 0; i < n_delta; i++) { w[sec.delta + 2 * i] = delta[i].first; w[sec.delta + 2 * i + 1] = delta[i].second; }
+    delta.clear();
+    TK_CUDA(h, cudaMemcpyAsync(h->d_step, w, sec.end * 4, cudaMemcpyHostToDevice, s));
+    TK_CUDA(h, cudaEventRecord(h->ev[r], s));
+    h->ev_pending[r] = true;
+    h->stats.bytes_h2d += (int64_t)sec.end * 4;
+
+    const int32_t* d = (const int32_t*)h->d_step;
+    tk::StepDev& dv = h->dev;
+    dv.seq = d + sec.seq; dv.len = d + sec.len; dv.chunk_base = d + sec.chunk_base;
+    dv.tok_b = d + sec.tok_b; dv.tok_pos = d + sec.tok_pos;
+    dv.items = (const int4*)(d + sec.items); dv.seals = (const int4*)(d + sec.seals);
+    dv.n_seqs = n_seqs; dv.n_tokens = n_tok; dv.n_items = n_items; dv.n_seals = n_seals;
+    dv.chunk_tokens = p.chunk_tokens;
+    if (n_delta) {
+        TK_CUDA(h, tk::launch_apply_delta(h->d_table, (const int2*)(d + sec.delta), n_delta, s));
+        h->launches++;
+    }
+    h->have_step = true;
+    return TK_OK;
+}
+
+int tk_kv_step_num_tokens(const tk_kv* h) { return h && h->have_step ? (int)h->plan.tok_b.size() : -1; }
+int tk_kv_step_num_work_items(const tk_kv* h) { return h && h->have_step ? (int)h->plan.items.size() : -1; }
+int tk_kv_step_chunk_tokens(const tk_kv* h) { return h && h->have_step ? h->plan.chunk_tokens : -1; }
+
+int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t* slots_out, void* stream) {
+    if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (h->host_only) return fail(h, TK_CUDA_ERROR, "append: handle has no device (bookkeeping only)");
+    if (!h->have_step) return fail(h, TK_INVALID_ARG, "append: no step in progress (call tk_kv_step_begin)");
+    if (h->dev.n_tokens == 0) return TK_OK;
+    if (!k || !v) return fail(h, TK_INVALID_ARG, "append: null k/v");
+    int n = 0;
+    cudaError_t e = tk::launch_append(h->geo, h->layer(layer), h->dev, h->d_table, k, v, slots_out,
+                                      (cudaStream_t)stream, &n);
+    h->launches += n;
+    if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "append launch: %s", cudaGetErrorString(e));
+    return TK_OK;
+}
+
+static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* partial_out, cudaStream_t s) {
+    if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode: handle has no device (bookkeeping only)");
+    if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode: no step in progress (call tk_kv_step_begin)");
+    if (h->dev.n_seqs == 0) return TK_OK;
+    if (!q || (!out && !partial_out)) return fail(h, TK_INVALID_ARG, "decode: null q/out");
+    const tk::LayerPtrs lp = h->layer(layer);
+    cudaError_t e = cudaSuccess;
+    const bool mma = h->use_mma && h->dev.chunk_tokens <= 2048;
+    if (mma) {
+        tk::StepDev pool = h->dev;
+        pool.n_items = h->n_pool_items;
+        if (pool.n_items > 0) {
+            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], pool, h->d_table, q, h->d_partials, h->d_status, s);
+            h->launches++;
+        }
+        if (e == cudaSuccess && h->dev.n_items > h->n_pool_items) {      // FP8 open pages: 16-bit tail
+            tk::StepDev open = h->dev;
+            open.items = h->dev.items + h->n_pool_items;
+            open.n_items = h->dev.n_items - h->n_pool_items;
+            e = tk::launch_decode_simt(h->geo, lp, open, h->d_table, q, h->d_partials, s);
+            h->launches++;
+        }
+    } else if (h->dev.n_items > 0) {
+        e = tk::launch_decode_simt(h->geo, lp, h->dev, h->d_table, q, h->d_partials, s);
+        h->launches++;
+    }
+    if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode launch: %s", cudaGetErrorString(e));
+    e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, h->cfg.io_dtype, partial_out, s);
+    h->launches++;
+    if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "combine launch: %s", cudaGetErrorString(e));
+    return TK_OK;
+}
+
+int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream) {
+    return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream);
+}
+int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial, void* stream) {
+    return decode_impl(h, layer, q, nullptr, partial, (cudaStream_t)stream);
+}
+
+int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int32_t head_dim, void* out,
+                        int32_t out_dtype, void* stream) {
+    if (!parts || !out || n_parts <= 0 || n_rows < 0 || head_dim <= 0) return TK_INVALID_ARG;
+    if (out_dtype != TK_FP32 && out_dtype != TK_FP16 && out_dtype != TK_BF16) return TK_INVALID_ARG;
+    cudaError_t e = tk::launch_combine_parts(parts, n_parts, n_rows, head_dim, out, out_dtype, (cudaStream_t)stream);
+    return e == cudaSuccess ? TK_OK : TK_CUDA_ERROR;
+}
+
+int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
+                             const void* q_host, void* out_host, void* stream) {
+    if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (h->host_only) return fail(h, TK_CUDA_ERROR, "append_decode_host: handle has no device");
+    if (!h->have_step) return fail(h, TK_INVALID_ARG, "append_decode_host: no step in progress");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t kv_bytes = (size_t)h->dev.n_tokens * h->cfg.num_kv_heads * h->cfg.head_dim * 2;
+    const size_t q_bytes = (size_t)h->dev.n_seqs * h->cfg.num_heads * h->cfg.head_dim * 2;
+    if (kv_bytes) {
+        if (!k_host || !v_host) return fail(h, TK_INVALID_ARG, "append_decode_host: null k/v");
+        TK_CUDA(h, cudaMemcpyAsync(h->d_k, k_host, kv_bytes, cudaMemcpyHostToDevice, s));
+        TK_CUDA(h, cudaMemcpyAsync(h->d_v, v_host, kv_bytes, cudaMemcpyHostToDevice, s));
+        int st = tk_kv_append(h, layer, h->d_k, h->d_v, nullptr, stream);
+        if (st != TK_OK) return st;
+        h->stats.bytes_h2d += 2 * (int64_t)kv_bytes;
+    }
+    if (q_bytes) {
+        if (!q_host || !out_host) return fail(h, TK_INVALID_ARG, "append_decode_host: null q/out");
+        TK_CUDA(h, cudaMemcpyAsync(h->d_q, q_host, q_bytes, cudaMemcpyHostToDevice, s));
+        int st = tk_kv_decode(h, layer, h->d_q, h->d_out, stream);
+        if (st != TK_OK) return st;
+        TK_CUDA(h, cudaMemcpyAsync(out_host, h->d_out, q_bytes, cudaMemcpyDeviceToHost, s));
+        h->stats.bytes_h2d += (int64_t)q_bytes;
+        h->stats.bytes_d2h += (int64_t)q_bytes;
+    }
+    TK_CUDA(h, cudaStreamSynchronize(s));
+    return TK_OK;
+}
+
+int tk_kv_device_status(tk_kv* h, void* stream) {
+    if (!h || h->host_only) return TK_INVALID_ARG;
+    int st = 0;
+    TK_CUDA(h, cudaMemcpyAsync(&st, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    TK_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream));
+    if (st != 0) {
+        cudaMemsetAsync(h->d_status, 0, sizeof(int), (cudaStream_t)stream);
+        return fail(h, st, "a device-side wait gave up (status %d)", st);
+    }
+    return TK_OK;
+}
+
+int64_t tk_kv_launch_count(const tk_kv* h) { return h ? h->launches : 0; }
+
+}  // extern "C"

@@ -1,0 +1,73 @@
+// tk_kernels.cuh — device-side views and launcher declarations shared by the
+// kernels of the paged KV-cache path and the C ABI (titan_kv.cu).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace tk {
+
+// Storage numbering = titan::DType (reference: src/core/types.h:17-21).
+enum : int { DT_FP32 = 0, DT_FP16 = 1, DT_BF16 = 2, DT_FP8 = 3 };
+
+struct Geometry {
+    int H, Hkv, D, ps;          // query heads, kv heads, head dim, tokens per page
+    int dtype, io_dtype;        // storage type; type of q/k/v/out and of FP8 open pages
+    int num_pages, max_seqs, max_pages_per_seq;
+};
+
+// One layer of the pool.  16-bit / FP8 codes: [num_pages][Hkv][2 (K,V)][ps][D];
+// scales f32 [num_pages][Hkv][2]; open pages [max_seqs][Hkv][2][ps][D] in io_dtype.
+struct LayerPtrs {
+    void*  pool;
+    float* scales;
+    void*  open_pages;
+};
+
+// Device view of one step's metadata (all arrays live in one uploaded buffer).
+struct StepDev {
+    const int32_t* seq;         // [n_seqs] sequence slot
+    const int32_t* len;         // [n_seqs] length after this step's appends
+    const int32_t* chunk_base;  // [n_seqs+1] first partial row of each sequence
+    const int32_t* tok_b;       // [n_tokens] index into seq[]
+    const int32_t* tok_pos;     // [n_tokens]
+    const int4*    items;       // [n_items] (b, chunk, kvh, kind)
+    const int4*    seals;       // [n_seals] (b, logical page, old_len, tok_base)
+    int n_seqs, n_tokens, n_items, n_seals, chunk_tokens;
+};
+
+// partial row layout: [row][H][D+2] f32 = o[0..D) unnormalised, m at [D], l at [D+1]
+__host__ __device__ inline size_t partial_off(int row, int h, int H, int D) {
+    return ((size_t)row * H + h) * (size_t)(D + 2);
+}
+
+cudaError_t launch_apply_delta(int32_t* table, const int2* delta, int n, cudaStream_t s);
+
+cudaError_t launch_append(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
+                          const int32_t* page_table, const void* k, const void* v,
+                          int64_t* slots_out, cudaStream_t s, int* n_launches);
+
+// Generic SIMT decode: one CTA per work item, any supported shape.  Returns
+// cudaErrorNotSupported for shapes it has no instantiation for.
+cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
+                               const int32_t* page_table, const void* q, float* partials,
+                               cudaStream_t s);
+
+// TMA + mma.sync decode (16-bit and FP8 pools, page size 16, D in {64,128}).
+bool        decode_mma_supported(const Geometry& g);
+cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out);
+cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
+                              const StepDev& st, const int32_t* page_table, const void* q,
+                              float* partials, int* status, cudaStream_t s);
+
+// LSE merge over each sequence's partial rows.
+//   out != null     : normalised [n_seqs][H][D] in out_dtype
+//   partial_out!=null: merged but unnormalised [n_seqs][H][D+2]
+cudaError_t launch_combine_step(const Geometry& g, const StepDev& st, const float* partials,
+                                void* out, int out_dtype, float* partial_out, cudaStream_t s);
+// LSE merge of n_parts stacked partial sets [n_parts][n_rows][D+2] -> out [n_rows][D].
+cudaError_t launch_combine_parts(const float* parts, int n_parts, int n_rows, int D, void* out,
+                                 int out_dtype, cudaStream_t s);
+
+}  // namespace tk
