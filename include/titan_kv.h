@@ -160,6 +160,19 @@ int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int
 int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
                              const void* q_host, void* out_host, void* stream);
 
+/* Same without the final wait: the caller synchronises `stream` before reading out_host;
+ * the host buffers must be pinned and stay untouched until then. */
+int tk_kv_append_decode_host_async(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
+                                   const void* q_host, void* out_host, void* stream);
+
+/* Timing of the dominant decode kernel on its own stream: after enable(n), each of the next
+ * n tk_kv_decode calls brackets its main attention kernel with a CUDA event pair;
+ * read() waits for them and returns the summed kernel time and the number of launches.
+ * enable(0) turns it off.  (The reference times only with std::chrono around whole
+ * phases, src/inference/engine.cpp:179-201.) */
+int tk_kv_profile_enable(tk_kv* h, int32_t max_launches);
+int tk_kv_profile_read(tk_kv* h, double* total_ms, int64_t* launches);
+
 /* Reads the device status word after draining `stream`: TK_OK, or TK_TIMEOUT when a
  * bounded device-side wait gave up (the word is cleared). */
 int tk_kv_device_status(tk_kv* h, void* stream);

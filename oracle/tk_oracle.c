@@ -242,6 +242,27 @@ int tko_truncate(tko_mgr* m, int seq, int new_len) {
     m->seq_pages[seq] = keep; m->seq_len[seq] = new_len;
     return TKO_OK;
 }
+/* Install a caller-chosen page list on an empty live sequence; the pages leave the free
+ * stack, whose remaining order is kept. */
+int tko_adopt(tko_mgr* m, int seq, const int32_t* pages, int n_pages, int seq_len) {
+    if (!live(m, seq) || m->seq_pages[seq] != 0 || n_pages < 0 || n_pages > m->max_pages_per_seq) return TKO_INVALID_ARG;
+    if (seq_len < 0 || (seq_len + m->page_size - 1) / m->page_size != n_pages) return TKO_INVALID_ARG;
+    uint8_t* want = (uint8_t*)calloc((size_t)m->num_pages, 1);
+    int ok = 1, found = 0;
+    for (int i = 0; i < n_pages && ok; i++) {
+        if (pages[i] < 0 || pages[i] >= m->num_pages || want[pages[i]]) ok = 0; else want[pages[i]] = 1;
+    }
+    for (int i = 0; i < m->free_top && ok; i++) found += want[m->free_stack[i]];
+    if (!ok || found != n_pages) { free(want); return TKO_INVALID_ARG; }
+    int w = 0;
+    for (int i = 0; i < m->free_top; i++) if (!want[m->free_stack[i]]) m->free_stack[w++] = m->free_stack[i];
+    m->free_top = w;
+    int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
+    for (int i = 0; i < n_pages; i++) row[i] = pages[i];
+    m->seq_pages[seq] = n_pages; m->seq_len[seq] = seq_len;
+    free(want);
+    return TKO_OK;
+}
 int tko_seq_len(const tko_mgr* m, int seq) { return live(m, seq) ? m->seq_len[seq] : -1; }
 int tko_seq_num_pages(const tko_mgr* m, int seq) { return live(m, seq) ? m->seq_pages[seq] : -1; }
 int tko_num_free_pages(const tko_mgr* m) { return m->free_top; }

@@ -59,6 +59,7 @@ int      tko_seq_alloc(tko_mgr* m);                    /* lowest free slot, or -
 int      tko_seq_free(tko_mgr* m, int seq);
 int      tko_reserve(tko_mgr* m, int seq, int n_tokens);
 int      tko_truncate(tko_mgr* m, int seq, int new_len);
+int      tko_adopt(tko_mgr* m, int seq, const int32_t* pages, int n_pages, int seq_len);
 int      tko_seq_len(const tko_mgr* m, int seq);       /* -1 if seq not live */
 int      tko_seq_num_pages(const tko_mgr* m, int seq);
 int      tko_num_free_pages(const tko_mgr* m);

@@ -56,6 +56,7 @@ def lib() -> C.CDLL:
             "tko_seq_free": (i, [vp, i]),
             "tko_reserve": (i, [vp, i, i]),
             "tko_truncate": (i, [vp, i, i]),
+            "tko_adopt": (i, [vp, i, vp, i, i]),
             "tko_seq_len": (i, [vp, i]),
             "tko_seq_num_pages": (i, [vp, i]),
             "tko_num_free_pages": (i, [vp]),
@@ -149,6 +150,11 @@ class Manager:
     def seq_free(self, s): return self.l.tko_seq_free(self.h, s)
     def reserve(self, s, n): return self.l.tko_reserve(self.h, s, n)
     def truncate(self, s, n): return self.l.tko_truncate(self.h, s, n)
+
+    def adopt(self, s, pages, seq_len):
+        p = _c(pages, np.int32)
+        return self.l.tko_adopt(self.h, s, _p(p), len(p), seq_len)
+
     def seq_len(self, s): return self.l.tko_seq_len(self.h, s)
     def num_free_pages(self): return self.l.tko_num_free_pages(self.h)
     def slot(self, s, pos): return self.l.tko_slot(self.h, s, pos)

@@ -45,3 +45,99 @@ def assert_close(got: np.ndarray, want: np.ndarray, what: str = "", rtol: float 
         raise AssertionError(f"{what}: {bad.sum()} of {bad.size} outside rtol={rtol} atol={atol}; "
                              f"worst at {i}: got {got[i]:.6f} want {want[i]:.6f}; max abs err {err.max():.3e}")
     assert np.abs(got).max() > 0 or np.abs(want).max() == 0, f"{what}: result is all zero"
+
+
+class Twin:
+    """A GPU cache and the CPU oracle driven by the same calls, compared after every step.
+
+    Page tables / slot indices / pool bytes / FP8 codes and scales: bit-exact.
+    Attention outputs: within RTOL/ATOL of the oracle's FP32 result.
+    """
+
+    def __init__(self, L, H, Hkv, D, num_pages, max_seqs, mpps, dtype="bf16", impl="auto",
+                 chunk_tokens=0, max_step_tokens=4096, io=None, seed=0):
+        import torch
+        from titan_engine_b200 import PagedKVCache
+        self.torch = torch
+        self.L, self.H, self.Hkv, self.D, self.ps = L, H, Hkv, D, 16
+        self.dt = DT[dtype]
+        self.carrier = DT[io] if io else (O.BF16 if self.dt == O.FP8 else self.dt)
+        self.gpu = PagedKVCache(L, H, Hkv, D, num_pages, max_seqs, mpps, dtype=dtype, io_dtype=io,
+                                decode_impl=impl, chunk_tokens=chunk_tokens, max_step_tokens=max_step_tokens)
+        self.mgr = O.Manager(num_pages, max_seqs, mpps, 16)
+        self.pools = [O.Pool(self.dt, num_pages, H, Hkv, D, max_seqs, mpps, 16, self.carrier) for _ in range(L)]
+        self.g = rng(seed)
+        self.dev = self.gpu.device
+        self.max_err = 0.0
+
+    def seq_alloc(self):
+        a, b = self.gpu.seq_alloc(), self.mgr.seq_alloc()
+        assert a == b
+        return a
+
+    def seq_free(self, s):
+        self.gpu.seq_free(s)
+        assert self.mgr.seq_free(s) == O.OK
+
+    def adopt(self, s, pages, seq_len):
+        """Install a caller-chosen page list (a shuffled pool) on both sides."""
+        self.gpu.adopt(s, pages, seq_len)
+        assert self.mgr.adopt(s, pages, seq_len) == O.OK
+
+    def step(self, seq_ids, n_new, check_pool=False, decode=True, outlier_p=0.0, host_api=False):
+        torch = self.torch
+        n_new = [0] * len(seq_ids) if n_new is None else list(n_new)
+        old = [self.gpu.seq_len(s) for s in seq_ids]
+        self.gpu.step_begin(seq_ids, n_new)
+        for s, n in zip(seq_ids, n_new):
+            assert self.mgr.reserve(s, n) == O.OK
+        assert self.gpu.digest() == self.mgr.digest(), "page/slot state diverged from the oracle"
+        table = self.mgr.table()
+        tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seq_ids, n_new)] or [np.zeros(0, np.int32)])
+        tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)] or [np.zeros(0, np.int32)])
+        nt = len(tok_seq)
+        lens = [self.gpu.seq_len(s) for s in seq_ids]
+        outs = []
+        for layer in range(self.L):
+            k16 = normal16(self.g, (nt, self.Hkv, self.D), self.carrier, outlier_p)
+            v16 = normal16(self.g, (nt, self.Hkv, self.D), self.carrier, outlier_p)
+            q16 = normal16(self.g, (len(seq_ids), self.H, self.D), self.carrier)
+            want_slots = self.pools[layer].append(table, tok_seq, tok_pos, k16, v16)
+            if host_api:
+                kt, vt, qt = (to_torch16(x, self.carrier).pin_memory() for x in (k16, v16, q16))
+                out_h = torch.empty_like(qt).pin_memory()
+                self.gpu.append_decode_host(layer, kt, vt, qt, out_h)
+                got = out_h.to(torch.float32).numpy()
+            else:
+                slots = torch.full((max(nt, 1),), -7, dtype=torch.int64, device=self.dev)
+                if nt:
+                    self.gpu.append(layer, to_torch16(k16, self.carrier, self.dev), to_torch16(v16, self.carrier, self.dev), slots)
+                    np.testing.assert_array_equal(slots[:nt].cpu().numpy(), want_slots)
+                got = None
+                if decode:
+                    got = self.gpu.decode(layer, to_torch16(q16, self.carrier, self.dev)).to(torch.float32).cpu().numpy()
+            if check_pool:
+                self.check_pool(layer)
+            if decode or host_api:
+                want = self.pools[layer].decode(table, seq_ids, lens, q16)
+                assert_close(got, want, f"layer {layer} attention ({len(seq_ids)} seqs, lens {lens[:4]}...)")
+                self.max_err = max(self.max_err, float(np.abs(got - want).max()))
+                outs.append(got)
+        self.gpu.device_status()
+        return outs
+
+    def check_pool(self, layer):
+        pool, scales, open_pages = self.gpu.layer_views(layer)
+        o = self.pools[layer]
+        if self.dt == O.FP8:
+            np.testing.assert_array_equal(pool.cpu().numpy(), o.pool, err_msg="FP8 codes differ")
+            np.testing.assert_array_equal(scales.cpu().numpy().view(np.uint32), o.scales.view(np.uint32),
+                                          err_msg="FP8 scales differ")
+            # open pages: only rows below each live sequence's length are defined
+            got_open = from_torch16(open_pages)
+            for s in range(o.max_seqs):
+                n = self.mgr.seq_len(s)
+                if n > 0 and n % 16:
+                    np.testing.assert_array_equal(got_open[s, :, :, :n % 16], o.open_pages[s, :, :, :n % 16])
+        else:
+            np.testing.assert_array_equal(from_torch16(pool), o.pool, err_msg="pool bytes differ")

@@ -1,0 +1,227 @@
+"""GPU parity tests of the paged KV path through the C ABI, against the CPU oracle.
+
+Bit-exact: page tables, slot indices, pool bytes, FP8 codes and scales.
+Attention outputs (fp16/bf16): within 2e-3 relative / 1e-2 absolute of the oracle.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import DT, Twin, assert_close, from_torch16, normal16, rng, to_torch16
+from oracle import tk_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+IMPLS = ["simt", "mma"]
+
+
+@pytest.fixture(autouse=True)
+def _need_cuda():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    yield
+    torch.cuda.synchronize()
+
+
+# ---------------------------------------------------------------------------------------------
+# append: slots and pool bytes
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_append_scatter_bit_exact(dtype):
+    t = Twin(2, 8, 2, 64, 96, 4, 32, dtype=dtype, max_step_tokens=1024, seed=21)
+    a, b, c = t.seq_alloc(), t.seq_alloc(), t.seq_alloc()
+    t.step([a, b, c], [37, 1, 160], check_pool=True, decode=False)      # ragged prefill
+    t.step([a, b, c], [1, 1, 1], check_pool=True, decode=False)
+    t.seq_free(b)
+    d = t.seq_alloc()
+    t.step([c, d, a], [16, 33, 0], check_pool=True, decode=False)       # reuse of freed pages
+    t.step([], [], check_pool=True, decode=False)                        # empty step
+
+
+@pytest.mark.parametrize("io", ["bf16", "fp16"])
+def test_append_fp8_codes_and_scales_bit_exact(io):
+    t = Twin(2, 16, 2, 128, 64, 3, 24, dtype="fp8", io=io, max_step_tokens=1024, seed=22)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a, b], [70, 5], check_pool=True, decode=False, outlier_p=0.01)
+    t.step([a, b], [1, 11], check_pool=True, decode=False, outlier_p=0.01)   # b fills its first page exactly
+    t.step([a, b], [9, 40], check_pool=True, decode=False, outlier_p=0.01)   # a seals page 4 from open + new rows
+    for _ in range(18):
+        t.step([a, b], [1, 1], check_pool=True, decode=False, outlier_p=0.01)
+    assert t.gpu.stats()["pages_sealed"] > 8
+
+
+def test_fp8_all_zero_page_uses_clamped_scale():
+    t = Twin(1, 8, 1, 128, 8, 1, 8, dtype="fp8", max_step_tokens=64, seed=23)
+    s = t.seq_alloc()
+    t.gpu.step_begin([s], [16]); assert t.mgr.reserve(s, 16) == O.OK
+    z = np.zeros((16, 1, 128), dtype=np.uint16)
+    t.pools[0].append(t.mgr.table(), np.zeros(16, np.int32), np.arange(16, dtype=np.int32), z, z)
+    t.gpu.append(0, to_torch16(z, O.BF16, t.dev), to_torch16(z, O.BF16, t.dev))
+    t.check_pool(0)
+    _, scales, _ = t.gpu.layer_views(0)
+    assert scales[0, 0, 0].item() == np.float32(1e-10)
+
+
+# ---------------------------------------------------------------------------------------------
+# decode attention
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("n", [1, 15, 16, 17, 255, 256, 257])
+def test_decode_page_boundaries(impl, n):
+    t = Twin(1, 8, 2, 64, 40, 2, 20, dtype="fp16", impl=impl, chunk_tokens=128, max_step_tokens=512, seed=30 + n)
+    s = t.seq_alloc()
+    t.step([s], [n])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("shape", [
+    # H, Hkv, D, dtype
+    (8, 2, 64, "fp16"),      # tiny config
+    (32, 8, 128, "bf16"),    # 8B head shape
+    (32, 8, 128, "fp16"),
+    (4, 4, 128, "bf16"),     # MHA, G=1
+    (16, 1, 64, "bf16"),     # MQA, G=16
+    (16, 8, 64, "bf16"),     # G=2
+])
+def test_decode_shapes_ragged_batch(impl, shape):
+    H, Hkv, D, dtype = shape
+    t = Twin(2, H, Hkv, D, 400, 6, 80, dtype=dtype, impl=impl, max_step_tokens=4096, seed=40)
+    seqs = [t.seq_alloc() for _ in range(5)]
+    t.step(seqs, [1000, 3, 129, 512, 77])
+    t.step(seqs, [1, 1, 1, 1, 1])
+    t.step(seqs[1:4], None)                               # decode only, subset, no append
+    assert t.max_err > 0                                  # outputs are not trivially equal/zero
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("chunk", [16, 64, 0])
+def test_decode_split_kv_chunkings_agree(impl, chunk):
+    t = Twin(1, 32, 8, 128, 300, 3, 100, dtype="bf16", impl=impl, chunk_tokens=chunk, max_step_tokens=2048, seed=41)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a, b], [1500, 260])
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+@pytest.mark.parametrize("io", ["bf16", "fp16"])
+def test_decode_fp8(impl, io):
+    t = Twin(2, 64, 8, 128, 200, 4, 64, dtype="fp8", io=io, impl=impl, max_step_tokens=2048, seed=42)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [700, 16, 5], check_pool=True, outlier_p=0.01)       # sealed + open, exactly one page, open only
+    for _ in range(12):
+        t.step(seqs, [1, 1, 1], outlier_p=0.01)                       # crosses a seal for two sequences
+    t.check_pool(1)
+
+
+def test_decode_shuffled_pool_c2_style():
+    """Page tables as inputs: a seeded permutation of the pool, batch of ragged contexts."""
+    H, Hkv, D = 32, 8, 128
+    g = rng(2)
+    lens = g.integers(64, 700, size=12)
+    n_pages = int(sum((l + 15) // 16 for l in lens)) + 12
+    t = Twin(1, H, Hkv, D, n_pages, 12, 64, dtype="bf16", impl="mma", max_step_tokens=8192, seed=43)
+    perm = g.permutation(n_pages).astype(np.int32)
+    bits = normal16(g, t.pools[0].pool.shape, O.BF16)            # the pool arrives already filled
+    t.pools[0].pool[:] = bits
+    t.gpu.layer_views(0)[0].copy_(to_torch16(bits, O.BF16, t.dev))
+    seqs, at = [], 0
+    for l in lens:
+        s = t.seq_alloc()
+        npg = (int(l) + 15) // 16
+        t.adopt(s, perm[at:at + npg], int(l))
+        at += npg
+        seqs.append(s)
+    # one decode step per layer: append 1 token per sequence, then attention over everything
+    t.step(seqs, [1] * len(seqs), check_pool=True)
+    np.testing.assert_array_equal(t.gpu.page_table(seqs[0])[:3], perm[:3])
+
+
+def test_tiny_config_prefill_then_64_decode_steps():
+    """Tiny workload: 1 sequence, 8 q heads / 2 kv heads, D 64, 2 layers, fp16; 512-token prefill via
+    append, then 64 decode steps; pages come off the free list as 0,1,2,..."""
+    for impl in IMPLS:
+        t = Twin(2, 8, 2, 64, 40, 1, 40, dtype="fp16", impl=impl, max_step_tokens=512, seed=1)
+        s = t.seq_alloc()
+        t.step([s], [512], check_pool=True)
+        for _ in range(64):
+            t.step([s], [1])
+        np.testing.assert_array_equal(t.gpu.page_table(s), np.arange(36))
+        t.check_pool(0); t.check_pool(1)
+
+
+def test_known_answers_on_gpu():
+    """Closed-form cases straight through the CUDA path: equal keys -> mean of V; one token -> V."""
+    for impl in IMPLS:
+        t = Twin(1, 8, 2, 64, 8, 1, 8, dtype="fp16", impl=impl, max_step_tokens=128, seed=5)
+        s = t.seq_alloc()
+        n = 40
+        t.gpu.step_begin([s], [n])
+        g = rng(6)
+        k = np.repeat(normal16(g, (1, 2, 64), O.FP16), n, axis=0)
+        v = normal16(g, (n, 2, 64), O.FP16)
+        q = normal16(g, (1, 8, 64), O.FP16)
+        t.gpu.append(0, to_torch16(k, O.FP16, t.dev), to_torch16(v, O.FP16, t.dev))
+        out = t.gpu.decode(0, to_torch16(q, O.FP16, t.dev)).float().cpu().numpy()[0]
+        vf = O.to_f32(v, O.FP16)
+        for h in range(8):
+            assert_close(out[h], vf[:, h // 4].mean(0), f"{impl}: uniform weights, head {h}")
+
+
+def test_host_buffer_entry_point():
+    t = Twin(2, 32, 8, 128, 120, 4, 40, dtype="bf16", max_step_tokens=1024, seed=44)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [300, 17, 64], host_api=True)
+    t.step(seqs, [1, 1, 1], host_api=True)
+    st = t.gpu.stats()
+    assert st["bytes_h2d"] > 0 and st["bytes_d2h"] > 0 and t.gpu.launch_count > 0
+
+
+def test_partials_and_cross_rank_combine():
+    """Two 'ranks' each hold half of one sequence; merged partials equal single-cache attention."""
+    from titan_engine_b200 import _lib as L
+    H, Hkv, D, n = 32, 8, 128, 640
+    g = rng(45)
+    k = normal16(g, (n, Hkv, D), O.BF16); v = normal16(g, (n, Hkv, D), O.BF16); q = normal16(g, (1, H, D), O.BF16)
+    dev = torch.device("cuda")
+    from titan_engine_b200 import PagedKVCache
+    parts = []
+    for lo, hi in ((0, 320), (320, n)):
+        c = PagedKVCache(1, H, Hkv, D, 64, 1, 64, dtype="bf16", max_step_tokens=1024)
+        s = c.seq_alloc()
+        c.step_begin([s], [hi - lo])
+        c.append(0, to_torch16(k[lo:hi], O.BF16, dev), to_torch16(v[lo:hi], O.BF16, dev))
+        parts.append(c.decode_partial(0, to_torch16(q, O.BF16, dev)))
+        c.close()
+    stacked = torch.stack(parts).contiguous()                  # [2][1][H][D+2]
+    out = torch.empty(H, D, dtype=torch.bfloat16, device=dev)
+    st = L.lib().tk_combine_partials(stacked.data_ptr(), 2, H, D, out.data_ptr(), L.TK_BF16,
+                                     torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    want = O.attention_decode_f32(O.to_f32(q[0], O.BF16), O.to_f32(k, O.BF16), O.to_f32(v, O.BF16), H, Hkv, D, n)
+    assert_close(out.float().cpu().numpy(), want, "2-rank LSE combine")
+    # the partial format itself: (o, m, l) of rank 0 against the oracle's partial
+    pool = O.Pool(O.BF16, 64, H, Hkv, D, 1, 64)
+    table = np.arange(64, dtype=np.int32)[None]
+    pool.append(table, np.zeros(320, np.int32), np.arange(320, dtype=np.int32), k[:320], v[:320])
+    m, l, o = pool.decode_partial(table, 0, 320, 0, 320, q[0])
+    p0 = parts[0][0].cpu().numpy()
+    np.testing.assert_allclose(p0[:, D], m, rtol=1e-3, atol=2e-3)
+    scale = np.exp(m - p0[:, D])                               # bring both to the same reference max
+    assert_close(p0[:, D + 1], l * scale, "partial l", rtol=5e-3)
+    assert_close(p0[:, :D], o * scale[:, None], "partial o", rtol=5e-3, atol=5e-2)
+
+
+def test_churn_small_bit_exact_and_close():
+    """Continuous-batching churn on a small pool: retire / admit / append every step."""
+    t = Twin(1, 32, 8, 128, 700, 16, 64, dtype="fp16", impl="mma", max_step_tokens=4096, seed=3)
+    g = rng(33)
+    live = []
+    for _ in range(16):
+        s = t.seq_alloc()
+        live.append(s)
+    t.step(live, [int(min(600, max(1, round(float(np.exp(g.normal(np.log(120.0), 1.0))))))) for _ in live], decode=False)
+    for step in range(12):
+        for s in sorted(g.choice(live, size=2, replace=False).tolist()):
+            t.seq_free(s); live.remove(s)
+        new = [t.seq_alloc() for _ in range(2)]
+        ids = sorted(live) + new
+        t.step(ids, [1] * len(live) + [int(g.integers(16, 200)) for _ in new], check_pool=(step % 4 == 0))
+        live = ids

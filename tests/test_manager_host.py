@@ -1,0 +1,187 @@
+"""Host logic of the page manager through the C ABI, with no device (device = -2:
+bookkeeping only).  Page tables, slot indices and the free list must be bit-exact
+against the oracle's manager under the same call sequence."""
+import re
+import os
+
+import numpy as np
+import pytest
+
+from helpers import rng
+from oracle import tk_oracle as O
+from titan_engine_b200 import KvError, PagedKVCache, _lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def host_cache(num_pages=64, max_seqs=8, mpps=64, dtype="fp16", **kw):
+    return PagedKVCache(2, 8, 2, 64, num_pages, max_seqs, mpps, dtype=dtype, host_only=True,
+                        max_step_tokens=kw.pop("max_step_tokens", 4096), **kw)
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "titan_kv.h")).read()
+    declared = set(re.findall(r"\b(tk_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 30
+    lib = L.lib()
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in titan_kv.h but not exported"
+    assert declared == set(L.SIGNATURES), declared ^ set(L.SIGNATURES)
+
+
+def test_compute_fails_loudly_without_device():
+    c = host_cache()
+    s = c.seq_alloc()
+    c.step_begin([s], [3])
+    with pytest.raises(KvError) as e:
+        c._check(c._lib.tk_kv_append(c._h, 0, None, None, None, None))
+    assert e.value.status == L.TK_CUDA_ERROR
+    with pytest.raises(KvError):
+        c._check(c._lib.tk_kv_decode(c._h, 0, None, None, None))
+
+
+def test_fresh_pool_hands_out_sequential_pages_and_slots():
+    c = host_cache()
+    s = c.seq_alloc()
+    assert s == 0
+    c.reserve(s, 512)
+    np.testing.assert_array_equal(c.page_table(s), np.arange(32))
+    for pos in (0, 15, 16, 511):
+        assert c.slot(s, pos) == pos
+    assert c.slot(s, 512) == -1
+    assert c.num_free_pages == 32
+    for _ in range(64):
+        c.reserve(s, 1)
+    assert c.seq_len(s) == 576 and len(c.page_table(s)) == 36
+
+
+def test_lifo_reuse_and_lowest_free_slot():
+    c = host_cache()
+    a, b = c.seq_alloc(), c.seq_alloc()
+    c.reserve(a, 40)            # pages 0,1,2
+    c.reserve(b, 20)            # pages 3,4
+    c.seq_free(a)               # pushes 0,1,2 -> 2 is on top
+    assert c.seq_alloc() == 0   # lowest free slot index, like BatchScheduler::allocate_slot
+    c.reserve(0, 50)            # needs 4 pages: 2,1,0 then 5
+    np.testing.assert_array_equal(c.page_table(0), [2, 1, 0, 5])
+    assert c.seq_len(1) == 20 and c.seq_len(5) == -1
+
+
+def test_out_of_pages_changes_nothing():
+    c = host_cache(num_pages=4)
+    s = c.seq_alloc()
+    c.reserve(s, 40)
+    d = c.digest()
+    with pytest.raises(KvError) as e:
+        c.reserve(s, 100)
+    assert e.value.status == L.TK_OUT_OF_PAGES
+    assert c.digest() == d and c.seq_len(s) == 40
+    t = c.seq_alloc()
+    with pytest.raises(KvError) as e:           # step_begin is all-or-nothing across sequences
+        c.step_begin([s, t], [8, 17])
+    assert e.value.status == L.TK_OUT_OF_PAGES
+    assert c.seq_len(s) == 40 and c.seq_len(t) == 0 and c.num_free_pages == 1
+    c.step_begin([s, t], [8, 16])
+    assert c.num_free_pages == 0
+
+
+def test_invalid_arguments():
+    c = host_cache()
+    with pytest.raises(KvError):
+        c.reserve(3, 1)                         # not live
+    s = c.seq_alloc()
+    with pytest.raises(KvError):
+        c.reserve(s, 64 * 16 + 1)               # exceeds max_pages_per_seq
+    with pytest.raises(KvError):
+        c.step_begin([s, s], [1, 1])            # duplicate sequence
+    with pytest.raises(KvError):
+        c.seq_free(5)
+    for _ in range(7):
+        c.seq_alloc()
+    with pytest.raises(KvError) as e:
+        c.seq_alloc()
+    assert e.value.status == L.TK_OUT_OF_SEQS
+    with pytest.raises(KvError):
+        PagedKVCache(2, 8, 3, 64, 8, 2, 4, host_only=True)   # 8 heads / 3 kv heads
+
+
+def test_adopt_and_truncate():
+    c = host_cache(num_pages=32)
+    s = c.seq_alloc()
+    c.adopt(s, [7, 3, 30], 40)
+    np.testing.assert_array_equal(c.page_table(s), [7, 3, 30])
+    assert c.slot(s, 17) == 3 * 16 + 1 and c.num_free_pages == 29
+    t = c.seq_alloc()
+    with pytest.raises(KvError):
+        c.adopt(t, [3], 5)                      # page 3 is taken
+    c.reserve(t, 16)                            # next free after removing 7,3,30: 0
+    np.testing.assert_array_equal(c.page_table(t), [0])
+    c.truncate(s, 16)
+    np.testing.assert_array_equal(c.page_table(s), [7])
+    c.reserve(t, 32)                            # freed 3 then 30 -> 30 on top, then 3
+    np.testing.assert_array_equal(c.page_table(t), [0, 30, 3])
+
+
+def test_step_plan_shapes():
+    c = host_cache(num_pages=256, mpps=64, chunk_tokens=128)
+    a, b = c.seq_alloc(), c.seq_alloc()
+    c.step_begin([a, b], [300, 5])
+    assert c.step_num_tokens == 305 and c.step_chunk_tokens == 128
+    assert c.step_num_work_items == (3 + 1) * 2      # ceil(300/128)=3 chunks + 1 chunk, x 2 kv heads
+    c.step_begin([b, a], None)                       # decode only
+    assert c.step_num_tokens == 0 and c.step_num_work_items == 8
+    f = host_cache(num_pages=256, mpps=64, chunk_tokens=128, dtype="fp8")
+    s = f.seq_alloc()
+    f.step_begin([s], [300])                         # 18 sealed pages (288 tokens) + 12 open
+    assert f.step_num_work_items == (3 + 1) * 2 and f.stats()["pages_sealed"] == 18
+    f.step_begin([s], [4])                           # 304 tokens: 19 sealed, nothing open
+    assert f.step_num_work_items == 3 * 2 and f.stats()["pages_sealed"] == 19
+
+
+@pytest.mark.parametrize("seed", [3, 4])
+def test_churn_matches_oracle_manager_bit_exact(seed):
+    """Retire ~5% per step in ascending slot order, admit replacements in ascending slot order,
+    every survivor appends one token: page tables, slots and free list equal the oracle's."""
+    num_pages, max_seqs, mpps, ps = 3000, 64, 160, 16
+    c = host_cache(num_pages, max_seqs, mpps, max_step_tokens=1 << 16)
+    o = O.Manager(num_pages, max_seqs, mpps, ps)
+    g = rng(seed)
+    live = []
+    for _ in range(max_seqs):
+        s, so = c.seq_alloc(), o.seq_alloc()
+        assert s == so
+        n = int(min(2048, max(1, round(float(np.exp(g.normal(np.log(300.0), 1.0)))))))
+        c.step_begin([s], [n]); assert o.reserve(so, n) == O.OK
+        live.append(s)
+    assert c.digest() == o.digest()
+    for step in range(60):
+        retire = sorted(g.choice(live, size=3, replace=False).tolist())
+        for s in retire:
+            c.seq_free(s); assert o.seq_free(s) == O.OK
+            live.remove(s)
+        admitted = []
+        for _ in retire:
+            s, so = c.seq_alloc(), o.seq_alloc()
+            assert s == so
+            admitted.append(s)
+        prefill = [int(g.integers(16, 257)) for _ in admitted]
+        ids = sorted(live) + admitted
+        n_new = [1] * len(live) + prefill
+        need = sum(((c.seq_len(s) + n + ps - 1) // ps) - len(c.page_table(s)) for s, n in zip(ids, n_new))
+        if need > c.num_free_pages:
+            with pytest.raises(KvError):
+                c.step_begin(ids, n_new)
+            ids, n_new = sorted(live), [1] * len(live)
+            for s in admitted:
+                c.seq_free(s); o.seq_free(s)
+            admitted = []
+        c.step_begin(ids, n_new)
+        for s, n in zip(ids, n_new):
+            assert o.reserve(s, n) == O.OK
+        live = sorted(live) + admitted
+        assert c.digest() == o.digest(), f"step {step}"
+        s = live[int(g.integers(len(live)))]
+        np.testing.assert_array_equal(c.page_table(s), o.page_table(s))
+        pos = c.seq_len(s) - 1
+        assert c.slot(s, pos) == o.slot(s, pos)
+    assert c.stats()["page_frees"] > 0

@@ -65,6 +65,9 @@ SIGNATURES = {
     "tk_kv_decode_partial": (C.c_int, [_P, C.c_int32, _P, _P, _P]),
     "tk_combine_partials": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
     "tk_kv_append_decode_host": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
+    "tk_kv_append_decode_host_async": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
+    "tk_kv_profile_enable": (C.c_int, [_P, C.c_int32]),
+    "tk_kv_profile_read": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "tk_kv_device_status": (C.c_int, [_P, _P]),
     "tk_kv_launch_count": (C.c_int64, [_P]),
 }

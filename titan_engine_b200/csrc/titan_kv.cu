@@ -99,6 +99,11 @@ struct tk_kv {
     bool have_step = false;
     int n_pool_items = 0;                // items of kind 0 come first
 
+    // optional timing of the dominant decode kernel: one event pair per launch
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_ev;    // start/stop pairs
+    size_t prof_used = 0;
+
     tk_kv_stats stats{};
     int64_t launches = 0;
     std::string err;
@@ -148,6 +153,7 @@ void release(tk_kv* h) {
             if (h->h_step[i]) cudaFreeHost(h->h_step[i]);
             if (h->ev[i]) cudaEventDestroy(h->ev[i]);
         }
+        for (cudaEvent_t e : h->prof_ev) cudaEventDestroy(e);
     }
     delete h->mgr;
     delete h;
@@ -499,6 +505,8 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     const tk::LayerPtrs lp = h->layer(layer);
     cudaError_t e = cudaSuccess;
     const bool mma = h->use_mma && h->dev.chunk_tokens <= 2048;
+    const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
+    if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
     if (mma) {
         tk::StepDev pool = h->dev;
         pool.n_items = h->n_pool_items;
@@ -506,6 +514,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
             e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], pool, h->d_table, q, h->d_partials, h->d_status, s);
             h->launches++;
         }
+        if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
         if (e == cudaSuccess && h->dev.n_items > h->n_pool_items) {      // FP8 open pages: 16-bit tail
             tk::StepDev open = h->dev;
             open.items = h->dev.items + h->n_pool_items;
@@ -513,9 +522,12 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
             e = tk::launch_decode_simt(h->geo, lp, open, h->d_table, q, h->d_partials, s);
             h->launches++;
         }
-    } else if (h->dev.n_items > 0) {
-        e = tk::launch_decode_simt(h->geo, lp, h->dev, h->d_table, q, h->d_partials, s);
-        h->launches++;
+    } else {
+        if (h->dev.n_items > 0) {
+            e = tk::launch_decode_simt(h->geo, lp, h->dev, h->d_table, q, h->d_partials, s);
+            h->launches++;
+        }
+        if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
     }
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode launch: %s", cudaGetErrorString(e));
     e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, h->cfg.io_dtype, partial_out, s);
@@ -539,8 +551,8 @@ int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int
     return e == cudaSuccess ? TK_OK : TK_CUDA_ERROR;
 }
 
-int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
-                             const void* q_host, void* out_host, void* stream) {
+static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
+                                   const void* q_host, void* out_host, void* stream, bool wait) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "append_decode_host: handle has no device");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "append_decode_host: no step in progress");
@@ -564,7 +576,43 @@ int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const 
         h->stats.bytes_h2d += (int64_t)q_bytes;
         h->stats.bytes_d2h += (int64_t)q_bytes;
     }
-    TK_CUDA(h, cudaStreamSynchronize(s));
+    if (wait) TK_CUDA(h, cudaStreamSynchronize(s));
+    return TK_OK;
+}
+
+int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
+                             const void* q_host, void* out_host, void* stream) {
+    return append_decode_host_impl(h, layer, k_host, v_host, q_host, out_host, stream, true);
+}
+int tk_kv_append_decode_host_async(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
+                                   const void* q_host, void* out_host, void* stream) {
+    return append_decode_host_impl(h, layer, k_host, v_host, q_host, out_host, stream, false);
+}
+
+int tk_kv_profile_enable(tk_kv* h, int32_t max_launches) {
+    if (!h || h->host_only || max_launches < 0) return TK_INVALID_ARG;
+    TK_CUDA(h, cudaSetDevice(h->device));
+    while (h->prof_ev.size() < 2 * (size_t)max_launches) {
+        cudaEvent_t e;
+        TK_CUDA(h, cudaEventCreate(&e));
+        h->prof_ev.push_back(e);
+    }
+    h->prof_used = 0;
+    h->profiling = max_launches > 0;
+    return TK_OK;
+}
+int tk_kv_profile_read(tk_kv* h, double* total_ms, int64_t* launches) {
+    if (!h || h->host_only || !total_ms || !launches) return TK_INVALID_ARG;
+    double sum = 0.0;
+    for (size_t i = 0; i + 1 < h->prof_used; i += 2) {
+        TK_CUDA(h, cudaEventSynchronize(h->prof_ev[i + 1]));
+        float ms = 0.0f;
+        TK_CUDA(h, cudaEventElapsedTime(&ms, h->prof_ev[i], h->prof_ev[i + 1]));
+        sum += ms;
+    }
+    *total_ms = sum;
+    *launches = (int64_t)(h->prof_used / 2);
+    h->prof_used = 0;
     return TK_OK;
 }
 

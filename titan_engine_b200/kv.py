@@ -217,6 +217,22 @@ class PagedKVCache:
         self._check(self._lib.tk_kv_append_decode_host(self._h, layer, k.data_ptr(), v.data_ptr(),
                                                        q.data_ptr(), out.data_ptr(), self._stream()))
 
+    def append_decode_host_async(self, layer: int, k, v, q, out) -> None:
+        """As append_decode_host but returns at once; pinned host tensors, caller syncs the stream."""
+        for t in (k, v, q, out):
+            assert t.device.type == "cpu" and t.is_contiguous() and t.is_pinned() and t.dtype == self.io_torch_dtype
+        self._check(self._lib.tk_kv_append_decode_host_async(self._h, layer, k.data_ptr(), v.data_ptr(),
+                                                             q.data_ptr(), out.data_ptr(), self._stream()))
+
+    def profile_enable(self, max_launches: int) -> None:
+        self._check(self._lib.tk_kv_profile_enable(self._h, max_launches))
+
+    def profile_read(self):
+        """-> (summed decode-kernel milliseconds, launches) since profile_enable."""
+        ms, n = C.c_double(0.0), C.c_int64(0)
+        self._check(self._lib.tk_kv_profile_read(self._h, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
     def device_status(self) -> None:
         self._check(self._lib.tk_kv_device_status(self._h, self._stream()))
 
