@@ -134,6 +134,15 @@ int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out);
  * single counter does (kv_cache.cpp:148-150). */
 int tk_kv_step_begin(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new,
                      void* stream);
+/* Same, with len_cap[i] limiting how many leading tokens of seq_ids[i] attention covers
+ * (cuda::attention_decode takes seq_len as an argument, src/compute/dispatch.h:73-75, so a
+ * caller may attend to a prefix).  16-bit storage only. */
+int tk_kv_step_begin_capped(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new,
+                            const int32_t* len_cap, void* stream);
+/* The query-head count is an argument of cuda::attention_decode, not of KVCache::initialize
+ * (src/inference/kv_cache.h:21-23): a handle sized for cfg.num_heads may be told a smaller
+ * head count (same kv heads) before a step. */
+int tk_kv_set_num_heads(tk_kv* h, int32_t num_heads);
 int tk_kv_step_num_tokens(const tk_kv* h);
 int tk_kv_step_num_work_items(const tk_kv* h);
 int tk_kv_step_chunk_tokens(const tk_kv* h);
@@ -148,6 +157,10 @@ int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t*
  * of the step: q, out device [n_seqs][H][D] in io_dtype.  Paged GQA attention,
  * online softmax, split-KV partials and log-sum-exp combine. */
 int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream);
+/* tk_kv_decode with explicit types: q_dtype and out_dtype are each TK_FP32 (the reference's
+ * float* interface) or the handle's io dtype. */
+int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, void* out, int32_t out_dtype,
+                    void* stream);
 /* Same, but stops before normalisation: partial[n_seqs][H][D+2] f32 =
  * (o unnormalised [D], m, l), for a cross-GPU combine. */
 int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial, void* stream);

@@ -57,6 +57,9 @@ SIGNATURES = {
     "tk_kv_state_digest": (C.c_uint64, [_P]),
     "tk_kv_get_stats": (C.c_int, [_P, C.POINTER(KvStats)]),
     "tk_kv_step_begin": (C.c_int, [_P, C.c_int32, _I32P, _I32P, _P]),
+    "tk_kv_step_begin_capped": (C.c_int, [_P, C.c_int32, _I32P, _I32P, _I32P, _P]),
+    "tk_kv_set_num_heads": (C.c_int, [_P, C.c_int32]),
+    "tk_kv_decode_ex": (C.c_int, [_P, C.c_int32, _P, C.c_int32, _P, C.c_int32, _P]),
     "tk_kv_step_num_tokens": (C.c_int, [_P]),
     "tk_kv_step_num_work_items": (C.c_int, [_P]),
     "tk_kv_step_chunk_tokens": (C.c_int, [_P]),

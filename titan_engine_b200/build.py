@@ -46,6 +46,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     cmd = [nvcc_path(), *NVCC_FLAGS, "-I", os.path.join(HERE, "..", "include"), "-I", CSRC,
+           "-I", os.path.join(CSRC, "compat"),
            "-o", LIB, *sources()]
     if verbose:
         cmd.insert(1, "-Xptxas")

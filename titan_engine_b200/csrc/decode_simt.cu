@@ -252,6 +252,17 @@ cudaError_t launch_combine_step(const Geometry& g, const StepDev& st, const floa
     return cudaGetLastError();
 }
 
+__global__ void f32_to_16_kernel(const float* __restrict__ src, void* __restrict__ dst, size_t n, int dtype) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) store_out(dst, i, src[i], dtype);
+}
+
+cudaError_t launch_f32_to_16(const float* src, void* dst, size_t n, int dtype, cudaStream_t s) {
+    if (n == 0) return cudaSuccess;
+    f32_to_16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(src, dst, n, dtype);
+    return cudaGetLastError();
+}
+
 // parts [n_parts][n_rows][D+2]; grid = n_rows
 __global__ void combine_parts_kernel(const float* __restrict__ parts, int n_parts, int n_rows, int D,
                                      void* __restrict__ out, int out_dtype) {

@@ -22,6 +22,20 @@ void PageManager::set_entry(int seq, int idx, int32_t value) {
     delta_.emplace_back(flat, value);
 }
 
+void PageManager::compact_delta() {
+    if (delta_.size() < 2) return;
+    if (delta_stamp_.size() != table_.size()) delta_stamp_.assign(table_.size(), 0);
+    if (++delta_gen_ == 0) { std::fill(delta_stamp_.begin(), delta_stamp_.end(), 0u); delta_gen_ = 1; }
+    size_t w = delta_.size();
+    for (size_t i = delta_.size(); i-- > 0;) {            // newest first; keep the first sighting
+        uint32_t& st = delta_stamp_[delta_[i].first];
+        if (st == delta_gen_) continue;
+        st = delta_gen_;
+        delta_[--w] = delta_[i];
+    }
+    delta_.erase(delta_.begin(), delta_.begin() + (ptrdiff_t)w);
+}
+
 // Lowest free index, like BatchScheduler::allocate_slot (src/inference/batch.cpp:86-96).
 int PageManager::seq_alloc() {
     for (int i = 0; i < max_seqs_; i++)
@@ -118,7 +132,7 @@ uint64_t PageManager::digest() const {
 
 int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                            bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
-                           int max_partial_rows, StepPlan* plan) {
+                           int max_partial_rows, StepPlan* plan, const int32_t* len_cap) {
     if (n_seqs < 0 || (n_seqs > 0 && !seqs) || !plan) return ST_INVALID_ARG;
     const int ps = page_size_;
     if (chunk_tokens < 0 || chunk_tokens % ps != 0) return ST_INVALID_ARG;
@@ -146,6 +160,7 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         int64_t rows = 0, items = 0;
         for (int i = 0; i < n_seqs; i++) {
             int64_t len = (int64_t)seq_len_[seqs[i]] + (n_new ? n_new[i] : 0);
+            if (len_cap && len_cap[i] < len) len = len_cap[i] < 0 ? 0 : len_cap[i];
             int64_t pool_tokens = fp8 ? (len / ps) * ps : len;
             int64_t r = (pool_tokens + chunk - 1) / chunk + ((fp8 && len > pool_tokens) ? 1 : 0);
             rows += r;
@@ -185,11 +200,13 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         int st = reserve(s, add);
         if (st != ST_OK) return st;                     // cannot happen after the checks above
         int len = seq_len_[s];
+        const int full_len = len;
+        if (len_cap && len_cap[i] < len) len = len_cap[i] < 0 ? 0 : len_cap[i];   // attend to a prefix only
         plan->len[i] = len;
         int tok_base = (int)plan->tok_b.size();
-        for (int p = old_len; p < len; p++) { plan->tok_b.push_back(i); plan->tok_pos.push_back(p); }
+        for (int p = old_len; p < full_len; p++) { plan->tok_b.push_back(i); plan->tok_pos.push_back(p); }
         if (fp8)
-            for (int lp = old_len / ps; (lp + 1) * ps <= len; lp++)
+            for (int lp = old_len / ps; (lp + 1) * ps <= full_len; lp++)
                 plan->seals.push_back({i, lp, old_len, tok_base});
         int pool_tokens = fp8 ? (len / ps) * ps : len;
         int n_chunks = (pool_tokens + chunk - 1) / chunk;

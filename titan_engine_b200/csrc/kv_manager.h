@@ -69,13 +69,17 @@ public:
 
     // (flat index into the table, new value) pairs since the last take_delta()
     std::vector<std::pair<int32_t, int32_t>>& delta() { return delta_; }
+    // Keep only the last write to each index: the device applies the patches in
+    // parallel, so an index must not appear twice (free then re-map of a slot's row).
+    void compact_delta();
 
     // Reserve n_new[i] tokens for seqs[i] (all or nothing), then lay out the step:
     // token list in call order then position, FP8 seal list, split-KV work list.
     // chunk_tokens == 0 picks a chunk so that about `target_items` items exist.
+    // len_cap (optional, 16-bit storage only) limits the attended prefix of each sequence.
     int plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                   bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
-                  int max_partial_rows, StepPlan* plan);
+                  int max_partial_rows, StepPlan* plan, const int32_t* len_cap = nullptr);
 
     struct Counters { int64_t page_allocs = 0, page_frees = 0, seq_allocs = 0, seq_frees = 0; } counters;
 
@@ -87,6 +91,8 @@ private:
     std::vector<int32_t> seq_len_;      // -1 = slot free
     std::vector<int32_t> seq_pages_;
     std::vector<std::pair<int32_t, int32_t>> delta_;
+    std::vector<uint32_t> delta_stamp_;  // per table index: generation of the last compaction that saw it
+    uint32_t delta_gen_ = 0;
 };
 
 // status codes shared with include/titan_kv.h

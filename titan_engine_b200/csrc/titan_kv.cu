@@ -395,17 +395,20 @@ int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out) {
 }
 
 // ---- step ----------------------------------------------------------------------------------
-int tk_kv_step_begin(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new, void* stream) {
+static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new,
+                           const int32_t* len_cap, void* stream) {
     if (!h) return TK_INVALID_ARG;
+    if (len_cap && h->cfg.dtype == TK_FP8_E4M3)
+        return fail(h, TK_UNSUPPORTED, "step_begin: an attended-length cap needs 16-bit storage");
     h->have_step = false;
     const char* env_chunk = getenv("TK_CHUNK_TOKENS");
     int chunk = h->cfg.chunk_tokens;
     if (chunk == 0 && env_chunk) chunk = atoi(env_chunk);
     const char* env_target = getenv("TK_TARGET_ITEMS");
-    int target = env_target ? atoi(env_target) : 24 * h->num_sms;
+    int target = env_target ? atoi(env_target) : 8 * h->num_sms;   // ~4 waves of 2 CTAs/SM; larger chunks measured faster
     // the tensor-core kernel keeps one page id per lane per warp: chunk <= 16*4*32 tokens
     int st = h->mgr->plan_step(n_seqs, seq_ids, n_new, h->cfg.num_kv_heads, h->cfg.dtype == TK_FP8_E4M3,
-                               chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan);
+                               chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan, len_cap);
     if (st != TK_OK) return fail(h, st, "step_begin: %s", tk_status_str(st));
     tk::StepPlan& p = h->plan;
     if (chunk == 0 && p.chunk_tokens > 2048) {
@@ -423,6 +426,7 @@ int tk_kv_step_begin(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int
 
     cudaStream_t s = (cudaStream_t)stream;
     TK_CUDA(h, cudaSetDevice(h->device));
+    h->mgr->compact_delta();
     auto& delta = h->mgr->delta();
     int n_delta = (int)delta.size();
     if (n_delta > kMaxDelta) {
@@ -478,6 +482,24 @@ int tk_kv_step_begin(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int
     return TK_OK;
 }
 
+int tk_kv_step_begin(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new, void* stream) {
+    return step_begin_impl(h, n_seqs, seq_ids, n_new, nullptr, stream);
+}
+int tk_kv_step_begin_capped(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new,
+                            const int32_t* len_cap, void* stream) {
+    return step_begin_impl(h, n_seqs, seq_ids, n_new, len_cap, stream);
+}
+
+int tk_kv_set_num_heads(tk_kv* h, int32_t num_heads) {
+    if (!h) return TK_INVALID_ARG;
+    const int hkv = h->cfg.num_kv_heads;
+    const int g = num_heads > 0 && num_heads % hkv == 0 ? num_heads / hkv : 0;
+    if (g != 1 && g != 2 && g != 4 && g != 8 && g != 16) return fail(h, TK_INVALID_ARG, "set_num_heads(%d): heads per kv head must be 1, 2, 4, 8 or 16", num_heads);
+    if (num_heads > h->cfg.num_heads) return fail(h, TK_INVALID_ARG, "set_num_heads(%d): above the %d the handle was sized for", num_heads, h->cfg.num_heads);
+    h->geo.H = num_heads;
+    return TK_OK;
+}
+
 int tk_kv_step_num_tokens(const tk_kv* h) { return h && h->have_step ? (int)h->plan.tok_b.size() : -1; }
 int tk_kv_step_num_work_items(const tk_kv* h) { return h && h->have_step ? (int)h->plan.items.size() : -1; }
 int tk_kv_step_chunk_tokens(const tk_kv* h) { return h && h->have_step ? h->plan.chunk_tokens : -1; }
@@ -496,7 +518,8 @@ int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t*
     return TK_OK;
 }
 
-static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* partial_out, cudaStream_t s) {
+static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* partial_out, cudaStream_t s,
+                       int q_dtype = -1, int out_dtype = -1) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode: no step in progress (call tk_kv_step_begin)");
@@ -504,6 +527,18 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     if (!q || (!out && !partial_out)) return fail(h, TK_INVALID_ARG, "decode: null q/out");
     const tk::LayerPtrs lp = h->layer(layer);
     cudaError_t e = cudaSuccess;
+    if (q_dtype == TK_FP32) {                               // FP32 callers: narrow q into the staging buffer
+        e = tk::launch_f32_to_16((const float*)q, h->d_q, (size_t)h->dev.n_seqs * h->geo.H * h->geo.D,
+                                 h->cfg.io_dtype, s);
+        h->launches++;
+        if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "q conversion launch: %s", cudaGetErrorString(e));
+        q = h->d_q;
+    } else if (q_dtype >= 0 && q_dtype != h->cfg.io_dtype) {
+        return fail(h, TK_INVALID_ARG, "decode: q dtype must be FP32 or the handle's io dtype");
+    }
+    if (out_dtype < 0) out_dtype = h->cfg.io_dtype;
+    if (out_dtype != TK_FP32 && out_dtype != h->cfg.io_dtype)
+        return fail(h, TK_INVALID_ARG, "decode: out dtype must be FP32 or the handle's io dtype");
     const bool mma = h->use_mma && h->dev.chunk_tokens <= 2048;
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
     if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
@@ -530,7 +565,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
     }
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode launch: %s", cudaGetErrorString(e));
-    e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, h->cfg.io_dtype, partial_out, s);
+    e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, out_dtype, partial_out, s);
     h->launches++;
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "combine launch: %s", cudaGetErrorString(e));
     return TK_OK;
@@ -538,6 +573,10 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
 
 int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream) {
     return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream);
+}
+int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, void* out, int32_t out_dtype,
+                    void* stream) {
+    return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream, q_dtype, out_dtype);
 }
 int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial, void* stream) {
     return decode_impl(h, layer, q, nullptr, partial, (cudaStream_t)stream);

@@ -61,6 +61,9 @@ cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUte
                               const StepDev& st, const int32_t* page_table, const void* q,
                               float* partials, int* status, cudaStream_t s);
 
+// n FP32 values -> the 16-bit type `dtype` (round to nearest even).
+cudaError_t launch_f32_to_16(const float* src, void* dst, size_t n, int dtype, cudaStream_t s);
+
 // LSE merge over each sequence's partial rows.
 //   out != null     : normalised [n_seqs][H][D] in out_dtype
 //   partial_out!=null: merged but unnormalised [n_seqs][H][D+2]
