@@ -186,6 +186,26 @@ int tk_kv_append_decode_host_async(tk_kv* h, int32_t layer, const void* k_host, 
 int tk_kv_profile_enable(tk_kv* h, int32_t max_launches);
 int tk_kv_profile_read(tk_kv* h, double* total_ms, int64_t* launches);
 
+/* Paged decode attention for callers that cannot allocate device memory (a plugin inside a
+ * process whose allocator belongs to someone else, a serving loop that has handed all of
+ * HBM to its own arena, a caller that wants a step guaranteed not to reach the driver's
+ * allocator).  No counterpart in the reference.  No handle, no workspace: the split-KV
+ * scratch is one fixed 4 MiB array inside the library image (held by every GPU that loads
+ * the library), so the call allocates nothing on the device and is refused — not truncated —
+ * beyond n_seqs 256, 4096 (sequence, 256-token chunk, kv head) work items or 4 MiB of
+ * partial rows.  All calls on a device share that array: calls whose kernels may overlap
+ * race, keep them on one stream.  A device's first call looks the array's address up; make
+ * it outside stream capture.
+ *   pool        device, one layer: [num_pages][Hkv][2][16][D] in dtype (TK_FP16 / TK_BF16)
+ *   page_table  device int32 [n_seqs][max_pages_per_seq]
+ *   seq_lens    HOST int32 [n_seqs]
+ *   q, out      device [n_seqs][H][D] in dtype */
+int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t num_pages,
+                           const int32_t* page_table, int32_t max_pages_per_seq,
+                           const int32_t* seq_lens, int32_t n_seqs, int32_t num_heads,
+                           int32_t num_kv_heads, int32_t head_dim, const void* q, void* out,
+                           void* stream);
+
 /* Reads the device status word after draining `stream`: TK_OK, or TK_TIMEOUT when a
  * bounded device-side wait gave up (the word is cleared). */
 int tk_kv_device_status(tk_kv* h, void* stream);
