@@ -251,13 +251,17 @@ def run_ours(args):
     def step_device():
         cache.step_begin(seqs, ones)
         for l in range(L):
-            cache.append(l, k, v)
-            cache.decode(l, q, out)
+            if args.separate:
+                cache.append(l, k, v)
+                cache.decode(l, q, out)
+            else:
+                cache.append_decode(l, k, v, q, out)
 
     def step_host():
         cache.step_begin(seqs, ones)
         for l in range(L):
             cache.append_decode_host_async(l, hk, hv, hq, hout)
+        cache.host_wait()
         torch.cuda.current_stream().synchronize()              # the step's result is on the host
 
     def barrier():
@@ -354,6 +358,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=0, help="split-KV chunk tokens (0 = library default)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--separate", action="store_true", help="call append and decode separately (two entry points)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

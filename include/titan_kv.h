@@ -157,6 +157,12 @@ int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t*
  * of the step: q, out device [n_seqs][H][D] in io_dtype.  Paged GQA attention,
  * online softmax, split-KV partials and log-sum-exp combine. */
 int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream);
+/* update + attention_decode of one layer in one call (the pair at src/model/dense.cpp:388-398).
+ * On a decode step (at most one new token per sequence) with 16-bit storage this is ONE kernel:
+ * the attention kernel writes the new token's K/V rows into the page it is about to read.
+ * In every other case it does tk_kv_append then tk_kv_decode. */
+int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
+                        void* stream);
 /* tk_kv_decode with explicit types: q_dtype and out_dtype are each TK_FP32 (the reference's
  * float* interface) or the handle's io dtype. */
 int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, void* out, int32_t out_dtype,
@@ -173,10 +179,15 @@ int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int
 int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
                              const void* q_host, void* out_host, void* stream);
 
-/* Same without the final wait: the caller synchronises `stream` before reading out_host;
- * the host buffers must be pinned and stay untouched until then. */
+/* Same without the final wait.  Copies run on the handle's own copy streams so that they
+ * overlap the kernels of neighbouring calls; before reading out_host the caller calls
+ * tk_kv_host_wait(h, stream) and synchronises `stream`.  The host buffers must be pinned and
+ * stay untouched until then. */
 int tk_kv_append_decode_host_async(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
                                    const void* q_host, void* out_host, void* stream);
+
+/* Makes `stream` wait for every device-to-host copy the *_host calls have queued. */
+int tk_kv_host_wait(tk_kv* h, void* stream);
 
 /* Timing of the dominant decode kernel on its own stream: after enable(n), each of the next
  * n tk_kv_decode calls brackets its main attention kernel with a CUDA event pair;

@@ -91,7 +91,7 @@ class Twin:
         self.gpu.adopt(s, pages, seq_len)
         assert self.mgr.adopt(s, pages, seq_len) == O.OK
 
-    def step(self, seq_ids, n_new, check_pool=False, decode=True, outlier_p=0.0, host_api=False):
+    def step(self, seq_ids, n_new, check_pool=False, decode=True, outlier_p=0.0, host_api=False, fused=False):
         torch = self.torch
         n_new = [0] * len(seq_ids) if n_new is None else list(n_new)
         old = [self.gpu.seq_len(s) for s in seq_ids]
@@ -115,6 +115,10 @@ class Twin:
                 out_h = torch.empty_like(qt).pin_memory()
                 self.gpu.append_decode_host(layer, kt, vt, qt, out_h)
                 got = out_h.to(torch.float32).numpy()
+            elif fused:
+                got = self.gpu.append_decode(layer, to_torch16(k16, self.carrier, self.dev),
+                                             to_torch16(v16, self.carrier, self.dev),
+                                             to_torch16(q16, self.carrier, self.dev)).to(torch.float32).cpu().numpy()
             else:
                 slots = torch.full((max(nt, 1),), -7, dtype=torch.int64, device=self.dev)
                 if nt:
@@ -125,7 +129,7 @@ class Twin:
                     got = self.gpu.decode(layer, to_torch16(q16, self.carrier, self.dev)).to(torch.float32).cpu().numpy()
             if check_pool:
                 self.check_pool(layer)
-            if decode or host_api:
+            if decode or host_api or fused:
                 want = self.pools[layer].decode(table, seq_ids, lens, q16)
                 assert_close(got, want, f"layer {layer} attention ({len(seq_ids)} seqs, lens {lens[:4]}...)",
                              out_mantissa_bits=7 if self.carrier == O.BF16 else 10)

@@ -111,6 +111,24 @@ def test_decode_fp8(impl, io):
     t.check_pool(1)
 
 
+@pytest.mark.parametrize("shape", [(8, 2, 64, "fp16"), (32, 8, 128, "bf16"), (16, 1, 128, "fp16")])
+def test_fused_append_decode_single_launch(shape):
+    """Decode steps through tk_kv_append_decode: the attention kernel writes the new token's rows
+    itself.  Outputs and the pool bytes it leaves behind must match append-then-decode."""
+    H, Hkv, D, dtype = shape
+    t = Twin(2, H, Hkv, D, 200, 5, 48, dtype=dtype, impl="mma", max_step_tokens=2048, seed=50)
+    seqs = [t.seq_alloc() for _ in range(4)]
+    t.step(seqs, [14, 16, 250, 1], fused=True, check_pool=True)      # prefill: falls back to two kernels
+    n0 = t.gpu.launch_count
+    t.step(seqs, [1, 1, 1, 1], fused=True, check_pool=True)          # rows 14, 0 (fresh page), 10, 1
+    assert t.gpu.launch_count - n0 <= 1 + 2                           # page-table patch + one kernel per layer
+    for i in range(20):
+        t.step(seqs, [1, 1, 1, i % 2], fused=True, check_pool=(i % 5 == 0))   # one sequence sometimes idle
+    t.step(seqs[:2], [1, 1], fused=True, check_pool=True)
+    for layer in range(2):
+        t.check_pool(layer)
+
+
 def test_decode_shuffled_pool_c2_style():
     """Page tables as inputs: a seeded permutation of the pool, batch of ragged contexts."""
     H, Hkv, D = 32, 8, 128

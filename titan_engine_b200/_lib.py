@@ -65,10 +65,12 @@ SIGNATURES = {
     "tk_kv_step_chunk_tokens": (C.c_int, [_P]),
     "tk_kv_append": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P]),
     "tk_kv_decode": (C.c_int, [_P, C.c_int32, _P, _P, _P]),
+    "tk_kv_append_decode": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
     "tk_kv_decode_partial": (C.c_int, [_P, C.c_int32, _P, _P, _P]),
     "tk_combine_partials": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
     "tk_kv_append_decode_host": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
     "tk_kv_append_decode_host_async": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
+    "tk_kv_host_wait": (C.c_int, [_P, _P]),
     "tk_kv_profile_enable": (C.c_int, [_P, C.c_int32]),
     "tk_kv_profile_read": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "tk_paged_decode_static": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _I32P, C.c_int32, C.c_int32,

@@ -48,6 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     cmd = [nvcc_path(), *NVCC_FLAGS, "-I", os.path.join(HERE, "..", "include"), "-I", CSRC,
            "-I", os.path.join(CSRC, "compat"),
            "-o", LIB, *sources()]
+    cmd += os.environ.get("TK_NVCC_DEFS", "").split()     # experiments: e.g. -DTK_MMA_STAGES=2
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

@@ -11,8 +11,8 @@
 // TMA box of 32 rows x 128 bytes (two boxes when a row is 256 bytes) brings K and V of a
 // page into shared memory with the 128-byte swizzle that makes ldmatrix conflict-free.
 // Each of the 4 warps owns every 4th page of the chunk and runs a private ring of
-// kStages TMA stages (own mbarriers, no CTA-wide barrier in the loop), so a CTA keeps up
-// to 4*kStages page tiles in flight.  The G query heads of the group are the M rows of
+// 2-3 TMA stages (own mbarriers, no CTA-wide barrier in the loop), so a CTA keeps up to 8-12
+// page tiles in flight and three CTAs share an SM.  The G query heads of the group are the M rows of
 // m16n8k16 MMAs (rows >= G are zero padding): S = Q K^T over one page (2 n-tiles x D/16
 // k-steps), softmax in registers, O += P V (D/8 n-tiles).  FP8 pools are expanded to
 // fp16 in registers (cvt.rn.f16x2.e4m3x2, exact) with the per-page K scale folded into
@@ -23,6 +23,7 @@
 // because the op is a large contraction.  tcgen05 needs M >= 64 rows; with 4-16 query
 // rows mma.sync is the fitting instruction.
 #include "tk_kernels.cuh"
+#include "tk_merge.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -32,8 +33,18 @@ namespace tk {
 
 namespace {
 
+// Tunables (overridable at build time for experiments).  Measured on B200, 8B-shape bf16:
+// 2 stages x 3 CTAs/SM beats 3 x 2 (fewer idle slots while a CTA ramps up or merges) and 4 x 1.
+#ifndef TK_MMA_STAGES_BIG
+#define TK_MMA_STAGES_BIG 2       // tiles of 8 KB (16-bit, D=128)
+#endif
+#ifndef TK_MMA_STAGES_SMALL
+#define TK_MMA_STAGES_SMALL 3     // tiles of 4 KB (FP8, or D=64)
+#endif
+#ifndef TK_MMA_MIN_CTAS
+#define TK_MMA_MIN_CTAS 3
+#endif
 constexpr int kWarps = 4;
-constexpr int kStages = 3;
 constexpr int kPage = 16;               // tokens per page on this path
 constexpr int kBoxBytes = 32 * 128;     // one TMA box: 32 rows (K 0-15, V 16-31) x 128 B
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // bounded mbarrier wait
@@ -131,22 +142,25 @@ struct Cfg {
     static constexpr int STAGE_BYTES = NBOX * kBoxBytes;
     static constexpr int BOX_W = 128 / ESIZE;               // box width in elements
     static constexpr bool MMA_BF16 = KIND == K_BF16;        // FP8 computes in fp16
-    static constexpr int SMEM_BYTES = kWarps * kStages * STAGE_BYTES + 1024 + 128;
+    static constexpr int STAGES = STAGE_BYTES >= 8192 ? TK_MMA_STAGES_BIG : TK_MMA_STAGES_SMALL;
+    static constexpr int SMEM_BYTES = kWarps * STAGES * STAGE_BYTES + 1024 + 128;
 };
 
 // IO_BF16: type of q (relevant for FP8, where the MMA type is fp16 regardless).
 // GHI: group has more than 8 query heads (rows 8..15 of the M tile carry data).
 template <int KIND, int D, bool IO_BF16, bool GHI>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, TK_MMA_MIN_CTAS)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtrs lp, StepDev st,
                   const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q,
-                  float* __restrict__ partials, int* __restrict__ status) {
+                  float* __restrict__ partials, int* __restrict__ status, MergeOut mo, FuseAppend fa) {
     using C = Cfg<KIND, D>;
+    constexpr int kStages = C::STAGES;
     constexpr bool BF = C::MMA_BF16;
     constexpr int KS = D / 16;                              // k-steps of QK^T
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + kWarps * kStages * C::STAGE_BYTES);
+    int* s_flag = (int*)(bars + kWarps * kStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gr = lane >> 2, j = lane & 3;                 // fragment row / column-pair index
@@ -161,6 +175,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtr
     const int n_pages = (t1 - t0 + kPage - 1) / kPage;
     const int lp0 = t0 / kPage;
     const int n_w = n_pages > warp ? (n_pages - warp + kWarps - 1) / kWarps : 0;   // pages of this warp (<= 32)
+    // fused append (decode steps, 16-bit pools): row of this sequence's new token in fa.k / fa.v
+    const int new_tok = (KIND != K_FP8 && fa.k != nullptr) ? st.new_tok[b] : -1;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kWarps * kStages; i++) mbar_init(smem_u32(&bars[i]), 1);
@@ -253,6 +269,21 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtr
             sc_v = __shfl_sync(0xFFFFFFFFu, my_vs, i);
         }
 
+        if (KIND != K_FP8 && new_tok >= 0 && tok_base == ((len - 1) & ~(kPage - 1))) {
+            // This page holds the token appended by this step.  The TMA tile has the stale row:
+            // put the new K/V row into shared memory for the MMAs and into the pool for later steps.
+            const int r = (len - 1) & (kPage - 1);
+            const int page = __shfl_sync(0xFFFFFFFFu, my_page, i);
+            const int kv = lane >> 4;
+            const uint16_t* src = (const uint16_t*)(kv ? fa.v : fa.k) + ((size_t)new_tok * g.Hkv + kvh) * D;
+            uint16_t* dst = (uint16_t*)lp.pool + ((((size_t)page * g.Hkv + kvh) * 2 + kv) * kPage + r) * D;
+            for (int c = lane & 15; c < D / 8; c += 16) {
+                const uint4 val = *reinterpret_cast<const uint4*>(src + c * 8);
+                *reinterpret_cast<uint4*>(stg + (c >> 3) * kBoxBytes + swz(kv * 16 + r, c & 7)) = val;
+                *reinterpret_cast<uint4*>(dst + c * 8) = val;
+            }
+            __syncwarp();
+        }
         if (KIND != K_FP8 && n_valid < kPage) {
             // stale rows of a partly filled page: zero the V rows so 0 * garbage cannot make NaN
             for (int idx = lane; idx < (kPage - n_valid) * 8 * C::NBOX; idx += 32) {
@@ -421,12 +452,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtr
         }
         partials[partial_off(prow, kvh * G + row, g.H, D) + d] = val;
     }
+    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag);
 }
 
 template <int KIND, int D, bool IO_BF16, bool GHI>
 cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
                        const int32_t* page_table, const void* q, float* partials, int* status,
-                       cudaStream_t s) {
+                       cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
     using C = Cfg<KIND, D>;
     auto kern = decode_mma_kernel<KIND, D, IO_BF16, GHI>;
     static bool attr_done[64] = {};                         // per instantiation and device
@@ -438,19 +470,19 @@ cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
     kern<<<st.n_items, kWarps * 32, C::SMEM_BYTES, s>>>(*map, g, lp, st, page_table, (const uint16_t*)q,
-                                                        partials, status);
+                                                        partials, status, mo, fa);
     return cudaGetLastError();
 }
 
 template <int KIND, int D>
 cudaError_t launch_kd(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
                       const int32_t* page_table, const void* q, float* partials, int* status,
-                      cudaStream_t s) {
+                      cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
     const bool io_bf16 = g.io_dtype == DT_BF16, ghi = g.H / g.Hkv > 8;
-    if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, st, page_table, q, partials, status, s);
-    if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, st, page_table, q, partials, status, s);
-    if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, st, page_table, q, partials, status, s);
-    return launch_one<KIND, D, false, false>(g, lp, map, st, page_table, q, partials, status, s);
+    if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
+    if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
+    if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
+    return launch_one<KIND, D, false, false>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
 }
 
 }  // namespace
@@ -488,14 +520,17 @@ cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMa
 
 cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                               const StepDev& st, const int32_t* page_table, const void* q,
-                              float* partials, int* status, cudaStream_t s) {
+                              float* partials, int* status, cudaStream_t s, const MergeOut* merge,
+                              const FuseAppend* fuse) {
     if (st.n_items <= 0) return cudaSuccess;
+    const MergeOut mo = merge ? *merge : MergeOut{nullptr, nullptr, nullptr, 0};
+    const FuseAppend fa = fuse ? *fuse : FuseAppend{nullptr, nullptr};
     if (!decode_mma_supported(g) || st.chunk_tokens > kPage * kWarps * 32) return cudaErrorNotSupported;
-    if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, st, page_table, q, partials, status, s);
-    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd<K_BF16, 128>(g, lp, map, st, page_table, q, partials, status, s)
-                                              : launch_kd<K_BF16, 64>(g, lp, map, st, page_table, q, partials, status, s);
-    return g.D == 128 ? launch_kd<K_F16, 128>(g, lp, map, st, page_table, q, partials, status, s)
-                      : launch_kd<K_F16, 64>(g, lp, map, st, page_table, q, partials, status, s);
+    if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
+    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd<K_BF16, 128>(g, lp, map, st, page_table, q, partials, status, s, mo, fa)
+                                              : launch_kd<K_BF16, 64>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
+    return g.D == 128 ? launch_kd<K_F16, 128>(g, lp, map, st, page_table, q, partials, status, s, mo, fa)
+                      : launch_kd<K_F16, 64>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
 }
 
 }  // namespace tk

@@ -12,6 +12,7 @@
 // open page of an FP8 cache; the TMA + tensor-core kernel in decode_mma.cu is the
 // fast path for full pool pages.
 #include "tk_kernels.cuh"
+#include "tk_merge.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -68,10 +69,11 @@ __device__ __forceinline__ void load8(const uint8_t* row, int lane, float scale,
 template <int G, int EPL, bool FP8, bool BF16>
 __global__ void __launch_bounds__(kWarps * 32)
 decode_simt_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restrict__ page_table,
-                   const uint16_t* __restrict__ q, float* __restrict__ partials) {
+                   const uint16_t* __restrict__ q, float* __restrict__ partials, MergeOut mo) {
     constexpr int D = EPL * 32;
     __shared__ float qs[G][D];
     __shared__ float red[kWarps][G][D + 2];
+    __shared__ int s_flag;
 
     const int4 it = st.items[blockIdx.x];
     const int b = it.x, chunk = it.y, kvh = it.z, kind = it.w;
@@ -163,27 +165,30 @@ decode_simt_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restri
         }
         partials[partial_off(row, kvh * G + gq, g.H, D) + d] = val;
     }
+    merge_if_last(g, st, mo, b, kvh, G, partials, &s_flag);
 }
 
 template <int G, int EPL>
 cudaError_t launch_simt_ge(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
-                           const int32_t* page_table, const void* q, float* partials, cudaStream_t s) {
+                           const int32_t* page_table, const void* q, float* partials, cudaStream_t s,
+                           const MergeOut& mo) {
     const bool fp8 = g.dtype == DT_FP8, bf16 = g.io_dtype == DT_BF16;
     dim3 grid(st.n_items), block(kWarps * 32);
     const uint16_t* qq = (const uint16_t*)q;
-    if (fp8 && bf16)       decode_simt_kernel<G, EPL, true, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials);
-    else if (fp8)          decode_simt_kernel<G, EPL, true, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials);
-    else if (bf16)         decode_simt_kernel<G, EPL, false, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials);
-    else                   decode_simt_kernel<G, EPL, false, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials);
+    if (fp8 && bf16)       decode_simt_kernel<G, EPL, true, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    else if (fp8)          decode_simt_kernel<G, EPL, true, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    else if (bf16)         decode_simt_kernel<G, EPL, false, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    else                   decode_simt_kernel<G, EPL, false, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
     return cudaGetLastError();
 }
 
 template <int G>
 cudaError_t launch_simt_g(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
-                          const int32_t* page_table, const void* q, float* partials, cudaStream_t s) {
+                          const int32_t* page_table, const void* q, float* partials, cudaStream_t s,
+                          const MergeOut& mo) {
     switch (g.D) {
-        case 64:  return launch_simt_ge<G, 2>(g, lp, st, page_table, q, partials, s);
-        case 128: return launch_simt_ge<G, 4>(g, lp, st, page_table, q, partials, s);
+        case 64:  return launch_simt_ge<G, 2>(g, lp, st, page_table, q, partials, s, mo);
+        case 128: return launch_simt_ge<G, 4>(g, lp, st, page_table, q, partials, s, mo);
         default:  return cudaErrorNotSupported;
     }
 }
@@ -192,15 +197,16 @@ cudaError_t launch_simt_g(const Geometry& g, const LayerPtrs& lp, const StepDev&
 
 cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
                                const int32_t* page_table, const void* q, float* partials,
-                               cudaStream_t s) {
+                               cudaStream_t s, const MergeOut* merge) {
     if (st.n_items <= 0) return cudaSuccess;
     if (g.Hkv <= 0 || g.H % g.Hkv != 0) return cudaErrorNotSupported;
+    const MergeOut mo = merge ? *merge : MergeOut{nullptr, nullptr, nullptr, 0};
     switch (g.H / g.Hkv) {
-        case 1:  return launch_simt_g<1>(g, lp, st, page_table, q, partials, s);
-        case 2:  return launch_simt_g<2>(g, lp, st, page_table, q, partials, s);
-        case 4:  return launch_simt_g<4>(g, lp, st, page_table, q, partials, s);
-        case 8:  return launch_simt_g<8>(g, lp, st, page_table, q, partials, s);
-        case 16: return launch_simt_g<16>(g, lp, st, page_table, q, partials, s);
+        case 1:  return launch_simt_g<1>(g, lp, st, page_table, q, partials, s, mo);
+        case 2:  return launch_simt_g<2>(g, lp, st, page_table, q, partials, s, mo);
+        case 4:  return launch_simt_g<4>(g, lp, st, page_table, q, partials, s, mo);
+        case 8:  return launch_simt_g<8>(g, lp, st, page_table, q, partials, s, mo);
+        case 16: return launch_simt_g<16>(g, lp, st, page_table, q, partials, s, mo);
         default: return cudaErrorNotSupported;
     }
 }
@@ -209,12 +215,6 @@ cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const Ste
 // LSE combine.  M = max m_i, L = sum l_i e^{m_i-M}, O = sum o_i e^{m_i-M},
 // out = O * 1/(L + 1e-8f)  (the reference's normaliser, attention.cu:142).
 // ---------------------------------------------------------------------------------
-__device__ __forceinline__ void store_out(void* out, size_t idx, float v, int dt) {
-    if (dt == DT_BF16)      ((__nv_bfloat16*)out)[idx] = __float2bfloat16_rn(v);
-    else if (dt == DT_FP16) ((__half*)out)[idx] = __float2half_rn(v);
-    else                    ((float*)out)[idx] = v;
-}
-
 // grid = (H, n_seqs); block = 128 threads striding over D
 __global__ void combine_step_kernel(Geometry g, StepDev st, const float* __restrict__ partials,
                                     void* __restrict__ out, int out_dtype,

@@ -191,6 +191,9 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     plan->len.resize(n_seqs);
     plan->chunk_base.assign(n_seqs + 1, 0);
     plan->tok_b.clear(); plan->tok_pos.clear(); plan->items.clear(); plan->seals.clear();
+    plan->new_tok.assign(n_seqs, -1);
+    plan->one_token_steps = true;
+    plan->has_empty_seq = false;
 
     std::vector<int32_t> item_tokens;
     for (int i = 0; i < n_seqs; i++) {
@@ -204,6 +207,9 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         if (len_cap && len_cap[i] < len) len = len_cap[i] < 0 ? 0 : len_cap[i];   // attend to a prefix only
         plan->len[i] = len;
         int tok_base = (int)plan->tok_b.size();
+        if (add == 1) plan->new_tok[i] = tok_base;
+        if (add > 1) plan->one_token_steps = false;
+        if (len == 0) plan->has_empty_seq = true;
         for (int p = old_len; p < full_len; p++) { plan->tok_b.push_back(i); plan->tok_pos.push_back(p); }
         if (fp8)
             for (int lp = old_len / ps; (lp + 1) * ps <= full_len; lp++)

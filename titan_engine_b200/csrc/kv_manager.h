@@ -40,6 +40,9 @@ struct StepPlan {
     std::vector<int32_t> chunk_base; // [n_seqs+1] prefix sum of partial rows per sequence
     std::vector<int32_t> tok_b;      // [n_tokens] index into seq[]
     std::vector<int32_t> tok_pos;    // [n_tokens] position inside the sequence
+    std::vector<int32_t> new_tok;    // [n_seqs] row of the sequence's single new token, or -1
+    bool one_token_steps = false;    // every sequence appends at most one token (a decode step)
+    bool has_empty_seq = false;      // some sequence attends to zero tokens
     std::vector<WorkItem> items;
     std::vector<SealItem> seals;
 };

@@ -81,6 +81,7 @@ struct tk_kv {
     float* d_partials = nullptr;
     int max_partial_rows = 0, max_items = 0, max_seals = 0;
     int* d_status = nullptr;
+    int* d_counters = nullptr;           // [max_seqs * Hkv] arrival counters of the in-kernel merge
 
     size_t step_bytes = 0;
     uint8_t* d_step = nullptr;
@@ -90,7 +91,13 @@ struct tk_kv {
     int ring_pos = 0;
 
     // staging for the *_host entry point
-    void *d_k = nullptr, *d_v = nullptr, *d_q = nullptr, *d_out = nullptr;
+    void* d_q = nullptr;                 // FP32 callers: q narrowed to the io type
+    // the *_host entry points: two staging sets, so that the copies of one layer overlap the
+    // kernel of another on the copy engines (copy-in stream, caller's stream, copy-out stream)
+    void *hs_k[2] = {}, *hs_v[2] = {}, *hs_q[2] = {}, *hs_out[2] = {};
+    cudaStream_t st_in = nullptr, st_out = nullptr;
+    cudaEvent_t ev_in[2] = {}, ev_compute[2] = {}, ev_out[2] = {};
+    uint64_t host_calls = 0;
 
     std::vector<CUtensorMap> maps;       // one per layer (MMA path)
 
@@ -144,11 +151,20 @@ void release(tk_kv* h) {
         if (h->d_table) cudaFree(h->d_table);
         if (h->d_partials) cudaFree(h->d_partials);
         if (h->d_status) cudaFree(h->d_status);
+        if (h->d_counters) cudaFree(h->d_counters);
         if (h->d_step) cudaFree(h->d_step);
-        if (h->d_k) cudaFree(h->d_k);
-        if (h->d_v) cudaFree(h->d_v);
         if (h->d_q) cudaFree(h->d_q);
-        if (h->d_out) cudaFree(h->d_out);
+        for (int i = 0; i < 2; i++) {
+            if (h->hs_k[i]) cudaFree(h->hs_k[i]);
+            if (h->hs_v[i]) cudaFree(h->hs_v[i]);
+            if (h->hs_q[i]) cudaFree(h->hs_q[i]);
+            if (h->hs_out[i]) cudaFree(h->hs_out[i]);
+            if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
+            if (h->ev_compute[i]) cudaEventDestroy(h->ev_compute[i]);
+            if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
+        }
+        if (h->st_in) cudaStreamDestroy(h->st_in);
+        if (h->st_out) cudaStreamDestroy(h->st_out);
         for (int i = 0; i < kRing; i++) {
             if (h->h_step[i]) cudaFreeHost(h->h_step[i]);
             if (h->ev[i]) cudaEventDestroy(h->ev[i]);
@@ -185,7 +201,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->max_seals = c.max_step_tokens / c.page_size + c.max_seqs;
 
     // one buffer holds every per-step array; sections are 16-byte aligned
-    size_t ints = 3 * (size_t)c.max_seqs + 4 + 8 + 2 * (size_t)c.max_step_tokens + 8 +
+    size_t ints = 4 * (size_t)c.max_seqs + 4 + 12 + 2 * (size_t)c.max_step_tokens + 8 +
                   4 * (size_t)h->max_items + 4 * (size_t)h->max_seals + 2 * (size_t)kMaxDelta + 32;
     h->step_bytes = align_up(ints * 4, 256);
 
@@ -227,6 +243,8 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
                            (size_t)h->max_partial_rows * c.num_heads * (c.head_dim + 2) * sizeof(float)));
     CREATE_CUDA(cudaMalloc((void**)&h->d_status, 256));
     CREATE_CUDA(cudaMemset(h->d_status, 0, 256));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_counters, sizeof(int) * (size_t)c.max_seqs * c.num_kv_heads));
+    CREATE_CUDA(cudaMemset(h->d_counters, 0, sizeof(int) * (size_t)c.max_seqs * c.num_kv_heads));
     CREATE_CUDA(cudaMalloc((void**)&h->d_step, h->step_bytes));
     for (int i = 0; i < kRing; i++) {
         CREATE_CUDA(cudaHostAlloc((void**)&h->h_step[i], h->step_bytes, cudaHostAllocDefault));
@@ -234,10 +252,18 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     }
     const size_t kv_bytes = (size_t)c.max_step_tokens * c.num_kv_heads * c.head_dim * 2;
     const size_t q_bytes = (size_t)c.max_seqs * c.num_heads * c.head_dim * 2;
-    CREATE_CUDA(cudaMalloc(&h->d_k, kv_bytes));
-    CREATE_CUDA(cudaMalloc(&h->d_v, kv_bytes));
     CREATE_CUDA(cudaMalloc(&h->d_q, q_bytes));
-    CREATE_CUDA(cudaMalloc(&h->d_out, q_bytes));
+    for (int i = 0; i < 2; i++) {
+        CREATE_CUDA(cudaMalloc(&h->hs_k[i], kv_bytes));
+        CREATE_CUDA(cudaMalloc(&h->hs_v[i], kv_bytes));
+        CREATE_CUDA(cudaMalloc(&h->hs_q[i], q_bytes));
+        CREATE_CUDA(cudaMalloc(&h->hs_out[i], q_bytes));
+        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming));
+        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_compute[i], cudaEventDisableTiming));
+        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming));
+    }
+    CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_in, cudaStreamNonBlocking));
+    CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_out, cudaStreamNonBlocking));
 
     const bool mma_ok = tk::decode_mma_supported(h->geo);
     if (c.decode_impl == TK_DECODE_MMA && !mma_ok) {
@@ -256,7 +282,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
 }
 
 struct Sections {       // offsets (in int32 units) of the arrays inside a step buffer
-    size_t seq, len, chunk_base, tok_b, tok_pos, items, seals, delta, end;
+    size_t seq, len, chunk_base, new_tok, tok_b, tok_pos, items, seals, delta, end;
 };
 Sections sections(int n_seqs, int n_tokens, int n_items, int n_seals, int n_delta) {
     auto a4 = [](size_t x) { return (x + 3) / 4 * 4; };
@@ -265,6 +291,7 @@ Sections sections(int n_seqs, int n_tokens, int n_items, int n_seals, int n_delt
     s.seq = o;        o = a4(o + n_seqs);
     s.len = o;        o = a4(o + n_seqs);
     s.chunk_base = o; o = a4(o + n_seqs + 1);
+    s.new_tok = o;    o = a4(o + n_seqs);
     s.tok_b = o;      o = a4(o + n_tokens);
     s.tok_pos = o;    o = a4(o + n_tokens);
     s.items = o;      o = a4(o + 4 * (size_t)n_items);
@@ -452,6 +479,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     if (n_seqs) {
         memcpy(w + sec.seq, p.seq.data(), 4 * (size_t)n_seqs);
         memcpy(w + sec.len, p.len.data(), 4 * (size_t)n_seqs);
+        memcpy(w + sec.new_tok, p.new_tok.data(), 4 * (size_t)n_seqs);
     }
     memcpy(w + sec.chunk_base, p.chunk_base.data(), 4 * (size_t)(n_seqs + 1));
     if (n_tok) {
@@ -470,6 +498,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     const int32_t* d = (const int32_t*)h->d_step;
     tk::StepDev& dv = h->dev;
     dv.seq = d + sec.seq; dv.len = d + sec.len; dv.chunk_base = d + sec.chunk_base;
+    dv.new_tok = d + sec.new_tok;
     dv.tok_b = d + sec.tok_b; dv.tok_pos = d + sec.tok_pos;
     dv.items = (const int4*)(d + sec.items); dv.seals = (const int4*)(d + sec.seals);
     dv.n_seqs = n_seqs; dv.n_tokens = n_tok; dv.n_items = n_items; dv.n_seals = n_seals;
@@ -519,7 +548,8 @@ int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t*
 }
 
 static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* partial_out, cudaStream_t s,
-                       int q_dtype = -1, int out_dtype = -1) {
+                       int q_dtype = -1, int out_dtype = -1, const void* fuse_k = nullptr,
+                       const void* fuse_v = nullptr) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode: no step in progress (call tk_kv_step_begin)");
@@ -540,13 +570,19 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     if (out_dtype != TK_FP32 && out_dtype != h->cfg.io_dtype)
         return fail(h, TK_INVALID_ARG, "decode: out dtype must be FP32 or the handle's io dtype");
     const bool mma = h->use_mma && h->dev.chunk_tokens <= 2048;
+    // the last CTA of each (sequence, kv head) merges the split-KV rows itself; a sequence that
+    // attends to nothing has no CTA, so such steps keep the separate combine kernel
+    const bool fused_merge = !h->plan.has_empty_seq && getenv("TK_SEPARATE_COMBINE") == nullptr;
+    const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype};
+    const tk::FuseAppend fa{fuse_k, fuse_v};
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
     if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
     if (mma) {
         tk::StepDev pool = h->dev;
         pool.n_items = h->n_pool_items;
         if (pool.n_items > 0) {
-            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], pool, h->d_table, q, h->d_partials, h->d_status, s);
+            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], pool, h->d_table, q, h->d_partials, h->d_status, s,
+                                      &mo, &fa);
             h->launches++;
         }
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
@@ -554,26 +590,47 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
             tk::StepDev open = h->dev;
             open.items = h->dev.items + h->n_pool_items;
             open.n_items = h->dev.n_items - h->n_pool_items;
-            e = tk::launch_decode_simt(h->geo, lp, open, h->d_table, q, h->d_partials, s);
+            e = tk::launch_decode_simt(h->geo, lp, open, h->d_table, q, h->d_partials, s, &mo);
             h->launches++;
         }
     } else {
         if (h->dev.n_items > 0) {
-            e = tk::launch_decode_simt(h->geo, lp, h->dev, h->d_table, q, h->d_partials, s);
+            e = tk::launch_decode_simt(h->geo, lp, h->dev, h->d_table, q, h->d_partials, s, &mo);
             h->launches++;
         }
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
     }
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode launch: %s", cudaGetErrorString(e));
-    e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, out_dtype, partial_out, s);
-    h->launches++;
-    if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "combine launch: %s", cudaGetErrorString(e));
+    if (!fused_merge) {
+        e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, out_dtype, partial_out, s);
+        h->launches++;
+        if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "combine launch: %s", cudaGetErrorString(e));
+    }
     return TK_OK;
 }
 
 int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream) {
     return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream);
 }
+// Decode step in one launch where the shape allows it: the attention kernel writes the new
+// token's rows itself.  Otherwise the two calls it stands for.
+int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
+                        void* stream) {
+    if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (h->host_only) return fail(h, TK_CUDA_ERROR, "append_decode: handle has no device (bookkeeping only)");
+    if (!h->have_step) return fail(h, TK_INVALID_ARG, "append_decode: no step in progress (call tk_kv_step_begin)");
+    const bool fusable = h->use_mma && h->cfg.dtype != TK_FP8_E4M3 && h->plan.one_token_steps &&
+                         h->dev.chunk_tokens <= 2048 && h->dev.n_tokens > 0 && h->dev.n_seqs > 0 &&
+                         !h->plan.has_empty_seq && getenv("TK_SEPARATE_APPEND") == nullptr;
+    if (!fusable) {
+        int st = tk_kv_append(h, layer, k, v, nullptr, stream);
+        if (st != TK_OK) return st;
+        return tk_kv_decode(h, layer, q, out, stream);
+    }
+    if (!k || !v) return fail(h, TK_INVALID_ARG, "append_decode: null k/v");
+    return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream, -1, -1, k, v);
+}
+
 int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, void* out, int32_t out_dtype,
                     void* stream) {
     return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream, q_dtype, out_dtype);
@@ -590,6 +647,12 @@ int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int
     return e == cudaSuccess ? TK_OK : TK_CUDA_ERROR;
 }
 
+// Host-buffer path.  Call n uses staging set n&1:
+//   copy-in stream : (wait: kernel of call n-2 done with this set)  H2D k, v, q
+//   caller's stream: (wait: H2D done, D2H of call n-2 done)         append + decode
+//   copy-out stream: (wait: kernel done)                            D2H out
+// so the copies of neighbouring layers ride the copy engines while a kernel runs.
+// tk_kv_host_wait() makes the caller's stream wait for the outstanding D2H copies.
 static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
                                    const void* q_host, void* out_host, void* stream, bool wait) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
@@ -598,24 +661,44 @@ static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, 
     cudaStream_t s = (cudaStream_t)stream;
     const size_t kv_bytes = (size_t)h->dev.n_tokens * h->cfg.num_kv_heads * h->cfg.head_dim * 2;
     const size_t q_bytes = (size_t)h->dev.n_seqs * h->cfg.num_heads * h->cfg.head_dim * 2;
+    if (kv_bytes && (!k_host || !v_host)) return fail(h, TK_INVALID_ARG, "append_decode_host: null k/v");
+    if (q_bytes && (!q_host || !out_host)) return fail(h, TK_INVALID_ARG, "append_decode_host: null q/out");
+    const int set = (int)(h->host_calls++ & 1);
+    TK_CUDA(h, cudaStreamWaitEvent(h->st_in, h->ev_compute[set], 0));
     if (kv_bytes) {
-        if (!k_host || !v_host) return fail(h, TK_INVALID_ARG, "append_decode_host: null k/v");
-        TK_CUDA(h, cudaMemcpyAsync(h->d_k, k_host, kv_bytes, cudaMemcpyHostToDevice, s));
-        TK_CUDA(h, cudaMemcpyAsync(h->d_v, v_host, kv_bytes, cudaMemcpyHostToDevice, s));
-        int st = tk_kv_append(h, layer, h->d_k, h->d_v, nullptr, stream);
-        if (st != TK_OK) return st;
+        TK_CUDA(h, cudaMemcpyAsync(h->hs_k[set], k_host, kv_bytes, cudaMemcpyHostToDevice, h->st_in));
+        TK_CUDA(h, cudaMemcpyAsync(h->hs_v[set], v_host, kv_bytes, cudaMemcpyHostToDevice, h->st_in));
         h->stats.bytes_h2d += 2 * (int64_t)kv_bytes;
     }
     if (q_bytes) {
-        if (!q_host || !out_host) return fail(h, TK_INVALID_ARG, "append_decode_host: null q/out");
-        TK_CUDA(h, cudaMemcpyAsync(h->d_q, q_host, q_bytes, cudaMemcpyHostToDevice, s));
-        int st = tk_kv_decode(h, layer, h->d_q, h->d_out, stream);
-        if (st != TK_OK) return st;
-        TK_CUDA(h, cudaMemcpyAsync(out_host, h->d_out, q_bytes, cudaMemcpyDeviceToHost, s));
+        TK_CUDA(h, cudaMemcpyAsync(h->hs_q[set], q_host, q_bytes, cudaMemcpyHostToDevice, h->st_in));
         h->stats.bytes_h2d += (int64_t)q_bytes;
+    }
+    TK_CUDA(h, cudaEventRecord(h->ev_in[set], h->st_in));
+    TK_CUDA(h, cudaStreamWaitEvent(s, h->ev_in[set], 0));
+    TK_CUDA(h, cudaStreamWaitEvent(s, h->ev_out[set], 0));
+    int st = TK_OK;
+    if (kv_bytes && q_bytes)  st = tk_kv_append_decode(h, layer, h->hs_k[set], h->hs_v[set], h->hs_q[set], h->hs_out[set], stream);
+    else if (kv_bytes)        st = tk_kv_append(h, layer, h->hs_k[set], h->hs_v[set], nullptr, stream);
+    else if (q_bytes)         st = tk_kv_decode(h, layer, h->hs_q[set], h->hs_out[set], stream);
+    if (st != TK_OK) return st;
+    TK_CUDA(h, cudaEventRecord(h->ev_compute[set], s));
+    if (q_bytes) {
+        TK_CUDA(h, cudaStreamWaitEvent(h->st_out, h->ev_compute[set], 0));
+        TK_CUDA(h, cudaMemcpyAsync(out_host, h->hs_out[set], q_bytes, cudaMemcpyDeviceToHost, h->st_out));
+        TK_CUDA(h, cudaEventRecord(h->ev_out[set], h->st_out));
         h->stats.bytes_d2h += (int64_t)q_bytes;
     }
-    if (wait) TK_CUDA(h, cudaStreamSynchronize(s));
+    if (wait) {
+        TK_CUDA(h, cudaStreamSynchronize(s));
+        TK_CUDA(h, cudaStreamSynchronize(h->st_out));
+    }
+    return TK_OK;
+}
+
+int tk_kv_host_wait(tk_kv* h, void* stream) {
+    if (!h || h->host_only) return TK_INVALID_ARG;
+    for (int i = 0; i < 2; i++) TK_CUDA(h, cudaStreamWaitEvent((cudaStream_t)stream, h->ev_out[i], 0));
     return TK_OK;
 }
 

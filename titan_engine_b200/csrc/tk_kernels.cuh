@@ -34,6 +34,7 @@ struct StepDev {
     const int32_t* tok_pos;     // [n_tokens]
     const int4*    items;       // [n_items] (b, chunk, kvh, kind)
     const int4*    seals;       // [n_seals] (b, logical page, old_len, tok_base)
+    const int32_t* new_tok;     // [n_seqs] row of the sequence's single new token in k/v, or -1
     int n_seqs, n_tokens, n_items, n_seals, chunk_tokens;
 };
 
@@ -41,6 +42,22 @@ struct StepDev {
 __host__ __device__ inline size_t partial_off(int row, int h, int H, int D) {
     return ((size_t)row * H + h) * (size_t)(D + 2);
 }
+
+// Where the last CTA of each (sequence, kv head) puts the merged result (tk_merge.cuh).
+// counters == nullptr: no in-kernel merge; partial rows are left for launch_combine_step.
+struct MergeOut {
+    int*   counters;            // [n_seqs * Hkv] arrival counters, zero between launches
+    void*  out;                 // normalised [n_seqs][H][D] in out_dtype, or null
+    float* partial_out;         // merged, unnormalised [n_seqs][H][D+2], or null
+    int    out_dtype;
+};
+
+// Decode steps (at most one new token per sequence): the decode kernel itself writes the
+// new token's K/V rows into the page it is about to read.  k == nullptr: nothing fused.
+struct FuseAppend {
+    const void* k;              // [n_tokens][Hkv][D] 16-bit
+    const void* v;
+};
 
 cudaError_t launch_apply_delta(int32_t* table, const int2* delta, int n, cudaStream_t s);
 
@@ -52,14 +69,15 @@ cudaError_t launch_append(const Geometry& g, const LayerPtrs& lp, const StepDev&
 // cudaErrorNotSupported for shapes it has no instantiation for.
 cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
                                const int32_t* page_table, const void* q, float* partials,
-                               cudaStream_t s);
+                               cudaStream_t s, const MergeOut* merge = nullptr);
 
 // TMA + mma.sync decode (16-bit and FP8 pools, page size 16, D in {64,128}).
 bool        decode_mma_supported(const Geometry& g);
 cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out);
 cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                               const StepDev& st, const int32_t* page_table, const void* q,
-                              float* partials, int* status, cudaStream_t s);
+                              float* partials, int* status, cudaStream_t s,
+                              const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
 
 // n FP32 values -> the 16-bit type `dtype` (round to nearest even).
 cudaError_t launch_f32_to_16(const float* src, void* dst, size_t n, int dtype, cudaStream_t s);

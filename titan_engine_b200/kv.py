@@ -200,6 +200,18 @@ class PagedKVCache:
         self._check(self._lib.tk_kv_decode(self._h, layer, q.data_ptr(), out.data_ptr(), self._stream()))
         return out
 
+    def append_decode(self, layer: int, k: torch.Tensor, v: torch.Tensor, q: torch.Tensor,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """append + decode of one layer; a single fused kernel on 16-bit decode steps."""
+        self._check_io(k, self._n_tokens, self.cfg.num_kv_heads, "k")
+        self._check_io(v, self._n_tokens, self.cfg.num_kv_heads, "v")
+        self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
+        if out is None:
+            out = torch.empty_like(q)
+        self._check(self._lib.tk_kv_append_decode(self._h, layer, k.data_ptr(), v.data_ptr(), q.data_ptr(),
+                                                  out.data_ptr(), self._stream()))
+        return out
+
     def decode_partial(self, layer: int, q: torch.Tensor, partial: Optional[torch.Tensor] = None) -> torch.Tensor:
         """-> [n_seqs, H, D+2] f32: unnormalised o, then m, then l."""
         self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
@@ -223,6 +235,10 @@ class PagedKVCache:
             assert t.device.type == "cpu" and t.is_contiguous() and t.is_pinned() and t.dtype == self.io_torch_dtype
         self._check(self._lib.tk_kv_append_decode_host_async(self._h, layer, k.data_ptr(), v.data_ptr(),
                                                              q.data_ptr(), out.data_ptr(), self._stream()))
+
+    def host_wait(self) -> None:
+        """Current stream waits for the device-to-host copies queued by append_decode_host_async."""
+        self._check(self._lib.tk_kv_host_wait(self._h, self._stream()))
 
     def profile_enable(self, max_launches: int) -> None:
         self._check(self._lib.tk_kv_profile_enable(self._h, max_launches))
