@@ -1,0 +1,107 @@
+"""Multi-GPU partitioning of the paged KV path: one process per GPU, torch.distributed for the
+plumbing.
+
+The reference is single-GPU (GPU 0 only: src/memory/memory_manager.cpp:15); this module defines
+how the path shards:
+
+  * batched decode — by sequence (default) or by kv head: independent units, no collective;
+  * one very long sequence — contiguous page-aligned token ranges per rank; every rank computes
+    the merged, unnormalised (o, m, l) of its range, ONE all-gather of [n_seqs][H][D+2] floats
+    per layer exchanges them, and the log-sum-exp combine kernel consumes the gathered buffer.
+
+Nothing here computes attention: partials and the combine come from libtitan_kv.so (or, in the
+CPU tests of this logic, from the oracle through the same two callables).
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_sequences(n_seqs: int, rank: int, world: int) -> range:
+    """Contiguous block of sequence indices for `rank`; sizes differ by at most one."""
+    base, extra = divmod(n_seqs, world)
+    lo = rank * base + min(rank, extra)
+    return range(lo, lo + base + (1 if rank < extra else 0))
+
+
+def shard_kv_heads(num_kv_heads: int, num_heads: int, rank: int, world: int) -> Tuple[range, range]:
+    """(kv heads, query heads) of `rank` when the batch is smaller than the world: rank r holds
+    kv heads [r*Hkv/world, ...) and the query heads that map onto them (kv = h // (H/Hkv))."""
+    if num_kv_heads % world != 0:
+        raise ValueError(f"{num_kv_heads} kv heads do not split over {world} ranks")
+    per = num_kv_heads // world
+    g = num_heads // num_kv_heads
+    return range(rank * per, (rank + 1) * per), range(rank * per * g, (rank + 1) * per * g)
+
+
+def token_ranges(n_tokens: int, world: int, page_size: int = 16) -> List[Tuple[int, int]]:
+    """Contiguous, page-aligned [start, end) token range of every rank for one long sequence.
+    Pages are dealt out as evenly as possible; trailing ranks may be empty for short sequences."""
+    n_pages = (n_tokens + page_size - 1) // page_size
+    out = []
+    for r in range(world):
+        pr = shard_sequences(n_pages, r, world)
+        out.append((min(pr.start * page_size, n_tokens), min(pr.stop * page_size, n_tokens)))
+    return out
+
+
+def hot_cold_split(rng_tokens: Tuple[int, int], seq_len: int, hot_window: int, page_size: int = 16) -> Tuple[int, int]:
+    """(cold tokens, hot tokens) of a rank's range: a page is cold iff its last token index is
+    below seq_len - hot_window."""
+    lo, hi = rng_tokens
+    if hot_window <= 0:
+        return 0, hi - lo
+    limit = seq_len - hot_window
+    cold_end = lo
+    p = lo
+    while p < hi:
+        last = min(p + page_size, hi) - 1
+        if last < limit:
+            cold_end = min(p + page_size, hi)
+        else:
+            break
+        p += page_size
+    return cold_end - lo, hi - cold_end
+
+
+class LongContextDecoder:
+    """Decode attention for sequences whose tokens are spread over the ranks of `group`.
+
+    partial_fn(layer, q) -> tensor [n_seqs, H, D+2] float32 (o unnormalised, m, l) of THIS rank's
+    tokens; combine_fn(stacked [world, n_seqs, H, D+2]) -> [n_seqs, H, D].  With the CUDA library
+    these are PagedKVCache.decode_partial and combine_partials (below); the collective runs on
+    the current stream between them, so there is no host synchronisation in a layer.
+    """
+
+    def __init__(self, partial_fn: Callable, combine_fn: Callable, group: Optional[dist.ProcessGroup] = None):
+        self.partial_fn, self.combine_fn, self.group = partial_fn, combine_fn, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self._gathered = None
+
+    def decode(self, layer: int, q: torch.Tensor) -> torch.Tensor:
+        part = self.partial_fn(layer, q)
+        if self.world == 1:
+            return self.combine_fn(part.unsqueeze(0))
+        if self._gathered is None or self._gathered.shape[1:] != part.shape or self._gathered.device != part.device:
+            self._gathered = torch.empty((self.world,) + tuple(part.shape), dtype=part.dtype, device=part.device)
+        # concatenation along dim 0 is the same memory as the [world, ...] stack
+        flat = self._gathered.view((self.world * part.shape[0],) + tuple(part.shape[1:]))
+        dist.all_gather_into_tensor(flat, part.contiguous(), group=self.group)
+        return self.combine_fn(self._gathered)
+
+
+def combine_partials(stacked: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """CUDA log-sum-exp merge of stacked per-rank partials [R, n_seqs, H, D+2] -> [n_seqs, H, D]."""
+    from . import _lib as L
+    assert stacked.is_cuda and stacked.dtype == torch.float32 and stacked.is_contiguous()
+    r, n_seqs, h, d2 = stacked.shape
+    out = torch.empty(n_seqs, h, d2 - 2, dtype=out_dtype, device=stacked.device)
+    code = {torch.float32: L.TK_FP32, torch.float16: L.TK_FP16, torch.bfloat16: L.TK_BF16}[out_dtype]
+    st = L.lib().tk_combine_partials(stacked.data_ptr(), r, n_seqs * h, d2 - 2, out.data_ptr(), code,
+                                     torch.cuda.current_stream().cuda_stream)
+    if st != L.TK_OK:
+        raise RuntimeError(f"tk_combine_partials failed with status {st}")
+    return out
