@@ -65,8 +65,11 @@ typedef struct tk_kv_config {
     int32_t decode_impl;        /* TK_DECODE_* */
     int32_t device;             /* CUDA ordinal, -1 = current, -2 = none: page bookkeeping only,
                                    every compute call fails (there is no CPU compute path) */
-    int32_t hot_window;         /* tokens kept in HBM per sequence; 0 = everything (no cold tier) */
-    int32_t reserved[5];
+    int32_t hot_window;         /* most recent tokens of a sequence kept in HBM; 0 = everything (no cold
+                                   tier).  A page whose last token index < seq_len - hot_window is moved
+                                   to pinned host memory and staged back one layer ahead of its use. */
+    int32_t cold_pages;         /* capacity of the host pool, pages per layer (needed when hot_window > 0) */
+    int32_t reserved[4];
 } tk_kv_config;
 
 typedef struct tk_kv_stats {    /* in the style of CacheStats, src/memory/memory_manager.h:211-220 */

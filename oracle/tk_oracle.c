@@ -186,6 +186,9 @@ struct tko_mgr {
     int num_pages, max_seqs, max_pages_per_seq, page_size;
     int32_t* free_stack; int free_top;
     int32_t* page_table; int32_t* seq_len; int32_t* seq_pages;
+    /* cold tier (off unless tko_mgr_enable_cold): host-resident pages, ids from their own LIFO stack;
+     * a cold page is recorded in the table as -2 - cold_id */
+    int hot_window, num_cold_pages; int32_t* cold_stack; int cold_top;
 };
 
 tko_mgr* tko_mgr_create(int num_pages, int max_seqs, int max_pages_per_seq, int page_size) {
@@ -206,7 +209,7 @@ tko_mgr* tko_mgr_create(int num_pages, int max_seqs, int max_pages_per_seq, int 
 }
 void tko_mgr_destroy(tko_mgr* m) {
     if (!m) return;
-    free(m->free_stack); free(m->page_table); free(m->seq_len); free(m->seq_pages); free(m);
+    free(m->cold_stack); free(m->free_stack); free(m->page_table); free(m->seq_len); free(m->seq_pages); free(m);
 }
 int tko_seq_alloc(tko_mgr* m) {
     for (int i = 0; i < m->max_seqs; i++)
@@ -217,10 +220,44 @@ static int live(const tko_mgr* m, int seq) { return seq >= 0 && seq < m->max_seq
 int tko_seq_free(tko_mgr* m, int seq) {
     if (!live(m, seq)) return TKO_INVALID_ARG;
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
-    for (int i = 0; i < m->seq_pages[seq]; i++) { m->free_stack[m->free_top++] = row[i]; row[i] = -1; }
+    for (int i = 0; i < m->seq_pages[seq]; i++) {
+        if (row[i] <= -2) m->cold_stack[m->cold_top++] = -2 - row[i];
+        else              m->free_stack[m->free_top++] = row[i];
+        row[i] = -1;
+    }
     m->seq_pages[seq] = 0; m->seq_len[seq] = -1;
     return TKO_OK;
 }
+/* Cold tier.  A page is cold iff its last token index < seq_len - hot_window.  Cold ids come from
+ * a LIFO stack that pops 0,1,2,... on a fresh pool; the hot page goes back to the free stack. */
+int tko_mgr_enable_cold(tko_mgr* m, int hot_window, int num_cold_pages) {
+    if (hot_window < m->page_size || num_cold_pages <= 0 || m->cold_stack) return TKO_INVALID_ARG;
+    m->hot_window = hot_window; m->num_cold_pages = num_cold_pages;
+    m->cold_stack = (int32_t*)malloc(sizeof(int32_t) * (size_t)num_cold_pages);
+    for (int i = 0; i < num_cold_pages; i++) m->cold_stack[i] = num_cold_pages - 1 - i;
+    m->cold_top = num_cold_pages;
+    return TKO_OK;
+}
+/* Move every newly cold page of `seq` (ascending logical order) to the cold tier; stable_len is
+ * the sequence length before the current step (its tokens are already stored).  Returns the
+ * number moved, or -1 when the cold pool is exhausted (nothing is moved then). */
+int tko_evict_cold(tko_mgr* m, int seq, int stable_len) {
+    if (!live(m, seq) || !m->cold_stack) return 0;
+    int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
+    int limit = m->seq_len[seq] - m->hot_window;           /* tokens below this index are cold */
+    if (limit > stable_len) limit = stable_len;            /* but never a page the current step still writes */
+    int n_cold = limit > 0 ? limit / m->page_size : 0;     /* pages entirely below the limit */
+    int need = 0;
+    for (int i = 0; i < n_cold; i++) need += row[i] >= 0;
+    if (need > m->cold_top) return -1;
+    for (int i = 0; i < n_cold; i++) {
+        if (row[i] < 0) continue;
+        m->free_stack[m->free_top++] = row[i];
+        row[i] = -2 - m->cold_stack[--m->cold_top];
+    }
+    return need;
+}
+int tko_num_cold_used(const tko_mgr* m) { return m->cold_stack ? m->num_cold_pages - m->cold_top : 0; }
 int tko_reserve(tko_mgr* m, int seq, int n_tokens) {
     if (!live(m, seq) || n_tokens < 0) return TKO_INVALID_ARG;
     int64_t new_len = (int64_t)m->seq_len[seq] + n_tokens;
@@ -238,7 +275,11 @@ int tko_truncate(tko_mgr* m, int seq, int new_len) {
     if (!live(m, seq) || new_len < 0 || new_len > m->seq_len[seq]) return TKO_INVALID_ARG;
     int keep = (new_len + m->page_size - 1) / m->page_size;
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
-    for (int i = keep; i < m->seq_pages[seq]; i++) { m->free_stack[m->free_top++] = row[i]; row[i] = -1; }
+    for (int i = keep; i < m->seq_pages[seq]; i++) {
+        if (row[i] <= -2) m->cold_stack[m->cold_top++] = -2 - row[i];
+        else              m->free_stack[m->free_top++] = row[i];
+        row[i] = -1;
+    }
     m->seq_pages[seq] = keep; m->seq_len[seq] = new_len;
     return TKO_OK;
 }
@@ -285,6 +326,11 @@ uint64_t tko_state_digest(const tko_mgr* m) {
     int32_t top = m->free_top;
     h = fnv(h, &top, sizeof(top));
     h = fnv(h, m->free_stack, sizeof(int32_t) * (size_t)m->free_top);
+    if (m->cold_stack) {
+        int32_t ct = m->cold_top;
+        h = fnv(h, &ct, sizeof(ct));
+        h = fnv(h, m->cold_stack, sizeof(int32_t) * (size_t)m->cold_top);
+    }
     return h;
 }
 

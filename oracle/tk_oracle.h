@@ -60,6 +60,9 @@ int      tko_seq_free(tko_mgr* m, int seq);
 int      tko_reserve(tko_mgr* m, int seq, int n_tokens);
 int      tko_truncate(tko_mgr* m, int seq, int new_len);
 int      tko_adopt(tko_mgr* m, int seq, const int32_t* pages, int n_pages, int seq_len);
+int      tko_mgr_enable_cold(tko_mgr* m, int hot_window, int num_cold_pages);
+int      tko_evict_cold(tko_mgr* m, int seq, int stable_len);   /* pages moved, -1 if the cold pool is full */
+int      tko_num_cold_used(const tko_mgr* m);
 int      tko_seq_len(const tko_mgr* m, int seq);       /* -1 if seq not live */
 int      tko_seq_num_pages(const tko_mgr* m, int seq);
 int      tko_num_free_pages(const tko_mgr* m);

@@ -57,6 +57,9 @@ def lib() -> C.CDLL:
             "tko_reserve": (i, [vp, i, i]),
             "tko_truncate": (i, [vp, i, i]),
             "tko_adopt": (i, [vp, i, vp, i, i]),
+            "tko_mgr_enable_cold": (i, [vp, i, i]),
+            "tko_evict_cold": (i, [vp, i, i]),
+            "tko_num_cold_used": (i, [vp]),
             "tko_seq_len": (i, [vp, i]),
             "tko_seq_num_pages": (i, [vp, i]),
             "tko_num_free_pages": (i, [vp]),
@@ -155,6 +158,9 @@ class Manager:
         p = _c(pages, np.int32)
         return self.l.tko_adopt(self.h, s, _p(p), len(p), seq_len)
 
+    def enable_cold(self, hot_window, num_cold_pages): return self.l.tko_mgr_enable_cold(self.h, hot_window, num_cold_pages)
+    def evict_cold(self, s, stable_len): return self.l.tko_evict_cold(self.h, s, stable_len)
+    def num_cold_used(self): return self.l.tko_num_cold_used(self.h)
     def seq_len(self, s): return self.l.tko_seq_len(self.h, s)
     def num_free_pages(self): return self.l.tko_num_free_pages(self.h)
     def slot(self, s, pos): return self.l.tko_slot(self.h, s, pos)

@@ -62,7 +62,7 @@ class Twin:
     """
 
     def __init__(self, L, H, Hkv, D, num_pages, max_seqs, mpps, dtype="bf16", impl="auto",
-                 chunk_tokens=0, max_step_tokens=4096, io=None, seed=0):
+                 chunk_tokens=0, max_step_tokens=4096, io=None, seed=0, hot_window=0, cold_pages=0):
         import torch
         from titan_engine_b200 import PagedKVCache
         self.torch = torch
@@ -70,9 +70,19 @@ class Twin:
         self.dt = DT[dtype]
         self.carrier = DT[io] if io else (O.BF16 if self.dt == O.FP8 else self.dt)
         self.gpu = PagedKVCache(L, H, Hkv, D, num_pages, max_seqs, mpps, dtype=dtype, io_dtype=io,
-                                decode_impl=impl, chunk_tokens=chunk_tokens, max_step_tokens=max_step_tokens)
+                                decode_impl=impl, chunk_tokens=chunk_tokens, max_step_tokens=max_step_tokens,
+                                hot_window=hot_window, cold_pages=cold_pages)
         self.mgr = O.Manager(num_pages, max_seqs, mpps, 16)
-        self.pools = [O.Pool(self.dt, num_pages, H, Hkv, D, max_seqs, mpps, 16, self.carrier) for _ in range(L)]
+        # With a cold tier the oracle keeps two managers: `mgr` follows the tiering rule (page/slot
+        # state parity), `flat` holds the same logical data in one untiered pool (attention parity:
+        # where a page lives must not change any result).
+        self.tiered = hot_window > 0
+        self.flat = None
+        if self.tiered:
+            assert self.mgr.enable_cold(hot_window, cold_pages) == O.OK
+            self.flat = O.Manager(num_pages + cold_pages, max_seqs, mpps, 16)
+        data_pages = num_pages + cold_pages
+        self.pools = [O.Pool(self.dt, data_pages, H, Hkv, D, max_seqs, mpps, 16, self.carrier) for _ in range(L)]
         self.g = rng(seed)
         self.dev = self.gpu.device
         self.max_err = 0.0
@@ -80,11 +90,15 @@ class Twin:
     def seq_alloc(self):
         a, b = self.gpu.seq_alloc(), self.mgr.seq_alloc()
         assert a == b
+        if self.flat:
+            assert self.flat.seq_alloc() == a
         return a
 
     def seq_free(self, s):
         self.gpu.seq_free(s)
         assert self.mgr.seq_free(s) == O.OK
+        if self.flat:
+            assert self.flat.seq_free(s) == O.OK
 
     def adopt(self, s, pages, seq_len):
         """Install a caller-chosen page list (a shuffled pool) on both sides."""
@@ -98,8 +112,13 @@ class Twin:
         self.gpu.step_begin(seq_ids, n_new)
         for s, n in zip(seq_ids, n_new):
             assert self.mgr.reserve(s, n) == O.OK
+            if self.flat:
+                assert self.flat.reserve(s, n) == O.OK
+        if self.tiered:                                   # after every reservation of the step, in call order
+            for s, o in zip(seq_ids, old):               # never a page the step itself is still writing
+                assert self.mgr.evict_cold(s, o) >= 0
         assert self.gpu.digest() == self.mgr.digest(), "page/slot state diverged from the oracle"
-        table = self.mgr.table()
+        table = (self.flat or self.mgr).table()
         tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seq_ids, n_new)] or [np.zeros(0, np.int32)])
         tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)] or [np.zeros(0, np.int32)])
         nt = len(tok_seq)
@@ -123,6 +142,8 @@ class Twin:
                 slots = torch.full((max(nt, 1),), -7, dtype=torch.int64, device=self.dev)
                 if nt:
                     self.gpu.append(layer, to_torch16(k16, self.carrier, self.dev), to_torch16(v16, self.carrier, self.dev), slots)
+                    if self.tiered:                       # device slots follow the tiered manager
+                        want_slots = np.array([self.mgr.slot(int(a), int(b)) for a, b in zip(tok_seq, tok_pos)], dtype=np.int64)
                     np.testing.assert_array_equal(slots[:nt].cpu().numpy(), want_slots)
                 got = None
                 if decode:

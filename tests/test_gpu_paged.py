@@ -243,3 +243,29 @@ def test_churn_small_bit_exact_and_close():
         ids = sorted(live) + new
         t.step(ids, [1] * len(live) + [int(g.integers(16, 200)) for _ in new], check_pool=(step % 4 == 0))
         live = ids
+
+
+@pytest.mark.parametrize("impl", IMPLS)
+def test_cold_tier_eviction_and_prefetch(impl):
+    """Pages older than the hot window move to pinned host memory and are staged back one layer
+    ahead.  State (page ids, cold ids, free lists) is bit-exact against the oracle's tiering rule;
+    attention equals the untiered oracle: where a page lives must not change any result."""
+    t = Twin(3, 32, 8, 128, 80, 3, 200, dtype="bf16", impl=impl, max_step_tokens=4096, seed=60,
+             hot_window=128, cold_pages=400)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a, b], [1000, 100])                  # pages written by this step stay hot for it
+    assert t.gpu.stats()["pages_cold"] == 0
+    t.step([a, b], [1, 1])                       # a: 54 pages go cold at once; b: entirely hot
+    st = t.gpu.stats()
+    assert st["pages_cold"] == (1001 - 128) // 16 and st["evictions"] == st["pages_cold"]
+    assert t.gpu.num_free_pages == 80 - (63 - 54) - 7
+    for i in range(40):                          # decode steps: pages keep falling out of the window
+        t.step([a, b], [1, 1], fused=(i % 2 == 0))
+    st = t.gpu.stats()
+    assert st["pages_cold"] == (1041 - 128) // 16 + (141 - 128) // 16
+    assert st["prefetch_hits"] > 0 and st["prefetch_misses"] > 0 and st["bytes_d2h"] > 0
+    t.seq_free(a)                                # cold ids go back to their own free list
+    c = t.seq_alloc()
+    t.step([c, b], [500, 1])
+    t.step([c, b], [1, 1], fused=True)           # 23 of c's pages are cold now
+    assert t.gpu.seq_len(c) == 501 and t.gpu.stats()["pages_cold"] == (501 - 128) // 16 + (143 - 128) // 16

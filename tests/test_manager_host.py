@@ -185,3 +185,42 @@ def test_churn_matches_oracle_manager_bit_exact(seed):
         pos = c.seq_len(s) - 1
         assert c.slot(s, pos) == o.slot(s, pos)
     assert c.stats()["page_frees"] > 0
+
+
+def test_cold_tier_state_matches_oracle_manager():
+    """Window-driven eviction: page ids, cold ids and both free lists equal the oracle's."""
+    num_pages, cold_pages, max_seqs, mpps, window = 64, 200, 4, 128, 64
+    c = PagedKVCache(2, 8, 2, 64, num_pages, max_seqs, mpps, dtype="fp16", host_only=True,
+                     max_step_tokens=4096, hot_window=window, cold_pages=cold_pages)
+    o = O.Manager(num_pages, max_seqs, mpps, 16)
+    assert o.enable_cold(window, cold_pages) == O.OK
+    a, b = c.seq_alloc(), c.seq_alloc()
+    assert (o.seq_alloc(), o.seq_alloc()) == (a, b)
+
+    def step(ids, n_new):
+        old = [c.seq_len(s) for s in ids]
+        c.step_begin(ids, n_new)
+        for s, n in zip(ids, n_new):
+            assert o.reserve(s, n) == O.OK
+        for s, ol in zip(ids, old):
+            assert o.evict_cold(s, ol) >= 0
+        assert c.digest() == o.digest()
+
+    step([a, b], [300, 50])                      # pages written by this very step stay hot ...
+    assert c.stats()["pages_cold"] == 0
+    step([a, b], [0, 0])                         # ... a: 300-64=236 -> 14 pages cold; b: none
+    assert c.stats()["pages_cold"] == 14 == o.num_cold_used()
+    assert c.num_free_pages == num_pages - (19 - 14) - 4
+    assert c.slot(a, 0) == -1 and c.slot(a, 299) >= 0          # cold tokens have no device slot
+    for _ in range(40):
+        step([a, b], [1, 1])
+    assert c.stats()["pages_cold"] == (340 - 64) // 16 + (90 - 64) // 16
+    c.seq_free(a); assert o.seq_free(a) == O.OK
+    assert c.digest() == o.digest() and c.stats()["pages_cold"] == 1
+    d = c.seq_alloc(); assert o.seq_alloc() == d
+    step([d, b], [700, 1])                       # 44 pages, 39 of them cold from the next step on
+    step([d, b], [1, 1])
+    assert c.stats()["pages_cold"] == (701 - 64) // 16 + (92 - 64) // 16
+    assert c.seq_len(d) == 701 and c.stats()["evictions"] == o.num_cold_used() + 17
+    with pytest.raises(KvError):
+        PagedKVCache(2, 8, 2, 64, 8, 2, 8, dtype="fp8", host_only=True, hot_window=64, cold_pages=8)

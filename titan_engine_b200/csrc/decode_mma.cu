@@ -150,7 +150,7 @@ struct Cfg {
 // GHI: group has more than 8 query heads (rows 8..15 of the M tile carry data).
 template <int KIND, int D, bool IO_BF16, bool GHI>
 __global__ void __launch_bounds__(kWarps * 32, TK_MMA_MIN_CTAS)
-decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtrs lp, StepDev st,
+decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_cold, Geometry g, LayerPtrs lp, StepDev st,
                   const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q,
                   float* __restrict__ partials, int* __restrict__ status, MergeOut mo, FuseAppend fa) {
     using C = Cfg<KIND, D>;
@@ -203,9 +203,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtr
             const uint32_t bar = smem_u32(&bars[warp * kStages + s]);
             const uint32_t dst = smem_u32(wstage + (size_t)s * C::STAGE_BYTES);
             mbar_expect_tx(bar, C::STAGE_BYTES);
-            const int row = (page * g.Hkv + kvh) * 32;
+            const CUtensorMap* src = (page & kColdBit) ? &tmap_cold : &tmap;   // cold pages come from the staged copy
+            const int row = ((page & ~kColdBit) * g.Hkv + kvh) * 32;
 #pragma unroll
-            for (int h = 0; h < C::NBOX; h++) tma_load_2d(dst + h * kBoxBytes, &tmap, h * C::BOX_W, row, bar);
+            for (int h = 0; h < C::NBOX; h++) tma_load_2d(dst + h * kBoxBytes, src, h * C::BOX_W, row, bar);
         }
     };
     for (int i = 0; i < kStages && i < n_w; i++) issue(i);
@@ -456,7 +457,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, LayerPtr
 }
 
 template <int KIND, int D, bool IO_BF16, bool GHI>
-cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
+cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
+                       const CUtensorMap* map_cold, const StepDev& st,
                        const int32_t* page_table, const void* q, float* partials, int* status,
                        cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
     using C = Cfg<KIND, D>;
@@ -469,20 +471,21 @@ cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    kern<<<st.n_items, kWarps * 32, C::SMEM_BYTES, s>>>(*map, g, lp, st, page_table, (const uint16_t*)q,
+    kern<<<st.n_items, kWarps * 32, C::SMEM_BYTES, s>>>(*map, *map_cold, g, lp, st, page_table, (const uint16_t*)q,
                                                         partials, status, mo, fa);
     return cudaGetLastError();
 }
 
 template <int KIND, int D>
-cudaError_t launch_kd(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
+cudaError_t launch_kd(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
+                      const CUtensorMap* map_cold, const StepDev& st,
                       const int32_t* page_table, const void* q, float* partials, int* status,
                       cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
     const bool io_bf16 = g.io_dtype == DT_BF16, ghi = g.H / g.Hkv > 8;
-    if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
-    if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
-    if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
-    return launch_one<KIND, D, false, false>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
+    if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
+    if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
+    if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
+    return launch_one<KIND, D, false, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
 }
 
 }  // namespace
@@ -519,18 +522,19 @@ cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMa
 }
 
 cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
-                              const StepDev& st, const int32_t* page_table, const void* q,
+                              const CUtensorMap* map_cold, const StepDev& st, const int32_t* page_table, const void* q,
                               float* partials, int* status, cudaStream_t s, const MergeOut* merge,
                               const FuseAppend* fuse) {
     if (st.n_items <= 0) return cudaSuccess;
     const MergeOut mo = merge ? *merge : MergeOut{nullptr, nullptr, nullptr, 0};
     const FuseAppend fa = fuse ? *fuse : FuseAppend{nullptr, nullptr};
+    if (!map_cold) map_cold = map;
     if (!decode_mma_supported(g) || st.chunk_tokens > kPage * kWarps * 32) return cudaErrorNotSupported;
-    if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
-    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd<K_BF16, 128>(g, lp, map, st, page_table, q, partials, status, s, mo, fa)
-                                              : launch_kd<K_BF16, 64>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
-    return g.D == 128 ? launch_kd<K_F16, 128>(g, lp, map, st, page_table, q, partials, status, s, mo, fa)
-                      : launch_kd<K_F16, 64>(g, lp, map, st, page_table, q, partials, status, s, mo, fa);
+    if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
+    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd<K_BF16, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa)
+                                              : launch_kd<K_BF16, 64>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
+    return g.D == 128 ? launch_kd<K_F16, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa)
+                      : launch_kd<K_F16, 64>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
 }
 
 }  // namespace tk

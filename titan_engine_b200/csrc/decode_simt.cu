@@ -119,7 +119,11 @@ decode_simt_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restri
         } else {
             const uint16_t* kt;
             if (FP8) kt = (const uint16_t*)lp.open_pages + ((size_t)seq * g.Hkv + kvh) * 2 * ps * D + (size_t)r * D;
-            else     kt = (const uint16_t*)lp.pool + ((size_t)prow[t / ps] * g.Hkv + kvh) * 2 * ps * D + (size_t)r * D;
+            else {
+                const int pg = prow[t / ps];
+                const uint16_t* base = (const uint16_t*)((pg & kColdBit) ? lp.cold_stage : lp.pool);
+                kt = base + ((size_t)(pg & ~kColdBit) * g.Hkv + kvh) * 2 * ps * D + (size_t)r * D;
+            }
             load16<EPL, BF16>(kt, lane, kf);
             load16<EPL, BF16>(kt + (size_t)ps * D, lane, vf);
         }

@@ -47,7 +47,8 @@ int PageManager::seq_free(int seq) {
     if (!live(seq)) return ST_INVALID_ARG;
     const int32_t* r = row(seq);
     for (int i = 0; i < seq_pages_[seq]; i++) {
-        free_stack_.push_back(r[i]);
+        if (r[i] <= -2) cold_stack_.push_back(-2 - r[i]);
+        else            free_stack_.push_back(r[i]);
         set_entry(seq, i, -1);
     }
     counters.page_frees += seq_pages_[seq];
@@ -79,7 +80,8 @@ int PageManager::truncate(int seq, int new_len) {
     int keep = (new_len + page_size_ - 1) / page_size_;
     const int32_t* r = row(seq);
     for (int i = keep; i < seq_pages_[seq]; i++) {
-        free_stack_.push_back(r[i]);
+        if (r[i] <= -2) cold_stack_.push_back(-2 - r[i]);
+        else            free_stack_.push_back(r[i]);
         set_entry(seq, i, -1);
         counters.page_frees++;
     }
@@ -109,9 +111,42 @@ int PageManager::adopt(int seq, const int32_t* pages, int n_pages, int seq_len) 
     return ST_OK;
 }
 
+int PageManager::enable_cold(int hot_window, int num_cold_pages) {
+    if (hot_window < page_size_ || num_cold_pages <= 0 || cold_enabled()) return ST_INVALID_ARG;
+    hot_window_ = hot_window;
+    num_cold_pages_ = num_cold_pages;
+    cold_stack_.resize(num_cold_pages);
+    for (int i = 0; i < num_cold_pages; i++) cold_stack_[i] = num_cold_pages - 1 - i;   // pops give 0,1,2,...
+    return ST_OK;
+}
+
+int PageManager::evict_cold(int seq, int stable_len, std::vector<Eviction>* moved) {
+    if (!live(seq) || !cold_enabled()) return 0;
+    const int32_t* r = row(seq);
+    int limit = seq_len_[seq] - hot_window_;                // tokens below this index are cold ...
+    if (limit > stable_len) limit = stable_len;             // ... but never a page this step still writes
+    const int n_cold = limit > 0 ? limit / page_size_ : 0;  // pages that lie entirely below it
+    int need = 0;
+    for (int i = 0; i < n_cold; i++) need += r[i] >= 0;
+    if (need > (int)cold_stack_.size()) return -1;
+    for (int i = 0; i < n_cold; i++) {
+        if (r[i] < 0) continue;
+        const int32_t hot = r[i], cold = cold_stack_.back();
+        cold_stack_.pop_back();
+        free_stack_.push_back(hot);
+        set_entry(seq, i, -2 - cold);
+        if (cold + 1 > cold_high_water_) cold_high_water_ = cold + 1;
+        if (moved) moved->push_back({hot, cold});
+    }
+    counters.evictions += need;
+    return need;
+}
+
 int64_t PageManager::slot(int seq, int pos) const {
     if (!live(seq) || pos < 0 || pos >= seq_len_[seq]) return -1;
-    return (int64_t)row(seq)[pos / page_size_] * page_size_ + pos % page_size_;
+    const int32_t page = row(seq)[pos / page_size_];
+    if (page < 0) return -1;                               // cold pages have no device slot
+    return (int64_t)page * page_size_ + pos % page_size_;
 }
 
 static uint64_t fnv(uint64_t h, const void* p, size_t n) {
@@ -127,6 +162,11 @@ uint64_t PageManager::digest() const {
     int32_t top = (int32_t)free_stack_.size();
     h = fnv(h, &top, sizeof(top));
     h = fnv(h, free_stack_.data(), sizeof(int32_t) * free_stack_.size());
+    if (cold_enabled()) {
+        int32_t ct = (int32_t)cold_stack_.size();
+        h = fnv(h, &ct, sizeof(ct));
+        h = fnv(h, cold_stack_.data(), sizeof(int32_t) * cold_stack_.size());
+    }
     return h;
 }
 
@@ -191,11 +231,14 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     plan->len.resize(n_seqs);
     plan->chunk_base.assign(n_seqs + 1, 0);
     plan->tok_b.clear(); plan->tok_pos.clear(); plan->items.clear(); plan->seals.clear();
+    plan->evictions.clear();
     plan->new_tok.assign(n_seqs, -1);
     plan->one_token_steps = true;
     plan->has_empty_seq = false;
 
     std::vector<int32_t> item_tokens;
+    std::vector<int32_t> old_lens(n_seqs);
+    for (int i = 0; i < n_seqs; i++) old_lens[i] = seq_len_[seqs[i]];
     for (int i = 0; i < n_seqs; i++) {
         int s = seqs[i];
         int add = n_new ? n_new[i] : 0;
@@ -231,6 +274,9 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         }
         plan->chunk_base[i + 1] = plan->chunk_base[i] + rows;
     }
+    // after every reservation of the step: pages that fell out of the hot window go cold
+    if (cold_enabled())
+        for (int i = 0; i < n_seqs; i++) evict_cold(seqs[i], old_lens[i], &plan->evictions);
     // biggest items first, so the short tails fill the end of the schedule
     std::vector<int32_t> order(plan->items.size());
     for (size_t i = 0; i < order.size(); i++) order[i] = (int32_t)i;

@@ -33,6 +33,11 @@ struct SealItem {      // FP8: one logical page completed by this step
     int32_t tok_base;  // index of the sequence's first new token in the step's token list
 };
 
+struct Eviction {      // a page that moved from the device pool to the host (cold) pool
+    int32_t hot_page;
+    int32_t cold_id;
+};
+
 struct StepPlan {
     int32_t chunk_tokens = 0;
     std::vector<int32_t> seq;        // [n_seqs] sequence slot ids
@@ -45,6 +50,7 @@ struct StepPlan {
     bool has_empty_seq = false;      // some sequence attends to zero tokens
     std::vector<WorkItem> items;
     std::vector<SealItem> seals;
+    std::vector<Eviction> evictions; // pages that went cold in this step (copy out before reuse)
 };
 
 class PageManager {
@@ -56,6 +62,16 @@ public:
     int  reserve(int seq, int n_tokens);           // status
     int  truncate(int seq, int new_len);           // status
     int  adopt(int seq, const int32_t* pages, int n_pages, int seq_len);  // status
+    // Cold tier: a page is cold iff its last token index < seq_len - hot_window.  Cold pages
+    // live in a host pool with its own LIFO id stack; the table holds -2 - cold_id for them.
+    // The idiom is the reference's expert cache (evict, count, keep a host copy:
+    // src/memory/memory_manager.cpp:266-278) with the eviction order fixed by the window.
+    int  enable_cold(int hot_window, int num_cold_pages);                  // status
+    int  evict_cold(int seq, int stable_len, std::vector<Eviction>* moved); // pages moved, -1 = cold pool full;
+                                                                           // stable_len = length before the current step
+    bool cold_enabled() const { return hot_window_ > 0; }
+    int  num_cold_used() const { return num_cold_pages_ - (int)cold_stack_.size(); }
+    int  cold_high_water() const { return cold_high_water_; }
     bool live(int seq) const { return seq >= 0 && seq < max_seqs_ && seq_len_[seq] >= 0; }
     int  seq_len(int seq) const { return live(seq) ? seq_len_[seq] : -1; }
     int  seq_pages(int seq) const { return live(seq) ? seq_pages_[seq] : -1; }
@@ -84,7 +100,7 @@ public:
                   bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
                   int max_partial_rows, StepPlan* plan, const int32_t* len_cap = nullptr);
 
-    struct Counters { int64_t page_allocs = 0, page_frees = 0, seq_allocs = 0, seq_frees = 0; } counters;
+    struct Counters { int64_t page_allocs = 0, page_frees = 0, seq_allocs = 0, seq_frees = 0, evictions = 0; } counters;
 
 private:
     void set_entry(int seq, int idx, int32_t value);
@@ -93,6 +109,8 @@ private:
     std::vector<int32_t> table_;        // [max_seqs][max_pages_per_seq], -1 = unmapped
     std::vector<int32_t> seq_len_;      // -1 = slot free
     std::vector<int32_t> seq_pages_;
+    int hot_window_ = 0, num_cold_pages_ = 0, cold_high_water_ = 0;
+    std::vector<int32_t> cold_stack_;   // back() is the next cold id handed out
     std::vector<std::pair<int32_t, int32_t>> delta_;
     std::vector<uint32_t> delta_stamp_;  // per table index: generation of the last compaction that saw it
     uint32_t delta_gen_ = 0;

@@ -60,6 +60,12 @@ const char* validate(const tk_kv_config& c) {
     if (c.max_step_tokens <= 0) return "max_step_tokens must be positive";
     if (c.chunk_tokens < 0 || c.chunk_tokens % c.page_size != 0) return "chunk_tokens must be a multiple of page_size";
     if (c.decode_impl < TK_DECODE_AUTO || c.decode_impl > TK_DECODE_MMA) return "bad decode_impl";
+    if (c.hot_window < 0 || c.cold_pages < 0) return "hot_window and cold_pages must not be negative";
+    if (c.hot_window > 0) {
+        if (c.hot_window < c.page_size) return "hot_window must cover at least one page";
+        if (c.cold_pages == 0) return "hot_window needs cold_pages > 0";
+        if (c.dtype == TK_FP8_E4M3) return "the cold tier needs 16-bit storage";
+    }
     return nullptr;
 }
 
@@ -100,6 +106,16 @@ struct tk_kv {
     uint64_t host_calls = 0;
 
     std::vector<CUtensorMap> maps;       // one per layer (MMA path)
+
+    // cold tier (hot_window > 0): pages older than the window live in pinned host memory and are
+    // staged back, one layer ahead of use, into a two-slot device ring indexed by cold id
+    uint8_t* h_cold = nullptr;           // pinned [L][cold_pages][page_bytes]
+    uint8_t* d_stage[2] = {};            // device [cold_pages][page_bytes]
+    size_t page_bytes = 0;
+    cudaStream_t st_pf = nullptr, st_ev = nullptr;
+    cudaEvent_t ev_pf[2] = {}, ev_used[2] = {}, ev_user = nullptr, ev_evict = nullptr;
+    int staged_layer[2] = {-1, -1};
+    CUtensorMap stage_maps[2];
 
     tk::StepPlan plan;
     tk::StepDev dev{};
@@ -170,6 +186,16 @@ void release(tk_kv* h) {
             if (h->ev[i]) cudaEventDestroy(h->ev[i]);
         }
         for (cudaEvent_t e : h->prof_ev) cudaEventDestroy(e);
+        if (h->h_cold) cudaFreeHost(h->h_cold);
+        for (int i = 0; i < 2; i++) {
+            if (h->d_stage[i]) cudaFree(h->d_stage[i]);
+            if (h->ev_pf[i]) cudaEventDestroy(h->ev_pf[i]);
+            if (h->ev_used[i]) cudaEventDestroy(h->ev_used[i]);
+        }
+        if (h->ev_user) cudaEventDestroy(h->ev_user);
+        if (h->ev_evict) cudaEventDestroy(h->ev_evict);
+        if (h->st_pf) cudaStreamDestroy(h->st_pf);
+        if (h->st_ev) cudaStreamDestroy(h->st_ev);
     }
     delete h->mgr;
     delete h;
@@ -191,6 +217,8 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->mgr = new tk::PageManager(c.num_pages, c.max_seqs, c.max_pages_per_seq, c.page_size);
     h->lay = arena_layout(c);
     h->host_only = c.device == TK_DEVICE_NONE;
+    h->page_bytes = (size_t)c.num_kv_heads * 2 * c.page_size * c.head_dim * (c.dtype == TK_FP8_E4M3 ? 1 : 2);
+    if (c.hot_window > 0) h->mgr->enable_cold(c.hot_window, c.cold_pages);
     h->stats.pages_total = c.num_pages;
 
     const int min_chunk = c.chunk_tokens ? c.chunk_tokens : 128;
@@ -275,9 +303,70 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
         h->maps.resize(c.num_layers);
         for (int l = 0; l < c.num_layers; l++) CREATE_CUDA(tk::make_pool_tensor_map(h->geo, h->layer(l).pool, &h->maps[l]));
     }
+    if (c.hot_window > 0) {
+        const size_t layer_bytes = (size_t)c.cold_pages * h->page_bytes;
+        CREATE_CUDA(cudaHostAlloc((void**)&h->h_cold, layer_bytes * c.num_layers, cudaHostAllocDefault));
+        tk::Geometry cold_geo = h->geo;
+        cold_geo.num_pages = c.cold_pages;
+        for (int i = 0; i < 2; i++) {
+            CREATE_CUDA(cudaMalloc((void**)&h->d_stage[i], layer_bytes));
+            CREATE_CUDA(cudaMemset(h->d_stage[i], 0, layer_bytes));
+            CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_pf[i], cudaEventDisableTiming));
+            CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_used[i], cudaEventDisableTiming));
+            if (h->use_mma) CREATE_CUDA(tk::make_pool_tensor_map(cold_geo, h->d_stage[i], &h->stage_maps[i]));
+        }
+        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_user, cudaEventDisableTiming));
+        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_evict, cudaEventDisableTiming));
+        CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_pf, cudaStreamNonBlocking));
+        CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_ev, cudaStreamNonBlocking));
+    }
     CREATE_CUDA(cudaDeviceSynchronize());
 #undef CREATE_CUDA
     *out = h;
+    return TK_OK;
+}
+
+// device encoding of a host page-table entry: cold pages (-2 - id on the host) carry kColdBit
+inline int32_t dev_entry(int32_t v) { return v <= -2 ? (tk::kColdBit | (-2 - v)) : v; }
+
+// Copy pages that just went cold, for every layer, device pool -> pinned host pool.  Runs on the
+// eviction stream after the caller's stream has finished with the pages; the caller's stream
+// (whose later appends may reuse them) and the prefetch stream then wait for the copies.
+int run_evictions(tk_kv* h, const std::vector<tk::Eviction>& ev, cudaStream_t s) {
+    if (ev.empty()) return TK_OK;
+    TK_CUDA(h, cudaEventRecord(h->ev_user, s));
+    TK_CUDA(h, cudaStreamWaitEvent(h->st_ev, h->ev_user, 0));
+    const size_t pb = h->page_bytes, cold_layer = (size_t)h->cfg.cold_pages * pb;
+    for (size_t i = 0; i < ev.size();) {
+        size_t j = i + 1;                                   // runs with consecutive ids on both sides: one copy
+        while (j < ev.size() && ev[j].hot_page == ev[j - 1].hot_page + 1 && ev[j].cold_id == ev[j - 1].cold_id + 1) j++;
+        for (int l = 0; l < h->cfg.num_layers; l++)
+            TK_CUDA(h, cudaMemcpyAsync(h->h_cold + cold_layer * l + (size_t)ev[i].cold_id * pb,
+                                       (const uint8_t*)h->layer(l).pool + (size_t)ev[i].hot_page * pb, (j - i) * pb,
+                                       cudaMemcpyDeviceToHost, h->st_ev));
+        i = j;
+    }
+    TK_CUDA(h, cudaEventRecord(h->ev_evict, h->st_ev));
+    TK_CUDA(h, cudaStreamWaitEvent(s, h->ev_evict, 0));
+    TK_CUDA(h, cudaStreamWaitEvent(h->st_pf, h->ev_evict, 0));
+    h->stats.bytes_d2h += (int64_t)ev.size() * (int64_t)pb * h->cfg.num_layers;
+    return TK_OK;
+}
+
+// Stage layer `layer`'s cold pages into ring slot layer&1 on the prefetch stream.
+int prefetch_layer(tk_kv* h, int layer, bool ahead) {
+    const int n = h->mgr->cold_high_water();
+    if (n == 0 || layer < 0 || layer >= h->cfg.num_layers) return TK_OK;
+    const int slot = layer & 1;
+    if (h->staged_layer[slot] == layer) return TK_OK;
+    const size_t bytes = (size_t)n * h->page_bytes;
+    TK_CUDA(h, cudaStreamWaitEvent(h->st_pf, h->ev_used[slot], 0));     // the kernel that last read this slot
+    TK_CUDA(h, cudaMemcpyAsync(h->d_stage[slot], h->h_cold + (size_t)h->cfg.cold_pages * h->page_bytes * layer, bytes,
+                               cudaMemcpyHostToDevice, h->st_pf));
+    TK_CUDA(h, cudaEventRecord(h->ev_pf[slot], h->st_pf));
+    h->staged_layer[slot] = layer;
+    (ahead ? h->stats.prefetch_hits : h->stats.prefetch_misses) += n;
+    h->stats.bytes_h2d += (int64_t)bytes;
     return TK_OK;
 }
 
@@ -414,6 +503,8 @@ int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out) {
     if (!h || !out) return TK_INVALID_ARG;
     *out = h->stats;
     out->pages_free = h->mgr->num_free_pages();
+    out->pages_cold = h->mgr->num_cold_used();
+    out->evictions = h->mgr->counters.evictions;
     out->page_allocs = h->mgr->counters.page_allocs;
     out->page_frees = h->mgr->counters.page_frees;
     out->seq_allocs = h->mgr->counters.seq_allocs;
@@ -458,9 +549,10 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     int n_delta = (int)delta.size();
     if (n_delta > kMaxDelta) {
         // rare (bulk adopt / huge prefill): copy the whole table from pageable memory
-        TK_CUDA(h, cudaMemcpyAsync(h->d_table, h->mgr->page_table(),
-                                   (size_t)h->cfg.max_seqs * h->cfg.max_pages_per_seq * sizeof(int32_t),
-                                   cudaMemcpyHostToDevice, s));
+        const size_t n_entries = (size_t)h->cfg.max_seqs * h->cfg.max_pages_per_seq;
+        std::vector<int32_t> full(n_entries);
+        for (size_t i = 0; i < n_entries; i++) full[i] = dev_entry(h->mgr->page_table()[i]);
+        TK_CUDA(h, cudaMemcpyAsync(h->d_table, full.data(), n_entries * sizeof(int32_t), cudaMemcpyHostToDevice, s));
         TK_CUDA(h, cudaStreamSynchronize(s));
         h->stats.bytes_h2d += (int64_t)h->cfg.max_seqs * h->cfg.max_pages_per_seq * 4;
         delta.clear();
@@ -488,7 +580,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     }
     if (n_items) memcpy(w + sec.items, p.items.data(), 16 * (size_t)n_items);
     if (n_seals) memcpy(w + sec.seals, p.seals.data(), 16 * (size_t)n_seals);
-    for (int i = 0; i < n_delta; i++) { w[sec.delta + 2 * i] = delta[i].first; w[sec.delta + 2 * i + 1] = delta[i].second; }
+    for (int i = 0; i < n_delta; i++) { w[sec.delta + 2 * i] = delta[i].first; w[sec.delta + 2 * i + 1] = dev_entry(delta[i].second); }
     delta.clear();
     TK_CUDA(h, cudaMemcpyAsync(h->d_step, w, sec.end * 4, cudaMemcpyHostToDevice, s));
     TK_CUDA(h, cudaEventRecord(h->ev[r], s));
@@ -506,6 +598,13 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     if (n_delta) {
         TK_CUDA(h, tk::launch_apply_delta(h->d_table, (const int2*)(d + sec.delta), n_delta, s));
         h->launches++;
+    }
+    if (h->mgr->cold_enabled()) {
+        int est = run_evictions(h, p.evictions, s);
+        if (est != TK_OK) return est;
+        h->staged_layer[0] = h->staged_layer[1] = -1;       // cold contents may have changed
+        est = prefetch_layer(h, 0, /*ahead=*/false);
+        if (est != TK_OK) return est;
     }
     h->have_step = true;
     return TK_OK;
@@ -555,8 +654,16 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode: no step in progress (call tk_kv_step_begin)");
     if (h->dev.n_seqs == 0) return TK_OK;
     if (!q || (!out && !partial_out)) return fail(h, TK_INVALID_ARG, "decode: null q/out");
-    const tk::LayerPtrs lp = h->layer(layer);
+    tk::LayerPtrs lp = h->layer(layer);
     cudaError_t e = cudaSuccess;
+    const bool cold = h->mgr->cold_enabled() && h->mgr->cold_high_water() > 0;
+    const int slot = layer & 1;
+    if (cold) {
+        int pst = prefetch_layer(h, layer, /*ahead=*/false);   // no-op when it was staged ahead
+        if (pst != TK_OK) return pst;
+        TK_CUDA(h, cudaStreamWaitEvent(s, h->ev_pf[slot], 0));
+        lp.cold_stage = h->d_stage[slot];
+    }
     if (q_dtype == TK_FP32) {                               // FP32 callers: narrow q into the staging buffer
         e = tk::launch_f32_to_16((const float*)q, h->d_q, (size_t)h->dev.n_seqs * h->geo.H * h->geo.D,
                                  h->cfg.io_dtype, s);
@@ -581,8 +688,8 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
         tk::StepDev pool = h->dev;
         pool.n_items = h->n_pool_items;
         if (pool.n_items > 0) {
-            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], pool, h->d_table, q, h->d_partials, h->d_status, s,
-                                      &mo, &fa);
+            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], cold ? &h->stage_maps[slot] : nullptr, pool,
+                                      h->d_table, q, h->d_partials, h->d_status, s, &mo, &fa);
             h->launches++;
         }
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
@@ -601,6 +708,11 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
     }
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode launch: %s", cudaGetErrorString(e));
+    if (cold) {
+        TK_CUDA(h, cudaEventRecord(h->ev_used[slot], s));
+        int pst = prefetch_layer(h, layer + 1, /*ahead=*/true);   // next layer's pages ride PCIe under this kernel
+        if (pst != TK_OK) return pst;
+    }
     if (!fused_merge) {
         e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, out_dtype, partial_out, s);
         h->launches++;

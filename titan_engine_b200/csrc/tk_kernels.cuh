@@ -23,7 +23,11 @@ struct LayerPtrs {
     void*  pool;
     float* scales;
     void*  open_pages;
+    void*  cold_stage;          // this layer's cold pages staged from host memory, indexed by cold id
 };
+
+// Page-table entries with this bit set name a cold page: low bits = cold id = index into cold_stage.
+constexpr int kColdBit = 1 << 30;
 
 // Device view of one step's metadata (all arrays live in one uploaded buffer).
 struct StepDev {
@@ -75,7 +79,7 @@ cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const Ste
 bool        decode_mma_supported(const Geometry& g);
 cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out);
 cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
-                              const StepDev& st, const int32_t* page_table, const void* q,
+                              const CUtensorMap* map_cold, const StepDev& st, const int32_t* page_table, const void* q,
                               float* partials, int* status, cudaStream_t s,
                               const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
 

@@ -42,7 +42,8 @@ class PagedKVCache:
                  num_pages: int, max_seqs: int, max_pages_per_seq: int, dtype: str = "bf16",
                  io_dtype: Optional[str] = None, page_size: int = 16,
                  max_step_tokens: Optional[int] = None, chunk_tokens: int = 0,
-                 decode_impl: str = "auto", device: Optional[int] = None, host_only: bool = False):
+                 decode_impl: str = "auto", device: Optional[int] = None, host_only: bool = False,
+                 hot_window: int = 0, cold_pages: int = 0):
         self._lib = L.lib()
         cfg = L.KvConfig()
         self._lib.tk_kv_config_default(C.byref(cfg))
@@ -52,6 +53,7 @@ class PagedKVCache:
         cfg.num_pages, cfg.max_seqs, cfg.max_pages_per_seq = num_pages, max_seqs, max_pages_per_seq
         cfg.max_step_tokens = max_step_tokens or max_seqs
         cfg.chunk_tokens, cfg.decode_impl = chunk_tokens, _IMPLS[decode_impl]
+        cfg.hot_window, cfg.cold_pages = hot_window, cold_pages
         self._h = C.c_void_p()
         self.host_only = host_only
         self._arena = None
