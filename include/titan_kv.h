@@ -117,6 +117,9 @@ int tk_kv_truncate(tk_kv* h, int32_t seq, int32_t new_len);
 /* Install a caller-chosen page list (e.g. a shuffled pool) as the table of `seq`;
  * the pages must be free. */
 int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t seq_len);
+/* For a sequence whose tokens are split over several caches (one per GPU): tail_tokens of it
+ * follow this cache's last token, so the hot window is measured from seq_len + tail_tokens. */
+int tk_kv_seq_set_tail(tk_kv* h, int32_t seq, int32_t tail_tokens);
 /* KVCache::seq_len (kv_cache.h:50), per sequence here; -1 if the slot is free */
 int tk_kv_seq_len(const tk_kv* h, int32_t seq);
 int tk_kv_num_free_pages(const tk_kv* h);

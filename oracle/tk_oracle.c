@@ -189,6 +189,7 @@ struct tko_mgr {
     /* cold tier (off unless tko_mgr_enable_cold): host-resident pages, ids from their own LIFO stack;
      * a cold page is recorded in the table as -2 - cold_id */
     int hot_window, num_cold_pages; int32_t* cold_stack; int cold_top;
+    int32_t* seq_tail;   /* tokens of the logical sequence held AFTER this cache's last one (other ranks) */
 };
 
 tko_mgr* tko_mgr_create(int num_pages, int max_seqs, int max_pages_per_seq, int page_size) {
@@ -204,16 +205,17 @@ tko_mgr* tko_mgr_create(int num_pages, int max_seqs, int max_pages_per_seq, int 
     for (size_t i = 0; i < n; i++) m->page_table[i] = -1;
     m->seq_len = (int32_t*)malloc(sizeof(int32_t) * (size_t)max_seqs);
     m->seq_pages = (int32_t*)calloc((size_t)max_seqs, sizeof(int32_t));
+    m->seq_tail = (int32_t*)calloc((size_t)max_seqs, sizeof(int32_t));
     for (int i = 0; i < max_seqs; i++) m->seq_len[i] = -1;
     return m;
 }
 void tko_mgr_destroy(tko_mgr* m) {
     if (!m) return;
-    free(m->cold_stack); free(m->free_stack); free(m->page_table); free(m->seq_len); free(m->seq_pages); free(m);
+    free(m->seq_tail); free(m->cold_stack); free(m->free_stack); free(m->page_table); free(m->seq_len); free(m->seq_pages); free(m);
 }
 int tko_seq_alloc(tko_mgr* m) {
     for (int i = 0; i < m->max_seqs; i++)
-        if (m->seq_len[i] < 0) { m->seq_len[i] = 0; m->seq_pages[i] = 0; return i; }
+        if (m->seq_len[i] < 0) { m->seq_len[i] = 0; m->seq_pages[i] = 0; m->seq_tail[i] = 0; return i; }
     return -1;
 }
 static int live(const tko_mgr* m, int seq) { return seq >= 0 && seq < m->max_seqs && m->seq_len[seq] >= 0; }
@@ -244,7 +246,7 @@ int tko_mgr_enable_cold(tko_mgr* m, int hot_window, int num_cold_pages) {
 int tko_evict_cold(tko_mgr* m, int seq, int stable_len) {
     if (!live(m, seq) || !m->cold_stack) return 0;
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
-    int limit = m->seq_len[seq] - m->hot_window;           /* tokens below this index are cold */
+    int limit = m->seq_len[seq] + m->seq_tail[seq] - m->hot_window;   /* tokens below this index are cold */
     if (limit > stable_len) limit = stable_len;            /* but never a page the current step still writes */
     int n_cold = limit > 0 ? limit / m->page_size : 0;     /* pages entirely below the limit */
     int need = 0;
@@ -256,6 +258,12 @@ int tko_evict_cold(tko_mgr* m, int seq, int stable_len) {
         row[i] = -2 - m->cold_stack[--m->cold_top];
     }
     return need;
+}
+/* For a sequence split over several caches: `tail` tokens of it follow this cache's last token. */
+int tko_set_tail(tko_mgr* m, int seq, int tail) {
+    if (!live(m, seq) || tail < 0) return TKO_INVALID_ARG;
+    m->seq_tail[seq] = tail;
+    return TKO_OK;
 }
 int tko_num_cold_used(const tko_mgr* m) { return m->cold_stack ? m->num_cold_pages - m->cold_top : 0; }
 int tko_reserve(tko_mgr* m, int seq, int n_tokens) {

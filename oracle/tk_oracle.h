@@ -63,6 +63,7 @@ int      tko_adopt(tko_mgr* m, int seq, const int32_t* pages, int n_pages, int s
 int      tko_mgr_enable_cold(tko_mgr* m, int hot_window, int num_cold_pages);
 int      tko_evict_cold(tko_mgr* m, int seq, int stable_len);   /* pages moved, -1 if the cold pool is full */
 int      tko_num_cold_used(const tko_mgr* m);
+int      tko_set_tail(tko_mgr* m, int seq, int tail);
 int      tko_seq_len(const tko_mgr* m, int seq);       /* -1 if seq not live */
 int      tko_seq_num_pages(const tko_mgr* m, int seq);
 int      tko_num_free_pages(const tko_mgr* m);

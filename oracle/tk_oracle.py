@@ -60,6 +60,7 @@ def lib() -> C.CDLL:
             "tko_mgr_enable_cold": (i, [vp, i, i]),
             "tko_evict_cold": (i, [vp, i, i]),
             "tko_num_cold_used": (i, [vp]),
+            "tko_set_tail": (i, [vp, i, i]),
             "tko_seq_len": (i, [vp, i]),
             "tko_seq_num_pages": (i, [vp, i]),
             "tko_num_free_pages": (i, [vp]),
@@ -161,6 +162,7 @@ class Manager:
     def enable_cold(self, hot_window, num_cold_pages): return self.l.tko_mgr_enable_cold(self.h, hot_window, num_cold_pages)
     def evict_cold(self, s, stable_len): return self.l.tko_evict_cold(self.h, s, stable_len)
     def num_cold_used(self): return self.l.tko_num_cold_used(self.h)
+    def set_tail(self, s, tail): return self.l.tko_set_tail(self.h, s, tail)
     def seq_len(self, s): return self.l.tko_seq_len(self.h, s)
     def num_free_pages(self): return self.l.tko_num_free_pages(self.h)
     def slot(self, s, pos): return self.l.tko_slot(self.h, s, pos)

@@ -27,6 +27,8 @@ def main():
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--hot-window", type=int, default=0,
+                    help="most recent tokens kept in HBM; older pages live in pinned host memory (0 = all in HBM)")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -40,12 +42,16 @@ def main():
     full = torch.randn(n_pg, Hkv, 2, 16, Dh, device=dev, generator=gen).to(torch.bfloat16)   # layer-shared data
 
     my_pages = (hi - lo) // 16
-    cache = PagedKVCache(L, H, Hkv, Dh, max(my_pages, 1), 1, max(my_pages, 1), dtype="bf16")
+    cache = PagedKVCache(L, H, Hkv, Dh, max(my_pages, 1), 1, max(my_pages, 1), dtype="bf16",
+                         hot_window=args.hot_window, cold_pages=max(my_pages, 1) if args.hot_window else 0)
     s = cache.seq_alloc()
     cache.adopt(s, np.arange(my_pages, dtype=np.int32), hi - lo)
     for l in range(L):
         cache.layer_views(l)[0][:my_pages].copy_(full[lo // 16:hi // 16])
-    cache.step_begin([s], None)
+    if args.hot_window:
+        cache.set_tail(s, n - hi)                      # tokens held by later ranks push this rank's pages out
+    torch.cuda.synchronize()
+    cache.step_begin([s], None)                        # evicts what lies outside the window
     dec = D.LongContextDecoder(cache.decode_partial, lambda st: D.combine_partials(st, torch.bfloat16))
     out = dec.decode(0, q)
     torch.cuda.synchronize()
@@ -84,7 +90,11 @@ def main():
         print(json.dumps({"workload": f"one {n}-token sequence over {world} GPUs, 8B head shape, bf16",
                           "ok": ok, "max_abs_err_vs_single_gpu": err, "n_gpus": world, "layers": L,
                           "us_per_layer": ms_layer * 1e3, "aggregate_kv_gbs": kv_bytes / (ms_layer * 1e-3) / 1e9,
-                          "exchange_bytes_per_rank_per_layer": H * (Dh + 2) * 4}), flush=True)
+                          "exchange_bytes_per_rank_per_layer": H * (Dh + 2) * 4,
+                          "hot_window": args.hot_window, "rank0_stats": {k: v for k, v in cache.stats().items()
+                                                                          if k in ("pages_cold", "evictions", "prefetch_hits",
+                                                                                   "prefetch_misses", "bytes_h2d", "bytes_d2h")}}),
+              flush=True)
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
 

@@ -211,3 +211,41 @@ def test_c5_long_context_partials_over_8_emulated_ranks():
     o.pool[:] = from_torch16(wpool)
     ref = o.decode(np.arange(n // 16, dtype=np.int32)[None], [0], [n], from_torch16(q))[0]
     assert_close(want, ref, "131072-token sequence vs oracle", out_mantissa_bits=7)
+
+
+def test_c5_cold_window_on_one_rank():
+    """The share of one rank of the 131072-token sequence (16384 tokens) with every page outside
+    the hot window: all 1024 pages per layer live in pinned host memory, are staged back layer by
+    layer, and attention equals the all-in-HBM result bit for bit."""
+    from titan_engine_b200 import PagedKVCache
+    H, Hkv, D, per, L = 32, 8, 128, 16384, 3
+    dev = torch.device("cuda")
+    gen = torch.Generator(device=dev); gen.manual_seed(55)
+    q = torch.randn(1, H, D, device=dev, generator=gen).to(torch.bfloat16)
+    data = torch.randn(L, per // 16, Hkv, 2, 16, D, device=dev, generator=gen).to(torch.bfloat16)
+    outs = {}
+    for tiered in (False, True):
+        c = PagedKVCache(L, H, Hkv, D, per // 16, 1, per // 16, dtype="bf16",
+                         hot_window=32768 if tiered else 0, cold_pages=per // 16 if tiered else 0)
+        s = c.seq_alloc()
+        c.adopt(s, np.arange(per // 16, dtype=np.int32), per)
+        for l in range(L):
+            c.layer_views(l)[0].copy_(data[l])
+        if tiered:
+            c.set_tail(s, 131072 - per)                 # rank 0 of 8: 114688 tokens follow
+        torch.cuda.synchronize()
+        c.step_begin([s], None)
+        if tiered:
+            st = c.stats()
+            assert st["pages_cold"] == per // 16 and c.num_free_pages == per // 16
+            for l in range(L):
+                c.layer_views(l)[0].zero_()             # the device pool no longer holds the data
+        outs[tiered] = [c.decode(l, q).clone() for l in range(L)]
+        c.device_status()
+        if tiered:
+            st = c.stats()
+            assert st["prefetch_hits"] == (L - 1) * (per // 16) and st["prefetch_misses"] == per // 16
+        c.close()
+    for l in range(L):
+        assert torch.equal(outs[True][l], outs[False][l]), f"layer {l}: staged pages changed the result"
+        assert float(outs[True][l].float().abs().max()) > 0

@@ -29,6 +29,16 @@ def test_long_context_split_over_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_long_context_with_cold_tier_over_two_gpus():
+    # hot window of 16384 over 32768 tokens: rank 0's pages live in pinned host memory
+    res = _torchrun(2, "tests/multi_gpu/long_context_worker.py", "--tokens", "32768", "--layers", "3", "--steps", "3",
+                    "--hot-window", "16384")
+    assert res.returncode == 0, res.stdout + res.stderr
+    line = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["ok"] and line["rank0_stats"]["pages_cold"] == 1024 and line["rank0_stats"]["prefetch_hits"] > 0
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_bench_shards_by_sequence_over_two_gpus():
     res = _torchrun(2, "bench.py", "--gpus", "2", "--steps", "3", "--warmup", "3", "--layers", "4", "--no-cpu")
     assert res.returncode == 0, res.stdout + res.stderr

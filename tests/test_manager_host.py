@@ -222,5 +222,9 @@ def test_cold_tier_state_matches_oracle_manager():
     step([d, b], [1, 1])
     assert c.stats()["pages_cold"] == (701 - 64) // 16 + (92 - 64) // 16
     assert c.seq_len(d) == 701 and c.stats()["evictions"] == o.num_cold_used() + 17
+    # a rank holding an early part of a long sequence: the tokens after it push its pages out
+    c.set_tail(b, 1000); assert o.set_tail(b, 1000) == O.OK
+    step([d, b], [0, 0])
+    assert c.stats()["pages_cold"] == (701 - 64) // 16 + 92 // 16
     with pytest.raises(KvError):
         PagedKVCache(2, 8, 2, 64, 8, 2, 8, dtype="fp8", host_only=True, hot_window=64, cold_pages=8)

@@ -14,6 +14,7 @@ PageManager::PageManager(int num_pages, int max_seqs, int max_pages_per_seq, int
     table_.assign((size_t)max_seqs * max_pages_per_seq, -1);
     seq_len_.assign(max_seqs, -1);
     seq_pages_.assign(max_seqs, 0);
+    seq_tail_.assign(max_seqs, 0);
 }
 
 void PageManager::set_entry(int seq, int idx, int32_t value) {
@@ -39,7 +40,7 @@ void PageManager::compact_delta() {
 // Lowest free index, like BatchScheduler::allocate_slot (src/inference/batch.cpp:86-96).
 int PageManager::seq_alloc() {
     for (int i = 0; i < max_seqs_; i++)
-        if (seq_len_[i] < 0) { seq_len_[i] = 0; seq_pages_[i] = 0; counters.seq_allocs++; return i; }
+        if (seq_len_[i] < 0) { seq_len_[i] = 0; seq_pages_[i] = 0; seq_tail_[i] = 0; counters.seq_allocs++; return i; }
     return -1;
 }
 
@@ -120,10 +121,16 @@ int PageManager::enable_cold(int hot_window, int num_cold_pages) {
     return ST_OK;
 }
 
+int PageManager::set_tail(int seq, int tail) {
+    if (!live(seq) || tail < 0) return ST_INVALID_ARG;
+    seq_tail_[seq] = tail;
+    return ST_OK;
+}
+
 int PageManager::evict_cold(int seq, int stable_len, std::vector<Eviction>* moved) {
     if (!live(seq) || !cold_enabled()) return 0;
     const int32_t* r = row(seq);
-    int limit = seq_len_[seq] - hot_window_;                // tokens below this index are cold ...
+    int limit = seq_len_[seq] + seq_tail_[seq] - hot_window_;   // tokens below this index are cold ...
     if (limit > stable_len) limit = stable_len;             // ... but never a page this step still writes
     const int n_cold = limit > 0 ? limit / page_size_ : 0;  // pages that lie entirely below it
     int need = 0;

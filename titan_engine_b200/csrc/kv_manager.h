@@ -69,6 +69,9 @@ public:
     int  enable_cold(int hot_window, int num_cold_pages);                  // status
     int  evict_cold(int seq, int stable_len, std::vector<Eviction>* moved); // pages moved, -1 = cold pool full;
                                                                            // stable_len = length before the current step
+    // A sequence split over several caches: `tail` tokens of it follow this cache's last token,
+    // so the window is measured from seq_len + tail.
+    int  set_tail(int seq, int tail);
     bool cold_enabled() const { return hot_window_ > 0; }
     int  num_cold_used() const { return num_cold_pages_ - (int)cold_stack_.size(); }
     int  cold_high_water() const { return cold_high_water_; }
@@ -109,6 +112,7 @@ private:
     std::vector<int32_t> table_;        // [max_seqs][max_pages_per_seq], -1 = unmapped
     std::vector<int32_t> seq_len_;      // -1 = slot free
     std::vector<int32_t> seq_pages_;
+    std::vector<int32_t> seq_tail_;
     int hot_window_ = 0, num_cold_pages_ = 0, cold_high_water_ = 0;
     std::vector<int32_t> cold_stack_;   // back() is the next cold id handed out
     std::vector<std::pair<int32_t, int32_t>> delta_;

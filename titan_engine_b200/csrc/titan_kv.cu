@@ -485,6 +485,11 @@ int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages
     int st = h->mgr->adopt(seq, pages, n_pages, seq_len);
     return st == TK_OK ? TK_OK : fail(h, st, "seq_adopt(%d): pages must be distinct, in range and free", seq);
 }
+int tk_kv_seq_set_tail(tk_kv* h, int32_t seq, int32_t tail_tokens) {
+    if (!h) return TK_INVALID_ARG;
+    int st = h->mgr->set_tail(seq, tail_tokens);
+    return st == TK_OK ? TK_OK : fail(h, st, "seq_set_tail(%d, %d): sequence not live or negative tail", seq, tail_tokens);
+}
 int tk_kv_seq_len(const tk_kv* h, int32_t seq) { return h ? h->mgr->seq_len(seq) : -1; }
 int tk_kv_num_free_pages(const tk_kv* h) { return h ? h->mgr->num_free_pages() : -1; }
 int tk_kv_page_table(const tk_kv* h, int32_t seq, int32_t* out, int32_t cap, int32_t* n_out) {

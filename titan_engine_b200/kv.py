@@ -122,6 +122,10 @@ class PagedKVCache:
         p = _i32(pages)
         self._check(self._lib.tk_kv_seq_adopt(self._h, seq, _ptr(p), len(p), seq_len))
 
+    def set_tail(self, seq: int, tail_tokens: int) -> None:
+        """Tokens of this logical sequence held by later ranks (moves the hot window)."""
+        self._check(self._lib.tk_kv_seq_set_tail(self._h, seq, tail_tokens))
+
     def seq_len(self, seq: int) -> int:
         return self._lib.tk_kv_seq_len(self._h, seq)
 
