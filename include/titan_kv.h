@@ -169,6 +169,13 @@ int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream
  * In every other case it does tk_kv_append then tk_kv_decode. */
 int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
                         void* stream);
+/* apply_rope + update + attention_decode of one layer: the three calls of the reference's layer
+ * loop (src/model/dense.cpp:382-398; rope_kernel, src/compute/cuda/attention.cu:15-48).  q and k are
+ * the rows BEFORE rotation and are not modified; a q row takes the position of its sequence's
+ * newest token, a k row its own.  On a decode step with 16-bit storage everything is ONE kernel:
+ * q is rotated as it is loaded, the new K row as it is stored. */
+int tk_kv_rope_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
+                             float theta, float scaling, void* stream);
 /* tk_kv_decode with explicit types: q_dtype and out_dtype are each TK_FP32 (the reference's
  * float* interface) or the handle's io dtype. */
 int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, void* out, int32_t out_dtype,

@@ -269,3 +269,63 @@ def test_cold_tier_eviction_and_prefetch(impl):
     t.step([c, b], [500, 1])
     t.step([c, b], [1, 1], fused=True)           # 23 of c's pages are cold now
     assert t.gpu.seq_len(c) == 501 and t.gpu.stats()["pages_cold"] == (501 - 128) // 16 + (143 - 128) // 16
+
+
+@pytest.mark.parametrize("shape", [(32, 8, 128, "bf16"), (8, 2, 64, "fp16")])
+def test_rope_append_decode_fused(shape):
+    """apply_rope -> update -> attention_decode as one call (one kernel on decode steps).  The oracle
+    rotates in FP32 exactly as the reference's rope_kernel, rounds to the storage type, appends and
+    attends; K rows may differ from it by one unit in the last place of the 16-bit type (device
+    powf/sinf/cosf vs libm), V rows not at all."""
+    H, Hkv, D, dtype = shape
+    dt = DT[dtype]
+    theta = 500000.0
+    t = Twin(2, H, Hkv, D, 120, 3, 60, dtype=dtype, impl="mma", max_step_tokens=1024, seed=70)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    g = rng(71)
+
+    def rot(x16, heads, positions):                     # x16: [rows][heads][D] bits; one position per row
+        xf = O.to_f32(x16, dt)
+        out = np.empty_like(xf)
+        for r, pos in enumerate(positions):
+            if heads == H:
+                out[r], _ = O.rope_f32(xf[r], np.zeros((Hkv, D), np.float32), H, Hkv, D, int(pos), theta)
+            else:
+                _, out[r] = O.rope_f32(np.zeros((H, D), np.float32), xf[r], H, Hkv, D, int(pos), theta)
+        return O.f32_to_16(out, dt)
+
+    def step(n_new):
+        old = [t.gpu.seq_len(s) for s in seqs]
+        t.gpu.step_begin(seqs, n_new)
+        for s, n in zip(seqs, n_new):
+            assert t.mgr.reserve(s, n) == O.OK
+        assert t.gpu.digest() == t.mgr.digest()
+        table = t.mgr.table()
+        tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seqs, n_new)])
+        tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)])
+        lens = [t.gpu.seq_len(s) for s in seqs]
+        n0 = t.gpu.launch_count
+        for layer in range(2):
+            k16 = normal16(g, (len(tok_seq), Hkv, D), dt); v16 = normal16(g, (len(tok_seq), Hkv, D), dt)
+            q16 = normal16(g, (3, H, D), dt)
+            got = t.gpu.rope_append_decode(layer, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev),
+                                           to_torch16(q16, dt, t.dev), theta).float().cpu().numpy()
+            t.pools[layer].append(table, tok_seq, tok_pos, rot(k16, Hkv, tok_pos), v16)
+            want = t.pools[layer].decode(table, seqs, lens, rot(q16, H, [n - 1 for n in lens]))
+            assert_close(got, want, f"rope+append+decode layer {layer}", out_mantissa_bits=7 if dt == O.BF16 else 10)
+            pool = from_torch16(t.gpu.layer_views(layer)[0])
+            np.testing.assert_array_equal(pool[:, :, 1], t.pools[layer].pool[:, :, 1])       # V: plain copy
+            kg, kw = O.to_f32(pool[:, :, 0], dt), O.to_f32(t.pools[layer].pool[:, :, 0], dt)
+            # one unit in the last place; near zero the angle error (an ulp of freq times the position)
+            # dominates, so magnitudes are floored at 0.05 for the purpose of the bound
+            ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(kw), 0.05))) - (7 if dt == O.BF16 else 10))
+            assert (np.abs(kg - kw) <= ulp).all(), "rotated K rows differ by more than one ulp"
+            assert (kg == kw).mean() > 0.98
+        return t.gpu.launch_count - n0
+
+    step([300, 17, 1])                                  # prefill: rope kernel + append + decode
+    launches = step([1, 1, 1])                          # decode step: one kernel per layer (+ page-table patch)
+    assert launches <= 3
+    for _ in range(20):
+        step([1, 1, 1])
+    t.gpu.device_status()

@@ -67,6 +67,7 @@ SIGNATURES = {
     "tk_kv_append": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P]),
     "tk_kv_decode": (C.c_int, [_P, C.c_int32, _P, _P, _P]),
     "tk_kv_append_decode": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
+    "tk_kv_rope_append_decode": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, C.c_float, C.c_float, _P]),
     "tk_kv_decode_partial": (C.c_int, [_P, C.c_int32, _P, _P, _P]),
     "tk_combine_partials": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, _P]),
     "tk_kv_append_decode_host": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),

@@ -1,0 +1,74 @@
+// rope_append.cu — rotary position embedding of a step's q and k rows (16-bit in, 16-bit out).
+//
+// Same arithmetic as the reference's rope_kernel (src/compute/cuda/attention.cu:15-48), which its
+// layer loop runs immediately before KVCache::update (src/model/dense.cpp:382-388): interleaved
+// pairs (d, d+1), freq = (1/powf(theta, d/D)) * scaling, angle = position * freq, in FP32.
+// Positions come from the step plan: a q row belongs to the newest token of its sequence
+// (len-1), a k row to its own token.  On decode steps with 16-bit storage this kernel is not
+// launched at all — the rotation rides inside the attention kernel (decode_mma.cu).
+#include "tk_kernels.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace tk {
+
+namespace {
+
+template <bool BF16>
+__device__ __forceinline__ void rotate_store(const uint16_t* src, uint16_t* dst, int d, int D, int position,
+                                             float theta, float scaling) {
+    float x0, x1;
+    if (BF16) { x0 = __uint_as_float((uint32_t)src[d] << 16); x1 = __uint_as_float((uint32_t)src[d + 1] << 16); }
+    else      { x0 = __half2float(__ushort_as_half(src[d])); x1 = __half2float(__ushort_as_half(src[d + 1])); }
+    float freq = 1.0f / powf(theta, (float)d / D);
+    freq *= scaling;
+    const float angle = position * freq;
+    const float c = cosf(angle), s = sinf(angle);
+    const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;
+    if (BF16) {
+        dst[d] = __bfloat16_as_ushort(__float2bfloat16_rn(y0));
+        dst[d + 1] = __bfloat16_as_ushort(__float2bfloat16_rn(y1));
+    } else {
+        dst[d] = __half_as_ushort(__float2half_rn(y0));
+        dst[d + 1] = __half_as_ushort(__float2half_rn(y1));
+    }
+}
+
+// blocks [0, n_seqs): q rows of one sequence (H heads); blocks [n_seqs, n_seqs + n_tokens): k rows
+// of one token (Hkv heads).  Threads stride over (head, pair).
+template <bool BF16>
+__global__ void rope16_kernel(Geometry g, StepDev st, const uint16_t* __restrict__ q, const uint16_t* __restrict__ k,
+                              uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_out, float theta, float scaling) {
+    const int half = g.D / 2;
+    if ((int)blockIdx.x < st.n_seqs) {
+        const int b = blockIdx.x, pos = st.len[b] - 1;
+        for (int i = threadIdx.x; i < g.H * half; i += blockDim.x) {
+            const size_t row = ((size_t)b * g.H + i / half) * g.D;
+            rotate_store<BF16>(q + row, q_out + row, (i % half) * 2, g.D, pos < 0 ? 0 : pos, theta, scaling);
+        }
+    } else {
+        const int t = blockIdx.x - st.n_seqs, pos = st.tok_pos[t];
+        for (int i = threadIdx.x; i < g.Hkv * half; i += blockDim.x) {
+            const size_t row = ((size_t)t * g.Hkv + i / half) * g.D;
+            rotate_store<BF16>(k + row, k_out + row, (i % half) * 2, g.D, pos, theta, scaling);
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_rope16(const Geometry& g, const StepDev& st, const void* q, const void* k, void* q_out,
+                          void* k_out, float theta, float scaling, cudaStream_t s) {
+    const int blocks = st.n_seqs + st.n_tokens;
+    if (blocks <= 0) return cudaSuccess;
+    if (g.io_dtype == DT_BF16)
+        rope16_kernel<true><<<blocks, 256, 0, s>>>(g, st, (const uint16_t*)q, (const uint16_t*)k, (uint16_t*)q_out,
+                                                   (uint16_t*)k_out, theta, scaling);
+    else
+        rope16_kernel<false><<<blocks, 256, 0, s>>>(g, st, (const uint16_t*)q, (const uint16_t*)k, (uint16_t*)q_out,
+                                                    (uint16_t*)k_out, theta, scaling);
+    return cudaGetLastError();
+}
+
+}  // namespace tk

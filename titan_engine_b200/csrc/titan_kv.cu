@@ -98,6 +98,7 @@ struct tk_kv {
 
     // staging for the *_host entry point
     void* d_q = nullptr;                 // FP32 callers: q narrowed to the io type
+    void *d_rq = nullptr, *d_rk = nullptr;   // rotated q / k when RoPE cannot ride inside the attention kernel
     // the *_host entry points: two staging sets, so that the copies of one layer overlap the
     // kernel of another on the copy engines (copy-in stream, caller's stream, copy-out stream)
     void *hs_k[2] = {}, *hs_v[2] = {}, *hs_q[2] = {}, *hs_out[2] = {};
@@ -170,6 +171,8 @@ void release(tk_kv* h) {
         if (h->d_counters) cudaFree(h->d_counters);
         if (h->d_step) cudaFree(h->d_step);
         if (h->d_q) cudaFree(h->d_q);
+        if (h->d_rq) cudaFree(h->d_rq);
+        if (h->d_rk) cudaFree(h->d_rk);
         for (int i = 0; i < 2; i++) {
             if (h->hs_k[i]) cudaFree(h->hs_k[i]);
             if (h->hs_v[i]) cudaFree(h->hs_v[i]);
@@ -281,6 +284,8 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     const size_t kv_bytes = (size_t)c.max_step_tokens * c.num_kv_heads * c.head_dim * 2;
     const size_t q_bytes = (size_t)c.max_seqs * c.num_heads * c.head_dim * 2;
     CREATE_CUDA(cudaMalloc(&h->d_q, q_bytes));
+    CREATE_CUDA(cudaMalloc(&h->d_rq, q_bytes));
+    CREATE_CUDA(cudaMalloc(&h->d_rk, kv_bytes));
     for (int i = 0; i < 2; i++) {
         CREATE_CUDA(cudaMalloc(&h->hs_k[i], kv_bytes));
         CREATE_CUDA(cudaMalloc(&h->hs_v[i], kv_bytes));
@@ -653,7 +658,7 @@ int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t*
 
 static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* partial_out, cudaStream_t s,
                        int q_dtype = -1, int out_dtype = -1, const void* fuse_k = nullptr,
-                       const void* fuse_v = nullptr) {
+                       const void* fuse_v = nullptr, const float* rope = nullptr) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode: no step in progress (call tk_kv_step_begin)");
@@ -686,7 +691,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     // attends to nothing has no CTA, so such steps keep the separate combine kernel
     const bool fused_merge = !h->plan.has_empty_seq && getenv("TK_SEPARATE_COMBINE") == nullptr;
     const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype};
-    const tk::FuseAppend fa{fuse_k, fuse_v};
+    const tk::FuseAppend fa{fuse_k, fuse_v, rope ? 1 : 0, rope ? rope[0] : 0.0f, rope ? rope[1] : 0.0f};
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
     if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
     if (mma) {
@@ -746,6 +751,26 @@ int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, c
     }
     if (!k || !v) return fail(h, TK_INVALID_ARG, "append_decode: null k/v");
     return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream, -1, -1, k, v);
+}
+
+// rope_kernel + update + attention_decode of one layer (src/model/dense.cpp:382-398).
+int tk_kv_rope_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
+                             float theta, float scaling, void* stream) {
+    if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (h->host_only) return fail(h, TK_CUDA_ERROR, "rope_append_decode: handle has no device (bookkeeping only)");
+    if (!h->have_step) return fail(h, TK_INVALID_ARG, "rope_append_decode: no step in progress (call tk_kv_step_begin)");
+    if (!q || !out || (h->dev.n_tokens > 0 && (!k || !v))) return fail(h, TK_INVALID_ARG, "rope_append_decode: null argument");
+    const bool fusable = h->use_mma && h->cfg.dtype != TK_FP8_E4M3 && h->plan.one_token_steps &&
+                         h->dev.chunk_tokens <= 2048 && h->dev.n_tokens > 0 && h->dev.n_seqs > 0 &&
+                         !h->plan.has_empty_seq && getenv("TK_SEPARATE_APPEND") == nullptr;
+    if (fusable) {
+        const float rope[2] = {theta, scaling};
+        return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream, -1, -1, k, v, rope);
+    }
+    cudaError_t e = tk::launch_rope16(h->geo, h->dev, q, k, h->d_rq, h->d_rk, theta, scaling, (cudaStream_t)stream);
+    h->launches++;
+    if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "rope launch: %s", cudaGetErrorString(e));
+    return tk_kv_append_decode(h, layer, h->d_rk, v, h->d_rq, out, stream);
 }
 
 int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, void* out, int32_t out_dtype,

@@ -61,7 +61,16 @@ struct MergeOut {
 struct FuseAppend {
     const void* k;              // [n_tokens][Hkv][D] 16-bit
     const void* v;
+    // rope != 0: q and the new K row are rotated on the fly (interleaved pairs (d, d+1),
+    // freq = (1/powf(theta, d/D)) * scaling, angle = position * freq) before they are used/stored
+    int   rope;
+    float rope_theta, rope_scaling;
 };
+
+// RoPE of a step's rows into separate buffers (used when the rotation cannot ride inside the
+// attention kernel): q rows take position len-1 of their sequence, k rows their token position.
+cudaError_t launch_rope16(const Geometry& g, const StepDev& st, const void* q, const void* k, void* q_out,
+                          void* k_out, float theta, float scaling, cudaStream_t s);
 
 cudaError_t launch_apply_delta(int32_t* table, const int2* delta, int n, cudaStream_t s);
 

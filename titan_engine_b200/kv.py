@@ -218,6 +218,18 @@ class PagedKVCache:
                                                   out.data_ptr(), self._stream()))
         return out
 
+    def rope_append_decode(self, layer: int, k: torch.Tensor, v: torch.Tensor, q: torch.Tensor,
+                           theta: float, scaling: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """RoPE(q, k) + append + decode of one layer; q and k are given before rotation."""
+        self._check_io(k, self._n_tokens, self.cfg.num_kv_heads, "k")
+        self._check_io(v, self._n_tokens, self.cfg.num_kv_heads, "v")
+        self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
+        if out is None:
+            out = torch.empty_like(q)
+        self._check(self._lib.tk_kv_rope_append_decode(self._h, layer, k.data_ptr(), v.data_ptr(), q.data_ptr(),
+                                                       out.data_ptr(), theta, scaling, self._stream()))
+        return out
+
     def decode_partial(self, layer: int, q: torch.Tensor, partial: Optional[torch.Tensor] = None) -> torch.Tensor:
         """-> [n_seqs, H, D+2] f32: unnormalised o, then m, then l."""
         self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
