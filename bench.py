@@ -254,6 +254,8 @@ def run_ours(args):
             if args.separate:
                 cache.append(l, k, v)
                 cache.decode(l, q, out)
+            elif args.rope:
+                cache.rope_append_decode(l, k, v, q, 500000.0, 1.0, out)
             else:
                 cache.append_decode(l, k, v, q, out)
 
@@ -358,6 +360,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=0, help="split-KV chunk tokens (0 = library default)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--rope", action="store_true", help="also fuse RoPE of q and the new K rows into each layer's call")
     ap.add_argument("--separate", action="store_true", help="call append and decode separately (two entry points)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

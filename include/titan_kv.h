@@ -234,6 +234,40 @@ int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t num_pages,
  * bounded device-side wait gave up (the word is cleared). */
 int tk_kv_device_status(tk_kv* h, void* stream);
 
+/* ---- continuous batching over the paged cache -------------------------------------------
+ * Stands for BatchScheduler (src/inference/batch.h:75-140): submit / cancel / one
+ * schedule_iteration at a time (src/inference/batch.cpp:103-167), with pages instead of
+ * whole-sequence KV slots, chunked prefill and preemption when the pool runs dry.  Host only. */
+typedef struct tk_sched tk_sched;
+typedef struct tk_sched_config {        /* BatchSchedulerConfig, batch.h:68-73 */
+    int32_t max_batch_size;             /* concurrent requests */
+    int32_t max_prefill_tokens;         /* prompt tokens appended per iteration, all requests together */
+    int32_t reserved[6];
+} tk_sched_config;
+typedef struct tk_sched_stats {         /* BatchScheduler::Stats, batch.h:99-108 */
+    int32_t active_requests, queued_requests, completed_requests, cancelled_requests;
+    int64_t total_tokens_generated, total_prompt_tokens, iterations, preemptions;
+    float avg_ttft_ms, avg_tps, batch_utilization;
+} tk_sched_stats;
+int tk_sched_create(tk_kv* kv, const tk_sched_config* cfg, tk_sched** out);      /* BatchScheduler::initialize */
+int tk_sched_destroy(tk_sched* s);
+int tk_sched_submit(tk_sched* s, int32_t prompt_tokens, int32_t max_output_tokens, int32_t* request_id);
+int tk_sched_cancel(tk_sched* s, int32_t request_id);
+/* One iteration: retire finished/cancelled (ascending slot), admit FIFO, lay out the step
+ * (decoding requests 1 token, prefilling requests their next chunk), tk_kv_step_begin on `stream`
+ * (preempting the most recently admitted request while pages are short).  Row i of the step:
+ * request, sequence slot, tokens appended, and whether its attention output is sampled from. */
+int tk_sched_next(tk_sched* s, int32_t cap, int32_t* req_ids, int32_t* seq_ids, int32_t* n_new, int32_t* samples,
+                  int32_t* n_out, void* stream);
+/* After sampling: finished[i] != 0 when row i's request produced its last token (EOS). */
+int tk_sched_commit(tk_sched* s, int32_t n, const int32_t* finished);
+/* state: 0 queued, 1 prefilling, 2 decoding, 3 finished, 4 cancelled (RequestState, batch.h:31-37) */
+int tk_sched_request_state(const tk_sched* s, int32_t request_id, int32_t* state, int32_t* seq, int32_t* prefill_pos,
+                           int32_t* output_tokens);
+/* Sequence slots touched by the last tk_sched_next: which = 0 retired, 1 admitted, 2 preempted. */
+int tk_sched_last_events(const tk_sched* s, int32_t which, int32_t cap, int32_t* seqs, int32_t* n_out);
+int tk_sched_get_stats(const tk_sched* s, tk_sched_stats* out);
+
 /* Number of kernels this library has launched on this handle so far. */
 int64_t tk_kv_launch_count(const tk_kv* h);
 

@@ -105,11 +105,15 @@ class Twin:
         self.gpu.adopt(s, pages, seq_len)
         assert self.mgr.adopt(s, pages, seq_len) == O.OK
 
-    def step(self, seq_ids, n_new, check_pool=False, decode=True, outlier_p=0.0, host_api=False, fused=False):
+    def step(self, seq_ids, n_new, check_pool=False, decode=True, outlier_p=0.0, host_api=False, fused=False, begun=False):
+        """begun=True: the step was already begun on the GPU cache (e.g. by the scheduler)."""
         torch = self.torch
         n_new = [0] * len(seq_ids) if n_new is None else list(n_new)
-        old = [self.gpu.seq_len(s) for s in seq_ids]
-        self.gpu.step_begin(seq_ids, n_new)
+        if begun:
+            old = [self.gpu.seq_len(s) - n for s, n in zip(seq_ids, n_new)]
+        else:
+            old = [self.gpu.seq_len(s) for s in seq_ids]
+            self.gpu.step_begin(seq_ids, n_new)
         for s, n in zip(seq_ids, n_new):
             assert self.mgr.reserve(s, n) == O.OK
             if self.flat:

@@ -30,6 +30,16 @@ class KvStats(C.Structure):
         "steps", "tokens_appended", "pages_sealed")]
 
 
+class SchedConfig(C.Structure):
+    _fields_ = [("max_batch_size", C.c_int32), ("max_prefill_tokens", C.c_int32), ("reserved", C.c_int32 * 6)]
+
+
+class SchedStats(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("active_requests", "queued_requests", "completed_requests", "cancelled_requests")] + \
+               [(n, C.c_int64) for n in ("total_tokens_generated", "total_prompt_tokens", "iterations", "preemptions")] + \
+               [(n, C.c_float) for n in ("avg_ttft_ms", "avg_tps", "batch_utilization")]
+
+
 _P = C.c_void_p
 _I32P = C.POINTER(C.c_int32)
 
@@ -79,6 +89,15 @@ SIGNATURES = {
                                         C.c_int32, C.c_int32, _P, _P, _P]),
     "tk_kv_device_status": (C.c_int, [_P, _P]),
     "tk_kv_launch_count": (C.c_int64, [_P]),
+    "tk_sched_create": (C.c_int, [_P, C.POINTER(SchedConfig), C.POINTER(_P)]),
+    "tk_sched_destroy": (C.c_int, [_P]),
+    "tk_sched_submit": (C.c_int, [_P, C.c_int32, C.c_int32, _I32P]),
+    "tk_sched_cancel": (C.c_int, [_P, C.c_int32]),
+    "tk_sched_next": (C.c_int, [_P, C.c_int32, _I32P, _I32P, _I32P, _I32P, _I32P, _P]),
+    "tk_sched_commit": (C.c_int, [_P, C.c_int32, _I32P]),
+    "tk_sched_request_state": (C.c_int, [_P, C.c_int32, _I32P, _I32P, _I32P, _I32P]),
+    "tk_sched_last_events": (C.c_int, [_P, C.c_int32, C.c_int32, _I32P, _I32P]),
+    "tk_sched_get_stats": (C.c_int, [_P, C.POINTER(SchedStats)]),
 }
 
 _lib = None

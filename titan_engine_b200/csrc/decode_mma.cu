@@ -132,15 +132,12 @@ __device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_codes) {
 // RoPE of one (d, d+1) pair held as two 16-bit values in one register; same arithmetic as the
 // reference's rope_kernel (src/compute/cuda/attention.cu:22-37), result rounded to the storage type.
 template <bool BF16>
-__device__ __forceinline__ uint32_t rope_pair(uint32_t w, int d, int D, int position, float theta, float scaling) {
+__device__ __forceinline__ uint32_t rope_pair(uint32_t w, const float2* __restrict__ tab, int d) {
     float x0, x1;
     if (BF16) { x0 = __uint_as_float(w << 16); x1 = __uint_as_float(w & 0xFFFF0000u); }
     else { const __half2 h = *reinterpret_cast<const __half2*>(&w); x0 = __low2float(h); x1 = __high2float(h); }
-    float freq = 1.0f / powf(theta, (float)d / D);
-    freq *= scaling;
-    const float angle = position * freq;
-    const float c = cosf(angle), s = sinf(angle);
-    return pack2<BF16>(x0 * c - x1 * s, x0 * s + x1 * c);
+    const float2 cs = tab[d >> 1];                          // (cos, sin) of this sequence's newest position
+    return pack2<BF16>(x0 * cs.x - x1 * cs.y, x0 * cs.y + x1 * cs.x);
 }
 
 // swizzled byte offset of 16-byte chunk `c` of row `r` inside a 32x128-byte box
@@ -251,12 +248,13 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                 w[2] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + 16 * kk + 8 + 2 * j) : 0u;
                 w[1] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 2 * j) : 0u;
                 w[3] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 8 + 2 * j) : 0u;
-                if (fa.rope) {                              // the query is the token at position len-1
-                    w[0] = rope_pair<BF>(w[0], 16 * kk + 2 * j, D, len - 1, fa.rope_theta, fa.rope_scaling);
-                    w[2] = rope_pair<BF>(w[2], 16 * kk + 8 + 2 * j, D, len - 1, fa.rope_theta, fa.rope_scaling);
+                if (fa.rope_tab) {                          // the query is the token at position len-1
+                    const float2* tab = fa.rope_tab + (size_t)b * (D / 2);
+                    w[0] = rope_pair<BF>(w[0], tab, 16 * kk + 2 * j);
+                    w[2] = rope_pair<BF>(w[2], tab, 16 * kk + 8 + 2 * j);
                     if (GHI) {
-                        w[1] = rope_pair<BF>(w[1], 16 * kk + 2 * j, D, len - 1, fa.rope_theta, fa.rope_scaling);
-                        w[3] = rope_pair<BF>(w[3], 16 * kk + 8 + 2 * j, D, len - 1, fa.rope_theta, fa.rope_scaling);
+                        w[1] = rope_pair<BF>(w[1], tab, 16 * kk + 2 * j);
+                        w[3] = rope_pair<BF>(w[3], tab, 16 * kk + 8 + 2 * j);
                     }
                 }
             }
@@ -302,11 +300,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
             uint16_t* dst = (uint16_t*)lp.pool + ((((size_t)page * g.Hkv + kvh) * 2 + kv) * kPage + r) * D;
             for (int c = lane & 15; c < D / 8; c += 16) {
                 uint4 val = *reinterpret_cast<const uint4*>(src + c * 8);
-                if (fa.rope && kv == 0) {                   // K row: rotate its 4 pairs before it is stored
-                    val.x = rope_pair<BF>(val.x, c * 8 + 0, D, len - 1, fa.rope_theta, fa.rope_scaling);
-                    val.y = rope_pair<BF>(val.y, c * 8 + 2, D, len - 1, fa.rope_theta, fa.rope_scaling);
-                    val.z = rope_pair<BF>(val.z, c * 8 + 4, D, len - 1, fa.rope_theta, fa.rope_scaling);
-                    val.w = rope_pair<BF>(val.w, c * 8 + 6, D, len - 1, fa.rope_theta, fa.rope_scaling);
+                if (fa.rope_tab && kv == 0) {               // K row: rotate its 4 pairs before it is stored
+                    const float2* tab = fa.rope_tab + (size_t)b * (D / 2);
+                    val.x = rope_pair<BF>(val.x, tab, c * 8 + 0);
+                    val.y = rope_pair<BF>(val.y, tab, c * 8 + 2);
+                    val.z = rope_pair<BF>(val.z, tab, c * 8 + 4);
+                    val.w = rope_pair<BF>(val.w, tab, c * 8 + 6);
                 }
                 *reinterpret_cast<uint4*>(stg + (c >> 3) * kBoxBytes + swz(kv * 16 + r, c & 7)) = val;
                 *reinterpret_cast<uint4*>(dst + c * 8) = val;
@@ -555,7 +554,7 @@ cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUte
                               const FuseAppend* fuse) {
     if (st.n_items <= 0) return cudaSuccess;
     const MergeOut mo = merge ? *merge : MergeOut{nullptr, nullptr, nullptr, 0};
-    const FuseAppend fa = fuse ? *fuse : FuseAppend{nullptr, nullptr, 0, 0.0f, 0.0f};
+    const FuseAppend fa = fuse ? *fuse : FuseAppend{nullptr, nullptr, nullptr};
     if (!map_cold) map_cold = map;
     if (!decode_mma_supported(g) || st.chunk_tokens > kPage * kWarps * 32) return cudaErrorNotSupported;
     if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);

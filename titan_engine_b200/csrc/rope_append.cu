@@ -56,7 +56,28 @@ __global__ void rope16_kernel(Geometry g, StepDev st, const uint16_t* __restrict
     }
 }
 
+// (cos, sin) of every sequence's newest position, one entry per pair: tab[b][d/2].
+__global__ void rope_table_kernel(Geometry g, StepDev st, float2* __restrict__ tab, float theta, float scaling) {
+    const int half = g.D / 2;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= st.n_seqs * half) return;
+    const int b = i / half, d = (i % half) * 2;
+    const int pos = st.len[b] > 0 ? st.len[b] - 1 : 0;
+    float freq = 1.0f / powf(theta, (float)d / g.D);
+    freq *= scaling;
+    const float angle = pos * freq;
+    tab[i] = make_float2(cosf(angle), sinf(angle));
+}
+
 }  // namespace
+
+cudaError_t launch_rope_table(const Geometry& g, const StepDev& st, float2* tab, float theta, float scaling,
+                              cudaStream_t s) {
+    const int n = st.n_seqs * (g.D / 2);
+    if (n <= 0) return cudaSuccess;
+    rope_table_kernel<<<(n + 255) / 256, 256, 0, s>>>(g, st, tab, theta, scaling);
+    return cudaGetLastError();
+}
 
 cudaError_t launch_rope16(const Geometry& g, const StepDev& st, const void* q, const void* k, void* q_out,
                           void* k_out, float theta, float scaling, cudaStream_t s) {

@@ -99,6 +99,9 @@ struct tk_kv {
     // staging for the *_host entry point
     void* d_q = nullptr;                 // FP32 callers: q narrowed to the io type
     void *d_rq = nullptr, *d_rk = nullptr;   // rotated q / k when RoPE cannot ride inside the attention kernel
+    float2* d_rope_tab = nullptr;        // [max_seqs][D/2] (cos, sin) of each sequence's newest position
+    int64_t rope_tab_step = -1;          // step the table was filled for, with which parameters
+    float rope_tab_theta = 0, rope_tab_scaling = 0;
     // the *_host entry points: two staging sets, so that the copies of one layer overlap the
     // kernel of another on the copy engines (copy-in stream, caller's stream, copy-out stream)
     void *hs_k[2] = {}, *hs_v[2] = {}, *hs_q[2] = {}, *hs_out[2] = {};
@@ -172,6 +175,7 @@ void release(tk_kv* h) {
         if (h->d_step) cudaFree(h->d_step);
         if (h->d_q) cudaFree(h->d_q);
         if (h->d_rq) cudaFree(h->d_rq);
+        if (h->d_rope_tab) cudaFree(h->d_rope_tab);
         if (h->d_rk) cudaFree(h->d_rk);
         for (int i = 0; i < 2; i++) {
             if (h->hs_k[i]) cudaFree(h->hs_k[i]);
@@ -285,6 +289,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     const size_t q_bytes = (size_t)c.max_seqs * c.num_heads * c.head_dim * 2;
     CREATE_CUDA(cudaMalloc(&h->d_q, q_bytes));
     CREATE_CUDA(cudaMalloc(&h->d_rq, q_bytes));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_rope_tab, sizeof(float2) * (size_t)c.max_seqs * (c.head_dim / 2)));
     CREATE_CUDA(cudaMalloc(&h->d_rk, kv_bytes));
     for (int i = 0; i < 2; i++) {
         CREATE_CUDA(cudaMalloc(&h->hs_k[i], kv_bytes));
@@ -691,7 +696,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     // attends to nothing has no CTA, so such steps keep the separate combine kernel
     const bool fused_merge = !h->plan.has_empty_seq && getenv("TK_SEPARATE_COMBINE") == nullptr;
     const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype};
-    const tk::FuseAppend fa{fuse_k, fuse_v, rope ? 1 : 0, rope ? rope[0] : 0.0f, rope ? rope[1] : 0.0f};
+    const tk::FuseAppend fa{fuse_k, fuse_v, rope ? h->d_rope_tab : nullptr};
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
     if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
     if (mma) {
@@ -765,6 +770,13 @@ int tk_kv_rope_append_decode(tk_kv* h, int32_t layer, const void* k, const void*
                          !h->plan.has_empty_seq && getenv("TK_SEPARATE_APPEND") == nullptr;
     if (fusable) {
         const float rope[2] = {theta, scaling};
+        // cos/sin of each sequence's newest position: computed once per step, shared by all layers
+        if (h->rope_tab_step != h->stats.steps || h->rope_tab_theta != theta || h->rope_tab_scaling != scaling) {
+            cudaError_t te = tk::launch_rope_table(h->geo, h->dev, h->d_rope_tab, theta, scaling, (cudaStream_t)stream);
+            h->launches++;
+            if (te != cudaSuccess) return fail(h, TK_CUDA_ERROR, "rope table launch: %s", cudaGetErrorString(te));
+            h->rope_tab_step = h->stats.steps; h->rope_tab_theta = theta; h->rope_tab_scaling = scaling;
+        }
         return decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream, -1, -1, k, v, rope);
     }
     cudaError_t e = tk::launch_rope16(h->geo, h->dev, q, k, h->d_rq, h->d_rk, theta, scaling, (cudaStream_t)stream);

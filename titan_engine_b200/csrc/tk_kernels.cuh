@@ -61,11 +61,14 @@ struct MergeOut {
 struct FuseAppend {
     const void* k;              // [n_tokens][Hkv][D] 16-bit
     const void* v;
-    // rope != 0: q and the new K row are rotated on the fly (interleaved pairs (d, d+1),
-    // freq = (1/powf(theta, d/D)) * scaling, angle = position * freq) before they are used/stored
-    int   rope;
-    float rope_theta, rope_scaling;
+    // rope_tab != null: q and the new K row are rotated on the fly (interleaved pairs (d, d+1))
+    // before they are used/stored; rope_tab[b][d/2] = (cos, sin) of position len_b - 1, filled once
+    // per step by launch_rope_table with freq = (1/powf(theta, d/D)) * scaling, angle = pos * freq
+    const float2* rope_tab;
 };
+
+cudaError_t launch_rope_table(const Geometry& g, const StepDev& st, float2* tab, float theta, float scaling,
+                              cudaStream_t s);
 
 // RoPE of a step's rows into separate buffers (used when the rotation cannot ride inside the
 // attention kernel): q rows take position len-1 of their sequence, k rows their token position.
