@@ -34,6 +34,10 @@ METRIC = "paged_decode_steps_per_s"
 UNIT = "decode steps/s (1 step = 64 seqs x 32 layers: append 1 token + paged GQA attention)"
 SHAPE = dict(H=32, Hkv=8, D=128, L=32, B=64, lo=1024, hi=8192, ps=16)
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch divided by its algorithmic
+# bytes, from the ncu captures summarised under profiles/ (taken on a 4-layer / 2-layer cut of the
+# same workload; the traffic is proportional to the tokens read, so it scales to a full launch)
+TRAFFIC_OVER_ALGORITHMIC = {"8b-bf16": 1.0085, "70b-fp8": 1.0108}
 
 
 def measured_peak():
@@ -52,12 +56,15 @@ def contexts(rank: int, B: int, lo: int, hi: int) -> np.ndarray:
 
 
 def algorithmic_bytes(ctx: np.ndarray, s=SHAPE):
-    """Per layer per step: K+V of every live token read once per kv head + appended rows +
-    q read and out write + page-table entries; `kernel` is the share the decode kernel moves."""
-    esize = 2
+    """Per layer per step: K+V of every live token read once per kv head (+ FP8 page scales) +
+    appended rows + q read and out write + page-table entries; `kernel` is the share the decode
+    kernel moves."""
+    esize = s.get("esize", 2)
     kv = int(ctx.sum()) * s["Hkv"] * s["D"] * 2 * esize
-    app = len(ctx) * s["Hkv"] * s["D"] * 2 * esize
-    qo = 2 * len(ctx) * s["H"] * s["D"] * esize
+    if esize == 1:
+        kv += int(((ctx + s["ps"] - 1) // s["ps"]).sum()) * s["Hkv"] * 2 * 4
+    app = len(ctx) * s["Hkv"] * s["D"] * 2 * 2
+    qo = 2 * len(ctx) * s["H"] * s["D"] * 2
     pt = int(((ctx + s["ps"] - 1) // s["ps"]).sum()) * 4
     return {"layer": kv + app + qo + pt, "kernel": kv + qo // 2 + pt}
 
@@ -191,6 +198,13 @@ def run_reference(args):
 
 
 def config_dict(ctx, n_gpus):
+    if SHAPE.get("esize", 2) == 1:
+        return {"workload": "llama-3-70b-shape FP8 decode: 64 q heads / 8 kv heads, head_dim 128, FP8-E4M3 pool with "
+                            "per-page per-head scales, 32 sequences/GPU at 32768 tokens, page 16, shuffled pool; "
+                            "resident layer subset (80 layers = 172 GB do not fit one GPU)",
+                "sequences_per_gpu": int(len(ctx)), "live_tokens_per_gpu": int(ctx.sum()),
+                "parallelism": f"by sequence x{n_gpus} (no data-path collective)",
+                "l2": "inputs larger than L2: each layer reads its own ~2.1 GB of pool per step"}
     return {"workload": "llama-3.1-8b-shape batched decode: 32 q heads / 8 kv heads, head_dim 128, "
                         "32 layers, bf16, 64 sequences/GPU, context U[1024,8192], page 16, shuffled pool",
             "sequences_per_gpu": int(len(ctx)), "live_tokens_per_gpu": int(ctx.sum()),
@@ -226,7 +240,8 @@ def run_ours(args):
     pages_end = (ctx + total_steps + ps - 1) // ps
     num_pages = int(pages_end.sum()) + 64
     mpps = int(pages_end.max()) + 1
-    cache = PagedKVCache(L, s["H"], s["Hkv"], s["D"], num_pages, B, mpps, dtype="bf16",
+    fp8 = s.get("esize", 2) == 1
+    cache = PagedKVCache(L, s["H"], s["Hkv"], s["D"], num_pages, B, mpps, dtype="fp8" if fp8 else "bf16",
                          max_step_tokens=B, decode_impl=args.decode_impl, chunk_tokens=args.chunk)
     g = np.random.Generator(np.random.Philox(2 + 1000 * rank))
     perm = g.permutation(num_pages).astype(np.int32)
@@ -238,7 +253,17 @@ def run_ours(args):
         seqs.append(sid)
     gen = torch.Generator(device=dev); gen.manual_seed(1234 + rank)
     for l in range(L):                                          # N(0,1) K/V in every page
-        cache.layer_views(l)[0].normal_(generator=gen)
+        pool, scales, open_pages = cache.layer_views(l)
+        if not fp8:
+            pool.normal_(generator=gen)
+            continue
+        # sealed pages as appending N(0,1) data would leave them: scale ~ amax/448, E4M3 codes of x/scale
+        scales.uniform_(0.008, 0.010, generator=gen)
+        for p0 in range(0, pool.shape[0], 8192):
+            sl = slice(p0, min(p0 + 8192, pool.shape[0]))
+            x = torch.randn(pool[sl].shape, device=dev, generator=gen)
+            pool[sl] = (x / scales[sl][..., None, None]).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        open_pages.normal_(generator=gen)
     k = torch.randn(B, s["Hkv"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
     v = torch.randn(B, s["Hkv"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
     q = torch.randn(B, s["H"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
@@ -321,19 +346,24 @@ def run_ours(args):
     value = world * args.steps / (ms / 1e3)
     kern_avg_ms = kern_ms / max(kern_n, 1)
     achieved = ab["kernel"] / (kern_avg_ms * 1e-3) / 1e9 if kern_n else None
+    unit = UNIT if not fp8 else (f"decode steps/s (1 step = {B} seqs x {L} layers: append 1 token + paged GQA "
+                                 "attention over the FP8 pool)")
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config_dict(ctx, world),
+        "vs_baseline": None, "dtype": "fp8_e4m3 storage, fp16 mma, f32 accumulate" if fp8 else "bf16",
+        "data": "synthetic", "config": config_dict(ctx, world),
         "hbm_gbs_step": ab["layer"] * L / (ms_per_step * 1e-3) / 1e9,
         "hbm_frac_step": ab["layer"] * L / (ms_per_step * 1e-3) / 1e9 / peak,
         "layers": L, "chunk_tokens": cache.step_chunk_tokens, "work_items_per_layer": cache.step_num_work_items,
         "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if args.decode_impl != "simt" else "decode_simt_kernel",
                      "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": (achieved / peak) if achieved else None, "traffic": None,
+                     "frac": (achieved / peak) if achieved else None,
+                     "traffic": int(ab["kernel"] * TRAFFIC_OVER_ALGORITHMIC[args.workload]),
+                     "traffic_source": "ncu dram bytes of a reduced-layer capture (profiles/), scaled by tokens",
                      "algorithmic_bytes_per_launch": ab["kernel"], "avg_launch_ms": kern_avg_ms,
                      "launches_timed": kern_n, "peak_source": peak_src},
-        "e2e": {"value": world * args.steps / (ms_e2e / 1e3), "unit": UNIT,
+        "e2e": {"value": world * args.steps / (ms_e2e / 1e3), "unit": unit,
                 "h2d_bytes_per_step": int(L * (hk.numel() + hv.numel() + hq.numel()) * 2),
                 "d2h_bytes_per_step": int(L * hout.numel() * 2), "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clocks,
@@ -355,7 +385,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=SHAPE["L"])
+    ap.add_argument("--workload", default="8b-bf16", choices=["8b-bf16", "70b-fp8"],
+                    help="8b-bf16: the headline batched decode; 70b-fp8: 64 q / 8 kv heads, 32 sequences at 32768 "
+                         "tokens, FP8-E4M3 pool, a resident subset of the 80 layers (extra, not the headline)")
+    ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--decode-impl", default="auto", choices=["auto", "simt", "mma"])
     ap.add_argument("--chunk", type=int, default=0, help="split-KV chunk tokens (0 = library default)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
@@ -363,6 +396,10 @@ def main():
     ap.add_argument("--rope", action="store_true", help="also fuse RoPE of q and the new K rows into each layer's call")
     ap.add_argument("--separate", action="store_true", help="call append and decode separately (two entry points)")
     args = ap.parse_args()
+    if args.workload == "70b-fp8":
+        SHAPE.update(H=64, Hkv=8, D=128, L=16, B=32, lo=32768, hi=32768, esize=1)
+        args.no_cpu = True
+    args.layers = args.layers or SHAPE["L"]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
