@@ -268,6 +268,13 @@ int tk_sched_request_state(const tk_sched* s, int32_t request_id, int32_t* state
 int tk_sched_last_events(const tk_sched* s, int32_t which, int32_t cap, int32_t* seqs, int32_t* n_out);
 int tk_sched_get_stats(const tk_sched* s, tk_sched_stats* out);
 
+/* Failure-detection self-test.  Every device-side wait in this library is bounded; this launches
+ * one warp that waits limit_ms (1..2000) on a barrier nothing completes, so the wait runs out and
+ * the kernel returns normally with the status word set: the next tk_kv_device_status reports
+ * TK_TIMEOUT and the context stays usable.  (The reference reports failures as bool / log lines
+ * only, src/inference/kv_cache.cpp:34-47.) */
+int tk_kv_selftest_bounded_wait(tk_kv* h, int32_t limit_ms, void* stream);
+
 /* Number of kernels this library has launched on this handle so far. */
 int64_t tk_kv_launch_count(const tk_kv* h);
 

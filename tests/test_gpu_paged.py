@@ -360,3 +360,19 @@ def test_scheduler_drives_churn_on_gpu():
     st = s.stats()
     assert st["completed_requests"] == 10 and st["active_requests"] == 0 and steps > 50
     assert t.gpu.num_free_pages == 48 and t.gpu.digest() == t.mgr.digest()
+
+
+def test_bounded_device_wait_reports_timeout_and_context_survives():
+    """Failure detection without a fault: a device wait that nothing satisfies runs out after its
+    limit, the kernel returns, the host reads TK_TIMEOUT, and the same handle keeps working."""
+    from titan_engine_b200 import KvError, _lib as L
+    t = Twin(1, 8, 2, 64, 16, 1, 16, dtype="fp16", impl="mma", max_step_tokens=64, seed=90)
+    s = t.seq_alloc()
+    t.step([s], [40])
+    st = t.gpu._lib.tk_kv_selftest_bounded_wait(t.gpu._h, 50, torch.cuda.current_stream().cuda_stream)
+    assert st == L.TK_OK
+    with pytest.raises(KvError) as e:
+        t.gpu.device_status()
+    assert e.value.status == L.TK_TIMEOUT
+    t.gpu.device_status()                     # the word was cleared
+    t.step([s], [1])                          # and the context is fine

@@ -88,6 +88,7 @@ SIGNATURES = {
     "tk_paged_decode_static": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _I32P, C.c_int32, C.c_int32,
                                         C.c_int32, C.c_int32, _P, _P, _P]),
     "tk_kv_device_status": (C.c_int, [_P, _P]),
+    "tk_kv_selftest_bounded_wait": (C.c_int, [_P, C.c_int32, _P]),
     "tk_kv_launch_count": (C.c_int64, [_P]),
     "tk_sched_create": (C.c_int, [_P, C.POINTER(SchedConfig), C.POINTER(_P)]),
     "tk_sched_destroy": (C.c_int, [_P]),

@@ -75,11 +75,12 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     return t;
 }
 // Wait with a wall-clock bound: on expiry record it and give up instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int* status,
+                                                  unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     while (!mbar_try_wait(bar, parity)) {
-        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             if (status) atomicExch(status, 4 /* TK_TIMEOUT */);
             return false;
         }
@@ -483,6 +484,18 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     merge_if_last(g, st, mo, b, kvh, G, partials, s_flag);
 }
 
+// One warp waits, with the same bounded wait the decode kernel uses, on a barrier that nothing
+// ever completes: the wait runs out, the status word is set, the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    (void)__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&bar), 0u, status, limit_ns));
+}
+
 template <int KIND, int D, bool IO_BF16, bool GHI>
 cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                        const CUtensorMap* map_cold, const StepDev& st,
@@ -516,6 +529,11 @@ cudaError_t launch_kd(const Geometry& g, const LayerPtrs& lp, const CUtensorMap*
 }
 
 }  // namespace
+
+cudaError_t launch_bounded_wait_selftest(int* status, unsigned long long limit_ns, cudaStream_t s) {
+    bounded_wait_selftest_kernel<<<1, 32, 0, s>>>(status, limit_ns);
+    return cudaGetLastError();
+}
 
 bool decode_mma_supported(const Geometry& g) {
     if (g.ps != kPage || g.Hkv <= 0 || g.H % g.Hkv != 0 || g.H / g.Hkv > 16) return false;

@@ -904,6 +904,14 @@ int tk_kv_device_status(tk_kv* h, void* stream) {
     return TK_OK;
 }
 
+int tk_kv_selftest_bounded_wait(tk_kv* h, int32_t limit_ms, void* stream) {
+    if (!h || h->host_only || limit_ms <= 0 || limit_ms > 2000) return TK_INVALID_ARG;
+    cudaError_t e = tk::launch_bounded_wait_selftest(h->d_status, (unsigned long long)limit_ms * 1000000ull,
+                                                     (cudaStream_t)stream);
+    h->launches++;
+    return e == cudaSuccess ? TK_OK : fail(h, TK_CUDA_ERROR, "selftest launch: %s", cudaGetErrorString(e));
+}
+
 int64_t tk_kv_launch_count(const tk_kv* h) { return h ? h->launches : 0; }
 
 }  // extern "C"

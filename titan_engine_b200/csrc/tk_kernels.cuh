@@ -98,6 +98,10 @@ cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUte
 // n FP32 values -> the 16-bit type `dtype` (round to nearest even).
 cudaError_t launch_f32_to_16(const float* src, void* dst, size_t n, int dtype, cudaStream_t s);
 
+// Failure-detection self-test: a bounded device wait that is made to run out (nothing completes
+// the barrier); sets *status to TK_TIMEOUT after limit_ns and returns.
+cudaError_t launch_bounded_wait_selftest(int* status, unsigned long long limit_ns, cudaStream_t s);
+
 // LSE merge over each sequence's partial rows.
 //   out != null     : normalised [n_seqs][H][D] in out_dtype
 //   partial_out!=null: merged but unnormalised [n_seqs][H][D+2]
