@@ -51,7 +51,9 @@ def measured_peak():
 
 
 def contexts(rank: int, B: int, lo: int, hi: int) -> np.ndarray:
-    g = np.random.Generator(np.random.Philox(2 + 1000 * rank))
+    """Context lengths of one GPU's batch.  Every rank draws the SAME lengths (seed 2), so that the
+    per-GPU work is fixed as N grows (weak scaling); page placement and K/V data differ per rank."""
+    g = np.random.Generator(np.random.Philox(2))
     return g.integers(lo, hi + 1, size=B).astype(np.int64)
 
 
