@@ -700,21 +700,13 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
     if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
     if (mma) {
-        tk::StepDev pool = h->dev;
-        pool.n_items = h->n_pool_items;
-        if (pool.n_items > 0) {
-            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], cold ? &h->stage_maps[slot] : nullptr, pool,
+        // FP8: the 16-bit open pages are items of kind 1 of the same launch
+        if (h->dev.n_items > 0) {
+            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], cold ? &h->stage_maps[slot] : nullptr, h->dev,
                                       h->d_table, q, h->d_partials, h->d_status, s, &mo, &fa);
             h->launches++;
         }
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }
-        if (e == cudaSuccess && h->dev.n_items > h->n_pool_items) {      // FP8 open pages: 16-bit tail
-            tk::StepDev open = h->dev;
-            open.items = h->dev.items + h->n_pool_items;
-            open.n_items = h->dev.n_items - h->n_pool_items;
-            e = tk::launch_decode_simt(h->geo, lp, open, h->d_table, q, h->d_partials, s, &mo);
-            h->launches++;
-        }
     } else {
         if (h->dev.n_items > 0) {
             e = tk::launch_decode_simt(h->geo, lp, h->dev, h->d_table, q, h->d_partials, s, &mo);
@@ -746,9 +738,12 @@ int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, c
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "append_decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "append_decode: no step in progress (call tk_kv_step_begin)");
-    const bool fusable = h->use_mma && h->cfg.dtype != TK_FP8_E4M3 && h->plan.one_token_steps &&
-                         h->dev.chunk_tokens <= 2048 && h->dev.n_tokens > 0 && h->dev.n_seqs > 0 &&
-                         !h->plan.has_empty_seq && getenv("TK_SEPARATE_APPEND") == nullptr;
+    // 16-bit storage: the new row goes into the page the kernel is about to read.  FP8 storage: it
+    // goes into the sequence's 16-bit open page, unless this step completes (seals) a page.
+    const bool fusable = h->use_mma && h->plan.one_token_steps && h->dev.chunk_tokens <= 2048 &&
+                         h->dev.n_tokens > 0 && h->dev.n_seqs > 0 && !h->plan.has_empty_seq &&
+                         (h->cfg.dtype != TK_FP8_E4M3 || h->plan.seals.empty()) &&
+                         getenv("TK_SEPARATE_APPEND") == nullptr;
     if (!fusable) {
         int st = tk_kv_append(h, layer, k, v, nullptr, stream);
         if (st != TK_OK) return st;
