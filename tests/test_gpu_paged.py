@@ -376,3 +376,30 @@ def test_bounded_device_wait_reports_timeout_and_context_survives():
     assert e.value.status == L.TK_TIMEOUT
     t.gpu.device_status()                     # the word was cleared
     t.step([s], [1])                          # and the context is fine
+
+
+def test_edge_cases_on_gpu():
+    """Empty and maximal inputs: a sequence with no tokens attends to nothing (output 0, the
+    reference's 0/(0+1e-8)); a sequence filling its whole page-table row; pool exhaustion that must
+    leave the device state untouched; FP8 with head_dim 64 (no tensor-core path: generic kernel)."""
+    from titan_engine_b200 import KvError, _lib as L
+    t = Twin(1, 8, 2, 64, 12, 3, 8, dtype="fp16", impl="mma", max_step_tokens=256, seed=95)
+    a, b, c = t.seq_alloc(), t.seq_alloc(), t.seq_alloc()
+    outs = t.step([a, b, c], [128, 0, 5])                 # a fills all 8 entries of its row; b is empty
+    assert np.all(outs[0][1] == 0.0)
+    with pytest.raises(KvError) as e:
+        t.gpu.step_begin([a], [1])                        # a 9th page does not fit the row
+    assert e.value.status == L.TK_INVALID_ARG
+    with pytest.raises(KvError) as e:
+        t.gpu.step_begin([b, c], [40, 30])                # 3 + 2 more pages, 3 free
+    assert e.value.status == L.TK_OUT_OF_PAGES
+    assert t.gpu.digest() == t.mgr.digest()               # nothing changed
+    t.step([c, b], [11, 33])                              # exactly the 3 free pages
+    assert t.gpu.num_free_pages == 0
+    t.step([a, b, c], None, fused=False)                  # decode only on a full pool
+
+    f = Twin(1, 8, 2, 64, 16, 2, 8, dtype="fp8", io="fp16", impl="auto", max_step_tokens=256, seed=96)
+    s = f.seq_alloc()
+    f.step([s], [50], check_pool=True)
+    for _ in range(15):
+        f.step([s], [1], check_pool=True, fused=True)

@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -130,6 +131,10 @@ struct tk_kv {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_ev;    // start/stop pairs
     size_t prof_used = 0;
+
+    // guards the page manager: allocator calls may come from another thread than the stepping one
+    // (the reference's pools are mutex-guarded the same way: src/memory/vram_pool.cpp:47)
+    std::mutex mgr_mu;
 
     tk_kv_stats stats{};
     int64_t launches = 0;
@@ -465,6 +470,7 @@ int tk_kv_layer_ptrs(const tk_kv* h, int layer, void** pool, float** scales, voi
 // ---- sequences and pages -------------------------------------------------------------
 int tk_kv_seq_alloc(tk_kv* h, int32_t* seq_out) {
     if (!h || !seq_out) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
     int s = h->mgr->seq_alloc();
     if (s < 0) return fail(h, TK_OUT_OF_SEQS, "all %d sequence slots are in use", h->cfg.max_seqs);
     *seq_out = s;
@@ -472,16 +478,19 @@ int tk_kv_seq_alloc(tk_kv* h, int32_t* seq_out) {
 }
 int tk_kv_seq_free(tk_kv* h, int32_t seq) {
     if (!h) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
     int st = h->mgr->seq_free(seq);
     return st == TK_OK ? TK_OK : fail(h, st, "seq_free(%d): sequence is not live", seq);
 }
 int tk_kv_reserve(tk_kv* h, int32_t seq, int32_t n) {
     if (!h) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
     int st = h->mgr->reserve(seq, n);
     return st == TK_OK ? TK_OK : fail(h, st, "reserve(%d, %d): %s", seq, n, tk_status_str(st));
 }
 int tk_kv_truncate(tk_kv* h, int32_t seq, int32_t new_len) {
     if (!h) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
     if (h->cfg.dtype == TK_FP8_E4M3 && h->mgr->live(seq) && new_len % h->cfg.page_size != 0 &&
         new_len / h->cfg.page_size < h->mgr->seq_len(seq) / h->cfg.page_size)
         return fail(h, TK_UNSUPPORTED, "FP8: cannot truncate into a sealed page (length must stay page-aligned there)");
@@ -490,6 +499,7 @@ int tk_kv_truncate(tk_kv* h, int32_t seq, int32_t new_len) {
 }
 int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t seq_len) {
     if (!h || (n_pages > 0 && !pages)) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
     if (h->cfg.dtype == TK_FP8_E4M3 && seq_len % h->cfg.page_size != 0)
         return fail(h, TK_UNSUPPORTED, "FP8: adopted length must be page-aligned (no open page to adopt)");
     int st = h->mgr->adopt(seq, pages, n_pages, seq_len);
@@ -497,6 +507,7 @@ int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages
 }
 int tk_kv_seq_set_tail(tk_kv* h, int32_t seq, int32_t tail_tokens) {
     if (!h) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
     int st = h->mgr->set_tail(seq, tail_tokens);
     return st == TK_OK ? TK_OK : fail(h, st, "seq_set_tail(%d, %d): sequence not live or negative tail", seq, tail_tokens);
 }
@@ -533,6 +544,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     if (!h) return TK_INVALID_ARG;
     if (len_cap && h->cfg.dtype == TK_FP8_E4M3)
         return fail(h, TK_UNSUPPORTED, "step_begin: an attended-length cap needs 16-bit storage");
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
     h->have_step = false;
     const char* env_chunk = getenv("TK_CHUNK_TOKENS");
     int chunk = h->cfg.chunk_tokens;
