@@ -117,6 +117,12 @@ int tk_kv_truncate(tk_kv* h, int32_t seq, int32_t new_len);
 /* Install a caller-chosen page list (e.g. a shuffled pool) as the table of `seq`;
  * the pages must be free. */
 int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages, int32_t seq_len);
+/* Prefix sharing: a new sequence (lowest free slot) with the same tokens as `parent`.  Full pages
+ * are shared between the two (reference-counted, freed when the last owner lets go); a partly
+ * filled last page is copied on `stream` into a fresh page, so that both can go on appending.
+ * TK_OUT_OF_SEQS / TK_OUT_OF_PAGES change nothing.  Not available with a cold tier.
+ * (The reference has neither prefix sharing nor rollback: src/inference/speculative.cpp:306-307.) */
+int tk_kv_seq_fork(tk_kv* h, int32_t parent, int32_t* child_out, void* stream);
 /* For a sequence whose tokens are split over several caches (one per GPU): tail_tokens of it
  * follow this cache's last token, so the hot window is measured from seq_len + tail_tokens. */
 int tk_kv_seq_set_tail(tk_kv* h, int32_t seq, int32_t tail_tokens);

@@ -189,6 +189,7 @@ struct tko_mgr {
     /* cold tier (off unless tko_mgr_enable_cold): host-resident pages, ids from their own LIFO stack;
      * a cold page is recorded in the table as -2 - cold_id */
     int hot_window, num_cold_pages; int32_t* cold_stack; int cold_top;
+    int32_t* refcount;   /* per page: sequences whose table names it (prefix sharing after a fork) */
     int32_t* seq_tail;   /* tokens of the logical sequence held AFTER this cache's last one (other ranks) */
 };
 
@@ -206,17 +207,22 @@ tko_mgr* tko_mgr_create(int num_pages, int max_seqs, int max_pages_per_seq, int 
     m->seq_len = (int32_t*)malloc(sizeof(int32_t) * (size_t)max_seqs);
     m->seq_pages = (int32_t*)calloc((size_t)max_seqs, sizeof(int32_t));
     m->seq_tail = (int32_t*)calloc((size_t)max_seqs, sizeof(int32_t));
+    m->refcount = (int32_t*)calloc((size_t)num_pages, sizeof(int32_t));
     for (int i = 0; i < max_seqs; i++) m->seq_len[i] = -1;
     return m;
 }
 void tko_mgr_destroy(tko_mgr* m) {
     if (!m) return;
-    free(m->seq_tail); free(m->cold_stack); free(m->free_stack); free(m->page_table); free(m->seq_len); free(m->seq_pages); free(m);
+    free(m->refcount); free(m->seq_tail); free(m->cold_stack); free(m->free_stack); free(m->page_table); free(m->seq_len); free(m->seq_pages); free(m);
 }
 int tko_seq_alloc(tko_mgr* m) {
     for (int i = 0; i < m->max_seqs; i++)
         if (m->seq_len[i] < 0) { m->seq_len[i] = 0; m->seq_pages[i] = 0; m->seq_tail[i] = 0; return i; }
     return -1;
+}
+/* A sequence lets go of a device page: back to the free stack when nobody else names it. */
+static void release_page(tko_mgr* m, int32_t page) {
+    if (--m->refcount[page] <= 0) { m->refcount[page] = 0; m->free_stack[m->free_top++] = page; }
 }
 static int live(const tko_mgr* m, int seq) { return seq >= 0 && seq < m->max_seqs && m->seq_len[seq] >= 0; }
 int tko_seq_free(tko_mgr* m, int seq) {
@@ -224,7 +230,7 @@ int tko_seq_free(tko_mgr* m, int seq) {
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
     for (int i = 0; i < m->seq_pages[seq]; i++) {
         if (row[i] <= -2) m->cold_stack[m->cold_top++] = -2 - row[i];
-        else              m->free_stack[m->free_top++] = row[i];
+        else              release_page(m, row[i]);
         row[i] = -1;
     }
     m->seq_pages[seq] = 0; m->seq_len[seq] = -1;
@@ -254,7 +260,7 @@ int tko_evict_cold(tko_mgr* m, int seq, int stable_len) {
     if (need > m->cold_top) return -1;
     for (int i = 0; i < n_cold; i++) {
         if (row[i] < 0) continue;
-        m->free_stack[m->free_top++] = row[i];
+        release_page(m, row[i]);
         row[i] = -2 - m->cold_stack[--m->cold_top];
     }
     return need;
@@ -274,7 +280,7 @@ int tko_reserve(tko_mgr* m, int seq, int n_tokens) {
     int extra = (int)need_pages - m->seq_pages[seq];
     if (extra > m->free_top) return TKO_OUT_OF_PAGES;
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
-    for (int i = 0; i < extra; i++) row[m->seq_pages[seq]++] = m->free_stack[--m->free_top];
+    for (int i = 0; i < extra; i++) { int32_t pg = m->free_stack[--m->free_top]; m->refcount[pg] = 1; row[m->seq_pages[seq]++] = pg; }
     m->seq_len[seq] = (int32_t)new_len;
     return TKO_OK;
 }
@@ -285,7 +291,7 @@ int tko_truncate(tko_mgr* m, int seq, int new_len) {
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
     for (int i = keep; i < m->seq_pages[seq]; i++) {
         if (row[i] <= -2) m->cold_stack[m->cold_top++] = -2 - row[i];
-        else              m->free_stack[m->free_top++] = row[i];
+        else              release_page(m, row[i]);
         row[i] = -1;
     }
     m->seq_pages[seq] = keep; m->seq_len[seq] = new_len;
@@ -307,10 +313,41 @@ int tko_adopt(tko_mgr* m, int seq, const int32_t* pages, int n_pages, int seq_le
     for (int i = 0; i < m->free_top; i++) if (!want[m->free_stack[i]]) m->free_stack[w++] = m->free_stack[i];
     m->free_top = w;
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
-    for (int i = 0; i < n_pages; i++) row[i] = pages[i];
+    for (int i = 0; i < n_pages; i++) { row[i] = pages[i]; m->refcount[pages[i]] = 1; }
     m->seq_pages[seq] = n_pages; m->seq_len[seq] = seq_len;
     free(want);
     return TKO_OK;
+}
+/* Prefix sharing: a new sequence (lowest free slot) with the same tokens as `parent`.  Full pages
+ * are shared (reference-counted); a partly filled last page is copied into a fresh page taken
+ * from the free stack (*copy_src / *copy_dst name it, -1 when there is none).  Returns the child
+ * slot, -1 when no slot is free, -2 when no page is free (nothing changes in either case). */
+int tko_fork(tko_mgr* m, int parent, int32_t* copy_src, int32_t* copy_dst) {
+    if (copy_src) *copy_src = -1;
+    if (copy_dst) *copy_dst = -1;
+    if (!live(m, parent) || m->cold_stack) return -3;
+    const int len = m->seq_len[parent], n_pg = m->seq_pages[parent];
+    const int partial = len % m->page_size != 0;
+    int child = -1;
+    for (int i = 0; i < m->max_seqs; i++) if (m->seq_len[i] < 0) { child = i; break; }
+    if (child < 0) return -1;
+    if (partial && m->free_top < 1) return -2;
+    const int32_t* prow = m->page_table + (size_t)parent * m->max_pages_per_seq;
+    int32_t* crow = m->page_table + (size_t)child * m->max_pages_per_seq;
+    for (int i = 0; i < n_pg; i++) {
+        if (partial && i == n_pg - 1) {
+            int32_t pg = m->free_stack[--m->free_top];
+            m->refcount[pg] = 1;
+            crow[i] = pg;
+            if (copy_src) *copy_src = prow[i];
+            if (copy_dst) *copy_dst = pg;
+        } else {
+            crow[i] = prow[i];
+            m->refcount[prow[i]]++;
+        }
+    }
+    m->seq_len[child] = len; m->seq_pages[child] = n_pg; m->seq_tail[child] = 0;
+    return child;
 }
 int tko_seq_len(const tko_mgr* m, int seq) { return live(m, seq) ? m->seq_len[seq] : -1; }
 int tko_seq_num_pages(const tko_mgr* m, int seq) { return live(m, seq) ? m->seq_pages[seq] : -1; }

@@ -64,6 +64,7 @@ int      tko_mgr_enable_cold(tko_mgr* m, int hot_window, int num_cold_pages);
 int      tko_evict_cold(tko_mgr* m, int seq, int stable_len);   /* pages moved, -1 if the cold pool is full */
 int      tko_num_cold_used(const tko_mgr* m);
 int      tko_set_tail(tko_mgr* m, int seq, int tail);
+int      tko_fork(tko_mgr* m, int parent, int32_t* copy_src, int32_t* copy_dst);  /* child slot; -1 no slot, -2 no page */
 int      tko_seq_len(const tko_mgr* m, int seq);       /* -1 if seq not live */
 int      tko_seq_num_pages(const tko_mgr* m, int seq);
 int      tko_num_free_pages(const tko_mgr* m);

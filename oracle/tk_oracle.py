@@ -61,6 +61,7 @@ def lib() -> C.CDLL:
             "tko_evict_cold": (i, [vp, i, i]),
             "tko_num_cold_used": (i, [vp]),
             "tko_set_tail": (i, [vp, i, i]),
+            "tko_fork": (i, [vp, i, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
             "tko_seq_len": (i, [vp, i]),
             "tko_seq_num_pages": (i, [vp, i]),
             "tko_num_free_pages": (i, [vp]),
@@ -163,6 +164,12 @@ class Manager:
     def evict_cold(self, s, stable_len): return self.l.tko_evict_cold(self.h, s, stable_len)
     def num_cold_used(self): return self.l.tko_num_cold_used(self.h)
     def set_tail(self, s, tail): return self.l.tko_set_tail(self.h, s, tail)
+    def fork(self, parent):
+        """-> (child slot or negative code, copy_src page, copy_dst page)"""
+        a, b = C.c_int32(-1), C.c_int32(-1)
+        child = self.l.tko_fork(self.h, parent, C.byref(a), C.byref(b))
+        return child, a.value, b.value
+
     def seq_len(self, s): return self.l.tko_seq_len(self.h, s)
     def num_free_pages(self): return self.l.tko_num_free_pages(self.h)
     def slot(self, s, pos): return self.l.tko_slot(self.h, s, pos)

@@ -100,6 +100,20 @@ class Twin:
         if self.flat:
             assert self.flat.seq_free(s) == O.OK
 
+    def fork(self, parent):
+        """Prefix sharing on both sides: shared full pages, private copy of a partly filled last page."""
+        child = self.gpu.fork(parent)
+        o_child, src, dst = self.mgr.fork(parent)
+        assert child == o_child
+        if dst >= 0:
+            for p in self.pools:
+                if self.dt == O.FP8:
+                    p.open_pages[child] = p.open_pages[parent]
+                else:
+                    p.pool[dst] = p.pool[src]
+        assert self.gpu.digest() == self.mgr.digest()
+        return child
+
     def adopt(self, s, pages, seq_len):
         """Install a caller-chosen page list (a shuffled pool) on both sides."""
         self.gpu.adopt(s, pages, seq_len)

@@ -403,3 +403,25 @@ def test_edge_cases_on_gpu():
     f.step([s], [50], check_pool=True)
     for _ in range(15):
         f.step([s], [1], check_pool=True, fused=True)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+def test_fork_prefix_sharing(dtype):
+    """Two sequences share the pages of a common prefix; each then appends its own tokens.  Page
+    state is bit-exact against the oracle, attention of both within tolerance, and freeing one of
+    them leaves the other intact."""
+    t = Twin(2, 32, 8, 128, 64, 4, 32, dtype=dtype, impl="mma", max_step_tokens=1024, seed=97)
+    a = t.seq_alloc()
+    t.step([a], [200], check_pool=True)                   # 12 full pages + 8 tokens
+    b = t.fork(a)
+    assert t.gpu.page_table(b)[:12].tolist() == t.gpu.page_table(a)[:12].tolist()
+    assert t.gpu.page_table(b)[12] != t.gpu.page_table(a)[12]
+    t.step([a, b], [1, 1], check_pool=True, fused=True)   # diverge: different tokens in their own last pages
+    for i in range(12):
+        t.step([a, b], [1, 3 if i % 2 else 1], check_pool=(i % 4 == 0), fused=(i % 2 == 0))
+    c = t.fork(b)
+    t.step([a, b, c], [1, 1, 17], check_pool=True)
+    t.seq_free(a)
+    t.step([b, c], [1, 1], check_pool=True, fused=True)
+    t.seq_free(b); t.seq_free(c)
+    assert t.gpu.num_free_pages == 64

@@ -228,3 +228,41 @@ def test_cold_tier_state_matches_oracle_manager():
     assert c.stats()["pages_cold"] == (701 - 64) // 16 + 92 // 16
     with pytest.raises(KvError):
         PagedKVCache(2, 8, 2, 64, 8, 2, 8, dtype="fp8", host_only=True, hot_window=64, cold_pages=8)
+
+
+def test_fork_shares_full_pages_and_counts_references():
+    c = host_cache(num_pages=16, max_seqs=4, mpps=8)
+    o = O.Manager(16, 4, 8, 16)
+    a = c.seq_alloc(); assert o.seq_alloc() == a
+    c.reserve(a, 40); assert o.reserve(a, 40) == O.OK           # pages 0,1 full-ish: 0,1 full, 2 partial
+    b = c.fork(a)
+    ob, src, dst = o.fork(a)
+    assert (b, ob, src, dst) == (1, 1, 2, 3)
+    np.testing.assert_array_equal(c.page_table(b), [0, 1, 3])   # shares 0 and 1, own copy of the partial page
+    assert c.seq_len(b) == 40 and c.num_free_pages == 12 and c.digest() == o.digest()
+    c.reserve(b, 30); assert o.reserve(b, 30) == O.OK           # both keep growing independently
+    c.reserve(a, 10); assert o.reserve(a, 10) == O.OK
+    assert c.digest() == o.digest()
+    c.seq_free(a); assert o.seq_free(a) == O.OK                 # shared pages stay with b
+    assert c.num_free_pages == o.num_free_pages() == 16 - 5 and c.digest() == o.digest()
+    np.testing.assert_array_equal(c.page_table(b), [0, 1, 3, 4, 5])
+    d = c.fork(b); od, src, dst = o.fork(b)
+    assert d == od == 0 and dst >= 0 and c.digest() == o.digest()
+    with pytest.raises(KvError) as e:
+        c.truncate(d, 20)                                       # would reopen page 1, which b also holds
+    assert e.value.status == L.TK_UNSUPPORTED
+    c.truncate(d, 32); assert o.truncate(d, 32) == O.OK         # page-aligned is fine
+    c.seq_free(b); assert o.seq_free(b) == O.OK
+    c.seq_free(d); assert o.seq_free(d) == O.OK
+    assert c.num_free_pages == 16 and c.digest() == o.digest()
+    # page-aligned parent: nothing to copy, no page taken
+    a = c.seq_alloc(); o.seq_alloc(); c.reserve(a, 32); o.reserve(a, 32)
+    free0 = c.num_free_pages
+    b = c.fork(a); assert o.fork(a) == (b, -1, -1) and c.num_free_pages == free0
+    # no slot / no page left: nothing changes
+    t = host_cache(num_pages=1, max_seqs=2, mpps=4)
+    s = t.seq_alloc(); t.reserve(s, 5)
+    dg = t.digest()
+    with pytest.raises(KvError) as e:
+        t.fork(s)
+    assert e.value.status == L.TK_OUT_OF_PAGES and t.digest() == dg

@@ -60,6 +60,7 @@ SIGNATURES = {
     "tk_kv_reserve": (C.c_int, [_P, C.c_int32, C.c_int32]),
     "tk_kv_truncate": (C.c_int, [_P, C.c_int32, C.c_int32]),
     "tk_kv_seq_adopt": (C.c_int, [_P, C.c_int32, _I32P, C.c_int32, C.c_int32]),
+    "tk_kv_seq_fork": (C.c_int, [_P, C.c_int32, _I32P, _P]),
     "tk_kv_seq_set_tail": (C.c_int, [_P, C.c_int32, C.c_int32]),
     "tk_kv_seq_len": (C.c_int, [_P, C.c_int32]),
     "tk_kv_num_free_pages": (C.c_int, [_P]),

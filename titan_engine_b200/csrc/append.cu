@@ -24,6 +24,23 @@ cudaError_t launch_apply_delta(int32_t* table, const int2* delta, int n, cudaStr
     return cudaGetLastError();
 }
 
+__global__ void copy_layers_kernel(const uint8_t* __restrict__ src, size_t src_stride, uint8_t* __restrict__ dst,
+                                   size_t dst_stride, size_t bytes) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src + (size_t)blockIdx.y * src_stride);
+    uint4* d4 = reinterpret_cast<uint4*>(dst + (size_t)blockIdx.y * dst_stride);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < bytes / 16; i += (size_t)gridDim.x * blockDim.x)
+        d4[i] = s4[i];
+}
+
+cudaError_t launch_copy_layers(const void* src, size_t src_stride, void* dst, size_t dst_stride, size_t bytes,
+                               int n_layers, cudaStream_t s) {
+    if (bytes == 0 || n_layers <= 0) return cudaSuccess;
+    dim3 grid((unsigned)((bytes / 16 + 255) / 256), n_layers);
+    if (grid.x > 64) grid.x = 64;
+    copy_layers_kernel<<<grid, 256, 0, s>>>((const uint8_t*)src, src_stride, (uint8_t*)dst, dst_stride, bytes);
+    return cudaGetLastError();
+}
+
 __device__ __forceinline__ size_t tile_off(int page, int kvh, int kv, int Hkv, int ps, int D) {
     return (((size_t)page * Hkv + kvh) * 2 + kv) * (size_t)ps * D;
 }

@@ -15,6 +15,11 @@ PageManager::PageManager(int num_pages, int max_seqs, int max_pages_per_seq, int
     seq_len_.assign(max_seqs, -1);
     seq_pages_.assign(max_seqs, 0);
     seq_tail_.assign(max_seqs, 0);
+    refcount_.assign(num_pages, 0);
+}
+
+void PageManager::release_page(int32_t page) {
+    if (--refcount_[page] <= 0) { refcount_[page] = 0; free_stack_.push_back(page); }
 }
 
 void PageManager::set_entry(int seq, int idx, int32_t value) {
@@ -49,7 +54,7 @@ int PageManager::seq_free(int seq) {
     const int32_t* r = row(seq);
     for (int i = 0; i < seq_pages_[seq]; i++) {
         if (r[i] <= -2) cold_stack_.push_back(-2 - r[i]);
-        else            free_stack_.push_back(r[i]);
+        else            release_page(r[i]);
         set_entry(seq, i, -1);
     }
     counters.page_frees += seq_pages_[seq];
@@ -69,6 +74,7 @@ int PageManager::reserve(int seq, int n_tokens) {
     for (int i = 0; i < extra; i++) {
         int32_t page = free_stack_.back();
         free_stack_.pop_back();
+        refcount_[page] = 1;
         set_entry(seq, seq_pages_[seq]++, page);
     }
     counters.page_allocs += extra > 0 ? extra : 0;
@@ -80,9 +86,11 @@ int PageManager::truncate(int seq, int new_len) {
     if (!live(seq) || new_len < 0 || new_len > seq_len_[seq]) return ST_INVALID_ARG;
     int keep = (new_len + page_size_ - 1) / page_size_;
     const int32_t* r = row(seq);
+    // the new last page would be appended to later: it must not be shared with another sequence
+    if (new_len % page_size_ != 0 && keep > 0 && r[keep - 1] >= 0 && refcount_[r[keep - 1]] > 1) return ST_UNSUPPORTED;
     for (int i = keep; i < seq_pages_[seq]; i++) {
         if (r[i] <= -2) cold_stack_.push_back(-2 - r[i]);
-        else            free_stack_.push_back(r[i]);
+        else            release_page(r[i]);
         set_entry(seq, i, -1);
         counters.page_frees++;
     }
@@ -105,10 +113,42 @@ int PageManager::adopt(int seq, const int32_t* pages, int n_pages, int seq_len) 
     free_stack_.erase(std::remove_if(free_stack_.begin(), free_stack_.end(),
                                      [&](int32_t p) { return want[p] != 0; }),
                       free_stack_.end());
-    for (int i = 0; i < n_pages; i++) set_entry(seq, i, pages[i]);
+    for (int i = 0; i < n_pages; i++) { set_entry(seq, i, pages[i]); refcount_[pages[i]] = 1; }
     seq_pages_[seq] = n_pages;
     seq_len_[seq] = seq_len;
     counters.page_allocs += n_pages;
+    return ST_OK;
+}
+
+int PageManager::fork(int parent, int* child_out, int32_t* copy_src, int32_t* copy_dst) {
+    if (copy_src) *copy_src = -1;
+    if (copy_dst) *copy_dst = -1;
+    if (!live(parent) || !child_out) return ST_INVALID_ARG;
+    if (cold_enabled()) return ST_UNSUPPORTED;
+    const int len = seq_len_[parent], n_pg = seq_pages_[parent];
+    const bool partial = len % page_size_ != 0;
+    int child = -1;
+    for (int i = 0; i < max_seqs_; i++) if (seq_len_[i] < 0) { child = i; break; }
+    if (child < 0) return ST_OUT_OF_SEQS;
+    if (partial && free_stack_.empty()) return ST_OUT_OF_PAGES;
+    seq_len_[child] = len; seq_pages_[child] = n_pg; seq_tail_[child] = 0;
+    counters.seq_allocs++;
+    for (int i = 0; i < n_pg; i++) {
+        const int32_t src = row(parent)[i];
+        if (partial && i == n_pg - 1) {
+            const int32_t page = free_stack_.back();
+            free_stack_.pop_back();
+            refcount_[page] = 1;
+            set_entry(child, i, page);
+            counters.page_allocs++;
+            if (copy_src) *copy_src = src;
+            if (copy_dst) *copy_dst = page;
+        } else {
+            set_entry(child, i, src);
+            refcount_[src]++;
+        }
+    }
+    *child_out = child;
     return ST_OK;
 }
 
@@ -140,7 +180,7 @@ int PageManager::evict_cold(int seq, int stable_len, std::vector<Eviction>* move
         if (r[i] < 0) continue;
         const int32_t hot = r[i], cold = cold_stack_.back();
         cold_stack_.pop_back();
-        free_stack_.push_back(hot);
+        release_page(hot);
         set_entry(seq, i, -2 - cold);
         if (cold + 1 > cold_high_water_) cold_high_water_ = cold + 1;
         if (moved) moved->push_back({hot, cold});

@@ -62,6 +62,12 @@ public:
     int  reserve(int seq, int n_tokens);           // status
     int  truncate(int seq, int new_len);           // status
     int  adopt(int seq, const int32_t* pages, int n_pages, int seq_len);  // status
+    // Prefix sharing: a new sequence (lowest free slot) holding the same tokens as `parent`.  Full
+    // pages are shared and reference-counted; a partly filled last page gets a fresh page whose
+    // contents the caller must copy (*copy_src -> *copy_dst, -1 when there is none).  On
+    // ST_OUT_OF_SEQS / ST_OUT_OF_PAGES nothing changes.  Not available with a cold tier.
+    int  fork(int parent, int* child, int32_t* copy_src, int32_t* copy_dst);
+    int  refcount(int page) const { return page >= 0 && page < num_pages_ ? refcount_[page] : 0; }
     // Cold tier: a page is cold iff its last token index < seq_len - hot_window.  Cold pages
     // live in a host pool with its own LIFO id stack; the table holds -2 - cold_id for them.
     // The idiom is the reference's expert cache (evict, count, keep a host copy:
@@ -107,6 +113,8 @@ public:
 
 private:
     void set_entry(int seq, int idx, int32_t value);
+    void release_page(int32_t page);      // free stack once no sequence names it
+    std::vector<int32_t> refcount_;
     int num_pages_, max_seqs_, max_pages_per_seq_, page_size_;
     std::vector<int32_t> free_stack_;   // back() is the next page handed out
     std::vector<int32_t> table_;        // [max_seqs][max_pages_per_seq], -1 = unmapped

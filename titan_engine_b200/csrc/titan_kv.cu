@@ -505,6 +505,30 @@ int tk_kv_seq_adopt(tk_kv* h, int32_t seq, const int32_t* pages, int32_t n_pages
     int st = h->mgr->adopt(seq, pages, n_pages, seq_len);
     return st == TK_OK ? TK_OK : fail(h, st, "seq_adopt(%d): pages must be distinct, in range and free", seq);
 }
+int tk_kv_seq_fork(tk_kv* h, int32_t parent, int32_t* child_out, void* stream) {
+    if (!h || !child_out) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
+    int child = -1;
+    int32_t src = -1, dst = -1;
+    const int st = h->mgr->fork(parent, &child, &src, &dst);
+    if (st != TK_OK) return fail(h, st, "seq_fork(%d): %s", parent, tk_status_str(st));
+    *child_out = child;
+    if (h->host_only || dst < 0) return TK_OK;
+    // the partly filled last page is private: copy it for every layer (FP8: it is the open page)
+    cudaError_t e;
+    if (h->cfg.dtype == TK_FP8_E4M3) {
+        const size_t open_tile = h->page_bytes * 2;       // 16-bit rows
+        e = tk::launch_copy_layers(h->arena + h->lay.open_off + (size_t)parent * open_tile, h->lay.open_layer,
+                                   h->arena + h->lay.open_off + (size_t)child * open_tile, h->lay.open_layer, open_tile,
+                                   h->cfg.num_layers, (cudaStream_t)stream);
+    } else {
+        e = tk::launch_copy_layers(h->arena + h->lay.pool_off + (size_t)src * h->page_bytes, h->lay.pool_layer,
+                                   h->arena + h->lay.pool_off + (size_t)dst * h->page_bytes, h->lay.pool_layer,
+                                   h->page_bytes, h->cfg.num_layers, (cudaStream_t)stream);
+    }
+    h->launches++;
+    return e == cudaSuccess ? TK_OK : fail(h, TK_CUDA_ERROR, "seq_fork copy: %s", cudaGetErrorString(e));
+}
 int tk_kv_seq_set_tail(tk_kv* h, int32_t seq, int32_t tail_tokens) {
     if (!h) return TK_INVALID_ARG;
     std::lock_guard<std::mutex> lock(h->mgr_mu);

@@ -75,6 +75,11 @@ cudaError_t launch_rope_table(const Geometry& g, const StepDev& st, float2* tab,
 cudaError_t launch_rope16(const Geometry& g, const StepDev& st, const void* q, const void* k, void* q_out,
                           void* k_out, float theta, float scaling, cudaStream_t s);
 
+// Copies `bytes` (multiple of 16) from src + l*src_stride to dst + l*dst_stride for l in [0, n_layers):
+// one page (or open page) of every layer after a fork.
+cudaError_t launch_copy_layers(const void* src, size_t src_stride, void* dst, size_t dst_stride, size_t bytes,
+                               int n_layers, cudaStream_t s);
+
 cudaError_t launch_apply_delta(int32_t* table, const int2* delta, int n, cudaStream_t s);
 
 cudaError_t launch_append(const Geometry& g, const LayerPtrs& lp, const StepDev& st,

@@ -122,6 +122,13 @@ class PagedKVCache:
         p = _i32(pages)
         self._check(self._lib.tk_kv_seq_adopt(self._h, seq, _ptr(p), len(p), seq_len))
 
+    def fork(self, parent: int) -> int:
+        """New sequence sharing `parent`'s full pages; its partly filled last page is copied."""
+        child = C.c_int32(-1)
+        stream = None if self.host_only else self._stream()
+        self._check(self._lib.tk_kv_seq_fork(self._h, parent, C.byref(child), stream))
+        return child.value
+
     def set_tail(self, seq: int, tail_tokens: int) -> None:
         """Tokens of this logical sequence held by later ranks (moves the hot window)."""
         self._check(self._lib.tk_kv_seq_set_tail(self._h, seq, tail_tokens))
