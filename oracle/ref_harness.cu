@@ -73,6 +73,27 @@ int tkref_attention_decode(const float* q, const float* k, const float* v, float
     return 0;
 }
 
+// cuda::attention_decode_mla on contiguous host arrays k: [seq_len][Hkv][Dk], v: [seq_len][Hkv][Dv].
+int tkref_attention_decode_mla(const float* q, const float* k, const float* v, float* out,
+                               int H, int Hkv, int Dk, int Dv, int seq_len) {
+    size_t k_bytes = (size_t)seq_len * Hkv * Dk * sizeof(float), v_bytes = (size_t)seq_len * Hkv * Dv * sizeof(float);
+    size_t q_bytes = (size_t)H * Dk * sizeof(float), o_bytes = (size_t)H * Dv * sizeof(float);
+    float *dk = nullptr, *dv = nullptr, *dq = nullptr, *dout = nullptr;
+    TKREF_CHECK(cudaMalloc(&dk, k_bytes));
+    TKREF_CHECK(cudaMalloc(&dv, v_bytes));
+    TKREF_CHECK(cudaMalloc(&dq, q_bytes));
+    TKREF_CHECK(cudaMalloc(&dout, o_bytes));
+    TKREF_CHECK(cudaMemcpy(dk, k, k_bytes, cudaMemcpyHostToDevice));
+    TKREF_CHECK(cudaMemcpy(dv, v, v_bytes, cudaMemcpyHostToDevice));
+    TKREF_CHECK(cudaMemcpy(dq, q, q_bytes, cudaMemcpyHostToDevice));
+    titan::cuda::attention_decode_mla(dq, dk, dv, dout, H, Hkv, Dk, Dv, seq_len, nullptr);
+    TKREF_CHECK(cudaGetLastError());
+    TKREF_CHECK(cudaDeviceSynchronize());
+    TKREF_CHECK(cudaMemcpy(out, dout, o_bytes, cudaMemcpyDeviceToHost));
+    cudaFree(dk); cudaFree(dv); cudaFree(dq); cudaFree(dout);
+    return 0;
+}
+
 // cuda::apply_rope in place on host arrays q: [H][D], k: [Hkv][D].
 int tkref_apply_rope(float* q, float* k, int H, int Hkv, int D, int position,
                      float theta, float scaling) {

@@ -106,13 +106,15 @@ int tko_kv_update_f32(float* k_data, float* v_data, int num_layers, int max_seq_
  *   score = dot * scale (:85-92), max from -1e30f (:97), expf (:122),
  *   inv = 1/(sum + 1e-8f) (:142), out = sum_p w[p]*V[p] in position order (:149-156).
  * `scores` is scratch of seq_len floats. */
-static void attn_head_f32(const float* qh, const float* k_rows, const float* v_rows,
-                          size_t row_stride, int head_dim, int seq_len, float scale,
-                          float* scores, float* out) {
+static void attn_head_kv(const float* qh, const float* k_rows, const float* v_rows,
+                         size_t k_stride, size_t v_stride, int k_dim, int v_dim, int seq_len, float scale,
+                         float* scores, float* out) {
+    const int head_dim = v_dim;
+    const size_t row_stride = v_stride;
     for (int p = 0; p < seq_len; p++) {
-        const float* kh = k_rows + (size_t)p * row_stride;
+        const float* kh = k_rows + (size_t)p * k_stride;
         float dot = 0.0f;
-        for (int d = 0; d < head_dim; d++) dot += qh[d] * kh[d];
+        for (int d = 0; d < k_dim; d++) dot += qh[d] * kh[d];
         scores[p] = dot * scale;
     }
     float max_val = -1e30f;
@@ -127,6 +129,28 @@ static void attn_head_f32(const float* qh, const float* k_rows, const float* v_r
         float w = scores[p];
         for (int d = 0; d < head_dim; d++) out[d] += w * vh[d];
     }
+}
+
+static void attn_head_f32(const float* qh, const float* k_rows, const float* v_rows,
+                          size_t row_stride, int head_dim, int seq_len, float scale,
+                          float* scores, float* out) {
+    attn_head_kv(qh, k_rows, v_rows, row_stride, row_stride, head_dim, head_dim, seq_len, scale, scores, out);
+}
+
+/* cuda::attention_decode_mla, src/compute/cuda/attention.cu:168-253,332-349: K rows of k_head_dim
+ * (scores, scale = 1/sqrtf(k_head_dim)), V rows and output of v_head_dim; otherwise the same
+ * three-pass softmax as attention_decode. */
+void tko_attention_decode_mla_f32(const float* q, const float* k_cache, const float* v_cache, float* out,
+                                  int num_heads, int num_kv_heads, int k_head_dim, int v_head_dim, int seq_len) {
+    float scale = 1.0f / sqrtf((float)k_head_dim);
+    float* scores = (float*)malloc(sizeof(float) * (size_t)(seq_len > 0 ? seq_len : 1));
+    for (int h = 0; h < num_heads; h++) {
+        int kvh = h / (num_heads / num_kv_heads);
+        attn_head_kv(q + (size_t)h * k_head_dim, k_cache + (size_t)kvh * k_head_dim, v_cache + (size_t)kvh * v_head_dim,
+                     (size_t)num_kv_heads * k_head_dim, (size_t)num_kv_heads * v_head_dim, k_head_dim, v_head_dim,
+                     seq_len, scale, scores, out + (size_t)h * v_head_dim);
+    }
+    free(scores);
 }
 
 /* cuda::attention_decode, src/compute/cuda/attention.cu:315-330 (scale = 1/sqrtf(D));
@@ -382,8 +406,12 @@ uint64_t tko_state_digest(const tko_mgr* m) {
 /* ======================================================================== */
 /* tier (2): append                                                          */
 /* ======================================================================== */
+/* tile of (page, kv head): page_size rows of K (D elements) then page_size rows of V (Dv elements) */
+static inline size_t tile_off2(int page, int kvh, int kv, int Hkv, int page_size, int D, int Dv) {
+    return ((size_t)page * Hkv + kvh) * (size_t)page_size * (D + Dv) + (kv ? (size_t)page_size * D : 0);
+}
 static inline size_t tile_off(int page, int kvh, int kv, int Hkv, int page_size, int D) {
-    return (((size_t)page * Hkv + kvh) * 2 + kv) * (size_t)page_size * D;
+    return tile_off2(page, kvh, kv, Hkv, page_size, D, D);
 }
 
 /* Page-table scatter of 16-bit rows: an exact copy, like the reference's
@@ -392,16 +420,24 @@ void tko_append_16(uint16_t* pool, int Hkv, int D, int page_size,
                    const int32_t* page_table, int max_pages_per_seq,
                    int n_tokens, const int32_t* tok_seq, const int32_t* tok_pos,
                    const uint16_t* k, const uint16_t* v, int64_t* slots_out) {
+    tko_append_16_kv(pool, Hkv, D, D, page_size, page_table, max_pages_per_seq, n_tokens, tok_seq, tok_pos, k, v, slots_out);
+}
+
+/* Same with K rows of D and V rows of Dv elements (the MLA cache: src/inference/kv_cache.cpp:83-108). */
+void tko_append_16_kv(uint16_t* pool, int Hkv, int D, int Dv, int page_size,
+                      const int32_t* page_table, int max_pages_per_seq,
+                      int n_tokens, const int32_t* tok_seq, const int32_t* tok_pos,
+                      const uint16_t* k, const uint16_t* v, int64_t* slots_out) {
     for (int t = 0; t < n_tokens; t++) {
         int pos = tok_pos[t];
         int page = page_table[(size_t)tok_seq[t] * max_pages_per_seq + pos / page_size];
         int r = pos % page_size;
         if (slots_out) slots_out[t] = (int64_t)page * page_size + r;
         for (int h = 0; h < Hkv; h++) {
-            memcpy(pool + tile_off(page, h, 0, Hkv, page_size, D) + (size_t)r * D,
+            memcpy(pool + tile_off2(page, h, 0, Hkv, page_size, D, Dv) + (size_t)r * D,
                    k + ((size_t)t * Hkv + h) * D, sizeof(uint16_t) * (size_t)D);
-            memcpy(pool + tile_off(page, h, 1, Hkv, page_size, D) + (size_t)r * D,
-                   v + ((size_t)t * Hkv + h) * D, sizeof(uint16_t) * (size_t)D);
+            memcpy(pool + tile_off2(page, h, 1, Hkv, page_size, D, Dv) + (size_t)r * Dv,
+                   v + ((size_t)t * Hkv + h) * Dv, sizeof(uint16_t) * (size_t)Dv);
         }
     }
 }
@@ -449,12 +485,14 @@ void tko_append_fp8(uint8_t* codes, float* scales, uint16_t* open_pages, int car
 void tko_gather_f32(const tko_view* vw, int seq, int seq_len, int kvh, int t0, int t1,
                     float* k_rows, float* v_rows) {
     int D = vw->head_dim, ps = vw->page_size, Hkv = vw->num_kv_heads;
+    int Dv = vw->v_head_dim > 0 ? vw->v_head_dim : D;
     const int32_t* row = vw->page_table + (size_t)seq * vw->max_pages_per_seq;
     int sealed_end = (seq_len / ps) * ps;      /* FP8: tokens >= sealed_end sit in the open page */
     for (int t = t0; t < t1; t++) {
         int page = row[t / ps], r = t % ps;
         for (int kv = 0; kv < 2; kv++) {
-            float* dst = (kv ? v_rows : k_rows) + (size_t)(t - t0) * D;
+            int Dx = kv ? Dv : D;
+            float* dst = (kv ? v_rows : k_rows) + (size_t)(t - t0) * Dx;
             if (vw->dtype == TKO_FP8_E4M3) {
                 if (t < sealed_end) {
                     const uint8_t* c = (const uint8_t*)vw->pool + tile_off(page, kvh, kv, Hkv, ps, D) + (size_t)r * D;
@@ -465,8 +503,8 @@ void tko_gather_f32(const tko_view* vw, int seq, int seq_len, int kvh, int t0, i
                     for (int d = 0; d < D; d++) dst[d] = to_f32(o[d], vw->carrier_dtype);
                 }
             } else {
-                const uint16_t* p = (const uint16_t*)vw->pool + tile_off(page, kvh, kv, Hkv, ps, D) + (size_t)r * D;
-                for (int d = 0; d < D; d++) dst[d] = to_f32(p[d], vw->dtype);
+                const uint16_t* p = (const uint16_t*)vw->pool + tile_off2(page, kvh, kv, Hkv, ps, D, Dv) + (size_t)r * Dx;
+                for (int d = 0; d < Dx; d++) dst[d] = to_f32(p[d], vw->dtype);
             }
         }
     }
@@ -475,6 +513,7 @@ void tko_gather_f32(const tko_view* vw, int seq, int seq_len, int kvh, int t0, i
 void tko_decode_paged(const tko_view* vw, int n_seqs, const int32_t* seq_ids,
                       const int32_t* seq_lens, const uint16_t* q, float* out) {
     int H = vw->num_heads, Hkv = vw->num_kv_heads, D = vw->head_dim, G = H / Hkv;
+    int Dv = vw->v_head_dim > 0 ? vw->v_head_dim : D;
     float scale = 1.0f / sqrtf((float)D);
     int n_units = n_seqs * Hkv;
 #ifdef _OPENMP
@@ -485,14 +524,14 @@ void tko_decode_paged(const tko_view* vw, int n_seqs, const int32_t* seq_ids,
         int len = seq_lens[b];
         size_t n = (size_t)(len > 0 ? len : 1);
         float* kr = (float*)malloc(sizeof(float) * n * D);
-        float* vr = (float*)malloc(sizeof(float) * n * D);
+        float* vr = (float*)malloc(sizeof(float) * n * Dv);
         float* sc = (float*)malloc(sizeof(float) * n);
         float* qf = (float*)malloc(sizeof(float) * (size_t)D);
         tko_gather_f32(vw, seq_ids[b], len, kvh, 0, len, kr, vr);
         for (int g = 0; g < G; g++) {
             int h = kvh * G + g;           /* inverse of kv_head = h / (H/Hkv) */
             tko_16_to_f32(q + ((size_t)b * H + h) * D, qf, (size_t)D, vw->carrier_dtype);
-            attn_head_f32(qf, kr, vr, (size_t)D, D, len, scale, sc, out + ((size_t)b * H + h) * D);
+            attn_head_kv(qf, kr, vr, (size_t)D, (size_t)Dv, D, Dv, len, scale, sc, out + ((size_t)b * H + h) * Dv);
         }
         free(kr); free(vr); free(sc); free(qf);
     }
@@ -501,10 +540,11 @@ void tko_decode_paged(const tko_view* vw, int n_seqs, const int32_t* seq_ids,
 void tko_decode_partial(const tko_view* vw, int seq, int seq_len, int t0, int t1,
                         const uint16_t* q, float* m, float* l, float* o) {
     int H = vw->num_heads, Hkv = vw->num_kv_heads, D = vw->head_dim, G = H / Hkv;
+    int Dv = vw->v_head_dim > 0 ? vw->v_head_dim : D;
     float scale = 1.0f / sqrtf((float)D);
     int n = t1 - t0;
     float* kr = (float*)malloc(sizeof(float) * (size_t)(n > 0 ? n : 1) * D);
-    float* vr = (float*)malloc(sizeof(float) * (size_t)(n > 0 ? n : 1) * D);
+    float* vr = (float*)malloc(sizeof(float) * (size_t)(n > 0 ? n : 1) * Dv);
     float* sc = (float*)malloc(sizeof(float) * (size_t)(n > 0 ? n : 1));
     float* qf = (float*)malloc(sizeof(float) * (size_t)D);
     for (int kvh = 0; kvh < Hkv; kvh++) {
@@ -519,11 +559,11 @@ void tko_decode_partial(const tko_view* vw, int seq, int seq_len, int t0, int t1
                 sc[p] = dot * scale; mx = fmaxf(mx, sc[p]);
             }
             float sum = 0.0f;
-            float* oh = o + (size_t)h * D;
-            for (int d = 0; d < D; d++) oh[d] = 0.0f;
+            float* oh = o + (size_t)h * Dv;
+            for (int d = 0; d < Dv; d++) oh[d] = 0.0f;
             for (int p = 0; p < n; p++) {
                 float e = expf(sc[p] - mx); sum += e;
-                for (int d = 0; d < D; d++) oh[d] += e * vr[(size_t)p * D + d];
+                for (int d = 0; d < Dv; d++) oh[d] += e * vr[(size_t)p * Dv + d];
             }
             m[h] = mx; l[h] = sum;
         }

@@ -51,6 +51,10 @@ void tko_attention_decode_f32(const float* q, const float* k_cache, const float*
                               float* out, int num_heads, int num_kv_heads, int head_dim,
                               int seq_len);
 
+/* cuda::attention_decode_mla, src/compute/cuda/attention.cu:168-253,332-349 */
+void tko_attention_decode_mla_f32(const float* q, const float* k_cache, const float* v_cache, float* out,
+                                  int num_heads, int num_kv_heads, int k_head_dim, int v_head_dim, int seq_len);
+
 /* ---- tier (2): page manager (semantics defined here) ------------------- */
 typedef struct tko_mgr tko_mgr;
 tko_mgr* tko_mgr_create(int num_pages, int max_seqs, int max_pages_per_seq, int page_size);
@@ -81,6 +85,10 @@ void tko_append_16(uint16_t* pool, int num_kv_heads, int head_dim, int page_size
                    const int32_t* page_table, int max_pages_per_seq,
                    int n_tokens, const int32_t* tok_seq, const int32_t* tok_pos,
                    const uint16_t* k, const uint16_t* v, int64_t* slots_out);
+void tko_append_16_kv(uint16_t* pool, int num_kv_heads, int head_dim, int v_head_dim, int page_size,
+                      const int32_t* page_table, int max_pages_per_seq,
+                      int n_tokens, const int32_t* tok_seq, const int32_t* tok_pos,
+                      const uint16_t* k, const uint16_t* v, int64_t* slots_out);
 /* FP8 pool: codes [num_pages][Hkv][2][page_size][D] bytes, scales [num_pages][Hkv][2] f32,
  * open pages [max_seqs][Hkv][2][page_size][D] in the 16-bit carrier type.  Tokens are
  * processed in order; a token landing on the last row of a page seals that page:
@@ -101,6 +109,7 @@ typedef struct {
     const float*    scales;    /* FP8 only */
     const uint16_t* open_pages;/* FP8 only */
     const int32_t*  page_table; int max_pages_per_seq;
+    int v_head_dim;            /* V rows / output width when it differs from head_dim (MLA); 0 = head_dim */
 } tko_view;
 /* Gather kv head `kvh` of tokens [t0,t1) of sequence `seq` (length seq_len) to FP32 rows. */
 void tko_gather_f32(const tko_view* v, int seq, int seq_len, int kvh, int t0, int t1,

@@ -30,7 +30,7 @@ class View(C.Structure):
     _fields_ = [("dtype", C.c_int), ("carrier_dtype", C.c_int), ("num_heads", C.c_int),
                 ("num_kv_heads", C.c_int), ("head_dim", C.c_int), ("page_size", C.c_int),
                 ("pool", C.c_void_p), ("scales", C.c_void_p), ("open_pages", C.c_void_p),
-                ("page_table", C.c_void_p), ("max_pages_per_seq", C.c_int)]
+                ("page_table", C.c_void_p), ("max_pages_per_seq", C.c_int), ("v_head_dim", C.c_int)]
 
 
 _lib = None
@@ -50,6 +50,8 @@ def lib() -> C.CDLL:
             "tko_16_to_f32": (None, [vp, vp, C.c_size_t, i]),
             "tko_kv_update_f32": (i, [vp, vp, i, i, i, i, i, i, vp, vp, i]),
             "tko_attention_decode_f32": (None, [vp, vp, vp, vp, i, i, i, i]),
+            "tko_attention_decode_mla_f32": (None, [vp, vp, vp, vp, i, i, i, i, i]),
+            "tko_append_16_kv": (None, [vp, i, i, i, i, vp, i, i, vp, vp, vp, vp, vp]),
             "tko_mgr_create": (vp, [i, i, i, i]),
             "tko_mgr_destroy": (None, [vp]),
             "tko_seq_alloc": (i, [vp]),
@@ -126,6 +128,13 @@ def attention_decode_f32(q, k_cache, v_cache, H, Hkv, D, seq_len) -> np.ndarray:
     return out
 
 
+def attention_decode_mla_f32(q, k_cache, v_cache, H, Hkv, Dk, Dv, seq_len) -> np.ndarray:
+    q, k_cache, v_cache = _c(q, np.float32), _c(k_cache, np.float32), _c(v_cache, np.float32)
+    out = np.empty((H, Dv), dtype=np.float32)
+    lib().tko_attention_decode_mla_f32(_p(q), _p(k_cache), _p(v_cache), _p(out), H, Hkv, Dk, Dv, seq_len)
+    return out
+
+
 def kv_update_f32(k_data, v_data, L, max_seq, Hkv, D, layer, pos, key, value, seq_len) -> int:
     key, value = _c(key, np.float32), _c(value, np.float32)
     assert k_data.dtype == np.float32 and k_data.flags.c_contiguous
@@ -188,11 +197,13 @@ class Manager:
 class Pool:
     """One layer of a paged pool in host memory, with the oracle's append and decode."""
 
-    def __init__(self, dtype, num_pages, H, Hkv, D, max_seqs, max_pages_per_seq, page_size=16, carrier=None):
+    def __init__(self, dtype, num_pages, H, Hkv, D, max_seqs, max_pages_per_seq, page_size=16, carrier=None, Dv=None):
         self.dtype, self.carrier = dtype, (carrier or (BF16 if dtype == FP8 else dtype))
         self.num_pages, self.H, self.Hkv, self.D = num_pages, H, Hkv, D
+        self.Dv = Dv or D                      # V rows / output width (differs from D for the MLA cache)
         self.max_seqs, self.mpps, self.ps = max_seqs, max_pages_per_seq, page_size
-        shape = (num_pages, Hkv, 2, page_size, D)
+        # tile of (page, kv head): page_size K rows of D, then page_size V rows of Dv
+        shape = (num_pages, Hkv, 2, page_size, D) if self.Dv == D else (num_pages, Hkv, page_size * (D + self.Dv))
         if dtype == FP8:
             self.pool = np.zeros(shape, dtype=np.uint8)
             self.scales = np.zeros((num_pages, Hkv, 2), dtype=np.float32)
@@ -212,18 +223,18 @@ class Pool:
                                  self.Hkv, self.D, self.ps, _p(table), self.mpps, n, _p(tok_seq),
                                  _p(tok_pos), _p(k16), _p(v16), _p(slots))
         else:
-            lib().tko_append_16(_p(self.pool), self.Hkv, self.D, self.ps, _p(table), self.mpps, n,
-                                _p(tok_seq), _p(tok_pos), _p(k16), _p(v16), _p(slots))
+            lib().tko_append_16_kv(_p(self.pool), self.Hkv, self.D, self.Dv, self.ps, _p(table), self.mpps, n,
+                                   _p(tok_seq), _p(tok_pos), _p(k16), _p(v16), _p(slots))
         return slots
 
     def view(self, table: np.ndarray) -> View:
         self._table = _c(table, np.int32)
         return View(self.dtype, self.carrier, self.H, self.Hkv, self.D, self.ps, _p(self.pool),
-                    _p(self.scales), _p(self.open_pages), _p(self._table), self.mpps)
+                    _p(self.scales), _p(self.open_pages), _p(self._table), self.mpps, self.Dv)
 
     def decode(self, table, seq_ids, seq_lens, q16) -> np.ndarray:
         seq_ids, seq_lens, q16 = _c(seq_ids, np.int32), _c(seq_lens, np.int32), _c(q16, np.uint16)
-        out = np.empty((len(seq_ids), self.H, self.D), dtype=np.float32)
+        out = np.empty((len(seq_ids), self.H, self.Dv), dtype=np.float32)
         v = self.view(table)
         lib().tko_decode_paged(C.byref(v), len(seq_ids), _p(seq_ids), _p(seq_lens), _p(q16), _p(out))
         return out
@@ -232,14 +243,14 @@ class Pool:
         q16 = _c(q16, np.uint16)
         m = np.empty(self.H, dtype=np.float32)
         l = np.empty(self.H, dtype=np.float32)
-        o = np.empty((self.H, self.D), dtype=np.float32)
+        o = np.empty((self.H, self.Dv), dtype=np.float32)
         v = self.view(table)
         lib().tko_decode_partial(C.byref(v), seq, seq_len, t0, t1, _p(q16), _p(m), _p(l), _p(o))
         return m, l, o
 
     def gather(self, table, seq, seq_len, kvh, t0, t1):
         k = np.empty((t1 - t0, self.D), dtype=np.float32)
-        vv = np.empty((t1 - t0, self.D), dtype=np.float32)
+        vv = np.empty((t1 - t0, self.Dv), dtype=np.float32)
         v = self.view(table)
         lib().tko_gather_f32(C.byref(v), seq, seq_len, kvh, t0, t1, _p(k), _p(vv))
         return k, vv
@@ -270,6 +281,8 @@ def ref_lib() -> Optional[C.CDLL]:
         r.tkref_update_and_decode.argtypes = [vp, vp, vp, vp, i, i, i, i, i, i, i, C.POINTER(C.c_int)]
         r.tkref_attention_decode.restype = i
         r.tkref_attention_decode.argtypes = [vp, vp, vp, vp, i, i, i, i]
+        r.tkref_attention_decode_mla.restype = i
+        r.tkref_attention_decode_mla.argtypes = [vp, vp, vp, vp, i, i, i, i, i]
         r.tkref_apply_rope.restype = i
         r.tkref_apply_rope.argtypes = [vp, vp, i, i, i, i, f, f]
         _ref = r
@@ -282,6 +295,15 @@ def ref_attention_decode(q, k, v, H, Hkv, D, seq_len) -> np.ndarray:
     st = ref_lib().tkref_attention_decode(_p(q), _p(k), _p(v), _p(out), H, Hkv, D, seq_len)
     if st != 0:
         raise RuntimeError(f"reference attention_decode failed: cudaError {st}")
+    return out
+
+
+def ref_attention_decode_mla(q, k, v, H, Hkv, Dk, Dv, seq_len) -> np.ndarray:
+    q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+    out = np.empty((H, Dv), dtype=np.float32)
+    st = ref_lib().tkref_attention_decode_mla(_p(q), _p(k), _p(v), _p(out), H, Hkv, Dk, Dv, seq_len)
+    if st != 0:
+        raise RuntimeError(f"reference attention_decode_mla failed: cudaError {st}")
     return out
 
 
