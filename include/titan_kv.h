@@ -53,7 +53,7 @@ typedef struct tk_kv_config {
     int32_t num_layers;
     int32_t num_heads;          /* query heads */
     int32_t num_kv_heads;
-    int32_t head_dim;           /* 64 or 128 */
+    int32_t head_dim;           /* 64 or 128; 192 with v_head_dim 128 for the MLA cache */
     int32_t page_size;          /* tokens per page: 16 */
     int32_t dtype;              /* storage: TK_FP16 / TK_BF16 / TK_FP8_E4M3 */
     int32_t io_dtype;           /* type of q, k, v, out and of FP8 open pages: TK_FP16 / TK_BF16; 0 = dtype */
@@ -69,7 +69,11 @@ typedef struct tk_kv_config {
                                    tier).  A page whose last token index < seq_len - hot_window is moved
                                    to pinned host memory and staged back one layer ahead of its use. */
     int32_t cold_pages;         /* capacity of the host pool, pages per layer (needed when hot_window > 0) */
-    int32_t reserved[4];
+    int32_t v_head_dim;         /* width of V rows and of the output; 0 = head_dim.  192/128 is the MLA cache
+                                   (KVCache::initialize_external_mla, src/inference/kv_cache.cpp:83-108;
+                                   attention_decode_mla, src/compute/cuda/attention.cu:168-253): K rows and q
+                                   have head_dim, scale = 1/sqrtf(head_dim); 16-bit storage, generic kernel */
+    int32_t reserved[3];
 } tk_kv_config;
 
 typedef struct tk_kv_stats {    /* in the style of CacheStats, src/memory/memory_manager.h:211-220 */

@@ -20,6 +20,9 @@ CASES = [  # seed, H, Hkv, D, seq_len
     (101, 8, 2, 64, 1), (102, 8, 2, 64, 17), (103, 8, 2, 64, 576),
     (104, 32, 8, 128, 300), (105, 32, 8, 128, 2049), (106, 64, 8, 128, 129),
 ]
+MLA_CASES = [  # seed, H, Hkv, k_head_dim, v_head_dim, seq_len
+    (301, 16, 16, 192, 128, 77), (302, 16, 4, 192, 128, 513),
+]
 ROPE_CASES = [(201, 32, 8, 128, 0, 500000.0), (202, 32, 8, 128, 1234, 500000.0), (203, 8, 2, 64, 77, 10000.0)]
 
 
@@ -27,6 +30,12 @@ def inputs(seed, H, Hkv, D, n):
     g = np.random.Generator(np.random.Philox(seed))
     return (g.standard_normal((H, D), dtype=np.float32), g.standard_normal((n, Hkv, D), dtype=np.float32),
             g.standard_normal((n, Hkv, D), dtype=np.float32))
+
+
+def mla_inputs(seed, H, Hkv, Dk, Dv, n):
+    g = np.random.Generator(np.random.Philox(seed))
+    return (g.standard_normal((H, Dk), dtype=np.float32), g.standard_normal((n, Hkv, Dk), dtype=np.float32),
+            g.standard_normal((n, Hkv, Dv), dtype=np.float32))
 
 
 def rope_inputs(seed, H, Hkv, D):
@@ -46,6 +55,10 @@ def main():
     kk = np.stack([k, v]); vv = np.stack([v, k])          # two layers with different content
     out, seq_len = O.ref_update_and_decode(kk, vv, q, 2, 1, 8, 2, 64, 40, 64)
     data["update_out"], data["update_seq_len"] = out, np.int64(seq_len)
+    data["mla_cases"] = np.array(MLA_CASES, dtype=np.int64)
+    for i, (seed, H, Hkv, Dk, Dv, n) in enumerate(MLA_CASES):
+        q, k, v = mla_inputs(seed, H, Hkv, Dk, Dv, n)
+        data[f"mla_out_{i}"] = O.ref_attention_decode_mla(q, k, v, H, Hkv, Dk, Dv, n)
     for i, (seed, H, Hkv, D, pos, theta) in enumerate(ROPE_CASES):
         q, k = rope_inputs(seed, H, Hkv, D)
         rq, rk = O.ref_apply_rope(q, k, H, Hkv, D, pos, theta, 1.0)

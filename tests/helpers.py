@@ -62,16 +62,17 @@ class Twin:
     """
 
     def __init__(self, L, H, Hkv, D, num_pages, max_seqs, mpps, dtype="bf16", impl="auto",
-                 chunk_tokens=0, max_step_tokens=4096, io=None, seed=0, hot_window=0, cold_pages=0):
+                 chunk_tokens=0, max_step_tokens=4096, io=None, seed=0, hot_window=0, cold_pages=0, Dv=None):
         import torch
         from titan_engine_b200 import PagedKVCache
         self.torch = torch
         self.L, self.H, self.Hkv, self.D, self.ps = L, H, Hkv, D, 16
+        self.Dv = Dv or D
         self.dt = DT[dtype]
         self.carrier = DT[io] if io else (O.BF16 if self.dt == O.FP8 else self.dt)
         self.gpu = PagedKVCache(L, H, Hkv, D, num_pages, max_seqs, mpps, dtype=dtype, io_dtype=io,
                                 decode_impl=impl, chunk_tokens=chunk_tokens, max_step_tokens=max_step_tokens,
-                                hot_window=hot_window, cold_pages=cold_pages)
+                                hot_window=hot_window, cold_pages=cold_pages, v_head_dim=self.Dv if self.Dv != D else 0)
         self.mgr = O.Manager(num_pages, max_seqs, mpps, 16)
         # With a cold tier the oracle keeps two managers: `mgr` follows the tiering rule (page/slot
         # state parity), `flat` holds the same logical data in one untiered pool (attention parity:
@@ -82,7 +83,7 @@ class Twin:
             assert self.mgr.enable_cold(hot_window, cold_pages) == O.OK
             self.flat = O.Manager(num_pages + cold_pages, max_seqs, mpps, 16)
         data_pages = num_pages + cold_pages
-        self.pools = [O.Pool(self.dt, data_pages, H, Hkv, D, max_seqs, mpps, 16, self.carrier) for _ in range(L)]
+        self.pools = [O.Pool(self.dt, data_pages, H, Hkv, D, max_seqs, mpps, 16, self.carrier, Dv=self.Dv) for _ in range(L)]
         self.g = rng(seed)
         self.dev = self.gpu.device
         self.max_err = 0.0
@@ -144,12 +145,12 @@ class Twin:
         outs = []
         for layer in range(self.L):
             k16 = normal16(self.g, (nt, self.Hkv, self.D), self.carrier, outlier_p)
-            v16 = normal16(self.g, (nt, self.Hkv, self.D), self.carrier, outlier_p)
+            v16 = normal16(self.g, (nt, self.Hkv, self.Dv), self.carrier, outlier_p)
             q16 = normal16(self.g, (len(seq_ids), self.H, self.D), self.carrier)
             want_slots = self.pools[layer].append(table, tok_seq, tok_pos, k16, v16)
             if host_api:
                 kt, vt, qt = (to_torch16(x, self.carrier).pin_memory() for x in (k16, v16, q16))
-                out_h = torch.empty_like(qt).pin_memory()
+                out_h = torch.empty(len(seq_ids), self.H, self.Dv, dtype=qt.dtype).pin_memory()
                 self.gpu.append_decode_host(layer, kt, vt, qt, out_h)
                 got = out_h.to(torch.float32).numpy()
             elif fused:

@@ -60,3 +60,13 @@ def test_oracle_rope_matches_reference_golden():
         atol = 2e-4 + 2e-6 * pos          # one ulp of freq is ~6e-8*pos radians of angle
         np.testing.assert_allclose(oq, d[f"rope_q_{i}"], rtol=1e-4, atol=atol)
         np.testing.assert_allclose(ok, d[f"rope_k_{i}"], rtol=1e-4, atol=atol)
+
+
+def test_oracle_mla_attention_matches_reference_golden():
+    """attention_decode_mla (K rows of 192, V rows of 128) of the reference, run on a B200."""
+    d = _load()
+    np.testing.assert_array_equal(d["mla_cases"], np.array(G.MLA_CASES, dtype=np.int64))
+    for i, (seed, H, Hkv, Dk, Dv, n) in enumerate(G.MLA_CASES):
+        q, k, v = G.mla_inputs(seed, H, Hkv, Dk, Dv, n)
+        got = O.attention_decode_mla_f32(q, k, v, H, Hkv, Dk, Dv, n)
+        np.testing.assert_allclose(got, d[f"mla_out_{i}"], rtol=2e-4, atol=2e-5, err_msg=f"MLA case {i}")

@@ -425,3 +425,19 @@ def test_fork_prefix_sharing(dtype):
     t.step([b, c], [1, 1], check_pool=True, fused=True)
     t.seq_free(b); t.seq_free(c)
     assert t.gpu.num_free_pages == 64
+
+
+@pytest.mark.parametrize("heads", [(16, 16), (32, 8)])
+def test_mla_cache_shape(heads):
+    """K rows of 192, V rows and outputs of 128 (the MLA cache): append, decode, churn, host entry
+    point; pool bytes bit-exact, attention within tolerance."""
+    H, Hkv = heads
+    t = Twin(2, H, Hkv, 192, 60, 3, 40, dtype="bf16", impl="auto", max_step_tokens=1024, seed=98, Dv=128)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a, b], [300, 17], check_pool=True)
+    for i in range(20):
+        t.step([a, b], [1, 1], check_pool=(i % 5 == 0), fused=(i % 2 == 0))
+    t.seq_free(a)
+    c = t.seq_alloc()
+    t.step([c, b], [33, 1], check_pool=True, host_api=True)
+    assert t.gpu.cfg.v_head_dim == 128

@@ -87,3 +87,23 @@ def test_rope_oracle_matches_reference_kernel(ref):
         atol = 2e-4 + 2e-6 * pos
         np.testing.assert_allclose(oq, rq, rtol=1e-4, atol=atol)
         np.testing.assert_allclose(ok, rk, rtol=1e-4, atol=atol)
+
+
+@pytest.mark.parametrize("case", [(16, 16, 192, 128, 77), (16, 4, 192, 128, 1000)])
+def test_mla_oracle_and_library_match_reference_kernel(ref, case):
+    """attention_decode_mla of the reference vs the oracle (FP32) and vs the paged library (bf16)."""
+    from titan_engine_b200 import PagedKVCache
+    H, Hkv, Dk, Dv, n = case
+    g = rng(3000 + n)
+    k16 = normal16(g, (n, Hkv, Dk), O.BF16); v16 = normal16(g, (n, Hkv, Dv), O.BF16); q16 = normal16(g, (1, H, Dk), O.BF16)
+    qf, kf, vf = O.to_f32(q16[0], O.BF16), O.to_f32(k16, O.BF16), O.to_f32(v16, O.BF16)
+    want = O.ref_attention_decode_mla(qf, kf, vf, H, Hkv, Dk, Dv, n)
+    np.testing.assert_allclose(O.attention_decode_mla_f32(qf, kf, vf, H, Hkv, Dk, Dv, n), want, rtol=2e-4, atol=2e-5)
+    n_pages = (n + 15) // 16
+    c = PagedKVCache(1, H, Hkv, Dk, n_pages, 1, n_pages, dtype="bf16", v_head_dim=Dv, max_step_tokens=n)
+    s = c.seq_alloc()
+    c.step_begin([s], [n])
+    c.append(0, to_torch16(k16, O.BF16, c.device), to_torch16(v16, O.BF16, c.device))
+    got = c.decode(0, to_torch16(q16, O.BF16, c.device)).float().cpu().numpy()[0]
+    assert got.shape == (H, Dv)
+    assert_close(got, want, f"MLA {case} vs reference kernel", out_mantissa_bits=7)

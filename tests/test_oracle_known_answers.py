@@ -204,3 +204,21 @@ def test_rope_pairs_rotate():
     np.testing.assert_allclose(np.hypot(q3[:, 0::2], q3[:, 1::2]), np.hypot(q[:, 0::2], q[:, 1::2]), rtol=1e-5)
     ang = 5.0 * 1.0                                                             # d=0: freq 1
     np.testing.assert_allclose(k3[0, 0], k[0, 0] * np.cos(ang) - k[0, 1] * np.sin(ang), rtol=1e-5)
+
+
+def test_mla_shape_paged_equals_contiguous_and_float64():
+    """K rows of 192 (scores, scale 1/sqrt(192)), V rows and output of 128."""
+    H, Hkv, Dk, Dv, n, ps = 8, 2, 192, 128, 131, 16
+    g = rng(13)
+    k16 = normal16(g, (n, Hkv, Dk), O.BF16); v16 = normal16(g, (n, Hkv, Dv), O.BF16); q16 = normal16(g, (1, H, Dk), O.BF16)
+    n_pages = (n + ps - 1) // ps
+    table = g.permutation(n_pages).astype(np.int32)[None].copy()
+    pool = O.Pool(O.BF16, n_pages, H, Hkv, Dk, 1, n_pages, ps, Dv=Dv)
+    pool.append(table, np.zeros(n, np.int32), np.arange(n, dtype=np.int32), k16, v16)
+    out = pool.decode(table, [0], [n], q16)[0]
+    qf, kf, vf = O.to_f32(q16[0], O.BF16), O.to_f32(k16, O.BF16), O.to_f32(v16, O.BF16)
+    np.testing.assert_array_equal(out, O.attention_decode_mla_f32(qf, kf, vf, H, Hkv, Dk, Dv, n))
+    for h in range(H):
+        s = (kf[:, h // 4].astype(np.float64) @ qf[h].astype(np.float64)) / np.sqrt(Dk)
+        w = np.exp(s - s.max()); w /= w.sum()
+        np.testing.assert_allclose(out[h], w @ vf[:, h // 4].astype(np.float64), rtol=2e-5, atol=2e-6)

@@ -20,7 +20,7 @@ class KvConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "num_layers", "num_heads", "num_kv_heads", "head_dim", "page_size", "dtype", "io_dtype",
         "num_pages", "max_seqs", "max_pages_per_seq", "max_step_tokens", "chunk_tokens",
-        "decode_impl", "device", "hot_window", "cold_pages")] + [("reserved", C.c_int32 * 4)]
+        "decode_impl", "device", "hot_window", "cold_pages", "v_head_dim")] + [("reserved", C.c_int32 * 3)]
 
 
 class KvStats(C.Structure):

@@ -70,14 +70,15 @@ append_rows_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restri
         base = (uint16_t*)lp.pool;
         tile_page = page;
     }
-    const int vec_per_row = g.D / 8;           // 16-byte vectors per head row
-    const int n_vec = g.Hkv * 2 * vec_per_row;
+    const int vk = g.D / 8, vv = g.Dv / 8;     // 16-byte vectors per K row / per V row
+    const int n_k = g.Hkv * vk, n_vec = n_k + g.Hkv * vv;
     for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
-        const int c = i % vec_per_row;
-        const int kv = (i / vec_per_row) % 2;
-        const int h = i / (2 * vec_per_row);
-        const uint16_t* src = (kv ? v : k) + ((size_t)t * g.Hkv + h) * g.D + c * 8;
-        uint16_t* dst = base + tile_off(tile_page, h, kv, g.Hkv, g.ps, g.D) + (size_t)r * g.D + c * 8;
+        const int kv = i >= n_k;
+        const int per = kv ? vv : vk, dim = kv ? g.Dv : g.D;
+        const int ii = kv ? i - n_k : i;
+        const int h = ii / per, c = ii % per;
+        const uint16_t* src = (kv ? v : k) + ((size_t)t * g.Hkv + h) * dim + c * 8;
+        uint16_t* dst = base + tile_offset(g, tile_page, h, kv) + (size_t)r * dim + c * 8;
         *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
     }
 }

@@ -647,7 +647,7 @@ cudaError_t launch_bounded_wait_selftest(int* status, unsigned long long limit_n
 }
 
 bool decode_mma_supported(const Geometry& g) {
-    if (g.ps != kPage || g.Hkv <= 0 || g.H % g.Hkv != 0 || g.H / g.Hkv > 16) return false;
+    if (g.ps != kPage || g.Hkv <= 0 || g.H % g.Hkv != 0 || g.H / g.Hkv > 16 || g.Dv != g.D) return false;
     if (g.dtype == DT_FP8) return g.D == 128;
     if (g.dtype == DT_FP16 || g.dtype == DT_BF16) return (g.D == 64 || g.D == 128) && g.io_dtype == g.dtype;
     return false;

@@ -42,6 +42,13 @@ __device__ __forceinline__ void load16(const uint16_t* row, int lane, float (&ou
     if constexpr (EPL == 2) {
         uint32_t w = *reinterpret_cast<const uint32_t*>(p);
         out[0] = cvt16<BF16>((uint16_t)(w & 0xFFFF)); out[1] = cvt16<BF16>((uint16_t)(w >> 16));
+    } else if constexpr (EPL == 6) {
+        const uint32_t* pw = reinterpret_cast<const uint32_t*>(p);
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            const uint32_t w = pw[i];
+            out[2 * i] = cvt16<BF16>((uint16_t)(w & 0xFFFF)); out[2 * i + 1] = cvt16<BF16>((uint16_t)(w >> 16));
+        }
     } else if constexpr (EPL == 4) {
         uint2 w = *reinterpret_cast<const uint2*>(p);
         out[0] = cvt16<BF16>((uint16_t)(w.x & 0xFFFF)); out[1] = cvt16<BF16>((uint16_t)(w.x >> 16));
@@ -64,15 +71,15 @@ __device__ __forceinline__ void load8(const uint8_t* row, int lane, float scale,
     for (int i = 0; i < EPL; i++) out[i] = cvt_e4m3(p[i]) * scale;
 }
 
-// G = query heads per kv head, EPL = D/32 elements per lane, FP8 = pool holds E4M3 codes,
-// BF16 = 16-bit type is bf16 (else fp16).
-template <int G, int EPL, bool FP8, bool BF16>
+// G = query heads per kv head, EPL = D/32 and EPLV = Dv/32 elements per lane (they differ only for
+// the MLA cache, 192/128), FP8 = pool holds E4M3 codes, BF16 = 16-bit type is bf16 (else fp16).
+template <int G, int EPL, int EPLV, bool FP8, bool BF16>
 __global__ void __launch_bounds__(kWarps * 32)
 decode_simt_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restrict__ page_table,
                    const uint16_t* __restrict__ q, float* __restrict__ partials, MergeOut mo) {
-    constexpr int D = EPL * 32;
+    constexpr int D = EPL * 32, DV = EPLV * 32;
     __shared__ float qs[G][D];
-    __shared__ float red[kWarps][G][D + 2];
+    __shared__ float red[kWarps][G][DV + 2];
     __shared__ int s_flag;
 
     const int4 it = st.items[blockIdx.x];
@@ -97,35 +104,35 @@ decode_simt_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restri
     __syncthreads();
 
     const float scale = 1.0f / sqrtf((float)D);
-    float m[G], l[G], o[G][EPL];
+    float m[G], l[G], o[G][EPLV];
 #pragma unroll
     for (int gq = 0; gq < G; gq++) {
         m[gq] = -1e30f; l[gq] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < EPL; i++) o[gq][i] = 0.0f;
+        for (int i = 0; i < EPLV; i++) o[gq][i] = 0.0f;
     }
 
     const int32_t* prow = page_table + (size_t)seq * g.max_pages_per_seq;
     for (int t = t0 + warp; t < t1; t += kWarps) {
         const int r = t % ps;
-        float kf[EPL], vf[EPL];
+        float kf[EPL], vf[EPLV];
         if (FP8 && kind == 0) {
             const int page = prow[t / ps];
             const size_t tile = ((size_t)page * g.Hkv + kvh) * 2;
             const uint8_t* kt = (const uint8_t*)lp.pool + tile * ps * D + (size_t)r * D;
             const float ks = lp.scales[tile], vs = lp.scales[tile + 1];
             load8<EPL>(kt, lane, ks, kf);
-            load8<EPL>(kt + (size_t)ps * D, lane, vs, vf);
+            load8<EPLV>(kt + (size_t)ps * D, lane, vs, vf);
         } else {
-            const uint16_t* kt;
-            if (FP8) kt = (const uint16_t*)lp.open_pages + ((size_t)seq * g.Hkv + kvh) * 2 * ps * D + (size_t)r * D;
+            const uint16_t* tile;                       // K rows (D wide), then V rows (DV wide)
+            if (FP8) tile = (const uint16_t*)lp.open_pages + ((size_t)seq * g.Hkv + kvh) * ps * (D + DV);
             else {
                 const int pg = prow[t / ps];
                 const uint16_t* base = (const uint16_t*)((pg & kColdBit) ? lp.cold_stage : lp.pool);
-                kt = base + ((size_t)(pg & ~kColdBit) * g.Hkv + kvh) * 2 * ps * D + (size_t)r * D;
+                tile = base + ((size_t)(pg & ~kColdBit) * g.Hkv + kvh) * ps * (D + DV);
             }
-            load16<EPL, BF16>(kt, lane, kf);
-            load16<EPL, BF16>(kt + (size_t)ps * D, lane, vf);
+            load16<EPL, BF16>(tile + (size_t)r * D, lane, kf);
+            load16<EPLV, BF16>(tile + (size_t)ps * D + (size_t)r * DV, lane, vf);
         }
 #pragma unroll
         for (int gq = 0; gq < G; gq++) {
@@ -140,7 +147,7 @@ decode_simt_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restri
             const float p = expf(s - m_new);
             l[gq] = l[gq] * alpha + p;
 #pragma unroll
-            for (int i = 0; i < EPL; i++) o[gq][i] = o[gq][i] * alpha + p * vf[i];
+            for (int i = 0; i < EPLV; i++) o[gq][i] = o[gq][i] * alpha + p * vf[i];
             m[gq] = m_new;
         }
     }
@@ -148,41 +155,42 @@ decode_simt_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restri
 #pragma unroll
     for (int gq = 0; gq < G; gq++) {
 #pragma unroll
-        for (int i = 0; i < EPL; i++) red[warp][gq][lane * EPL + i] = o[gq][i];
-        if (lane == 0) { red[warp][gq][D] = m[gq]; red[warp][gq][D + 1] = l[gq]; }
+        for (int i = 0; i < EPLV; i++) red[warp][gq][lane * EPLV + i] = o[gq][i];
+        if (lane == 0) { red[warp][gq][DV] = m[gq]; red[warp][gq][DV + 1] = l[gq]; }
     }
     __syncthreads();
 
     const int row = st.chunk_base[b] + chunk;
-    for (int i = threadIdx.x; i < G * (D + 2); i += blockDim.x) {
-        const int gq = i / (D + 2), d = i % (D + 2);
+    for (int i = threadIdx.x; i < G * (DV + 2); i += blockDim.x) {
+        const int gq = i / (DV + 2), d = i % (DV + 2);
         float M = -1e30f;
 #pragma unroll
-        for (int w = 0; w < kWarps; w++) M = fmaxf(M, red[w][gq][D]);
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, red[w][gq][DV]);
         float val;
-        if (d == D) {
+        if (d == DV) {
             val = M;
         } else {
             val = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kWarps; w++) val += red[w][gq][d] * expf(red[w][gq][D] - M);
+            for (int w = 0; w < kWarps; w++) val += red[w][gq][d] * expf(red[w][gq][DV] - M);
         }
-        partials[partial_off(row, kvh * G + gq, g.H, D) + d] = val;
+        partials[partial_off(row, kvh * G + gq, g.H, DV) + d] = val;
     }
     merge_if_last(g, st, mo, b, kvh, G, partials, &s_flag);
 }
 
-template <int G, int EPL>
+template <int G, int EPL, int EPLV = EPL>
 cudaError_t launch_simt_ge(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
                            const int32_t* page_table, const void* q, float* partials, cudaStream_t s,
                            const MergeOut& mo) {
     const bool fp8 = g.dtype == DT_FP8, bf16 = g.io_dtype == DT_BF16;
+    if (fp8 && EPLV != EPL) return cudaErrorNotSupported;
     dim3 grid(st.n_items), block(kWarps * 32);
     const uint16_t* qq = (const uint16_t*)q;
-    if (fp8 && bf16)       decode_simt_kernel<G, EPL, true, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
-    else if (fp8)          decode_simt_kernel<G, EPL, true, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
-    else if (bf16)         decode_simt_kernel<G, EPL, false, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
-    else                   decode_simt_kernel<G, EPL, false, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    if (fp8 && bf16)       decode_simt_kernel<G, EPL, EPLV, true, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    else if (fp8)          decode_simt_kernel<G, EPL, EPLV, true, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    else if (bf16)         decode_simt_kernel<G, EPL, EPLV, false, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    else                   decode_simt_kernel<G, EPL, EPLV, false, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
     return cudaGetLastError();
 }
 
@@ -190,6 +198,8 @@ template <int G>
 cudaError_t launch_simt_g(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
                           const int32_t* page_table, const void* q, float* partials, cudaStream_t s,
                           const MergeOut& mo) {
+    if (g.D == 192 && g.Dv == 128) return launch_simt_ge<G, 6, 4>(g, lp, st, page_table, q, partials, s, mo);
+    if (g.Dv != g.D) return cudaErrorNotSupported;
     switch (g.D) {
         case 64:  return launch_simt_ge<G, 2>(g, lp, st, page_table, q, partials, s, mo);
         case 128: return launch_simt_ge<G, 4>(g, lp, st, page_table, q, partials, s, mo);
@@ -223,7 +233,7 @@ cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const Ste
 __global__ void combine_step_kernel(Geometry g, StepDev st, const float* __restrict__ partials,
                                     void* __restrict__ out, int out_dtype,
                                     float* __restrict__ partial_out) {
-    const int h = blockIdx.x, b = blockIdx.y, D = g.D;
+    const int h = blockIdx.x, b = blockIdx.y, D = g.Dv;
     const int r0 = st.chunk_base[b], r1 = st.chunk_base[b + 1];
     float M = -1e30f;
     for (int r = r0; r < r1; r++) M = fmaxf(M, partials[partial_off(r, h, g.H, D) + D]);

@@ -120,7 +120,7 @@ extern "C" int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t n
         return TK_CUDA_ERROR;
     }
 
-    tk::Geometry g{num_heads, num_kv_heads, head_dim, kPage, dtype, dtype, num_pages, n_seqs, max_pages_per_seq};
+    tk::Geometry g{num_heads, num_kv_heads, head_dim, kPage, dtype, dtype, num_pages, n_seqs, max_pages_per_seq, head_dim};
     tk::LayerPtrs lp{const_cast<void*>(pool), nullptr, nullptr, nullptr};
     tk::StepDev st{};
     st.seq = sc->seq; st.len = sc->len; st.chunk_base = sc->chunk_base;

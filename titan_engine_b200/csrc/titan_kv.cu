@@ -33,7 +33,7 @@ struct ArenaLayout {
 ArenaLayout arena_layout(const tk_kv_config& c) {
     ArenaLayout a{};
     const size_t esize = c.dtype == TK_FP8_E4M3 ? 1 : 2;
-    const size_t tile = (size_t)c.num_kv_heads * 2 * c.page_size * c.head_dim;
+    const size_t tile = (size_t)c.num_kv_heads * c.page_size * (c.head_dim + c.v_head_dim);   // K rows + V rows
     a.pool_layer = align_up((size_t)c.num_pages * tile * esize, 1024);
     if (c.dtype == TK_FP8_E4M3) {
         a.scales_layer = align_up((size_t)c.num_pages * c.num_kv_heads * 2 * sizeof(float), 1024);
@@ -51,7 +51,10 @@ const char* validate(const tk_kv_config& c) {
     if (c.num_heads % c.num_kv_heads != 0) return "num_heads must be a multiple of num_kv_heads";
     const int G = c.num_heads / c.num_kv_heads;
     if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return "heads per kv head must be 1, 2, 4, 8 or 16";
-    if (c.head_dim != 64 && c.head_dim != 128) return "head_dim must be 64 or 128";
+    const bool mla = c.head_dim == 192 && c.v_head_dim == 128;      // K = nope + rope dims, V = nope dims
+    if (!mla && ((c.head_dim != 64 && c.head_dim != 128) || c.v_head_dim != c.head_dim))
+        return "head_dim must be 64 or 128 (v_head_dim equal), or 192 with v_head_dim 128 (MLA)";
+    if (mla && c.dtype == TK_FP8_E4M3) return "the MLA shape needs 16-bit storage";
     if (c.page_size <= 0 || c.page_size % 8 != 0) return "page_size must be a positive multiple of 8";
     if (c.dtype != TK_FP16 && c.dtype != TK_BF16 && c.dtype != TK_FP8_E4M3) return "dtype must be FP16, BF16 or FP8_E4M3";
     if (c.io_dtype != TK_FP16 && c.io_dtype != TK_BF16) return "io_dtype must be FP16 or BF16";
@@ -219,17 +222,18 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     tk_kv_config c = *cfg_in;
     if (c.io_dtype == 0) c.io_dtype = c.dtype == TK_FP8_E4M3 ? TK_BF16 : c.dtype;
     if (c.max_step_tokens == 0) c.max_step_tokens = c.max_seqs;
+    if (c.v_head_dim == 0) c.v_head_dim = c.head_dim;
     if (const char* why = validate(c)) return fail(nullptr, TK_INVALID_ARG, "config: %s", why);
 
     tk_kv* h = new (std::nothrow) tk_kv();
     if (!h) return fail(nullptr, TK_INVALID_ARG, "out of host memory");
     h->cfg = c;
     h->geo = tk::Geometry{c.num_heads, c.num_kv_heads, c.head_dim, c.page_size, c.dtype, c.io_dtype,
-                          c.num_pages, c.max_seqs, c.max_pages_per_seq};
+                          c.num_pages, c.max_seqs, c.max_pages_per_seq, c.v_head_dim};
     h->mgr = new tk::PageManager(c.num_pages, c.max_seqs, c.max_pages_per_seq, c.page_size);
     h->lay = arena_layout(c);
     h->host_only = c.device == TK_DEVICE_NONE;
-    h->page_bytes = (size_t)c.num_kv_heads * 2 * c.page_size * c.head_dim * (c.dtype == TK_FP8_E4M3 ? 1 : 2);
+    h->page_bytes = (size_t)c.num_kv_heads * c.page_size * (c.head_dim + c.v_head_dim) * (c.dtype == TK_FP8_E4M3 ? 1 : 2);
     if (c.hot_window > 0) h->mgr->enable_cold(c.hot_window, c.cold_pages);
     h->stats.pages_total = c.num_pages;
 
@@ -280,7 +284,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     CREATE_CUDA(cudaMalloc((void**)&h->d_table, table_bytes));
     CREATE_CUDA(cudaMemset(h->d_table, 0xFF, table_bytes));
     CREATE_CUDA(cudaMalloc((void**)&h->d_partials,
-                           (size_t)h->max_partial_rows * c.num_heads * (c.head_dim + 2) * sizeof(float)));
+                           (size_t)h->max_partial_rows * c.num_heads * (c.v_head_dim + 2) * sizeof(float)));
     CREATE_CUDA(cudaMalloc((void**)&h->d_status, 256));
     CREATE_CUDA(cudaMemset(h->d_status, 0, 256));
     CREATE_CUDA(cudaMalloc((void**)&h->d_counters, sizeof(int) * (size_t)c.max_seqs * c.num_kv_heads));
@@ -290,8 +294,8 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
         CREATE_CUDA(cudaHostAlloc((void**)&h->h_step[i], h->step_bytes, cudaHostAllocDefault));
         CREATE_CUDA(cudaEventCreateWithFlags(&h->ev[i], cudaEventDisableTiming));
     }
-    const size_t kv_bytes = (size_t)c.max_step_tokens * c.num_kv_heads * c.head_dim * 2;
-    const size_t q_bytes = (size_t)c.max_seqs * c.num_heads * c.head_dim * 2;
+    const size_t kv_bytes = (size_t)c.max_step_tokens * c.num_kv_heads * c.head_dim * 2;   // sized for K rows (>= V rows)
+    const size_t q_bytes = (size_t)c.max_seqs * c.num_heads * c.head_dim * 2;              // q rows (>= out rows)
     CREATE_CUDA(cudaMalloc(&h->d_q, q_bytes));
     CREATE_CUDA(cudaMalloc(&h->d_rq, q_bytes));
     CREATE_CUDA(cudaMalloc((void**)&h->d_rope_tab, sizeof(float2) * (size_t)c.max_seqs * (c.head_dim / 2)));
@@ -437,6 +441,7 @@ size_t tk_kv_arena_bytes(const tk_kv_config* cfg) {
     tk_kv_config c = *cfg;
     if (c.io_dtype == 0) c.io_dtype = c.dtype == TK_FP8_E4M3 ? TK_BF16 : c.dtype;
     if (c.max_step_tokens == 0) c.max_step_tokens = c.max_seqs;
+    if (c.v_head_dim == 0) c.v_head_dim = c.head_dim;
     if (validate(c)) return 0;
     return arena_layout(c).total;
 }
@@ -796,6 +801,8 @@ int tk_kv_rope_append_decode(tk_kv* h, int32_t layer, const void* k, const void*
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "rope_append_decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "rope_append_decode: no step in progress (call tk_kv_step_begin)");
     if (!q || !out || (h->dev.n_tokens > 0 && (!k || !v))) return fail(h, TK_INVALID_ARG, "rope_append_decode: null argument");
+    if (h->cfg.v_head_dim != h->cfg.head_dim)
+        return fail(h, TK_UNSUPPORTED, "rope_append_decode: the MLA shape rotates only its rope dims; rotate before the call");
     const bool fusable = h->use_mma && h->cfg.dtype != TK_FP8_E4M3 && h->plan.one_token_steps &&
                          h->dev.chunk_tokens <= 2048 && h->dev.n_tokens > 0 && h->dev.n_seqs > 0 &&
                          !h->plan.has_empty_seq && getenv("TK_SEPARATE_APPEND") == nullptr;
@@ -845,15 +852,17 @@ static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, 
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "append_decode_host: no step in progress");
     cudaStream_t s = (cudaStream_t)stream;
     const size_t kv_bytes = (size_t)h->dev.n_tokens * h->cfg.num_kv_heads * h->cfg.head_dim * 2;
+    const size_t vv_bytes = (size_t)h->dev.n_tokens * h->cfg.num_kv_heads * h->cfg.v_head_dim * 2;
     const size_t q_bytes = (size_t)h->dev.n_seqs * h->cfg.num_heads * h->cfg.head_dim * 2;
+    const size_t o_bytes = (size_t)h->dev.n_seqs * h->cfg.num_heads * h->cfg.v_head_dim * 2;
     if (kv_bytes && (!k_host || !v_host)) return fail(h, TK_INVALID_ARG, "append_decode_host: null k/v");
     if (q_bytes && (!q_host || !out_host)) return fail(h, TK_INVALID_ARG, "append_decode_host: null q/out");
     const int set = (int)(h->host_calls++ & 1);
     TK_CUDA(h, cudaStreamWaitEvent(h->st_in, h->ev_compute[set], 0));
     if (kv_bytes) {
         TK_CUDA(h, cudaMemcpyAsync(h->hs_k[set], k_host, kv_bytes, cudaMemcpyHostToDevice, h->st_in));
-        TK_CUDA(h, cudaMemcpyAsync(h->hs_v[set], v_host, kv_bytes, cudaMemcpyHostToDevice, h->st_in));
-        h->stats.bytes_h2d += 2 * (int64_t)kv_bytes;
+        TK_CUDA(h, cudaMemcpyAsync(h->hs_v[set], v_host, vv_bytes, cudaMemcpyHostToDevice, h->st_in));
+        h->stats.bytes_h2d += (int64_t)kv_bytes + (int64_t)vv_bytes;
     }
     if (q_bytes) {
         TK_CUDA(h, cudaMemcpyAsync(h->hs_q[set], q_host, q_bytes, cudaMemcpyHostToDevice, h->st_in));
@@ -870,9 +879,9 @@ static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, 
     TK_CUDA(h, cudaEventRecord(h->ev_compute[set], s));
     if (q_bytes) {
         TK_CUDA(h, cudaStreamWaitEvent(h->st_out, h->ev_compute[set], 0));
-        TK_CUDA(h, cudaMemcpyAsync(out_host, h->hs_out[set], q_bytes, cudaMemcpyDeviceToHost, h->st_out));
+        TK_CUDA(h, cudaMemcpyAsync(out_host, h->hs_out[set], o_bytes, cudaMemcpyDeviceToHost, h->st_out));
         TK_CUDA(h, cudaEventRecord(h->ev_out[set], h->st_out));
-        h->stats.bytes_d2h += (int64_t)q_bytes;
+        h->stats.bytes_d2h += (int64_t)o_bytes;
     }
     if (wait) {
         TK_CUDA(h, cudaStreamSynchronize(s));

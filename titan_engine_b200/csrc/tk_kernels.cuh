@@ -15,7 +15,14 @@ struct Geometry {
     int H, Hkv, D, ps;          // query heads, kv heads, head dim, tokens per page
     int dtype, io_dtype;        // storage type; type of q/k/v/out and of FP8 open pages
     int num_pages, max_seqs, max_pages_per_seq;
+    int Dv;                     // V rows / output width; == D except for the MLA cache (D = 192, Dv = 128)
 };
+
+// Element offset of the K (kv = 0) or V (kv = 1) rows of tile (page, kv head): a tile is ps rows
+// of K (D elements each) followed by ps rows of V (Dv elements each).
+__host__ __device__ inline size_t tile_offset(const Geometry& g, int page, int kvh, int kv) {
+    return ((size_t)page * g.Hkv + kvh) * (size_t)g.ps * (g.D + g.Dv) + (kv ? (size_t)g.ps * g.D : 0);
+}
 
 // One layer of the pool.  16-bit / FP8 codes: [num_pages][Hkv][2 (K,V)][ps][D];
 // scales f32 [num_pages][Hkv][2]; open pages [max_seqs][Hkv][2][ps][D] in io_dtype.

@@ -26,7 +26,7 @@ __device__ __forceinline__ void store_out(void* out, size_t idx, float v, int dt
 __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& st, const MergeOut& mo,
                                               int b, int kvh, int G, const float* partials, int* s_flag) {
     if (!mo.counters) return;
-    const int D = g.D;
+    const int D = g.Dv;                                // width of a partial / output row
     const int r0 = st.chunk_base[b], n = st.chunk_base[b + 1] - r0;
     __syncthreads();                                   // the CTA's partial row is complete ...
     if (threadIdx.x == 0) {

@@ -43,7 +43,7 @@ class PagedKVCache:
                  io_dtype: Optional[str] = None, page_size: int = 16,
                  max_step_tokens: Optional[int] = None, chunk_tokens: int = 0,
                  decode_impl: str = "auto", device: Optional[int] = None, host_only: bool = False,
-                 hot_window: int = 0, cold_pages: int = 0):
+                 hot_window: int = 0, cold_pages: int = 0, v_head_dim: int = 0):
         self._lib = L.lib()
         cfg = L.KvConfig()
         self._lib.tk_kv_config_default(C.byref(cfg))
@@ -53,7 +53,7 @@ class PagedKVCache:
         cfg.num_pages, cfg.max_seqs, cfg.max_pages_per_seq = num_pages, max_seqs, max_pages_per_seq
         cfg.max_step_tokens = max_step_tokens or max_seqs
         cfg.chunk_tokens, cfg.decode_impl = chunk_tokens, _IMPLS[decode_impl]
-        cfg.hot_window, cfg.cold_pages = hot_window, cold_pages
+        cfg.hot_window, cfg.cold_pages, cfg.v_head_dim = hot_window, cold_pages, v_head_dim
         self._h = C.c_void_p()
         self.host_only = host_only
         self._arena = None
@@ -188,10 +188,11 @@ class PagedKVCache:
         return self._lib.tk_kv_step_chunk_tokens(self._h)
 
     def _check_io(self, t: torch.Tensor, rows: int, heads: int, what: str) -> None:
+        dim = self.cfg.v_head_dim if what in ("v", "out") else self.cfg.head_dim
         if t.device != self.device or t.dtype != self.io_torch_dtype or not t.is_contiguous():
             raise KvError(L.TK_INVALID_ARG, f"{what}: need a contiguous {self.io_torch_dtype} tensor on {self.device}")
-        if t.numel() != rows * heads * self.cfg.head_dim:
-            raise KvError(L.TK_INVALID_ARG, f"{what}: expected [{rows}, {heads}, {self.cfg.head_dim}]")
+        if t.numel() != rows * heads * dim:
+            raise KvError(L.TK_INVALID_ARG, f"{what}: expected [{rows}, {heads}, {dim}]")
 
     def append(self, layer: int, k: torch.Tensor, v: torch.Tensor,
                slots_out: Optional[torch.Tensor] = None) -> None:
@@ -208,7 +209,7 @@ class PagedKVCache:
         """q: [n_seqs, H, D] -> out [n_seqs, H, D], io dtype."""
         self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
         if out is None:
-            out = torch.empty_like(q)
+            out = torch.empty(q.shape[0], self.cfg.num_heads, self.cfg.v_head_dim, dtype=q.dtype, device=q.device)
         self._check_io(out, self._n_seqs, self.cfg.num_heads, "out")
         self._check(self._lib.tk_kv_decode(self._h, layer, q.data_ptr(), out.data_ptr(), self._stream()))
         return out
@@ -220,7 +221,7 @@ class PagedKVCache:
         self._check_io(v, self._n_tokens, self.cfg.num_kv_heads, "v")
         self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
         if out is None:
-            out = torch.empty_like(q)
+            out = torch.empty(q.shape[0], self.cfg.num_heads, self.cfg.v_head_dim, dtype=q.dtype, device=q.device)
         self._check(self._lib.tk_kv_append_decode(self._h, layer, k.data_ptr(), v.data_ptr(), q.data_ptr(),
                                                   out.data_ptr(), self._stream()))
         return out
@@ -232,7 +233,7 @@ class PagedKVCache:
         self._check_io(v, self._n_tokens, self.cfg.num_kv_heads, "v")
         self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
         if out is None:
-            out = torch.empty_like(q)
+            out = torch.empty(q.shape[0], self.cfg.num_heads, self.cfg.v_head_dim, dtype=q.dtype, device=q.device)
         self._check(self._lib.tk_kv_rope_append_decode(self._h, layer, k.data_ptr(), v.data_ptr(), q.data_ptr(),
                                                        out.data_ptr(), theta, scaling, self._stream()))
         return out
@@ -241,7 +242,7 @@ class PagedKVCache:
         """-> [n_seqs, H, D+2] f32: unnormalised o, then m, then l."""
         self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
         if partial is None:
-            partial = torch.empty(self._n_seqs, self.cfg.num_heads, self.cfg.head_dim + 2,
+            partial = torch.empty(self._n_seqs, self.cfg.num_heads, self.cfg.v_head_dim + 2,
                                   dtype=torch.float32, device=self.device)
         self._check(self._lib.tk_kv_decode_partial(self._h, layer, q.data_ptr(), partial.data_ptr(), self._stream()))
         return partial
@@ -298,5 +299,8 @@ class PagedKVCache:
             oshape = (c.max_seqs, c.num_kv_heads, 2, c.page_size, c.head_dim)
             open_pages = self._view(o.value, int(np.prod(oshape)) * 2).view(self.io_torch_dtype).view(oshape)
             return pool, scales, open_pages
+        if c.v_head_dim != c.head_dim:        # MLA tile: page_size K rows of head_dim, then V rows of v_head_dim
+            shape = (c.num_pages, c.num_kv_heads, c.page_size * (c.head_dim + c.v_head_dim))
+            n = int(np.prod(shape))
         pool = self._view(p.value, n * 2).view(_TORCH16[c.dtype]).view(shape)
         return pool, None, None
