@@ -37,7 +37,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch divided by its algorithmic
 # bytes, from the ncu captures summarised under profiles/ (taken on a 4-layer / 2-layer cut of the
 # same workload; the traffic is proportional to the tokens read, so it scales to a full launch)
-TRAFFIC_OVER_ALGORITHMIC = {"8b-bf16": 1.0085, "70b-fp8": 1.0108}
+TRAFFIC_OVER_ALGORITHMIC = {"8b-bf16": 1.0085, "70b-fp8": 1.0108, "mla-bf16": None}
 
 
 def measured_peak():
@@ -62,13 +62,15 @@ def algorithmic_bytes(ctx: np.ndarray, s=SHAPE):
     appended rows + q read and out write + page-table entries; `kernel` is the share the decode
     kernel moves."""
     esize = s.get("esize", 2)
-    kv = int(ctx.sum()) * s["Hkv"] * s["D"] * 2 * esize
+    dv = s.get("Dv", s["D"])
+    kv = int(ctx.sum()) * s["Hkv"] * (s["D"] + dv) * esize
     if esize == 1:
         kv += int(((ctx + s["ps"] - 1) // s["ps"]).sum()) * s["Hkv"] * 2 * 4
-    app = len(ctx) * s["Hkv"] * s["D"] * 2 * 2
-    qo = 2 * len(ctx) * s["H"] * s["D"] * 2
+    app = len(ctx) * s["Hkv"] * (s["D"] + dv) * 2
+    q_b = len(ctx) * s["H"] * s["D"] * 2
+    o_b = len(ctx) * s["H"] * dv * 2
     pt = int(((ctx + s["ps"] - 1) // s["ps"]).sum()) * 4
-    return {"layer": kv + app + qo + pt, "kernel": kv + qo // 2 + pt}
+    return {"layer": kv + app + q_b + o_b + pt, "kernel": kv + q_b + pt}
 
 
 class ClockSampler:
@@ -200,6 +202,12 @@ def run_reference(args):
 
 
 def config_dict(ctx, n_gpus):
+    if "Dv" in SHAPE:
+        return {"workload": "MLA-shape decode (K rows 192 = nope 128 + rope 64, V rows 128): 128 q heads / 128 kv heads, "
+                            "bf16, 16 sequences/GPU at 4096 tokens, page 16, shuffled pool; resident layer subset",
+                "sequences_per_gpu": int(len(ctx)), "live_tokens_per_gpu": int(ctx.sum()),
+                "parallelism": f"by sequence x{n_gpus} (no data-path collective)",
+                "l2": "inputs larger than L2: each layer reads its own ~5.4 GB of pool per step"}
     if SHAPE.get("esize", 2) == 1:
         return {"workload": "llama-3-70b-shape FP8 decode: 64 q heads / 8 kv heads, head_dim 128, FP8-E4M3 pool with "
                             "per-page per-head scales, 32 sequences/GPU at 32768 tokens, page 16, shuffled pool; "
@@ -243,8 +251,10 @@ def run_ours(args):
     num_pages = int(pages_end.sum()) + 64
     mpps = int(pages_end.max()) + 1
     fp8 = s.get("esize", 2) == 1
+    dv = s.get("Dv", s["D"])
     cache = PagedKVCache(L, s["H"], s["Hkv"], s["D"], num_pages, B, mpps, dtype="fp8" if fp8 else "bf16",
-                         max_step_tokens=B, decode_impl=args.decode_impl, chunk_tokens=args.chunk)
+                         max_step_tokens=B, decode_impl=args.decode_impl, chunk_tokens=args.chunk,
+                         v_head_dim=dv if dv != s["D"] else 0)
     g = np.random.Generator(np.random.Philox(2 + 1000 * rank))
     perm = g.permutation(num_pages).astype(np.int32)
     seqs, at = [], 0
@@ -267,11 +277,11 @@ def run_ours(args):
             pool[sl] = (x / scales[sl][..., None, None]).clamp_(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
         open_pages.normal_(generator=gen)
     k = torch.randn(B, s["Hkv"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
-    v = torch.randn(B, s["Hkv"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B, s["Hkv"], dv, device=dev, generator=gen).to(torch.bfloat16)
     q = torch.randn(B, s["H"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
-    out = torch.empty_like(q)
+    out = torch.empty(B, s["H"], dv, device=dev, dtype=torch.bfloat16)
     hk, hv, hq = (t.cpu().pin_memory() for t in (k, v, q))
-    hout = torch.empty_like(hq).pin_memory()
+    hout = torch.empty_like(out, device="cpu").pin_memory()
     ones = [1] * B
     lens = ctx.copy()
 
@@ -348,8 +358,12 @@ def run_ours(args):
     value = world * args.steps / (ms / 1e3)
     kern_avg_ms = kern_ms / max(kern_n, 1)
     achieved = ab["kernel"] / (kern_avg_ms * 1e-3) / 1e9 if kern_n else None
-    unit = UNIT if not fp8 else (f"decode steps/s (1 step = {B} seqs x {L} layers: append 1 token + paged GQA "
-                                 "attention over the FP8 pool)")
+    unit = UNIT
+    if fp8 or "Dv" in s:
+        unit = (f"decode steps/s (1 step = {B} seqs x {L} layers: append 1 token + paged "
+                + ("GQA attention over the FP8 pool)" if fp8 else "MLA-shape attention)"))
+    simt = args.decode_impl == "simt" or "Dv" in s
+    ratio = TRAFFIC_OVER_ALGORITHMIC[args.workload]
     line = {
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -358,10 +372,10 @@ def run_ours(args):
         "hbm_gbs_step": ab["layer"] * L / (ms_per_step * 1e-3) / 1e9,
         "hbm_frac_step": ab["layer"] * L / (ms_per_step * 1e-3) / 1e9 / peak,
         "layers": L, "chunk_tokens": cache.step_chunk_tokens, "work_items_per_layer": cache.step_num_work_items,
-        "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel" if args.decode_impl != "simt" else "decode_simt_kernel",
+        "roofline": {"bound": "hbm", "kernel": "decode_simt_kernel" if simt else "decode_mma_kernel",
                      "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": (achieved / peak) if achieved else None,
-                     "traffic": int(ab["kernel"] * TRAFFIC_OVER_ALGORITHMIC[args.workload]),
+                     "traffic": int(ab["kernel"] * ratio) if ratio else None,
                      "traffic_source": "ncu dram bytes of a reduced-layer capture (profiles/), scaled by tokens",
                      "algorithmic_bytes_per_launch": ab["kernel"], "avg_launch_ms": kern_avg_ms,
                      "launches_timed": kern_n, "peak_source": peak_src},
@@ -387,9 +401,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="8b-bf16", choices=["8b-bf16", "70b-fp8"],
+    ap.add_argument("--workload", default="8b-bf16", choices=["8b-bf16", "70b-fp8", "mla-bf16"],
                     help="8b-bf16: the headline batched decode; 70b-fp8: 64 q / 8 kv heads, 32 sequences at 32768 "
-                         "tokens, FP8-E4M3 pool, a resident subset of the 80 layers (extra, not the headline)")
+                         "tokens, FP8-E4M3 pool, a resident subset of the 80 layers; mla-bf16: K rows 192 / V rows "
+                         "128, 128 kv heads, 16 sequences at 4096 tokens (extras, not the headline)")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--decode-impl", default="auto", choices=["auto", "simt", "mma"])
     ap.add_argument("--chunk", type=int, default=0, help="split-KV chunk tokens (0 = library default)")
@@ -400,6 +415,9 @@ def main():
     args = ap.parse_args()
     if args.workload == "70b-fp8":
         SHAPE.update(H=64, Hkv=8, D=128, L=16, B=32, lo=32768, hi=32768, esize=1)
+        args.no_cpu = True
+    if args.workload == "mla-bf16":
+        SHAPE.update(H=128, Hkv=128, D=192, Dv=128, L=8, B=16, lo=4096, hi=4096)
         args.no_cpu = True
     args.layers = args.layers or SHAPE["L"]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

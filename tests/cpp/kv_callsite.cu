@@ -20,10 +20,56 @@ static uint32_t lcg(uint32_t& s) { s = s * 1664525u + 1013904223u; return s >> 8
 // values with <= 10 significant bits: exactly representable in fp16 and in fp32
 static float val(uint32_t& s) { return ((int)(lcg(s) % 1025) - 512) / 256.0f; }
 
+// The MLA layer loop (reference: src/model/moe.cpp:832-838): K rows of nope+rope dims, V rows of
+// nope dims, the cache placed in caller memory by initialize_external_mla.
+static int run_mla(const char* path, int n_tokens) {
+    const uint32_t L = 2, H = 8, Hkv = 8, Dk = 192, Dv = 128, max_seq = 256;
+    titan::KVCache cache;
+    float *kbuf = nullptr, *vbuf = nullptr;
+    CHECK(cudaMalloc(&kbuf, (size_t)L * max_seq * Hkv * Dk * sizeof(float)));
+    CHECK(cudaMalloc(&vbuf, (size_t)L * max_seq * Hkv * Dv * sizeof(float)));
+    if (!cache.initialize_external_mla(L, Hkv, Dk, Dv, max_seq, kbuf, vbuf)) { fprintf(stderr, "initialize_external_mla failed\n"); return 3; }
+    if (cache.k_head_dim() != Dk || cache.v_head_dim() != Dv || cache.seq_len() != 0) return 4;
+    float *dq, *dk, *dv, *dout;
+    CHECK(cudaMalloc(&dq, H * Dk * sizeof(float)));
+    CHECK(cudaMalloc(&dk, Hkv * Dk * sizeof(float)));
+    CHECK(cudaMalloc(&dv, Hkv * Dv * sizeof(float)));
+    CHECK(cudaMalloc(&dout, H * Dv * sizeof(float)));
+    cudaStream_t stream;
+    CHECK(cudaStreamCreate(&stream));
+    std::vector<float> q(H * Dk), k(Hkv * Dk), v(Hkv * Dv), out(H * Dv);
+    FILE* f = fopen(path, "wb");
+    if (!f) return 5;
+    uint32_t seed = 777;
+    for (int pos = 0; pos < n_tokens; pos++) {
+        for (uint32_t l = 0; l < L; l++) {
+            for (auto& x : q) x = val(seed);
+            for (auto& x : k) x = val(seed);
+            for (auto& x : v) x = val(seed);
+            CHECK(cudaMemcpyAsync(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice, stream));
+            CHECK(cudaMemcpyAsync(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice, stream));
+            CHECK(cudaMemcpyAsync(dv, v.data(), v.size() * 4, cudaMemcpyHostToDevice, stream));
+            cache.update(l, pos, dk, dv, stream);
+            const int seq_len = cache.seq_len();
+            if (seq_len != pos + 1) { fprintf(stderr, "seq_len %d at pos %d\n", seq_len, pos); return 6; }
+            titan::cuda::attention_decode_mla(dq, cache.k_cache(l), cache.v_cache(l), dout, H, Hkv, Dk, Dv, seq_len, stream);
+            CHECK(cudaGetLastError());
+            CHECK(cudaMemcpyAsync(out.data(), dout, out.size() * 4, cudaMemcpyDeviceToHost, stream));
+            CHECK(cudaStreamSynchronize(stream));
+            fwrite(out.data(), 4, out.size(), f);
+        }
+    }
+    fclose(f);
+    printf("ok %d tokens (MLA), memory_bytes %zu\n", n_tokens, cache.memory_bytes());
+    return 0;
+}
+
 int main(int argc, char** argv) {
-    if (argc < 2) { fprintf(stderr, "usage: %s out.bin [n_tokens] [external]\n", argv[0]); return 2; }
+    if (argc < 2) { fprintf(stderr, "usage: %s out.bin [n_tokens] [0 owned | 1 external | 2 external MLA]\n", argv[0]); return 2; }
     const int n_tokens = argc > 2 ? atoi(argv[2]) : 150;
-    const bool external = argc > 3 && atoi(argv[3]) != 0;
+    const int mode = argc > 3 ? atoi(argv[3]) : 0;
+    if (mode == 2) return run_mla(argv[1], n_tokens);
+    const bool external = mode != 0;
     const uint32_t L = 2, H = 8, Hkv = 2, D = 64, max_seq = 256;
     const float theta = 10000.0f;
 

@@ -32,3 +32,13 @@ def test_same_call_sites_same_results(tmp_path, external):
     assert np.abs(ref).max() > 0.1
     # K after RoPE is rounded to fp16 by the paged store; everything else is FP32 on both sides
     assert_close(ours, ref, "compat KVCache + attention_decode vs the reference's own objects")
+
+
+def test_mla_call_sites_same_results(tmp_path):
+    """initialize_external_mla + attention_decode_mla (K rows 192, V rows 128), mode 2 of the program."""
+    n = 70
+    ref = _run("kv_callsite_ref", str(tmp_path / "ref.bin"), n, 2)
+    ours = _run("kv_callsite_ours", str(tmp_path / "ours.bin"), n, 2)
+    assert ref.shape == ours.shape == (n * 2 * 8 * 128,)
+    assert np.abs(ref).max() > 0.1
+    assert_close(ours, ref, "compat MLA KVCache + attention_decode_mla vs the reference's own objects")

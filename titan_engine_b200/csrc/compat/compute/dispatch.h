@@ -14,6 +14,12 @@ namespace cuda {
 void attention_decode(const float* q, const float* k_cache, const float* v_cache, float* output,
                       int num_heads, int num_kv_heads, int head_dim, int seq_len, cudaStream_t stream);
 
+// The same with K rows (and q) of k_head_dim and V rows / output of v_head_dim
+// (reference: attention_decode_mla, src/compute/cuda/attention.cu:168-253,332-349).
+void attention_decode_mla(const float* q, const float* k_cache, const float* v_cache, float* output,
+                          int num_heads, int num_kv_heads, int k_head_dim, int v_head_dim, int seq_len,
+                          cudaStream_t stream);
+
 // Interleaved-pair RoPE on q [num_heads, head_dim] and k [num_kv_heads, head_dim] in place
 // (reference: rope_kernel, src/compute/cuda/attention.cu:15-48).
 void apply_rope(float* q, float* k, int num_heads, int num_kv_heads, int head_dim, int position,

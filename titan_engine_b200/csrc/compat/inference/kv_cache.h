@@ -13,8 +13,8 @@
 //   * k_cache(layer) / v_cache(layer) return addresses inside the cache's own device slabs
 //     that identify (cache, layer) to cuda::attention_decode; they are tokens for that call,
 //     not FP32 rows to be read directly;
-//   * the MLA variant (different K and V head dims) is not provided: initialize_external_mla
-//     returns false.
+//   * the MLA variant (initialize_external_mla: K rows of nope+rope dims, V rows of nope dims)
+//     is served for the 192 / 128 shape.
 #pragma once
 
 #include "core/types.h"
@@ -60,7 +60,7 @@ public:
     uint32_t num_kv_heads() const { return num_kv_heads_; }
     uint32_t head_dim() const { return head_dim_; }
     uint32_t k_head_dim() const { return head_dim_; }
-    uint32_t v_head_dim() const { return head_dim_; }
+    uint32_t v_head_dim() const { return v_head_dim_ > 0 ? v_head_dim_ : head_dim_; }
     uint32_t max_seq_len() const { return max_seq_len_; }
 
     size_t memory_bytes() const;
@@ -73,7 +73,7 @@ public:
     bool attend(int layer, const float* q, float* out, int num_heads, int seq_len, cudaStream_t stream);
 
 private:
-    bool setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t max_seq, DType dtype, float* k_buf, float* v_buf);
+    bool setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t Dv, uint32_t max_seq, DType dtype, float* k_buf, float* v_buf);
     void release();
 
     tk_kv*   h_ = nullptr;
@@ -81,7 +81,7 @@ private:
     float*   v_base_ = nullptr;        // slab whose addresses only serve as v_cache() tokens
     void*    arena_ = nullptr;         // 1024-byte aligned start of the pool inside k_base_
     bool     owns_memory_ = true;
-    uint32_t num_layers_ = 0, num_kv_heads_ = 0, head_dim_ = 0, max_seq_len_ = 0;
+    uint32_t num_layers_ = 0, num_kv_heads_ = 0, head_dim_ = 0, v_head_dim_ = 0, max_seq_len_ = 0;
     int      seq_len_ = 0;
     int      capacity_ = 0;            // tokens the pool can hold (multiple of the page size)
     int      seq_ = -1;                // sequence slot inside the handle

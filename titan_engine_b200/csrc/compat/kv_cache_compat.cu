@@ -31,21 +31,21 @@ struct Registry {
 
 // One token's K and V rows: FP32 -> 16-bit while scattering to the page slot.
 // grid covers Hkv*D elements; dst rows are D contiguous 16-bit values.
+// grid covers Hkv*(D + Dv) elements: first the K row elements, then the V row elements.
 __global__ void compat_update_kernel(void* __restrict__ pool, const float* __restrict__ key,
-                                     const float* __restrict__ value, int Hkv, int D, int page, int r,
+                                     const float* __restrict__ value, int Hkv, int D, int Dv, int page, int r,
                                      int bf16) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= Hkv * D) return;
-    const int h = i / D, d = i % D;
-    const size_t k_off = (((size_t)page * Hkv + h) * 2 + 0) * kPage * D + (size_t)r * D + d;
-    const size_t v_off = k_off + (size_t)kPage * D;
-    if (bf16) {
-        ((__nv_bfloat16*)pool)[k_off] = __float2bfloat16_rn(key[i]);
-        ((__nv_bfloat16*)pool)[v_off] = __float2bfloat16_rn(value[i]);
-    } else {
-        ((__half*)pool)[k_off] = __float2half_rn(key[i]);
-        ((__half*)pool)[v_off] = __float2half_rn(value[i]);
-    }
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= Hkv * (D + Dv)) return;
+    const bool is_v = i >= Hkv * D;
+    if (is_v) i -= Hkv * D;
+    const int dim = is_v ? Dv : D;
+    const int h = i / dim, d = i % dim;
+    // tile of (page, head): kPage K rows of D, then kPage V rows of Dv
+    const size_t off = ((size_t)page * Hkv + h) * kPage * (D + Dv) + (is_v ? (size_t)kPage * D : 0) + (size_t)r * dim + d;
+    const float x = is_v ? value[i] : key[i];
+    if (bf16) ((__nv_bfloat16*)pool)[off] = __float2bfloat16_rn(x);
+    else      ((__half*)pool)[off] = __float2half_rn(x);
 }
 
 // Same arithmetic, operation by operation, as the reference's rope_kernel
@@ -95,14 +95,15 @@ void KVCache::release() {
     arena_ = nullptr;
 }
 
-bool KVCache::setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t max_seq, DType dtype, float* k_buf,
+bool KVCache::setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t Dv, uint32_t max_seq, DType dtype, float* k_buf,
                     float* v_buf) {
     release();
-    num_layers_ = L; num_kv_heads_ = Hkv; head_dim_ = D; max_seq_len_ = max_seq;
+    num_layers_ = L; num_kv_heads_ = Hkv; head_dim_ = D; v_head_dim_ = Dv == D ? 0 : Dv; max_seq_len_ = max_seq;
     seq_len_ = 0; planned_len_ = planned_heads_ = -1;
     store_dtype_ = dtype == DType::BF16 ? TK_BF16 : TK_FP16;    // FP32 / FP16 requests are stored as FP16
-    const size_t ref_stride = (size_t)max_seq * Hkv * D;        // floats per layer in the reference's slab
-    const size_t tile = (size_t)Hkv * 2 * kPage * D * 2;         // bytes of one page of one layer
+    const size_t ref_stride = (size_t)max_seq * Hkv * D;        // floats per layer in the reference's K slab
+    const size_t ref_vstride = (size_t)max_seq * Hkv * Dv;      // ... and in its V slab
+    const size_t tile = (size_t)Hkv * kPage * (D + Dv) * 2;      // bytes of one page of one layer
     int pages = (int)((max_seq + kPage - 1) / kPage);
     if (L == 0 || Hkv == 0 || tile == 0 || pages == 0) { KV_LOG("KV cache: bad dimensions"); return false; }
 
@@ -126,8 +127,9 @@ bool KVCache::setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t max_seq, DTyp
         v_layer_stride_ = 64;
     } else {
         k_base_ = k_buf; v_base_ = v_buf;
-        k_bytes_ = v_bytes_ = (size_t)L * ref_stride * sizeof(float);
-        v_layer_stride_ = ref_stride;
+        k_bytes_ = (size_t)L * ref_stride * sizeof(float);
+        v_bytes_ = (size_t)L * ref_vstride * sizeof(float);
+        v_layer_stride_ = ref_vstride;
     }
     k_layer_stride_ = ref_stride;
     const size_t shift = (1024 - ((uintptr_t)k_base_ & 1023)) & 1023;
@@ -140,7 +142,7 @@ bool KVCache::setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t max_seq, DTyp
     tk_kv_config cfg;
     tk_kv_config_default(&cfg);
     cfg.num_layers = (int)L; cfg.num_kv_heads = (int)Hkv; cfg.num_heads = (int)Hkv * 16;  // real count comes with attention_decode
-    cfg.head_dim = (int)D; cfg.page_size = kPage; cfg.dtype = store_dtype_; cfg.io_dtype = store_dtype_;
+    cfg.head_dim = (int)D; cfg.v_head_dim = Dv == D ? 0 : (int)Dv; cfg.page_size = kPage; cfg.dtype = store_dtype_; cfg.io_dtype = store_dtype_;
     cfg.num_pages = pages; cfg.max_seqs = 1; cfg.max_pages_per_seq = pages; cfg.max_step_tokens = kPage;
     int st = tk_kv_create_external(&cfg, arena_, avail, &h_);
     if (st != TK_OK) {
@@ -165,18 +167,19 @@ bool KVCache::setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t max_seq, DTyp
 
 bool KVCache::initialize(uint32_t num_layers, uint32_t num_kv_heads, uint32_t head_dim, uint32_t max_seq_len,
                          DType dtype) {
-    return setup(num_layers, num_kv_heads, head_dim, max_seq_len, dtype, nullptr, nullptr);
+    return setup(num_layers, num_kv_heads, head_dim, head_dim, max_seq_len, dtype, nullptr, nullptr);
 }
 
 bool KVCache::initialize_external(uint32_t num_layers, uint32_t num_kv_heads, uint32_t head_dim,
                                   uint32_t max_seq_len, float* k_buf, float* v_buf) {
     if (!k_buf || !v_buf) return false;                       // reference: kv_cache.cpp:62
-    return setup(num_layers, num_kv_heads, head_dim, max_seq_len, DType::FP32, k_buf, v_buf);
+    return setup(num_layers, num_kv_heads, head_dim, head_dim, max_seq_len, DType::FP32, k_buf, v_buf);
 }
 
-bool KVCache::initialize_external_mla(uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, float*, float*) {
-    KV_LOG("KV cache (MLA): different K and V head dims are not supported by the paged cache");
-    return false;
+bool KVCache::initialize_external_mla(uint32_t num_layers, uint32_t num_kv_heads, uint32_t k_head_dim,
+                                      uint32_t v_head_dim, uint32_t max_seq_len, float* k_buf, float* v_buf) {
+    if (!k_buf || !v_buf) return false;                       // reference: kv_cache.cpp:87
+    return setup(num_layers, num_kv_heads, k_head_dim, v_head_dim, max_seq_len, DType::FP32, k_buf, v_buf);
 }
 
 float* KVCache::k_cache(uint32_t layer) const {
@@ -199,10 +202,10 @@ void KVCache::update(uint32_t layer, int position, const float* key, const float
     if (slot < 0) return;
     void* pool = nullptr;
     if (tk_kv_layer_ptrs(h_, (int)layer, &pool, nullptr, nullptr) != TK_OK) return;
-    const int n = (int)(num_kv_heads_ * head_dim_);
+    const int n = (int)(num_kv_heads_ * (head_dim_ + v_head_dim()));
     compat_update_kernel<<<(n + 255) / 256, 256, 0, stream>>>(pool, key, value, (int)num_kv_heads_, (int)head_dim_,
-                                                              (int)(slot / kPage), (int)(slot % kPage),
-                                                              store_dtype_ == TK_BF16);
+                                                              (int)v_head_dim(), (int)(slot / kPage),
+                                                              (int)(slot % kPage), store_dtype_ == TK_BF16);
     if (position >= seq_len_) seq_len_ = position + 1;         // reference: kv_cache.cpp:148-150
 }
 
@@ -256,9 +259,8 @@ bool KVCache::attend(int layer, const float* q, float* out, int num_heads, int s
 
 namespace cuda {
 
-void attention_decode(const float* q, const float* k_cache, const float* v_cache, float* output, int num_heads,
-                      int num_kv_heads, int head_dim, int seq_len, cudaStream_t stream) {
-    (void)v_cache;
+static void attend_impl(const char* what, const float* q, const float* k_cache, float* output, int num_heads,
+                        int num_kv_heads, int head_dim, int v_head_dim, int seq_len, cudaStream_t stream) {
     KVCache* owner = nullptr;
     int layer = -1;
     {
@@ -272,15 +274,28 @@ void attention_decode(const float* q, const float* k_cache, const float* v_cache
         }
     }
     if (!owner) {
-        KV_LOG("attention_decode: k_cache %p was not returned by a KVCache::k_cache(); nothing launched", (const void*)k_cache);
+        KV_LOG("%s: k_cache %p was not returned by a KVCache::k_cache(); nothing launched", what, (const void*)k_cache);
         return;
     }
-    if ((int)owner->num_kv_heads() != num_kv_heads || (int)owner->head_dim() != head_dim) {
-        KV_LOG("attention_decode: shape (%d kv heads, dim %d) does not match the cache (%u, %u)", num_kv_heads, head_dim,
-               owner->num_kv_heads(), owner->head_dim());
+    if ((int)owner->num_kv_heads() != num_kv_heads || (int)owner->k_head_dim() != head_dim ||
+        (int)owner->v_head_dim() != v_head_dim) {
+        KV_LOG("%s: shape (%d kv heads, dims %d/%d) does not match the cache (%u, %u/%u)", what, num_kv_heads, head_dim,
+               v_head_dim, owner->num_kv_heads(), owner->k_head_dim(), owner->v_head_dim());
         return;
     }
     owner->attend(layer, q, output, num_heads, seq_len, stream);
+}
+
+void attention_decode(const float* q, const float* k_cache, const float* v_cache, float* output, int num_heads,
+                      int num_kv_heads, int head_dim, int seq_len, cudaStream_t stream) {
+    (void)v_cache;
+    attend_impl("attention_decode", q, k_cache, output, num_heads, num_kv_heads, head_dim, head_dim, seq_len, stream);
+}
+
+void attention_decode_mla(const float* q, const float* k_cache, const float* v_cache, float* output, int num_heads,
+                          int num_kv_heads, int k_head_dim, int v_head_dim, int seq_len, cudaStream_t stream) {
+    (void)v_cache;
+    attend_impl("attention_decode_mla", q, k_cache, output, num_heads, num_kv_heads, k_head_dim, v_head_dim, seq_len, stream);
 }
 
 void apply_rope(float* q, float* k, int num_heads, int num_kv_heads, int head_dim, int position, float theta,
