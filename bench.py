@@ -362,7 +362,7 @@ def run_ours(args):
     if fp8 or "Dv" in s:
         unit = (f"decode steps/s (1 step = {B} seqs x {L} layers: append 1 token + paged "
                 + ("GQA attention over the FP8 pool)" if fp8 else "MLA-shape attention)"))
-    simt = args.decode_impl == "simt" or "Dv" in s
+    kernel = "decode_simt_kernel" if args.decode_impl == "simt" else ("decode_mma_mla_kernel" if "Dv" in s else "decode_mma_kernel")
     ratio = TRAFFIC_OVER_ALGORITHMIC[args.workload]
     line = {
         "metric": METRIC, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
@@ -372,7 +372,7 @@ def run_ours(args):
         "hbm_gbs_step": ab["layer"] * L / (ms_per_step * 1e-3) / 1e9,
         "hbm_frac_step": ab["layer"] * L / (ms_per_step * 1e-3) / 1e9 / peak,
         "layers": L, "chunk_tokens": cache.step_chunk_tokens, "work_items_per_layer": cache.step_num_work_items,
-        "roofline": {"bound": "hbm", "kernel": "decode_simt_kernel" if simt else "decode_mma_kernel",
+        "roofline": {"bound": "hbm", "kernel": kernel,
                      "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": (achieved / peak) if achieved else None,
                      "traffic": int(ab["kernel"] * ratio) if ratio else None,

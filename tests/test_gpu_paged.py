@@ -427,12 +427,15 @@ def test_fork_prefix_sharing(dtype):
     assert t.gpu.num_free_pages == 64
 
 
-@pytest.mark.parametrize("heads", [(16, 16), (32, 8)])
-def test_mla_cache_shape(heads):
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("impl", ["mma", "simt"])
+@pytest.mark.parametrize("heads", [(16, 16), (32, 8), (16, 2)])
+def test_mla_cache_shape(heads, impl, dtype):
     """K rows of 192, V rows and outputs of 128 (the MLA cache): append, decode, churn, host entry
-    point; pool bytes bit-exact, attention within tolerance."""
+    point; pool bytes bit-exact, attention within tolerance.  Both kernels: the tensor-core one
+    (groups of up to 8 query heads) and the generic one."""
     H, Hkv = heads
-    t = Twin(2, H, Hkv, 192, 60, 3, 40, dtype="bf16", impl="auto", max_step_tokens=1024, seed=98, Dv=128)
+    t = Twin(2, H, Hkv, 192, 60, 3, 40, dtype=dtype, impl=impl, max_step_tokens=1024, seed=98, Dv=128)
     a, b = t.seq_alloc(), t.seq_alloc()
     t.step([a, b], [300, 17], check_pool=True)
     for i in range(20):
@@ -441,3 +444,27 @@ def test_mla_cache_shape(heads):
     c = t.seq_alloc()
     t.step([c, b], [33, 1], check_pool=True, host_api=True)
     assert t.gpu.cfg.v_head_dim == 128
+
+
+def test_mla_split_kv_long_context_and_chunks():
+    """MLA shape on the tensor-core kernel with several split-KV chunks per sequence, ragged lengths
+    (partly filled last pages) and fused decode-step appends that cross page boundaries."""
+    t = Twin(1, 8, 8, 192, 700, 4, 200, dtype="bf16", impl="mma", max_step_tokens=4096, seed=5, Dv=128,
+             chunk_tokens=256)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [2500, 1, 1023], check_pool=True)
+    for i in range(36):
+        t.step(seqs, [1, 1, 1], check_pool=(i % 12 == 0), fused=True)
+    t.step(seqs[:2], [1, 40], check_pool=True)
+
+
+def test_mla_wide_group_falls_back_to_generic_kernel():
+    """Groups of more than 8 query heads are outside the MLA tensor-core kernel: auto picks the generic one,
+    an explicit request for it is refused."""
+    from titan_engine_b200 import KvError, PagedKVCache
+    t = Twin(1, 16, 1, 192, 20, 1, 20, dtype="fp16", impl="auto", max_step_tokens=256, seed=6, Dv=128)
+    s = t.seq_alloc()
+    t.step([s], [100], check_pool=True)
+    t.step([s], [1], check_pool=True, fused=True)
+    with pytest.raises(KvError):
+        PagedKVCache(1, 16, 1, 192, 20, 1, 20, dtype="fp16", decode_impl="mma", v_head_dim=128)

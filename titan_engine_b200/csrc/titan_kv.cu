@@ -113,7 +113,9 @@ struct tk_kv {
     cudaEvent_t ev_in[2] = {}, ev_compute[2] = {}, ev_out[2] = {};
     uint64_t host_calls = 0;
 
-    std::vector<CUtensorMap> maps;       // one per layer (MMA path)
+    std::vector<CUtensorMap> maps;       // one per layer (MMA path); MLA shape: the K-row view
+    std::vector<CUtensorMap> maps_v;     // MLA shape: the V-row view
+    bool mla_mma = false;
 
     // cold tier (hot_window > 0): pages older than the window live in pinned host memory and are
     // staged back, one layer ahead of use, into a two-slot device ring indexed by cold id
@@ -312,15 +314,23 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_in, cudaStreamNonBlocking));
     CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_out, cudaStreamNonBlocking));
 
-    const bool mma_ok = tk::decode_mma_supported(h->geo);
+    // MLA shape: tensor-core kernel of its own; cold pages stay on the generic kernel
+    h->mla_mma = tk::decode_mma_mla_supported(h->geo) && c.hot_window == 0;
+    const bool mma_ok = tk::decode_mma_supported(h->geo) || h->mla_mma;
     if (c.decode_impl == TK_DECODE_MMA && !mma_ok) {
         release(h);
-        return fail(nullptr, TK_UNSUPPORTED, "decode_impl=MMA needs page_size 16 and head_dim 64/128 (128 for FP8)");
+        return fail(nullptr, TK_UNSUPPORTED, "decode_impl=MMA needs page_size 16 and head_dim 64/128 (128 for FP8), or the "
+                                             "192/128 shape with 16-bit storage, groups of <= 8 heads and no cold tier");
     }
     h->use_mma = mma_ok && c.decode_impl != TK_DECODE_SIMT;
+    h->mla_mma = h->mla_mma && h->use_mma;
     if (h->use_mma) {
         h->maps.resize(c.num_layers);
-        for (int l = 0; l < c.num_layers; l++) CREATE_CUDA(tk::make_pool_tensor_map(h->geo, h->layer(l).pool, &h->maps[l]));
+        if (h->mla_mma) h->maps_v.resize(c.num_layers);
+        for (int l = 0; l < c.num_layers; l++) {
+            if (h->mla_mma) CREATE_CUDA(tk::make_mla_tensor_maps(h->geo, h->layer(l).pool, &h->maps[l], &h->maps_v[l]));
+            else CREATE_CUDA(tk::make_pool_tensor_map(h->geo, h->layer(l).pool, &h->maps[l]));
+        }
     }
     if (c.hot_window > 0) {
         const size_t layer_bytes = (size_t)c.cold_pages * h->page_bytes;
@@ -743,8 +753,12 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     if (mma) {
         // FP8: the 16-bit open pages are items of kind 1 of the same launch
         if (h->dev.n_items > 0) {
-            e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], cold ? &h->stage_maps[slot] : nullptr, h->dev,
-                                      h->d_table, q, h->d_partials, h->d_status, s, &mo, &fa);
+            if (h->mla_mma)
+                e = tk::launch_decode_mma_mla(h->geo, lp, &h->maps[layer], &h->maps_v[layer], h->dev, h->d_table, q,
+                                              h->d_partials, h->d_status, s, &mo, &fa);
+            else
+                e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], cold ? &h->stage_maps[slot] : nullptr, h->dev,
+                                          h->d_table, q, h->d_partials, h->d_status, s, &mo, &fa);
             h->launches++;
         }
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }

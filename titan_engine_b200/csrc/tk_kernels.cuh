@@ -107,6 +107,14 @@ cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUte
                               float* partials, int* status, cudaStream_t s,
                               const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
 
+// The same for the MLA cache shape (K rows 192, V rows 128; 16-bit pools, groups of <= 8 heads).
+bool        decode_mma_mla_supported(const Geometry& g);
+cudaError_t make_mla_tensor_maps(const Geometry& g, void* layer_pool, CUtensorMap* k_map, CUtensorMap* v_map);
+cudaError_t launch_decode_mma_mla(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map,
+                                  const CUtensorMap* v_map, const StepDev& st, const int32_t* page_table,
+                                  const void* q, float* partials, int* status, cudaStream_t s,
+                                  const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
+
 // n FP32 values -> the 16-bit type `dtype` (round to nearest even).
 cudaError_t launch_f32_to_16(const float* src, void* dst, size_t n, int dtype, cudaStream_t s);
 
