@@ -37,7 +37,7 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch divided by its algorithmic
 # bytes, from the ncu captures summarised under profiles/ (taken on a 4-layer / 2-layer cut of the
 # same workload; the traffic is proportional to the tokens read, so it scales to a full launch)
-TRAFFIC_OVER_ALGORITHMIC = {"8b-bf16": 1.0085, "70b-fp8": 1.0108, "mla-bf16": None}
+TRAFFIC_OVER_ALGORITHMIC = {"8b-bf16": 1.0085, "70b-fp8": 1.0108, "mla-bf16": 1.0044}
 
 
 def measured_peak():
@@ -202,6 +202,13 @@ def run_reference(args):
 
 
 def config_dict(ctx, n_gpus):
+    d = _config_dict(ctx, n_gpus)
+    if SHAPE.get("modified"):
+        d["workload"] += f" [MODIFIED for an experiment: {len(ctx)} sequences, context U[{SHAPE['lo']},{SHAPE['hi']}]]"
+    return d
+
+
+def _config_dict(ctx, n_gpus):
     if "Dv" in SHAPE:
         return {"workload": "MLA-shape decode (K rows 192 = nope 128 + rope 64, V rows 128): 128 q heads / 128 kv heads, "
                             "bf16, 16 sequences/GPU at 4096 tokens, page 16, shuffled pool; resident layer subset",
@@ -411,6 +418,9 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--rope", action="store_true", help="also fuse RoPE of q and the new K rows into each layer's call")
+    ap.add_argument("--ctx-range", type=int, nargs=2, default=None, metavar=("LO", "HI"),
+                    help="experiment: context lengths uniform in [LO, HI] instead of the workload's (reported in config)")
+    ap.add_argument("--seqs", type=int, default=0, help="experiment: sequences per GPU instead of the workload's")
     ap.add_argument("--separate", action="store_true", help="call append and decode separately (two entry points)")
     args = ap.parse_args()
     if args.workload == "70b-fp8":
@@ -419,6 +429,10 @@ def main():
     if args.workload == "mla-bf16":
         SHAPE.update(H=128, Hkv=128, D=192, Dv=128, L=8, B=16, lo=4096, hi=4096)
         args.no_cpu = True
+    if args.ctx_range:
+        SHAPE.update(lo=args.ctx_range[0], hi=args.ctx_range[1], modified=True)
+    if args.seqs:
+        SHAPE.update(B=args.seqs, modified=True)
     args.layers = args.layers or SHAPE["L"]
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
