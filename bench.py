@@ -328,7 +328,8 @@ def run_ours(args):
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
-        prof = cache.profile_read() if profile else (0.0, 0)
+        each = cache.profile_read_each(steps * L) if profile else np.zeros(0, np.float32)
+        prof = (float(each.sum()), int(each.size), each)
         if profile:
             cache.profile_enable(0)
         launches = cache.launch_count - n0
@@ -344,7 +345,7 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms, launches, (kern_ms, kern_n) = timed(step_device, args.steps, profile=True)
+    ms, launches, (kern_ms, kern_n, kern_each) = timed(step_device, args.steps, profile=True)
     clocks = sampler.stop() if rank == 0 else None
     cache.device_status()
     ctx_timed = lens_mid + (args.steps + 1) / 2.0               # mean context over the timed steps
@@ -385,6 +386,7 @@ def run_ours(args):
                      "traffic": int(ab["kernel"] * ratio) if ratio else None,
                      "traffic_source": "ncu dram bytes of a reduced-layer capture (profiles/), scaled by tokens",
                      "algorithmic_bytes_per_launch": ab["kernel"], "avg_launch_ms": kern_avg_ms,
+                     "launch_ms_p10_p50_p90": [float(x) for x in np.percentile(kern_each, [10, 50, 90])] if kern_n else None,
                      "launches_timed": kern_n, "peak_source": peak_src},
         "e2e": {"value": world * args.steps / (ms_e2e / 1e3), "unit": unit,
                 "h2d_bytes_per_step": int(L * (hk.numel() + hv.numel() + hq.numel()) * 2),

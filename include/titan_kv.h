@@ -219,6 +219,9 @@ int tk_kv_host_wait(tk_kv* h, void* stream);
  * phases, src/inference/engine.cpp:179-201.) */
 int tk_kv_profile_enable(tk_kv* h, int32_t max_launches);
 int tk_kv_profile_read(tk_kv* h, double* total_ms, int64_t* launches);
+/* The same, one duration per launch: writes up to `cap` kernel times (milliseconds, in launch
+ * order) to ms_out and the number of timed launches to *launches. */
+int tk_kv_profile_read_each(tk_kv* h, float* ms_out, int32_t cap, int32_t* launches);
 
 /* Paged decode attention for callers that cannot allocate device memory (a plugin inside a
  * process whose allocator belongs to someone else, a serving loop that has handed all of

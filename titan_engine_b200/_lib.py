@@ -86,6 +86,7 @@ SIGNATURES = {
     "tk_kv_host_wait": (C.c_int, [_P, _P]),
     "tk_kv_profile_enable": (C.c_int, [_P, C.c_int32]),
     "tk_kv_profile_read": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
+    "tk_kv_profile_read_each": (C.c_int, [_P, C.POINTER(C.c_float), C.c_int32, C.POINTER(C.c_int32)]),
     "tk_paged_decode_static": (C.c_int, [_P, C.c_int32, C.c_int32, _P, C.c_int32, _I32P, C.c_int32, C.c_int32,
                                         C.c_int32, C.c_int32, _P, _P, _P]),
     "tk_kv_device_status": (C.c_int, [_P, _P]),

@@ -82,6 +82,10 @@ struct tk_kv {
     bool host_only = false;
     int device = 0, num_sms = 148;
     bool use_mma = false;
+    // debugging knobs, read from the environment once when the handle is made
+    int env_chunk = 0, env_target = 0;       // TK_CHUNK_TOKENS, TK_TARGET_ITEMS
+    bool separate_combine = false;           // TK_SEPARATE_COMBINE: combine kernel instead of the in-kernel merge
+    bool separate_append = false;            // TK_SEPARATE_APPEND: append launch instead of the fused row store
 
     uint8_t* arena = nullptr;
     bool owns_arena = false;
@@ -233,6 +237,10 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->geo = tk::Geometry{c.num_heads, c.num_kv_heads, c.head_dim, c.page_size, c.dtype, c.io_dtype,
                           c.num_pages, c.max_seqs, c.max_pages_per_seq, c.v_head_dim};
     h->mgr = new tk::PageManager(c.num_pages, c.max_seqs, c.max_pages_per_seq, c.page_size);
+    if (const char* e = getenv("TK_CHUNK_TOKENS")) h->env_chunk = atoi(e);
+    if (const char* e = getenv("TK_TARGET_ITEMS")) h->env_target = atoi(e);
+    h->separate_combine = getenv("TK_SEPARATE_COMBINE") != nullptr;
+    h->separate_append = getenv("TK_SEPARATE_APPEND") != nullptr;
     h->lay = arena_layout(c);
     h->host_only = c.device == TK_DEVICE_NONE;
     h->page_bytes = (size_t)c.num_kv_heads * c.page_size * (c.head_dim + c.v_head_dim) * (c.dtype == TK_FP8_E4M3 ? 1 : 2);
@@ -585,11 +593,9 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
         return fail(h, TK_UNSUPPORTED, "step_begin: an attended-length cap needs 16-bit storage");
     std::lock_guard<std::mutex> lock(h->mgr_mu);
     h->have_step = false;
-    const char* env_chunk = getenv("TK_CHUNK_TOKENS");
     int chunk = h->cfg.chunk_tokens;
-    if (chunk == 0 && env_chunk) chunk = atoi(env_chunk);
-    const char* env_target = getenv("TK_TARGET_ITEMS");
-    int target = env_target ? atoi(env_target) : 8 * h->num_sms;   // ~4 waves of 2 CTAs/SM; larger chunks measured faster
+    if (chunk == 0) chunk = h->env_chunk;
+    int target = h->env_target > 0 ? h->env_target : 8 * h->num_sms;   // ~4 waves of 2 CTAs/SM; larger chunks measured faster
     // the tensor-core kernel keeps one page id per lane per warp: chunk <= 16*4*32 tokens
     int st = h->mgr->plan_step(n_seqs, seq_ids, n_new, h->cfg.num_kv_heads, h->cfg.dtype == TK_FP8_E4M3,
                                chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan, len_cap);
@@ -745,7 +751,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     const bool mma = h->use_mma && h->dev.chunk_tokens <= 2048;
     // the last CTA of each (sequence, kv head) merges the split-KV rows itself; a sequence that
     // attends to nothing has no CTA, so such steps keep the separate combine kernel
-    const bool fused_merge = !h->plan.has_empty_seq && getenv("TK_SEPARATE_COMBINE") == nullptr;
+    const bool fused_merge = !h->plan.has_empty_seq && !h->separate_combine;
     const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype};
     const tk::FuseAppend fa{fuse_k, fuse_v, rope ? h->d_rope_tab : nullptr};
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
@@ -798,7 +804,7 @@ int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, c
     const bool fusable = h->use_mma && h->plan.one_token_steps && h->dev.chunk_tokens <= 2048 &&
                          h->dev.n_tokens > 0 && h->dev.n_seqs > 0 && !h->plan.has_empty_seq &&
                          (h->cfg.dtype != TK_FP8_E4M3 || h->plan.seals.empty()) &&
-                         getenv("TK_SEPARATE_APPEND") == nullptr;
+                         !h->separate_append;
     if (!fusable) {
         int st = tk_kv_append(h, layer, k, v, nullptr, stream);
         if (st != TK_OK) return st;
@@ -819,7 +825,7 @@ int tk_kv_rope_append_decode(tk_kv* h, int32_t layer, const void* k, const void*
         return fail(h, TK_UNSUPPORTED, "rope_append_decode: the MLA shape rotates only its rope dims; rotate before the call");
     const bool fusable = h->use_mma && h->cfg.dtype != TK_FP8_E4M3 && h->plan.one_token_steps &&
                          h->dev.chunk_tokens <= 2048 && h->dev.n_tokens > 0 && h->dev.n_seqs > 0 &&
-                         !h->plan.has_empty_seq && getenv("TK_SEPARATE_APPEND") == nullptr;
+                         !h->plan.has_empty_seq && !h->separate_append;
     if (fusable) {
         const float rope[2] = {theta, scaling};
         // cos/sin of each sequence's newest position: computed once per step, shared by all layers
@@ -942,6 +948,20 @@ int tk_kv_profile_read(tk_kv* h, double* total_ms, int64_t* launches) {
     }
     *total_ms = sum;
     *launches = (int64_t)(h->prof_used / 2);
+    h->prof_used = 0;
+    return TK_OK;
+}
+
+int tk_kv_profile_read_each(tk_kv* h, float* ms_out, int32_t cap, int32_t* launches) {
+    if (!h || h->host_only || !launches || cap < 0 || (cap > 0 && !ms_out)) return TK_INVALID_ARG;
+    int32_t n = 0;
+    for (size_t i = 0; i + 1 < h->prof_used; i += 2, n++) {
+        TK_CUDA(h, cudaEventSynchronize(h->prof_ev[i + 1]));
+        float ms = 0.0f;
+        TK_CUDA(h, cudaEventElapsedTime(&ms, h->prof_ev[i], h->prof_ev[i + 1]));
+        if (n < cap) ms_out[n] = ms;
+    }
+    *launches = n;
     h->prof_used = 0;
     return TK_OK;
 }

@@ -275,6 +275,14 @@ class PagedKVCache:
         self._check(self._lib.tk_kv_profile_read(self._h, C.byref(ms), C.byref(n)))
         return ms.value, n.value
 
+    def profile_read_each(self, cap: int) -> np.ndarray:
+        """-> per-launch decode-kernel milliseconds (launch order) since profile_enable."""
+        buf = np.zeros(max(cap, 1), dtype=np.float32)
+        n = C.c_int32(0)
+        self._check(self._lib.tk_kv_profile_read_each(self._h, buf.ctypes.data_as(C.POINTER(C.c_float)), cap,
+                                                      C.byref(n)))
+        return buf[:min(n.value, cap)].copy()
+
     def device_status(self) -> None:
         self._check(self._lib.tk_kv_device_status(self._h, self._stream()))
 
