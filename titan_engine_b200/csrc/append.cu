@@ -4,7 +4,7 @@
 // Replaces the two cudaMemcpyAsync D2D copies per layer per token of
 // KVCache::update (reference: src/inference/kv_cache.cpp:121-151) with one launch
 // per layer for all tokens of all sequences of the step.  HBM-bound byte movement:
-// every thread moves 16 bytes, rows are 128- or 256-byte contiguous runs.
+// every lane moves 16-byte vectors, rows are 128- to 384-byte contiguous runs.
 #include "tk_kernels.cuh"
 
 #include <cuda_bf16.h>
@@ -45,41 +45,53 @@ __device__ __forceinline__ size_t tile_off(int page, int kvh, int kv, int Hkv, i
     return (((size_t)page * Hkv + kvh) * 2 + kv) * (size_t)ps * D;
 }
 
-// One CTA per token.  16-bit storage: rows go to the pool page the table names.
-// FP8 storage: rows that stay in a still-open page go to the sequence's open page;
-// rows of pages sealed by this step were already consumed by seal_kernel.
-__global__ void __launch_bounds__(256)
+// One warp per token.  The destination row comes from the step plan (tok_dst): 16-bit storage:
+// pool slot page*ps + r; FP8 storage: slot seq*ps + r of the sequence's 16-bit open page, or -1 for
+// rows of pages sealed by this step, which seal_*_kernel consumes.  No dependent page-table lookups
+// stand between a warp and its copies.
+constexpr int kAppendWarps = 8;
+__global__ void __launch_bounds__(kAppendWarps * 32)
 append_rows_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restrict__ page_table,
                    const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
                    int64_t* __restrict__ slots_out) {
-    const int t = blockIdx.x;
-    const int b = st.tok_b[t], pos = st.tok_pos[t];
-    const int seq = st.seq[b];
-    const int page = page_table[(size_t)seq * g.max_pages_per_seq + pos / g.ps];
-    const int r = pos % g.ps;
-    if (threadIdx.x == 0 && slots_out) slots_out[t] = (int64_t)page * g.ps + r;
-
-    uint16_t* base;
-    int tile_page;
-    if (g.dtype == DT_FP8) {
-        const int sealed_end = (st.len[b] / g.ps) * g.ps;
-        if (pos < sealed_end) return;
-        base = (uint16_t*)lp.open_pages;
-        tile_page = seq;                       // open pages are indexed by sequence slot
-    } else {
-        base = (uint16_t*)lp.pool;
-        tile_page = page;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * kAppendWarps + warp;
+    if (t >= st.n_tokens) return;
+    if (slots_out && lane == 0) {                       // pool slot of the token (what a caller would index)
+        const int b = st.tok_b[t], pos = st.tok_pos[t];
+        const int page = page_table[(size_t)st.seq[b] * g.max_pages_per_seq + pos / g.ps];
+        slots_out[t] = (int64_t)page * g.ps + pos % g.ps;
     }
+    const int dst_slot = st.tok_dst[t];
+    if (dst_slot < 0) return;
+    const int tile_page = dst_slot / g.ps, r = dst_slot % g.ps;
+    uint16_t* base = g.dtype == DT_FP8 ? (uint16_t*)lp.open_pages : (uint16_t*)lp.pool;
     const int vk = g.D / 8, vv = g.Dv / 8;     // 16-byte vectors per K row / per V row
     const int n_k = g.Hkv * vk, n_vec = n_k + g.Hkv * vv;
-    for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
+    auto addr = [&](int i, const uint16_t*& src, uint16_t*& dst) {
         const int kv = i >= n_k;
         const int per = kv ? vv : vk, dim = kv ? g.Dv : g.D;
         const int ii = kv ? i - n_k : i;
         const int h = ii / per, c = ii % per;
-        const uint16_t* src = (kv ? v : k) + ((size_t)t * g.Hkv + h) * dim + c * 8;
-        uint16_t* dst = base + tile_offset(g, tile_page, h, kv) + (size_t)r * dim + c * 8;
-        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        src = (kv ? v : k) + ((size_t)t * g.Hkv + h) * dim + c * 8;
+        dst = base + tile_offset(g, tile_page, h, kv) + (size_t)r * dim + c * 8;
+    };
+    for (int i0 = lane; i0 < n_vec; i0 += 4 * 32) {     // four copies in flight per lane
+        uint4 val[4];
+        uint16_t* dst[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + 32 * u;
+            dst[u] = nullptr;
+            if (i < n_vec) {
+                const uint16_t* src;
+                addr(i, src, dst[u]);
+                val[u] = *reinterpret_cast<const uint4*>(src);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+            if (dst[u]) *reinterpret_cast<uint4*>(dst[u]) = val[u];
     }
 }
 
@@ -89,30 +101,106 @@ __device__ __forceinline__ float cvt16(uint16_t x) {
     return __half2float(__ushort_as_half(x));
 }
 
-// FP8 seal: one CTA per (completed page, kv head, K|V).  absmax over the ps*D values,
+// FP8 seal of the tiles (completed page, kv head, K|V): absmax over the ps*D values,
 // scale = max(amax/448, 1e-10), code = e4m3_rn_satfinite(x * (1/scale)): the recipe of
 // quantize_fp4_kernel (reference: src/compute/cuda/fp4.cu:102-113) with the E4M3 maximum.
-// Rows older than the step come from the open page, newer rows from this step's input.
-// Every float op is a single IEEE-rounded operation so codes and scales are bit-exact
-// against a plain C restatement.
+// Rows older than the step come from the open page, newer rows from this step's input; which rows,
+// which physical page and which input token are in the seal item, so nothing is looked up on the
+// way to the loads.  Every float op is a single IEEE-rounded operation (the absmax is taken on the
+// 16-bit values, where a maximum is exact), so codes and scales are bit-exact against a plain C
+// restatement.
 template <bool BF16>
-__global__ void __launch_bounds__(256)
-seal_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restrict__ page_table,
-            const uint16_t* __restrict__ k, const uint16_t* __restrict__ v) {
-    const int4 it = st.seals[blockIdx.x];
-    const int b = it.x, lpage = it.y, old_len = it.z, tok_base = it.w;
-    const int kvh = blockIdx.y >> 1, kv = blockIdx.y & 1;
-    const int seq = st.seq[b];
-    const int page = page_table[(size_t)seq * g.max_pages_per_seq + lpage];
+__device__ __forceinline__ uint32_t abs16x2(uint32_t w) { return w & 0x7FFF7FFFu; }
+// maximum of two packed non-negative 16-bit floats (NaN patterns lose, as with fmaxf)
+template <bool BF16>
+__device__ __forceinline__ uint32_t max16x2(uint32_t a, uint32_t b) {
+    if (BF16) {
+        const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<const uint32_t*>(&r);
+    }
+    const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+// two 16-bit values (low half first) times inv_scale -> two E4M3 codes (low byte first)
+template <bool BF16>
+__device__ __forceinline__ uint32_t quant2(uint32_t w, float inv_scale) {
+    const float lo = __fmul_rn(cvt16<BF16>((uint16_t)w), inv_scale);
+    const float hi = __fmul_rn(cvt16<BF16>((uint16_t)(w >> 16)), inv_scale);
+    return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
+
+// One warp per tile, the tile held in registers (up to 32*VPL vectors of 16 bytes: page 16 x D 128
+// is 256 vectors), one read of the rows, no shared memory; 8 tiles per CTA.
+template <bool BF16, int VPL>
+__global__ void __launch_bounds__(256, VPL <= 8 ? 3 : 2)
+seal_warp_kernel(Geometry g, LayerPtrs lp, StepDev st, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_seal = g.Hkv * 2;
+    const long long tile = (long long)blockIdx.x * 8 + warp;
+    if (tile >= (long long)st.n_seals * per_seal) return;
+    const int4 it = st.seals[tile / per_seal];
+    const int rem = (int)(tile % per_seal);
+    const int seq = it.x, page = it.y, n_old = it.z, tok0 = it.w;
+    const int kvh = rem >> 1, kv = rem & 1;
     const int vec_per_row = g.D / 8;
     const int n_vec = g.ps * vec_per_row;
     const uint16_t* open = (const uint16_t*)lp.open_pages + tile_off(seq, kvh, kv, g.Hkv, g.ps, g.D);
-    const uint16_t* in = kv ? v : k;
+    const uint16_t* in = (kv ? v : k) + ((ptrdiff_t)(tok0 - n_old) * g.Hkv + kvh) * g.D;   // + r * Hkv * D for row r >= n_old
 
+    uint4 raw[VPL];
+    uint32_t mx = 0u;
+#pragma unroll
+    for (int u = 0; u < VPL; u++) {
+        const int i = lane + 32 * u;
+        raw[u] = make_uint4(0, 0, 0, 0);
+        if (i < n_vec) {
+            const int r = i / vec_per_row, c = i % vec_per_row;
+            const uint16_t* src = r < n_old ? open + (size_t)r * g.D : in + (size_t)r * g.Hkv * g.D;
+            raw[u] = *reinterpret_cast<const uint4*>(src + c * 8);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < VPL; u++) {
+        mx = max16x2<BF16>(mx, abs16x2<BF16>(raw[u].x));
+        mx = max16x2<BF16>(mx, abs16x2<BF16>(raw[u].y));
+        mx = max16x2<BF16>(mx, abs16x2<BF16>(raw[u].z));
+        mx = max16x2<BF16>(mx, abs16x2<BF16>(raw[u].w));
+    }
+    float amax = fmaxf(cvt16<BF16>((uint16_t)mx), cvt16<BF16>((uint16_t)(mx >> 16)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));
+
+    float scale = __fdiv_rn(amax, 448.0f);
+    if (scale < 1e-10f) scale = 1e-10f;
+    const float inv_scale = __fdiv_rn(1.0f, scale);
+    if (lane == 0) lp.scales[((size_t)page * g.Hkv + kvh) * 2 + kv] = scale;
+
+    uint8_t* codes = (uint8_t*)lp.pool + tile_off(page, kvh, kv, g.Hkv, g.ps, g.D);
+#pragma unroll
+    for (int u = 0; u < VPL; u++) {
+        const int i = lane + 32 * u;
+        if (i < n_vec) {
+            uint2 out;
+            out.x = quant2<BF16>(raw[u].x, inv_scale) | (quant2<BF16>(raw[u].y, inv_scale) << 16);
+            out.y = quant2<BF16>(raw[u].z, inv_scale) | (quant2<BF16>(raw[u].w, inv_scale) << 16);
+            *reinterpret_cast<uint2*>(codes + (size_t)i * 8) = out;
+        }
+    }
+}
+
+// Tiles too large for a warp's registers: one CTA per tile, two passes over the rows.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+seal_kernel(Geometry g, LayerPtrs lp, StepDev st, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v) {
+    const int4 it = st.seals[blockIdx.x];
+    const int seq = it.x, page = it.y, n_old = it.z, tok0 = it.w;
+    const int kvh = blockIdx.y >> 1, kv = blockIdx.y & 1;
+    const int vec_per_row = g.D / 8;
+    const int n_vec = g.ps * vec_per_row;
+    const uint16_t* open = (const uint16_t*)lp.open_pages + tile_off(seq, kvh, kv, g.Hkv, g.ps, g.D);
+    const uint16_t* in = (kv ? v : k) + ((ptrdiff_t)(tok0 - n_old) * g.Hkv + kvh) * g.D;
     auto row_src = [&](int r) -> const uint16_t* {
-        const int pos = lpage * g.ps + r;
-        if (pos < old_len) return open + (size_t)r * g.D;
-        return in + ((size_t)(tok_base + pos - old_len) * g.Hkv + kvh) * g.D;
+        return r < n_old ? open + (size_t)r * g.D : in + (size_t)r * g.Hkv * g.D;
     };
 
     float amax = 0.0f;
@@ -138,16 +226,24 @@ seal_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restrict__ pa
 
     uint8_t* codes = (uint8_t*)lp.pool + tile_off(page, kvh, kv, g.Hkv, g.ps, g.D);
     for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
-        const int r = i / vec_per_row, c = i % vec_per_row;
-        const uint4 raw = *reinterpret_cast<const uint4*>(row_src(r) + c * 8);
-        const uint16_t* e = reinterpret_cast<const uint16_t*>(&raw);
-        uint8_t out[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++)
-            out[j] = (uint8_t)__nv_cvt_float_to_fp8(__fmul_rn(cvt16<BF16>(e[j]), inv_scale),
-                                                    __NV_SATFINITE, __NV_E4M3);
-        *reinterpret_cast<uint2*>(codes + (size_t)r * g.D + c * 8) = *reinterpret_cast<const uint2*>(out);
+        const uint4 raw = *reinterpret_cast<const uint4*>(row_src(i / vec_per_row) + (i % vec_per_row) * 8);
+        uint2 out;
+        out.x = quant2<BF16>(raw.x, inv_scale) | (quant2<BF16>(raw.y, inv_scale) << 16);
+        out.y = quant2<BF16>(raw.z, inv_scale) | (quant2<BF16>(raw.w, inv_scale) << 16);
+        *reinterpret_cast<uint2*>(codes + (size_t)i * 8) = out;
     }
+}
+
+template <bool BF16>
+cudaError_t launch_seal(const Geometry& g, const LayerPtrs& lp, const StepDev& st, const uint16_t* k,
+                        const uint16_t* v, cudaStream_t s) {
+    const int n_vec = g.ps * (g.D / 8);
+    const long long tiles = (long long)st.n_seals * g.Hkv * 2;
+    const unsigned grid = (unsigned)((tiles + 7) / 8);
+    if (n_vec <= 256)      seal_warp_kernel<BF16, 8><<<grid, 256, 0, s>>>(g, lp, st, k, v);
+    else if (n_vec <= 512) seal_warp_kernel<BF16, 16><<<grid, 256, 0, s>>>(g, lp, st, k, v);
+    else                   seal_kernel<BF16><<<dim3(st.n_seals, g.Hkv * 2), 256, 0, s>>>(g, lp, st, k, v);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_append(const Geometry& g, const LayerPtrs& lp, const StepDev& st,
@@ -156,17 +252,14 @@ cudaError_t launch_append(const Geometry& g, const LayerPtrs& lp, const StepDev&
     *n_launches = 0;
     if (st.n_tokens <= 0) return cudaSuccess;
     if (g.dtype == DT_FP8 && st.n_seals > 0) {
-        dim3 grid(st.n_seals, g.Hkv * 2);
-        if (g.io_dtype == DT_BF16)
-            seal_kernel<true><<<grid, 256, 0, s>>>(g, lp, st, page_table, (const uint16_t*)k, (const uint16_t*)v);
-        else
-            seal_kernel<false><<<grid, 256, 0, s>>>(g, lp, st, page_table, (const uint16_t*)k, (const uint16_t*)v);
+        cudaError_t e = g.io_dtype == DT_BF16
+            ? launch_seal<true>(g, lp, st, (const uint16_t*)k, (const uint16_t*)v, s)
+            : launch_seal<false>(g, lp, st, (const uint16_t*)k, (const uint16_t*)v, s);
         (*n_launches)++;
-        cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    append_rows_kernel<<<st.n_tokens, 256, 0, s>>>(g, lp, st, page_table, (const uint16_t*)k,
-                                                   (const uint16_t*)v, slots_out);
+    append_rows_kernel<<<(st.n_tokens + kAppendWarps - 1) / kAppendWarps, kAppendWarps * 32, 0, s>>>(
+        g, lp, st, page_table, (const uint16_t*)k, (const uint16_t*)v, slots_out);
     (*n_launches)++;
     return cudaGetLastError();
 }

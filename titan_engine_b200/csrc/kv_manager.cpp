@@ -277,7 +277,7 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     plan->seq.assign(seqs, seqs + n_seqs);
     plan->len.resize(n_seqs);
     plan->chunk_base.assign(n_seqs + 1, 0);
-    plan->tok_b.clear(); plan->tok_pos.clear(); plan->items.clear(); plan->seals.clear();
+    plan->tok_b.clear(); plan->tok_pos.clear(); plan->tok_dst.clear(); plan->items.clear(); plan->seals.clear();
     plan->evictions.clear();
     plan->new_tok.assign(n_seqs, -1);
     plan->one_token_steps = true;
@@ -300,10 +300,20 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         if (add == 1) plan->new_tok[i] = tok_base;
         if (add > 1) plan->one_token_steps = false;
         if (len == 0) plan->has_empty_seq = true;
-        for (int p = old_len; p < full_len; p++) { plan->tok_b.push_back(i); plan->tok_pos.push_back(p); }
+        const int sealed_end = (full_len / ps) * ps;    // FP8: rows below it are in sealed pages after this step
+        for (int p = old_len; p < full_len; p++) {
+            plan->tok_b.push_back(i);
+            plan->tok_pos.push_back(p);
+            if (fp8) plan->tok_dst.push_back(p < sealed_end ? -1 : s * ps + p % ps);
+            else plan->tok_dst.push_back(table_[(size_t)s * max_pages_per_seq_ + p / ps] * ps + p % ps);
+        }
         if (fp8)
             for (int lp = old_len / ps; (lp + 1) * ps <= full_len; lp++)
-                plan->seals.push_back({i, lp, old_len, tok_base});
+            {
+                const int n_old = std::min(ps, std::max(0, old_len - lp * ps));
+                plan->seals.push_back({s, table_[(size_t)s * max_pages_per_seq_ + lp], n_old,
+                                       tok_base + lp * ps + n_old - old_len});
+            }
         int pool_tokens = fp8 ? (len / ps) * ps : len;
         int n_chunks = (pool_tokens + chunk - 1) / chunk;
         for (int c = 0; c < n_chunks; c++)

@@ -27,10 +27,10 @@ struct WorkItem {      // one CTA's worth of decode work; mirrors the device int
 };
 
 struct SealItem {      // FP8: one logical page completed by this step
-    int32_t b;         // index into the step's sequence list
-    int32_t lpage;     // logical page
-    int32_t old_len;   // sequence length before the step
-    int32_t tok_base;  // index of the sequence's first new token in the step's token list
+    int32_t seq;       // sequence slot (its open page holds the rows that predate the step)
+    int32_t page;      // physical page that receives the codes
+    int32_t n_old;     // rows [0, n_old) come from the open page, the rest from this step's input
+    int32_t tok0;      // index in the step's token list of the token that is row n_old
 };
 
 struct Eviction {      // a page that moved from the device pool to the host (cold) pool
@@ -45,6 +45,7 @@ struct StepPlan {
     std::vector<int32_t> chunk_base; // [n_seqs+1] prefix sum of partial rows per sequence
     std::vector<int32_t> tok_b;      // [n_tokens] index into seq[]
     std::vector<int32_t> tok_pos;    // [n_tokens] position inside the sequence
+    std::vector<int32_t> tok_dst;    // [n_tokens] destination row: pool slot, FP8: open-page slot or -1 (sealed)
     std::vector<int32_t> new_tok;    // [n_seqs] row of the sequence's single new token, or -1
     bool one_token_steps = false;    // every sequence appends at most one token (a decode step)
     bool has_empty_seq = false;      // some sequence attends to zero tokens

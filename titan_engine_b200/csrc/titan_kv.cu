@@ -255,7 +255,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->max_seals = c.max_step_tokens / c.page_size + c.max_seqs;
 
     // one buffer holds every per-step array; sections are 16-byte aligned
-    size_t ints = 4 * (size_t)c.max_seqs + 4 + 12 + 2 * (size_t)c.max_step_tokens + 8 +
+    size_t ints = 4 * (size_t)c.max_seqs + 4 + 12 + 3 * (size_t)c.max_step_tokens + 12 +
                   4 * (size_t)h->max_items + 4 * (size_t)h->max_seals + 2 * (size_t)kMaxDelta + 32;
     h->step_bytes = align_up(ints * 4, 256);
 
@@ -408,7 +408,7 @@ int prefetch_layer(tk_kv* h, int layer, bool ahead) {
 }
 
 struct Sections {       // offsets (in int32 units) of the arrays inside a step buffer
-    size_t seq, len, chunk_base, new_tok, tok_b, tok_pos, items, seals, delta, end;
+    size_t seq, len, chunk_base, new_tok, tok_b, tok_pos, tok_dst, items, seals, delta, end;
 };
 Sections sections(int n_seqs, int n_tokens, int n_items, int n_seals, int n_delta) {
     auto a4 = [](size_t x) { return (x + 3) / 4 * 4; };
@@ -420,6 +420,7 @@ Sections sections(int n_seqs, int n_tokens, int n_items, int n_seals, int n_delt
     s.new_tok = o;    o = a4(o + n_seqs);
     s.tok_b = o;      o = a4(o + n_tokens);
     s.tok_pos = o;    o = a4(o + n_tokens);
+    s.tok_dst = o;    o = a4(o + n_tokens);
     s.items = o;      o = a4(o + 4 * (size_t)n_items);
     s.seals = o;      o = a4(o + 4 * (size_t)n_seals);
     s.delta = o;      o = a4(o + 2 * (size_t)n_delta);
@@ -649,6 +650,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     if (n_tok) {
         memcpy(w + sec.tok_b, p.tok_b.data(), 4 * (size_t)n_tok);
         memcpy(w + sec.tok_pos, p.tok_pos.data(), 4 * (size_t)n_tok);
+        memcpy(w + sec.tok_dst, p.tok_dst.data(), 4 * (size_t)n_tok);
     }
     if (n_items) memcpy(w + sec.items, p.items.data(), 16 * (size_t)n_items);
     if (n_seals) memcpy(w + sec.seals, p.seals.data(), 16 * (size_t)n_seals);
@@ -663,7 +665,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     tk::StepDev& dv = h->dev;
     dv.seq = d + sec.seq; dv.len = d + sec.len; dv.chunk_base = d + sec.chunk_base;
     dv.new_tok = d + sec.new_tok;
-    dv.tok_b = d + sec.tok_b; dv.tok_pos = d + sec.tok_pos;
+    dv.tok_b = d + sec.tok_b; dv.tok_pos = d + sec.tok_pos; dv.tok_dst = d + sec.tok_dst;
     dv.items = (const int4*)(d + sec.items); dv.seals = (const int4*)(d + sec.seals);
     dv.n_seqs = n_seqs; dv.n_tokens = n_tok; dv.n_items = n_items; dv.n_seals = n_seals;
     dv.chunk_tokens = p.chunk_tokens;

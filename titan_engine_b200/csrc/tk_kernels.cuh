@@ -43,8 +43,10 @@ struct StepDev {
     const int32_t* chunk_base;  // [n_seqs+1] first partial row of each sequence
     const int32_t* tok_b;       // [n_tokens] index into seq[]
     const int32_t* tok_pos;     // [n_tokens]
+    const int32_t* tok_dst;     // [n_tokens] row the token is stored to: page*ps + r of the pool (16-bit
+                                //   storage), seq*ps + r of the open pages (FP8), -1 = sealed by this step
     const int4*    items;       // [n_items] (b, chunk, kvh, kind)
-    const int4*    seals;       // [n_seals] (b, logical page, old_len, tok_base)
+    const int4*    seals;       // [n_seals] (seq slot, physical page, rows from the open page, token of the next row)
     const int32_t* new_tok;     // [n_seqs] row of the sequence's single new token in k/v, or -1
     int n_seqs, n_tokens, n_items, n_seals, chunk_tokens;
 };
