@@ -197,6 +197,43 @@ int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial,
  * out [n_rows][D] in out_dtype (TK_FP16 / TK_BF16 / TK_FP32). */
 int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int32_t head_dim,
                         void* out, int32_t out_dtype, void* stream);
+
+/* ---- cross-GPU exchange of partials over peer memory, fused with the combine -----------------
+ * One process per GPU.  Every rank owns a mailbox in its device memory; tk_peer_export gives the
+ * CUDA IPC handle of it, the ranks swap handles over whatever transport they have, and
+ * tk_peer_connect maps the peers' mailboxes.  tk_peer_exchange_combine then is ONE kernel that
+ * stores this rank's partial rows [n_rows][dv+2] into every peer's mailbox (plain NVLink peer
+ * stores), publishes a flag per peer, waits - with a limit - for the peers' flags and writes the
+ * log-sum-exp combine of all ranks' rows (rank order, same arithmetic as tk_combine_partials) to
+ * out [n_rows][dv].  Calls of one tk_peer must be ordered on one stream and made by every rank
+ * the same number of times.  A peer whose rows do not arrive within the limit (default 2 s)
+ * leaves `out` unwritten and makes tk_peer_status return TK_TIMEOUT.  The reference runs on one
+ * GPU (src/memory/memory_manager.cpp:15) and has no counterpart. */
+typedef struct tk_peer tk_peer;
+#define TK_PEER_HANDLE_BYTES 64
+int tk_peer_create(int32_t rank, int32_t world, int32_t max_rows, int32_t row_floats, int32_t device,
+                   tk_peer** out);                        /* row_floats = dv + 2; world <= 16 */
+void tk_peer_destroy(tk_peer* p);
+const char* tk_peer_last_error(const tk_peer* p);
+int tk_peer_export(tk_peer* p, void* handle_out);         /* TK_PEER_HANDLE_BYTES bytes */
+int tk_peer_connect(tk_peer* p, const void* handles);     /* world x TK_PEER_HANDLE_BYTES, indexed by rank */
+/* Ranks that live in one process (or a test) connect with the mailbox addresses themselves. */
+void* tk_peer_mailbox(const tk_peer* p);
+size_t tk_peer_mailbox_bytes(const tk_peer* p);
+int tk_peer_connect_ptrs(tk_peer* p, void* const* mailboxes);
+int tk_peer_set_wait_limit_ms(tk_peer* p, int32_t ms);
+int tk_peer_exchange_combine(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* out,
+                             int32_t out_dtype, void* stream);
+/* The two halves as launches of their own (send early, combine later; also how ranks that share
+ * a GPU must be driven: all sends first, so that no kernel waits for a later launch). */
+int tk_peer_send(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* stream);
+int tk_peer_recv_combine(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* out,
+                         int32_t out_dtype, void* stream);
+int tk_peer_status(tk_peer* p, void* stream);
+/* tk_kv_decode_partial of one layer followed by tk_peer_exchange_combine of its rows, in one call:
+ * out [n_seqs][H][v_head_dim] in the handle's io dtype holds the attention over every rank's tokens. */
+int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer, void* out, void* stream);
+
 /* update + attention_decode of one layer with HOST buffers (pageable or pinned):
  * copies k, v, q in, runs append and decode, copies out back, and waits for it. */
 int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,

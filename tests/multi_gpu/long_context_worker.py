@@ -29,6 +29,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--hot-window", type=int, default=0,
                     help="most recent tokens kept in HBM; older pages live in pinned host memory (0 = all in HBM)")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
+                    help="nccl: all-gather + combine kernel; peer: one kernel storing into the peers' mailboxes over "
+                         "NVLink, waiting for theirs and combining")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -52,9 +55,22 @@ def main():
         cache.set_tail(s, n - hi)                      # tokens held by later ranks push this rank's pages out
     torch.cuda.synchronize()
     cache.step_begin([s], None)                        # evicts what lies outside the window
-    dec = D.LongContextDecoder(cache.decode_partial, lambda st: D.combine_partials(st, torch.bfloat16))
+    ex = D.PeerExchange(H, Dh + 2) if args.exchange == "peer" else None
+    dec = D.LongContextDecoder(cache.decode_partial, lambda st: D.combine_partials(st, torch.bfloat16), exchange=ex,
+                               fused_fn=cache.decode_exchange)
     out = dec.decode(0, q)
     torch.cuda.synchronize()
+    if ex is not None:
+        ex.status()
+        two_calls = D.LongContextDecoder(cache.decode_partial, None, exchange=ex).decode(0, q)   # partial, then exchange
+        torch.cuda.synchronize()
+        assert torch.equal(two_calls, out)
+        # the all-gather route must give the same bytes: same rows, same arithmetic, same order
+        ref = D.LongContextDecoder(cache.decode_partial, lambda st: D.combine_partials(st, torch.bfloat16)).decode(0, q)
+        torch.cuda.synchronize()
+        same_as_nccl = bool(torch.equal(ref, out))
+    else:
+        same_as_nccl = True
 
     ok, err = True, 0.0
     if rank == 0:
@@ -65,7 +81,7 @@ def main():
         whole.step_begin([ws], None)
         want = whole.decode(0, q).float()
         err = float((out.float() - want).abs().max())
-        ok = bool(torch.allclose(out.float(), want, rtol=2e-3, atol=1e-2)) and float(want.abs().max()) > 0
+        ok = bool(torch.allclose(out.float(), want, rtol=2e-3, atol=1e-2)) and float(want.abs().max()) > 0 and same_as_nccl
         whole.close()
     del full
 
@@ -82,19 +98,25 @@ def main():
         step()
     e1.record()
     torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    if ex is not None:
+        ex.status()
     t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         ms_layer = float(t.item()) / args.steps / L
         kv_bytes = n * Hkv * Dh * 2 * 2
         print(json.dumps({"workload": f"one {n}-token sequence over {world} GPUs, 8B head shape, bf16",
-                          "ok": ok, "max_abs_err_vs_single_gpu": err, "n_gpus": world, "layers": L,
+                          "ok": ok, "exchange": args.exchange, "same_bytes_as_all_gather_route": same_as_nccl,
+                          "max_abs_err_vs_single_gpu": err, "n_gpus": world, "layers": L,
                           "us_per_layer": ms_layer * 1e3, "aggregate_kv_gbs": kv_bytes / (ms_layer * 1e-3) / 1e9,
                           "exchange_bytes_per_rank_per_layer": H * (Dh + 2) * 4,
                           "hot_window": args.hot_window, "rank0_stats": {k: v for k, v in cache.stats().items()
                                                                           if k in ("pages_cold", "evictions", "prefetch_hits",
                                                                                    "prefetch_misses", "bytes_h2d", "bytes_d2h")}}),
               flush=True)
+    if ex is not None:
+        torch.cuda.synchronize(); dist.barrier()
+        ex.close()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
 

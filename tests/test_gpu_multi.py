@@ -29,6 +29,16 @@ def test_long_context_split_over_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_long_context_peer_exchange_over_two_gpus():
+    """The exchange as one kernel over peer memory (CUDA IPC mailboxes): same bytes as the all-gather route."""
+    res = _torchrun(2, "tests/multi_gpu/long_context_worker.py", "--tokens", "32768", "--layers", "2", "--steps", "3",
+                    "--exchange", "peer")
+    assert res.returncode == 0, res.stdout + res.stderr
+    line = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["ok"] and line["n_gpus"] == 2 and line["exchange"] == "peer" and line["same_bytes_as_all_gather_route"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_long_context_with_cold_tier_over_two_gpus():
     # hot window of 16384 over 32768 tokens: rank 0's pages live in pinned host memory
     res = _torchrun(2, "tests/multi_gpu/long_context_worker.py", "--tokens", "32768", "--layers", "3", "--steps", "3",

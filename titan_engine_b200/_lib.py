@@ -14,6 +14,7 @@ TK_OK, TK_INVALID_ARG, TK_OUT_OF_PAGES, TK_CUDA_ERROR, TK_TIMEOUT, TK_OUT_OF_SEQ
 TK_FP32, TK_FP16, TK_BF16, TK_FP8_E4M3 = 0, 1, 2, 3
 TK_DECODE_AUTO, TK_DECODE_SIMT, TK_DECODE_MMA = 0, 1, 2
 TK_DEVICE_NONE = -2
+TK_PEER_HANDLE_BYTES = 64
 
 
 class KvConfig(C.Structure):
@@ -84,6 +85,20 @@ SIGNATURES = {
     "tk_kv_append_decode_host": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
     "tk_kv_append_decode_host_async": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),
     "tk_kv_host_wait": (C.c_int, [_P, _P]),
+    "tk_peer_create": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.POINTER(_P)]),
+    "tk_peer_destroy": (None, [_P]),
+    "tk_peer_last_error": (C.c_char_p, [_P]),
+    "tk_peer_export": (C.c_int, [_P, C.c_void_p]),
+    "tk_peer_connect": (C.c_int, [_P, C.c_void_p]),
+    "tk_peer_mailbox": (C.c_void_p, [_P]),
+    "tk_peer_mailbox_bytes": (C.c_size_t, [_P]),
+    "tk_peer_connect_ptrs": (C.c_int, [_P, C.POINTER(C.c_void_p)]),
+    "tk_peer_set_wait_limit_ms": (C.c_int, [_P, C.c_int32]),
+    "tk_peer_exchange_combine": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
+    "tk_peer_send": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "tk_peer_recv_combine": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
+    "tk_peer_status": (C.c_int, [_P, C.c_void_p]),
+    "tk_kv_decode_exchange": (C.c_int, [_P, C.c_int32, C.c_void_p, _P, C.c_void_p, C.c_void_p]),
     "tk_kv_profile_enable": (C.c_int, [_P, C.c_int32]),
     "tk_kv_profile_read": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "tk_kv_profile_read_each": (C.c_int, [_P, C.POINTER(C.c_float), C.c_int32, C.POINTER(C.c_int32)]),

@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtitan_kv.so")
-SOURCES = ["titan_kv.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_mma_mla.cu", "decode_static.cu", "rope_append.cu",
+SOURCES = ["titan_kv.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_mma_mla.cu", "decode_static.cu", "peer_exchange.cu", "rope_append.cu",
            "kv_manager.cpp", "kv_scheduler.cpp", "sched_abi.cpp", "compat/kv_cache_compat.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "-Xcompiler", "-fPIC", "-shared"]

@@ -119,6 +119,7 @@ struct tk_kv {
 
     std::vector<CUtensorMap> maps;       // one per layer (MMA path); MLA shape: the K-row view
     std::vector<CUtensorMap> maps_v;     // MLA shape: the V-row view
+    float* d_xpartial = nullptr;         // this rank's merged partial rows for tk_kv_decode_exchange
     bool mla_mma = false;
 
     // cold tier (hot_window > 0): pages older than the window live in pinned host memory and are
@@ -184,6 +185,7 @@ void release(tk_kv* h) {
         if (h->owns_arena && h->arena) cudaFree(h->arena);
         if (h->d_table) cudaFree(h->d_table);
         if (h->d_partials) cudaFree(h->d_partials);
+        if (h->d_xpartial) cudaFree(h->d_xpartial);
         if (h->d_status) cudaFree(h->d_status);
         if (h->d_counters) cudaFree(h->d_counters);
         if (h->d_step) cudaFree(h->d_step);
@@ -851,6 +853,25 @@ int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, voi
 }
 int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial, void* stream) {
     return decode_impl(h, layer, q, nullptr, partial, (cudaStream_t)stream);
+}
+
+// decode_partial + the peer exchange of one layer in one call: two launches, no collective.
+int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer, void* out, void* stream) {
+    if (!h || !peer || !out) return TK_INVALID_ARG;
+    if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode_exchange: handle has no device (bookkeeping only)");
+    if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode_exchange: no step in progress (call tk_kv_step_begin)");
+    const size_t need = (size_t)h->cfg.max_seqs * h->cfg.num_heads * (h->cfg.v_head_dim + 2) * sizeof(float);
+    if (!h->d_xpartial) {                                   // first use only
+        TK_CUDA(h, cudaSetDevice(h->device));
+        TK_CUDA(h, cudaMalloc((void**)&h->d_xpartial, need));
+    }
+    int st = decode_impl(h, layer, q, nullptr, h->d_xpartial, (cudaStream_t)stream);
+    if (st != TK_OK) return st;
+    st = tk_peer_exchange_combine(peer, h->d_xpartial, h->dev.n_seqs * h->geo.H, h->cfg.v_head_dim, out,
+                                  h->cfg.io_dtype, stream);
+    h->launches++;
+    if (st != TK_OK) return fail(h, st, "decode_exchange: %s", tk_peer_last_error(peer));
+    return TK_OK;
 }
 
 int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int32_t head_dim, void* out,

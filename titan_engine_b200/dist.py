@@ -6,8 +6,10 @@ how the path shards:
 
   * batched decode — by sequence (default) or by kv head: independent units, no collective;
   * one very long sequence — contiguous page-aligned token ranges per rank; every rank computes
-    the merged, unnormalised (o, m, l) of its range, ONE all-gather of [n_seqs][H][D+2] floats
-    per layer exchanges them, and the log-sum-exp combine kernel consumes the gathered buffer.
+    the merged, unnormalised (o, m, l) of its range; per layer either ONE kernel stores the rows
+    into every peer's memory over NVLink, waits for the peers' rows and combines (PeerExchange),
+    or ONE all-gather of [n_seqs][H][D+2] floats exchanges them and the log-sum-exp combine
+    kernel consumes the gathered buffer (portable route).
 
 Nothing here computes attention: partials and the combine come from libtitan_kv.so (or, in the
 CPU tests of this logic, from the oracle through the same two callables).
@@ -76,13 +78,22 @@ class LongContextDecoder:
     the current stream between them, so there is no host synchronisation in a layer.
     """
 
-    def __init__(self, partial_fn: Callable, combine_fn: Callable, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, partial_fn: Callable, combine_fn: Callable, group: Optional[dist.ProcessGroup] = None,
+                 exchange: Optional["PeerExchange"] = None, out_dtype: torch.dtype = torch.bfloat16,
+                 fused_fn: Optional[Callable] = None):
+        """exchange: swap rows over peer memory instead of the all-gather.  fused_fn(layer, q, exchange)
+        (PagedKVCache.decode_exchange) does partial + exchange in one library call."""
         self.partial_fn, self.combine_fn, self.group = partial_fn, combine_fn, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.exchange, self.out_dtype, self.fused_fn = exchange, out_dtype, fused_fn
         self._gathered = None
 
     def decode(self, layer: int, q: torch.Tensor) -> torch.Tensor:
+        if self.exchange is not None and self.fused_fn is not None:
+            return self.fused_fn(layer, q, self.exchange)
         part = self.partial_fn(layer, q)
+        if self.exchange is not None:                     # peer stores + combine in one kernel, no collective
+            return self.exchange.exchange_combine(part, self.out_dtype)
         if self.world == 1:
             return self.combine_fn(part.unsqueeze(0))
         if self._gathered is None or self._gathered.shape[1:] != part.shape or self._gathered.device != part.device:
@@ -105,3 +116,97 @@ def combine_partials(stacked: torch.Tensor, out_dtype: torch.dtype = torch.bfloa
     if st != L.TK_OK:
         raise RuntimeError(f"tk_combine_partials failed with status {st}")
     return out
+
+
+class PeerExchange:
+    """Mailboxes in every rank's device memory, mapped into every other rank through CUDA IPC; the
+    handles travel over torch.distributed (any backend).  exchange_combine(partial) is one kernel:
+    peer stores of this rank's rows, flags, bounded wait for the peers' rows, log-sum-exp combine."""
+
+    def __init__(self, max_rows: int, row_floats: int, group: Optional[dist.ProcessGroup] = None,
+                 rank: Optional[int] = None, world: Optional[int] = None, connect: bool = True):
+        import ctypes as C
+        from . import _lib as L
+        self._L, self._C = L, C
+        self._lib = L.lib()
+        if rank is None:
+            rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if world is None:
+            world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank, self.world, self.group = rank, world, group
+        self.row_floats = row_floats
+        self._h = C.c_void_p()
+        st = self._lib.tk_peer_create(rank, world, max_rows, row_floats, torch.cuda.current_device(), C.byref(self._h))
+        if st != L.TK_OK:
+            raise RuntimeError(f"tk_peer_create failed with status {st}")
+        if connect and world > 1:
+            self.connect()
+
+    def _check(self, st: int) -> None:
+        if st != self._L.TK_OK:
+            msg = self._lib.tk_peer_last_error(self._h)
+            raise RuntimeError(f"peer exchange: status {st}: {msg.decode() if msg else ''}")
+
+    def connect(self) -> None:
+        """Swap CUDA IPC handles with the other ranks of the group and map their mailboxes."""
+        C = self._C
+        mine = C.create_string_buffer(self._L.TK_PEER_HANDLE_BYTES)
+        self._check(self._lib.tk_peer_export(self._h, mine))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(mine.raw), group=self.group)
+        self._check(self._lib.tk_peer_connect(self._h, b"".join(handles)))
+        dist.barrier(group=self.group)                    # every rank has mapped every mailbox
+
+    def connect_local(self, others: Sequence["PeerExchange"]) -> None:
+        """Ranks living in one process: `others` indexed by rank (this rank's own entry is ignored)."""
+        C = self._C
+        arr = (C.c_void_p * self.world)()
+        for r, o in enumerate(others):
+            arr[r] = self._lib.tk_peer_mailbox(o._h)
+        self._check(self._lib.tk_peer_connect_ptrs(self._h, arr))
+
+    def set_wait_limit_ms(self, ms: int) -> None:
+        self._check(self._lib.tk_peer_set_wait_limit_ms(self._h, ms))
+
+    def _code(self, dtype: torch.dtype) -> int:
+        L = self._L
+        return {torch.float32: L.TK_FP32, torch.float16: L.TK_FP16, torch.bfloat16: L.TK_BF16}[dtype]
+
+    def _rows(self, partial: torch.Tensor):
+        assert partial.is_cuda and partial.dtype == torch.float32 and partial.is_contiguous()
+        assert partial.shape[-1] == self.row_floats
+        return partial.numel() // self.row_floats, self.row_floats - 2
+
+    def exchange_combine(self, partial: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        n_rows, dv = self._rows(partial)
+        out = torch.empty(tuple(partial.shape[:-1]) + (dv,), dtype=out_dtype, device=partial.device)
+        self._check(self._lib.tk_peer_exchange_combine(self._h, partial.data_ptr(), n_rows, dv, out.data_ptr(),
+                                                       self._code(out_dtype), torch.cuda.current_stream().cuda_stream))
+        return out
+
+    def send(self, partial: torch.Tensor) -> None:
+        n_rows, dv = self._rows(partial)
+        self._check(self._lib.tk_peer_send(self._h, partial.data_ptr(), n_rows, dv,
+                                           torch.cuda.current_stream().cuda_stream))
+
+    def recv_combine(self, partial: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        n_rows, dv = self._rows(partial)
+        out = torch.empty(tuple(partial.shape[:-1]) + (dv,), dtype=out_dtype, device=partial.device)
+        self._check(self._lib.tk_peer_recv_combine(self._h, partial.data_ptr(), n_rows, dv, out.data_ptr(),
+                                                   self._code(out_dtype), torch.cuda.current_stream().cuda_stream))
+        return out
+
+    def status(self) -> None:
+        """Raises if a device-side wait of this exchange gave up (a peer never published its rows)."""
+        self._check(self._lib.tk_peer_status(self._h, torch.cuda.current_stream().cuda_stream))
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.tk_peer_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

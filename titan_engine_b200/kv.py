@@ -247,6 +247,17 @@ class PagedKVCache:
         self._check(self._lib.tk_kv_decode_partial(self._h, layer, q.data_ptr(), partial.data_ptr(), self._stream()))
         return partial
 
+    def decode_exchange(self, layer: int, q: torch.Tensor, exchange, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Attention over the tokens of EVERY rank of `exchange` (a dist.PeerExchange): this rank's
+        partial rows, then one kernel that swaps rows with the peers over NVLink and combines."""
+        self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
+        if out is None:
+            out = torch.empty(self._n_seqs, self.cfg.num_heads, self.cfg.v_head_dim, dtype=self.io_torch_dtype,
+                              device=self.device)
+        self._check(self._lib.tk_kv_decode_exchange(self._h, layer, q.data_ptr(), exchange._h, out.data_ptr(),
+                                                    self._stream()))
+        return out
+
     def append_decode_host(self, layer: int, k: torch.Tensor, v: torch.Tensor, q: torch.Tensor,
                            out: torch.Tensor) -> None:
         """Host (CPU, ideally pinned) tensors in and out; copies are part of the call."""
