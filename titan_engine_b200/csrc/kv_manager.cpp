@@ -258,17 +258,34 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     };
     int chunk = chunk_tokens;
     if (chunk == 0) {
-        static const int cands[] = {2048, 1024, 512, 256, 128};
-        chunk = 0;
-        for (int c : cands) {
-            if (c % ps != 0) continue;
-            int64_t items = 0;
-            int64_t rows = rows_for(c, &items);
-            if (rows > max_partial_rows) break;        // smaller chunks only need more rows
-            chunk = c;
-            if (items >= target_items) break;
+        // Measured on B200 (8B head shape, 3 resident CTAs per SM): an item costs a few microseconds
+        // beyond its bytes, the CTA that finishes last merges one row per chunk, and a little more than
+        // one wave of equal items is the worst schedule.  So: the largest chunk, unless that leaves
+        // between 0.9 and 1.5 waves (then the largest chunk of at least 1024 tokens that gives 1.5
+        // waves) or fewer than 128 items (then the largest chunk, down to 256 tokens, that gives 128).
+        const int64_t slots = std::max<int64_t>(1, (int64_t)target_items * 3 / 8);   // target = 8 per SM, 3 CTAs per SM
+        std::vector<int> cands;                         // descending, multiples of the page size
+        for (int c : {2048, 1792, 1536, 1280, 1024, 896, 768, 640, 512, 384, 256, 128}) {
+            const int r = c / ps * ps;
+            if (r > 0 && (cands.empty() || cands.back() != r)) cands.push_back(r);
         }
-        if (chunk == 0) return ST_INVALID_ARG;
+        auto fits = [&](int c, int64_t* items) { return rows_for(c, items) <= max_partial_rows; };
+        int64_t items_max = 0;
+        size_t first = cands.size();                    // index of the largest admissible chunk
+        for (size_t i = 0; i < cands.size(); i++)
+            if (fits(cands[i], &items_max)) { first = i; break; }
+        if (first == cands.size()) return ST_INVALID_ARG;
+        chunk = cands[first];
+        if (items_max * 10 > slots * 9 && items_max * 2 < slots * 3) {
+            for (size_t i = first + 1; i < cands.size() && cands[i] >= 1024; i++) {
+                int64_t items = 0;
+                if (fits(cands[i], &items) && items * 2 >= slots * 3) { chunk = cands[i]; break; }
+            }
+        } else if (items_max < 128) {
+            int64_t items = items_max;
+            for (size_t i = first + 1; i < cands.size() && cands[i] >= 256 && items < 128; i++)
+                if (fits(cands[i], &items)) chunk = cands[i];
+        }
     } else if (rows_for(chunk, nullptr) > max_partial_rows) {
         return ST_INVALID_ARG;
     }

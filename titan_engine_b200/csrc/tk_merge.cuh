@@ -56,13 +56,34 @@ __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& 
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xFFFFFFFFu, L, o);
+        // rows are added in ascending order; eight rows' loads are in flight at a time (the merge of a
+        // long single sequence is a chain of L2 round trips otherwise)
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < n; r++) {
-            const float* p = partials + partial_off(r0 + r, h, g.H, D);
-            const float w = expf(__ldcg(p + D) - M);
+        constexpr int U = 8;
+        for (int rb = 0; rb < n; rb += U) {
+            float m[U], x[U][4];
 #pragma unroll
-            for (int e = 0; e < 4; e++)
-                if (e < epl) acc[e] += __ldcg(p + lane * epl + e) * w;
+            for (int u = 0; u < U; u++) {
+                const bool live = rb + u < n;
+                const float* p = partials + partial_off(r0 + (live ? rb + u : rb), h, g.H, D);
+                m[u] = live ? __ldcg(p + D) : -1e30f;
+                if (epl == 4) {                         // rows start on 8-byte, not 16-byte, boundaries
+                    const float2 v0 = __ldcg(reinterpret_cast<const float2*>(p) + 2 * lane);
+                    const float2 v1 = __ldcg(reinterpret_cast<const float2*>(p) + 2 * lane + 1);
+                    x[u][0] = v0.x; x[u][1] = v0.y; x[u][2] = v1.x; x[u][3] = v1.y;
+                } else {
+                    const float2 v = __ldcg(reinterpret_cast<const float2*>(p) + lane);
+                    x[u][0] = v.x; x[u][1] = v.y; x[u][2] = 0.f; x[u][3] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                if (rb + u >= n) break;
+                const float w = expf(m[u] - M);
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (e < epl) acc[e] += x[u][e] * w;
+            }
         }
         const float inv = 1.0f / (L + 1e-8f);
 #pragma unroll
