@@ -222,6 +222,10 @@ void* tk_peer_mailbox(const tk_peer* p);
 size_t tk_peer_mailbox_bytes(const tk_peer* p);
 int tk_peer_connect_ptrs(tk_peer* p, void* const* mailboxes);
 int tk_peer_set_wait_limit_ms(tk_peer* p, int32_t ms);
+/* Rows are published in groups of `rows` rows, one flag each (0 = all rows as one group, the default).
+ * tk_kv_decode_exchange publishes one group per (sequence, kv head), i.e. num_heads / num_kv_heads rows:
+ * a rank that feeds the same exchange through tk_peer_send / tk_peer_recv_combine sets that value. */
+int tk_peer_set_group_rows(tk_peer* p, int32_t rows);
 int tk_peer_exchange_combine(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* out,
                              int32_t out_dtype, void* stream);
 /* The two halves as launches of their own (send early, combine later; also how ranks that share
@@ -230,8 +234,10 @@ int tk_peer_send(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, v
 int tk_peer_recv_combine(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* out,
                          int32_t out_dtype, void* stream);
 int tk_peer_status(tk_peer* p, void* stream);
-/* tk_kv_decode_partial of one layer followed by tk_peer_exchange_combine of its rows, in one call:
- * out [n_seqs][H][v_head_dim] in the handle's io dtype holds the attention over every rank's tokens. */
+/* Attention of one layer over the tokens of EVERY rank: out [n_seqs][H][v_head_dim] in the handle's io
+ * dtype.  Where the step allows it this is ONE launch: the attention kernel's merging CTAs store their
+ * rows into the peers' mailboxes, publish and await one flag per (sequence, kv head) and write the
+ * combine.  Otherwise tk_kv_decode_partial followed by the exchange kernel, on the same flags. */
 int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer, void* out, void* stream);
 
 /* update + attention_decode of one layer with HOST buffers (pageable or pinned):

@@ -32,6 +32,9 @@ def main():
     ap.add_argument("--exchange", default="nccl", choices=["nccl", "peer"],
                     help="nccl: all-gather + combine kernel; peer: one kernel storing into the peers' mailboxes over "
                          "NVLink, waiting for theirs and combining")
+    ap.add_argument("--mixed", action="store_true",
+                    help="odd ranks take the two-launch route (rows, then the exchange kernel) while even ranks let "
+                         "the attention kernel carry the exchange: the routes must meet on the same flags")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -45,6 +48,8 @@ def main():
     full = torch.randn(n_pg, Hkv, 2, 16, Dh, device=dev, generator=gen).to(torch.bfloat16)   # layer-shared data
 
     my_pages = (hi - lo) // 16
+    if args.mixed and rank % 2 == 1:
+        os.environ["TK_SEPARATE_COMBINE"] = "1"         # read when the handle is made
     cache = PagedKVCache(L, H, Hkv, Dh, max(my_pages, 1), 1, max(my_pages, 1), dtype="bf16",
                          hot_window=args.hot_window, cold_pages=max(my_pages, 1) if args.hot_window else 0)
     s = cache.seq_alloc()

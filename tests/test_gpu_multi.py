@@ -39,6 +39,16 @@ def test_long_context_peer_exchange_over_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_long_context_peer_exchange_mixed_routes_over_two_gpus():
+    """Rank 0: attention kernel carries the exchange (one launch); rank 1: rows, then the exchange kernel."""
+    res = _torchrun(2, "tests/multi_gpu/long_context_worker.py", "--tokens", "32768", "--layers", "2", "--steps", "3",
+                    "--exchange", "peer", "--mixed")
+    assert res.returncode == 0, res.stdout + res.stderr
+    line = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["ok"] and line["exchange"] == "peer" and line["same_bytes_as_all_gather_route"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_long_context_with_cold_tier_over_two_gpus():
     # hot window of 16384 over 32768 tokens: rank 0's pages live in pinned host memory
     res = _torchrun(2, "tests/multi_gpu/long_context_worker.py", "--tokens", "32768", "--layers", "3", "--steps", "3",

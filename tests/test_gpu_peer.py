@@ -93,3 +93,75 @@ def test_argument_checks():
         D.PeerExchange(4, 131, rank=0, world=1)             # odd row width
     with pytest.raises(RuntimeError):
         D.PeerExchange(4, 130, rank=0, world=17)
+
+
+def _split_caches(dev, n, H, Hkv, D, world, gen):
+    """One sequence of n tokens: `whole` holds all of it, parts[r] holds rank r's page-aligned range."""
+    from titan_engine_b200 import PagedKVCache
+    pg = n // 16
+    full = torch.randn(pg, Hkv, 2, 16, D, device=dev, generator=gen).to(torch.bfloat16)
+    whole = PagedKVCache(1, H, Hkv, D, pg, 1, pg, dtype="bf16")
+    ws = whole.seq_alloc(); whole.adopt(ws, np.arange(pg, dtype=np.int32), n)
+    whole.layer_views(0)[0].copy_(full)
+    whole.step_begin([ws], None)
+    parts = []
+    for lo, hi in D_ranges(n, world):
+        mp = (hi - lo) // 16
+        c = PagedKVCache(1, H, Hkv, D, mp, 1, mp, dtype="bf16")
+        s = c.seq_alloc(); c.adopt(s, np.arange(mp, dtype=np.int32), hi - lo)
+        c.layer_views(0)[0].copy_(full[lo // 16:hi // 16])
+        c.step_begin([s], None)
+        parts.append(c)
+    return whole, parts
+
+
+def D_ranges(n, world):
+    return D.token_ranges(n, world)
+
+
+@pytest.mark.parametrize("shape", [(32, 8, 128), (8, 8, 64), (16, 1, 128)])
+def test_attention_kernel_carries_the_exchange_and_meets_the_two_launch_route(shape):
+    """Two ranks in this process, each with half of one sequence.  The rank that goes second runs
+    tk_kv_decode_exchange as ONE launch (its merging CTAs find the first rank's rows and flags already
+    there); the rank that goes first feeds the same exchange with send / recv_combine.  Both must get
+    the attention of the whole sequence, and the same bytes as each other."""
+    H, Hkv, Dh = shape
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev); gen.manual_seed(11)
+    whole, parts = _split_caches(dev, 4096, H, Hkv, Dh, 2, gen)
+    ranks = [D.PeerExchange(H, Dh + 2, rank=r, world=2, connect=False) for r in range(2)]
+    for r in ranks:
+        r.connect_local(ranks)
+        r.set_group_rows(H // Hkv)
+        r.set_wait_limit_ms(200)
+    for epoch in range(4):
+        q = torch.randn(1, H, Dh, device=dev, generator=gen).to(torch.bfloat16)
+        want = whole.decode(0, q).float()
+        first, second = (0, 1) if epoch % 2 == 0 else (1, 0)
+        p_first = parts[first].decode_partial(0, q)
+        ranks[first].send(p_first)
+        n0 = parts[second].launch_count
+        out_second = parts[second].decode_exchange(0, q, ranks[second])
+        assert parts[second].launch_count - n0 == 1                  # attention + exchange + combine: one kernel
+        out_first = ranks[first].recv_combine(p_first, torch.bfloat16).view(1, H, Dh)
+        for r in ranks:
+            r.status()
+        assert torch.equal(out_first, out_second)
+        torch.testing.assert_close(out_second.float(), want, rtol=2e-3, atol=1e-2)
+    for c in parts + [whole]:
+        c.close()
+    for r in ranks:
+        r.close()
+
+
+def test_decode_exchange_alone_in_the_world_equals_decode():
+    from titan_engine_b200 import PagedKVCache
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev); gen.manual_seed(12)
+    whole, parts = _split_caches(dev, 2048, 32, 8, 128, 1, gen)
+    ex = D.PeerExchange(32, 130, rank=0, world=1)
+    for _ in range(3):
+        q = torch.randn(1, 32, 128, device=dev, generator=gen).to(torch.bfloat16)
+        assert torch.equal(whole.decode_exchange(0, q, ex), whole.decode(0, q))
+    ex.status()
+    ex.close(); whole.close(); parts[0].close()

@@ -10,7 +10,7 @@
 //
 // Mailbox of a rank (device memory of that rank):
 //   payload[2 parities][world sources][max_rows * row_floats] float   (slots 256-byte aligned)
-//   flags  [2 parities][world sources] uint32, one per 128-byte line; value = epoch of the data
+//   flags  [2 parities][world sources][max_rows] uint32; value = epoch of that source's rows of one group
 // The epoch counts exchanges (1, 2, ...), parity = epoch & 1.  Two parities are enough: a rank can
 // only start sending epoch e+2 after it finished e+1, which needed every peer's e+1 flag, which a
 // peer sends only after its own epoch-e kernel (the reader of that parity) has finished.
@@ -21,6 +21,7 @@
 #include "../../include/titan_kv.h"
 #include "tk_kernels.cuh"
 #include "tk_merge.cuh"
+#include "tk_peer.cuh"
 
 #include <cstdio>
 #include <cstring>
@@ -28,85 +29,66 @@
 
 namespace {
 
-constexpr int kMaxWorld = 16;
-constexpr int kFlagStride = 128;
-
-struct PeerBoxes { uint8_t* box[kMaxWorld]; };
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+using tk::PeerCtx;
+constexpr int kMaxWorld = tk::kPeerMaxWorld;
 
 // mode bit 0: send this rank's rows to every peer and publish the flags;
 // mode bit 1: wait for the peers' rows and combine.  Both: one launch does the whole exchange.
+// Rows are published in groups of group_rows rows (one flag per group), the granularity at which the
+// attention kernels publish when they carry the exchange themselves.
 __global__ void __launch_bounds__(512)
-peer_exchange_combine_kernel(PeerBoxes boxes, int rank, int world, uint32_t* __restrict__ epoch_ctr, size_t slot_bytes,
-                             size_t flags_off, const float* __restrict__ partial, int n_rows, int dv,
-                             void* __restrict__ out, int out_dtype, unsigned* __restrict__ ticket,
-                             int* __restrict__ status, unsigned long long limit_ns, int mode) {
-    // ticket[0]: CTAs that have sent; ticket[1]: CTAs that have read the epoch and are about to leave
-    const uint32_t epoch = __ldcg(epoch_ctr) + ((mode & 1) ? 1u : 0u);   // a send opens the next exchange
+peer_exchange_combine_kernel(const PeerCtx* __restrict__ ctx_p, const float* __restrict__ partial, int n_rows, int dv,
+                             int group_rows, void* __restrict__ out, int out_dtype, int mode) {
+    const PeerCtx& c = *ctx_p;
+    const int rank = c.rank, world = c.world;
+    const uint32_t epoch = __ldcg(c.epoch) + ((mode & 1) ? 1u : 0u);   // a send opens the next exchange
     // called by the whole CTA on every way out: the last CTA to leave stores the epoch for the next
     // launch (by then every CTA of this launch has read the old value)
     auto leave = [&]() {
         __syncthreads();
-        if ((mode & 1) && threadIdx.x == 0 && atomicAdd(ticket + 1, 1u) == gridDim.x - 1) {
-            atomicExch(ticket + 1, 0u);
-            atomicExch(epoch_ctr, epoch);
+        if ((mode & 1) && threadIdx.x == 0 && atomicAdd(c.tickets + 1, 1u) == gridDim.x - 1) {
+            atomicExch(c.tickets + 1, 0u);
+            atomicExch(c.epoch, epoch);
         }
     };
     const int parity = (int)(epoch & 1u);
-    const size_t parity_bytes = slot_bytes * (size_t)world;
     const int row_floats = dv + 2;
-    __shared__ int s_ok;
+    const int n_groups = (n_rows + group_rows - 1) / group_rows;
+    __shared__ int s_flag;
 
     if (mode & 1) {
         const size_t n2 = (size_t)n_rows * row_floats / 2;                 // row_floats is even
         const float2* src = reinterpret_cast<const float2*>(partial);
         for (int p = 0; p < world; p++) {
             if (p == rank) continue;
-            float2* dst = reinterpret_cast<float2*>(boxes.box[p] + parity * parity_bytes + rank * slot_bytes);
+            float2* dst = reinterpret_cast<float2*>(tk::peer_rows(c, p, parity, rank));
             for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n2; i += (size_t)gridDim.x * blockDim.x)
                 dst[i] = src[i];
         }
         __threadfence_system();                                            // this thread's rows are out ...
+        if (threadIdx.x == 0) s_flag = 0;
         __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned t = atomicAdd(ticket, 1u);
-            if (t == gridDim.x - 1) {                                      // ... and so are every CTA's
-                atomicExch(ticket, 0u);
-                __threadfence_system();
-                for (int p = 0; p < world; p++)
-                    if (p != rank)
-                        st_release_sys(reinterpret_cast<uint32_t*>(boxes.box[p] + flags_off + (size_t)(parity * world + rank) * kFlagStride), epoch);
-            }
+        if (threadIdx.x == 0 && atomicAdd(c.tickets, 1u) == gridDim.x - 1) {   // ... and so are every CTA's
+            atomicExch(c.tickets, 0u);
+            __threadfence_system();
+            s_flag = 1;
         }
+        __syncthreads();
+        if (s_flag)
+            for (int i = threadIdx.x; i < world * n_groups; i += blockDim.x) {
+                const int p = i / n_groups, g = i % n_groups;
+                if (p != rank) tk::st_release_sys(tk::peer_flag(c, p, parity, rank, g), epoch);
+            }
     }
     if (!(mode & 2)) { leave(); return; }
 
-    uint8_t* mine = boxes.box[rank];
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
-    if (threadIdx.x < world && threadIdx.x != rank) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine + flags_off + (size_t)(parity * world + threadIdx.x) * kFlagStride);
-        const unsigned long long t0 = now_ns();
-        while (ld_acquire_sys(flag) != epoch) {
-            if (now_ns() - t0 > limit_ns) { s_ok = 0; break; }             // give up: the peer never published
-        }
+    bool ok = true;
+    for (int i = threadIdx.x; i < world * n_groups; i += blockDim.x) {
+        const int src = i / n_groups, g = i % n_groups;
+        if (src != rank && ok) ok = tk::peer_wait_flag(tk::peer_flag(c, rank, parity, src, g), epoch, c.limit_ns);
     }
-    __syncthreads();
-    if (!s_ok) {
-        if (threadIdx.x == 0) atomicExch(status, (int)TK_TIMEOUT);
+    if (!__syncthreads_and(ok)) {                                          // give up: a peer never published
+        if (threadIdx.x == 0) atomicExch(c.status, (int)TK_TIMEOUT);
         leave();
         return;
     }
@@ -118,9 +100,7 @@ peer_exchange_combine_kernel(PeerBoxes boxes, int rank, int world, uint32_t* __r
         const float* src[kMaxWorld];
 #pragma unroll
         for (int r = 0; r < kMaxWorld; r++)
-            if (r < world)
-                src[r] = (r == rank ? partial : reinterpret_cast<const float*>(mine + parity * parity_bytes + r * slot_bytes)) +
-                         (size_t)row * row_floats;
+            if (r < world) src[r] = (r == rank ? partial : tk::peer_rows(c, rank, parity, r)) + (size_t)row * row_floats;
         float M = -1e30f;
         for (int r = 0; r < world; r++) M = fmaxf(M, __ldcg(src[r] + dv));
         float L = 0.0f;
@@ -145,8 +125,10 @@ struct tk_peer {
     bool opened[kMaxWorld] = {};           // mapped through CUDA IPC (to be closed)
     bool connected = false;
     bool sent_once = false;
+    int group_rows = 0;                    // rows per published group for the plain entry points; 0 = all rows
     uint32_t* d_epoch = nullptr;
-    unsigned* d_ticket = nullptr;          // two counters
+    unsigned* d_ticket = nullptr;          // three counters
+    tk::PeerCtx* d_ctx = nullptr;          // device copy of the context, written at connect
     int* d_status = nullptr;
     unsigned long long limit_ns = 2000000000ull;
     int num_sms = 148;
@@ -154,6 +136,19 @@ struct tk_peer {
 };
 
 namespace {
+
+// (re)writes the device copy of the context; synchronous, used at connect time only
+cudaError_t upload_ctx(tk_peer* p) {
+    tk::PeerCtx c{};
+    for (int r = 0; r < kMaxWorld; r++) c.box[r] = r < p->world ? p->peers[r] : nullptr;
+    c.rank = p->rank; c.world = p->world; c.max_rows = p->max_rows; c.row_floats = p->row_floats;
+    c.slot_bytes = p->slot_bytes; c.flags_off = p->flags_off;
+    c.epoch = p->d_epoch; c.tickets = p->d_ticket; c.status = p->d_status; c.limit_ns = p->limit_ns;
+    cudaError_t e = cudaSetDevice(p->device);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();      // no kernel may be reading the old copy
+    if (e == cudaSuccess) e = cudaMemcpy(p->d_ctx, &c, sizeof(c), cudaMemcpyHostToDevice);
+    return e;
+}
 
 int pfail(tk_peer* p, int st, const char* what, cudaError_t e = cudaSuccess) {
     if (p) {
@@ -178,14 +173,15 @@ int tk_peer_create(int32_t rank, int32_t world, int32_t max_rows, int32_t row_fl
     p->device = device;
     p->slot_bytes = ((size_t)max_rows * row_floats * sizeof(float) + 255) / 256 * 256;
     p->flags_off = 2 * p->slot_bytes * world;
-    p->total = p->flags_off + 2 * (size_t)world * kFlagStride;
+    p->total = p->flags_off + 2 * (size_t)world * max_rows * sizeof(uint32_t);
     cudaDeviceProp prop;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete p; return TK_CUDA_ERROR; }
     p->num_sms = prop.multiProcessorCount;
     cudaError_t e = cudaMalloc((void**)&p->local, p->total);
     if (e == cudaSuccess) e = cudaMemset(p->local, 0, p->total);
-    if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_ticket, 2 * sizeof(unsigned));
-    if (e == cudaSuccess) e = cudaMemset(p->d_ticket, 0, 2 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_ticket, 4 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(p->d_ticket, 0, 4 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_ctx, sizeof(tk::PeerCtx));
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_epoch, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(p->d_epoch, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_status, sizeof(int));
@@ -197,11 +193,13 @@ int tk_peer_create(int32_t rank, int32_t world, int32_t max_rows, int32_t row_fl
         if (p->d_ticket) cudaFree(p->d_ticket);
         if (p->d_epoch) cudaFree(p->d_epoch);
         if (p->d_status) cudaFree(p->d_status);
+        if (p->d_ctx) cudaFree(p->d_ctx);
         delete p;
         return TK_CUDA_ERROR;
     }
     p->peers[rank] = p->local;
     p->connected = world == 1;
+    if (p->connected && upload_ctx(p) != cudaSuccess) { tk_peer_destroy(p); return TK_CUDA_ERROR; }
     *out = p;
     return TK_OK;
 }
@@ -216,6 +214,7 @@ void tk_peer_destroy(tk_peer* p) {
     if (p->d_ticket) cudaFree(p->d_ticket);
     if (p->d_epoch) cudaFree(p->d_epoch);
     if (p->d_status) cudaFree(p->d_status);
+    if (p->d_ctx) cudaFree(p->d_ctx);
     delete p;
 }
 
@@ -250,6 +249,8 @@ int tk_peer_connect(tk_peer* p, const void* handles) {
         p->peers[r] = (uint8_t*)ptr;
         p->opened[r] = true;
     }
+    e = upload_ctx(p);
+    if (e != cudaSuccess) return pfail(p, TK_CUDA_ERROR, "context upload", e);
     p->connected = true;
     return TK_OK;
 }
@@ -261,19 +262,33 @@ int tk_peer_connect_ptrs(tk_peer* p, void* const* mailboxes) {
         if (!mailboxes[r]) return pfail(p, TK_INVALID_ARG, "connect_ptrs: null mailbox");
         p->peers[r] = (uint8_t*)mailboxes[r];
     }
+    cudaError_t e = upload_ctx(p);
+    if (e != cudaSuccess) return pfail(p, TK_CUDA_ERROR, "context upload", e);
     p->connected = true;
+    return TK_OK;
+}
+
+int tk_peer_set_group_rows(tk_peer* p, int32_t rows) {
+    if (!p || rows < 0) return TK_INVALID_ARG;
+    p->group_rows = rows;
     return TK_OK;
 }
 
 int tk_peer_set_wait_limit_ms(tk_peer* p, int32_t ms) {
     if (!p || ms <= 0) return TK_INVALID_ARG;
     p->limit_ns = (unsigned long long)ms * 1000000ull;
+    if (p->connected) {
+        cudaError_t e = upload_ctx(p);
+        if (e != cudaSuccess) return pfail(p, TK_CUDA_ERROR, "context upload", e);
+    }
     return TK_OK;
 }
 
 static int peer_launch(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* out, int32_t out_dtype,
-                       void* stream, int mode) {
-    if (!p || n_rows < 0 || dv <= 0) return TK_INVALID_ARG;
+                       void* stream, int mode, int group_rows = 0) {
+    if (!p || n_rows < 0 || dv <= 0 || group_rows < 0) return TK_INVALID_ARG;
+    if (group_rows == 0) group_rows = p ? p->group_rows : 0;
+    if (group_rows == 0) group_rows = n_rows > 0 ? n_rows : 1;   // one group: one flag per source
     if (!p->connected) return pfail(p, TK_INVALID_ARG, "peers are not connected");
     if (dv + 2 != p->row_floats || n_rows > p->max_rows) return pfail(p, TK_INVALID_ARG, "rows do not fit the mailbox");
     if ((mode & 1) && !partial) return pfail(p, TK_INVALID_ARG, "null partial");
@@ -281,15 +296,12 @@ static int peer_launch(tk_peer* p, const float* partial, int32_t n_rows, int32_t
     if ((mode & 2) && out_dtype != TK_FP32 && out_dtype != TK_FP16 && out_dtype != TK_BF16) return pfail(p, TK_INVALID_ARG, "bad out dtype");
     if (mode & 1) p->sent_once = true;
     if (!p->sent_once) return pfail(p, TK_INVALID_ARG, "recv_combine before any send");
-    PeerBoxes boxes;
-    for (int r = 0; r < kMaxWorld; r++) boxes.box[r] = r < p->world ? p->peers[r] : nullptr;
     const size_t work = (size_t)n_rows * p->row_floats / 2;
     int grid = (int)((work + 4095) / 4096);
     if (grid < 1) grid = 1;
     if (grid > p->num_sms) grid = p->num_sms;
-    peer_exchange_combine_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(
-        boxes, p->rank, p->world, p->d_epoch, p->slot_bytes, p->flags_off, partial, n_rows, dv, out, out_dtype,
-        p->d_ticket, p->d_status, p->limit_ns, mode);
+    peer_exchange_combine_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(p->d_ctx, partial, n_rows, dv, group_rows, out,
+                                                                         out_dtype, mode);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return pfail(p, TK_CUDA_ERROR, "exchange launch", e);
     return TK_OK;
@@ -321,3 +333,17 @@ int tk_peer_status(tk_peer* p, void* stream) {
 }
 
 }  // extern "C"
+
+namespace tk {
+
+const PeerCtx* peer_device_ctx(const tk_peer* p) { return p && p->connected ? p->d_ctx : nullptr; }
+int peer_max_rows(const tk_peer* p) { return p ? p->max_rows : 0; }
+int peer_row_floats(const tk_peer* p) { return p ? p->row_floats : 0; }
+int peer_exchange_grouped(tk_peer* p, const float* partial, int n_rows, int dv, int group_rows, void* out, int out_dtype,
+                          void* stream) {
+    return peer_launch(p, partial, n_rows, dv, out, out_dtype, stream, 3, group_rows);
+}
+// An attention launch that carries the exchange itself counts as this exchange's send.
+void peer_note_fused_send(tk_peer* p) { if (p) p->sent_once = true; }
+
+}  // namespace tk

@@ -4,6 +4,7 @@
 
 #include "kv_manager.h"
 #include "tk_kernels.cuh"
+#include "tk_peer.cuh"
 
 #include <algorithm>
 #include <cstdarg>
@@ -724,7 +725,8 @@ int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t*
 
 static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* partial_out, cudaStream_t s,
                        int q_dtype = -1, int out_dtype = -1, const void* fuse_k = nullptr,
-                       const void* fuse_v = nullptr, const float* rope = nullptr) {
+                       const void* fuse_v = nullptr, const float* rope = nullptr,
+                       const tk::PeerCtx* peer_ctx = nullptr) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode: no step in progress (call tk_kv_step_begin)");
@@ -756,7 +758,8 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     // the last CTA of each (sequence, kv head) merges the split-KV rows itself; a sequence that
     // attends to nothing has no CTA, so such steps keep the separate combine kernel
     const bool fused_merge = !h->plan.has_empty_seq && !h->separate_combine;
-    const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype};
+    if (peer_ctx && !fused_merge) return fail(h, TK_INVALID_ARG, "decode: the in-kernel exchange needs the in-kernel merge");
+    const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype, peer_ctx};
     const tk::FuseAppend fa{fuse_k, fuse_v, rope ? h->d_rope_tab : nullptr};
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
     if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
@@ -855,11 +858,30 @@ int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial,
     return decode_impl(h, layer, q, nullptr, partial, (cudaStream_t)stream);
 }
 
-// decode_partial + the peer exchange of one layer in one call: two launches, no collective.
+// Attention over a sequence whose tokens are spread over the ranks of `peer`.  One launch where the
+// step allows it: the attention kernel's merging CTAs store their merged rows into every rank's
+// mailbox, publish and await one flag per (sequence, kv head) and write the combine themselves.
+// Otherwise two launches: this rank's merged rows, then the exchange kernel, publishing the same
+// flags - so ranks that take different routes for the same layer still meet.
 int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer, void* out, void* stream) {
     if (!h || !peer || !out) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode_exchange: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode_exchange: no step in progress (call tk_kv_step_begin)");
+    const tk::PeerCtx* ctx = tk::peer_device_ctx(peer);
+    if (!ctx) return fail(h, TK_INVALID_ARG, "decode_exchange: peers are not connected");
+    const int n_rows = h->dev.n_seqs * h->geo.H, dv = h->cfg.v_head_dim, G = h->geo.H / h->geo.Hkv;
+    if (tk::peer_row_floats(peer) != dv + 2 || n_rows > tk::peer_max_rows(peer))
+        return fail(h, TK_INVALID_ARG, "decode_exchange: %d rows of %d floats do not fit the mailbox", n_rows, dv + 2);
+    if (h->dev.n_seqs == 0) return TK_OK;
+    // a merging CTA waits for its peers while it holds a CTA slot: keep those few against the slots of a
+    // launch, or ranks could fill their GPUs with CTAs that wait for CTAs the other ranks cannot start
+    const bool in_kernel = !h->plan.has_empty_seq && !h->separate_combine && h->dev.n_items > 0 &&
+                           h->dev.n_seqs * h->geo.Hkv <= h->num_sms / 2;
+    if (in_kernel) {
+        int st = decode_impl(h, layer, q, out, nullptr, (cudaStream_t)stream, -1, -1, nullptr, nullptr, nullptr, ctx);
+        if (st == TK_OK) tk::peer_note_fused_send(peer);
+        return st;
+    }
     const size_t need = (size_t)h->cfg.max_seqs * h->cfg.num_heads * (h->cfg.v_head_dim + 2) * sizeof(float);
     if (!h->d_xpartial) {                                   // first use only
         TK_CUDA(h, cudaSetDevice(h->device));
@@ -867,8 +889,7 @@ int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer,
     }
     int st = decode_impl(h, layer, q, nullptr, h->d_xpartial, (cudaStream_t)stream);
     if (st != TK_OK) return st;
-    st = tk_peer_exchange_combine(peer, h->d_xpartial, h->dev.n_seqs * h->geo.H, h->cfg.v_head_dim, out,
-                                  h->cfg.io_dtype, stream);
+    st = tk::peer_exchange_grouped(peer, h->d_xpartial, n_rows, dv, G, out, h->cfg.io_dtype, stream);
     h->launches++;
     if (st != TK_OK) return fail(h, st, "decode_exchange: %s", tk_peer_last_error(peer));
     return TK_OK;

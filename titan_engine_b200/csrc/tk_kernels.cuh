@@ -63,6 +63,10 @@ struct MergeOut {
     void*  out;                 // normalised [n_seqs][H][D] in out_dtype, or null
     float* partial_out;         // merged, unnormalised [n_seqs][H][D+2], or null
     int    out_dtype;
+    // != null: the sequences' other tokens live on other GPUs.  The merging CTA stores its merged rows
+    // into every rank's mailbox, publishes and awaits the per-(sequence, kv head) flags and writes the
+    // combine over all ranks to `out` (tk_peer.cuh); partial_out is not used then.
+    const struct PeerCtx* peer;
 };
 
 // Decode steps (at most one new token per sequence): the decode kernel itself writes the

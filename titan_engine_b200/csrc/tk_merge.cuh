@@ -7,6 +7,7 @@
 #pragma once
 
 #include "tk_kernels.cuh"
+#include "tk_peer.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -19,30 +20,16 @@ __device__ __forceinline__ void store_out(void* out, size_t idx, float v, int dt
     else                    ((float*)out)[idx] = v;
 }
 
-// Every thread of the CTA calls this after the CTA's partial row for heads [kvh*G, kvh*G+G)
-// of step-sequence b is in global memory.  The CTA that arrives last for (b, kvh) merges all
-// of that sequence's rows for those heads and writes the result; it also re-arms the counter.
-// `s_flag` is one int of shared memory.  Returns without merging when mo.counters is null.
-__device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& st, const MergeOut& mo,
-                                              int b, int kvh, int G, const float* partials, int* s_flag) {
-    if (!mo.counters) return;
-    const int D = g.Dv;                                // width of a partial / output row
-    const int r0 = st.chunk_base[b], n = st.chunk_base[b + 1] - r0;
-    __syncthreads();                                   // the CTA's partial row is complete ...
-    if (threadIdx.x == 0) {
-        __threadfence();                               // ... and ordered before the ticket, device-wide
-        int* c = mo.counters + (size_t)b * g.Hkv + kvh;
-        const int ticket = atomicAdd(c, 1);
-        const int last = ticket == n - 1;
-        if (last) *c = 0;                              // nobody else touches it again in this launch
-        *s_flag = last;
-    }
-    __syncthreads();
-    if (!*s_flag) return;
+// The merge itself, by every thread of the CTA that arrived last for (b, kvh): rows r0 .. r0+n-1.
+__device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo, int b, int kvh, int G, int r0, int n,
+                                           const float* partials) {
     __threadfence();                                   // see the other CTAs' rows
-
+    const int D = g.Dv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const int epl = D >> 5;                            // dims per lane: 2 (D=64) or 4 (D=128)
+    const PeerCtx* pc = mo.peer;
+    const uint32_t epoch = pc ? __ldcg(pc->epoch) + 1u : 0u;
+    const int parity = (int)(epoch & 1u);
     for (int gq = warp; gq < G; gq += n_warps) {
         const int h = kvh * G + gq;
         float M = -1e30f;
@@ -85,6 +72,15 @@ __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& 
                     if (e < epl) acc[e] += x[u][e] * w;
             }
         }
+        if (pc) {                                      // this rank's merged row goes to every rank's mailbox
+            for (int p = 0; p < pc->world; p++) {
+                float* row = peer_rows(*pc, p, parity, pc->rank) + partial_off(b, h, g.H, D);
+                reinterpret_cast<float2*>(row)[lane * (epl / 2)] = make_float2(acc[0], acc[1]);
+                if (epl == 4) reinterpret_cast<float2*>(row)[lane * 2 + 1] = make_float2(acc[2], acc[3]);
+                if (lane == 0) *reinterpret_cast<float2*>(row + D) = make_float2(M, L);
+            }
+            continue;
+        }
         const float inv = 1.0f / (L + 1e-8f);
 #pragma unroll
         for (int e = 0; e < 4; e++) {
@@ -96,6 +92,72 @@ __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& 
         if (mo.partial_out && lane == 0) {
             mo.partial_out[partial_off(b, h, g.H, D) + D] = M;
             mo.partial_out[partial_off(b, h, g.H, D) + D + 1] = L;
+        }
+    }
+    if (!pc) return;
+
+    // publish this (sequence, kv head) group to every peer, wait for theirs, combine in rank order
+    const PeerCtx& c = *pc;
+    const int group = b * g.Hkv + kvh;
+    __threadfence_system();
+    __syncthreads();
+    bool ok = true;
+    if ((int)threadIdx.x < c.world && (int)threadIdx.x != c.rank) {
+        st_release_sys(peer_flag(c, threadIdx.x, parity, c.rank, group), epoch);
+        ok = peer_wait_flag(peer_flag(c, c.rank, parity, threadIdx.x, group), epoch, c.limit_ns);
+    }
+    if (!__syncthreads_and(ok)) {                      // a peer never published: report, leave `out` alone
+        if (threadIdx.x == 0) atomicExch(c.status, 4 /* TK_TIMEOUT */);
+        return;
+    }
+    for (int gq = warp; gq < G; gq += n_warps) {
+        const int h = kvh * G + gq;
+        const size_t off = partial_off(b, h, g.H, D);
+        float M = -1e30f;
+        for (int r = 0; r < c.world; r++) M = fmaxf(M, __ldcg(peer_rows(c, c.rank, parity, r) + off + D));
+        float L = 0.0f;
+        for (int r = 0; r < c.world; r++) {
+            const float* row = peer_rows(c, c.rank, parity, r) + off;
+            L += __ldcg(row + D + 1) * expf(__ldcg(row + D) - M);
+        }
+        const float inv = 1.0f / (L + 1e-8f);
+        for (int d = lane; d < D; d += 32) {
+            float acc = 0.0f;
+            for (int r = 0; r < c.world; r++) {
+                const float* row = peer_rows(c, c.rank, parity, r) + off;
+                acc += __ldcg(row + d) * expf(__ldcg(row + D) - M);
+            }
+            store_out(mo.out, ((size_t)b * g.H + h) * D + d, acc * inv, mo.out_dtype);
+        }
+    }
+}
+
+
+// Every thread of the CTA calls this after the CTA's partial row for heads [kvh*G, kvh*G+G)
+// of step-sequence b is in global memory.  The CTA that arrives last for (b, kvh) merges all
+// of that sequence's rows for those heads and writes the result; it also re-arms the counter.
+// `s_flag` is one int of shared memory.  Returns without merging when mo.counters is null.
+__device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& st, const MergeOut& mo,
+                                              int b, int kvh, int G, const float* partials, int* s_flag) {
+    if (!mo.counters) return;
+    const int r0 = st.chunk_base[b], n = st.chunk_base[b + 1] - r0;
+    __syncthreads();                                   // the CTA's partial row is complete ...
+    if (threadIdx.x == 0) {
+        __threadfence();                               // ... and ordered before the ticket, device-wide
+        int* c = mo.counters + (size_t)b * g.Hkv + kvh;
+        const int ticket = atomicAdd(c, 1);
+        const int last = ticket == n - 1;
+        if (last) *c = 0;                              // nobody else touches it again in this launch
+        *s_flag = last;
+    }
+    __syncthreads();
+    if (*s_flag) merge_rows(g, mo, b, kvh, G, r0, n, partials);
+    if (mo.peer) {                                     // the CTA that leaves last closes this exchange
+        const PeerCtx& c = *mo.peer;
+        __syncthreads();
+        if (threadIdx.x == 0 && atomicAdd(c.tickets + 2, 1u) == gridDim.x - 1) {
+            atomicExch(c.tickets + 2, 0u);
+            atomicExch(c.epoch, __ldcg(c.epoch) + 1u);
         }
     }
 }
