@@ -138,6 +138,28 @@ def test_step_plan_shapes():
     assert f.step_num_work_items == 3 * 2 and f.stats()["pages_sealed"] == 19
 
 
+@pytest.mark.parametrize("n_seqs,tokens,want_chunk,want_items", [
+    (1, 65536, 2048, 256),      # under a wave of items: the largest chunk
+    (1, 131072, 1536, 688),     # 512 items would be a little more than one wave of 444: go to 1.5 waves
+    (8, 16384, 1536, 704),
+    (1, 16384, 1024, 128),      # fewer than 128 items at 2048: shrink until there are 128
+    (1, 4096, 256, 128),
+    (64, 4600, 2048, 1536),     # a batch: the largest chunk
+])
+def test_auto_chunk_rule(n_seqs, tokens, want_chunk, want_items):
+    """The split-KV chunk the planner picks on its own (8 kv heads, 148 SMs assumed without a device)."""
+    pages = (tokens + 15) // 16
+    c = PagedKVCache(1, 32, 8, 128, pages * n_seqs + 8, n_seqs, pages + 1, dtype="bf16", host_only=True,
+                     max_step_tokens=64)
+    seqs = []
+    for b in range(n_seqs):
+        s = c.seq_alloc()
+        c.adopt(s, np.arange(b * pages, (b + 1) * pages, dtype=np.int32), tokens)
+        seqs.append(s)
+    c.step_begin(seqs, None)
+    assert (c.step_chunk_tokens, c.step_num_work_items) == (want_chunk, want_items)
+
+
 @pytest.mark.parametrize("seed", [3, 4])
 def test_churn_matches_oracle_manager_bit_exact(seed):
     """Retire ~5% per step in ascending slot order, admit replacements in ascending slot order,
