@@ -59,6 +59,17 @@ def test_long_context_with_cold_tier_over_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_long_context_peer_exchange_with_cold_tier_over_two_gpus():
+    """Rank 0 reads its pages through the cold tier (milliseconds per layer) while rank 1's merging CTAs wait
+    for its rows inside their attention kernel: the bounded wait must simply be long enough."""
+    res = _torchrun(2, "tests/multi_gpu/long_context_worker.py", "--tokens", "32768", "--layers", "3", "--steps", "3",
+                    "--hot-window", "16384", "--exchange", "peer")
+    assert res.returncode == 0, res.stdout + res.stderr
+    line = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["ok"] and line["rank0_stats"]["pages_cold"] == 1024 and line["same_bytes_as_all_gather_route"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_bench_shards_by_sequence_over_two_gpus():
     res = _torchrun(2, "bench.py", "--gpus", "2", "--steps", "3", "--warmup", "3", "--layers", "4", "--no-cpu")
     assert res.returncode == 0, res.stdout + res.stderr
