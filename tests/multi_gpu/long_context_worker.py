@@ -90,9 +90,14 @@ def main():
         whole.close()
     del full
 
+    out_buf = torch.empty_like(out) if ex is not None else None
+
     def step():
         for l in range(L):
-            dec.decode(l, q)
+            if out_buf is not None:
+                dec.decode(l, q, out_buf)
+            else:
+                dec.decode(l, q)
 
     for _ in range(args.warmup):
         step()

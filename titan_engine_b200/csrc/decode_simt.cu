@@ -184,11 +184,16 @@ cudaError_t launch_simt_ge(const Geometry& g, const LayerPtrs& lp, const StepDev
                            const int32_t* page_table, const void* q, float* partials, cudaStream_t s,
                            const MergeOut& mo) {
     const bool fp8 = g.dtype == DT_FP8, bf16 = g.io_dtype == DT_BF16;
-    if (fp8 && EPLV != EPL) return cudaErrorNotSupported;
     dim3 grid(st.n_items), block(kWarps * 32);
     const uint16_t* qq = (const uint16_t*)q;
-    if (fp8 && bf16)       decode_simt_kernel<G, EPL, EPLV, true, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
-    else if (fp8)          decode_simt_kernel<G, EPL, EPLV, true, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+    if (fp8) {
+        if constexpr (EPLV != EPL) {
+            return cudaErrorNotSupported;                   // the MLA shape is stored in 16 bits only
+        } else {
+            if (bf16) decode_simt_kernel<G, EPL, EPLV, true, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+            else      decode_simt_kernel<G, EPL, EPLV, true, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
+        }
+    }
     else if (bf16)         decode_simt_kernel<G, EPL, EPLV, false, true><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
     else                   decode_simt_kernel<G, EPL, EPLV, false, false><<<grid, block, 0, s>>>(g, lp, st, page_table, qq, partials, mo);
     return cudaGetLastError();

@@ -88,9 +88,9 @@ class LongContextDecoder:
         self.exchange, self.out_dtype, self.fused_fn = exchange, out_dtype, fused_fn
         self._gathered = None
 
-    def decode(self, layer: int, q: torch.Tensor) -> torch.Tensor:
+    def decode(self, layer: int, q: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.exchange is not None and self.fused_fn is not None:
-            return self.fused_fn(layer, q, self.exchange)
+            return self.fused_fn(layer, q, self.exchange, out)
         part = self.partial_fn(layer, q)
         if self.exchange is not None:                     # peer stores + combine in one kernel, no collective
             return self.exchange.exchange_combine(part, self.out_dtype)
