@@ -112,4 +112,21 @@ int tkref_apply_rope(float* q, float* k, int H, int Hkv, int D, int position,
     return 0;
 }
 
+// cuda::apply_rope_mla in place on host arrays q: [H][nope+rope], k: [Hkv][nope+rope].
+int tkref_apply_rope_mla(float* q, float* k, int H, int Hkv, int nope_hd, int rope_hd, int position, float theta) {
+    size_t qb = (size_t)H * (nope_hd + rope_hd) * sizeof(float), kb = (size_t)Hkv * (nope_hd + rope_hd) * sizeof(float);
+    float *dq = nullptr, *dk = nullptr;
+    TKREF_CHECK(cudaMalloc(&dq, qb));
+    TKREF_CHECK(cudaMalloc(&dk, kb));
+    TKREF_CHECK(cudaMemcpy(dq, q, qb, cudaMemcpyHostToDevice));
+    TKREF_CHECK(cudaMemcpy(dk, k, kb, cudaMemcpyHostToDevice));
+    titan::cuda::apply_rope_mla(dq, dk, H, Hkv, nope_hd, rope_hd, position, theta, nullptr);
+    TKREF_CHECK(cudaGetLastError());
+    TKREF_CHECK(cudaDeviceSynchronize());
+    TKREF_CHECK(cudaMemcpy(q, dq, qb, cudaMemcpyDeviceToHost));
+    TKREF_CHECK(cudaMemcpy(k, dk, kb, cudaMemcpyDeviceToHost));
+    cudaFree(dq); cudaFree(dk);
+    return 0;
+}
+
 }  // extern "C"

@@ -170,6 +170,31 @@ void tko_attention_decode_f32(const float* q, const float* k_cache, const float*
     free(scores);
 }
 
+/* rope_mla_kernel, src/compute/cuda/attention.cu:259-294: the same rotation on the rope dims only
+ * (the last rope_hd dims of rows of nope_hd + rope_hd), freq = 1/powf(theta, d/rope_hd), no scaling. */
+void tko_rope_mla_f32(float* q, float* k, int num_heads, int num_kv_heads, int nope_hd, int rope_hd,
+                      int position, float theta_base) {
+    int max_heads = num_heads > num_kv_heads ? num_heads : num_kv_heads;
+    int head_dim = nope_hd + rope_hd;
+    for (int head = 0; head < max_heads; head++) {
+        for (int d = 0; d < rope_hd; d += 2) {
+            float freq = 1.0f / powf(theta_base, (float)d / rope_hd);
+            float angle = position * freq;
+            float c = cosf(angle), s = sinf(angle);
+            if (head < num_heads) {
+                float* qh = q + (size_t)head * head_dim + nope_hd;
+                float a = qh[d], b = qh[d + 1];
+                qh[d] = a * c - b * s; qh[d + 1] = a * s + b * c;
+            }
+            if (head < num_kv_heads) {
+                float* kh = k + (size_t)head * head_dim + nope_hd;
+                float a = kh[d], b = kh[d + 1];
+                kh[d] = a * c - b * s; kh[d + 1] = a * s + b * c;
+            }
+        }
+    }
+}
+
 /* rope_kernel, src/compute/cuda/attention.cu:15-48: interleaved pairs (d, d+1),
  * freq = (1/powf(theta, d/D)) * scaling, angle = position * freq. */
 void tko_rope_f32(float* q, float* k, int num_heads, int num_kv_heads, int head_dim,

@@ -127,6 +127,9 @@ void tko_combine(int n_parts, const float* m, const float* l, const float* o, in
 /* ---- "next" row: RoPE exactly as rope_kernel, src/compute/cuda/attention.cu:15-48 */
 void tko_rope_f32(float* q, float* k, int num_heads, int num_kv_heads, int head_dim,
                   int position, float theta_base, float rope_scaling);
+/* ... and as rope_mla_kernel, src/compute/cuda/attention.cu:259-294 (rope dims of MLA rows only) */
+void tko_rope_mla_f32(float* q, float* k, int num_heads, int num_kv_heads, int nope_hd, int rope_hd,
+                      int position, float theta_base);
 
 int tko_num_threads(void);
 

@@ -78,6 +78,7 @@ def lib() -> C.CDLL:
             "tko_decode_partial": (None, [C.POINTER(View), i, i, i, i, vp, vp, vp, vp]),
             "tko_combine": (None, [i, vp, vp, vp, i, vp]),
             "tko_rope_f32": (None, [vp, vp, i, i, i, i, f, f]),
+            "tko_rope_mla_f32": (None, [vp, vp, i, i, i, i, i, f]),
             "tko_num_threads": (i, []),
         }
         for name, (res, args) in sig.items():
@@ -144,6 +145,12 @@ def kv_update_f32(k_data, v_data, L, max_seq, Hkv, D, layer, pos, key, value, se
 def rope_f32(q, k, H, Hkv, D, position, theta, scaling=1.0):
     q, k = _c(q, np.float32).copy(), _c(k, np.float32).copy()
     lib().tko_rope_f32(_p(q), _p(k), H, Hkv, D, position, theta, scaling)
+    return q, k
+
+
+def rope_mla_f32(q, k, H, Hkv, nope, rope, position, theta):
+    q, k = _c(q, np.float32).copy(), _c(k, np.float32).copy()
+    lib().tko_rope_mla_f32(_p(q), _p(k), H, Hkv, nope, rope, position, theta)
     return q, k
 
 
@@ -285,6 +292,8 @@ def ref_lib() -> Optional[C.CDLL]:
         r.tkref_attention_decode_mla.argtypes = [vp, vp, vp, vp, i, i, i, i, i]
         r.tkref_apply_rope.restype = i
         r.tkref_apply_rope.argtypes = [vp, vp, i, i, i, i, f, f]
+        r.tkref_apply_rope_mla.restype = i
+        r.tkref_apply_rope_mla.argtypes = [vp, vp, i, i, i, i, i, f]
         _ref = r
     return _ref
 
@@ -316,6 +325,14 @@ def ref_update_and_decode(k, v, q, L, layer, H, Hkv, D, seq_len, max_seq_len):
     if st != 0:
         raise RuntimeError(f"reference update+decode failed: cudaError {st}")
     return out, n.value
+
+
+def ref_apply_rope_mla(q, k, H, Hkv, nope, rope, position, theta):
+    q, k = _c(q, np.float32).copy(), _c(k, np.float32).copy()
+    st = ref_lib().tkref_apply_rope_mla(_p(q), _p(k), H, Hkv, nope, rope, position, theta)
+    if st != 0:
+        raise RuntimeError(f"reference apply_rope_mla failed: cudaError {st}")
+    return q, k
 
 
 def ref_apply_rope(q, k, H, Hkv, D, position, theta, scaling=1.0):

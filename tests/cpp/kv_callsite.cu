@@ -49,6 +49,7 @@ static int run_mla(const char* path, int n_tokens) {
             CHECK(cudaMemcpyAsync(dq, q.data(), q.size() * 4, cudaMemcpyHostToDevice, stream));
             CHECK(cudaMemcpyAsync(dk, k.data(), k.size() * 4, cudaMemcpyHostToDevice, stream));
             CHECK(cudaMemcpyAsync(dv, v.data(), v.size() * 4, cudaMemcpyHostToDevice, stream));
+            titan::cuda::apply_rope_mla(dq, dk, H, Hkv, Dk - 64, 64, pos, 10000.0f, stream);
             cache.update(l, pos, dk, dv, stream);
             const int seq_len = cache.seq_len();
             if (seq_len != pos + 1) { fprintf(stderr, "seq_len %d at pos %d\n", seq_len, pos); return 6; }

@@ -23,6 +23,7 @@ CASES = [  # seed, H, Hkv, D, seq_len
 MLA_CASES = [  # seed, H, Hkv, k_head_dim, v_head_dim, seq_len
     (301, 16, 16, 192, 128, 77), (302, 16, 4, 192, 128, 513),
 ]
+ROPE_MLA_CASES = [(401, 16, 16, 128, 64, 0, 10000.0), (402, 16, 4, 128, 64, 4321, 10000.0)]   # seed, H, Hkv, nope, rope, pos, theta
 ROPE_CASES = [(201, 32, 8, 128, 0, 500000.0), (202, 32, 8, 128, 1234, 500000.0), (203, 8, 2, 64, 77, 10000.0)]
 
 
@@ -63,6 +64,11 @@ def main():
         q, k = rope_inputs(seed, H, Hkv, D)
         rq, rk = O.ref_apply_rope(q, k, H, Hkv, D, pos, theta, 1.0)
         data[f"rope_q_{i}"], data[f"rope_k_{i}"] = rq, rk
+    data["rope_mla_cases"] = np.array(ROPE_MLA_CASES, dtype=np.float64)
+    for i, (seed, H, Hkv, nope, rope, pos, theta) in enumerate(ROPE_MLA_CASES):
+        q, k = rope_inputs(seed, H, Hkv, nope + rope)
+        rq, rk = O.ref_apply_rope_mla(q, k, H, Hkv, nope, rope, pos, theta)
+        data[f"rope_mla_q_{i}"], data[f"rope_mla_k_{i}"] = rq, rk
     path = os.path.join(out_dir, "reference_attention.npz")
     np.savez_compressed(path, **data)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -62,6 +62,21 @@ def test_oracle_rope_matches_reference_golden():
         np.testing.assert_allclose(ok, d[f"rope_k_{i}"], rtol=1e-4, atol=atol)
 
 
+def test_oracle_rope_mla_matches_reference_golden():
+    """apply_rope_mla of the reference (rope dims of 128 + 64 rows), run on a B200."""
+    d = _load()
+    np.testing.assert_array_equal(d["rope_mla_cases"], np.array(G.ROPE_MLA_CASES, dtype=np.float64))
+    for i, (seed, H, Hkv, nope, rope, pos, theta) in enumerate(G.ROPE_MLA_CASES):
+        H, Hkv, nope, rope, pos = int(H), int(Hkv), int(nope), int(rope), int(pos)
+        q, k = G.rope_inputs(int(seed), H, Hkv, nope + rope)
+        oq, ok = O.rope_mla_f32(q, k, H, Hkv, nope, rope, pos, float(theta))
+        atol = 2e-4 + 2e-6 * pos
+        np.testing.assert_allclose(oq, d[f"rope_mla_q_{i}"], rtol=1e-4, atol=atol)
+        np.testing.assert_allclose(ok, d[f"rope_mla_k_{i}"], rtol=1e-4, atol=atol)
+        np.testing.assert_array_equal(oq[:, :nope], q[:, :nope])          # the nope dims are untouched
+        assert np.abs(oq[:, nope:] - q[:, nope:]).max() > (0.1 if pos else -1)
+
+
 def test_oracle_mla_attention_matches_reference_golden():
     """attention_decode_mla (K rows of 192, V rows of 128) of the reference, run on a B200."""
     d = _load()

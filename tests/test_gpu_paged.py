@@ -331,6 +331,68 @@ def test_rope_append_decode_fused(shape):
     t.gpu.device_status()
 
 
+@pytest.mark.parametrize("impl", ["mma", "simt"])
+@pytest.mark.parametrize("heads", [(16, 16), (32, 8)])
+def test_rope_append_decode_mla_shape(heads, impl):
+    """The MLA layer step as one call: apply_rope_mla (only the 64 rope dims at the end of the 192-wide q / K
+    rows rotate) -> update -> attention_decode_mla.  Oracle: rope_mla_f32 in FP32, rounded to the storage
+    type, appended, attended; K rows may differ by one unit in the last place, V rows not at all."""
+    H, Hkv = heads
+    D, Dv, nope, rope = 192, 128, 128, 64
+    dt, theta = O.BF16, 10000.0
+    t = Twin(2, H, Hkv, D, 120, 3, 60, dtype="bf16", impl=impl, max_step_tokens=1024, seed=72, Dv=Dv)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    g = rng(73)
+
+    def rot(x16, is_q, positions):                      # x16: [rows][heads][192] bits; one position per row
+        xf = O.to_f32(x16, dt)
+        out = np.empty_like(xf)
+        for r, pos in enumerate(positions):
+            if is_q:
+                out[r], _ = O.rope_mla_f32(xf[r], np.zeros((Hkv, D), np.float32), H, Hkv, nope, rope, int(pos), theta)
+            else:
+                _, out[r] = O.rope_mla_f32(np.zeros((H, D), np.float32), xf[r], H, Hkv, nope, rope, int(pos), theta)
+        return O.f32_to_16(out, dt)
+
+    def step(n_new):
+        old = [t.gpu.seq_len(s) for s in seqs]
+        t.gpu.step_begin(seqs, n_new)
+        for s, n in zip(seqs, n_new):
+            assert t.mgr.reserve(s, n) == O.OK
+        assert t.gpu.digest() == t.mgr.digest()
+        table = t.mgr.table()
+        tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seqs, n_new)])
+        tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)])
+        lens = [t.gpu.seq_len(s) for s in seqs]
+        q_pos = [n - 1 for n in lens]
+        n0 = t.gpu.launch_count
+        for layer in range(2):
+            k16 = normal16(g, (len(tok_seq), Hkv, D), dt); v16 = normal16(g, (len(tok_seq), Hkv, Dv), dt)
+            q16 = normal16(g, (3, H, D), dt)
+            got = t.gpu.rope_append_decode(layer, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev),
+                                           to_torch16(q16, dt, t.dev), theta).float().cpu().numpy()
+            t.pools[layer].append(table, tok_seq, tok_pos, rot(k16, False, tok_pos), v16)
+            want = t.pools[layer].decode(table, seqs, lens, rot(q16, True, q_pos))
+            assert_close(got, want, f"rope+append+decode (MLA shape) layer {layer}", out_mantissa_bits=7)
+            pool = from_torch16(t.gpu.layer_views(layer)[0])                     # [pages][Hkv][16*192 K | 16*128 V]
+            np.testing.assert_array_equal(pool[:, :, 16 * D:], t.pools[layer].pool[:, :, 16 * D:])   # V: plain copy
+            kg = O.to_f32(pool[:, :, :16 * D], dt).reshape(-1, 16, D)
+            kw = O.to_f32(t.pools[layer].pool[:, :, :16 * D], dt).reshape(-1, 16, D)
+            np.testing.assert_array_equal(kg[:, :, :nope], kw[:, :, :nope])      # nope dims: plain copy
+            ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(kw), 0.05))) - 7)
+            assert (np.abs(kg - kw) <= ulp).all(), "rotated K rows differ by more than one ulp"
+            assert (kg == kw).mean() > 0.98
+        return t.gpu.launch_count - n0
+
+    step([300, 17, 1])                                  # prefill: rope kernel + append + decode
+    launches = step([1, 1, 1])
+    if impl == "mma":
+        assert launches <= 4                            # one kernel per layer (+ table patch, + cos/sin table)
+    for _ in range(18):
+        step([1, 1, 1])
+    t.gpu.device_status()
+
+
 def test_scheduler_drives_churn_on_gpu():
     """The continuous-batching scheduler as the caller: requests arrive, prefill in chunks, decode,
     finish and get preempted on a small pool; every step's page state is bit-exact against the
@@ -468,3 +530,36 @@ def test_mla_wide_group_falls_back_to_generic_kernel():
     t.step([s], [1], check_pool=True, fused=True)
     with pytest.raises(KvError):
         PagedKVCache(1, 16, 1, 192, 20, 1, 20, dtype="fp16", decode_impl="mma", v_head_dim=128)
+
+
+def test_shard_by_kv_head_outputs_are_head_slices_of_the_whole():
+    """The other way to spread a small batch over GPUs: rank r keeps kv heads [r*Hkv/N, ...) and the query
+    heads that map onto them.  Two such caches (both on this GPU) fed the matching slices of k, v and q
+    must reproduce, head for head, the outputs of one cache holding every head."""
+    from titan_engine_b200 import PagedKVCache
+    from titan_engine_b200 import dist as D
+    H, Hkv, Dh, world = 32, 8, 128, 2
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev); gen.manual_seed(77)
+    lens = [700, 33, 1500]
+    mk = lambda h, hkv: PagedKVCache(1, h, hkv, Dh, 200, 3, 100, dtype="bf16", max_step_tokens=4096, chunk_tokens=256)
+    whole = mk(H, Hkv)
+    shards = [mk(H // world, Hkv // world) for _ in range(world)]
+    seqs = [whole.seq_alloc() for _ in lens]
+    for c in shards:
+        assert [c.seq_alloc() for _ in lens] == seqs
+    n = sum(lens)
+    k = torch.randn(n, Hkv, Dh, device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(n, Hkv, Dh, device=dev, generator=gen).to(torch.bfloat16)
+    q = torch.randn(len(lens), H, Dh, device=dev, generator=gen).to(torch.bfloat16)
+    whole.step_begin(seqs, lens)
+    whole.append(0, k, v)
+    want = whole.decode(0, q)
+    for r, c in enumerate(shards):
+        kvr, qr = D.shard_kv_heads(Hkv, H, r, world)
+        c.step_begin(seqs, lens)
+        c.append(0, k[:, kvr.start:kvr.stop].contiguous(), v[:, kvr.start:kvr.stop].contiguous())
+        got = c.decode(0, q[:, qr.start:qr.stop].contiguous())
+        assert torch.equal(got, want[:, qr.start:qr.stop]), f"rank {r}"
+        c.close()
+    whole.close()

@@ -89,6 +89,18 @@ def test_rope_oracle_matches_reference_kernel(ref):
         np.testing.assert_allclose(ok, rk, rtol=1e-4, atol=atol)
 
 
+def test_rope_mla_oracle_matches_reference_kernel(ref):
+    H, Hkv, nope, rope = 16, 4, 128, 64
+    g = rng(10)
+    q = g.standard_normal((H, nope + rope), dtype=np.float32); k = g.standard_normal((Hkv, nope + rope), dtype=np.float32)
+    for pos in (0, 3, 500, 8191):
+        rq, rk = O.ref_apply_rope_mla(q, k, H, Hkv, nope, rope, pos, 10000.0)
+        oq, ok = O.rope_mla_f32(q, k, H, Hkv, nope, rope, pos, 10000.0)
+        atol = 2e-4 + 2e-6 * pos
+        np.testing.assert_allclose(oq, rq, rtol=1e-4, atol=atol)
+        np.testing.assert_allclose(ok, rk, rtol=1e-4, atol=atol)
+
+
 @pytest.mark.parametrize("case", [(16, 16, 192, 128, 77), (16, 4, 192, 128, 1000)])
 def test_mla_oracle_and_library_match_reference_kernel(ref, case):
     """attention_decode_mla of the reference vs the oracle (FP32) and vs the paged library (bf16)."""

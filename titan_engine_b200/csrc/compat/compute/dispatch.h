@@ -24,6 +24,10 @@ void attention_decode_mla(const float* q, const float* k_cache, const float* v_c
 // (reference: rope_kernel, src/compute/cuda/attention.cu:15-48).
 void apply_rope(float* q, float* k, int num_heads, int num_kv_heads, int head_dim, int position,
                 float theta, float scaling, cudaStream_t stream);
+// The same on the rope dims only: the last rope_hd dims of rows of nope_hd + rope_hd
+// (reference: rope_mla_kernel, src/compute/cuda/attention.cu:259-294,351-366).
+void apply_rope_mla(float* q, float* k, int num_heads, int num_kv_heads, int nope_hd, int rope_hd, int position,
+                    float theta, cudaStream_t stream);
 
 }  // namespace cuda
 }  // namespace titan

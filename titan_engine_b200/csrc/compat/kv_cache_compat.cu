@@ -75,6 +75,31 @@ __global__ void compat_rope_kernel(float* __restrict__ q, float* __restrict__ k,
     }
 }
 
+// Same arithmetic as the reference's rope_mla_kernel (src/compute/cuda/attention.cu:259-294): only the
+// rope dims, freq = 1/powf(theta, d/rope_hd).  One thread per (head, pair).
+__global__ void compat_rope_mla_kernel(float* __restrict__ q, float* __restrict__ k, int num_heads, int num_kv_heads,
+                                       int nope_hd, int rope_hd, int position, float theta_base) {
+    const int head = blockIdx.x;
+    const int d = threadIdx.x * 2;
+    if (d >= rope_hd) return;
+    const float freq = 1.0f / powf(theta_base, (float)d / rope_hd);
+    const float angle = position * freq;
+    const float c = cosf(angle), s = sinf(angle);
+    const int head_dim = nope_hd + rope_hd;
+    if (head < num_heads) {
+        float* p = q + (size_t)head * head_dim + nope_hd;
+        const float a = p[d], b = p[d + 1];
+        p[d] = a * c - b * s;
+        p[d + 1] = a * s + b * c;
+    }
+    if (head < num_kv_heads) {
+        float* p = k + (size_t)head * head_dim + nope_hd;
+        const float a = p[d], b = p[d + 1];
+        p[d] = a * c - b * s;
+        p[d + 1] = a * s + b * c;
+    }
+}
+
 }  // namespace
 
 KVCache::~KVCache() { release(); }
@@ -304,6 +329,15 @@ void apply_rope(float* q, float* k, int num_heads, int num_kv_heads, int head_di
     const int threads = head_dim / 2;
     if (max_heads <= 0 || threads <= 0) return;
     compat_rope_kernel<<<max_heads, threads, 0, stream>>>(q, k, num_heads, num_kv_heads, head_dim, position, theta, scaling);
+}
+
+void apply_rope_mla(float* q, float* k, int num_heads, int num_kv_heads, int nope_hd, int rope_hd, int position,
+                    float theta, cudaStream_t stream) {
+    const int max_heads = num_heads > num_kv_heads ? num_heads : num_kv_heads;
+    const int threads = rope_hd / 2;
+    if (threads < 1 || max_heads < 1) return;
+    compat_rope_mla_kernel<<<max_heads, threads, 0, stream>>>(q, k, num_heads, num_kv_heads, nope_hd, rope_hd, position,
+                                                             theta);
 }
 
 }  // namespace cuda

@@ -102,10 +102,16 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     {
         const uint16_t* qrow = q + ((size_t)b * g.H + (size_t)kvh * G + gr) * kDk;
         const bool valid = gr < G;
+        // fused RoPE: the query is the token at position len-1; only dims kDv.. (the rope dims) rotate
+        const float2* tab = fa.rope_tab ? fa.rope_tab + (size_t)b * ((kDk - kDv) / 2) : nullptr;
 #pragma unroll
         for (int kk = 0; kk < KS; kk++) {
             qa[kk][0] = valid ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 2 * j) : 0u;
             qa[kk][1] = valid ? *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8 + 2 * j) : 0u;
+            if (16 * kk >= kDv && tab) {
+                qa[kk][0] = rope_pair<BF>(qa[kk][0], tab, 16 * kk - kDv + 2 * j);
+                qa[kk][1] = rope_pair<BF>(qa[kk][1], tab, 16 * kk - kDv + 8 + 2 * j);
+            }
         }
     }
 
@@ -131,7 +137,15 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
             const int r = (len - 1) & (kPage - 1);
             const int page = __shfl_sync(0xFFFFFFFFu, my_page, i);
             if (lane < kDk / 8) {
-                const uint4 val = *reinterpret_cast<const uint4*>((const uint16_t*)fa.k + ((size_t)new_tok * g.Hkv + kvh) * kDk + lane * 8);
+                uint4 val = *reinterpret_cast<const uint4*>((const uint16_t*)fa.k + ((size_t)new_tok * g.Hkv + kvh) * kDk + lane * 8);
+                if (fa.rope_tab && lane >= kDv / 8) {           // rope dims of the K row: rotate its 4 pairs before it is stored
+                    const float2* tab = fa.rope_tab + (size_t)b * ((kDk - kDv) / 2);
+                    const int d = lane * 8 - kDv;
+                    val.x = rope_pair<BF>(val.x, tab, d + 0);
+                    val.y = rope_pair<BF>(val.y, tab, d + 2);
+                    val.z = rope_pair<BF>(val.z, tab, d + 4);
+                    val.w = rope_pair<BF>(val.w, tab, d + 6);
+                }
                 *reinterpret_cast<uint4*>(stg + k_off(r, lane)) = val;
                 *reinterpret_cast<uint4*>((uint16_t*)lp.pool + tile_offset(g, page, kvh, 0) + (size_t)r * kDk + lane * 8) = val;
             }

@@ -6,6 +6,9 @@
 // Positions come from the step plan: a q row belongs to the newest token of its sequence
 // (len-1), a k row to its own token.  On decode steps with 16-bit storage this kernel is not
 // launched at all — the rotation rides inside the attention kernel (decode_mma.cu).
+// The MLA cache shape rotates only the rope dims at the end of each q / K row, with
+// freq = 1/powf(theta, d/rope_dims) (rope_mla_kernel, src/compute/cuda/attention.cu:259-294):
+// rope_off(g) dims are copied, the remaining rope_dims(g) rotated.
 #include "tk_kernels.cuh"
 
 #include <cuda_bf16.h>
@@ -15,6 +18,7 @@ namespace tk {
 
 namespace {
 
+// src / dst point at the first rotated dim of the row; d counts from there, D = number of rotated dims
 template <bool BF16>
 __device__ __forceinline__ void rotate_store(const uint16_t* src, uint16_t* dst, int d, int D, int position,
                                              float theta, float scaling) {
@@ -40,30 +44,30 @@ __device__ __forceinline__ void rotate_store(const uint16_t* src, uint16_t* dst,
 template <bool BF16>
 __global__ void rope16_kernel(Geometry g, StepDev st, const uint16_t* __restrict__ q, const uint16_t* __restrict__ k,
                               uint16_t* __restrict__ q_out, uint16_t* __restrict__ k_out, float theta, float scaling) {
-    const int half = g.D / 2;
-    if ((int)blockIdx.x < st.n_seqs) {
-        const int b = blockIdx.x, pos = st.len[b] - 1;
-        for (int i = threadIdx.x; i < g.H * half; i += blockDim.x) {
-            const size_t row = ((size_t)b * g.H + i / half) * g.D;
-            rotate_store<BF16>(q + row, q_out + row, (i % half) * 2, g.D, pos < 0 ? 0 : pos, theta, scaling);
-        }
-    } else {
-        const int t = blockIdx.x - st.n_seqs, pos = st.tok_pos[t];
-        for (int i = threadIdx.x; i < g.Hkv * half; i += blockDim.x) {
-            const size_t row = ((size_t)t * g.Hkv + i / half) * g.D;
-            rotate_store<BF16>(k + row, k_out + row, (i % half) * 2, g.D, pos, theta, scaling);
-        }
+    const int half = g.D / 2, off = rope_off(g), rd = rope_dims(g);
+    const bool is_q = (int)blockIdx.x < st.n_seqs;
+    const int unit = is_q ? blockIdx.x : blockIdx.x - st.n_seqs;         // sequence of the step, or token
+    const int heads = is_q ? g.H : g.Hkv;
+    int pos = is_q ? st.len[unit] - 1 : st.tok_pos[unit];
+    if (pos < 0) pos = 0;
+    const uint16_t* src = is_q ? q : k;
+    uint16_t* dst = is_q ? q_out : k_out;
+    for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+        const size_t row = ((size_t)unit * heads + i / half) * g.D;
+        const int d = (i % half) * 2;
+        if (d < off) { dst[row + d] = src[row + d]; dst[row + d + 1] = src[row + d + 1]; }
+        else rotate_store<BF16>(src + row + off, dst + row + off, d - off, rd, pos, theta, scaling);
     }
 }
 
 // (cos, sin) of every sequence's newest position, one entry per pair: tab[b][d/2].
 __global__ void rope_table_kernel(Geometry g, StepDev st, float2* __restrict__ tab, float theta, float scaling) {
-    const int half = g.D / 2;
+    const int rd = rope_dims(g), half = rd / 2;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= st.n_seqs * half) return;
     const int b = i / half, d = (i % half) * 2;
     const int pos = st.len[b] > 0 ? st.len[b] - 1 : 0;
-    float freq = 1.0f / powf(theta, (float)d / g.D);
+    float freq = 1.0f / powf(theta, (float)d / rd);
     freq *= scaling;
     const float angle = pos * freq;
     tab[i] = make_float2(cosf(angle), sinf(angle));
@@ -73,7 +77,7 @@ __global__ void rope_table_kernel(Geometry g, StepDev st, float2* __restrict__ t
 
 cudaError_t launch_rope_table(const Geometry& g, const StepDev& st, float2* tab, float theta, float scaling,
                               cudaStream_t s) {
-    const int n = st.n_seqs * (g.D / 2);
+    const int n = st.n_seqs * (rope_dims(g) / 2);
     if (n <= 0) return cudaSuccess;
     rope_table_kernel<<<(n + 255) / 256, 256, 0, s>>>(g, st, tab, theta, scaling);
     return cudaGetLastError();

@@ -828,8 +828,6 @@ int tk_kv_rope_append_decode(tk_kv* h, int32_t layer, const void* k, const void*
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "rope_append_decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "rope_append_decode: no step in progress (call tk_kv_step_begin)");
     if (!q || !out || (h->dev.n_tokens > 0 && (!k || !v))) return fail(h, TK_INVALID_ARG, "rope_append_decode: null argument");
-    if (h->cfg.v_head_dim != h->cfg.head_dim)
-        return fail(h, TK_UNSUPPORTED, "rope_append_decode: the MLA shape rotates only its rope dims; rotate before the call");
     const bool fusable = h->use_mma && h->cfg.dtype != TK_FP8_E4M3 && h->plan.one_token_steps &&
                          h->dev.chunk_tokens <= 2048 && h->dev.n_tokens > 0 && h->dev.n_seqs > 0 &&
                          !h->plan.has_empty_seq && !h->separate_append;

@@ -24,6 +24,11 @@ __host__ __device__ inline size_t tile_offset(const Geometry& g, int page, int k
     return ((size_t)page * g.Hkv + kvh) * (size_t)g.ps * (g.D + g.Dv) + (kv ? (size_t)g.ps * g.D : 0);
 }
 
+// Rotary embedding covers the whole row, except for the MLA cache shape (D != Dv), whose q / K rows
+// are [nope dims = Dv][rope dims = D - Dv] and only the rope dims rotate.
+__host__ __device__ inline int rope_off(const Geometry& g) { return g.D != g.Dv ? g.Dv : 0; }
+__host__ __device__ inline int rope_dims(const Geometry& g) { return g.D - rope_off(g); }
+
 // One layer of the pool.  16-bit / FP8 codes: [num_pages][Hkv][2 (K,V)][ps][D];
 // scales f32 [num_pages][Hkv][2]; open pages [max_seqs][Hkv][2][ps][D] in io_dtype.
 struct LayerPtrs {
@@ -76,7 +81,8 @@ struct FuseAppend {
     const void* v;
     // rope_tab != null: q and the new K row are rotated on the fly (interleaved pairs (d, d+1))
     // before they are used/stored; rope_tab[b][d/2] = (cos, sin) of position len_b - 1, filled once
-    // per step by launch_rope_table with freq = (1/powf(theta, d/D)) * scaling, angle = pos * freq
+    // per step by launch_rope_table with freq = (1/powf(theta, d/rope_dims)) * scaling, angle = pos * freq,
+    // d counted from the first rotated dim (rope_off)
     const float2* rope_tab;
 };
 
