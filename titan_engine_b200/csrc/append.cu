@@ -55,8 +55,11 @@ append_rows_kernel(Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restri
                    const uint16_t* __restrict__ k, const uint16_t* __restrict__ v,
                    int64_t* __restrict__ slots_out) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * kAppendWarps + warp;
-    if (t >= st.n_tokens) return;
+    // with slots_out every token is visited; otherwise FP8 visits only the rows that stay open
+    const bool listed = g.dtype == DT_FP8 && !slots_out;
+    const int i_tok = blockIdx.x * kAppendWarps + warp;
+    if (i_tok >= (listed ? st.n_open : st.n_tokens)) return;
+    const int t = listed ? st.tok_open[i_tok] : i_tok;
     if (slots_out && lane == 0) {                       // pool slot of the token (what a caller would index)
         const int b = st.tok_b[t], pos = st.tok_pos[t];
         const int page = page_table[(size_t)st.seq[b] * g.max_pages_per_seq + pos / g.ps];
@@ -258,7 +261,9 @@ cudaError_t launch_append(const Geometry& g, const LayerPtrs& lp, const StepDev&
         (*n_launches)++;
         if (e != cudaSuccess) return e;
     }
-    append_rows_kernel<<<(st.n_tokens + kAppendWarps - 1) / kAppendWarps, kAppendWarps * 32, 0, s>>>(
+    const int n_rows = (g.dtype == DT_FP8 && !slots_out) ? st.n_open : st.n_tokens;
+    if (n_rows <= 0) return cudaSuccess;                    // FP8: every row of the step went into a sealed page
+    append_rows_kernel<<<(n_rows + kAppendWarps - 1) / kAppendWarps, kAppendWarps * 32, 0, s>>>(
         g, lp, st, page_table, (const uint16_t*)k, (const uint16_t*)v, slots_out);
     (*n_launches)++;
     return cudaGetLastError();

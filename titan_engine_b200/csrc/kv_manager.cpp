@@ -294,7 +294,7 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     plan->seq.assign(seqs, seqs + n_seqs);
     plan->len.resize(n_seqs);
     plan->chunk_base.assign(n_seqs + 1, 0);
-    plan->tok_b.clear(); plan->tok_pos.clear(); plan->tok_dst.clear(); plan->items.clear(); plan->seals.clear();
+    plan->tok_b.clear(); plan->tok_pos.clear(); plan->tok_dst.clear(); plan->tok_open.clear(); plan->items.clear(); plan->seals.clear();
     plan->evictions.clear();
     plan->new_tok.assign(n_seqs, -1);
     plan->one_token_steps = true;
@@ -321,7 +321,10 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         for (int p = old_len; p < full_len; p++) {
             plan->tok_b.push_back(i);
             plan->tok_pos.push_back(p);
-            if (fp8) plan->tok_dst.push_back(p < sealed_end ? -1 : s * ps + p % ps);
+            if (fp8) {
+                if (p >= sealed_end) plan->tok_open.push_back((int32_t)plan->tok_b.size() - 1);
+                plan->tok_dst.push_back(p < sealed_end ? -1 : s * ps + p % ps);
+            }
             else plan->tok_dst.push_back(table_[(size_t)s * max_pages_per_seq_ + p / ps] * ps + p % ps);
         }
         if (fp8)

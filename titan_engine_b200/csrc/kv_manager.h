@@ -46,6 +46,7 @@ struct StepPlan {
     std::vector<int32_t> tok_b;      // [n_tokens] index into seq[]
     std::vector<int32_t> tok_pos;    // [n_tokens] position inside the sequence
     std::vector<int32_t> tok_dst;    // [n_tokens] destination row: pool slot, FP8: open-page slot or -1 (sealed)
+    std::vector<int32_t> tok_open;   // FP8: the tokens (indices into the lists above) that stay in an open page
     std::vector<int32_t> new_tok;    // [n_seqs] row of the sequence's single new token, or -1
     bool one_token_steps = false;    // every sequence appends at most one token (a decode step)
     bool has_empty_seq = false;      // some sequence attends to zero tokens

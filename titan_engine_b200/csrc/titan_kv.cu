@@ -258,7 +258,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->max_seals = c.max_step_tokens / c.page_size + c.max_seqs;
 
     // one buffer holds every per-step array; sections are 16-byte aligned
-    size_t ints = 4 * (size_t)c.max_seqs + 4 + 12 + 3 * (size_t)c.max_step_tokens + 12 +
+    size_t ints = 4 * (size_t)c.max_seqs + 4 + 12 + 4 * (size_t)c.max_step_tokens + 16 +
                   4 * (size_t)h->max_items + 4 * (size_t)h->max_seals + 2 * (size_t)kMaxDelta + 32;
     h->step_bytes = align_up(ints * 4, 256);
 
@@ -411,9 +411,9 @@ int prefetch_layer(tk_kv* h, int layer, bool ahead) {
 }
 
 struct Sections {       // offsets (in int32 units) of the arrays inside a step buffer
-    size_t seq, len, chunk_base, new_tok, tok_b, tok_pos, tok_dst, items, seals, delta, end;
+    size_t seq, len, chunk_base, new_tok, tok_b, tok_pos, tok_dst, tok_open, items, seals, delta, end;
 };
-Sections sections(int n_seqs, int n_tokens, int n_items, int n_seals, int n_delta) {
+Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals, int n_delta) {
     auto a4 = [](size_t x) { return (x + 3) / 4 * 4; };
     Sections s{};
     size_t o = 0;
@@ -424,6 +424,7 @@ Sections sections(int n_seqs, int n_tokens, int n_items, int n_seals, int n_delt
     s.tok_b = o;      o = a4(o + n_tokens);
     s.tok_pos = o;    o = a4(o + n_tokens);
     s.tok_dst = o;    o = a4(o + n_tokens);
+    s.tok_open = o;   o = a4(o + n_open);
     s.items = o;      o = a4(o + 4 * (size_t)n_items);
     s.seals = o;      o = a4(o + 4 * (size_t)n_seals);
     s.delta = o;      o = a4(o + 2 * (size_t)n_delta);
@@ -637,7 +638,8 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     const int n_tok = (int)p.tok_b.size(), n_items = (int)p.items.size(), n_seals = (int)p.seals.size();
     if (n_items > h->max_items || n_seals > h->max_seals)
         return fail(h, TK_INVALID_ARG, "step_begin: work list exceeds the workspace (%d items, %d seals)", n_items, n_seals);
-    Sections sec = sections(n_seqs, n_tok, n_items, n_seals, n_delta);
+    const int n_open = (int)p.tok_open.size();
+    Sections sec = sections(n_seqs, n_tok, n_open, n_items, n_seals, n_delta);
     if (sec.end * 4 > h->step_bytes) return fail(h, TK_INVALID_ARG, "step_begin: step metadata exceeds its buffer");
 
     const int r = h->ring_pos;
@@ -654,6 +656,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
         memcpy(w + sec.tok_b, p.tok_b.data(), 4 * (size_t)n_tok);
         memcpy(w + sec.tok_pos, p.tok_pos.data(), 4 * (size_t)n_tok);
         memcpy(w + sec.tok_dst, p.tok_dst.data(), 4 * (size_t)n_tok);
+        if (n_open) memcpy(w + sec.tok_open, p.tok_open.data(), 4 * (size_t)n_open);
     }
     if (n_items) memcpy(w + sec.items, p.items.data(), 16 * (size_t)n_items);
     if (n_seals) memcpy(w + sec.seals, p.seals.data(), 16 * (size_t)n_seals);
@@ -668,10 +671,10 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     tk::StepDev& dv = h->dev;
     dv.seq = d + sec.seq; dv.len = d + sec.len; dv.chunk_base = d + sec.chunk_base;
     dv.new_tok = d + sec.new_tok;
-    dv.tok_b = d + sec.tok_b; dv.tok_pos = d + sec.tok_pos; dv.tok_dst = d + sec.tok_dst;
+    dv.tok_b = d + sec.tok_b; dv.tok_pos = d + sec.tok_pos; dv.tok_dst = d + sec.tok_dst; dv.tok_open = d + sec.tok_open;
     dv.items = (const int4*)(d + sec.items); dv.seals = (const int4*)(d + sec.seals);
     dv.n_seqs = n_seqs; dv.n_tokens = n_tok; dv.n_items = n_items; dv.n_seals = n_seals;
-    dv.chunk_tokens = p.chunk_tokens;
+    dv.chunk_tokens = p.chunk_tokens; dv.n_open = n_open;
     if (n_delta) {
         TK_CUDA(h, tk::launch_apply_delta(h->d_table, (const int2*)(d + sec.delta), n_delta, s));
         h->launches++;

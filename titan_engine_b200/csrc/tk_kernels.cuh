@@ -50,10 +50,12 @@ struct StepDev {
     const int32_t* tok_pos;     // [n_tokens]
     const int32_t* tok_dst;     // [n_tokens] row the token is stored to: page*ps + r of the pool (16-bit
                                 //   storage), seq*ps + r of the open pages (FP8), -1 = sealed by this step
+    const int32_t* tok_open;    // FP8: [n_open] tokens that stay in an open page (the only rows the row kernel copies)
     const int4*    items;       // [n_items] (b, chunk, kvh, kind)
     const int4*    seals;       // [n_seals] (seq slot, physical page, rows from the open page, token of the next row)
     const int32_t* new_tok;     // [n_seqs] row of the sequence's single new token in k/v, or -1
     int n_seqs, n_tokens, n_items, n_seals, chunk_tokens;
+    int n_open;
 };
 
 // partial row layout: [row][H][D+2] f32 = o[0..D) unnormalised, m at [D], l at [D+1]
