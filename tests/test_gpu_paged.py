@@ -563,3 +563,75 @@ def test_shard_by_kv_head_outputs_are_head_slices_of_the_whole():
         assert torch.equal(got, want[:, qr.start:qr.stop]), f"rank {r}"
         c.close()
     whole.close()
+
+
+@pytest.mark.parametrize("shape", [
+    # H, Hkv, D, dtype, tokens per sequence and step
+    (32, 8, 128, "bf16", 4),     # 8B head shape: 4 heads x 4 tokens fill the 16 rows of the tile
+    (32, 8, 128, "fp16", 3),
+    (8, 2, 64, "fp16", 4),
+    (16, 16, 128, "bf16", 16),   # MHA: 16 tokens
+    (16, 16, 64, "bf16", 5),
+    (16, 1, 64, "fp16", 1),      # 16 heads per kv head: one token only
+])
+def test_decode_multi_tokens_causal(shape):
+    """Every token a step appended gets its own attention output, causal among the step's tokens, from one
+    pass over the pages (the verification of drafted tokens).  Oracle: the single-token decode of the
+    oracle, once per token, with the length cut at that token.  Then the rejected tokens are rolled back."""
+    H, Hkv, D, dtype, k = shape
+    dt = DT[dtype]
+    t = Twin(2, H, Hkv, D, 300, 4, 80, dtype=dtype, impl="mma", max_step_tokens=2048, seed=90, chunk_tokens=256)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [700, 13, 250])
+    g = rng(91)
+    bits = 7 if dt == O.BF16 else 10
+
+    def multi_step(n_new):
+        old = [t.gpu.seq_len(s) for s in seqs]
+        t.gpu.step_begin(seqs, n_new)
+        for s, n in zip(seqs, n_new):
+            assert t.mgr.reserve(s, n) == O.OK
+        assert t.gpu.digest() == t.mgr.digest()
+        table = t.mgr.table()
+        tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seqs, n_new)])
+        tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)])
+        n0 = t.gpu.launch_count
+        for layer in range(2):
+            k16 = normal16(g, (len(tok_seq), Hkv, D), dt); v16 = normal16(g, (len(tok_seq), Hkv, D), dt)
+            q16 = normal16(g, (len(tok_seq), H, D), dt)
+            t.gpu.append(layer, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev))
+            t.pools[layer].append(table, tok_seq, tok_pos, k16, v16)
+            got = t.gpu.decode_multi(layer, to_torch16(q16, dt, t.dev)).float().cpu().numpy()
+            want = t.pools[layer].decode(table, tok_seq, tok_pos + 1, q16)       # token by token, as the reference would
+            assert_close(got, want, f"multi-token attention layer {layer} {n_new}", out_mantissa_bits=bits)
+        assert t.gpu.launch_count - n0 == 2 * 2              # (append, attention) per layer
+        t.gpu.device_status()
+
+    multi_step([k, k, k])                                    # the second sequence crosses a page boundary (13 -> 13+k)
+    multi_step([k, 1, max(1, k // 2)])                       # ragged
+    for _ in range(3):
+        multi_step([k, k, k])
+    # two of the k tokens of the first sequence are rejected: roll back, then decode on as usual
+    if k > 2:
+        new_len = t.gpu.seq_len(seqs[0]) - 2
+        t.gpu.truncate(seqs[0], new_len); assert t.mgr.truncate(seqs[0], new_len) == O.OK
+    t.step(seqs, [1, 1, 1], check_pool=True)
+
+
+def test_decode_multi_refusals():
+    from titan_engine_b200 import KvError
+    t = Twin(1, 32, 8, 128, 64, 2, 32, dtype="bf16", impl="mma", max_step_tokens=256, seed=92)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a, b], [40, 40])
+    q = torch.zeros(6, 32, 128, device=t.dev, dtype=torch.bfloat16)
+    t.gpu.step_begin([a, b], [5, 1]); assert t.mgr.reserve(a, 5) == O.OK and t.mgr.reserve(b, 1) == O.OK
+    with pytest.raises(KvError):                             # 4 heads per kv head x 5 tokens > 16 rows
+        t.gpu.decode_multi(0, q)
+    t.gpu.step_begin([a, b], [2, 0]); assert t.mgr.reserve(a, 2) == O.OK
+    with pytest.raises(KvError):                             # a sequence without a new token
+        t.gpu.decode_multi(0, q[:2].contiguous())
+    f = Twin(1, 64, 8, 128, 16, 1, 16, dtype="fp8", impl="mma", max_step_tokens=64, seed=93)
+    s = f.seq_alloc()
+    f.gpu.step_begin([s], [2])
+    with pytest.raises(KvError):                             # FP8 pools are not served
+        f.gpu.decode_multi(0, torch.zeros(2, 64, 128, device=f.dev, dtype=torch.bfloat16))

@@ -144,8 +144,13 @@ struct Cfg {
 };
 
 // IO_BF16: type of q (relevant for FP8, where the MMA type is fp16 regardless).
-// GHI: group has more than 8 query heads (rows 8..15 of the M tile carry data).
-template <int KIND, int D, bool IO_BF16, bool GHI>
+// GHI: more than 8 rows of the M tile carry data (a group of more than 8 query heads, or several tokens).
+// MULTI (16-bit pools): every sequence brings nq query tokens - the tokens the step appended, already in
+// the pool - and token j attends causally to positions <= len - nq + j.  Row j*G + gg of the M tile is
+// token j, head gg of the group (G * nq <= 16), so the tokens share one pass over the pages: what a
+// speculative decoder's verification of nq drafted tokens needs (the reference runs the layer once per
+// token there: src/inference/speculative.cpp:262-272).
+template <int KIND, int D, bool IO_BF16, bool GHI, bool MULTI>
 __global__ void __launch_bounds__(kWarps * 32, TK_MMA_MIN_CTAS)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_cold, Geometry g, LayerPtrs lp, StepDev st,
                   const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q,
@@ -170,6 +175,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     }
     const int b = it.x, chunk = it.y, kvh = it.z;
     const int seq = st.seq[b], len = st.len[b];
+    const int nq = MULTI ? st.nq[b] : 1;                    // query tokens of this sequence
+    const int rows = G * nq;                                // rows of the M tile that carry data
+    const int q_row0 = MULTI ? st.q_base[b] : b;            // row of q / out of the sequence's first query token
     const int pool_tokens = KIND == K_FP8 ? (len / kPage) * kPage : len;
     const int t0 = chunk * st.chunk_tokens;
     const int t1 = min(pool_tokens, t0 + st.chunk_tokens);
@@ -215,9 +223,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     // ---- Q fragments (A operand), rows >= G are zero -------------------------------
     uint32_t qa[KS][4];
     {
-        const uint16_t* qrow0 = q + ((size_t)b * g.H + (size_t)kvh * G + gr) * D;
-        const uint16_t* qrow1 = qrow0 + (size_t)8 * D;
-        const bool v0 = gr < G, v1 = GHI && (gr + 8 < G);
+        // row r of the tile: token r / G of the sequence, head r % G of the group
+        const uint16_t* qrow0 = q + ((size_t)(q_row0 + (MULTI ? gr / G : 0)) * g.H + (size_t)kvh * G + (MULTI ? gr % G : gr)) * D;
+        const uint16_t* qrow1 = MULTI ? q + ((size_t)(q_row0 + (gr + 8) / G) * g.H + (size_t)kvh * G + (gr + 8) % G) * D
+                                      : qrow0 + (size_t)8 * D;
+        const bool v0 = gr < rows, v1 = GHI && (gr + 8 < rows);
 #pragma unroll
         for (int kk = 0; kk < KS; kk++) {
             uint32_t w[4];
@@ -273,6 +283,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         const uint32_t stg_u = smem_u32(stg);
         const int tok_base = (lp0 + warp + kWarps * i) * kPage;
         const int n_valid = min(kPage, t1 - tok_base);     // < 16 only on a sequence's last page
+        // tokens of this page that rows gr / gr+8 may attend to (causal limit of their query token)
+        const int nv0 = MULTI ? max(0, min(n_valid, len - nq + gr / G + 1 - tok_base)) : n_valid;
+        const int nv1 = MULTI ? max(0, min(n_valid, len - nq + (gr + 8) / G + 1 - tok_base)) : n_valid;
 
         float sc_k = sm_scale, sc_v = 1.0f;
         if (KIND == K_FP8) {
@@ -342,10 +355,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         {
             const int c0 = 2 * j;                           // token columns of this thread: c0, c0+1, c0+8, c0+9
             float a0 = s0[0] * sc_k, a1 = s0[1] * sc_k, a2 = s1[0] * sc_k, a3 = s1[1] * sc_k;
-            if (c0 >= n_valid) a0 = -1e30f;
-            if (c0 + 1 >= n_valid) a1 = -1e30f;
-            if (c0 + 8 >= n_valid) a2 = -1e30f;
-            if (c0 + 9 >= n_valid) a3 = -1e30f;
+            if (c0 >= nv0) a0 = -1e30f;
+            if (c0 + 1 >= nv0) a1 = -1e30f;
+            if (c0 + 8 >= nv0) a2 = -1e30f;
+            if (c0 + 9 >= nv0) a3 = -1e30f;
             float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
@@ -354,6 +367,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
             const float nb = -mn * kLog2e;
             p0[0] = ex2(fmaf(a0, kLog2e, nb)); p0[1] = ex2(fmaf(a1, kLog2e, nb));
             p1[0] = ex2(fmaf(a2, kLog2e, nb)); p1[1] = ex2(fmaf(a3, kLog2e, nb));
+            if (MULTI) {                                    // a row may see nothing of a page: exp(-1e30 + 1e30) is 1, not 0
+                if (c0 >= nv0) p0[0] = 0.0f;
+                if (c0 + 1 >= nv0) p0[1] = 0.0f;
+                if (c0 + 8 >= nv0) p1[0] = 0.0f;
+                if (c0 + 9 >= nv0) p1[1] = 0.0f;
+            }
             l0 = l0 * alpha + (p0[0] + p0[1] + p1[0] + p1[1]);
             // the running maximum rarely moves after the first pages: skip the 2*NT multiplies then
             if (!__all_sync(0xFFFFFFFFu, mn == m0)) {
@@ -365,10 +384,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         if (GHI) {
             const int c0 = 2 * j;
             float a0 = s0[2] * sc_k, a1 = s0[3] * sc_k, a2 = s1[2] * sc_k, a3 = s1[3] * sc_k;
-            if (c0 >= n_valid) a0 = -1e30f;
-            if (c0 + 1 >= n_valid) a1 = -1e30f;
-            if (c0 + 8 >= n_valid) a2 = -1e30f;
-            if (c0 + 9 >= n_valid) a3 = -1e30f;
+            if (c0 >= nv1) a0 = -1e30f;
+            if (c0 + 1 >= nv1) a1 = -1e30f;
+            if (c0 + 8 >= nv1) a2 = -1e30f;
+            if (c0 + 9 >= nv1) a3 = -1e30f;
             float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
@@ -377,6 +396,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
             const float nb = -mn * kLog2e;
             p0[2] = ex2(fmaf(a0, kLog2e, nb)); p0[3] = ex2(fmaf(a1, kLog2e, nb));
             p1[2] = ex2(fmaf(a2, kLog2e, nb)); p1[3] = ex2(fmaf(a3, kLog2e, nb));
+            if (MULTI) {
+                if (c0 >= nv1) p0[2] = 0.0f;
+                if (c0 + 1 >= nv1) p0[3] = 0.0f;
+                if (c0 + 8 >= nv1) p1[2] = 0.0f;
+                if (c0 + 9 >= nv1) p1[3] = 0.0f;
+            }
             l1 = l1 * alpha + (p0[2] + p0[3] + p1[2] + p1[3]);
             if (!__all_sync(0xFFFFFFFFu, mn == m1)) {
 #pragma unroll
@@ -431,12 +456,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
     __syncthreads();
-    float* red = reinterpret_cast<float*>(smem);            // [kWarps][G][D+2]
-    auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * G + row) * (D + 2) + d]; };
+    float* red = reinterpret_cast<float*>(smem);            // [kWarps][rows][D+2]
+    auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * rows + row) * (D + 2) + d]; };
 #pragma unroll
     for (int half = 0; half < 2; half++) {
         const int row = gr + 8 * half;
-        if (row < G && (half == 0 || GHI)) {
+        if (row < rows && (half == 0 || GHI)) {
             if (KIND == K_FP8) {
 #pragma unroll
                 for (int c = 0; c < D / 16; c++) {
@@ -460,7 +485,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     }
     __syncthreads();
     const int prow = st.chunk_base[b] + chunk;
-    for (int idx = threadIdx.x; idx < G * (D + 2); idx += blockDim.x) {
+    const int heads_per_row = MULTI ? g.H * st.nq_max : g.H;   // columns of a partial row
+    for (int idx = threadIdx.x; idx < rows * (D + 2); idx += blockDim.x) {
         const int row = idx / (D + 2), d = idx % (D + 2);
         float M = -1e30f;
 #pragma unroll
@@ -473,9 +499,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
 #pragma unroll
             for (int w = 0; w < kWarps; w++) val += red_at(w, row, d) * ex2((red_at(w, row, D) - M) * kLog2e);
         }
-        partials[partial_off(prow, kvh * G + row, g.H, D) + d] = val;
+        const int col = MULTI ? (row / G) * g.H + kvh * G + row % G : kvh * G + row;
+        partials[partial_off(prow, col, heads_per_row, D) + d] = val;
     }
-    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag);
+    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag, MergeMap{rows, heads_per_row, q_row0});
 }
 
 // One warp waits, with the same bounded wait the decode kernel uses, on a barrier that nothing
@@ -490,13 +517,13 @@ __global__ void bounded_wait_selftest_kernel(int* status, unsigned long long lim
     (void)__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&bar), 0u, status, limit_ns));
 }
 
-template <int KIND, int D, bool IO_BF16, bool GHI>
+template <int KIND, int D, bool IO_BF16, bool GHI, bool MULTI = false>
 cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                        const CUtensorMap* map_cold, const StepDev& st,
                        const int32_t* page_table, const void* q, float* partials, int* status,
                        cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
     using C = Cfg<KIND, D>;
-    auto kern = decode_mma_kernel<KIND, D, IO_BF16, GHI>;
+    auto kern = decode_mma_kernel<KIND, D, IO_BF16, GHI, MULTI>;
     static bool attr_done[64] = {};                         // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -515,14 +542,43 @@ cudaError_t launch_kd(const Geometry& g, const LayerPtrs& lp, const CUtensorMap*
                       const CUtensorMap* map_cold, const StepDev& st,
                       const int32_t* page_table, const void* q, float* partials, int* status,
                       cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
-    const bool io_bf16 = g.io_dtype == DT_BF16, ghi = g.H / g.Hkv > 8;
+    const bool io_bf16 = g.io_dtype == DT_BF16;
+    const bool ghi = g.H / g.Hkv > 8;
     if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
     if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
     if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
     return launch_one<KIND, D, false, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
 }
 
+template <int KIND, int D>
+cudaError_t launch_kd_multi(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
+                            const int32_t* page_table, const void* q, float* partials, int* status,
+                            cudaStream_t s, const MergeOut& mo) {
+    const FuseAppend fa{nullptr, nullptr, nullptr};
+    if ((g.H / g.Hkv) * st.nq_max > 8)
+        return launch_one<KIND, D, KIND == K_BF16, true, true>(g, lp, map, map, st, page_table, q, partials, status, s, mo, fa);
+    return launch_one<KIND, D, KIND == K_BF16, false, true>(g, lp, map, map, st, page_table, q, partials, status, s, mo, fa);
+}
+
 }  // namespace
+
+bool decode_mma_multi_supported(const Geometry& g, int nq_max) {
+    return decode_mma_supported(g) && g.dtype != DT_FP8 && nq_max >= 1 && (g.H / g.Hkv) * nq_max <= 16;
+}
+
+// Multi-token attention (st.nq / st.q_base / st.nq_max set): q and out are [n_tokens][H][D]; partial rows
+// hold H * nq_max columns.  16-bit pools without cold pages; the step's rows are already appended.
+cudaError_t launch_decode_mma_multi(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
+                                    const int32_t* page_table, const void* q, float* partials, int* status,
+                                    cudaStream_t s, const MergeOut& mo) {
+    if (st.n_items <= 0) return cudaSuccess;
+    if (!decode_mma_multi_supported(g, st.nq_max) || st.chunk_tokens > kPage * kWarps * 32 || !mo.counters || mo.peer)
+        return cudaErrorNotSupported;
+    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd_multi<K_BF16, 128>(g, lp, map, st, page_table, q, partials, status, s, mo)
+                                              : launch_kd_multi<K_BF16, 64>(g, lp, map, st, page_table, q, partials, status, s, mo);
+    return g.D == 128 ? launch_kd_multi<K_F16, 128>(g, lp, map, st, page_table, q, partials, status, s, mo)
+                      : launch_kd_multi<K_F16, 64>(g, lp, map, st, page_table, q, partials, status, s, mo);
+}
 
 cudaError_t launch_bounded_wait_selftest(int* status, unsigned long long limit_ns, cudaStream_t s) {
     bounded_wait_selftest_kernel<<<1, 32, 0, s>>>(status, limit_ns);

@@ -1,6 +1,8 @@
 // kv_manager.cpp — host-side page manager (see kv_manager.h).  No CUDA.
 #include "kv_manager.h"
 
+#include <cstdint>
+
 #include <algorithm>
 #include <cstring>
 
@@ -297,6 +299,10 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     plan->tok_b.clear(); plan->tok_pos.clear(); plan->tok_dst.clear(); plan->tok_open.clear(); plan->items.clear(); plan->seals.clear();
     plan->evictions.clear();
     plan->new_tok.assign(n_seqs, -1);
+    plan->q_base.assign(n_seqs, 0);
+    plan->nq.assign(n_seqs, 0);
+    plan->nq_max = 0;
+    plan->nq_min = n_seqs > 0 ? INT32_MAX : 0;
     plan->one_token_steps = true;
     plan->has_empty_seq = false;
 
@@ -314,6 +320,10 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         if (len_cap && len_cap[i] < len) len = len_cap[i] < 0 ? 0 : len_cap[i];   // attend to a prefix only
         plan->len[i] = len;
         int tok_base = (int)plan->tok_b.size();
+        plan->q_base[i] = tok_base;
+        plan->nq[i] = add;
+        plan->nq_max = std::max(plan->nq_max, add);
+        plan->nq_min = std::min(plan->nq_min, add);
         if (add == 1) plan->new_tok[i] = tok_base;
         if (add > 1) plan->one_token_steps = false;
         if (len == 0) plan->has_empty_seq = true;

@@ -48,6 +48,9 @@ struct StepPlan {
     std::vector<int32_t> tok_dst;    // [n_tokens] destination row: pool slot, FP8: open-page slot or -1 (sealed)
     std::vector<int32_t> tok_open;   // FP8: the tokens (indices into the lists above) that stay in an open page
     std::vector<int32_t> new_tok;    // [n_seqs] row of the sequence's single new token, or -1
+    std::vector<int32_t> q_base;     // [n_seqs] index of the sequence's first new token in the token lists
+    std::vector<int32_t> nq;         // [n_seqs] tokens the sequence appends in this step
+    int32_t nq_max = 0, nq_min = 0;  // over the step's sequences
     bool one_token_steps = false;    // every sequence appends at most one token (a decode step)
     bool has_empty_seq = false;      // some sequence attends to zero tokens
     std::vector<WorkItem> items;

@@ -258,7 +258,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->max_seals = c.max_step_tokens / c.page_size + c.max_seqs;
 
     // one buffer holds every per-step array; sections are 16-byte aligned
-    size_t ints = 4 * (size_t)c.max_seqs + 4 + 12 + 4 * (size_t)c.max_step_tokens + 16 +
+    size_t ints = 6 * (size_t)c.max_seqs + 4 + 20 + 4 * (size_t)c.max_step_tokens + 16 +
                   4 * (size_t)h->max_items + 4 * (size_t)h->max_seals + 2 * (size_t)kMaxDelta + 32;
     h->step_bytes = align_up(ints * 4, 256);
 
@@ -411,7 +411,7 @@ int prefetch_layer(tk_kv* h, int layer, bool ahead) {
 }
 
 struct Sections {       // offsets (in int32 units) of the arrays inside a step buffer
-    size_t seq, len, chunk_base, new_tok, tok_b, tok_pos, tok_dst, tok_open, items, seals, delta, end;
+    size_t seq, len, chunk_base, new_tok, q_base, nq, tok_b, tok_pos, tok_dst, tok_open, items, seals, delta, end;
 };
 Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals, int n_delta) {
     auto a4 = [](size_t x) { return (x + 3) / 4 * 4; };
@@ -421,6 +421,8 @@ Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals
     s.len = o;        o = a4(o + n_seqs);
     s.chunk_base = o; o = a4(o + n_seqs + 1);
     s.new_tok = o;    o = a4(o + n_seqs);
+    s.q_base = o;     o = a4(o + n_seqs);
+    s.nq = o;         o = a4(o + n_seqs);
     s.tok_b = o;      o = a4(o + n_tokens);
     s.tok_pos = o;    o = a4(o + n_tokens);
     s.tok_dst = o;    o = a4(o + n_tokens);
@@ -650,6 +652,8 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
         memcpy(w + sec.seq, p.seq.data(), 4 * (size_t)n_seqs);
         memcpy(w + sec.len, p.len.data(), 4 * (size_t)n_seqs);
         memcpy(w + sec.new_tok, p.new_tok.data(), 4 * (size_t)n_seqs);
+        memcpy(w + sec.q_base, p.q_base.data(), 4 * (size_t)n_seqs);
+        memcpy(w + sec.nq, p.nq.data(), 4 * (size_t)n_seqs);
     }
     memcpy(w + sec.chunk_base, p.chunk_base.data(), 4 * (size_t)(n_seqs + 1));
     if (n_tok) {
@@ -670,7 +674,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     const int32_t* d = (const int32_t*)h->d_step;
     tk::StepDev& dv = h->dev;
     dv.seq = d + sec.seq; dv.len = d + sec.len; dv.chunk_base = d + sec.chunk_base;
-    dv.new_tok = d + sec.new_tok;
+    dv.new_tok = d + sec.new_tok; dv.q_base = d + sec.q_base; dv.nq = d + sec.nq; dv.nq_max = p.nq_max;
     dv.tok_b = d + sec.tok_b; dv.tok_pos = d + sec.tok_pos; dv.tok_dst = d + sec.tok_dst; dv.tok_open = d + sec.tok_open;
     dv.items = (const int4*)(d + sec.items); dv.seals = (const int4*)(d + sec.seals);
     dv.n_seqs = n_seqs; dv.n_tokens = n_tok; dv.n_items = n_items; dv.n_seals = n_seals;
@@ -857,6 +861,35 @@ int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, voi
 }
 int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial, void* stream) {
     return decode_impl(h, layer, q, nullptr, partial, (cudaStream_t)stream);
+}
+
+// Attention for every token the step appended (several per sequence), causal among themselves, in one
+// pass over the pages: what the verification of drafted tokens needs.
+int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* stream) {
+    if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode_multi: handle has no device (bookkeeping only)");
+    if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode_multi: no step in progress (call tk_kv_step_begin)");
+    if (h->dev.n_seqs == 0) return TK_OK;
+    if (!q || !out) return fail(h, TK_INVALID_ARG, "decode_multi: null q/out");
+    const tk::StepPlan& p = h->plan;
+    if (p.nq_min < 1) return fail(h, TK_INVALID_ARG, "decode_multi: every sequence of the step must append at least one token");
+    if (!h->use_mma || h->mla_mma || !tk::decode_mma_multi_supported(h->geo, p.nq_max))
+        return fail(h, TK_UNSUPPORTED, "decode_multi: needs the tensor-core kernel on a 16-bit pool and (heads per kv head) x "
+                                       "(tokens per sequence) <= 16 (here %d x %d)", h->geo.H / h->geo.Hkv, p.nq_max);
+    if (h->mgr->cold_enabled() && h->mgr->cold_high_water() > 0)
+        return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
+    if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)
+        return fail(h, TK_UNSUPPORTED, "decode_multi: needs the in-kernel merge");
+    // partial rows hold H * nq_max columns here: the workspace was sized for H
+    if ((int64_t)p.chunk_base[h->dev.n_seqs] * p.nq_max > h->max_partial_rows)
+        return fail(h, TK_UNSUPPORTED, "decode_multi: split-KV workspace too small for %d rows of %d tokens",
+                    p.chunk_base[h->dev.n_seqs], p.nq_max);
+    const tk::MergeOut mo{h->d_counters, out, nullptr, h->cfg.io_dtype, nullptr};
+    cudaError_t e = tk::launch_decode_mma_multi(h->geo, h->layer(layer), &h->maps[layer], h->dev, h->d_table, q,
+                                                h->d_partials, h->d_status, (cudaStream_t)stream, mo);
+    h->launches++;
+    if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode_multi launch: %s", cudaGetErrorString(e));
+    return TK_OK;
 }
 
 // Attention over a sequence whose tokens are spread over the ranks of `peer`.  One launch where the

@@ -54,8 +54,11 @@ struct StepDev {
     const int4*    items;       // [n_items] (b, chunk, kvh, kind)
     const int4*    seals;       // [n_seals] (seq slot, physical page, rows from the open page, token of the next row)
     const int32_t* new_tok;     // [n_seqs] row of the sequence's single new token in k/v, or -1
+    const int32_t* q_base;      // [n_seqs] multi-token attention: row of the sequence's first new token in q / out
+    const int32_t* nq;          // [n_seqs] multi-token attention: query tokens of the sequence (its new tokens)
     int n_seqs, n_tokens, n_items, n_seals, chunk_tokens;
     int n_open;
+    int nq_max;                 // multi-token attention: largest nq of the step (row stride of the partials)
 };
 
 // partial row layout: [row][H][D+2] f32 = o[0..D) unnormalised, m at [D], l at [D+1]
@@ -120,6 +123,12 @@ cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUte
                               const CUtensorMap* map_cold, const StepDev& st, const int32_t* page_table, const void* q,
                               float* partials, int* status, cudaStream_t s,
                               const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
+
+// Several query tokens per sequence, causal among themselves (16-bit pools, G * nq_max <= 16).
+bool        decode_mma_multi_supported(const Geometry& g, int nq_max);
+cudaError_t launch_decode_mma_multi(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
+                                    const int32_t* page_table, const void* q, float* partials, int* status,
+                                    cudaStream_t s, const MergeOut& mo);
 
 // The same for the MLA cache shape (K rows 192, V rows 128; 16-bit pools, groups of <= 8 heads).
 bool        decode_mma_mla_supported(const Geometry& g);

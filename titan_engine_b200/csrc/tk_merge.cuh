@@ -20,9 +20,19 @@ __device__ __forceinline__ void store_out(void* out, size_t idx, float v, int dt
     else                    ((float*)out)[idx] = v;
 }
 
+// Which partial columns a (sequence, kv head) group owns and where its outputs go.  One query token
+// per sequence: the G heads of the kv head, out row = the sequence's index in the step.  Several query
+// tokens per sequence (multi-token attention): G * nq columns, column j*G + gg = token j, head gg of the
+// group; a partial row then holds heads_per_row = H * nq_max columns, token-major.
+struct MergeMap {
+    int cols;            // G * nq
+    int heads_per_row;   // H, or H * nq_max
+    int out_row0;        // row of `out` that token 0 of this sequence writes
+};
+
 // The merge itself, by every thread of the CTA that arrived last for (b, kvh): rows r0 .. r0+n-1.
 __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo, int b, int kvh, int G, int r0, int n,
-                                           const float* partials) {
+                                           const float* partials, const MergeMap& mm) {
     __threadfence();                                   // see the other CTAs' rows
     const int D = g.Dv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
@@ -30,15 +40,18 @@ __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo
     const PeerCtx* pc = mo.peer;
     const uint32_t epoch = pc ? __ldcg(pc->epoch) + 1u : 0u;
     const int parity = (int)(epoch & 1u);
-    for (int gq = warp; gq < G; gq += n_warps) {
-        const int h = kvh * G + gq;
+    for (int gq = warp; gq < mm.cols; gq += n_warps) {
+        const int tq = gq / G;                         // query token of the sequence (0 unless multi-token)
+        const int h = kvh * G + gq % G;                // query head
+        const int col = tq * g.H + h;                  // column of the partial rows
+        const int HP = mm.heads_per_row;
         float M = -1e30f;
-        for (int r = lane; r < n; r += 32) M = fmaxf(M, __ldcg(partials + partial_off(r0 + r, h, g.H, D) + D));
+        for (int r = lane; r < n; r += 32) M = fmaxf(M, __ldcg(partials + partial_off(r0 + r, col, HP, D) + D));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
         float L = 0.0f;
         for (int r = lane; r < n; r += 32) {
-            const float* p = partials + partial_off(r0 + r, h, g.H, D);
+            const float* p = partials + partial_off(r0 + r, col, HP, D);
             L += __ldcg(p + D + 1) * expf(__ldcg(p + D) - M);
         }
 #pragma unroll
@@ -52,7 +65,7 @@ __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const bool live = rb + u < n;
-                const float* p = partials + partial_off(r0 + (live ? rb + u : rb), h, g.H, D);
+                const float* p = partials + partial_off(r0 + (live ? rb + u : rb), col, HP, D);
                 m[u] = live ? __ldcg(p + D) : -1e30f;
                 if (epl == 4) {                         // rows start on 8-byte, not 16-byte, boundaries
                     const float2 v0 = __ldcg(reinterpret_cast<const float2*>(p) + 2 * lane);
@@ -86,7 +99,7 @@ __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo
         for (int e = 0; e < 4; e++) {
             if (e >= epl) break;
             const int d = lane * epl + e;
-            if (mo.out) store_out(mo.out, ((size_t)b * g.H + h) * D + d, acc[e] * inv, mo.out_dtype);
+            if (mo.out) store_out(mo.out, ((size_t)(mm.out_row0 + tq) * g.H + h) * D + d, acc[e] * inv, mo.out_dtype);
             if (mo.partial_out) mo.partial_out[partial_off(b, h, g.H, D) + d] = acc[e];
         }
         if (mo.partial_out && lane == 0) {
@@ -138,7 +151,8 @@ __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo
 // of that sequence's rows for those heads and writes the result; it also re-arms the counter.
 // `s_flag` is one int of shared memory.  Returns without merging when mo.counters is null.
 __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& st, const MergeOut& mo,
-                                              int b, int kvh, int G, const float* partials, int* s_flag) {
+                                              int b, int kvh, int G, const float* partials, int* s_flag,
+                                              const MergeMap& mm) {
     if (!mo.counters) return;
     const int r0 = st.chunk_base[b], n = st.chunk_base[b + 1] - r0;
     __syncthreads();                                   // the CTA's partial row is complete ...
@@ -151,7 +165,7 @@ __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& 
         *s_flag = last;
     }
     __syncthreads();
-    if (*s_flag) merge_rows(g, mo, b, kvh, G, r0, n, partials);
+    if (*s_flag) merge_rows(g, mo, b, kvh, G, r0, n, partials, mm);
     if (mo.peer) {                                     // the CTA that leaves last closes this exchange
         const PeerCtx& c = *mo.peer;
         __syncthreads();
@@ -160,6 +174,12 @@ __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& 
             atomicExch(c.epoch, __ldcg(c.epoch) + 1u);
         }
     }
+}
+
+// One query token per sequence.
+__device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& st, const MergeOut& mo,
+                                              int b, int kvh, int G, const float* partials, int* s_flag) {
+    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag, MergeMap{G, g.H, b});
 }
 
 }  // namespace tk

@@ -247,6 +247,14 @@ class PagedKVCache:
         self._check(self._lib.tk_kv_decode_partial(self._h, layer, q.data_ptr(), partial.data_ptr(), self._stream()))
         return partial
 
+    def decode_multi(self, layer: int, q: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Causal attention for every token the step appended: q, out [n_tokens, H, D] (rows as in append)."""
+        self._check_io(q, self._n_tokens, self.cfg.num_heads, "q")
+        if out is None:
+            out = torch.empty_like(q)
+        self._check(self._lib.tk_kv_decode_multi(self._h, layer, q.data_ptr(), out.data_ptr(), self._stream()))
+        return out
+
     def decode_exchange(self, layer: int, q: torch.Tensor, exchange, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention over the tokens of EVERY rank of `exchange` (a dist.PeerExchange): this rank's
         partial rows, then one kernel that swaps rows with the peers over NVLink and combines."""
