@@ -121,6 +121,8 @@ struct tk_kv {
     std::vector<CUtensorMap> maps;       // one per layer (MMA path); MLA shape: the K-row view
     std::vector<CUtensorMap> maps_v;     // MLA shape: the V-row view
     float* d_xpartial = nullptr;         // this rank's merged partial rows for tk_kv_decode_exchange
+    float* d_multi_partials = nullptr;   // split-KV rows of multi-token steps that outgrow d_partials
+    size_t multi_partials_floats = 0;
     bool mla_mma = false;
 
     // cold tier (hot_window > 0): pages older than the window live in pinned host memory and are
@@ -187,6 +189,7 @@ void release(tk_kv* h) {
         if (h->d_table) cudaFree(h->d_table);
         if (h->d_partials) cudaFree(h->d_partials);
         if (h->d_xpartial) cudaFree(h->d_xpartial);
+        if (h->d_multi_partials) cudaFree(h->d_multi_partials);
         if (h->d_status) cudaFree(h->d_status);
         if (h->d_counters) cudaFree(h->d_counters);
         if (h->d_step) cudaFree(h->d_step);
@@ -880,13 +883,23 @@ int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* 
         return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
     if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)
         return fail(h, TK_UNSUPPORTED, "decode_multi: needs the in-kernel merge");
-    // partial rows hold H * nq_max columns here: the workspace was sized for H
-    if ((int64_t)p.chunk_base[h->dev.n_seqs] * p.nq_max > h->max_partial_rows)
-        return fail(h, TK_UNSUPPORTED, "decode_multi: split-KV workspace too small for %d rows of %d tokens",
-                    p.chunk_base[h->dev.n_seqs], p.nq_max);
+    // partial rows hold H * nq_max columns here; the handle's workspace was sized for H columns, so steps
+    // that need more get a workspace of their own, grown when a step needs a larger one
+    float* partials = h->d_partials;
+    const size_t need = (size_t)p.chunk_base[h->dev.n_seqs] * h->geo.H * p.nq_max * (h->geo.Dv + 2);
+    if (need > (size_t)h->max_partial_rows * h->cfg.num_heads * (h->cfg.v_head_dim + 2)) {
+        if (need > h->multi_partials_floats) {
+            TK_CUDA(h, cudaSetDevice(h->device));
+            if (h->d_multi_partials) { TK_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream)); cudaFree(h->d_multi_partials); }
+            h->d_multi_partials = nullptr; h->multi_partials_floats = 0;
+            TK_CUDA(h, cudaMalloc((void**)&h->d_multi_partials, need * sizeof(float)));
+            h->multi_partials_floats = need;
+        }
+        partials = h->d_multi_partials;
+    }
     const tk::MergeOut mo{h->d_counters, out, nullptr, h->cfg.io_dtype, nullptr};
     cudaError_t e = tk::launch_decode_mma_multi(h->geo, h->layer(layer), &h->maps[layer], h->dev, h->d_table, q,
-                                                h->d_partials, h->d_status, (cudaStream_t)stream, mo);
+                                                partials, h->d_status, (cudaStream_t)stream, mo);
     h->launches++;
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode_multi launch: %s", cudaGetErrorString(e));
     return TK_OK;
