@@ -62,6 +62,8 @@ const char* validate(const tk_kv_config& c) {
     if (c.dtype != TK_FP8_E4M3 && c.io_dtype != c.dtype) return "io_dtype must equal dtype for 16-bit storage";
     if (c.num_pages <= 0 || c.max_seqs <= 0 || c.max_pages_per_seq <= 0) return "num_pages/max_seqs/max_pages_per_seq must be positive";
     if ((int64_t)c.max_seqs * c.max_pages_per_seq > (int64_t)1 << 30) return "page table too large";
+    if ((int64_t)c.num_pages * c.page_size >= (int64_t)1 << 31 || (int64_t)c.max_seqs * c.page_size >= (int64_t)1 << 31)
+        return "num_pages * page_size must stay below 2^31 (row indices are 32-bit)";
     if (c.max_step_tokens <= 0) return "max_step_tokens must be positive";
     if (c.chunk_tokens < 0 || c.chunk_tokens % c.page_size != 0) return "chunk_tokens must be a multiple of page_size";
     if (c.decode_impl < TK_DECODE_AUTO || c.decode_impl > TK_DECODE_MMA) return "bad decode_impl";
