@@ -635,3 +635,48 @@ def test_decode_multi_refusals():
     f.gpu.step_begin([s], [2])
     with pytest.raises(KvError):                             # FP8 pools are not served
         f.gpu.decode_multi(0, torch.zeros(2, 64, 128, device=f.dev, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_decode_multi_random_steps(seed):
+    """Random token counts per sequence and step (1 .. 16/G), small chunks so that the new tokens keep
+    crossing page and chunk boundaries, sequences joining and leaving between steps."""
+    H, Hkv, D, dt = 16, 4, 64, O.FP16
+    t = Twin(1, H, Hkv, D, 200, 5, 40, dtype="fp16", impl="mma", max_step_tokens=512, seed=95 + seed, chunk_tokens=64)
+    g = rng(200 + seed)
+    live = [t.seq_alloc() for _ in range(3)]
+    t.step(live, [int(x) for x in g.integers(1, 120, size=3)])
+    for it in range(25):
+        if it % 7 == 3 and len(live) > 1:
+            gone = live.pop(int(g.integers(0, len(live))))
+            t.seq_free(gone)
+        if it % 5 == 4 and len(live) < 5:
+            s = t.seq_alloc()
+            t.step([s], [int(g.integers(1, 60))])
+            live.append(s)
+        seqs = sorted(live)
+        n_new = [int(x) for x in g.integers(1, 16 // (H // Hkv) + 1, size=len(seqs))]
+        old = [t.gpu.seq_len(s) for s in seqs]
+        if max(o + n for o, n in zip(old, n_new)) > 40 * 16:
+            break
+        t.gpu.step_begin(seqs, n_new)
+        for s, n in zip(seqs, n_new):
+            assert t.mgr.reserve(s, n) == O.OK
+        assert t.gpu.digest() == t.mgr.digest()
+        table = t.mgr.table()
+        tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seqs, n_new)])
+        tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)])
+        k16 = normal16(g, (len(tok_seq), Hkv, D), dt); v16 = normal16(g, (len(tok_seq), Hkv, D), dt)
+        q16 = normal16(g, (len(tok_seq), H, D), dt)
+        t.gpu.append(0, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev))
+        t.pools[0].append(table, tok_seq, tok_pos, k16, v16)
+        got = t.gpu.decode_multi(0, to_torch16(q16, dt, t.dev)).float().cpu().numpy()
+        want = t.pools[0].decode(table, tok_seq, tok_pos + 1, q16)
+        assert_close(got, want, f"step {it}: {n_new} new tokens on lengths {old}", out_mantissa_bits=10)
+        # reject a random tail of one sequence's new tokens
+        j = int(g.integers(0, len(seqs)))
+        keep = int(g.integers(1, n_new[j] + 1))
+        new_len = old[j] + keep
+        t.gpu.truncate(seqs[j], new_len); assert t.mgr.truncate(seqs[j], new_len) == O.OK
+        assert t.gpu.digest() == t.mgr.digest()
+    t.gpu.device_status()
