@@ -192,11 +192,12 @@ int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, voi
                     void* stream);
 /* Attention for EVERY token the step appended, several per sequence: q and out are
  * [n_tokens][H][D] (the order of tk_kv_append's rows), token j of a sequence attends to positions
- * <= its own - causal among the step's tokens - and the tokens of a sequence share one pass over its
- * pages.  Call after tk_kv_append of the layer.  This is the batched verification of drafted tokens
+ * <= its own - causal among the step's tokens - and 16 / (num_heads / num_kv_heads) tokens of a
+ * sequence share one pass over its pages (more tokens take further passes, up to 8).  Call after
+ * tk_kv_append of the layer.  This is the batched verification of drafted tokens
  * that the reference's speculative decoder runs as one layer pass per token
  * (src/inference/speculative.cpp:262-272); rejected tokens are dropped with tk_kv_truncate.
- * 16-bit pools with the tensor-core kernel, (num_heads / num_kv_heads) x (tokens per sequence) <= 16,
+ * 16-bit pools with the tensor-core kernel, (num_heads / num_kv_heads) x (tokens per sequence) <= 128,
  * every sequence of the step appending at least one token; TK_UNSUPPORTED otherwise. */
 int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* stream);
 /* Same, but stops before normalisation: partial[n_seqs][H][D+2] f32 =

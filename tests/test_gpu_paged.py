@@ -572,7 +572,10 @@ def test_shard_by_kv_head_outputs_are_head_slices_of_the_whole():
     (8, 2, 64, "fp16", 4),
     (16, 16, 128, "bf16", 16),   # MHA: 16 tokens
     (16, 16, 64, "bf16", 5),
-    (16, 1, 64, "fp16", 1),      # 16 heads per kv head: one token only
+    (16, 1, 64, "fp16", 1),      # 16 heads per kv head: one token per pass
+    (16, 1, 64, "fp16", 3),      # ... three tokens: three token groups
+    (64, 8, 128, "bf16", 5),     # 70B head shape: 2 tokens per pass, 3 groups (the last one half full)
+    (32, 8, 128, "bf16", 19),    # 5 groups
 ])
 def test_decode_multi_tokens_causal(shape):
     """Every token a step appended gets its own attention output, causal among the step's tokens, from one
@@ -624,9 +627,9 @@ def test_decode_multi_refusals():
     a, b = t.seq_alloc(), t.seq_alloc()
     t.step([a, b], [40, 40])
     q = torch.zeros(6, 32, 128, device=t.dev, dtype=torch.bfloat16)
-    t.gpu.step_begin([a, b], [5, 1]); assert t.mgr.reserve(a, 5) == O.OK and t.mgr.reserve(b, 1) == O.OK
-    with pytest.raises(KvError):                             # 4 heads per kv head x 5 tokens > 16 rows
-        t.gpu.decode_multi(0, q)
+    t.gpu.step_begin([a, b], [33, 1]); assert t.mgr.reserve(a, 33) == O.OK and t.mgr.reserve(b, 1) == O.OK
+    with pytest.raises(KvError):                             # 4 heads per kv head x 33 tokens: more than 8 token groups
+        t.gpu.decode_multi(0, torch.zeros(34, 32, 128, device=t.dev, dtype=torch.bfloat16))
     t.gpu.step_begin([a, b], [2, 0]); assert t.mgr.reserve(a, 2) == O.OK
     with pytest.raises(KvError):                             # a sequence without a new token
         t.gpu.decode_multi(0, q[:2].contiguous())
@@ -639,7 +642,7 @@ def test_decode_multi_refusals():
 
 @pytest.mark.parametrize("seed", [1, 2])
 def test_decode_multi_random_steps(seed):
-    """Random token counts per sequence and step (1 .. 16/G), small chunks so that the new tokens keep
+    """Random token counts per sequence and step (1 .. 2*16/G + 1), small chunks so that the new tokens keep
     crossing page and chunk boundaries, sequences joining and leaving between steps."""
     H, Hkv, D, dt = 16, 4, 64, O.FP16
     t = Twin(1, H, Hkv, D, 200, 5, 40, dtype="fp16", impl="mma", max_step_tokens=512, seed=95 + seed, chunk_tokens=64)
@@ -655,7 +658,7 @@ def test_decode_multi_random_steps(seed):
             t.step([s], [int(g.integers(1, 60))])
             live.append(s)
         seqs = sorted(live)
-        n_new = [int(x) for x in g.integers(1, 16 // (H // Hkv) + 1, size=len(seqs))]
+        n_new = [int(x) for x in g.integers(1, 2 * (16 // (H // Hkv)) + 2, size=len(seqs))]     # up to 3 token groups
         old = [t.gpu.seq_len(s) for s in seqs]
         if max(o + n for o, n in zip(old, n_new)) > 40 * 16:
             break

@@ -30,6 +30,8 @@
 #include <cuda_fp16.h>
 #include <cudaTypedefs.h>
 
+#include <algorithm>
+
 namespace tk {
 
 namespace {
@@ -176,12 +178,16 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     const int b = it.x, chunk = it.y, kvh = it.z;
     const int seq = st.seq[b], len = st.len[b];
     const int nq = MULTI ? st.nq[b] : 1;                    // query tokens of this sequence
-    const int rows = G * nq;                                // rows of the M tile that carry data
-    const int q_row0 = MULTI ? st.q_base[b] : b;            // row of q / out of the sequence's first query token
+    const int tok0 = MULTI ? (int)blockIdx.y * (16 / G) : 0;  // first query token of this CTA's token group
+    const int nq_g = MULTI ? min(nq - tok0, 16 / G) : 1;    // query tokens of the group
+    if (MULTI && nq_g <= 0) return;                         // this sequence has no such group
+    const int rows = G * nq_g;                              // rows of the M tile that carry data
+    const int q_row0 = MULTI ? st.q_base[b] + tok0 : b;     // row of q / out of the group's first query token
     const int pool_tokens = KIND == K_FP8 ? (len / kPage) * kPage : len;
     const int t0 = chunk * st.chunk_tokens;
-    const int t1 = min(pool_tokens, t0 + st.chunk_tokens);
-    const int n_pages = (t1 - t0 + kPage - 1) / kPage;
+    // the group's last token sees len - nq + tok0 + nq_g positions: nothing beyond is fetched
+    const int t1 = min(MULTI ? len - nq + tok0 + nq_g : pool_tokens, t0 + st.chunk_tokens);
+    const int n_pages = t1 > t0 ? (t1 - t0 + kPage - 1) / kPage : 0;
     const int lp0 = t0 / kPage;
     const int n_w = n_pages > warp ? (n_pages - warp + kWarps - 1) / kWarps : 0;   // pages of this warp (<= 32)
     // fused append (decode steps, 16-bit pools): row of this sequence's new token in fa.k / fa.v
@@ -284,8 +290,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         const int tok_base = (lp0 + warp + kWarps * i) * kPage;
         const int n_valid = min(kPage, t1 - tok_base);     // < 16 only on a sequence's last page
         // tokens of this page that rows gr / gr+8 may attend to (causal limit of their query token)
-        const int nv0 = MULTI ? max(0, min(n_valid, len - nq + gr / G + 1 - tok_base)) : n_valid;
-        const int nv1 = MULTI ? max(0, min(n_valid, len - nq + (gr + 8) / G + 1 - tok_base)) : n_valid;
+        const int nv0 = MULTI ? max(0, min(n_valid, len - nq + tok0 + gr / G + 1 - tok_base)) : n_valid;
+        const int nv1 = MULTI ? max(0, min(n_valid, len - nq + tok0 + (gr + 8) / G + 1 - tok_base)) : n_valid;
 
         float sc_k = sm_scale, sc_v = 1.0f;
         if (KIND == K_FP8) {
@@ -499,10 +505,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
 #pragma unroll
             for (int w = 0; w < kWarps; w++) val += red_at(w, row, d) * ex2((red_at(w, row, D) - M) * kLog2e);
         }
-        const int col = MULTI ? (row / G) * g.H + kvh * G + row % G : kvh * G + row;
+        const int col = MULTI ? (tok0 + row / G) * g.H + kvh * G + row % G : kvh * G + row;
         partials[partial_off(prow, col, heads_per_row, D) + d] = val;
     }
-    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag, MergeMap{rows, heads_per_row, q_row0});
+    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag,
+                  MergeMap{rows, heads_per_row, q_row0, MULTI ? tok0 : 0, MULTI ? (int)blockIdx.y * st.n_seqs * g.Hkv : 0});
 }
 
 // One warp waits, with the same bounded wait the decode kernel uses, on a barrier that nothing
@@ -532,8 +539,11 @@ cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
-    kern<<<st.n_items, kWarps * 32, C::SMEM_BYTES, s>>>(*map, *map_cold, g, lp, st, page_table, (const uint16_t*)q,
-                                                        partials, status, mo, fa);
+    // multi-token attention: one grid row per group of 16/G query tokens
+    const int tpg = 16 / (g.H / g.Hkv);
+    const dim3 grid(st.n_items, MULTI ? (st.nq_max + tpg - 1) / tpg : 1);
+    kern<<<grid, kWarps * 32, C::SMEM_BYTES, s>>>(*map, *map_cold, g, lp, st, page_table, (const uint16_t*)q,
+                                                  partials, status, mo, fa);
     return cudaGetLastError();
 }
 
@@ -555,15 +565,22 @@ cudaError_t launch_kd_multi(const Geometry& g, const LayerPtrs& lp, const CUtens
                             const int32_t* page_table, const void* q, float* partials, int* status,
                             cudaStream_t s, const MergeOut& mo) {
     const FuseAppend fa{nullptr, nullptr, nullptr};
-    if ((g.H / g.Hkv) * st.nq_max > 8)
+    if ((g.H / g.Hkv) * std::min(st.nq_max, 16 / (g.H / g.Hkv)) > 8)
         return launch_one<KIND, D, KIND == K_BF16, true, true>(g, lp, map, map, st, page_table, q, partials, status, s, mo, fa);
     return launch_one<KIND, D, KIND == K_BF16, false, true>(g, lp, map, map, st, page_table, q, partials, status, s, mo, fa);
 }
 
 }  // namespace
 
+// Token groups per sequence are grid rows; each is a pass of its own over the pages it may see.
+constexpr int kMaxTokenGroups = 8;
 bool decode_mma_multi_supported(const Geometry& g, int nq_max) {
-    return decode_mma_supported(g) && g.dtype != DT_FP8 && nq_max >= 1 && (g.H / g.Hkv) * nq_max <= 16;
+    return decode_mma_supported(g) && g.dtype != DT_FP8 && nq_max >= 1 &&
+           (g.H / g.Hkv) * nq_max <= 16 * kMaxTokenGroups;
+}
+int decode_mma_multi_groups(const Geometry& g, int nq_max) {
+    const int tpg = 16 / (g.H / g.Hkv);
+    return (nq_max + tpg - 1) / tpg;
 }
 
 // Multi-token attention (st.nq / st.q_base / st.nq_max set): q and out are [n_tokens][H][D]; partial rows

@@ -98,7 +98,7 @@ struct tk_kv {
     float* d_partials = nullptr;
     int max_partial_rows = 0, max_items = 0, max_seals = 0;
     int* d_status = nullptr;
-    int* d_counters = nullptr;           // [max_seqs * Hkv] arrival counters of the in-kernel merge
+    int* d_counters = nullptr;           // [8 token groups][max_seqs * Hkv] arrival counters of the in-kernel merge
 
     size_t step_bytes = 0;
     uint8_t* d_step = nullptr;
@@ -305,8 +305,8 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
                            (size_t)h->max_partial_rows * c.num_heads * (c.v_head_dim + 2) * sizeof(float)));
     CREATE_CUDA(cudaMalloc((void**)&h->d_status, 256));
     CREATE_CUDA(cudaMemset(h->d_status, 0, 256));
-    CREATE_CUDA(cudaMalloc((void**)&h->d_counters, sizeof(int) * (size_t)c.max_seqs * c.num_kv_heads));
-    CREATE_CUDA(cudaMemset(h->d_counters, 0, sizeof(int) * (size_t)c.max_seqs * c.num_kv_heads));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_counters, sizeof(int) * 8 * (size_t)c.max_seqs * c.num_kv_heads));
+    CREATE_CUDA(cudaMemset(h->d_counters, 0, sizeof(int) * 8 * (size_t)c.max_seqs * c.num_kv_heads));
     CREATE_CUDA(cudaMalloc((void**)&h->d_step, h->step_bytes));
     for (int i = 0; i < kRing; i++) {
         CREATE_CUDA(cudaHostAlloc((void**)&h->h_step[i], h->step_bytes, cudaHostAllocDefault));
@@ -880,7 +880,7 @@ int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* 
     if (p.nq_min < 1) return fail(h, TK_INVALID_ARG, "decode_multi: every sequence of the step must append at least one token");
     if (!h->use_mma || h->mla_mma || !tk::decode_mma_multi_supported(h->geo, p.nq_max))
         return fail(h, TK_UNSUPPORTED, "decode_multi: needs the tensor-core kernel on a 16-bit pool and (heads per kv head) x "
-                                       "(tokens per sequence) <= 16 (here %d x %d)", h->geo.H / h->geo.Hkv, p.nq_max);
+                                       "(tokens per sequence) <= 128 (here %d x %d)", h->geo.H / h->geo.Hkv, p.nq_max);
     if (h->mgr->cold_enabled() && h->mgr->cold_high_water() > 0)
         return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
     if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)

@@ -124,8 +124,10 @@ cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUte
                               float* partials, int* status, cudaStream_t s,
                               const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
 
-// Several query tokens per sequence, causal among themselves (16-bit pools, G * nq_max <= 16).
+// Several query tokens per sequence, causal among themselves (16-bit pools): 16/G tokens per pass over the
+// pages, up to 8 such token groups.  `mo.counters` needs n_groups * n_seqs * Hkv zeroed counters.
 bool        decode_mma_multi_supported(const Geometry& g, int nq_max);
+int         decode_mma_multi_groups(const Geometry& g, int nq_max);
 cudaError_t launch_decode_mma_multi(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
                                     const int32_t* page_table, const void* q, float* partials, int* status,
                                     cudaStream_t s, const MergeOut& mo);

@@ -25,9 +25,11 @@ __device__ __forceinline__ void store_out(void* out, size_t idx, float v, int dt
 // tokens per sequence (multi-token attention): G * nq columns, column j*G + gg = token j, head gg of the
 // group; a partial row then holds heads_per_row = H * nq_max columns, token-major.
 struct MergeMap {
-    int cols;            // G * nq
+    int cols;            // G * (query tokens of the group)
     int heads_per_row;   // H, or H * nq_max
-    int out_row0;        // row of `out` that token 0 of this sequence writes
+    int out_row0;        // row of `out` that the group's first token writes
+    int tok0;            // index, within the sequence's query tokens, of the group's first token
+    int counter_off;     // this token group's block of arrival counters
 };
 
 // The merge itself, by every thread of the CTA that arrived last for (b, kvh): rows r0 .. r0+n-1.
@@ -43,7 +45,7 @@ __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo
     for (int gq = warp; gq < mm.cols; gq += n_warps) {
         const int tq = gq / G;                         // query token of the sequence (0 unless multi-token)
         const int h = kvh * G + gq % G;                // query head
-        const int col = tq * g.H + h;                  // column of the partial rows
+        const int col = (mm.tok0 + tq) * g.H + h;      // column of the partial rows
         const int HP = mm.heads_per_row;
         float M = -1e30f;
         for (int r = lane; r < n; r += 32) M = fmaxf(M, __ldcg(partials + partial_off(r0 + r, col, HP, D) + D));
@@ -158,7 +160,7 @@ __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& 
     __syncthreads();                                   // the CTA's partial row is complete ...
     if (threadIdx.x == 0) {
         __threadfence();                               // ... and ordered before the ticket, device-wide
-        int* c = mo.counters + (size_t)b * g.Hkv + kvh;
+        int* c = mo.counters + mm.counter_off + (size_t)b * g.Hkv + kvh;
         const int ticket = atomicAdd(c, 1);
         const int last = ticket == n - 1;
         if (last) *c = 0;                              // nobody else touches it again in this launch
@@ -179,7 +181,7 @@ __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& 
 // One query token per sequence.
 __device__ __forceinline__ void merge_if_last(const Geometry& g, const StepDev& st, const MergeOut& mo,
                                               int b, int kvh, int G, const float* partials, int* s_flag) {
-    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag, MergeMap{G, g.H, b});
+    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag, MergeMap{G, g.H, b, 0, 0});
 }
 
 }  // namespace tk
