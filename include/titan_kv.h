@@ -197,8 +197,9 @@ int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, voi
  * tk_kv_append of the layer.  This is the batched verification of drafted tokens
  * that the reference's speculative decoder runs as one layer pass per token
  * (src/inference/speculative.cpp:262-272); rejected tokens are dropped with tk_kv_truncate.
- * 16-bit pools with the tensor-core kernel, (num_heads / num_kv_heads) x (tokens per sequence) <= 128,
- * every sequence of the step appending at least one token; TK_UNSUPPORTED otherwise. */
+ * 16-bit pools with the tensor-core kernel, (num_heads / num_kv_heads) x (tokens per sequence) <= 128
+ * (<= 64 and 8 / (num_heads / num_kv_heads) tokens per pass for the MLA shape), every sequence of the step
+ * appending at least one token; TK_UNSUPPORTED otherwise. */
 int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* stream);
 /* Same, but stops before normalisation: partial[n_seqs][H][D+2] f32 =
  * (o unnormalised [D], m, l), for a cross-GPU combine. */

@@ -683,3 +683,33 @@ def test_decode_multi_random_steps(seed):
         t.gpu.truncate(seqs[j], new_len); assert t.mgr.truncate(seqs[j], new_len) == O.OK
         assert t.gpu.digest() == t.mgr.digest()
     t.gpu.device_status()
+
+
+@pytest.mark.parametrize("heads,k", [((16, 16), 2), ((16, 16), 8), ((16, 16), 11), ((32, 8), 2), ((32, 8), 5)])
+def test_decode_multi_mla_shape(heads, k):
+    """Multi-token attention on the MLA cache shape (K rows 192, V rows / outputs 128): 8/G tokens per pass."""
+    H, Hkv = heads
+    D, Dv, dt = 192, 128, O.BF16
+    t = Twin(1, H, Hkv, D, 200, 3, 60, dtype="bf16", impl="mma", max_step_tokens=1024, seed=96, Dv=Dv, chunk_tokens=256)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [500, 14, 250])
+    g = rng(97)
+    for n_new in ([k, k, k], [k, 1, max(1, k // 2)], [k, k, k], [k, k, k]):
+        old = [t.gpu.seq_len(s) for s in seqs]
+        t.gpu.step_begin(seqs, n_new)
+        for s, n in zip(seqs, n_new):
+            assert t.mgr.reserve(s, n) == O.OK
+        assert t.gpu.digest() == t.mgr.digest()
+        table = t.mgr.table()
+        tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seqs, n_new)])
+        tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)])
+        k16 = normal16(g, (len(tok_seq), Hkv, D), dt); v16 = normal16(g, (len(tok_seq), Hkv, Dv), dt)
+        q16 = normal16(g, (len(tok_seq), H, D), dt)
+        t.gpu.append(0, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev))
+        t.pools[0].append(table, tok_seq, tok_pos, k16, v16)
+        got = t.gpu.decode_multi(0, to_torch16(q16, dt, t.dev)).float().cpu().numpy()
+        assert got.shape == (len(tok_seq), H, Dv)
+        want = t.pools[0].decode(table, tok_seq, tok_pos + 1, q16)
+        assert_close(got, want, f"MLA multi-token attention {n_new}", out_mantissa_bits=7)
+    t.gpu.device_status()
+    t.step(seqs, [1, 1, 1], check_pool=True)

@@ -45,7 +45,10 @@ __device__ __forceinline__ uint32_t v_off(int t, int cc) {
     return (uint32_t)(kKBytes + (cc >> 3) * kVHalfBytes + t * 128 + (((cc & 7) ^ (t & 7)) << 4));
 }
 
-template <bool BF>
+// MULTI: every sequence brings nq query tokens (the tokens the step appended, already in the pool), token j
+// attending causally to positions <= len - nq + j; row j*G + gg of the tile is token j, head gg of the
+// group, 8/G tokens per pass, further token groups as grid rows (as in decode_mma.cu).
+template <bool BF, bool MULTI>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                       Geometry g, LayerPtrs lp, StepDev st, const int32_t* __restrict__ page_table,
@@ -65,9 +68,16 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     const int4 it = st.items[blockIdx.x];
     const int b = it.x, chunk = it.y, kvh = it.z;
     const int seq = st.seq[b], len = st.len[b];
+    const int nq = MULTI ? st.nq[b] : 1;                    // query tokens of this sequence
+    const int tok0 = MULTI ? (int)blockIdx.y * (8 / G) : 0; // first query token of this CTA's token group
+    const int nq_g = MULTI ? min(nq - tok0, 8 / G) : 1;
+    if (MULTI && nq_g <= 0) return;                         // this sequence has no such group
+    const int rows = G * nq_g;                              // rows of the M tile that carry data (<= 8)
+    const int q_row0 = MULTI ? st.q_base[b] + tok0 : b;     // row of q / out of the group's first query token
     const int t0 = chunk * st.chunk_tokens;
-    const int t1 = min(len, t0 + st.chunk_tokens);
-    const int n_pages = (t1 - t0 + kPage - 1) / kPage;
+    // the group's last token sees len - nq + tok0 + nq_g positions: nothing beyond is fetched
+    const int t1 = min(MULTI ? len - nq + tok0 + nq_g : len, t0 + st.chunk_tokens);
+    const int n_pages = t1 > t0 ? (t1 - t0 + kPage - 1) / kPage : 0;
     const int lp0 = t0 / kPage;
     const int n_w = n_pages > warp ? (n_pages - warp + kWarps - 1) / kWarps : 0;   // pages of this warp (<= 32)
     const int new_tok = fa.k != nullptr ? st.new_tok[b] : -1;                       // fused append (decode steps)
@@ -100,8 +110,8 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     // ---- Q fragments (A operand): row gr of the group, rows >= G and 8..15 are zero ----
     uint32_t qa[KS][2];
     {
-        const uint16_t* qrow = q + ((size_t)b * g.H + (size_t)kvh * G + gr) * kDk;
-        const bool valid = gr < G;
+        const uint16_t* qrow = q + ((size_t)(q_row0 + (MULTI ? gr / G : 0)) * g.H + (size_t)kvh * G + (MULTI ? gr % G : gr)) * kDk;
+        const bool valid = gr < rows;
         // fused RoPE: the query is the token at position len-1; only dims kDv.. (the rope dims) rotate
         const float2* tab = fa.rope_tab ? fa.rope_tab + (size_t)b * ((kDk - kDv) / 2) : nullptr;
 #pragma unroll
@@ -130,6 +140,8 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         const uint32_t stg_u = smem_u32(stg);
         const int tok_base = (lp0 + warp + kWarps * i) * kPage;
         const int n_valid = min(kPage, t1 - tok_base);     // < 16 only on a sequence's last page
+        // tokens of this page that row gr may attend to (causal limit of its query token)
+        const int nv0 = MULTI ? max(0, min(n_valid, len - nq + tok0 + gr / G + 1 - tok_base)) : n_valid;
 
         if (new_tok >= 0 && tok_base == ((len - 1) & ~(kPage - 1))) {
             // This page holds the token appended by this step.  The TMA tile has the stale row:
@@ -184,10 +196,10 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         {
             const int c0 = 2 * j;
             float a0 = s0[0] * sm_scale, a1 = s0[1] * sm_scale, a2 = s1[0] * sm_scale, a3 = s1[1] * sm_scale;
-            if (c0 >= n_valid) a0 = -1e30f;
-            if (c0 + 1 >= n_valid) a1 = -1e30f;
-            if (c0 + 8 >= n_valid) a2 = -1e30f;
-            if (c0 + 9 >= n_valid) a3 = -1e30f;
+            if (c0 >= nv0) a0 = -1e30f;
+            if (c0 + 1 >= nv0) a1 = -1e30f;
+            if (c0 + 8 >= nv0) a2 = -1e30f;
+            if (c0 + 9 >= nv0) a3 = -1e30f;
             float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
@@ -196,6 +208,12 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
             const float nb = -mn * kLog2e;
             p[0] = ex2(fmaf(a0, kLog2e, nb)); p[1] = ex2(fmaf(a1, kLog2e, nb));
             p[2] = ex2(fmaf(a2, kLog2e, nb)); p[3] = ex2(fmaf(a3, kLog2e, nb));
+            if (MULTI) {                                    // a row may see nothing of a page: exp(-1e30 + 1e30) is 1, not 0
+                if (c0 >= nv0) p[0] = 0.0f;
+                if (c0 + 1 >= nv0) p[1] = 0.0f;
+                if (c0 + 8 >= nv0) p[2] = 0.0f;
+                if (c0 + 9 >= nv0) p[3] = 0.0f;
+            }
             l0 = l0 * alpha + (p[0] + p[1] + p[2] + p[3]);
             // the running maximum rarely moves after the first pages: skip the multiplies then
             if (!__all_sync(0xFFFFFFFFu, mn == m0)) {
@@ -230,8 +248,8 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     __syncthreads();
     float* red = reinterpret_cast<float*>(smem);            // [kWarps][G][kDv+2]
-    auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * G + row) * (kDv + 2) + d]; };
-    if (gr < G) {
+    auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * rows + row) * (kDv + 2) + d]; };
+    if (gr < rows) {
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             red_at(warp, gr, 8 * nt + 2 * j + 0) = o[nt][0];
@@ -241,7 +259,8 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     }
     __syncthreads();
     const int prow = st.chunk_base[b] + chunk;
-    for (int idx = threadIdx.x; idx < G * (kDv + 2); idx += blockDim.x) {
+    const int heads_per_row = MULTI ? g.H * st.nq_max : g.H;   // columns of a partial row
+    for (int idx = threadIdx.x; idx < rows * (kDv + 2); idx += blockDim.x) {
         const int row = idx / (kDv + 2), d = idx % (kDv + 2);
         float M = -1e30f;
 #pragma unroll
@@ -254,9 +273,11 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
 #pragma unroll
             for (int w = 0; w < kWarps; w++) val += red_at(w, row, d) * ex2((red_at(w, row, kDv) - M) * kLog2e);
         }
-        partials[partial_off(prow, kvh * G + row, g.H, kDv) + d] = val;
+        const int col = MULTI ? (tok0 + row / G) * g.H + kvh * G + row % G : kvh * G + row;
+        partials[partial_off(prow, col, heads_per_row, kDv) + d] = val;
     }
-    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag);
+    merge_if_last(g, st, mo, b, kvh, G, partials, s_flag,
+                  MergeMap{rows, heads_per_row, q_row0, MULTI ? tok0 : 0, MULTI ? (int)blockIdx.y * st.n_seqs * g.Hkv : 0});
 }
 
 PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
@@ -308,6 +329,42 @@ cudaError_t make_mla_tensor_maps(const Geometry& g, void* layer_pool, CUtensorMa
     return cudaSuccess;
 }
 
+template <bool BF, bool MULTI>
+static cudaError_t launch_mla_cfg(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map, const CUtensorMap* v_map,
+                                  const StepDev& st, const int32_t* page_table, const void* q, float* partials, int* status,
+                                  cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
+    static bool attr_done[64] = {};                         // per instantiation and device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(decode_mma_mla_kernel<BF, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    const int tpg = 8 / (g.H / g.Hkv);                      // multi-token attention: tokens per pass
+    const dim3 grid(st.n_items, MULTI ? (st.nq_max + tpg - 1) / tpg : 1);
+    decode_mma_mla_kernel<BF, MULTI><<<grid, kWarps * 32, kMlaSmem, s>>>(*k_map, *v_map, g, lp, st, page_table,
+                                                                         (const uint16_t*)q, partials, status, mo, fa);
+    return cudaGetLastError();
+}
+
+bool decode_mma_mla_multi_supported(const Geometry& g, int nq_max) {
+    return decode_mma_mla_supported(g) && nq_max >= 1 && (g.H / g.Hkv) * nq_max <= 8 * 8;   // up to 8 token groups
+}
+
+// Multi-token attention for the MLA shape (st.nq / st.q_base / st.nq_max set): q [n_tokens][H][192],
+// out [n_tokens][H][128]; `mo.counters` needs n_groups * n_seqs * Hkv zeroed counters.
+cudaError_t launch_decode_mma_mla_multi(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map,
+                                        const CUtensorMap* v_map, const StepDev& st, const int32_t* page_table,
+                                        const void* q, float* partials, int* status, cudaStream_t s, const MergeOut& mo) {
+    if (st.n_items <= 0) return cudaSuccess;
+    if (!decode_mma_mla_multi_supported(g, st.nq_max) || st.chunk_tokens > kPage * kWarps * 32 || !mo.counters || mo.peer)
+        return cudaErrorNotSupported;
+    const FuseAppend fa{nullptr, nullptr, nullptr};
+    return g.dtype == DT_BF16 ? launch_mla_cfg<true, true>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa)
+                              : launch_mla_cfg<false, true>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa);
+}
+
 cudaError_t launch_decode_mma_mla(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map,
                                   const CUtensorMap* v_map, const StepDev& st, const int32_t* page_table,
                                   const void* q, float* partials, int* status, cudaStream_t s,
@@ -316,23 +373,8 @@ cudaError_t launch_decode_mma_mla(const Geometry& g, const LayerPtrs& lp, const 
     if (!decode_mma_mla_supported(g) || st.chunk_tokens > kPage * kWarps * 32) return cudaErrorNotSupported;
     const MergeOut mo = merge ? *merge : MergeOut{nullptr, nullptr, nullptr, 0};
     const FuseAppend fa = fuse ? *fuse : FuseAppend{nullptr, nullptr, nullptr};
-    static bool attr_done[2][64] = {};                      // per instantiation and device
-    const int bf = g.dtype == DT_BF16;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_done[bf][dev]) {
-        cudaError_t e = bf ? cudaFuncSetAttribute(decode_mma_mla_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem)
-                           : cudaFuncSetAttribute(decode_mma_mla_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem);
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) attr_done[bf][dev] = true;
-    }
-    if (bf)
-        decode_mma_mla_kernel<true><<<st.n_items, kWarps * 32, kMlaSmem, s>>>(*k_map, *v_map, g, lp, st, page_table,
-                                                                            (const uint16_t*)q, partials, status, mo, fa);
-    else
-        decode_mma_mla_kernel<false><<<st.n_items, kWarps * 32, kMlaSmem, s>>>(*k_map, *v_map, g, lp, st, page_table,
-                                                                             (const uint16_t*)q, partials, status, mo, fa);
-    return cudaGetLastError();
+    return g.dtype == DT_BF16 ? launch_mla_cfg<true, false>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa)
+                              : launch_mla_cfg<false, false>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa);
 }
 
 }  // namespace tk

@@ -878,9 +878,12 @@ int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* 
     if (!q || !out) return fail(h, TK_INVALID_ARG, "decode_multi: null q/out");
     const tk::StepPlan& p = h->plan;
     if (p.nq_min < 1) return fail(h, TK_INVALID_ARG, "decode_multi: every sequence of the step must append at least one token");
-    if (!h->use_mma || h->mla_mma || !tk::decode_mma_multi_supported(h->geo, p.nq_max))
+    const bool ok = h->use_mma && (h->mla_mma ? tk::decode_mma_mla_multi_supported(h->geo, p.nq_max)
+                                              : tk::decode_mma_multi_supported(h->geo, p.nq_max));
+    if (!ok)
         return fail(h, TK_UNSUPPORTED, "decode_multi: needs the tensor-core kernel on a 16-bit pool and (heads per kv head) x "
-                                       "(tokens per sequence) <= 128 (here %d x %d)", h->geo.H / h->geo.Hkv, p.nq_max);
+                                       "(tokens per sequence) <= %d (here %d x %d)", h->mla_mma ? 64 : 128,
+                    h->geo.H / h->geo.Hkv, p.nq_max);
     if (h->mgr->cold_enabled() && h->mgr->cold_high_water() > 0)
         return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
     if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)
@@ -900,8 +903,11 @@ int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* 
         partials = h->d_multi_partials;
     }
     const tk::MergeOut mo{h->d_counters, out, nullptr, h->cfg.io_dtype, nullptr};
-    cudaError_t e = tk::launch_decode_mma_multi(h->geo, h->layer(layer), &h->maps[layer], h->dev, h->d_table, q,
-                                                partials, h->d_status, (cudaStream_t)stream, mo);
+    cudaError_t e = h->mla_mma
+        ? tk::launch_decode_mma_mla_multi(h->geo, h->layer(layer), &h->maps[layer], &h->maps_v[layer], h->dev, h->d_table, q,
+                                          partials, h->d_status, (cudaStream_t)stream, mo)
+        : tk::launch_decode_mma_multi(h->geo, h->layer(layer), &h->maps[layer], h->dev, h->d_table, q,
+                                      partials, h->d_status, (cudaStream_t)stream, mo);
     h->launches++;
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode_multi launch: %s", cudaGetErrorString(e));
     return TK_OK;

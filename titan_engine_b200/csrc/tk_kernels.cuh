@@ -140,6 +140,12 @@ cudaError_t launch_decode_mma_mla(const Geometry& g, const LayerPtrs& lp, const 
                                   const void* q, float* partials, int* status, cudaStream_t s,
                                   const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
 
+// ... and its multi-token form: 8/G tokens per pass, up to 8 token groups.
+bool        decode_mma_mla_multi_supported(const Geometry& g, int nq_max);
+cudaError_t launch_decode_mma_mla_multi(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map,
+                                        const CUtensorMap* v_map, const StepDev& st, const int32_t* page_table,
+                                        const void* q, float* partials, int* status, cudaStream_t s, const MergeOut& mo);
+
 // n FP32 values -> the 16-bit type `dtype` (round to nearest even).
 cudaError_t launch_f32_to_16(const float* src, void* dst, size_t n, int dtype, cudaStream_t s);
 

@@ -251,7 +251,8 @@ class PagedKVCache:
         """Causal attention for every token the step appended: q, out [n_tokens, H, D] (rows as in append)."""
         self._check_io(q, self._n_tokens, self.cfg.num_heads, "q")
         if out is None:
-            out = torch.empty_like(q)
+            out = torch.empty(self._n_tokens, self.cfg.num_heads, self.cfg.v_head_dim, dtype=self.io_torch_dtype,
+                              device=self.device)
         self._check(self._lib.tk_kv_decode_multi(self._h, layer, q.data_ptr(), out.data_ptr(), self._stream()))
         return out
 
