@@ -1,4 +1,4 @@
-"""The BASELINE configurations at their FULL sizes (one layer each), checked through properties
+"""The five benchmark configurations at their FULL sizes (one layer each), checked through properties
 that do not need the oracle to process the whole workload, plus the oracle itself on a seeded
 sample of sequences:
   * sampled sequences: attention within 2e-3 rel / 1e-2 abs of the CPU oracle
