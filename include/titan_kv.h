@@ -16,7 +16,9 @@
  *    mutex, src/api/server.cpp:33); all device work is stream-ordered and no entry
  *    point other than create/destroy and the *_host variants synchronises the device
  *  - no device allocation after tk_kv_create* (reference invariant: no cudaMalloc
- *    during generation, src/model/moe.cpp:49-108)
+ *    during generation, src/model/moe.cpp:49-108); the two exceptions are one-off:
+ *    the first tk_kv_decode_exchange of a handle, and a tk_kv_decode_multi step that
+ *    needs more split-KV workspace than any step before it
  *  - there is no CPU fallback: without a CUDA device every compute call fails.
  */
 #ifndef TITAN_KV_H
