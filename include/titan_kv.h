@@ -203,6 +203,9 @@ int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, voi
  * (<= 64 and 8 / (num_heads / num_kv_heads) tokens per pass for the MLA shape), every sequence of the step
  * appending at least one token; TK_UNSUPPORTED otherwise. */
 int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* stream);
+/* tk_kv_append of the step's rows followed by tk_kv_decode_multi, in one call. */
+int tk_kv_append_decode_multi(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
+                              void* stream);
 /* Same, but stops before normalisation: partial[n_seqs][H][D+2] f32 =
  * (o unnormalised [D], m, l), for a cross-GPU combine. */
 int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial, void* stream);

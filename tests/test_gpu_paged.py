@@ -671,9 +671,9 @@ def test_decode_multi_random_steps(seed):
         tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)])
         k16 = normal16(g, (len(tok_seq), Hkv, D), dt); v16 = normal16(g, (len(tok_seq), Hkv, D), dt)
         q16 = normal16(g, (len(tok_seq), H, D), dt)
-        t.gpu.append(0, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev))
+        got = t.gpu.append_decode_multi(0, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev),
+                                        to_torch16(q16, dt, t.dev)).float().cpu().numpy()
         t.pools[0].append(table, tok_seq, tok_pos, k16, v16)
-        got = t.gpu.decode_multi(0, to_torch16(q16, dt, t.dev)).float().cpu().numpy()
         want = t.pools[0].decode(table, tok_seq, tok_pos + 1, q16)
         assert_close(got, want, f"step {it}: {n_new} new tokens on lengths {old}", out_mantissa_bits=10)
         # reject a random tail of one sequence's new tokens

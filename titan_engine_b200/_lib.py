@@ -100,6 +100,7 @@ SIGNATURES = {
     "tk_peer_recv_combine": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "tk_peer_status": (C.c_int, [_P, C.c_void_p]),
     "tk_kv_decode_multi": (C.c_int, [_P, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tk_kv_append_decode_multi": (C.c_int, [_P, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "tk_kv_decode_exchange": (C.c_int, [_P, C.c_int32, C.c_void_p, _P, C.c_void_p, C.c_void_p]),
     "tk_kv_profile_enable": (C.c_int, [_P, C.c_int32]),
     "tk_kv_profile_read": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),

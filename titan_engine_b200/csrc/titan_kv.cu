@@ -913,6 +913,13 @@ int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* 
     return TK_OK;
 }
 
+int tk_kv_append_decode_multi(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
+                              void* stream) {
+    int st = tk_kv_append(h, layer, k, v, nullptr, stream);
+    if (st != TK_OK) return st;
+    return tk_kv_decode_multi(h, layer, q, out, stream);
+}
+
 // Attention over a sequence whose tokens are spread over the ranks of `peer`.  One launch where the
 // step allows it: the attention kernel's merging CTAs store their merged rows into every rank's
 // mailbox, publish and await one flag per (sequence, kv head) and write the combine themselves.

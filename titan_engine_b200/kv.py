@@ -256,6 +256,19 @@ class PagedKVCache:
         self._check(self._lib.tk_kv_decode_multi(self._h, layer, q.data_ptr(), out.data_ptr(), self._stream()))
         return out
 
+    def append_decode_multi(self, layer: int, k: torch.Tensor, v: torch.Tensor, q: torch.Tensor,
+                            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """append(k, v) of the step's tokens, then decode_multi(q): one library call per layer."""
+        self._check_io(k, self._n_tokens, self.cfg.num_kv_heads, "k")
+        self._check_io(v, self._n_tokens, self.cfg.num_kv_heads, "v")
+        self._check_io(q, self._n_tokens, self.cfg.num_heads, "q")
+        if out is None:
+            out = torch.empty(self._n_tokens, self.cfg.num_heads, self.cfg.v_head_dim, dtype=self.io_torch_dtype,
+                              device=self.device)
+        self._check(self._lib.tk_kv_append_decode_multi(self._h, layer, k.data_ptr(), v.data_ptr(), q.data_ptr(),
+                                                        out.data_ptr(), self._stream()))
+        return out
+
     def decode_exchange(self, layer: int, q: torch.Tensor, exchange, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Attention over the tokens of EVERY rank of `exchange` (a dist.PeerExchange): this rank's
         partial rows, then one kernel that swaps rows with the peers over NVLink and combines."""
