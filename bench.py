@@ -404,6 +404,50 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_append(args):
+    """`--append-prefill T`: the append half of the path alone - one prefill step of B sequences x T tokens
+    appended to every layer (page-table scatter; FP8 pools seal every completed page).  Prints one JSON line
+    with the per-layer time and the read + write bandwidth; not the headline metric."""
+    import torch
+    from titan_engine_b200 import PagedKVCache
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    s, T, L = SHAPE, args.append_prefill, args.layers
+    B, Hkv, D = s["B"], s["Hkv"], s["D"]
+    fp8 = s.get("esize", 2) == 1
+    reps = args.warmup + args.steps
+    pages_per_seq = (T * reps + 15) // 16 + 1
+    cache = PagedKVCache(L, s["H"], Hkv, D, B * pages_per_seq + 64, B, pages_per_seq, dtype="fp8" if fp8 else "bf16",
+                         max_step_tokens=B * T)
+    seqs = [cache.seq_alloc() for _ in range(B)]
+    gen = torch.Generator(device=dev); gen.manual_seed(7)
+    k = torch.randn(B * T, Hkv, D, device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B * T, Hkv, D, device=dev, generator=gen).to(torch.bfloat16)
+    times = []
+    for _ in range(reps):
+        cache.step_begin(seqs, [T] * B)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for l in range(L):
+            cache.append(l, k, v)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / L)
+    cache.device_status()
+    ms = float(np.median(times[args.warmup:]))
+    rd = B * T * Hkv * D * 2 * 2
+    wr = B * T * Hkv * D * 2 * (1 if fp8 else 2) + (B * (T // 16) * Hkv * 2 * 4 if fp8 else 0)
+    peak, peak_src = measured_peak()
+    print(json.dumps({"metric": "prefill_append_gbs", "value": (rd + wr) / (ms * 1e-3) / 1e9, "unit": "GB/s read + written",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "us_per_layer": ms * 1e3,
+                      "config": {"workload": f"prefill append: {B} sequences x {T} tokens, {Hkv} kv heads, head_dim {D}, "
+                                             f"{'FP8-E4M3' if fp8 else 'bf16'} pool, {L} layers"},
+                      "bytes_read_per_layer": rd, "bytes_written_per_layer": wr,
+                      "roofline": {"bound": "hbm", "achieved": (rd + wr) / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                                   "frac": (rd + wr) / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_src}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -423,6 +467,8 @@ def main():
     ap.add_argument("--ctx-range", type=int, nargs=2, default=None, metavar=("LO", "HI"),
                     help="experiment: context lengths uniform in [LO, HI] instead of the workload's (reported in config)")
     ap.add_argument("--seqs", type=int, default=0, help="experiment: sequences per GPU instead of the workload's")
+    ap.add_argument("--append-prefill", type=int, default=0, metavar="T",
+                    help="measure the append kernels alone: one prefill step of T tokens per sequence and layer")
     ap.add_argument("--separate", action="store_true", help="call append and decode separately (two entry points)")
     args = ap.parse_args()
     if args.workload == "70b-fp8":
@@ -439,6 +485,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.append_prefill > 0:
+        run_append(args)
     else:
         run_ours(args)
 
