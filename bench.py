@@ -448,6 +448,60 @@ def run_append(args):
                                    "frac": (rd + wr) / (ms * 1e-3) / 1e9 / peak, "peak_source": peak_src}}), flush=True)
 
 
+def run_multi(args):
+    """`--multi K`: every sequence of the workload appends K tokens per step and gets K causal attention
+    outputs (tk_kv_append_decode_multi) - the verification step of a speculative decoder.  Prints one JSON
+    line with the time per layer and per token-layer; not the headline metric."""
+    import torch
+    from titan_engine_b200 import PagedKVCache
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    s, K, L = SHAPE, args.multi, args.layers
+    B, ps = s["B"], s["ps"]
+    ctx = contexts(0, B, s["lo"], s["hi"])
+    reps = args.warmup + args.steps
+    pages_end = (ctx + reps * K + ps - 1) // ps
+    cache = PagedKVCache(L, s["H"], s["Hkv"], s["D"], int(pages_end.sum()) + 64, B, int(pages_end.max()) + 1, dtype="bf16",
+                         max_step_tokens=B * K)
+    seqs, at = [], 0
+    for b in range(B):
+        sid = cache.seq_alloc()
+        n = int((ctx[b] + ps - 1) // ps)
+        cache.adopt(sid, np.arange(at, at + n, dtype=np.int32), int(ctx[b]))
+        at += n
+        seqs.append(sid)
+    gen = torch.Generator(device=dev); gen.manual_seed(11)
+    for l in range(L):
+        cache.layer_views(l)[0].normal_(generator=gen)
+    k = torch.randn(B * K, s["Hkv"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn(B * K, s["Hkv"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
+    q = torch.randn(B * K, s["H"], s["D"], device=dev, generator=gen).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    times = []
+    for _ in range(reps):
+        cache.step_begin(seqs, [K] * B)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for l in range(L):
+            if K == 1:
+                cache.append(l, k, v)
+                cache.decode(l, q, out)
+            else:
+                cache.append_decode_multi(l, k, v, q, out)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / L)
+    cache.device_status()
+    ms = float(np.median(times[args.warmup:]))
+    print(json.dumps({"metric": "multi_token_decode_us_per_layer", "value": ms * 1e3, "unit": "us per layer (append + attention)",
+                      "higher_is_better": False, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "tokens_per_sequence": K, "us_per_token_layer": ms * 1e3 / K,
+                      "config": {"workload": f"{B} sequences, context U[{s['lo']},{s['hi']}], {s['H']} q / {s['Hkv']} kv heads, "
+                                             f"head_dim {s['D']}, bf16, {L} layers, {K} new tokens per sequence and step"}}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -469,6 +523,8 @@ def main():
     ap.add_argument("--seqs", type=int, default=0, help="experiment: sequences per GPU instead of the workload's")
     ap.add_argument("--append-prefill", type=int, default=0, metavar="T",
                     help="measure the append kernels alone: one prefill step of T tokens per sequence and layer")
+    ap.add_argument("--multi", type=int, default=0, metavar="K",
+                    help="measure multi-token attention: K new tokens per sequence and step (1 = plain decode, separate launches)")
     ap.add_argument("--separate", action="store_true", help="call append and decode separately (two entry points)")
     args = ap.parse_args()
     if args.workload == "70b-fp8":
@@ -487,6 +543,8 @@ def main():
         run_reference(args)
     elif args.append_prefill > 0:
         run_append(args)
+    elif args.multi > 0:
+        run_multi(args)
     else:
         run_ours(args)
 
