@@ -9,6 +9,9 @@ values from a fixed seed.
 
   python bench.py --gpus N --steps K --warmup W            (N>1: launched by torchrun)
   python bench.py --impl reference ...                      CPU oracle port on the host cores
+  python bench.py --workload 70b-fp8 | mla-bf16             the FP8 70B shape / the MLA cache shape (extras)
+  python bench.py --append-prefill T                        the append kernels alone (prefill step of T tokens)
+  python bench.py --multi K                                 multi-token attention (K new tokens per sequence)
 
 Prints ONE JSON line on rank 0.  `value` is device-resident throughput (decode steps/s,
 all GPUs); `e2e` goes through the host-buffer C-ABI entry point with the H2D/D2H copies
