@@ -151,6 +151,13 @@ class CpuLayer:
         self.v = O.f32_to_16(g.standard_normal((B, s["Hkv"], s["D"]), dtype=np.float32), O.BF16)
         self.q = O.f32_to_16(g.standard_normal((B, s["H"], s["D"]), dtype=np.float32), O.BF16)
         self.seqs = np.arange(B, dtype=np.int32)
+        # all host cores this process may use, whatever OMP_NUM_THREADS a multi-process launcher exported
+        # (torchrun sets it to 1; the other ranks of the reference arm have exited by now)
+        try:
+            cores = len(os.sched_getaffinity(0))
+        except AttributeError:
+            cores = os.cpu_count() or 1
+        O.set_num_threads(cores)
         self.threads = O.num_threads()
 
     def run(self) -> float:

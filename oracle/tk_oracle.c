@@ -610,6 +610,16 @@ void tko_combine(int n_parts, const float* m, const float* l, const float* o, in
     for (int d = 0; d < D; d++) out[d] *= inv;
 }
 
+/* The launcher of multi-process jobs pins OMP_NUM_THREADS to 1; a timed CPU arm that is alone on the
+ * host asks for its threads explicitly. */
+void tko_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int tko_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

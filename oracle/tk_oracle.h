@@ -132,6 +132,7 @@ void tko_rope_mla_f32(float* q, float* k, int num_heads, int num_kv_heads, int n
                       int position, float theta_base);
 
 int tko_num_threads(void);
+void tko_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

@@ -80,6 +80,7 @@ def lib() -> C.CDLL:
             "tko_rope_f32": (None, [vp, vp, i, i, i, i, f, f]),
             "tko_rope_mla_f32": (None, [vp, vp, i, i, i, i, i, f]),
             "tko_num_threads": (i, []),
+            "tko_set_num_threads": (None, [i]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(l, name)
@@ -272,6 +273,10 @@ def combine(m, l, o) -> np.ndarray:
 
 def num_threads() -> int:
     return lib().tko_num_threads()
+
+
+def set_num_threads(n: int) -> None:
+    lib().tko_set_num_threads(int(n))
 
 
 # ---- the compiled reference (GPU only) ---------------------------------------------------------

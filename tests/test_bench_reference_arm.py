@@ -23,6 +23,14 @@ def test_reference_arm_line():
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
 
 
+def test_reference_arm_uses_the_host_cores_under_a_launcher_that_pins_one_thread():
+    """torchrun exports OMP_NUM_THREADS=1 to every rank; the CPU arm must still use the cores it may run on."""
+    lines = _line("--impl", "reference", "--steps", "1", "--warmup", "0",
+                  env={"OMP_NUM_THREADS": "1", "RANK": "0", "WORLD_SIZE": "2", "LOCAL_RANK": "0"})
+    d = json.loads(lines[0])
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+
+
 def test_reference_arm_is_silent_on_other_ranks():
     assert _line("--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0",
                  env={"RANK": "1", "WORLD_SIZE": "2", "LOCAL_RANK": "1"}) == []
