@@ -84,6 +84,8 @@ typedef struct tk_kv_stats {    /* in the style of CacheStats, src/memory/memory
     int64_t evictions, prefetch_hits, prefetch_misses;
     int64_t bytes_h2d, bytes_d2h;
     int64_t steps, tokens_appended, pages_sealed;
+    int64_t evictions_refused;  /* (sequence, step) pairs whose old pages stayed in HBM because the host pool was
+                                   full; the step still succeeds, later steps end in TK_OUT_OF_PAGES once HBM fills */
 } tk_kv_stats;
 
 typedef struct tk_kv tk_kv;
@@ -118,7 +120,8 @@ int tk_kv_seq_free(tk_kv* h, int32_t seq);
  * fresh pool).  TK_OUT_OF_PAGES leaves all state unchanged. */
 int tk_kv_reserve(tk_kv* h, int32_t seq, int32_t n_tokens);
 /* Drop tokens past new_len (speculative rollback; the reference has none:
- * src/inference/speculative.cpp:306-307). */
+ * src/inference/speculative.cpp:306-307).  TK_UNSUPPORTED when new_len ends inside a page that is
+ * shared with a forked sequence or lives in the host (cold) pool: later appends would have to write it. */
 int tk_kv_truncate(tk_kv* h, int32_t seq, int32_t new_len);
 /* Install a caller-chosen page list (e.g. a shuffled pool) as the table of `seq`;
  * the pages must be free. */

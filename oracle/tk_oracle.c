@@ -338,6 +338,8 @@ int tko_truncate(tko_mgr* m, int seq, int new_len) {
     if (!live(m, seq) || new_len < 0 || new_len > m->seq_len[seq]) return TKO_INVALID_ARG;
     int keep = (new_len + m->page_size - 1) / m->page_size;
     int32_t* row = m->page_table + (size_t)seq * m->max_pages_per_seq;
+    /* a page in the host pool cannot become the page that later appends write */
+    if (new_len % m->page_size != 0 && keep > 0 && row[keep - 1] <= -2) return TKO_UNSUPPORTED;
     for (int i = keep; i < m->seq_pages[seq]; i++) {
         if (row[i] <= -2) m->cold_stack[m->cold_top++] = -2 - row[i];
         else              release_page(m, row[i]);

@@ -27,7 +27,7 @@ extern "C" {
 #endif
 
 /* status codes: same numbering as the product C ABI (include/titan_kv.h) */
-enum { TKO_OK = 0, TKO_INVALID_ARG = 1, TKO_OUT_OF_PAGES = 2, TKO_OUT_OF_SEQS = 5 };
+enum { TKO_OK = 0, TKO_INVALID_ARG = 1, TKO_OUT_OF_PAGES = 2, TKO_OUT_OF_SEQS = 5, TKO_UNSUPPORTED = 6 };
 /* storage dtypes: numbering of the reference's titan::DType (src/core/types.h:17-21) */
 enum { TKO_FP16 = 1, TKO_BF16 = 2, TKO_FP8_E4M3 = 3 };
 

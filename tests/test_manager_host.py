@@ -252,6 +252,46 @@ def test_cold_tier_state_matches_oracle_manager():
         PagedKVCache(2, 8, 2, 64, 8, 2, 8, dtype="fp8", host_only=True, hot_window=64, cold_pages=8)
 
 
+def test_truncate_into_a_cold_page_is_refused():
+    """A length that ends inside a page held in the host pool would make the next append write a page
+    that has no device row: refused, state untouched; a page-aligned length is fine and the next
+    token gets a device slot."""
+    c = PagedKVCache(2, 8, 2, 64, 64, 2, 64, dtype="fp16", host_only=True, max_step_tokens=4096,
+                     hot_window=64, cold_pages=64)
+    o = O.Manager(64, 2, 64, 16); assert o.enable_cold(64, 64) == O.OK
+    a = c.seq_alloc(); assert o.seq_alloc() == a
+    c.step_begin([a], [300]); assert o.reserve(a, 300) == O.OK and o.evict_cold(a, 0) == 0
+    c.step_begin([a], [0]); assert o.evict_cold(a, 300) == 14            # pages 0..13 go cold
+    assert c.digest() == o.digest() and c.slot(a, 37) == -1
+    d = c.digest()
+    with pytest.raises(KvError) as e:
+        c.truncate(a, 37)                                                 # inside cold page 2
+    assert e.value.status == L.TK_UNSUPPORTED and c.digest() == d and c.seq_len(a) == 300
+    assert o.truncate(a, 37) == 6 and o.digest() == d                     # the oracle refuses it too
+    c.truncate(a, 32); assert o.truncate(a, 32) == O.OK                   # page-aligned: pages 0, 1 stay cold
+    assert c.digest() == o.digest()
+    c.step_begin([a], [1]); assert o.reserve(a, 1) == O.OK and o.evict_cold(a, 32) == 0
+    assert c.digest() == o.digest() and c.slot(a, 32) >= 0
+    # inside a hot page: allowed
+    c.step_begin([a], [40]); assert o.reserve(a, 40) == O.OK and o.evict_cold(a, 33) >= 0
+    c.truncate(a, 50); assert o.truncate(a, 50) == O.OK
+    c.step_begin([a], [1]); assert o.reserve(a, 1) == O.OK and o.evict_cold(a, 50) >= 0
+    assert c.digest() == o.digest() and c.slot(a, 50) >= 0
+
+
+def test_full_cold_pool_is_counted_not_hidden():
+    """When the host pool cannot take a sequence's old pages they stay in HBM, the step succeeds and
+    the refusal shows in the stats."""
+    c = PagedKVCache(2, 8, 2, 64, 64, 2, 64, dtype="fp16", host_only=True, max_step_tokens=4096,
+                     hot_window=32, cold_pages=4)
+    a = c.seq_alloc()
+    c.step_begin([a], [200])
+    c.step_begin([a], [0])                                                # 10 pages should go cold, 4 fit: none moves
+    st = c.stats()
+    assert st["evictions_refused"] == 1 and st["pages_cold"] == 0
+    assert "cold" in c._lib.tk_kv_last_error(c._h).decode()
+
+
 def test_fork_shares_full_pages_and_counts_references():
     c = host_cache(num_pages=16, max_seqs=4, mpps=8)
     o = O.Manager(16, 4, 8, 16)

@@ -28,7 +28,7 @@ class KvStats(C.Structure):
     _fields_ = [(n, C.c_int64) for n in (
         "pages_total", "pages_free", "pages_cold", "page_allocs", "page_frees", "seq_allocs",
         "seq_frees", "evictions", "prefetch_hits", "prefetch_misses", "bytes_h2d", "bytes_d2h",
-        "steps", "tokens_appended", "pages_sealed")]
+        "steps", "tokens_appended", "pages_sealed", "evictions_refused")]
 
 
 class SchedConfig(C.Structure):

@@ -90,6 +90,8 @@ int PageManager::truncate(int seq, int new_len) {
     const int32_t* r = row(seq);
     // the new last page would be appended to later: it must not be shared with another sequence
     if (new_len % page_size_ != 0 && keep > 0 && r[keep - 1] >= 0 && refcount_[r[keep - 1]] > 1) return ST_UNSUPPORTED;
+    // ... nor live in the host pool: a cold page has no device row a later append could write
+    if (new_len % page_size_ != 0 && keep > 0 && r[keep - 1] <= -2) return ST_UNSUPPORTED;
     for (int i = keep; i < seq_pages_[seq]; i++) {
         if (r[i] <= -2) cold_stack_.push_back(-2 - r[i]);
         else            release_page(r[i]);
@@ -238,6 +240,8 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         int64_t new_len = (int64_t)seq_len_[s] + add;
         int64_t need = (new_len + ps - 1) / ps;
         if (need > max_pages_per_seq_) return ST_INVALID_ARG;
+        // the partly filled last page receives this step's first rows: it must have a device row
+        if (add > 0 && seq_len_[s] % ps != 0 && row(s)[seq_len_[s] / ps] < 0) return ST_UNSUPPORTED;
         extra_pages += need - seq_pages_[s];
         total_new += add;
     }
@@ -362,8 +366,12 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         plan->chunk_base[i + 1] = plan->chunk_base[i] + rows;
     }
     // after every reservation of the step: pages that fell out of the hot window go cold
+    // (a full host pool moves nothing for that sequence: its pages stay hot and the step still
+    // succeeds; the caller sees it in evictions_refused and, later, as ST_OUT_OF_PAGES)
+    plan->evictions_refused = 0;
     if (cold_enabled())
-        for (int i = 0; i < n_seqs; i++) evict_cold(seqs[i], old_lens[i], &plan->evictions);
+        for (int i = 0; i < n_seqs; i++)
+            if (evict_cold(seqs[i], old_lens[i], &plan->evictions) < 0) plan->evictions_refused++;
     // biggest items first, so the short tails fill the end of the schedule
     std::vector<int32_t> order(plan->items.size());
     for (size_t i = 0; i < order.size(); i++) order[i] = (int32_t)i;

@@ -56,6 +56,7 @@ struct StepPlan {
     std::vector<WorkItem> items;
     std::vector<SealItem> seals;
     std::vector<Eviction> evictions; // pages that went cold in this step (copy out before reuse)
+    int32_t evictions_refused = 0;   // sequences whose pages stayed hot because the host pool was full
 };
 
 class PageManager {

@@ -624,6 +624,10 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     h->stats.steps++;
     h->stats.tokens_appended += (int64_t)p.tok_b.size();
     h->stats.pages_sealed += (int64_t)p.seals.size();
+    if (p.evictions_refused > 0) {
+        h->stats.evictions_refused += p.evictions_refused;
+        fail(h, TK_OK, "step_begin: host (cold) pool is full, %d sequence(s) kept their old pages in HBM", p.evictions_refused);
+    }
     if (h->host_only) { h->mgr->delta().clear(); h->have_step = true; return TK_OK; }
 
     cudaStream_t s = (cudaStream_t)stream;
