@@ -293,8 +293,9 @@ int tk_kv_profile_read_each(tk_kv* h, float* ms_out, int32_t cap, int32_t* launc
  * the library), so the call allocates nothing on the device and is refused — not truncated —
  * beyond n_seqs 256, 4096 (sequence, 256-token chunk, kv head) work items or 4 MiB of
  * partial rows.  All calls on a device share that array: calls whose kernels may overlap
- * race, keep them on one stream.  A device's first call looks the array's address up; make
- * it outside stream capture.
+ * race, keep them on one stream.  A device's first call looks the array's address up.  Every
+ * call uploads its work list from host memory that lives only until the call returns, so a call
+ * made while `stream` is being captured into a graph is refused (TK_INVALID_ARG).
  *   pool        device, one layer: [num_pages][Hkv][2][16][D] in dtype (TK_FP16 / TK_BF16)
  *   page_table  device int32 [n_seqs][max_pages_per_seq]
  *   seq_lens    HOST int32 [n_seqs]

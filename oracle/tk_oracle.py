@@ -21,9 +21,23 @@ FP16, BF16, FP8 = 1, 2, 3
 OK, INVALID_ARG, OUT_OF_PAGES = 0, 1, 2
 
 
+def reference_root() -> str:
+    """Root of the reference tree as BASELINE.json names it (`reference_path`), or "" when that
+    file or that directory is absent (e.g. on a GPU box, which only has the prebuilt files)."""
+    import json
+    try:
+        path = json.load(open(os.path.join(HERE, "..", "BASELINE.json"))).get("reference_path", "")
+    except (OSError, ValueError):
+        return ""
+    return path if path and os.path.isdir(os.path.join(path, "src")) else ""
+
+
 def build(ref: bool = True) -> None:
     """Compile the oracle (and, when the reference tree is present, the reference harness)."""
-    subprocess.run(["make", "-s", "-C", HERE, "oracle"] + (["ref"] if ref else []), check=True)
+    subprocess.run(["make", "-s", "-C", HERE, "oracle"], check=True)
+    root = reference_root()
+    if ref and root:
+        subprocess.run(["make", "-s", "-C", HERE, "ref", f"REF={root}"], check=True)
 
 
 class View(C.Structure):

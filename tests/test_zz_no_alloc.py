@@ -3,9 +3,11 @@
 It exists for callers that may not allocate device memory at the point where they need
 attention (no handle, no workspace: its split-KV scratch is a fixed array inside the
 library).  This test drives it through the C ABI on the pool and page tables of an ordinary
-cache and checks it against the handle-based entry point, tk_kv_decode, twice in a row:
-the second call reuses the scratch the first one left behind.  It also checks that oversized
-requests are refused and that the call leaves the device allocator alone.
+cache and checks it, twice in a row, against the CPU oracle and against the handle-based entry
+point tk_kv_decode: the second call reuses the scratch the first one left behind.  It also
+checks that oversized requests are refused and that a call takes no device memory: the
+driver's count of free bytes (which sees every allocation of the process, the library's own
+included) is the same before and after.
 
 Collected last (file name), so a run that stops at the first failure has already run
 every other test."""
@@ -41,26 +43,36 @@ def test_static_decode_matches_handle_decode_twice_in_a_row():
     for i, s in enumerate(seqs):
         pt = cache.page_table(s)
         table[i, :len(pt)] = pt
+    # the same rows in the CPU oracle's pool
+    ref_pool = O.Pool(O.BF16, n_pages, H, Hkv, D, len(lens), mpps, 16)
+    tok_seq = np.concatenate([np.full(n, i, np.int32) for i, n in enumerate(lens)])
+    tok_pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+    ref_pool.append(table, tok_seq, tok_pos, k, v)
     d_table = torch.from_numpy(table).to(dev)
     pool = cache.layer_views(0)[0]
     host_lens = np.asarray(lens, dtype=np.int32)
     stream = torch.cuda.current_stream().cuda_stream
 
-    for call in range(2):
-        q = to_torch16(normal16(g, (len(lens), H, D), O.BF16), O.BF16, dev)
-        want = cache.decode(0, q).float().cpu().numpy()
+    for call in range(3):                                  # call 0 also warms up (address look-up, module load)
+        q16 = normal16(g, (len(lens), H, D), O.BF16)
+        q = to_torch16(q16, O.BF16, dev)
+        want = ref_pool.decode(table, np.arange(len(lens)), lens, q16)
+        handle = cache.decode(0, q).float().cpu().numpy()
         out = torch.zeros_like(q)
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated(dev)
+        before = torch.cuda.mem_get_info(dev)[0]
         st = lib.tk_paged_decode_static(pool.data_ptr(), L.TK_BF16, n_pages, d_table.data_ptr(), mpps,
                                         host_lens.ctypes.data_as(C.POINTER(C.c_int32)), len(lens), H, Hkv, D,
                                         q.data_ptr(), out.data_ptr(), stream)
         assert st == L.TK_OK, f"call {call}: status {st}"
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated(dev) == before
+        if call > 0:
+            assert torch.cuda.mem_get_info(dev)[0] == before, "the call changed the device's free memory"
         got = out.float().cpu().numpy()
         assert np.abs(got).max() > 0
-        assert_close(got, want, f"static entry point vs tk_kv_decode, call {call}", rtol=RTOL, atol=ATOL,
+        assert_close(got, want, f"static entry point vs the CPU oracle, call {call}", rtol=RTOL, atol=ATOL,
+                     out_mantissa_bits=7)
+        assert_close(got, handle, f"static entry point vs tk_kv_decode, call {call}", rtol=RTOL, atol=ATOL,
                      out_mantissa_bits=7)
 
     # beyond the fixed scratch: refused with a status, nothing launched

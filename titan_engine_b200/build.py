@@ -57,7 +57,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return LIB
     os.makedirs(OBJ, exist_ok=True)
     nvcc = nvcc_path()
-    inc = ["-I", os.path.join(HERE, "..", "include"), "-I", CSRC, "-I", os.path.join(CSRC, "compat")]
+    inc = ["-I", os.path.join(HERE, "..", "include"), "-I", CSRC, "-I", os.path.join(CSRC, "compat"),
+           "-I", os.path.join(CSRC, "compat", "standalone")]
     hdr_time = max(os.path.getmtime(h) for h in headers())
 
     def compile_one(src: str) -> tuple[str, int, str]:

@@ -7,6 +7,7 @@
 #include "compute/dispatch.h"
 
 #include "../../../include/titan_kv.h"
+#include "../tk_kernels.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -48,58 +49,6 @@ __global__ void compat_update_kernel(void* __restrict__ pool, const float* __res
     else      ((__half*)pool)[off] = __float2half_rn(x);
 }
 
-// Same arithmetic, operation by operation, as the reference's rope_kernel
-// (src/compute/cuda/attention.cu:15-48): pairs (d, d+1), freq = (1/powf(theta, d/D)) * scaling,
-// angle = position * freq.  One thread per (head, pair).
-__global__ void compat_rope_kernel(float* __restrict__ q, float* __restrict__ k, int num_heads,
-                                   int num_kv_heads, int head_dim, int position, float theta_base,
-                                   float rope_scaling) {
-    const int head = blockIdx.x;
-    const int d = threadIdx.x * 2;
-    if (d >= head_dim) return;
-    float freq = 1.0f / powf(theta_base, (float)d / head_dim);
-    freq *= rope_scaling;
-    const float angle = position * freq;
-    const float c = cosf(angle), s = sinf(angle);
-    if (head < num_heads) {
-        float* p = q + (size_t)head * head_dim;
-        const float a = p[d], b = p[d + 1];
-        p[d] = a * c - b * s;
-        p[d + 1] = a * s + b * c;
-    }
-    if (head < num_kv_heads) {
-        float* p = k + (size_t)head * head_dim;
-        const float a = p[d], b = p[d + 1];
-        p[d] = a * c - b * s;
-        p[d + 1] = a * s + b * c;
-    }
-}
-
-// Same arithmetic as the reference's rope_mla_kernel (src/compute/cuda/attention.cu:259-294): only the
-// rope dims, freq = 1/powf(theta, d/rope_hd).  One thread per (head, pair).
-__global__ void compat_rope_mla_kernel(float* __restrict__ q, float* __restrict__ k, int num_heads, int num_kv_heads,
-                                       int nope_hd, int rope_hd, int position, float theta_base) {
-    const int head = blockIdx.x;
-    const int d = threadIdx.x * 2;
-    if (d >= rope_hd) return;
-    const float freq = 1.0f / powf(theta_base, (float)d / rope_hd);
-    const float angle = position * freq;
-    const float c = cosf(angle), s = sinf(angle);
-    const int head_dim = nope_hd + rope_hd;
-    if (head < num_heads) {
-        float* p = q + (size_t)head * head_dim + nope_hd;
-        const float a = p[d], b = p[d + 1];
-        p[d] = a * c - b * s;
-        p[d + 1] = a * s + b * c;
-    }
-    if (head < num_kv_heads) {
-        float* p = k + (size_t)head * head_dim + nope_hd;
-        const float a = p[d], b = p[d + 1];
-        p[d] = a * c - b * s;
-        p[d + 1] = a * s + b * c;
-    }
-}
-
 }  // namespace
 
 KVCache::~KVCache() { release(); }
@@ -125,6 +74,12 @@ bool KVCache::setup(uint32_t L, uint32_t Hkv, uint32_t D, uint32_t Dv, uint32_t 
     release();
     num_layers_ = L; num_kv_heads_ = Hkv; head_dim_ = D; v_head_dim_ = Dv == D ? 0 : Dv; max_seq_len_ = max_seq;
     seq_len_ = 0; planned_len_ = planned_heads_ = -1;
+    if (dtype != DType::FP32 && dtype != DType::FP16 && dtype != DType::BF16) {
+        // FP8 pools need the step interface (open pages, sealing); this class appends row by row
+        KV_LOG("KV cache: storage dtype %d is not served through titan::KVCache (FP32/FP16 -> fp16 pool, BF16 -> bf16 "
+               "pool); FP8-E4M3 pools are behind the C ABI (tk_kv_create with dtype TK_FP8_E4M3)", (int)dtype);
+        return false;
+    }
     store_dtype_ = dtype == DType::BF16 ? TK_BF16 : TK_FP16;    // FP32 / FP16 requests are stored as FP16
     const size_t ref_stride = (size_t)max_seq * Hkv * D;        // floats per layer in the reference's K slab
     const size_t ref_vstride = (size_t)max_seq * Hkv * Dv;      // ... and in its V slab
@@ -323,21 +278,17 @@ void attention_decode_mla(const float* q, const float* k_cache, const float* v_c
     attend_impl("attention_decode_mla", q, k_cache, output, num_heads, num_kv_heads, k_head_dim, v_head_dim, seq_len, stream);
 }
 
+// Both run the library's own FP32 rotation kernel (rope_append.cu).
 void apply_rope(float* q, float* k, int num_heads, int num_kv_heads, int head_dim, int position, float theta,
                 float scaling, cudaStream_t stream) {
-    const int max_heads = num_heads > num_kv_heads ? num_heads : num_kv_heads;
-    const int threads = head_dim / 2;
-    if (max_heads <= 0 || threads <= 0) return;
-    compat_rope_kernel<<<max_heads, threads, 0, stream>>>(q, k, num_heads, num_kv_heads, head_dim, position, theta, scaling);
+    if (head_dim < 2 || num_heads < 0 || num_kv_heads < 0) return;
+    tk::launch_rope_f32(q, k, num_heads, num_kv_heads, head_dim, 0, head_dim, position, theta, scaling, stream);
 }
 
 void apply_rope_mla(float* q, float* k, int num_heads, int num_kv_heads, int nope_hd, int rope_hd, int position,
                     float theta, cudaStream_t stream) {
-    const int max_heads = num_heads > num_kv_heads ? num_heads : num_kv_heads;
-    const int threads = rope_hd / 2;
-    if (threads < 1 || max_heads < 1) return;
-    compat_rope_mla_kernel<<<max_heads, threads, 0, stream>>>(q, k, num_heads, num_kv_heads, nope_hd, rope_hd, position,
-                                                             theta);
+    if (rope_hd < 2 || nope_hd < 0 || num_heads < 0 || num_kv_heads < 0) return;
+    tk::launch_rope_f32(q, k, num_heads, num_kv_heads, nope_hd + rope_hd, nope_hd, rope_hd, position, theta, 1.0f, stream);
 }
 
 }  // namespace cuda

@@ -1,5 +1,6 @@
-// compute/dispatch.h — the attention operators of the reference's operator header
-// (reference: src/compute/dispatch.h:68-75), served by the paged B200 KV cache.
+// standalone/compute/dispatch.h — the attention operators of the reference's operator header
+// (reference: src/compute/dispatch.h:68-79), served by the paged B200 KV cache.  For builds outside
+// the reference tree; inside it the reference's own dispatch.h declares the same four functions.
 #pragma once
 
 #include <cuda_runtime.h>

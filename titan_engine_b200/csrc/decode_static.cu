@@ -18,12 +18,15 @@
 //   * the array keeps whatever the previous call left.  Nothing in it has to start at zero:
 //     each call rewrites the work list and every partial row it later reads;
 //   * the device address of the array is looked up once per device, on that device's first
-//     call.  Make that first call outside any stream capture.
+//     call;
+//   * every call uploads its work list from host memory that lives only until the call returns,
+//     so a call is refused while its stream is being captured into a graph.
 #include "../../include/titan_kv.h"
 
 #include "tk_kernels.cuh"
 
 #include <cstdio>
+#include <mutex>
 #include <vector>
 
 namespace {
@@ -47,6 +50,7 @@ struct StaticScratch {
 static __device__ __align__(256) unsigned char g_static_scratch[sizeof(StaticScratch)];
 
 StaticScratch* g_scratch_addr[64] = {};
+std::mutex g_scratch_mu;        // first calls on a device may come from several host threads
 
 // Device address of the array on the current device; looked up on the first call per device.
 cudaError_t scratch_for_current_device(StaticScratch** out) {
@@ -54,6 +58,7 @@ cudaError_t scratch_for_current_device(StaticScratch** out) {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
     if (!g_scratch_addr[dev]) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_static_scratch);
@@ -85,12 +90,29 @@ extern "C" int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t n
     if (head_dim != 64 && head_dim != 128) return refuse("head_dim must be 64 or 128");
     if (num_pages <= 0 || max_pages_per_seq <= 0) return refuse("num_pages and max_pages_per_seq must be positive");
 
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone)
+        return refuse("the stream is being captured: this call uploads per-call host data and cannot be recorded");
+
+    // size check first, by arithmetic: nothing is built for a request that will be refused
+    int64_t total_chunks = 0;
+    for (int b = 0; b < n_seqs; b++) {
+        const int n = seq_lens_host[b];
+        if (n < 0 || ((int64_t)n + kPage - 1) / kPage > max_pages_per_seq) return refuse("a sequence length does not fit its page-table row");
+        total_chunks += ((int64_t)n + kChunkTokens - 1) / kChunkTokens;
+    }
+    if (total_chunks * num_kv_heads > kMaxItems)
+        return refuse("too much work for the fixed scratch: more than 4096 (sequence, chunk, kv head) items");
+    if ((size_t)total_chunks * num_heads * (head_dim + 2) > kMaxPartialFloats)
+        return refuse("too much work for the fixed scratch: partial rows exceed 4 MiB (use tk_kv_decode with a handle)");
+
     // work list: one item per (sequence, 256-token chunk, kv head), built on the host
     std::vector<int32_t> seq(n_seqs), len(n_seqs), chunk_base(n_seqs + 1, 0);
     std::vector<int4> items;
+    items.reserve((size_t)total_chunks * num_kv_heads);
     for (int b = 0; b < n_seqs; b++) {
         const int n = seq_lens_host[b];
-        if (n < 0 || (n + kPage - 1) / kPage > max_pages_per_seq) return refuse("a sequence length does not fit its page-table row");
         seq[b] = b;
         len[b] = n;
         const int chunks = (n + kChunkTokens - 1) / kChunkTokens;
@@ -98,18 +120,12 @@ extern "C" int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t n
         for (int c = 0; c < chunks; c++)
             for (int h = 0; h < num_kv_heads; h++) items.push_back(make_int4(b, c, h, 0));
     }
-    if ((int)items.size() > kMaxItems)
-        return refuse("too much work for the fixed scratch: more than 4096 (sequence, chunk, kv head) items");
-    if ((size_t)chunk_base[n_seqs] * num_heads * (head_dim + 2) > kMaxPartialFloats)
-        return refuse("too much work for the fixed scratch: partial rows exceed 4 MiB (use tk_kv_decode with a handle)");
-
     StaticScratch* sc = nullptr;
     cudaError_t e = scratch_for_current_device(&sc);
     if (e != cudaSuccess) {
         fprintf(stderr, "[titan-kv] tk_paged_decode_static: cudaGetSymbolAddress: %s\n", cudaGetErrorString(e));
         return TK_CUDA_ERROR;
     }
-    cudaStream_t s = (cudaStream_t)stream;
     // pageable sources: each copy is staged by the driver before the call returns
     if ((e = cudaMemcpyAsync(sc->seq, seq.data(), sizeof(int32_t) * n_seqs, cudaMemcpyHostToDevice, s)) != cudaSuccess ||
         (e = cudaMemcpyAsync(sc->len, len.data(), sizeof(int32_t) * n_seqs, cudaMemcpyHostToDevice, s)) != cudaSuccess ||

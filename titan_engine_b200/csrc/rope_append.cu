@@ -60,6 +60,28 @@ __global__ void rope16_kernel(Geometry g, StepDev st, const uint16_t* __restrict
     }
 }
 
+// FP32 rows in place, one position for all of them (the reference's operator interface:
+// apply_rope / apply_rope_mla, src/compute/dispatch.h:68-72).  The q heads and the k heads form one
+// flat list of (row, pair) units; a thread takes one unit.  Rows are row_dim floats, of which the
+// last rope_dims, starting at rope_off, rotate; freq = (1/powf(theta, d/rope_dims)) * scaling with d
+// counted from rope_off, angle = position * freq (rope_kernel / rope_mla_kernel,
+// src/compute/cuda/attention.cu:22-37,266-283).
+__global__ void rope_f32_kernel(float* __restrict__ q, float* __restrict__ k, int n_q_rows, int n_k_rows, int row_dim,
+                                int rope_off, int rope_dims, int position, float theta, float scaling) {
+    const int half = rope_dims / 2;
+    const int unit = blockIdx.x * blockDim.x + threadIdx.x;
+    if (unit >= (n_q_rows + n_k_rows) * half) return;
+    const int row = unit / half, d = (unit % half) * 2;
+    float* p = (row < n_q_rows ? q + (size_t)row * row_dim : k + (size_t)(row - n_q_rows) * row_dim) + rope_off;
+    float freq = 1.0f / powf(theta, (float)d / rope_dims);
+    freq *= scaling;
+    const float angle = position * freq;
+    const float c = cosf(angle), s = sinf(angle);
+    const float x0 = p[d], x1 = p[d + 1];
+    p[d] = x0 * c - x1 * s;
+    p[d + 1] = x0 * s + x1 * c;
+}
+
 // (cos, sin) of every sequence's newest position, one entry per pair: tab[b][d/2].
 __global__ void rope_table_kernel(Geometry g, StepDev st, float2* __restrict__ tab, float theta, float scaling) {
     const int rd = rope_dims(g), half = rd / 2;
@@ -80,6 +102,15 @@ cudaError_t launch_rope_table(const Geometry& g, const StepDev& st, float2* tab,
     const int n = st.n_seqs * (rope_dims(g) / 2);
     if (n <= 0) return cudaSuccess;
     rope_table_kernel<<<(n + 255) / 256, 256, 0, s>>>(g, st, tab, theta, scaling);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope_f32(float* q, float* k, int n_q_rows, int n_k_rows, int row_dim, int rope_off, int rope_dims,
+                            int position, float theta, float scaling, cudaStream_t s) {
+    const int units = (n_q_rows + n_k_rows) * (rope_dims / 2);
+    if (units <= 0) return cudaSuccess;
+    rope_f32_kernel<<<(units + 127) / 128, 128, 0, s>>>(q, k, n_q_rows, n_k_rows, row_dim, rope_off, rope_dims, position,
+                                                        theta, scaling);
     return cudaGetLastError();
 }
 

@@ -99,6 +99,11 @@ cudaError_t launch_rope_table(const Geometry& g, const StepDev& st, float2* tab,
 cudaError_t launch_rope16(const Geometry& g, const StepDev& st, const void* q, const void* k, void* q_out,
                           void* k_out, float theta, float scaling, cudaStream_t s);
 
+// RoPE of FP32 rows in place at one position: q [n_q_rows][row_dim], k [n_k_rows][row_dim]; the rope_dims
+// dims from rope_off on rotate (the whole row: rope_off 0, rope_dims = row_dim).
+cudaError_t launch_rope_f32(float* q, float* k, int n_q_rows, int n_k_rows, int row_dim, int rope_off, int rope_dims,
+                            int position, float theta, float scaling, cudaStream_t s);
+
 // Copies `bytes` (multiple of 16) from src + l*src_stride to dst + l*dst_stride for l in [0, n_layers):
 // one page (or open page) of every layer after a fork.
 cudaError_t launch_copy_layers(const void* src, size_t src_stride, void* dst, size_t dst_stride, size_t bytes,
