@@ -46,6 +46,9 @@ enum { TK_FP32 = 0, TK_FP16 = 1, TK_BF16 = 2, TK_FP8_E4M3 = 3 };
 
 /* which decode kernel tk_kv_decode launches */
 enum { TK_DECODE_AUTO = 0, TK_DECODE_SIMT = 1, TK_DECODE_MMA = 2 };
+/* who merges the split-KV partial rows: the attention kernel's last CTA per (sequence, kv head), or a
+ * combine launch of its own after it */
+enum { TK_MERGE_IN_KERNEL = 0, TK_MERGE_SEPARATE = 1 };
 
 /* Stands in for the (L, Hkv, D, max_seq_len, dtype) argument list of
  * KVCache::initialize (src/inference/kv_cache.h:21-23) plus the fields of
@@ -75,7 +78,8 @@ typedef struct tk_kv_config {
                                    (KVCache::initialize_external_mla, src/inference/kv_cache.cpp:83-108;
                                    attention_decode_mla, src/compute/cuda/attention.cu:168-253): K rows and q
                                    have head_dim, scale = 1/sqrtf(head_dim); 16-bit storage, generic kernel */
-    int32_t reserved[3];
+    int32_t merge_impl;         /* TK_MERGE_* */
+    int32_t reserved[2];
 } tk_kv_config;
 
 typedef struct tk_kv_stats {    /* in the style of CacheStats, src/memory/memory_manager.h:211-220 */
@@ -100,7 +104,9 @@ void   tk_kv_config_default(tk_kv_config* cfg);
 size_t tk_kv_arena_bytes(const tk_kv_config* cfg);     /* device bytes create_external needs */
 int    tk_kv_create(const tk_kv_config* cfg, tk_kv** out);
 /* Adopts caller-owned device memory (e.g. carved from the reference's VramPool,
- * src/model/moe.cpp:549-595); it is never freed by the handle (kv_cache.cpp:71). */
+ * src/model/moe.cpp:549-595); it is never freed by the handle (kv_cache.cpp:71).  All arena_bytes
+ * belong to the handle: when they exceed tk_kv_arena_bytes by 4 KiB or more, the 4 KiB behind the
+ * pool hold guard bytes (tk_kv_check_canaries). */
 int    tk_kv_create_external(const tk_kv_config* cfg, void* arena, size_t arena_bytes, tk_kv** out);
 int    tk_kv_destroy(tk_kv* h);
 int    tk_kv_get_config(const tk_kv* h, tk_kv_config* out);
@@ -206,6 +212,9 @@ int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, voi
  * (<= 64 and 8 / (num_heads / num_kv_heads) tokens per pass for the MLA shape), every sequence of the step
  * appending at least one token; TK_UNSUPPORTED otherwise. */
 int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* stream);
+/* tk_kv_decode_multi with the output type given: TK_FP32 (the reference's float* interface,
+ * src/compute/dispatch.h:73-75) or the handle's io dtype. */
+int tk_kv_decode_multi_ex(tk_kv* h, int32_t layer, const void* q, void* out, int32_t out_dtype, void* stream);
 /* tk_kv_append of the step's rows followed by tk_kv_decode_multi, in one call. */
 int tk_kv_append_decode_multi(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
                               void* stream);
@@ -350,6 +359,18 @@ int tk_sched_get_stats(const tk_sched* s, tk_sched_stats* out);
  * TK_TIMEOUT and the context stays usable.  (The reference reports failures as bool / log lines
  * only, src/inference/kv_cache.cpp:34-47.) */
 int tk_kv_selftest_bounded_wait(tk_kv* h, int32_t limit_ms, void* stream);
+
+/* Test hook for the fail-closed rule: sets the handle's device status word (TK_OK or TK_TIMEOUT) from the
+ * host, as a timed-out device wait would.  While the word is set, attention launches on the handle write no
+ * output; tk_kv_device_status reports and clears it. */
+int tk_kv_selftest_set_status(tk_kv* h, int32_t value, void* stream);
+/* Stray-write check (the reference relies on external memory checkers; this is built in): 4 KiB of guard
+ * bytes sit behind the pool arena (when the handle allocated it, or an external arena is 4 KiB larger than
+ * tk_kv_arena_bytes), the page table, the split-KV workspace and the step metadata.  Drains `stream`,
+ * compares them, and returns TK_CUDA_ERROR naming the buffer when any byte changed. */
+int tk_kv_check_canaries(tk_kv* h, void* stream);
+/* The same for an exchange mailbox (guard bytes behind the flags). */
+int tk_peer_check_canaries(tk_peer* p, void* stream);
 
 /* Number of kernels this library has launched on this handle so far. */
 int64_t tk_kv_launch_count(const tk_kv* h);

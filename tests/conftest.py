@@ -17,3 +17,19 @@ def oracle():
     from oracle import tk_oracle
     tk_oracle.lib()
     return tk_oracle
+
+
+@pytest.fixture(autouse=True)
+def _guard_bytes_intact(request):
+    """After every GPU test: no kernel wrote past the end of a buffer of any cache or exchange that is
+    still open (guard bytes behind the arena, the page table, the split-KV workspace, the step metadata
+    and the exchange mailbox).  Stands in for a memory checker on out-of-bounds stores."""
+    yield
+    if request.node.get_closest_marker("gpu") is None:
+        return
+    from titan_engine_b200.kv import PagedKVCache
+    from titan_engine_b200.dist import PeerExchange
+    for c in list(PagedKVCache.live):
+        c.check_canaries()
+    for x in list(PeerExchange.live or []):
+        x.check_canaries()

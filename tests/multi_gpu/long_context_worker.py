@@ -48,10 +48,9 @@ def main():
     full = torch.randn(n_pg, Hkv, 2, 16, Dh, device=dev, generator=gen).to(torch.bfloat16)   # layer-shared data
 
     my_pages = (hi - lo) // 16
-    if args.mixed and rank % 2 == 1:
-        os.environ["TK_SEPARATE_COMBINE"] = "1"         # read when the handle is made
     cache = PagedKVCache(L, H, Hkv, Dh, max(my_pages, 1), 1, max(my_pages, 1), dtype="bf16",
-                         hot_window=args.hot_window, cold_pages=max(my_pages, 1) if args.hot_window else 0)
+                         hot_window=args.hot_window, cold_pages=max(my_pages, 1) if args.hot_window else 0,
+                         separate_combine=args.mixed and rank % 2 == 1)
     s = cache.seq_alloc()
     cache.adopt(s, np.arange(my_pages, dtype=np.int32), hi - lo)
     for l in range(L):

@@ -440,6 +440,32 @@ def test_bounded_device_wait_reports_timeout_and_context_survives():
     t.step([s], [1])                          # and the context is fine
 
 
+@pytest.mark.parametrize("impl", ["mma", "simt"])
+def test_pending_timeout_leaves_the_output_alone(impl):
+    """Fail closed.  With the handle's status word saying that a device wait gave up (set from the host
+    here; no wait is made to run out), an attention launch writes nothing: `out` keeps its previous
+    bytes, tk_kv_device_status reports TK_TIMEOUT and clears the word, and the next launch works."""
+    from titan_engine_b200 import KvError, _lib as L
+    t = Twin(1, 32, 8, 128, 64, 2, 40, dtype="bf16", impl=impl, max_step_tokens=1024, seed=93)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a, b], [600, 33])
+    q = to_torch16(normal16(t.g, (2, 32, 128), O.BF16), O.BF16, t.dev)
+    t.gpu.step_begin([a, b], None)
+    good = t.gpu.decode(0, q).clone()
+    sentinel = torch.full_like(good, 7.0)
+    out = sentinel.clone()
+    t.gpu.selftest_set_status(L.TK_TIMEOUT)
+    t.gpu.decode(0, q, out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, sentinel), "a launch with a pending time-out wrote to `out`"
+    with pytest.raises(KvError) as e:
+        t.gpu.device_status()
+    assert e.value.status == L.TK_TIMEOUT
+    t.gpu.device_status()                                  # cleared
+    t.gpu.decode(0, q, out)
+    assert torch.equal(out, good)
+
+
 def test_edge_cases_on_gpu():
     """Empty and maximal inputs: a sequence with no tokens attends to nothing (output 0, the
     reference's 0/(0+1e-8)); a sequence filling its whole page-table row; pool exhaustion that must

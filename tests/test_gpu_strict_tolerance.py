@@ -1,0 +1,143 @@
+"""Attention parity at exactly the stated tolerance: |got - want| <= 1e-2 + 2e-3 |want|, nothing added.
+
+The other GPU tests read 16-bit outputs and therefore add the half-ulp of the output type to the
+tolerance.  Here the kernels leave their result in FP32 (tk_kv_decode_ex / tk_kv_decode_multi_ex with
+out_dtype = TK_FP32), so what is compared with the CPU oracle is the kernels' own arithmetic
+(16-bit probabilities in the PV product, ex2.approx, the order of the FP32 sums) and the bound is
+the stated one with no slack.  The reference arithmetic the oracle restates:
+src/compute/cuda/attention.cu:85-156.
+
+Set TK_ERROR_REPORT=<file> to get one JSON line per case with the largest absolute error and the
+largest error relative to the tolerance.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import ATOL, DT, RTOL, Twin, normal16, rng, to_torch16
+from oracle import tk_oracle as O
+from test_gpu_fullsize import build, oracle_sample
+
+pytestmark = pytest.mark.gpu
+
+
+def strict_close(got, want, what):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    assert got.shape == want.shape and np.isfinite(got).all(), what
+    err = np.abs(got - want)
+    tol = ATOL + RTOL * np.abs(want)                     # 1e-2 + 2e-3 |want|: the stated bound, as stated
+    worst = float((err / tol).max())
+    path = os.environ.get("TK_ERROR_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"case": what, "max_abs_err": float(err.max()), "max_err_over_tol": worst,
+                                "n": int(err.size)}) + "\n")
+    assert worst <= 1.0, (f"{what}: {int((err > tol).sum())} of {err.size} outside 1e-2 + 2e-3|x| "
+                          f"(worst {worst:.2f} x tolerance, max abs err {err.max():.3e})")
+    assert np.abs(got).max() > 0
+    return float(err.max())
+
+
+def test_tiny_config_every_decode_step():
+    """1 sequence, 8 q / 2 kv heads, head_dim 64, 2 layers, fp16: 512-token prefill, then 64 decode steps,
+    every step's FP32 output against the oracle."""
+    t = Twin(2, 8, 2, 64, 40, 1, 40, dtype="fp16", impl="mma", max_step_tokens=512, seed=1)
+    s = t.seq_alloc()
+    t.step([s], [512], decode=False)
+    worst = 0.0
+    for step in range(64):
+        t.gpu.step_begin([s], [1]); assert t.mgr.reserve(s, 1) == O.OK
+        n = t.gpu.seq_len(s)
+        table = t.mgr.table()
+        for layer in range(2):
+            k16 = normal16(t.g, (1, 2, 64), O.FP16); v16 = normal16(t.g, (1, 2, 64), O.FP16)
+            q16 = normal16(t.g, (1, 8, 64), O.FP16)
+            t.pools[layer].append(table, [s], [n - 1], k16, v16)
+            t.gpu.append(layer, to_torch16(k16, O.FP16, t.dev), to_torch16(v16, O.FP16, t.dev))
+            got = t.gpu.decode_f32(layer, to_torch16(q16, O.FP16, t.dev)).cpu().numpy()
+            want = t.pools[layer].decode(table, [s], [n], q16)
+            worst = max(worst, strict_close(got, want, f"tiny config step {step} layer {layer}"))
+    t.gpu.device_status()
+    assert worst > 0
+
+
+@pytest.mark.parametrize("impl", ["mma", "simt"])
+def test_8b_shape_full_size_sampled_sequences(impl):
+    """64 sequences, context U[1024, 8192], bf16, one full layer: the sampled sequences in FP32."""
+    lens = rng(2).integers(1024, 8193, size=64)
+    c, _, seqs, gen = build(32, 8, 128, "bf16", lens, seed=2, decode_impl=impl)
+    q = torch.randn(64, 32, 128, device=c.device, generator=gen).to(torch.bfloat16)
+    c.step_begin(seqs, None)
+    got = c.decode_f32(0, q).cpu().numpy()
+    c.device_status()
+    sample = [0, 17, 40, int(np.argmax(lens)), int(np.argmin(lens))]
+    for b, want in oracle_sample(c, seqs, lens, sample, q, "bf16").items():
+        strict_close(got[b], want, f"8B shape {impl} sequence {b} (len {lens[b]})")
+
+
+def test_70b_shape_fp8_sampled_sequences():
+    """32 sequences at 32768 tokens (+ an open page of 5 tokens), 64 q / 8 kv heads, FP8-E4M3 pool."""
+    lens = np.full(32, 32768 + 5)
+    c, _, seqs, gen = build(64, 8, 128, "fp8", lens, seed=4)
+    q = torch.randn(32, 64, 128, device=c.device, generator=gen).to(torch.bfloat16)
+    c.step_begin(seqs, None)
+    got = c.decode_f32(0, q).cpu().numpy()
+    c.device_status()
+    for b, want in oracle_sample(c, seqs, lens, [0, 13, 31], q, "fp8").items():
+        strict_close(got[b], want, f"70B shape FP8 sequence {b}")
+
+
+def test_fp8_with_outliers_through_append():
+    """FP8 pool filled through the append path with 1 % outliers x20 (the distribution of the FP8
+    configuration): sealed pages + open page, ragged lengths."""
+    t = Twin(1, 64, 8, 128, 200, 3, 80, dtype="fp8", impl="mma", max_step_tokens=2048, seed=44)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [1200, 16, 37], decode=False, outlier_p=0.01)
+    q16 = normal16(t.g, (3, 64, 128), O.BF16)
+    t.gpu.step_begin(seqs, None)
+    got = t.gpu.decode_f32(0, to_torch16(q16, O.BF16, t.dev)).cpu().numpy()
+    want = t.pools[0].decode(t.mgr.table(), seqs, [1200, 16, 37], q16)
+    strict_close(got, want, "FP8 with outliers")
+
+
+@pytest.mark.parametrize("heads", [(16, 16), (32, 8)])
+def test_mla_shape(heads):
+    """K rows of 192, V rows of 128 (the MLA cache), bf16, split-KV over a 3000-token sequence."""
+    H, Hkv = heads
+    t = Twin(1, H, Hkv, 192, 260, 2, 200, dtype="bf16", impl="mma", max_step_tokens=4096, seed=98, Dv=128)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a, b], [3000, 333], decode=False)
+    q16 = normal16(t.g, (2, H, 192), O.BF16)
+    t.gpu.step_begin([a, b], None)
+    got = t.gpu.decode_f32(0, to_torch16(q16, O.BF16, t.dev)).cpu().numpy()
+    want = t.pools[0].decode(t.mgr.table(), [a, b], [3000, 333], q16)
+    strict_close(got, want, f"MLA shape {H}/{Hkv}")
+
+
+@pytest.mark.parametrize("shape", [(32, 8, 128, "bf16", 4), (32, 8, 128, "fp16", 19), (64, 8, 128, "bf16", 48)])
+def test_multi_token_step(shape):
+    """Every token of a step that appends several per sequence, causal among them, in FP32."""
+    H, Hkv, D, dtype, k = shape
+    dt = DT[dtype]
+    t = Twin(1, H, Hkv, D, 300, 3, 100, dtype=dtype, impl="mma", max_step_tokens=2048, seed=90)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [700, 13, 250], decode=False)
+    n_new = [k, k, max(1, k // 2)]
+    old = [t.gpu.seq_len(s) for s in seqs]
+    t.gpu.step_begin(seqs, n_new)
+    for s, n in zip(seqs, n_new):
+        assert t.mgr.reserve(s, n) == O.OK
+    table = t.mgr.table()
+    tok_seq = np.concatenate([np.full(n, s, np.int32) for s, n in zip(seqs, n_new)])
+    tok_pos = np.concatenate([np.arange(o, o + n, dtype=np.int32) for o, n in zip(old, n_new)])
+    k16 = normal16(t.g, (len(tok_seq), Hkv, D), dt); v16 = normal16(t.g, (len(tok_seq), Hkv, D), dt)
+    q16 = normal16(t.g, (len(tok_seq), H, D), dt)
+    t.gpu.append(0, to_torch16(k16, dt, t.dev), to_torch16(v16, dt, t.dev))
+    t.pools[0].append(table, tok_seq, tok_pos, k16, v16)
+    got = t.gpu.decode_multi_f32(0, to_torch16(q16, dt, t.dev)).cpu().numpy()
+    want = t.pools[0].decode(table, tok_seq, tok_pos + 1, q16)
+    strict_close(got, want, f"multi-token step {shape}")
+    t.gpu.device_status()

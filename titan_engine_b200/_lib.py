@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(HERE, "libtitan_kv.so")
 TK_OK, TK_INVALID_ARG, TK_OUT_OF_PAGES, TK_CUDA_ERROR, TK_TIMEOUT, TK_OUT_OF_SEQS, TK_UNSUPPORTED = range(7)
 TK_FP32, TK_FP16, TK_BF16, TK_FP8_E4M3 = 0, 1, 2, 3
 TK_DECODE_AUTO, TK_DECODE_SIMT, TK_DECODE_MMA = 0, 1, 2
+TK_MERGE_IN_KERNEL, TK_MERGE_SEPARATE = 0, 1
 TK_DEVICE_NONE = -2
 TK_PEER_HANDLE_BYTES = 64
 
@@ -21,7 +22,7 @@ class KvConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "num_layers", "num_heads", "num_kv_heads", "head_dim", "page_size", "dtype", "io_dtype",
         "num_pages", "max_seqs", "max_pages_per_seq", "max_step_tokens", "chunk_tokens",
-        "decode_impl", "device", "hot_window", "cold_pages", "v_head_dim")] + [("reserved", C.c_int32 * 3)]
+        "decode_impl", "device", "hot_window", "cold_pages", "v_head_dim", "merge_impl")] + [("reserved", C.c_int32 * 2)]
 
 
 class KvStats(C.Structure):
@@ -100,6 +101,7 @@ SIGNATURES = {
     "tk_peer_recv_combine": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "tk_peer_status": (C.c_int, [_P, C.c_void_p]),
     "tk_kv_decode_multi": (C.c_int, [_P, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "tk_kv_decode_multi_ex": (C.c_int, [_P, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "tk_kv_append_decode_multi": (C.c_int, [_P, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "tk_kv_decode_exchange": (C.c_int, [_P, C.c_int32, C.c_void_p, _P, C.c_void_p, C.c_void_p]),
     "tk_kv_profile_enable": (C.c_int, [_P, C.c_int32]),
@@ -109,6 +111,9 @@ SIGNATURES = {
                                         C.c_int32, C.c_int32, _P, _P, _P]),
     "tk_kv_device_status": (C.c_int, [_P, _P]),
     "tk_kv_selftest_bounded_wait": (C.c_int, [_P, C.c_int32, _P]),
+    "tk_kv_selftest_set_status": (C.c_int, [_P, C.c_int32, _P]),
+    "tk_kv_check_canaries": (C.c_int, [_P, _P]),
+    "tk_peer_check_canaries": (C.c_int, [_P, _P]),
     "tk_kv_launch_count": (C.c_int64, [_P]),
     "tk_sched_create": (C.c_int, [_P, C.POINTER(SchedConfig), C.POINTER(_P)]),
     "tk_sched_destroy": (C.c_int, [_P]),

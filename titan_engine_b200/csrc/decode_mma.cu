@@ -36,17 +36,11 @@ namespace tk {
 
 namespace {
 
-// Tunables (overridable at build time for experiments).  Measured on B200, 8B-shape bf16:
-// 2 stages x 3 CTAs/SM beats 3 x 2 (fewer idle slots while a CTA ramps up or merges) and 4 x 1.
-#ifndef TK_MMA_STAGES_BIG
-#define TK_MMA_STAGES_BIG 2       // tiles of 8 KB (16-bit, D=128)
-#endif
-#ifndef TK_MMA_STAGES_SMALL
-#define TK_MMA_STAGES_SMALL 3     // tiles of 4 KB (FP8, or D=64)
-#endif
-#ifndef TK_MMA_MIN_CTAS
-#define TK_MMA_MIN_CTAS 3
-#endif
+// Measured on B200, 8B-shape bf16: 2 stages x 3 CTAs/SM beats 3 x 2 (fewer idle slots while a CTA
+// ramps up or merges) and 4 x 1.
+constexpr int kStagesBig = 2;       // tiles of 8 KB (16-bit, D=128)
+constexpr int kStagesSmall = 3;     // tiles of 4 KB (FP8, or D=64)
+constexpr int kMinCtas = 3;
 // FP8 caches keep each sequence's last, partly filled page in the 16-bit io type ("open page").
 // Its 1..15 tokens are one work item of kind 1: plain SIMT arithmetic (reference form: score =
 // q.k/sqrtf(D), expf, FP32), one token per warp at a time, all MAXG query heads of the group.
@@ -141,7 +135,7 @@ struct Cfg {
     static constexpr int STAGE_BYTES = NBOX * kBoxBytes;
     static constexpr int BOX_W = 128 / ESIZE;               // box width in elements
     static constexpr bool MMA_BF16 = KIND == K_BF16;        // FP8 computes in fp16
-    static constexpr int STAGES = STAGE_BYTES >= 8192 ? TK_MMA_STAGES_BIG : TK_MMA_STAGES_SMALL;
+    static constexpr int STAGES = STAGE_BYTES >= 8192 ? kStagesBig : kStagesSmall;
     static constexpr int SMEM_BYTES = kWarps * STAGES * STAGE_BYTES + 1024 + 128;
 };
 
@@ -153,7 +147,7 @@ struct Cfg {
 // speculative decoder's verification of nq drafted tokens needs (the reference runs the layer once per
 // token there: src/inference/speculative.cpp:262-272).
 template <int KIND, int D, bool IO_BF16, bool GHI, bool MULTI>
-__global__ void __launch_bounds__(kWarps * 32, TK_MMA_MIN_CTAS)
+__global__ void __launch_bounds__(kWarps * 32, kMinCtas)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_cold, Geometry g, LayerPtrs lp, StepDev st,
                   const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q,
                   float* __restrict__ partials, int* __restrict__ status, MergeOut mo, FuseAppend fa) {
@@ -456,6 +450,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
             issue(i + kStages);
         }
     }
+    // a wait that gave up has set the status word: the merging CTA sees it and writes no output
     (void)alive;
 
     // ---- merge the 4 warps through shared memory (stage memory is idle now) ----------
@@ -628,7 +623,7 @@ cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMa
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(out, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
                         layer_pool, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, TK_TMAP_L2_PROMOTION,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }

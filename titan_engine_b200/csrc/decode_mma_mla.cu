@@ -313,7 +313,7 @@ cudaError_t make_mla_tensor_maps(const Geometry& g, void* layer_pool, CUtensorMa
         cuuint64_t strides[3] = {128, 384, (cuuint64_t)kTileBytes};
         cuuint32_t box[4] = {64, 3, (cuuint32_t)kPage, 1};
         CUresult r = encode(k_map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, layer_pool, dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, TK_TMAP_L2_PROMOTION,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
@@ -323,7 +323,7 @@ cudaError_t make_mla_tensor_maps(const Geometry& g, void* layer_pool, CUtensorMa
         cuuint32_t box[4] = {64, 1, (cuuint32_t)kPage, 1};
         CUresult r = encode(v_map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, (uint8_t*)layer_pool + kKBytes, dims, strides,
                             box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                            TK_TMAP_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
     }
     return cudaSuccess;

@@ -237,7 +237,8 @@ cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const Ste
 // grid = (H, n_seqs); block = 128 threads striding over D
 __global__ void combine_step_kernel(Geometry g, StepDev st, const float* __restrict__ partials,
                                     void* __restrict__ out, int out_dtype,
-                                    float* __restrict__ partial_out) {
+                                    float* __restrict__ partial_out, const int* __restrict__ status) {
+    if (status && __ldcg(status) != 0) return;       // a device wait gave up on this handle: write nothing
     const int h = blockIdx.x, b = blockIdx.y, D = g.Dv;
     const int r0 = st.chunk_base[b], r1 = st.chunk_base[b + 1];
     float M = -1e30f;
@@ -264,10 +265,10 @@ __global__ void combine_step_kernel(Geometry g, StepDev st, const float* __restr
 }
 
 cudaError_t launch_combine_step(const Geometry& g, const StepDev& st, const float* partials,
-                                void* out, int out_dtype, float* partial_out, cudaStream_t s) {
+                                void* out, int out_dtype, float* partial_out, cudaStream_t s, const int* status) {
     if (st.n_seqs <= 0) return cudaSuccess;
     dim3 grid(g.H, st.n_seqs);
-    combine_step_kernel<<<grid, 128, 0, s>>>(g, st, partials, out, out_dtype, partial_out);
+    combine_step_kernel<<<grid, 128, 0, s>>>(g, st, partials, out, out_dtype, partial_out, status);
     return cudaGetLastError();
 }
 

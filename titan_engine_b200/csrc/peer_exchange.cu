@@ -31,6 +31,8 @@ namespace {
 
 using tk::PeerCtx;
 constexpr int kMaxWorld = tk::kPeerMaxWorld;
+constexpr size_t kCanaryBytes = 4096;      // guard bytes behind the mailbox (tk_peer_check_canaries)
+constexpr int kCanaryByte = 0xA5;
 
 // mode bit 0: send this rank's rows to every peer and publish the flags;
 // mode bit 1: wait for the peers' rows and combine.  Both: one launch does the whole exchange.
@@ -177,8 +179,9 @@ int tk_peer_create(int32_t rank, int32_t world, int32_t max_rows, int32_t row_fl
     cudaDeviceProp prop;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete p; return TK_CUDA_ERROR; }
     p->num_sms = prop.multiProcessorCount;
-    cudaError_t e = cudaMalloc((void**)&p->local, p->total);
+    cudaError_t e = cudaMalloc((void**)&p->local, p->total + kCanaryBytes);
     if (e == cudaSuccess) e = cudaMemset(p->local, 0, p->total);
+    if (e == cudaSuccess) e = cudaMemset(p->local + p->total, kCanaryByte, kCanaryBytes);
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_ticket, 4 * sizeof(unsigned));
     if (e == cudaSuccess) e = cudaMemset(p->d_ticket, 0, 4 * sizeof(unsigned));
     if (e == cudaSuccess) e = cudaMalloc((void**)&p->d_ctx, sizeof(tk::PeerCtx));
@@ -329,6 +332,18 @@ int tk_peer_status(tk_peer* p, void* stream) {
         cudaMemsetAsync(p->d_status, 0, sizeof(int), (cudaStream_t)stream);
         return pfail(p, st, "a peer's rows did not arrive within the wait limit");
     }
+    return TK_OK;
+}
+
+int tk_peer_check_canaries(tk_peer* p, void* stream) {
+    if (!p) return TK_INVALID_ARG;
+    cudaError_t e = cudaSetDevice(p->device);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    uint8_t buf[kCanaryBytes];
+    if (e == cudaSuccess) e = cudaMemcpy(buf, p->local + p->total, kCanaryBytes, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return pfail(p, TK_CUDA_ERROR, "canary read", e);
+    for (size_t i = 0; i < kCanaryBytes; i++)
+        if (buf[i] != (uint8_t)kCanaryByte) return pfail(p, TK_CUDA_ERROR, "guard bytes behind the mailbox were overwritten");
     return TK_OK;
 }
 

@@ -21,6 +21,11 @@ namespace {
 constexpr int kRing = 4;                 // pinned staging buffers in rotation
 constexpr int kMaxDelta = 1 << 16;       // page-table patches per upload; more -> full table copy
 constexpr int TK_DEVICE_NONE = -2;       // bookkeeping only: no device memory, compute calls fail
+// Guard bytes behind every buffer that kernels write at host-computed rows (the pool arena, the split-KV
+// workspace, the step metadata, the page table): filled with kCanaryByte at creation and compared by
+// tk_kv_check_canaries, which stands in for a memory checker on stray writes past a buffer's end.
+constexpr size_t kCanaryBytes = 4096;
+constexpr int kCanaryByte = 0xA5;
 
 std::string g_create_error;
 
@@ -67,6 +72,7 @@ const char* validate(const tk_kv_config& c) {
     if (c.max_step_tokens <= 0) return "max_step_tokens must be positive";
     if (c.chunk_tokens < 0 || c.chunk_tokens % c.page_size != 0) return "chunk_tokens must be a multiple of page_size";
     if (c.decode_impl < TK_DECODE_AUTO || c.decode_impl > TK_DECODE_MMA) return "bad decode_impl";
+    if (c.merge_impl != TK_MERGE_IN_KERNEL && c.merge_impl != TK_MERGE_SEPARATE) return "bad merge_impl";
     if (c.hot_window < 0 || c.cold_pages < 0) return "hot_window and cold_pages must not be negative";
     if (c.hot_window > 0) {
         if (c.hot_window < c.page_size) return "hot_window must cover at least one page";
@@ -85,10 +91,7 @@ struct tk_kv {
     bool host_only = false;
     int device = 0, num_sms = 148;
     bool use_mma = false;
-    // debugging knobs, read from the environment once when the handle is made
-    int env_chunk = 0, env_target = 0;       // TK_CHUNK_TOKENS, TK_TARGET_ITEMS
-    bool separate_combine = false;           // TK_SEPARATE_COMBINE: combine kernel instead of the in-kernel merge
-    bool separate_append = false;            // TK_SEPARATE_APPEND: append launch instead of the fused row store
+    bool separate_combine = false;           // cfg.merge_impl == TK_MERGE_SEPARATE: combine launch instead of the in-kernel merge
 
     uint8_t* arena = nullptr;
     bool owns_arena = false;
@@ -154,6 +157,9 @@ struct tk_kv {
     tk_kv_stats stats{};
     int64_t launches = 0;
     std::string err;
+
+    struct Canary { const char* name; uint8_t* at; };
+    std::vector<Canary> canaries;
 
     tk::LayerPtrs layer(int l) const {
         tk::LayerPtrs p{};
@@ -245,10 +251,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->geo = tk::Geometry{c.num_heads, c.num_kv_heads, c.head_dim, c.page_size, c.dtype, c.io_dtype,
                           c.num_pages, c.max_seqs, c.max_pages_per_seq, c.v_head_dim};
     h->mgr = new tk::PageManager(c.num_pages, c.max_seqs, c.max_pages_per_seq, c.page_size);
-    if (const char* e = getenv("TK_CHUNK_TOKENS")) h->env_chunk = atoi(e);
-    if (const char* e = getenv("TK_TARGET_ITEMS")) h->env_target = atoi(e);
-    h->separate_combine = getenv("TK_SEPARATE_COMBINE") != nullptr;
-    h->separate_append = getenv("TK_SEPARATE_APPEND") != nullptr;
+    h->separate_combine = c.merge_impl == TK_MERGE_SEPARATE;
     h->lay = arena_layout(c);
     h->host_only = c.device == TK_DEVICE_NONE;
     h->page_bytes = (size_t)c.num_kv_heads * c.page_size * (c.head_dim + c.v_head_dim) * (c.dtype == TK_FP8_E4M3 ? 1 : 2);
@@ -293,21 +296,28 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
             return fail(nullptr, TK_INVALID_ARG, "external arena must be 1024-byte aligned and >= %zu bytes", h->lay.total);
         }
         h->arena = (uint8_t*)arena;
+        // a caller that hands over kCanaryBytes more than the arena needs gets guard bytes there too
+        if (arena_bytes >= h->lay.total + kCanaryBytes) h->canaries.push_back({"pool arena", h->arena + h->lay.total});
     } else {
-        CREATE_CUDA(cudaMalloc((void**)&h->arena, h->lay.total));
+        CREATE_CUDA(cudaMalloc((void**)&h->arena, h->lay.total + kCanaryBytes));
         h->owns_arena = true;
+        h->canaries.push_back({"pool arena", h->arena + h->lay.total});
     }
     CREATE_CUDA(cudaMemset(h->arena, 0, h->lay.total));     // like KVCache::initialize, kv_cache.cpp:49-50
     const size_t table_bytes = (size_t)c.max_seqs * c.max_pages_per_seq * sizeof(int32_t);
-    CREATE_CUDA(cudaMalloc((void**)&h->d_table, table_bytes));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_table, table_bytes + kCanaryBytes));
     CREATE_CUDA(cudaMemset(h->d_table, 0xFF, table_bytes));
-    CREATE_CUDA(cudaMalloc((void**)&h->d_partials,
-                           (size_t)h->max_partial_rows * c.num_heads * (c.v_head_dim + 2) * sizeof(float)));
+    h->canaries.push_back({"page table", (uint8_t*)h->d_table + table_bytes});
+    const size_t partial_bytes = (size_t)h->max_partial_rows * c.num_heads * (c.v_head_dim + 2) * sizeof(float);
+    CREATE_CUDA(cudaMalloc((void**)&h->d_partials, partial_bytes + kCanaryBytes));
+    h->canaries.push_back({"split-KV workspace", (uint8_t*)h->d_partials + partial_bytes});
     CREATE_CUDA(cudaMalloc((void**)&h->d_status, 256));
     CREATE_CUDA(cudaMemset(h->d_status, 0, 256));
     CREATE_CUDA(cudaMalloc((void**)&h->d_counters, sizeof(int) * 8 * (size_t)c.max_seqs * c.num_kv_heads));
     CREATE_CUDA(cudaMemset(h->d_counters, 0, sizeof(int) * 8 * (size_t)c.max_seqs * c.num_kv_heads));
-    CREATE_CUDA(cudaMalloc((void**)&h->d_step, h->step_bytes));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_step, h->step_bytes + kCanaryBytes));
+    h->canaries.push_back({"step metadata", h->d_step + h->step_bytes});
+    for (const auto& cn : h->canaries) CREATE_CUDA(cudaMemset(cn.at, kCanaryByte, kCanaryBytes));
     for (int i = 0; i < kRing; i++) {
         CREATE_CUDA(cudaHostAlloc((void**)&h->h_step[i], h->step_bytes, cudaHostAllocDefault));
         CREATE_CUDA(cudaEventCreateWithFlags(&h->ev[i], cudaEventDisableTiming));
@@ -605,9 +615,8 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
         return fail(h, TK_UNSUPPORTED, "step_begin: an attended-length cap needs 16-bit storage");
     std::lock_guard<std::mutex> lock(h->mgr_mu);
     h->have_step = false;
-    int chunk = h->cfg.chunk_tokens;
-    if (chunk == 0) chunk = h->env_chunk;
-    int target = h->env_target > 0 ? h->env_target : 8 * h->num_sms;   // ~4 waves of 2 CTAs/SM; larger chunks measured faster
+    const int chunk = h->cfg.chunk_tokens;
+    const int target = 8 * h->num_sms;       // work items the planner aims for when it picks the chunk itself
     // the tensor-core kernel keeps one page id per lane per warp: chunk <= 16*4*32 tokens
     int st = h->mgr->plan_step(n_seqs, seq_ids, n_new, h->cfg.num_kv_heads, h->cfg.dtype == TK_FP8_E4M3,
                                chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan, len_cap);
@@ -775,7 +784,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     // attends to nothing has no CTA, so such steps keep the separate combine kernel
     const bool fused_merge = !h->plan.has_empty_seq && !h->separate_combine;
     if (peer_ctx && !fused_merge) return fail(h, TK_INVALID_ARG, "decode: the in-kernel exchange needs the in-kernel merge");
-    const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype, peer_ctx};
+    const tk::MergeOut mo{fused_merge ? h->d_counters : nullptr, out, partial_out, out_dtype, peer_ctx, h->d_status};
     const tk::FuseAppend fa{fuse_k, fuse_v, rope ? h->d_rope_tab : nullptr};
     const bool timed = h->profiling && h->prof_used + 2 <= h->prof_ev.size();
     if (timed) cudaEventRecord(h->prof_ev[h->prof_used], s);
@@ -805,7 +814,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
         if (pst != TK_OK) return pst;
     }
     if (!fused_merge) {
-        e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, out_dtype, partial_out, s);
+        e = tk::launch_combine_step(h->geo, h->dev, h->d_partials, out, out_dtype, partial_out, s, h->d_status);
         h->launches++;
         if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "combine launch: %s", cudaGetErrorString(e));
     }
@@ -826,8 +835,7 @@ int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, c
     // goes into the sequence's 16-bit open page, unless this step completes (seals) a page.
     const bool fusable = h->use_mma && h->plan.one_token_steps && h->dev.chunk_tokens <= 2048 &&
                          h->dev.n_tokens > 0 && h->dev.n_seqs > 0 && !h->plan.has_empty_seq &&
-                         (h->cfg.dtype != TK_FP8_E4M3 || h->plan.seals.empty()) &&
-                         !h->separate_append;
+                         (h->cfg.dtype != TK_FP8_E4M3 || h->plan.seals.empty());
     if (!fusable) {
         int st = tk_kv_append(h, layer, k, v, nullptr, stream);
         if (st != TK_OK) return st;
@@ -846,7 +854,7 @@ int tk_kv_rope_append_decode(tk_kv* h, int32_t layer, const void* k, const void*
     if (!q || !out || (h->dev.n_tokens > 0 && (!k || !v))) return fail(h, TK_INVALID_ARG, "rope_append_decode: null argument");
     const bool fusable = h->use_mma && h->cfg.dtype != TK_FP8_E4M3 && h->plan.one_token_steps &&
                          h->dev.chunk_tokens <= 2048 && h->dev.n_tokens > 0 && h->dev.n_seqs > 0 &&
-                         !h->plan.has_empty_seq && !h->separate_append;
+                         !h->plan.has_empty_seq;
     if (fusable) {
         const float rope[2] = {theta, scaling};
         // cos/sin of each sequence's newest position: computed once per step, shared by all layers
@@ -874,8 +882,10 @@ int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial,
 
 // Attention for every token the step appended (several per sequence), causal among themselves, in one
 // pass over the pages: what the verification of drafted tokens needs.
-int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* stream) {
+static int decode_multi_impl(tk_kv* h, int32_t layer, const void* q, void* out, int out_dtype, void* stream) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (out_dtype != TK_FP32 && out_dtype != h->cfg.io_dtype)
+        return fail(h, TK_INVALID_ARG, "decode_multi: out dtype must be FP32 or the handle's io dtype");
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode_multi: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode_multi: no step in progress (call tk_kv_step_begin)");
     if (h->dev.n_seqs == 0) return TK_OK;
@@ -906,7 +916,7 @@ int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* 
         }
         partials = h->d_multi_partials;
     }
-    const tk::MergeOut mo{h->d_counters, out, nullptr, h->cfg.io_dtype, nullptr};
+    const tk::MergeOut mo{h->d_counters, out, nullptr, out_dtype, nullptr, h->d_status};
     cudaError_t e = h->mla_mma
         ? tk::launch_decode_mma_mla_multi(h->geo, h->layer(layer), &h->maps[layer], &h->maps_v[layer], h->dev, h->d_table, q,
                                           partials, h->d_status, (cudaStream_t)stream, mo)
@@ -915,6 +925,13 @@ int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* 
     h->launches++;
     if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode_multi launch: %s", cudaGetErrorString(e));
     return TK_OK;
+}
+
+int tk_kv_decode_multi(tk_kv* h, int32_t layer, const void* q, void* out, void* stream) {
+    return decode_multi_impl(h, layer, q, out, h ? h->cfg.io_dtype : 0, stream);
+}
+int tk_kv_decode_multi_ex(tk_kv* h, int32_t layer, const void* q, void* out, int32_t out_dtype, void* stream) {
+    return decode_multi_impl(h, layer, q, out, out_dtype, stream);
 }
 
 int tk_kv_append_decode_multi(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
@@ -1094,6 +1111,29 @@ int tk_kv_selftest_bounded_wait(tk_kv* h, int32_t limit_ms, void* stream) {
                                                      (cudaStream_t)stream);
     h->launches++;
     return e == cudaSuccess ? TK_OK : fail(h, TK_CUDA_ERROR, "selftest launch: %s", cudaGetErrorString(e));
+}
+
+int tk_kv_selftest_set_status(tk_kv* h, int32_t value, void* stream) {
+    if (!h || h->host_only) return TK_INVALID_ARG;
+    if (value != TK_OK && value != TK_TIMEOUT) return fail(h, TK_INVALID_ARG, "selftest_set_status: value must be TK_OK or TK_TIMEOUT");
+    TK_CUDA(h, cudaMemcpyAsync(h->d_status, &value, sizeof(int), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    TK_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream));      // `value` lives on this call's stack
+    return TK_OK;
+}
+
+int tk_kv_check_canaries(tk_kv* h, void* stream) {
+    if (!h || h->host_only) return TK_INVALID_ARG;
+    TK_CUDA(h, cudaSetDevice(h->device));
+    TK_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream));
+    std::vector<uint8_t> buf(kCanaryBytes);
+    for (const auto& cn : h->canaries) {
+        TK_CUDA(h, cudaMemcpy(buf.data(), cn.at, kCanaryBytes, cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < kCanaryBytes; i++)
+            if (buf[i] != (uint8_t)kCanaryByte)
+                return fail(h, TK_CUDA_ERROR, "guard bytes behind the %s were overwritten (first at +%zu): a kernel wrote past its buffer",
+                            cn.name, i);
+    }
+    return TK_OK;
 }
 
 int64_t tk_kv_launch_count(const tk_kv* h) { return h ? h->launches : 0; }

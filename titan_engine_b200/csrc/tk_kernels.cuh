@@ -77,6 +77,10 @@ struct MergeOut {
     // into every rank's mailbox, publishes and awaits the per-(sequence, kv head) flags and writes the
     // combine over all ranks to `out` (tk_peer.cuh); partial_out is not used then.
     const struct PeerCtx* peer;
+    // != null: the handle's status word.  A merging CTA that finds it set (a bounded wait gave up
+    // somewhere on this handle and the host has not read it yet) writes nothing: no output is
+    // better than one computed from a tile that never arrived.
+    const int* status;
 };
 
 // Decode steps (at most one new token per sequence): the decode kernel itself writes the
@@ -161,8 +165,10 @@ cudaError_t launch_bounded_wait_selftest(int* status, unsigned long long limit_n
 // LSE merge over each sequence's partial rows.
 //   out != null     : normalised [n_seqs][H][D] in out_dtype
 //   partial_out!=null: merged but unnormalised [n_seqs][H][D+2]
+//   status != null  : the handle's status word; nothing is written while it is set
 cudaError_t launch_combine_step(const Geometry& g, const StepDev& st, const float* partials,
-                                void* out, int out_dtype, float* partial_out, cudaStream_t s);
+                                void* out, int out_dtype, float* partial_out, cudaStream_t s,
+                                const int* status = nullptr);
 // LSE merge of n_parts stacked partial sets [n_parts][n_rows][D+2] -> out [n_rows][D].
 cudaError_t launch_combine_parts(const float* parts, int n_parts, int n_rows, int D, void* out,
                                  int out_dtype, cudaStream_t s);

@@ -36,6 +36,7 @@ struct MergeMap {
 __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo, int b, int kvh, int G, int r0, int n,
                                            const float* partials, const MergeMap& mm) {
     __threadfence();                                   // see the other CTAs' rows
+    if (mo.status && __ldcg(mo.status) != 0) return;   // fail closed: a wait timed out, leave `out` alone
     const int D = g.Dv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const int epl = D >> 5;                            // dims per lane: 2 (D=64) or 4 (D=128)

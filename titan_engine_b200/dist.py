@@ -123,9 +123,14 @@ class PeerExchange:
     handles travel over torch.distributed (any backend).  exchange_combine(partial) is one kernel:
     peer stores of this rank's rows, flags, bounded wait for the peers' rows, log-sum-exp combine."""
 
+    live = None        # weak set of the open exchanges of this process (see check_canaries)
+
     def __init__(self, max_rows: int, row_floats: int, group: Optional[dist.ProcessGroup] = None,
                  rank: Optional[int] = None, world: Optional[int] = None, connect: bool = True):
         import ctypes as C
+        import weakref
+        if PeerExchange.live is None:
+            PeerExchange.live = weakref.WeakSet()
         from . import _lib as L
         self._L, self._C = L, C
         self._lib = L.lib()
@@ -139,6 +144,7 @@ class PeerExchange:
         st = self._lib.tk_peer_create(rank, world, max_rows, row_floats, torch.cuda.current_device(), C.byref(self._h))
         if st != L.TK_OK:
             raise RuntimeError(f"tk_peer_create failed with status {st}")
+        PeerExchange.live.add(self)
         if connect and world > 1:
             self.connect()
 
@@ -199,6 +205,11 @@ class PeerExchange:
         self._check(self._lib.tk_peer_recv_combine(self._h, partial.data_ptr(), n_rows, dv, out.data_ptr(),
                                                    self._code(out_dtype), torch.cuda.current_stream().cuda_stream))
         return out
+
+    def check_canaries(self) -> None:
+        """Raises when a kernel wrote past the end of this rank's mailbox."""
+        if self._h:
+            self._check(self._lib.tk_peer_check_canaries(self._h, torch.cuda.current_stream().cuda_stream))
 
     def status(self) -> None:
         """Raises if a device-side wait of this exchange gave up (a peer never published its rows)."""

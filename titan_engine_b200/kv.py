@@ -9,6 +9,7 @@ libtitan_kv.so; nothing here computes.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from typing import Optional, Sequence
 
 import numpy as np
@@ -38,12 +39,14 @@ def _ptr(a: Optional[np.ndarray]):
 class PagedKVCache:
     """Paged K/V pool + page manager + decode attention for one GPU."""
 
+    live = weakref.WeakSet()        # every open device-backed cache of this process (see check_canaries)
+
     def __init__(self, num_layers: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  num_pages: int, max_seqs: int, max_pages_per_seq: int, dtype: str = "bf16",
                  io_dtype: Optional[str] = None, page_size: int = 16,
                  max_step_tokens: Optional[int] = None, chunk_tokens: int = 0,
                  decode_impl: str = "auto", device: Optional[int] = None, host_only: bool = False,
-                 hot_window: int = 0, cold_pages: int = 0, v_head_dim: int = 0):
+                 hot_window: int = 0, cold_pages: int = 0, v_head_dim: int = 0, separate_combine: bool = False):
         self._lib = L.lib()
         cfg = L.KvConfig()
         self._lib.tk_kv_config_default(C.byref(cfg))
@@ -54,6 +57,7 @@ class PagedKVCache:
         cfg.max_step_tokens = max_step_tokens or max_seqs
         cfg.chunk_tokens, cfg.decode_impl = chunk_tokens, _IMPLS[decode_impl]
         cfg.hot_window, cfg.cold_pages, cfg.v_head_dim = hot_window, cold_pages, v_head_dim
+        cfg.merge_impl = L.TK_MERGE_SEPARATE if separate_combine else L.TK_MERGE_IN_KERNEL
         self._h = C.c_void_p()
         self.host_only = host_only
         self._arena = None
@@ -69,11 +73,12 @@ class PagedKVCache:
             nbytes = self._lib.tk_kv_arena_bytes(C.byref(cfg))
             if nbytes == 0:
                 raise KvError(L.TK_INVALID_ARG, "invalid configuration")
-            self._arena = torch.empty(nbytes + 1024, dtype=torch.uint8, device=self.device)
+            guard = 4096                                     # room for the library's guard bytes behind the arena
+            self._arena = torch.empty(nbytes + 1024 + guard, dtype=torch.uint8, device=self.device)
             self._arena_off = (-self._arena.data_ptr()) % 1024
             torch.cuda.synchronize(self.device)
             st = self._lib.tk_kv_create_external(C.byref(cfg), self._arena.data_ptr() + self._arena_off,
-                                                 nbytes, C.byref(self._h))
+                                                 nbytes + guard, C.byref(self._h))
         if st != L.TK_OK:
             raise KvError(st, self._lib.tk_kv_last_error(None).decode())
         self.cfg = L.KvConfig()
@@ -81,6 +86,8 @@ class PagedKVCache:
         self.io_torch_dtype = _TORCH16[self.cfg.io_dtype]
         self._n_seqs = 0
         self._n_tokens = 0
+        if not host_only:
+            PagedKVCache.live.add(self)
 
     # ---- plumbing ------------------------------------------------------------------
     def _check(self, st: int) -> None:
@@ -214,6 +221,21 @@ class PagedKVCache:
         self._check(self._lib.tk_kv_decode(self._h, layer, q.data_ptr(), out.data_ptr(), self._stream()))
         return out
 
+    def decode_f32(self, layer: int, q: torch.Tensor) -> torch.Tensor:
+        """decode() with the result left in FP32 (tk_kv_decode_ex): q [n_seqs, H, D] io dtype -> [n_seqs, H, Dv] f32."""
+        self._check_io(q, self._n_seqs, self.cfg.num_heads, "q")
+        out = torch.empty(q.shape[0], self.cfg.num_heads, self.cfg.v_head_dim, dtype=torch.float32, device=q.device)
+        self._check(self._lib.tk_kv_decode_ex(self._h, layer, q.data_ptr(), self.cfg.io_dtype, out.data_ptr(),
+                                              L.TK_FP32, self._stream()))
+        return out
+
+    def decode_multi_f32(self, layer: int, q: torch.Tensor) -> torch.Tensor:
+        """decode_multi() with the result left in FP32 (tk_kv_decode_multi_ex)."""
+        self._check_io(q, self._n_tokens, self.cfg.num_heads, "q")
+        out = torch.empty(self._n_tokens, self.cfg.num_heads, self.cfg.v_head_dim, dtype=torch.float32, device=self.device)
+        self._check(self._lib.tk_kv_decode_multi_ex(self._h, layer, q.data_ptr(), out.data_ptr(), L.TK_FP32, self._stream()))
+        return out
+
     def append_decode(self, layer: int, k: torch.Tensor, v: torch.Tensor, q: torch.Tensor,
                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """append + decode of one layer; a single fused kernel on 16-bit decode steps."""
@@ -318,6 +340,15 @@ class PagedKVCache:
 
     def device_status(self) -> None:
         self._check(self._lib.tk_kv_device_status(self._h, self._stream()))
+
+    def check_canaries(self) -> None:
+        """Raises when a kernel wrote past the end of the arena, the page table, the split-KV workspace
+        or the step metadata (guard bytes behind each are compared)."""
+        if getattr(self, "_h", None) and self._h.value and not self.host_only:
+            self._check(self._lib.tk_kv_check_canaries(self._h, self._stream()))
+
+    def selftest_set_status(self, value: int) -> None:
+        self._check(self._lib.tk_kv_selftest_set_status(self._h, value, self._stream()))
 
     # ---- views of the pool (parity dumps, synthetic fills) -------------------------------
     def _view(self, ptr: int, nbytes: int) -> torch.Tensor:
