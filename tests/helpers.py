@@ -120,8 +120,12 @@ class Twin:
         self.gpu.adopt(s, pages, seq_len)
         assert self.mgr.adopt(s, pages, seq_len) == O.OK
 
-    def step(self, seq_ids, n_new, check_pool=False, decode=True, outlier_p=0.0, host_api=False, fused=False, begun=False):
-        """begun=True: the step was already begun on the GPU cache (e.g. by the scheduler)."""
+    def step(self, seq_ids, n_new, check_pool=False, decode=True, outlier_p=0.0, host_api=False, fused=False, begun=False,
+             every_token=False, f32_out=False):
+        """begun=True: the step was already begun on the GPU cache (e.g. by the scheduler).
+        every_token=True: attention for EVERY token the step appends (tk_kv_decode_multi), each against the
+        oracle's single-token decode with the length cut at that token - what the reference's per-token
+        prefill loop computes."""
         torch = self.torch
         n_new = [0] * len(seq_ids) if n_new is None else list(n_new)
         if begun:
@@ -146,8 +150,20 @@ class Twin:
         for layer in range(self.L):
             k16 = normal16(self.g, (nt, self.Hkv, self.D), self.carrier, outlier_p)
             v16 = normal16(self.g, (nt, self.Hkv, self.Dv), self.carrier, outlier_p)
-            q16 = normal16(self.g, (len(seq_ids), self.H, self.D), self.carrier)
+            q16 = normal16(self.g, (nt if every_token else len(seq_ids), self.H, self.D), self.carrier)
             want_slots = self.pools[layer].append(table, tok_seq, tok_pos, k16, v16)
+            if every_token:
+                self.gpu.append(layer, to_torch16(k16, self.carrier, self.dev), to_torch16(v16, self.carrier, self.dev))
+                qt = to_torch16(q16, self.carrier, self.dev)
+                got = (self.gpu.decode_multi_f32(layer, qt) if f32_out else self.gpu.decode_multi(layer, qt).to(torch.float32)).cpu().numpy()
+                if check_pool:
+                    self.check_pool(layer)
+                want = self.pools[layer].decode(table, tok_seq, tok_pos + 1, q16)
+                assert_close(got, want, f"layer {layer} attention of every appended token ({n_new[:6]}...)",
+                             out_mantissa_bits=0 if f32_out else (7 if self.carrier == O.BF16 else 10))
+                self.max_err = max(self.max_err, float(np.abs(got - want).max()))
+                outs.append(got)
+                continue
             if host_api:
                 kt, vt, qt = (to_torch16(x, self.carrier).pin_memory() for x in (k16, v16, q16))
                 out_h = torch.empty(len(seq_ids), self.H, self.Dv, dtype=qt.dtype).pin_memory()

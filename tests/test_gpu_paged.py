@@ -396,14 +396,16 @@ def test_rope_append_decode_mla_shape(heads, impl):
 def test_scheduler_drives_churn_on_gpu():
     """The continuous-batching scheduler as the caller: requests arrive, prefill in chunks, decode,
     finish and get preempted on a small pool; every step's page state is bit-exact against the
-    oracle manager and every attention output within tolerance of the oracle."""
+    oracle manager and the attention output of EVERY token of every row - each prompt token of a
+    prefill chunk included, as the reference's per-token prefill loop computes them
+    (src/inference/engine.cpp:182-193) - within tolerance of the oracle."""
     from titan_engine_b200.scheduler import BatchScheduler
     t = Twin(1, 32, 8, 128, 48, 6, 48, dtype="fp16", impl="mma", max_step_tokens=256 + 6, seed=80)
     s = BatchScheduler(t.gpu, max_batch_size=6, max_prefill_tokens=256)
     g = rng(81)
     for _ in range(10):
         s.submit(int(g.integers(30, 300)), int(g.integers(5, 60)))
-    steps = 0
+    steps = multi_steps = 0
     for _ in range(3000):
         rows = s.next()
         ev = s.last_events()
@@ -416,11 +418,15 @@ def test_scheduler_drives_churn_on_gpu():
         if not rows and s.stats()["queued_requests"] == 0:
             break
         if rows:
-            t.step([r.seq for r in rows], [r.n_new for r in rows], begun=True, fused=(steps % 2 == 0))
+            if max(r.n_new for r in rows) > 1:
+                t.step([r.seq for r in rows], [r.n_new for r in rows], begun=True, every_token=True)
+                multi_steps += 1
+            else:
+                t.step([r.seq for r in rows], [r.n_new for r in rows], begun=True, fused=(steps % 2 == 0))
             steps += 1
         s.commit([bool(g.random() < 0.02) for _ in rows])
     st = s.stats()
-    assert st["completed_requests"] == 10 and st["active_requests"] == 0 and steps > 50
+    assert st["completed_requests"] == 10 and st["active_requests"] == 0 and steps > 50 and multi_steps >= 5
     assert t.gpu.num_free_pages == 48 and t.gpu.digest() == t.mgr.digest()
 
 
@@ -647,6 +653,45 @@ def test_decode_multi_tokens_causal(shape):
     t.step(seqs, [1, 1, 1], check_pool=True)
 
 
+@pytest.mark.parametrize("shape", [
+    # H, Hkv, D, dtype
+    (32, 8, 128, "bf16"),     # 8B head shape: 16 tokens per 64-row tile
+    (64, 8, 128, "fp16"),     # 70B head shape: 8 tokens per tile
+    (8, 2, 64, "fp16"),       # tiny config
+    (16, 16, 128, "bf16"),    # MHA: 64 tokens per tile
+    (16, 1, 64, "bf16"),      # 16 heads per kv head: 4 tokens per tile
+])
+def test_prefill_chunk_attention_every_token(shape):
+    """Prefill chunks through tk_kv_append + tk_kv_decode_multi: a fresh prompt (the chunk is the whole
+    context), a chunk on top of a long context (tiles split over the context and merged), short and
+    single-token rows in the same step (they stay with the decode kernel), ragged page boundaries."""
+    H, Hkv, D, dtype = shape
+    t = Twin(2, H, Hkv, D, 700, 6, 400, dtype=dtype, impl="mma", max_step_tokens=4096, seed=120)
+    a, b, c, d = (t.seq_alloc() for _ in range(4))
+    t.step([a, b], [3000, 45], decode=False)                       # a long context and a short one
+    t.step([a, b, c, d], [333, 1, 777, 2], every_token=True, check_pool=True)
+    items, ct, n_decode = t.gpu.step_prefill_plan()
+    assert len(items) > 0 and n_decode > 0                         # both kernels had work
+    t.step([a, b, c, d], [150, 150, 1, 129], every_token=True)
+    t.step([d, c], [1021, 300], every_token=True, f32_out=True)   # FP32 results: the stated tolerance with no slack
+    t.step([a, b, c, d], [1, 1, 1, 1], check_pool=True)           # plain decode goes on
+    t.gpu.device_status()
+
+
+def test_prefill_chunk_long_context_split_and_merge():
+    """A 40-token chunk on a 20000-token context at the 8B head shape: few tiles, so every tile is cut
+    into split-KV chunks whose partial rows the last CTA merges; and a 2500-token fresh prompt beside it."""
+    t = Twin(1, 32, 8, 128, 1600, 2, 1400, dtype="bf16", impl="mma", max_step_tokens=4096, seed=121)
+    a, b = t.seq_alloc(), t.seq_alloc()
+    t.step([a], [20000 - 4096 * 4], decode=False)
+    for _ in range(4):
+        t.step([a], [4096], decode=False)
+    t.step([a, b], [40, 2500], every_token=True, f32_out=True)
+    items, ct, _ = t.gpu.step_prefill_plan()
+    assert ct[0] < 20040 and len(set(items[items[:, 0] == 0][:, 1].tolist())) > 1     # sequence a was split
+    t.gpu.device_status()
+
+
 def test_decode_multi_refusals():
     from titan_engine_b200 import KvError
     t = Twin(1, 32, 8, 128, 64, 2, 32, dtype="bf16", impl="mma", max_step_tokens=256, seed=92)
@@ -654,8 +699,9 @@ def test_decode_multi_refusals():
     t.step([a, b], [40, 40])
     q = torch.zeros(6, 32, 128, device=t.dev, dtype=torch.bfloat16)
     t.gpu.step_begin([a, b], [33, 1]); assert t.mgr.reserve(a, 33) == O.OK and t.mgr.reserve(b, 1) == O.OK
-    with pytest.raises(KvError):                             # 4 heads per kv head x 33 tokens: more than 8 token groups
-        t.gpu.decode_multi(0, torch.zeros(34, 32, 128, device=t.dev, dtype=torch.bfloat16))
+    # 4 heads per kv head x 33 tokens is more than the decode kernel's 8 token groups: the prefill kernel takes it
+    t.gpu.decode_multi(0, torch.zeros(34, 32, 128, device=t.dev, dtype=torch.bfloat16))
+    assert len(t.gpu.step_prefill_plan()[0]) > 0
     t.gpu.step_begin([a, b], [2, 0]); assert t.mgr.reserve(a, 2) == O.OK
     with pytest.raises(KvError):                             # a sequence without a new token
         t.gpu.decode_multi(0, q[:2].contiguous())

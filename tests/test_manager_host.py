@@ -328,3 +328,59 @@ def test_fork_shares_full_pages_and_counts_references():
     with pytest.raises(KvError) as e:
         t.fork(s)
     assert e.value.status == L.TK_OUT_OF_PAGES and t.digest() == dg
+
+
+@pytest.mark.parametrize("shape", [(32, 8), (64, 8), (16, 16), (16, 1), (8, 4)])
+def test_prefill_work_list_covers_every_row_once(shape):
+    """Index arithmetic of the prefill attention kernel, replayed on the host: the tiles of 64 (token, head)
+    rows and their split-KV chunks cover every (query token, head) of the long sequences and every context
+    position that token may see exactly once; sequences with one 16-row tile stay with the decode kernel."""
+    H, Hkv = shape
+    G = H // Hkv
+    g = rng(7)
+    lens0 = [0, 5000, 33, 0, 40000, 700, 17]
+    n_new = [300, 1, 4096, 70, 37, 16 // G, max(2, 128 // G + 1)]
+    mpps = 3000
+    c = PagedKVCache(1, H, Hkv, 128, 9000, len(lens0), mpps, dtype="bf16", host_only=True, max_step_tokens=8192)
+    seqs = []
+    at = 0
+    for n in lens0:
+        s = c.seq_alloc()
+        pages = (n + 15) // 16
+        c.adopt(s, np.arange(at, at + pages, dtype=np.int32), n)
+        at += pages
+        seqs.append(s)
+    c.step_begin(seqs, n_new)
+    items, ct, n_decode = c.step_prefill_plan()
+    assert len(items) > 0
+    tpt = 64 // G
+    small = [i for i, n in enumerate(n_new) if n * G <= 16]
+    assert n_decode == sum(-(-(l + n) // c.step_chunk_tokens) * Hkv for i, (l, n) in enumerate(zip(lens0, n_new)) if i in small)
+    seen = {}
+    for b, chunk, kvh, tile in items.tolist():
+        assert b not in small and 0 <= kvh < Hkv
+        nq, ln = n_new[b], lens0[b] + n_new[b]
+        assert ct[b] % 16 == 0 and ct[b] <= 32768
+        tok_first = tile * tpt
+        tok_cnt = min(nq - tok_first, tpt)
+        assert tok_cnt >= 1
+        p_last = ln - nq + tok_first + tok_cnt - 1
+        t0, t1 = chunk * ct[b], min(chunk * ct[b] + ct[b], p_last + 1)
+        assert t1 > t0 and (t1 - t0 + 15) // 16 <= 2048
+        key = (b, kvh, tile)
+        seen.setdefault(key, []).append((t0, t1))
+    for b, nq in enumerate(n_new):
+        if b in small:
+            continue
+        tiles = -(-nq // tpt)
+        for kvh in range(Hkv):
+            for tile in range(tiles):
+                spans = sorted(seen.pop((b, kvh, tile)))
+                p_last = lens0[b] + min(nq, (tile + 1) * tpt) - 1
+                assert spans[0][0] == 0 and spans[-1][1] == p_last + 1
+                assert all(a[1] == bb[0] for a, bb in zip(spans, spans[1:]))
+                assert len(spans) == p_last // ct[b] + 1          # what the kernel takes as the group's item count
+    assert not seen
+    # a step the decode kernel's token groups can hold does not build the list
+    c.step_begin(seqs, [1, 1, 128 // G, 1, 1, 1, 1])
+    assert len(c.step_prefill_plan()[0]) == 0

@@ -77,6 +77,7 @@ SIGNATURES = {
     "tk_kv_step_num_tokens": (C.c_int, [_P]),
     "tk_kv_step_num_work_items": (C.c_int, [_P]),
     "tk_kv_step_chunk_tokens": (C.c_int, [_P]),
+    "tk_kv_step_prefill_plan": (C.c_int, [_P, C.c_int32, _I32P, _I32P, _I32P, _I32P]),
     "tk_kv_append": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P]),
     "tk_kv_decode": (C.c_int, [_P, C.c_int32, _P, _P, _P]),
     "tk_kv_append_decode": (C.c_int, [_P, C.c_int32, _P, _P, _P, _P, _P]),

@@ -223,7 +223,7 @@ uint64_t PageManager::digest() const {
 
 int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                            bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
-                           int max_partial_rows, StepPlan* plan, const int32_t* len_cap) {
+                           int max_partial_rows, StepPlan* plan, const int32_t* len_cap, int heads_per_kv) {
     if (n_seqs < 0 || (n_seqs > 0 && !seqs) || !plan) return ST_INVALID_ARG;
     const int ps = page_size_;
     if (chunk_tokens < 0 || chunk_tokens % ps != 0) return ST_INVALID_ARG;
@@ -380,6 +380,66 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     std::vector<WorkItem> sorted(order.size());
     for (size_t i = 0; i < order.size(); i++) sorted[i] = plan->items[order[i]];
     plan->items.swap(sorted);
+
+    // ---- prefill-sized steps: tiles of kPrefillRows rows for the sequences that append many tokens ----
+    plan->pf_built = false;
+    plan->pf_items.clear(); plan->pf_small_items.clear();
+    plan->pf_small_nq_max = 0; plan->pf_partial_rows = 0; plan->pf_groups = 0;
+    const int G = heads_per_kv;
+    if (!fp8 && !len_cap && G > 0 && G <= kDecodeTileRows && plan->nq_min >= 1 &&
+        (int64_t)plan->nq_max * G > (int64_t)kDecodeTileRows * kDecodeMaxTokenGroups) {
+        const int tpt = kPrefillRows / G;                      // query tokens per tile
+        const int max_ct = kPrefillMaxPages * ps;
+        plan->pf_ct.assign(n_seqs, 0); plan->pf_poff.assign(n_seqs, 0); plan->pf_cbase.assign(n_seqs, 0);
+        auto is_small = [&](int i) { return plan->nq[i] * G <= kDecodeTileRows; };
+        // split-KV chunk per sequence: about 48 items per sequence where its tiles alone give fewer; halve
+        // the number of chunks (shrink) until the split regions fit the workspace
+        for (int shrink = 0;; shrink++) {
+            int64_t rows = 0;
+            for (int i = 0; i < n_seqs; i++) {
+                if (is_small(i)) continue;
+                const int nq = plan->nq[i], len = plan->len[i];
+                const int tiles = (nq + tpt - 1) / tpt;
+                int want = (48 + tiles * num_kv_heads - 1) / (tiles * num_kv_heads);
+                want = std::max(1, want >> shrink);
+                int64_t ct = ((int64_t)len + want - 1) / want;
+                ct = (ct + 511) / 512 * 512;
+                ct = std::min<int64_t>(std::max<int64_t>(ct, 1024), max_ct);
+                plan->pf_ct[i] = (int32_t)ct;
+                const int n_chunks = (int)((len + ct - 1) / ct);
+                plan->pf_poff[i] = (int32_t)rows;
+                if (n_chunks > 1) rows += (int64_t)n_chunks * nq;
+            }
+            if (rows <= max_partial_rows) { plan->pf_partial_rows = (int32_t)rows; break; }
+            if (shrink > 8) return ST_INVALID_ARG;             // contexts beyond 32768 tokens per chunk and no room
+        }
+        std::vector<int64_t> weight;
+        for (int i = 0; i < n_seqs; i++) {
+            if (is_small(i)) { plan->pf_small_nq_max = std::max(plan->pf_small_nq_max, plan->nq[i]); continue; }
+            const int nq = plan->nq[i], len = plan->len[i], ct = plan->pf_ct[i];
+            const int tiles = (nq + tpt - 1) / tpt;
+            plan->pf_cbase[i] = plan->pf_groups;
+            plan->pf_groups += tiles * num_kv_heads;
+            for (int t = 0; t < tiles; t++) {
+                const int tok_cnt = std::min(nq - t * tpt, tpt);
+                const int p_last = len - nq + t * tpt + tok_cnt - 1;
+                for (int c = 0; c <= p_last / ct; c++)
+                    for (int h = 0; h < num_kv_heads; h++) {
+                        plan->pf_items.push_back({i, c, h, t});
+                        weight.push_back((int64_t)(std::min(ct, p_last + 1 - c * ct)) * (tok_cnt * G));
+                    }
+            }
+        }
+        for (const WorkItem& w : plan->items)
+            if (is_small(w.b)) plan->pf_small_items.push_back(w);     // already big-first
+        std::vector<int32_t> ord(plan->pf_items.size());
+        for (size_t i = 0; i < ord.size(); i++) ord[i] = (int32_t)i;
+        std::stable_sort(ord.begin(), ord.end(), [&](int32_t a, int32_t b) { return weight[a] > weight[b]; });
+        std::vector<WorkItem> pf_sorted(ord.size());
+        for (size_t i = 0; i < ord.size(); i++) pf_sorted[i] = plan->pf_items[ord[i]];
+        plan->pf_items.swap(pf_sorted);
+        plan->pf_built = true;
+    }
     return ST_OK;
 }
 

@@ -57,7 +57,27 @@ struct StepPlan {
     std::vector<SealItem> seals;
     std::vector<Eviction> evictions; // pages that went cold in this step (copy out before reuse)
     int32_t evictions_refused = 0;   // sequences whose pages stayed hot because the host pool was full
+
+    // Prefill-sized multi-token steps (16-bit storage, some sequence appending more tokens than the decode
+    // kernel's token groups hold).  Sequences whose (tokens x heads per kv head) rows fit one 16-row tile keep
+    // the decode kernel (pf_small_items, chunked by chunk_tokens); the others are cut into tiles of 64 rows
+    // and, where a sequence has too few tiles to fill the GPU, into split-KV chunks of pf_ct[b] tokens.
+    bool pf_built = false;
+    std::vector<WorkItem> pf_items;        // (b, chunk, kvh, tile)
+    std::vector<WorkItem> pf_small_items;  // (b, chunk, kvh, 0)
+    std::vector<int32_t> pf_ct;            // [n_seqs] split-KV chunk of the sequence in the prefill kernel (tokens)
+    std::vector<int32_t> pf_poff;          // [n_seqs] first token row of the sequence's split region (rows of H x (Dv+2) floats)
+    std::vector<int32_t> pf_cbase;         // [n_seqs] first arrival counter of the sequence: + kvh * tiles + tile
+    int32_t pf_small_nq_max = 0;           // most tokens a sequence of pf_small_items appends
+    int32_t pf_partial_rows = 0;           // token rows the split regions take
+    int32_t pf_groups = 0;                 // (sequence, kv head, tile) groups = arrival counters in use
 };
+
+// Geometry of the prefill kernel's work list, shared by the planner and the kernel.
+constexpr int kPrefillRows = 64;           // (token, head) rows per tile
+constexpr int kPrefillMaxPages = 2048;     // pages per item: a split-KV chunk holds at most 32768 tokens
+constexpr int kDecodeTileRows = 16;        // rows of the decode kernel's tile
+constexpr int kDecodeMaxTokenGroups = 8;   // token groups per sequence the decode kernel's multi-token form takes
 
 class PageManager {
 public:
@@ -111,9 +131,11 @@ public:
     // token list in call order then position, FP8 seal list, split-KV work list.
     // chunk_tokens == 0 picks a chunk so that about `target_items` items exist.
     // len_cap (optional, 16-bit storage only) limits the attended prefix of each sequence.
+    // heads_per_kv > 0 (16-bit storage): also lay out the prefill work lists when a sequence appends
+    // more tokens than the decode kernel's token groups hold.
     int plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                   bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
-                  int max_partial_rows, StepPlan* plan, const int32_t* len_cap = nullptr);
+                  int max_partial_rows, StepPlan* plan, const int32_t* len_cap = nullptr, int heads_per_kv = 0);
 
     struct Counters { int64_t page_allocs = 0, page_frees = 0, seq_allocs = 0, seq_frees = 0, evictions = 0; } counters;
 

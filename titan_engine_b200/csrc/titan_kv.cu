@@ -102,6 +102,10 @@ struct tk_kv {
     int max_partial_rows = 0, max_items = 0, max_seals = 0;
     int* d_status = nullptr;
     int* d_counters = nullptr;           // [8 token groups][max_seqs * Hkv] arrival counters of the in-kernel merge
+    int* d_pf_counters = nullptr;        // prefill kernel: one per (sequence, kv head, tile) group
+    int max_pf_groups = 0, max_pf_items = 0;
+    tk::PrefillDev pf_dev{};             // device view of the step's prefill work list
+    tk::StepDev small_dev{};             // ... and of the decode-kernel share of such a step
 
     size_t step_bytes = 0;
     uint8_t* d_step = nullptr;
@@ -200,6 +204,7 @@ void release(tk_kv* h) {
         if (h->d_multi_partials) cudaFree(h->d_multi_partials);
         if (h->d_status) cudaFree(h->d_status);
         if (h->d_counters) cudaFree(h->d_counters);
+        if (h->d_pf_counters) cudaFree(h->d_pf_counters);
         if (h->d_step) cudaFree(h->d_step);
         if (h->d_q) cudaFree(h->d_q);
         if (h->d_rq) cudaFree(h->d_rq);
@@ -264,10 +269,18 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->max_partial_rows = (int)rows;
     h->max_items = h->max_partial_rows * c.num_kv_heads;
     h->max_seals = c.max_step_tokens / c.page_size + c.max_seqs;
+    {   // prefill work list: tiles of 64 rows per (sequence, kv head), times the split-KV chunks a tile may see
+        const int G = c.num_heads / c.num_kv_heads;
+        const int64_t tiles = (int64_t)c.max_step_tokens * G / tk::kPrefillRows + c.max_seqs;
+        const int64_t long_chunks = ((int64_t)c.max_pages_per_seq + tk::kPrefillMaxPages - 1) / tk::kPrefillMaxPages;
+        h->max_pf_groups = (int)std::min<int64_t>(tiles * c.num_kv_heads, 1 << 24);
+        h->max_pf_items = (int)std::min<int64_t>(tiles * c.num_kv_heads * long_chunks + 128 * (int64_t)c.max_seqs, 1 << 24);
+    }
 
     // one buffer holds every per-step array; sections are 16-byte aligned
-    size_t ints = 6 * (size_t)c.max_seqs + 4 + 20 + 4 * (size_t)c.max_step_tokens + 16 +
-                  4 * (size_t)h->max_items + 4 * (size_t)h->max_seals + 2 * (size_t)kMaxDelta + 32;
+    size_t ints = 9 * (size_t)c.max_seqs + 4 + 32 + 4 * (size_t)c.max_step_tokens + 16 +
+                  8 * (size_t)h->max_items + 4 * (size_t)h->max_pf_items + 4 * (size_t)h->max_seals +
+                  2 * (size_t)kMaxDelta + 32;
     h->step_bytes = align_up(ints * 4, 256);
 
     if (h->host_only) { *out = h; return TK_OK; }
@@ -315,6 +328,8 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     CREATE_CUDA(cudaMemset(h->d_status, 0, 256));
     CREATE_CUDA(cudaMalloc((void**)&h->d_counters, sizeof(int) * 8 * (size_t)c.max_seqs * c.num_kv_heads));
     CREATE_CUDA(cudaMemset(h->d_counters, 0, sizeof(int) * 8 * (size_t)c.max_seqs * c.num_kv_heads));
+    CREATE_CUDA(cudaMalloc((void**)&h->d_pf_counters, sizeof(int) * (size_t)h->max_pf_groups));
+    CREATE_CUDA(cudaMemset(h->d_pf_counters, 0, sizeof(int) * (size_t)h->max_pf_groups));
     CREATE_CUDA(cudaMalloc((void**)&h->d_step, h->step_bytes + kCanaryBytes));
     h->canaries.push_back({"step metadata", h->d_step + h->step_bytes});
     for (const auto& cn : h->canaries) CREATE_CUDA(cudaMemset(cn.at, kCanaryByte, kCanaryBytes));
@@ -426,9 +441,10 @@ int prefetch_layer(tk_kv* h, int layer, bool ahead) {
 }
 
 struct Sections {       // offsets (in int32 units) of the arrays inside a step buffer
-    size_t seq, len, chunk_base, new_tok, q_base, nq, tok_b, tok_pos, tok_dst, tok_open, items, seals, delta, end;
+    size_t seq, len, chunk_base, new_tok, q_base, nq, tok_b, tok_pos, tok_dst, tok_open, items, seals, delta,
+           pf_ct, pf_poff, pf_cbase, pf_items, pf_small, end;
 };
-Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals, int n_delta) {
+Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals, int n_delta, int n_pf, int n_pf_small) {
     auto a4 = [](size_t x) { return (x + 3) / 4 * 4; };
     Sections s{};
     size_t o = 0;
@@ -445,6 +461,13 @@ Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals
     s.items = o;      o = a4(o + 4 * (size_t)n_items);
     s.seals = o;      o = a4(o + 4 * (size_t)n_seals);
     s.delta = o;      o = a4(o + 2 * (size_t)n_delta);
+    if (n_pf || n_pf_small) {
+        s.pf_ct = o;    o = a4(o + n_seqs);
+        s.pf_poff = o;  o = a4(o + n_seqs);
+        s.pf_cbase = o; o = a4(o + n_seqs);
+        s.pf_items = o; o = a4(o + 4 * (size_t)n_pf);
+        s.pf_small = o; o = a4(o + 4 * (size_t)n_pf_small);
+    }
     s.end = o;
     return s;
 }
@@ -619,7 +642,8 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     const int target = 8 * h->num_sms;       // work items the planner aims for when it picks the chunk itself
     // the tensor-core kernel keeps one page id per lane per warp: chunk <= 16*4*32 tokens
     int st = h->mgr->plan_step(n_seqs, seq_ids, n_new, h->cfg.num_kv_heads, h->cfg.dtype == TK_FP8_E4M3,
-                               chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan, len_cap);
+                               chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan, len_cap,
+                               h->geo.H / h->geo.Hkv);
     if (st != TK_OK) return fail(h, st, "step_begin: %s", tk_status_str(st));
     tk::StepPlan& p = h->plan;
     if (chunk == 0 && p.chunk_tokens > 2048) {
@@ -659,7 +683,10 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     if (n_items > h->max_items || n_seals > h->max_seals)
         return fail(h, TK_INVALID_ARG, "step_begin: work list exceeds the workspace (%d items, %d seals)", n_items, n_seals);
     const int n_open = (int)p.tok_open.size();
-    Sections sec = sections(n_seqs, n_tok, n_open, n_items, n_seals, n_delta);
+    const int n_pf = p.pf_built ? (int)p.pf_items.size() : 0, n_pf_small = p.pf_built ? (int)p.pf_small_items.size() : 0;
+    if (n_pf > h->max_pf_items || p.pf_groups > h->max_pf_groups)
+        return fail(h, TK_INVALID_ARG, "step_begin: prefill work list exceeds the workspace (%d items, %d groups)", n_pf, p.pf_groups);
+    Sections sec = sections(n_seqs, n_tok, n_open, n_items, n_seals, n_delta, n_pf, n_pf_small);
     if (sec.end * 4 > h->step_bytes) return fail(h, TK_INVALID_ARG, "step_begin: step metadata exceeds its buffer");
 
     const int r = h->ring_pos;
@@ -684,6 +711,13 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     if (n_seals) memcpy(w + sec.seals, p.seals.data(), 16 * (size_t)n_seals);
     for (int i = 0; i < n_delta; i++) { w[sec.delta + 2 * i] = delta[i].first; w[sec.delta + 2 * i + 1] = dev_entry(delta[i].second); }
     delta.clear();
+    if (p.pf_built) {
+        memcpy(w + sec.pf_ct, p.pf_ct.data(), 4 * (size_t)n_seqs);
+        memcpy(w + sec.pf_poff, p.pf_poff.data(), 4 * (size_t)n_seqs);
+        memcpy(w + sec.pf_cbase, p.pf_cbase.data(), 4 * (size_t)n_seqs);
+        if (n_pf) memcpy(w + sec.pf_items, p.pf_items.data(), 16 * (size_t)n_pf);
+        if (n_pf_small) memcpy(w + sec.pf_small, p.pf_small_items.data(), 16 * (size_t)n_pf_small);
+    }
     TK_CUDA(h, cudaMemcpyAsync(h->d_step, w, sec.end * 4, cudaMemcpyHostToDevice, s));
     TK_CUDA(h, cudaEventRecord(h->ev[r], s));
     h->ev_pending[r] = true;
@@ -697,6 +731,14 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     dv.items = (const int4*)(d + sec.items); dv.seals = (const int4*)(d + sec.seals);
     dv.n_seqs = n_seqs; dv.n_tokens = n_tok; dv.n_items = n_items; dv.n_seals = n_seals;
     dv.chunk_tokens = p.chunk_tokens; dv.n_open = n_open;
+    h->pf_dev = tk::PrefillDev{};
+    if (p.pf_built) {
+        h->pf_dev = tk::PrefillDev{(const int4*)(d + sec.pf_items), d + sec.pf_ct, d + sec.pf_poff, d + sec.pf_cbase, n_pf};
+        h->small_dev = dv;                                  // the decode kernel's share: the short sequences only
+        h->small_dev.items = (const int4*)(d + sec.pf_small);
+        h->small_dev.n_items = n_pf_small;
+        h->small_dev.nq_max = p.pf_small_nq_max;
+    }
     if (n_delta) {
         TK_CUDA(h, tk::launch_apply_delta(h->d_table, (const int2*)(d + sec.delta), n_delta, s));
         h->launches++;
@@ -733,6 +775,20 @@ int tk_kv_set_num_heads(tk_kv* h, int32_t num_heads) {
 int tk_kv_step_num_tokens(const tk_kv* h) { return h && h->have_step ? (int)h->plan.tok_b.size() : -1; }
 int tk_kv_step_num_work_items(const tk_kv* h) { return h && h->have_step ? (int)h->plan.items.size() : -1; }
 int tk_kv_step_chunk_tokens(const tk_kv* h) { return h && h->have_step ? h->plan.chunk_tokens : -1; }
+int tk_kv_step_prefill_plan(const tk_kv* h, int32_t cap, int32_t* items, int32_t* n_items, int32_t* chunk_tokens,
+                            int32_t* n_decode_items) {
+    if (!h || !h->have_step || !n_items) return TK_INVALID_ARG;
+    const tk::StepPlan& p = h->plan;
+    *n_items = p.pf_built ? (int32_t)p.pf_items.size() : 0;
+    if (n_decode_items) *n_decode_items = p.pf_built ? (int32_t)p.pf_small_items.size() : 0;
+    if (!p.pf_built) return TK_OK;
+    if (items) {
+        if (cap < *n_items) return TK_INVALID_ARG;
+        memcpy(items, p.pf_items.data(), 16 * p.pf_items.size());
+    }
+    if (chunk_tokens) memcpy(chunk_tokens, p.pf_ct.data(), 4 * p.pf_ct.size());
+    return TK_OK;
+}
 
 int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t* slots_out, void* stream) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
@@ -892,12 +948,43 @@ static int decode_multi_impl(tk_kv* h, int32_t layer, const void* q, void* out, 
     if (!q || !out) return fail(h, TK_INVALID_ARG, "decode_multi: null q/out");
     const tk::StepPlan& p = h->plan;
     if (p.nq_min < 1) return fail(h, TK_INVALID_ARG, "decode_multi: every sequence of the step must append at least one token");
+    if (p.pf_built && h->use_mma && !h->mla_mma && tk::prefill_mma_supported(h->geo)) {
+        // a prefill-sized step: the sequences with one tile of rows keep the decode kernel, the prefill
+        // kernel takes the others; the two write disjoint rows of `out`
+        if (h->mgr->cold_enabled() && h->mgr->cold_high_water() > 0)
+            return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
+        cudaError_t e = cudaSuccess;
+        if (h->small_dev.n_items > 0) {
+            if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)
+                return fail(h, TK_UNSUPPORTED, "decode_multi: needs the in-kernel merge");
+            const size_t need_small = (size_t)p.chunk_base[h->dev.n_seqs] * h->geo.H * p.pf_small_nq_max * (h->geo.Dv + 2);
+            if (need_small > (size_t)h->max_partial_rows * h->cfg.num_heads * (h->cfg.v_head_dim + 2))
+                return fail(h, TK_UNSUPPORTED, "decode_multi: split-KV workspace too small for the step's short sequences");
+            const tk::MergeOut mo{h->d_counters, out, nullptr, out_dtype, nullptr, h->d_status};
+            e = tk::launch_decode_mma_multi(h->geo, h->layer(layer), &h->maps[layer], h->small_dev, h->d_table, q,
+                                            h->d_partials, h->d_status, (cudaStream_t)stream, mo);
+            h->launches++;
+            if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode_multi launch: %s", cudaGetErrorString(e));
+        }
+        // the prefill kernel's split regions lie behind the rows the decode kernel's share uses
+        float* pf_partials = h->d_partials;
+        if (h->small_dev.n_items > 0 && p.pf_partial_rows > 0) {
+            const size_t small_rows = (size_t)p.chunk_base[h->dev.n_seqs] * p.pf_small_nq_max;
+            if (small_rows + (size_t)p.pf_partial_rows > (size_t)h->max_partial_rows)
+                return fail(h, TK_UNSUPPORTED, "decode_multi: split-KV workspace too small for this step");
+            pf_partials += small_rows * h->cfg.num_heads * (h->cfg.v_head_dim + 2);
+        }
+        e = tk::launch_prefill_mma(h->geo, &h->maps[layer], h->dev, h->pf_dev, h->d_table, q, out, out_dtype, pf_partials,
+                                   h->d_pf_counters, h->d_status, (cudaStream_t)stream);
+        if (h->pf_dev.n_items > 0) h->launches++;
+        if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "prefill attention launch: %s", cudaGetErrorString(e));
+        return TK_OK;
+    }
     const bool ok = h->use_mma && (h->mla_mma ? tk::decode_mma_mla_multi_supported(h->geo, p.nq_max)
                                               : tk::decode_mma_multi_supported(h->geo, p.nq_max));
     if (!ok)
-        return fail(h, TK_UNSUPPORTED, "decode_multi: needs the tensor-core kernel on a 16-bit pool and (heads per kv head) x "
-                                       "(tokens per sequence) <= %d (here %d x %d)", h->mla_mma ? 64 : 128,
-                    h->geo.H / h->geo.Hkv, p.nq_max);
+        return fail(h, TK_UNSUPPORTED, "decode_multi: needs the tensor-core kernels on a 16-bit pool (MLA shape: (heads per kv "
+                                       "head) x (tokens per sequence) <= 64; here %d x %d)", h->geo.H / h->geo.Hkv, p.nq_max);
     if (h->mgr->cold_enabled() && h->mgr->cold_high_water() > 0)
         return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
     if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "kv_manager.h"
+
 namespace tk {
 
 // Storage numbering = titan::DType (reference: src/core/types.h:17-21).
@@ -59,6 +61,17 @@ struct StepDev {
     int n_seqs, n_tokens, n_items, n_seals, chunk_tokens;
     int n_open;
     int nq_max;                 // multi-token attention: largest nq of the step (row stride of the partials)
+};
+
+// Work list of the prefill kernel (prefill_mma.cu): tiles of kPrefillRows (token, head) rows per
+// (sequence, kv head), each over the whole visible context or over split-KV chunks of ct[b] tokens.
+// (kPrefillRows, kPrefillMaxPages: kv_manager.h, shared with the planner)
+struct PrefillDev {
+    const int4*    items;       // [n_items] (b, chunk, kvh, tile)
+    const int32_t* ct;          // [n_seqs] split-KV chunk of the sequence, tokens
+    const int32_t* poff;        // [n_seqs] first token row of the sequence's split region in the workspace
+    const int32_t* cbase;       // [n_seqs] first arrival counter of the sequence (+ kvh * tiles + tile)
+    int n_items;
 };
 
 // partial row layout: [row][H][D+2] f32 = o[0..D) unnormalised, m at [D], l at [D+1]
@@ -140,6 +153,12 @@ int         decode_mma_multi_groups(const Geometry& g, int nq_max);
 cudaError_t launch_decode_mma_multi(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map, const StepDev& st,
                                     const int32_t* page_table, const void* q, float* partials, int* status,
                                     cudaStream_t s, const MergeOut& mo);
+
+// Attention for every token of a prefill chunk (16-bit pools, page size 16, D in {64,128}, no cold pages).
+bool        prefill_mma_supported(const Geometry& g);
+cudaError_t launch_prefill_mma(const Geometry& g, const CUtensorMap* map, const StepDev& st, const PrefillDev& pf,
+                               const int32_t* page_table, const void* q, void* out, int out_dtype, float* partials,
+                               int* counters, int* status, cudaStream_t s);
 
 // The same for the MLA cache shape (K rows 192, V rows 128; 16-bit pools, groups of <= 8 heads).
 bool        decode_mma_mla_supported(const Geometry& g);

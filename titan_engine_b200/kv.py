@@ -194,6 +194,17 @@ class PagedKVCache:
     def step_chunk_tokens(self) -> int:
         return self._lib.tk_kv_step_chunk_tokens(self._h)
 
+    def step_prefill_plan(self):
+        """-> (items [n, 4] int32: (sequence index, chunk, kv head, tile), chunk tokens per sequence, decode-kernel items)
+        of the prefill attention kernel for the current step; n == 0 when the step does not use it."""
+        n, nd = C.c_int32(0), C.c_int32(0)
+        self._check(self._lib.tk_kv_step_prefill_plan(self._h, 0, None, C.byref(n), None, C.byref(nd)))
+        items = np.zeros((n.value, 4), dtype=np.int32)
+        ct = np.zeros(max(self._n_seqs, 1), dtype=np.int32)
+        if n.value:
+            self._check(self._lib.tk_kv_step_prefill_plan(self._h, n.value, _ptr(items), C.byref(n), _ptr(ct), C.byref(nd)))
+        return items, ct[:self._n_seqs], nd.value
+
     def _check_io(self, t: torch.Tensor, rows: int, heads: int, what: str) -> None:
         dim = self.cfg.v_head_dim if what in ("v", "out") else self.cfg.head_dim
         if t.device != self.device or t.dtype != self.io_torch_dtype or not t.is_contiguous():
