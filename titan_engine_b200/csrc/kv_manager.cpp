@@ -392,6 +392,10 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         const int max_ct = kPrefillMaxPages * ps;
         plan->pf_ct.assign(n_seqs, 0); plan->pf_poff.assign(n_seqs, 0); plan->pf_cbase.assign(n_seqs, 0);
         auto is_small = [&](int i) { return plan->nq[i] * G <= kDecodeTileRows; };
+        for (int i = 0; i < n_seqs; i++)
+            if (is_small(i)) plan->pf_small_nq_max = std::max(plan->pf_small_nq_max, plan->nq[i]);
+        // rows of the workspace the decode kernel's share of the step uses; the split regions lie behind them
+        const int64_t small_rows = (int64_t)plan->chunk_base[n_seqs] * plan->pf_small_nq_max;
         // split-KV chunk per sequence: about 48 items per sequence where its tiles alone give fewer; halve
         // the number of chunks (shrink) until the split regions fit the workspace
         for (int shrink = 0;; shrink++) {
@@ -410,12 +414,12 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
                 plan->pf_poff[i] = (int32_t)rows;
                 if (n_chunks > 1) rows += (int64_t)n_chunks * nq;
             }
-            if (rows <= max_partial_rows) { plan->pf_partial_rows = (int32_t)rows; break; }
+            if (small_rows + rows <= max_partial_rows) { plan->pf_partial_rows = (int32_t)rows; break; }
             if (shrink > 8) return ST_INVALID_ARG;             // contexts beyond 32768 tokens per chunk and no room
         }
         std::vector<int64_t> weight;
         for (int i = 0; i < n_seqs; i++) {
-            if (is_small(i)) { plan->pf_small_nq_max = std::max(plan->pf_small_nq_max, plan->nq[i]); continue; }
+            if (is_small(i)) continue;
             const int nq = plan->nq[i], len = plan->len[i], ct = plan->pf_ct[i];
             const int tiles = (nq + tpt - 1) / tpt;
             plan->pf_cbase[i] = plan->pf_groups;

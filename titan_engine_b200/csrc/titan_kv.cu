@@ -1187,6 +1187,9 @@ int tk_kv_device_status(tk_kv* h, void* stream) {
     TK_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream));
     if (st != 0) {
         cudaMemsetAsync(h->d_status, 0, sizeof(int), (cudaStream_t)stream);
+        // CTAs that gave up may have left arrival counters of the in-kernel merges half counted
+        cudaMemsetAsync(h->d_counters, 0, sizeof(int) * 8 * (size_t)h->cfg.max_seqs * h->cfg.num_kv_heads, (cudaStream_t)stream);
+        cudaMemsetAsync(h->d_pf_counters, 0, sizeof(int) * (size_t)h->max_pf_groups, (cudaStream_t)stream);
         return fail(h, st, "a device-side wait gave up (status %d)", st);
     }
     return TK_OK;
