@@ -79,11 +79,15 @@ def test_8b_shape_full_size_sampled_sequences(impl):
 
 
 def test_70b_shape_fp8_sampled_sequences():
-    """32 sequences at 32768 tokens (+ an open page of 5 tokens), 64 q / 8 kv heads, FP8-E4M3 pool."""
-    lens = np.full(32, 32768 + 5)
-    c, _, seqs, gen = build(64, 8, 128, "fp8", lens, seed=4)
+    """32 sequences at 32768 tokens plus an open page of 5 tokens, 64 q / 8 kv heads, FP8-E4M3 pool."""
+    lens = np.full(32, 32768)
+    c, _, seqs, gen = build(64, 8, 128, "fp8", lens, seed=4, max_step_tokens=32 * 5)
     q = torch.randn(32, 64, 128, device=c.device, generator=gen).to(torch.bfloat16)
-    c.step_begin(seqs, None)
+    k = torch.randn(32 * 5, 8, 128, device=c.device, generator=gen).to(torch.bfloat16)
+    v = torch.randn(32 * 5, 8, 128, device=c.device, generator=gen).to(torch.bfloat16)
+    c.step_begin(seqs, [5] * 32)                         # five tokens per sequence: they stay in the 16-bit open pages
+    c.append(0, k, v)
+    lens = lens + 5
     got = c.decode_f32(0, q).cpu().numpy()
     c.device_status()
     for b, want in oracle_sample(c, seqs, lens, [0, 13, 31], q, "fp8").items():

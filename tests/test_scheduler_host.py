@@ -95,3 +95,82 @@ def test_preemption_when_pages_run_out_and_state_parity():
     assert st["completed_requests"] == 7 and st["preemptions"] > 0
     assert st["total_tokens_generated"] == sum(want.values())   # a preempted request resumes, it does not restart its count
     assert c.num_free_pages == 24 and 0 < st["batch_utilization"] <= 1
+
+
+def churn_lengths(g, n=256):
+    """The churn configuration's context lengths: lognormal, median 2048, sigma 1, capped at 32768."""
+    return [int(min(32768, max(1, round(float(np.exp(g.normal(np.log(2048.0), 1.0))))))) for _ in range(n)]
+
+
+def test_churn_configuration_full_size_200_steps_direct_calls():
+    """The continuous-batching churn configuration at FULL size on the bookkeeping-only handle: 256
+    sequences, lognormal lengths, 200 steps; every step retires 13 sequences (ascending slot), admits 13
+    with prompts of 256..4096 tokens (ascending slot), every survivor appends one token.  Page tables,
+    lengths and the free list equal the oracle manager's after EVERY step."""
+    g = rng(3)
+    lens = churn_lengths(g)
+    num_pages = sum((n + 15) // 16 for n in lens) + 13 * 257 * 8 + 4096
+    mpps = (32768 + 4096 + 256) // 16
+    c = PagedKVCache(2, 32, 8, 128, num_pages, 256, mpps, dtype="fp16", host_only=True, max_step_tokens=13 * 4096 + 256)
+    o = O.Manager(num_pages, 256, mpps, 16)
+    live = []
+    for n in lens:
+        s = c.seq_alloc(); assert o.seq_alloc() == s
+        c.reserve(s, n); assert o.reserve(s, n) == O.OK
+        live.append(s)
+    assert c.digest() == o.digest()
+    for step in range(200):
+        gone = sorted(g.choice(live, size=13, replace=False).tolist())
+        for s in gone:
+            c.seq_free(s); assert o.seq_free(s) == O.OK
+            live.remove(s)
+        new = []
+        for _ in gone:
+            s = c.seq_alloc(); assert o.seq_alloc() == s
+            new.append(s)
+        ids = sorted(live) + sorted(new)
+        n_new = [1] * len(live) + [int(g.integers(256, 4097)) for _ in new]
+        c.step_begin(ids, n_new)
+        for s, n in zip(ids, n_new):
+            assert o.reserve(s, n) == O.OK
+        assert c.digest() == o.digest(), f"churn step {step}: page/slot state diverged"
+        live = ids
+        # the prompts admitted by this step are prefill chunks for the attention kernel
+        items, ct, n_decode = c.step_prefill_plan()
+        assert len(items) > 0 and n_decode > 0 and len(set(items[:, 0].tolist())) == 13
+    st = c.stats()
+    assert st["steps"] == 200 and st["seq_frees"] == 200 * 13 and c.num_free_pages == o.num_free_pages()
+
+
+def test_churn_configuration_full_size_200_steps_through_the_scheduler():
+    """The same configuration driven through tk_sched_*: 256 requests, every step 13 of the decoding ones
+    finish and 13 new prompts are queued; the scheduler's retire / admit / step decisions replayed on the
+    oracle manager give bit-identical state after every one of the 200 steps."""
+    g = rng(33)
+    lens = churn_lengths(g)
+    budget = 13 * 4096
+    num_pages = sum((n + 15) // 16 for n in lens) + 13 * 257 * 8 + 4096
+    mpps = (32768 + 4096 + 4096 + 256) // 16
+    c = PagedKVCache(2, 32, 8, 128, num_pages, 256, mpps, dtype="fp16", host_only=True, max_step_tokens=budget + 256)
+    s = BatchScheduler(c, 256, budget)
+    o = O.Manager(num_pages, 256, mpps, 16)
+    for n in lens:
+        s.submit(n, 4096)
+    for _ in range(400):                                     # set-up: chunked prefill of the 256 contexts
+        rows = s.next(); replay(s, c, o, rows)
+        s.commit([False] * len(rows))
+        if len(rows) == 256 and all(r.n_new == 1 for r in rows):
+            break
+    else:
+        raise AssertionError("set-up did not converge")
+    admitted = 0
+    for step in range(200):
+        rows = s.next(); replay(s, c, o, rows)
+        admitted += len(s.last_events()["admitted"])
+        decoding = [j for j, r in enumerate(rows) if r.n_new == 1]
+        gone = set(g.choice(decoding, size=13, replace=False).tolist())
+        s.commit([j in gone for j in range(len(rows))])
+        for _ in range(13):
+            s.submit(int(g.integers(256, 4097)), 4096)
+    st = s.stats()
+    assert admitted == 199 * 13 and st["preemptions"] == 0 and st["completed_requests"] >= 199 * 13

@@ -414,8 +414,9 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
                 plan->pf_poff[i] = (int32_t)rows;
                 if (n_chunks > 1) rows += (int64_t)n_chunks * nq;
             }
-            if (small_rows + rows <= max_partial_rows) { plan->pf_partial_rows = (int32_t)rows; break; }
-            if (shrink > 8) return ST_INVALID_ARG;             // contexts beyond 32768 tokens per chunk and no room
+            // (past the last shrink every sequence has as few chunks as 32768-token items allow: the caller
+            // then finds room for the rows elsewhere)
+            if (small_rows + rows <= max_partial_rows || shrink > 8) { plan->pf_partial_rows = (int32_t)std::min<int64_t>(rows, INT32_MAX); break; }
         }
         std::vector<int64_t> weight;
         for (int i = 0; i < n_seqs; i++) {

@@ -936,6 +936,21 @@ int tk_kv_decode_partial(tk_kv* h, int32_t layer, const void* q, float* partial,
     return decode_impl(h, layer, q, nullptr, partial, (cudaStream_t)stream);
 }
 
+// Split-KV workspace of a multi-token step: the handle's own when `floats` fit it, else a buffer that is
+// allocated (and grown) on demand - the one device allocation a step may make after creation.
+static float* multi_workspace(tk_kv* h, size_t floats, cudaStream_t stream) {
+    if (floats <= (size_t)h->max_partial_rows * h->cfg.num_heads * (h->cfg.v_head_dim + 2)) return h->d_partials;
+    if (floats > h->multi_partials_floats) {
+        if (cudaSetDevice(h->device) != cudaSuccess) { fail(h, TK_CUDA_ERROR, "cudaSetDevice failed"); return nullptr; }
+        if (h->d_multi_partials) { cudaStreamSynchronize(stream); cudaFree(h->d_multi_partials); }
+        h->d_multi_partials = nullptr; h->multi_partials_floats = 0;
+        cudaError_t e = cudaMalloc((void**)&h->d_multi_partials, floats * sizeof(float));
+        if (e != cudaSuccess) { fail(h, TK_CUDA_ERROR, "split-KV workspace of %zu bytes: %s", floats * sizeof(float), cudaGetErrorString(e)); return nullptr; }
+        h->multi_partials_floats = floats;
+    }
+    return h->d_multi_partials;
+}
+
 // Attention for every token the step appended (several per sequence), causal among themselves, in one
 // pass over the pages: what the verification of drafted tokens needs.
 static int decode_multi_impl(tk_kv* h, int32_t layer, const void* q, void* out, int out_dtype, void* stream) {
@@ -953,27 +968,23 @@ static int decode_multi_impl(tk_kv* h, int32_t layer, const void* q, void* out, 
         // kernel takes the others; the two write disjoint rows of `out`
         if (h->mgr->cold_enabled() && h->mgr->cold_high_water() > 0)
             return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
+        // split-KV rows: the decode kernel's share first, the prefill kernel's split regions behind it; steps that
+        // outgrow the handle's workspace get one of their own, grown when a step needs a larger one
+        const size_t row_floats = (size_t)h->cfg.num_heads * (h->cfg.v_head_dim + 2);
+        const size_t small_rows = h->small_dev.n_items > 0 ? (size_t)p.chunk_base[h->dev.n_seqs] * p.pf_small_nq_max : 0;
+        float* ws = multi_workspace(h, (small_rows + (size_t)p.pf_partial_rows) * row_floats, (cudaStream_t)stream);
+        if (!ws) return TK_CUDA_ERROR;
         cudaError_t e = cudaSuccess;
         if (h->small_dev.n_items > 0) {
             if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)
                 return fail(h, TK_UNSUPPORTED, "decode_multi: needs the in-kernel merge");
-            const size_t need_small = (size_t)p.chunk_base[h->dev.n_seqs] * h->geo.H * p.pf_small_nq_max * (h->geo.Dv + 2);
-            if (need_small > (size_t)h->max_partial_rows * h->cfg.num_heads * (h->cfg.v_head_dim + 2))
-                return fail(h, TK_UNSUPPORTED, "decode_multi: split-KV workspace too small for the step's short sequences");
             const tk::MergeOut mo{h->d_counters, out, nullptr, out_dtype, nullptr, h->d_status};
             e = tk::launch_decode_mma_multi(h->geo, h->layer(layer), &h->maps[layer], h->small_dev, h->d_table, q,
-                                            h->d_partials, h->d_status, (cudaStream_t)stream, mo);
+                                            ws, h->d_status, (cudaStream_t)stream, mo);
             h->launches++;
             if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode_multi launch: %s", cudaGetErrorString(e));
         }
-        // the prefill kernel's split regions lie behind the rows the decode kernel's share uses
-        float* pf_partials = h->d_partials;
-        if (h->small_dev.n_items > 0 && p.pf_partial_rows > 0) {
-            const size_t small_rows = (size_t)p.chunk_base[h->dev.n_seqs] * p.pf_small_nq_max;
-            if (small_rows + (size_t)p.pf_partial_rows > (size_t)h->max_partial_rows)
-                return fail(h, TK_UNSUPPORTED, "decode_multi: split-KV workspace too small for this step");
-            pf_partials += small_rows * h->cfg.num_heads * (h->cfg.v_head_dim + 2);
-        }
+        float* pf_partials = ws + small_rows * row_floats;
         e = tk::launch_prefill_mma(h->geo, &h->maps[layer], h->dev, h->pf_dev, h->d_table, q, out, out_dtype, pf_partials,
                                    h->d_pf_counters, h->d_status, (cudaStream_t)stream);
         if (h->pf_dev.n_items > 0) h->launches++;
@@ -989,20 +1000,10 @@ static int decode_multi_impl(tk_kv* h, int32_t layer, const void* q, void* out, 
         return fail(h, TK_UNSUPPORTED, "decode_multi: not available while pages are cold");
     if (p.has_empty_seq || h->separate_combine || h->dev.chunk_tokens > 2048)
         return fail(h, TK_UNSUPPORTED, "decode_multi: needs the in-kernel merge");
-    // partial rows hold H * nq_max columns here; the handle's workspace was sized for H columns, so steps
-    // that need more get a workspace of their own, grown when a step needs a larger one
-    float* partials = h->d_partials;
-    const size_t need = (size_t)p.chunk_base[h->dev.n_seqs] * h->geo.H * p.nq_max * (h->geo.Dv + 2);
-    if (need > (size_t)h->max_partial_rows * h->cfg.num_heads * (h->cfg.v_head_dim + 2)) {
-        if (need > h->multi_partials_floats) {
-            TK_CUDA(h, cudaSetDevice(h->device));
-            if (h->d_multi_partials) { TK_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream)); cudaFree(h->d_multi_partials); }
-            h->d_multi_partials = nullptr; h->multi_partials_floats = 0;
-            TK_CUDA(h, cudaMalloc((void**)&h->d_multi_partials, need * sizeof(float)));
-            h->multi_partials_floats = need;
-        }
-        partials = h->d_multi_partials;
-    }
+    // partial rows hold H * nq_max columns here; the handle's workspace was sized for H columns
+    float* partials = multi_workspace(h, (size_t)p.chunk_base[h->dev.n_seqs] * h->geo.H * p.nq_max * (h->geo.Dv + 2),
+                                      (cudaStream_t)stream);
+    if (!partials) return TK_CUDA_ERROR;
     const tk::MergeOut mo{h->d_counters, out, nullptr, out_dtype, nullptr, h->d_status};
     cudaError_t e = h->mla_mma
         ? tk::launch_decode_mma_mla_multi(h->geo, h->layer(layer), &h->maps[layer], &h->maps_v[layer], h->dev, h->d_table, q,
