@@ -49,6 +49,9 @@ enum { TK_DECODE_AUTO = 0, TK_DECODE_SIMT = 1, TK_DECODE_MMA = 2 };
 /* who merges the split-KV partial rows: the attention kernel's last CTA per (sequence, kv head), or a
  * combine launch of its own after it */
 enum { TK_MERGE_IN_KERNEL = 0, TK_MERGE_SEPARATE = 1 };
+/* back-to-back attention launches of different layers: the later one may start (programmatic dependent
+ * launch) while the earlier one drains, or every launch waits for the one before it */
+enum { TK_OVERLAP_AUTO = 0, TK_OVERLAP_OFF = 1 };
 
 /* Stands in for the (L, Hkv, D, max_seq_len, dtype) argument list of
  * KVCache::initialize (src/inference/kv_cache.h:21-23) plus the fields of
@@ -79,7 +82,8 @@ typedef struct tk_kv_config {
                                    attention_decode_mla, src/compute/cuda/attention.cu:168-253): K rows and q
                                    have head_dim, scale = 1/sqrtf(head_dim); 16-bit storage, generic kernel */
     int32_t merge_impl;         /* TK_MERGE_* */
-    int32_t reserved[2];
+    int32_t launch_overlap;     /* TK_OVERLAP_* */
+    int32_t reserved[1];
 } tk_kv_config;
 
 typedef struct tk_kv_stats {    /* in the style of CacheStats, src/memory/memory_manager.h:211-220 */

@@ -66,10 +66,19 @@ static int run_mla(const char* path, int n_tokens) {
 }
 
 int main(int argc, char** argv) {
-    if (argc < 2) { fprintf(stderr, "usage: %s out.bin [n_tokens] [0 owned | 1 external | 2 external MLA]\n", argv[0]); return 2; }
+    if (argc < 2) { fprintf(stderr, "usage: %s out.bin [n_tokens] [0 owned | 1 external | 2 external MLA | 3 storage types]\n", argv[0]); return 2; }
     const int n_tokens = argc > 2 ? atoi(argv[2]) : 150;
     const int mode = argc > 3 ? atoi(argv[3]) : 0;
     if (mode == 2) return run_mla(argv[1], n_tokens);
+    if (mode == 3) {
+        // storage types (RuntimeConfig::kv_cache_dtype, src/core/types.h:243-248): the reference ignores the argument;
+        // the paged cache stores FP32/FP16 requests as fp16, BF16 as bf16 and refuses FP8 (that pool is behind the C ABI)
+        titan::KVCache a, b, c;
+        const bool f16 = a.initialize(2, 2, 64, 64, titan::DType::FP16), bf = b.initialize(2, 2, 64, 64, titan::DType::BF16);
+        const bool f8 = c.initialize(2, 2, 64, 64, titan::DType::FP8_E4M3);
+        printf("dtype fp16 %d bf16 %d fp8_e4m3 %d\n", (int)f16, (int)bf, (int)f8);
+        return 0;
+    }
     const bool external = mode != 0;
     const uint32_t L = 2, H = 8, Hkv = 2, D = 64, max_seq = 256;
     const float theta = 10000.0f;

@@ -42,3 +42,13 @@ def test_mla_call_sites_same_results(tmp_path):
     assert ref.shape == ours.shape == (n * 2 * 8 * 128,)
     assert np.abs(ref).max() > 0.1
     assert_close(ours, ref, "compat MLA KVCache + attention_decode_mla vs the reference's own objects")
+
+
+def test_storage_types_are_mapped_or_refused_never_substituted(tmp_path):
+    """KVCache::initialize(..., DType): FP16 -> fp16 pool, BF16 -> bf16 pool, FP8_E4M3 refused with false (the
+    FP8 pool is behind the C ABI); the reference accepts every value because it ignores the argument."""
+    exe = os.path.join(BUILD, "kv_callsite_ours")
+    res = subprocess.run([exe, str(tmp_path / "x.bin"), "1", "3"], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "dtype fp16 1 bf16 1 fp8_e4m3 0" in res.stdout
+    assert "FP8-E4M3 pools are behind the C ABI" in res.stderr

@@ -100,6 +100,7 @@ __device__ __forceinline__ void open_page_item(uint8_t* smem, const Geometry& g,
             }
         }
     }
+    pdl_launch_dependents();
     auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * G + row) * (D + 2) + d]; };
 #pragma unroll
     for (int gq = 0; gq < MAXG; gq++) {
@@ -110,6 +111,7 @@ __device__ __forceinline__ void open_page_item(uint8_t* smem, const Geometry& g,
         }
     }
     __syncthreads();
+    pdl_wait();                                             // the split-KV rows and counters are shared with the launch before
     const int prow = st.chunk_base[b] + row_idx;
     for (int idx = threadIdx.x; idx < G * (D + 2); idx += blockDim.x) {
         const int row = idx / (D + 2), d = idx % (D + 2);
@@ -452,6 +454,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     }
     // a wait that gave up has set the status word: the merging CTA sees it and writes no output
     (void)alive;
+    // Every page tile of this CTA has been fetched and used.  Up to here the CTA has read only what kernels
+    // of other layers leave alone (its layer's pool, q, the step's metadata) and written only its own
+    // layer's pool row, so a launch of the next layer may start now; what follows (split-KV rows, arrival
+    // counters, `out`) is shared with the launch before and waits for it to finish.
+    pdl_launch_dependents();
 
     // ---- merge the 4 warps through shared memory (stage memory is idle now) ----------
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
@@ -485,6 +492,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         }
     }
     __syncthreads();
+    pdl_wait();
     const int prow = st.chunk_base[b] + chunk;
     const int heads_per_row = MULTI ? g.H * st.nq_max : g.H;   // columns of a partial row
     for (int idx = threadIdx.x; idx < rows * (D + 2); idx += blockDim.x) {
@@ -523,7 +531,7 @@ template <int KIND, int D, bool IO_BF16, bool GHI, bool MULTI = false>
 cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                        const CUtensorMap* map_cold, const StepDev& st,
                        const int32_t* page_table, const void* q, float* partials, int* status,
-                       cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
+                       cudaStream_t s, const MergeOut& mo, const FuseAppend& fa, bool overlap_prev = false) {
     using C = Cfg<KIND, D>;
     auto kern = decode_mma_kernel<KIND, D, IO_BF16, GHI, MULTI>;
     static bool attr_done[64] = {};                         // per instantiation and device
@@ -537,22 +545,32 @@ cudaError_t launch_one(const Geometry& g, const LayerPtrs& lp, const CUtensorMap
     // multi-token attention: one grid row per group of 16/G query tokens
     const int tpg = 16 / (g.H / g.Hkv);
     const dim3 grid(st.n_items, MULTI ? (st.nq_max + tpg - 1) / tpg : 1);
-    kern<<<grid, kWarps * 32, C::SMEM_BYTES, s>>>(*map, *map_cold, g, lp, st, page_table, (const uint16_t*)q,
-                                                  partials, status, mo, fa);
-    return cudaGetLastError();
+    if (!overlap_prev) {
+        kern<<<grid, kWarps * 32, C::SMEM_BYTES, s>>>(*map, *map_cold, g, lp, st, page_table, (const uint16_t*)q,
+                                                      partials, status, mo, fa);
+        return cudaGetLastError();
+    }
+    // may start while the kernel before it in the stream drains (see pdl_wait in the kernel)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kWarps * 32); cfg.dynamicSmemBytes = C::SMEM_BYTES; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, *map, *map_cold, g, lp, st, page_table, (const uint16_t*)q, partials, status, mo, fa);
 }
 
 template <int KIND, int D>
 cudaError_t launch_kd(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                       const CUtensorMap* map_cold, const StepDev& st,
                       const int32_t* page_table, const void* q, float* partials, int* status,
-                      cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
+                      cudaStream_t s, const MergeOut& mo, const FuseAppend& fa, bool ov) {
     const bool io_bf16 = g.io_dtype == DT_BF16;
     const bool ghi = g.H / g.Hkv > 8;
-    if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
-    if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
-    if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
-    return launch_one<KIND, D, false, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
+    if (io_bf16 && ghi)  return launch_one<KIND, D, true, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov);
+    if (io_bf16)         return launch_one<KIND, D, true, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov);
+    if (ghi)             return launch_one<KIND, D, false, true>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov);
+    return launch_one<KIND, D, false, false>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov);
 }
 
 template <int KIND, int D>
@@ -631,17 +649,18 @@ cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMa
 cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                               const CUtensorMap* map_cold, const StepDev& st, const int32_t* page_table, const void* q,
                               float* partials, int* status, cudaStream_t s, const MergeOut* merge,
-                              const FuseAppend* fuse) {
+                              const FuseAppend* fuse, bool overlap_prev) {
     if (st.n_items <= 0) return cudaSuccess;
     const MergeOut mo = merge ? *merge : MergeOut{nullptr, nullptr, nullptr, 0};
     const FuseAppend fa = fuse ? *fuse : FuseAppend{nullptr, nullptr, nullptr};
     if (!map_cold) map_cold = map;
     if (!decode_mma_supported(g) || st.chunk_tokens > kPage * kWarps * 32) return cudaErrorNotSupported;
-    if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
-    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd<K_BF16, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa)
-                                              : launch_kd<K_BF16, 64>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
-    return g.D == 128 ? launch_kd<K_F16, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa)
-                      : launch_kd<K_F16, 64>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa);
+    const bool ov = overlap_prev;
+    if (g.dtype == DT_FP8)  return launch_kd<K_FP8, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov);
+    if (g.dtype == DT_BF16) return g.D == 128 ? launch_kd<K_BF16, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov)
+                                              : launch_kd<K_BF16, 64>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov);
+    return g.D == 128 ? launch_kd<K_F16, 128>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov)
+                      : launch_kd<K_F16, 64>(g, lp, map, map_cold, st, page_table, q, partials, status, s, mo, fa, ov);
 }
 
 }  // namespace tk

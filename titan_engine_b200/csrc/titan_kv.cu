@@ -73,6 +73,7 @@ const char* validate(const tk_kv_config& c) {
     if (c.chunk_tokens < 0 || c.chunk_tokens % c.page_size != 0) return "chunk_tokens must be a multiple of page_size";
     if (c.decode_impl < TK_DECODE_AUTO || c.decode_impl > TK_DECODE_MMA) return "bad decode_impl";
     if (c.merge_impl != TK_MERGE_IN_KERNEL && c.merge_impl != TK_MERGE_SEPARATE) return "bad merge_impl";
+    if (c.launch_overlap != TK_OVERLAP_AUTO && c.launch_overlap != TK_OVERLAP_OFF) return "bad launch_overlap";
     if (c.hot_window < 0 || c.cold_pages < 0) return "hot_window and cold_pages must not be negative";
     if (c.hot_window > 0) {
         if (c.hot_window < c.page_size) return "hot_window must cover at least one page";
@@ -104,6 +105,11 @@ struct tk_kv {
     int* d_counters = nullptr;           // [8 token groups][max_seqs * Hkv] arrival counters of the in-kernel merge
     int* d_pf_counters = nullptr;        // prefill kernel: one per (sequence, kv head, tile) group
     int max_pf_groups = 0, max_pf_items = 0;
+    // programmatic dependent launch of back-to-back attention kernels: the launch count right after the last
+    // attention launch, its layer and stream (another launch of this library in between breaks the chain)
+    int64_t chain_launches = -1;
+    int chain_layer = -1;
+    cudaStream_t chain_stream = nullptr;
     tk::PrefillDev pf_dev{};             // device view of the step's prefill work list
     tk::StepDev small_dev{};             // ... and of the decode-kernel share of such a step
 
@@ -850,9 +856,16 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
             if (h->mla_mma)
                 e = tk::launch_decode_mma_mla(h->geo, lp, &h->maps[layer], &h->maps_v[layer], h->dev, h->d_table, q,
                                               h->d_partials, h->d_status, s, &mo, &fa);
-            else
+            else {
+                // A launch of ANOTHER layer that directly follows an attention launch of this handle on the same
+                // stream may overlap that launch's tail: its page tiles belong to a pool the earlier kernel does
+                // not touch, and it waits for the earlier kernel before it writes split-KV rows or `out`.
+                const bool overlap = h->cfg.launch_overlap == TK_OVERLAP_AUTO && !cold && !timed &&
+                                     h->chain_launches == h->launches && h->chain_stream == s && h->chain_layer != layer;
                 e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], cold ? &h->stage_maps[slot] : nullptr, h->dev,
-                                          h->d_table, q, h->d_partials, h->d_status, s, &mo, &fa);
+                                          h->d_table, q, h->d_partials, h->d_status, s, &mo, &fa, overlap);
+                h->chain_launches = h->launches + 1; h->chain_layer = layer; h->chain_stream = s;
+            }
             h->launches++;
         }
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }

@@ -144,7 +144,8 @@ cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMa
 cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                               const CUtensorMap* map_cold, const StepDev& st, const int32_t* page_table, const void* q,
                               float* partials, int* status, cudaStream_t s,
-                              const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
+                              const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr,
+                              bool overlap_prev = false);   // launch may start while the stream's previous kernel drains
 
 // Several query tokens per sequence, causal among themselves (16-bit pools): 16/G tokens per pass over the
 // pages, up to 8 such token groups.  `mo.counters` needs n_groups * n_seqs * Hkv zeroed counters.

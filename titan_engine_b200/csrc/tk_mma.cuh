@@ -123,6 +123,14 @@ __device__ __forceinline__ uint32_t rope_pair(uint32_t w, const float2* __restri
     return pack2<BF16>(x0 * cs.x - x1 * cs.y, x0 * cs.y + x1 * cs.x);
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may
+// start while the kernel before it in the stream is still running, once every CTA of that kernel has
+// executed pdl_launch_dependents() or exited; it must call pdl_wait() - which returns when the earlier
+// kernel has finished and its writes are visible - before it touches anything that kernel reads or
+// writes.  Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // swizzled byte offset of 16-byte chunk `c` of row `r` inside a 32x128-byte box
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 
