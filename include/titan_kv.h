@@ -244,12 +244,13 @@ int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int
  * One process per GPU.  Every rank owns a mailbox in its device memory; tk_peer_export gives the
  * CUDA IPC handle of it, the ranks swap handles over whatever transport they have, and
  * tk_peer_connect maps the peers' mailboxes.  tk_peer_exchange_combine then is ONE kernel that
- * stores this rank's partial rows [n_rows][dv+2] into every peer's mailbox (plain NVLink peer
- * stores), publishes a flag per peer, waits - with a limit - for the peers' flags and writes the
- * log-sum-exp combine of all ranks' rows (rank order, same arithmetic as tk_combine_partials) to
- * out [n_rows][dv].  Calls of one tk_peer must be ordered on one stream and made by every rank
- * the same number of times.  A peer whose rows do not arrive within the limit (default 2 s)
- * leaves `out` unwritten and makes tk_peer_status return TK_TIMEOUT.  The reference runs on one
+ * stores this rank's partial rows [n_rows][dv+2] into every rank's mailbox (plain NVLink peer
+ * stores of 8-byte cells that carry the value and the exchange's epoch together, so no flag and no
+ * fence follows the rows), waits - with a limit - until the cells of every rank's rows show the epoch,
+ * and writes the log-sum-exp combine of all ranks' rows (rank order, same arithmetic as
+ * tk_combine_partials) to out [n_rows][dv].  Calls of one tk_peer must be ordered on one stream and made
+ * by every rank the same number of times.  A row for which some peer's cells do not arrive within the
+ * limit (default 2 s) stays unwritten and tk_peer_status returns TK_TIMEOUT.  The reference runs on one
  * GPU (src/memory/memory_manager.cpp:15) and has no counterpart. */
 typedef struct tk_peer tk_peer;
 #define TK_PEER_HANDLE_BYTES 64
@@ -264,10 +265,6 @@ void* tk_peer_mailbox(const tk_peer* p);
 size_t tk_peer_mailbox_bytes(const tk_peer* p);
 int tk_peer_connect_ptrs(tk_peer* p, void* const* mailboxes);
 int tk_peer_set_wait_limit_ms(tk_peer* p, int32_t ms);
-/* Rows are published in groups of `rows` rows, one flag each (0 = all rows as one group, the default).
- * tk_kv_decode_exchange publishes one group per (sequence, kv head), i.e. num_heads / num_kv_heads rows:
- * a rank that feeds the same exchange through tk_peer_send / tk_peer_recv_combine sets that value. */
-int tk_peer_set_group_rows(tk_peer* p, int32_t rows);
 int tk_peer_exchange_combine(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* out,
                              int32_t out_dtype, void* stream);
 /* The two halves as launches of their own (send early, combine later; also how ranks that share
@@ -278,8 +275,8 @@ int tk_peer_recv_combine(tk_peer* p, const float* partial, int32_t n_rows, int32
 int tk_peer_status(tk_peer* p, void* stream);
 /* Attention of one layer over the tokens of EVERY rank: out [n_seqs][H][v_head_dim] in the handle's io
  * dtype.  Where the step allows it this is ONE launch: the attention kernel's merging CTAs store their
- * rows into the peers' mailboxes, publish and await one flag per (sequence, kv head) and write the
- * combine.  Otherwise tk_kv_decode_partial followed by the exchange kernel, on the same flags. */
+ * rows into the peers' mailboxes, await the peers' rows of their (sequence, kv head) and write the
+ * combine.  Otherwise tk_kv_decode_partial followed by the exchange kernel, on the same mailbox cells. */
 int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer, void* out, void* stream);
 
 /* update + attention_decode of one layer with HOST buffers (pageable or pinned):
@@ -314,7 +311,7 @@ int tk_kv_profile_read_each(tk_kv* h, float* ms_out, int32_t cap, int32_t* launc
  * allocator).  No counterpart in the reference.  No handle, no workspace: the split-KV
  * scratch is one fixed 4 MiB array inside the library image (held by every GPU that loads
  * the library), so the call allocates nothing on the device and is refused — not truncated —
- * beyond n_seqs 256, 4096 (sequence, 256-token chunk, kv head) work items or 4 MiB of
+ * beyond n_seqs 256, 4096 (sequence, split-KV chunk, kv head) work items or 4 MiB of
  * partial rows.  All calls on a device share that array: calls whose kernels may overlap
  * race, keep them on one stream.  A device's first call looks the array's address up.  Every
  * call uploads its work list from host memory that lives only until the call returns, so a call
@@ -383,7 +380,7 @@ int tk_kv_selftest_set_status(tk_kv* h, int32_t value, void* stream);
  * tk_kv_arena_bytes), the page table, the split-KV workspace and the step metadata.  Drains `stream`,
  * compares them, and returns TK_CUDA_ERROR naming the buffer when any byte changed. */
 int tk_kv_check_canaries(tk_kv* h, void* stream);
-/* The same for an exchange mailbox (guard bytes behind the flags). */
+/* The same for an exchange mailbox (guard bytes behind its last slot). */
 int tk_peer_check_canaries(tk_peer* p, void* stream);
 
 /* Number of kernels this library has launched on this handle so far. */

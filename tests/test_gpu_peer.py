@@ -122,7 +122,7 @@ def D_ranges(n, world):
 @pytest.mark.parametrize("shape", [(32, 8, 128), (8, 8, 64), (16, 1, 128)])
 def test_attention_kernel_carries_the_exchange_and_meets_the_two_launch_route(shape):
     """Two ranks in this process, each with half of one sequence.  The rank that goes second runs
-    tk_kv_decode_exchange as ONE launch (its merging CTAs find the first rank's rows and flags already
+    tk_kv_decode_exchange as ONE launch (its merging CTAs find the first rank's rows already
     there); the rank that goes first feeds the same exchange with send / recv_combine.  Both must get
     the attention of the whole sequence, and the same bytes as each other."""
     H, Hkv, Dh = shape
@@ -132,7 +132,6 @@ def test_attention_kernel_carries_the_exchange_and_meets_the_two_launch_route(sh
     ranks = [D.PeerExchange(H, Dh + 2, rank=r, world=2, connect=False) for r in range(2)]
     for r in ranks:
         r.connect_local(ranks)
-        r.set_group_rows(H // Hkv)
         r.set_wait_limit_ms(200)
     for epoch in range(4):
         q = torch.randn(1, H, Dh, device=dev, generator=gen).to(torch.bfloat16)

@@ -97,7 +97,6 @@ SIGNATURES = {
     "tk_peer_mailbox_bytes": (C.c_size_t, [_P]),
     "tk_peer_connect_ptrs": (C.c_int, [_P, C.POINTER(C.c_void_p)]),
     "tk_peer_set_wait_limit_ms": (C.c_int, [_P, C.c_int32]),
-    "tk_peer_set_group_rows": (C.c_int, [_P, C.c_int32]),
     "tk_peer_exchange_combine": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),
     "tk_peer_send": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "tk_peer_recv_combine": (C.c_int, [_P, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]),

@@ -4,7 +4,7 @@
 // runs inside a serving loop which has handed all device memory to its own arena, a plugin
 // loaded into a process whose allocator is owned by someone else, or a caller that wants a
 // hard guarantee that a decode step never touches the driver's allocator.  For them
-// tk_paged_decode_static() runs the same split-KV decode + log-sum-exp combine as
+// tk_paged_decode_static() runs the same tensor-core split-KV decode + log-sum-exp combine as
 // tk_kv_decode(), but needs no handle and no workspace: the caller passes the pool, the
 // page table, the lengths, q and out, and the split-KV partials (plus the small work list)
 // live in ONE fixed array that is part of the library image.
@@ -15,8 +15,9 @@
 //   * every GPU that loads the library carries the array until the process exits;
 //   * all calls on a device share it: two calls whose kernels can overlap on the GPU (different
 //     streams, or different host threads) race on it.  Serialise them on one stream;
-//   * the array keeps whatever the previous call left.  Nothing in it has to start at zero:
-//     each call rewrites the work list and every partial row it later reads;
+//   * the array keeps whatever the previous call left.  Each call rewrites the work list and every
+//     partial row it later reads, and clears the one word that must start at zero (the status word a
+//     timed-out device wait sets) with a stream-ordered memset;
 //   * the device address of the array is looked up once per device, on that device's first
 //     call;
 //   * every call uploads its work list from host memory that lives only until the call returns,
@@ -25,6 +26,7 @@
 
 #include "tk_kernels.cuh"
 
+#include <algorithm>
 #include <cstdio>
 #include <mutex>
 #include <vector>
@@ -34,10 +36,10 @@ namespace {
 constexpr int kMaxSeqs = 256;
 constexpr int kMaxItems = 4096;
 constexpr size_t kMaxPartialFloats = (size_t)1 << 20;          // 4 MiB of (o, m, l) partial rows
-constexpr int kChunkTokens = 256;
 constexpr int kPage = 16;
 
 struct StaticScratch {
+    int32_t status[4];                                             // [0]: set when a bounded device wait gives up
     int32_t seq[kMaxSeqs];
     int32_t len[kMaxSeqs];
     int32_t chunk_base[kMaxSeqs + 4];
@@ -95,19 +97,26 @@ extern "C" int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t n
     if (cudaStreamIsCapturing(s, &capturing) != cudaSuccess || capturing != cudaStreamCaptureStatusNone)
         return refuse("the stream is being captured: this call uploads per-call host data and cannot be recorded");
 
-    // size check first, by arithmetic: nothing is built for a request that will be refused
-    int64_t total_chunks = 0;
+    // split-KV chunk: the largest of 2048 .. 256 tokens that still gives the GPU a few hundred work items
+    auto chunks_at = [&](int chunk) {
+        int64_t total = 0;
+        for (int b = 0; b < n_seqs; b++) total += ((int64_t)std::max(seq_lens_host[b], 0) + chunk - 1) / chunk;
+        return total;
+    };
     for (int b = 0; b < n_seqs; b++) {
         const int n = seq_lens_host[b];
         if (n < 0 || ((int64_t)n + kPage - 1) / kPage > max_pages_per_seq) return refuse("a sequence length does not fit its page-table row");
-        total_chunks += ((int64_t)n + kChunkTokens - 1) / kChunkTokens;
     }
+    int chunk_tokens = 2048;
+    while (chunk_tokens > 256 && chunks_at(chunk_tokens) * num_kv_heads < 592) chunk_tokens /= 2;
+    // size check first, by arithmetic: nothing is built for a request that will be refused
+    const int64_t total_chunks = chunks_at(chunk_tokens);
     if (total_chunks * num_kv_heads > kMaxItems)
         return refuse("too much work for the fixed scratch: more than 4096 (sequence, chunk, kv head) items");
     if ((size_t)total_chunks * num_heads * (head_dim + 2) > kMaxPartialFloats)
         return refuse("too much work for the fixed scratch: partial rows exceed 4 MiB (use tk_kv_decode with a handle)");
 
-    // work list: one item per (sequence, 256-token chunk, kv head), built on the host
+    // work list: one item per (sequence, chunk, kv head), built on the host
     std::vector<int32_t> seq(n_seqs), len(n_seqs), chunk_base(n_seqs + 1, 0);
     std::vector<int4> items;
     items.reserve((size_t)total_chunks * num_kv_heads);
@@ -115,7 +124,7 @@ extern "C" int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t n
         const int n = seq_lens_host[b];
         seq[b] = b;
         len[b] = n;
-        const int chunks = (n + kChunkTokens - 1) / kChunkTokens;
+        const int chunks = (n + chunk_tokens - 1) / chunk_tokens;
         chunk_base[b + 1] = chunk_base[b] + chunks;
         for (int c = 0; c < chunks; c++)
             for (int h = 0; h < num_kv_heads; h++) items.push_back(make_int4(b, c, h, 0));
@@ -138,12 +147,22 @@ extern "C" int tk_paged_decode_static(const void* pool, int32_t dtype, int32_t n
 
     tk::Geometry g{num_heads, num_kv_heads, head_dim, kPage, dtype, dtype, num_pages, n_seqs, max_pages_per_seq, head_dim};
     tk::LayerPtrs lp{const_cast<void*>(pool), nullptr, nullptr, nullptr};
+    // the pool as the TMA sees it: a descriptor built on the host and passed by value, nothing on the device
+    CUtensorMap map;
+    if ((e = tk::make_pool_tensor_map(g, const_cast<void*>(pool), &map)) != cudaSuccess ||
+        (e = cudaMemsetAsync(sc->status, 0, sizeof(sc->status), s)) != cudaSuccess) {
+        fprintf(stderr, "[titan-kv] tk_paged_decode_static: set-up: %s\n", cudaGetErrorString(e));
+        return TK_CUDA_ERROR;
+    }
     tk::StepDev st{};
     st.seq = sc->seq; st.len = sc->len; st.chunk_base = sc->chunk_base;
     st.items = sc->items;
-    st.n_seqs = n_seqs; st.n_items = (int)items.size(); st.chunk_tokens = kChunkTokens;
-    if ((e = tk::launch_decode_simt(g, lp, st, page_table, q, sc->partials, s)) != cudaSuccess ||
-        (e = tk::launch_combine_step(g, st, sc->partials, out, dtype, nullptr, s)) != cudaSuccess) {
+    st.n_seqs = n_seqs; st.n_items = (int)items.size(); st.chunk_tokens = chunk_tokens;
+    // the tensor-core decode kernel leaves (o, m, l) rows; the combine launch merges them and writes nothing
+    // if a bounded wait inside the kernel gave up
+    if ((st.n_items > 0 &&
+         (e = tk::launch_decode_mma(g, lp, &map, nullptr, st, page_table, q, sc->partials, sc->status, s)) != cudaSuccess) ||
+        (e = tk::launch_combine_step(g, st, sc->partials, out, dtype, nullptr, s, sc->status)) != cudaSuccess) {
         fprintf(stderr, "[titan-kv] tk_paged_decode_static: launch: %s\n", cudaGetErrorString(e));
         return TK_CUDA_ERROR;
     }

@@ -4,20 +4,21 @@
 // A sequence whose tokens are spread over several GPUs needs, per layer, every rank's merged
 // (o, m, l) rows on every rank.  Instead of a library all-gather followed by a combine launch,
 // ONE kernel per rank stores its rows straight into a mailbox in every peer's memory (plain
-// peer stores), publishes a flag per peer, waits (bounded) for the peers' flags in its own
+// peer stores), waits (bounded) for the peers' rows in its own
 // mailbox and combines what arrived.  The reference is single-GPU (GPU 0 only:
 // src/memory/memory_manager.cpp:15) and has no counterpart.
 //
 // Mailbox of a rank (device memory of that rank):
-//   payload[2 parities][world sources][max_rows * row_floats] float   (slots 256-byte aligned)
-//   flags  [2 parities][world sources][max_rows] uint32; value = epoch of that source's rows of one group
-// The epoch counts exchanges (1, 2, ...), parity = epoch & 1.  Two parities are enough: a rank can
-// only start sending epoch e+2 after it finished e+1, which needed every peer's e+1 flag, which a
-// peer sends only after its own epoch-e kernel (the reader of that parity) has finished.
+//   cells[2 parities][world sources][max_rows * row_floats], 8 bytes each: (float bits, epoch)
+// A cell is stored and loaded as one 64-bit atom, so a receiver that finds the epoch it waits for has the
+// value of that epoch with it: it polls the data itself, and a sender needs neither a flag nor a fence
+// behind its rows.  The epoch counts exchanges (1, 2, ...), parity = epoch & 1.  Two parities are enough:
+// a rank can only start sending epoch e+2 after it finished e+1, which needed every peer's e+1 rows,
+// which a peer sends only after its own epoch-e kernel (the reader of that parity) has finished.
 // The epoch lives in device memory and is advanced by the kernel itself (by the CTA that leaves
 // last), so a launch carries no per-call host state.
 //
-// No multicast, no multimem: plain stores and loads, system-scope release/acquire on the flags.
+// No multicast, no multimem: plain 64-bit stores and loads at system scope.
 #include "../../include/titan_kv.h"
 #include "tk_kernels.cuh"
 #include "tk_merge.cuh"
@@ -34,15 +35,13 @@ constexpr int kMaxWorld = tk::kPeerMaxWorld;
 constexpr size_t kCanaryBytes = 4096;      // guard bytes behind the mailbox (tk_peer_check_canaries)
 constexpr int kCanaryByte = 0xA5;
 
-// mode bit 0: send this rank's rows to every peer and publish the flags;
-// mode bit 1: wait for the peers' rows and combine.  Both: one launch does the whole exchange.
-// Rows are published in groups of group_rows rows (one flag per group), the granularity at which the
-// attention kernels publish when they carry the exchange themselves.
+// mode bit 0: send this rank's rows to every rank's mailbox (its own included);
+// mode bit 1: wait for every rank's rows and combine.  Both: one launch does the whole exchange.
 __global__ void __launch_bounds__(512)
 peer_exchange_combine_kernel(const PeerCtx* __restrict__ ctx_p, const float* __restrict__ partial, int n_rows, int dv,
-                             int group_rows, void* __restrict__ out, int out_dtype, int mode) {
+                             void* __restrict__ out, int out_dtype, int mode) {
     const PeerCtx& c = *ctx_p;
-    const int rank = c.rank, world = c.world;
+    const int world = c.world;
     const uint32_t epoch = __ldcg(c.epoch) + ((mode & 1) ? 1u : 0u);   // a send opens the next exchange
     // called by the whole CTA on every way out: the last CTA to leave stores the epoch for the next
     // launch (by then every CTA of this launch has read the old value)
@@ -55,62 +54,49 @@ peer_exchange_combine_kernel(const PeerCtx* __restrict__ ctx_p, const float* __r
     };
     const int parity = (int)(epoch & 1u);
     const int row_floats = dv + 2;
-    const int n_groups = (n_rows + group_rows - 1) / group_rows;
-    __shared__ int s_flag;
 
     if (mode & 1) {
         const size_t n2 = (size_t)n_rows * row_floats / 2;                 // row_floats is even
         const float2* src = reinterpret_cast<const float2*>(partial);
         for (int p = 0; p < world; p++) {
-            if (p == rank) continue;
-            float2* dst = reinterpret_cast<float2*>(tk::peer_rows(c, p, parity, rank));
-            for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n2; i += (size_t)gridDim.x * blockDim.x)
-                dst[i] = src[i];
-        }
-        __threadfence_system();                                            // this thread's rows are out ...
-        if (threadIdx.x == 0) s_flag = 0;
-        __syncthreads();
-        if (threadIdx.x == 0 && atomicAdd(c.tickets, 1u) == gridDim.x - 1) {   // ... and so are every CTA's
-            atomicExch(c.tickets, 0u);
-            __threadfence_system();
-            s_flag = 1;
-        }
-        __syncthreads();
-        if (s_flag)
-            for (int i = threadIdx.x; i < world * n_groups; i += blockDim.x) {
-                const int p = i / n_groups, g = i % n_groups;
-                if (p != rank) tk::st_release_sys(tk::peer_flag(c, p, parity, rank, g), epoch);
+            uint64_t* dst = tk::peer_cells(c, p, parity, c.rank);
+            for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n2; i += (size_t)gridDim.x * blockDim.x) {
+                const float2 v = src[i];
+                tk::st_cells2(dst + 2 * i, tk::make_cell(v.x, epoch), tk::make_cell(v.y, epoch));
             }
+        }
     }
     if (!(mode & 2)) { leave(); return; }
 
-    bool ok = true;
-    for (int i = threadIdx.x; i < world * n_groups; i += blockDim.x) {
-        const int src = i / n_groups, g = i % n_groups;
-        if (src != rank && ok) ok = tk::peer_wait_flag(tk::peer_flag(c, rank, parity, src, g), epoch, c.limit_ns);
-    }
-    if (!__syncthreads_and(ok)) {                                          // give up: a peer never published
-        if (threadIdx.x == 0) atomicExch(c.status, (int)TK_TIMEOUT);
-        leave();
-        return;
-    }
-
-    // log-sum-exp combine over the sources in rank order (own rows from `partial`, the others from
-    // the mailbox, read past L1): same arithmetic as the combine of stacked partials
+    // one warp per row: poll the row's cells of every source (they carry the epoch), then the
+    // log-sum-exp combine over the sources in rank order: same arithmetic as the combine of stacked partials.
+    // A row some source never sent stays unwritten and the status word says TK_TIMEOUT.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const size_t src_stride_pairs = c.slot_bytes / 16;
+    auto cell = [](const uint64_t* p) { return tk::cell_value(__ldcg(reinterpret_cast<const unsigned long long*>(p))); };
     for (int row = blockIdx.x * n_warps + warp; row < n_rows; row += gridDim.x * n_warps) {
-        const float* src[kMaxWorld];
+        const uint64_t* base = tk::peer_cells(c, c.rank, parity, 0) + (size_t)row * row_floats;
+        bool ok = true;
+        for (int pi = lane; pi < row_floats / 2 && ok; pi += 32)
+            for (int s0 = 0; s0 < world && ok; s0 += 8)
+                ok = tk::peer_wait_pairs(base + (size_t)s0 * 2 * src_stride_pairs + 2 * pi, src_stride_pairs,
+                                         min(8, world - s0), epoch, c.limit_ns);
+        if (!__all_sync(0xFFFFFFFFu, ok)) {
+            if (lane == 0) atomicExch(c.status, (int)TK_TIMEOUT);
+            continue;
+        }
+        const uint64_t* src[kMaxWorld];
 #pragma unroll
         for (int r = 0; r < kMaxWorld; r++)
-            if (r < world) src[r] = (r == rank ? partial : tk::peer_rows(c, rank, parity, r)) + (size_t)row * row_floats;
+            if (r < world) src[r] = tk::peer_cells(c, c.rank, parity, r) + (size_t)row * row_floats;
         float M = -1e30f;
-        for (int r = 0; r < world; r++) M = fmaxf(M, __ldcg(src[r] + dv));
+        for (int r = 0; r < world; r++) M = fmaxf(M, cell(src[r] + dv));
         float L = 0.0f;
-        for (int r = 0; r < world; r++) L += __ldcg(src[r] + dv + 1) * expf(__ldcg(src[r] + dv) - M);
+        for (int r = 0; r < world; r++) L += cell(src[r] + dv + 1) * expf(cell(src[r] + dv) - M);
         const float inv = 1.0f / (L + 1e-8f);
         for (int d = lane; d < dv; d += 32) {
             float acc = 0.0f;
-            for (int r = 0; r < world; r++) acc += __ldcg(src[r] + d) * expf(__ldcg(src[r] + dv) - M);
+            for (int r = 0; r < world; r++) acc += cell(src[r] + d) * expf(cell(src[r] + dv) - M);
             tk::store_out(out, (size_t)row * dv + d, acc * inv, out_dtype);
         }
     }
@@ -121,13 +107,12 @@ peer_exchange_combine_kernel(const PeerCtx* __restrict__ ctx_p, const float* __r
 
 struct tk_peer {
     int rank = 0, world = 1, max_rows = 0, row_floats = 0, device = 0;
-    size_t slot_bytes = 0, flags_off = 0, total = 0;
+    size_t slot_bytes = 0, total = 0;
     uint8_t* local = nullptr;
     uint8_t* peers[kMaxWorld] = {};
     bool opened[kMaxWorld] = {};           // mapped through CUDA IPC (to be closed)
     bool connected = false;
     bool sent_once = false;
-    int group_rows = 0;                    // rows per published group for the plain entry points; 0 = all rows
     uint32_t* d_epoch = nullptr;
     unsigned* d_ticket = nullptr;          // three counters
     tk::PeerCtx* d_ctx = nullptr;          // device copy of the context, written at connect
@@ -144,7 +129,7 @@ cudaError_t upload_ctx(tk_peer* p) {
     tk::PeerCtx c{};
     for (int r = 0; r < kMaxWorld; r++) c.box[r] = r < p->world ? p->peers[r] : nullptr;
     c.rank = p->rank; c.world = p->world; c.max_rows = p->max_rows; c.row_floats = p->row_floats;
-    c.slot_bytes = p->slot_bytes; c.flags_off = p->flags_off;
+    c.slot_bytes = p->slot_bytes;
     c.epoch = p->d_epoch; c.tickets = p->d_ticket; c.status = p->d_status; c.limit_ns = p->limit_ns;
     cudaError_t e = cudaSetDevice(p->device);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();      // no kernel may be reading the old copy
@@ -173,9 +158,8 @@ int tk_peer_create(int32_t rank, int32_t world, int32_t max_rows, int32_t row_fl
     p->rank = rank; p->world = world; p->max_rows = max_rows; p->row_floats = row_floats;
     if (device < 0 && cudaGetDevice(&device) != cudaSuccess) { delete p; return TK_CUDA_ERROR; }
     p->device = device;
-    p->slot_bytes = ((size_t)max_rows * row_floats * sizeof(float) + 255) / 256 * 256;
-    p->flags_off = 2 * p->slot_bytes * world;
-    p->total = p->flags_off + 2 * (size_t)world * max_rows * sizeof(uint32_t);
+    p->slot_bytes = ((size_t)max_rows * row_floats * sizeof(uint64_t) + 255) / 256 * 256;    // 8-byte cells
+    p->total = 2 * p->slot_bytes * world;
     cudaDeviceProp prop;
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete p; return TK_CUDA_ERROR; }
     p->num_sms = prop.multiProcessorCount;
@@ -271,12 +255,6 @@ int tk_peer_connect_ptrs(tk_peer* p, void* const* mailboxes) {
     return TK_OK;
 }
 
-int tk_peer_set_group_rows(tk_peer* p, int32_t rows) {
-    if (!p || rows < 0) return TK_INVALID_ARG;
-    p->group_rows = rows;
-    return TK_OK;
-}
-
 int tk_peer_set_wait_limit_ms(tk_peer* p, int32_t ms) {
     if (!p || ms <= 0) return TK_INVALID_ARG;
     p->limit_ns = (unsigned long long)ms * 1000000ull;
@@ -288,10 +266,8 @@ int tk_peer_set_wait_limit_ms(tk_peer* p, int32_t ms) {
 }
 
 static int peer_launch(tk_peer* p, const float* partial, int32_t n_rows, int32_t dv, void* out, int32_t out_dtype,
-                       void* stream, int mode, int group_rows = 0) {
-    if (!p || n_rows < 0 || dv <= 0 || group_rows < 0) return TK_INVALID_ARG;
-    if (group_rows == 0) group_rows = p ? p->group_rows : 0;
-    if (group_rows == 0) group_rows = n_rows > 0 ? n_rows : 1;   // one group: one flag per source
+                       void* stream, int mode) {
+    if (!p || n_rows < 0 || dv <= 0) return TK_INVALID_ARG;
     if (!p->connected) return pfail(p, TK_INVALID_ARG, "peers are not connected");
     if (dv + 2 != p->row_floats || n_rows > p->max_rows) return pfail(p, TK_INVALID_ARG, "rows do not fit the mailbox");
     if ((mode & 1) && !partial) return pfail(p, TK_INVALID_ARG, "null partial");
@@ -301,10 +277,10 @@ static int peer_launch(tk_peer* p, const float* partial, int32_t n_rows, int32_t
     if (!p->sent_once) return pfail(p, TK_INVALID_ARG, "recv_combine before any send");
     const size_t work = (size_t)n_rows * p->row_floats / 2;
     int grid = (int)((work + 4095) / 4096);
+    if ((mode & 2) && grid < (n_rows + 15) / 16) grid = (n_rows + 15) / 16;      // combine: one warp per row
     if (grid < 1) grid = 1;
     if (grid > p->num_sms) grid = p->num_sms;
-    peer_exchange_combine_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(p->d_ctx, partial, n_rows, dv, group_rows, out,
-                                                                         out_dtype, mode);
+    peer_exchange_combine_kernel<<<grid, 512, 0, (cudaStream_t)stream>>>(p->d_ctx, partial, n_rows, dv, out, out_dtype, mode);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return pfail(p, TK_CUDA_ERROR, "exchange launch", e);
     return TK_OK;
@@ -354,9 +330,8 @@ namespace tk {
 const PeerCtx* peer_device_ctx(const tk_peer* p) { return p && p->connected ? p->d_ctx : nullptr; }
 int peer_max_rows(const tk_peer* p) { return p ? p->max_rows : 0; }
 int peer_row_floats(const tk_peer* p) { return p ? p->row_floats : 0; }
-int peer_exchange_grouped(tk_peer* p, const float* partial, int n_rows, int dv, int group_rows, void* out, int out_dtype,
-                          void* stream) {
-    return peer_launch(p, partial, n_rows, dv, out, out_dtype, stream, 3, group_rows);
+int peer_exchange(tk_peer* p, const float* partial, int n_rows, int dv, void* out, int out_dtype, void* stream) {
+    return peer_launch(p, partial, n_rows, dv, out, out_dtype, stream, 3);
 }
 // An attention launch that carries the exchange itself counts as this exchange's send.
 void peer_note_fused_send(tk_peer* p) { if (p) p->sent_once = true; }

@@ -1044,16 +1044,16 @@ int tk_kv_append_decode_multi(tk_kv* h, int32_t layer, const void* k, const void
 
 // Attention over a sequence whose tokens are spread over the ranks of `peer`.  One launch where the
 // step allows it: the attention kernel's merging CTAs store their merged rows into every rank's
-// mailbox, publish and await one flag per (sequence, kv head) and write the combine themselves.
-// Otherwise two launches: this rank's merged rows, then the exchange kernel, publishing the same
-// flags - so ranks that take different routes for the same layer still meet.
+// mailbox, await every rank's rows of their (sequence, kv head) and write the combine themselves.
+// Otherwise two launches: this rank's merged rows, then the exchange kernel, which fills and reads the
+// same cells - so ranks that take different routes for the same layer still meet.
 int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer, void* out, void* stream) {
     if (!h || !peer || !out) return TK_INVALID_ARG;
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode_exchange: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode_exchange: no step in progress (call tk_kv_step_begin)");
     const tk::PeerCtx* ctx = tk::peer_device_ctx(peer);
     if (!ctx) return fail(h, TK_INVALID_ARG, "decode_exchange: peers are not connected");
-    const int n_rows = h->dev.n_seqs * h->geo.H, dv = h->cfg.v_head_dim, G = h->geo.H / h->geo.Hkv;
+    const int n_rows = h->dev.n_seqs * h->geo.H, dv = h->cfg.v_head_dim;
     if (tk::peer_row_floats(peer) != dv + 2 || n_rows > tk::peer_max_rows(peer))
         return fail(h, TK_INVALID_ARG, "decode_exchange: %d rows of %d floats do not fit the mailbox", n_rows, dv + 2);
     if (h->dev.n_seqs == 0) return TK_OK;
@@ -1073,7 +1073,7 @@ int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer,
     }
     int st = decode_impl(h, layer, q, nullptr, h->d_xpartial, (cudaStream_t)stream);
     if (st != TK_OK) return st;
-    st = tk::peer_exchange_grouped(peer, h->d_xpartial, n_rows, dv, G, out, h->cfg.io_dtype, stream);
+    st = tk::peer_exchange(peer, h->d_xpartial, n_rows, dv, out, h->cfg.io_dtype, stream);
     h->launches++;
     if (st != TK_OK) return fail(h, st, "decode_exchange: %s", tk_peer_last_error(peer));
     return TK_OK;

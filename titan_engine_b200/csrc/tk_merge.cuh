@@ -88,12 +88,12 @@ __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo
                     if (e < epl) acc[e] += x[u][e] * w;
             }
         }
-        if (pc) {                                      // this rank's merged row goes to every rank's mailbox
+        if (pc) {                                      // this rank's merged row goes to every rank's mailbox (its own too)
             for (int p = 0; p < pc->world; p++) {
-                float* row = peer_rows(*pc, p, parity, pc->rank) + partial_off(b, h, g.H, D);
-                reinterpret_cast<float2*>(row)[lane * (epl / 2)] = make_float2(acc[0], acc[1]);
-                if (epl == 4) reinterpret_cast<float2*>(row)[lane * 2 + 1] = make_float2(acc[2], acc[3]);
-                if (lane == 0) *reinterpret_cast<float2*>(row + D) = make_float2(M, L);
+                uint64_t* row = peer_cells(*pc, p, parity, pc->rank) + partial_off(b, h, g.H, D);
+                st_cells2(row + lane * epl, make_cell(acc[0], epoch), make_cell(acc[1], epoch));
+                if (epl == 4) st_cells2(row + lane * 4 + 2, make_cell(acc[2], epoch), make_cell(acc[3], epoch));
+                if (lane == 0) st_cells2(row + D, make_cell(M, epoch), make_cell(L, epoch));
             }
             continue;
         }
@@ -112,36 +112,43 @@ __device__ __forceinline__ void merge_rows(const Geometry& g, const MergeOut& mo
     }
     if (!pc) return;
 
-    // publish this (sequence, kv head) group to every peer, wait for theirs, combine in rank order
+    // Wait for every rank's rows of this (sequence, kv head) group by polling the cells themselves - each
+    // carries the epoch next to its value, so there is no flag and no fence behind the rows - then combine
+    // in rank order.  A rank whose rows do not arrive within the limit: report, leave `out` alone.
     const PeerCtx& c = *pc;
-    const int group = b * g.Hkv + kvh;
-    __threadfence_system();
-    __syncthreads();
+    const size_t src_stride_pairs = c.slot_bytes / 16;             // cell pairs between the slots of two sources
     bool ok = true;
-    if ((int)threadIdx.x < c.world && (int)threadIdx.x != c.rank) {
-        st_release_sys(peer_flag(c, threadIdx.x, parity, c.rank, group), epoch);
-        ok = peer_wait_flag(peer_flag(c, c.rank, parity, threadIdx.x, group), epoch, c.limit_ns);
+    for (int gq = warp; gq < G && ok; gq += n_warps) {
+        const uint64_t* base = peer_cells(c, c.rank, parity, 0) + partial_off(b, kvh * G + gq, g.H, D);
+        for (int s0 = 0; s0 < c.world && ok; s0 += 8) {            // eight sources' loads in flight at a time
+            const int n = min(8, c.world - s0);
+            const uint64_t* p0 = base + (size_t)s0 * 2 * src_stride_pairs;
+            ok = peer_wait_pairs(p0 + lane * epl, src_stride_pairs, n, epoch, c.limit_ns);
+            if (ok && epl == 4) ok = peer_wait_pairs(p0 + lane * 4 + 2, src_stride_pairs, n, epoch, c.limit_ns);
+            if (ok && lane == 0) ok = peer_wait_pairs(p0 + D, src_stride_pairs, n, epoch, c.limit_ns);
+        }
     }
-    if (!__syncthreads_and(ok)) {                      // a peer never published: report, leave `out` alone
+    if (!__syncthreads_and(ok)) {
         if (threadIdx.x == 0) atomicExch(c.status, 4 /* TK_TIMEOUT */);
         return;
     }
+    auto cell = [](const uint64_t* p) { return cell_value(__ldcg(reinterpret_cast<const unsigned long long*>(p))); };
     for (int gq = warp; gq < G; gq += n_warps) {
         const int h = kvh * G + gq;
         const size_t off = partial_off(b, h, g.H, D);
         float M = -1e30f;
-        for (int r = 0; r < c.world; r++) M = fmaxf(M, __ldcg(peer_rows(c, c.rank, parity, r) + off + D));
+        for (int r = 0; r < c.world; r++) M = fmaxf(M, cell(peer_cells(c, c.rank, parity, r) + off + D));
         float L = 0.0f;
         for (int r = 0; r < c.world; r++) {
-            const float* row = peer_rows(c, c.rank, parity, r) + off;
-            L += __ldcg(row + D + 1) * expf(__ldcg(row + D) - M);
+            const uint64_t* row = peer_cells(c, c.rank, parity, r) + off;
+            L += cell(row + D + 1) * expf(cell(row + D) - M);
         }
         const float inv = 1.0f / (L + 1e-8f);
         for (int d = lane; d < D; d += 32) {
             float acc = 0.0f;
             for (int r = 0; r < c.world; r++) {
-                const float* row = peer_rows(c, c.rank, parity, r) + off;
-                acc += __ldcg(row + d) * expf(__ldcg(row + D) - M);
+                const uint64_t* row = peer_cells(c, c.rank, parity, r) + off;
+                acc += cell(row + d) * expf(cell(row + D) - M);
             }
             store_out(mo.out, ((size_t)b * g.H + h) * D + d, acc * inv, mo.out_dtype);
         }

@@ -174,10 +174,6 @@ class PeerExchange:
     def set_wait_limit_ms(self, ms: int) -> None:
         self._check(self._lib.tk_peer_set_wait_limit_ms(self._h, ms))
 
-    def set_group_rows(self, rows: int) -> None:
-        """Rows per published group for send / recv_combine / exchange_combine (0 = all rows, one flag)."""
-        self._check(self._lib.tk_peer_set_group_rows(self._h, rows))
-
     def _code(self, dtype: torch.dtype) -> int:
         L = self._L
         return {torch.float32: L.TK_FP32, torch.float16: L.TK_FP16, torch.bfloat16: L.TK_BF16}[dtype]
