@@ -132,36 +132,40 @@ __device__ __forceinline__ uint32_t quant2(uint32_t w, float inv_scale) {
     return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
 }
 
-// One warp per tile, the tile held in registers (up to 32*VPL vectors of 16 bytes: page 16 x D 128
-// is 256 vectors), one read of the rows, no shared memory; 8 tiles per CTA.
-template <bool BF16, int VPL>
-__global__ void __launch_bounds__(256, VPL <= 8 ? 3 : 2)
+// One warp per tile, the tile held in registers, one read of the rows, no shared memory; 8 tiles per CTA.
+// D (row width) and the page size of 16 are compile-time constants: every index below is a shift or a
+// mask, which matters - the kernel issues a few hundred instructions per tile and is bound by issue slots,
+// not by HBM, when the addressing costs integer divisions.
+template <bool BF16, int D>
+__global__ void __launch_bounds__(256, 3)
 seal_warp_kernel(Geometry g, LayerPtrs lp, StepDev st, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v) {
+    constexpr int PS = 16;
+    constexpr int VPR = D / 8;                  // 16-byte vectors per row
+    constexpr int N_VEC = PS * VPR;             // vectors per tile
+    constexpr int VPL = N_VEC / 32;             // vectors per lane: 8 (D = 128) or 4 (D = 64)
+    constexpr int RPI = 32 / VPR;               // rows one warp-wide load covers: 2 or 4
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_seal = g.Hkv * 2;
     const long long tile = (long long)blockIdx.x * 8 + warp;
     if (tile >= (long long)st.n_seals * per_seal) return;
-    const int4 it = st.seals[tile / per_seal];
-    const int rem = (int)(tile % per_seal);
+    const int seal = (int)(tile / per_seal);
+    const int rem = (int)(tile - (long long)seal * per_seal);
+    const int4 it = st.seals[seal];
     const int seq = it.x, page = it.y, n_old = it.z, tok0 = it.w;
     const int kvh = rem >> 1, kv = rem & 1;
-    const int vec_per_row = g.D / 8;
-    const int n_vec = g.ps * vec_per_row;
-    const uint16_t* open = (const uint16_t*)lp.open_pages + tile_off(seq, kvh, kv, g.Hkv, g.ps, g.D);
-    const uint16_t* in = (kv ? v : k) + ((ptrdiff_t)(tok0 - n_old) * g.Hkv + kvh) * g.D;   // + r * Hkv * D for row r >= n_old
+    const int r_lane = lane / VPR, c = lane % VPR;          // this lane's row within a load, its vector within the row
+    const uint16_t* open = (const uint16_t*)lp.open_pages + tile_off(seq, kvh, kv, g.Hkv, PS, D) + c * 8;
+    const size_t in_stride = (size_t)g.Hkv * D;             // elements between two tokens' rows of the input
+    const uint16_t* in = (kv ? v : k) + ((ptrdiff_t)(tok0 - n_old) * g.Hkv + kvh) * D + c * 8;
 
     uint4 raw[VPL];
-    uint32_t mx = 0u;
 #pragma unroll
     for (int u = 0; u < VPL; u++) {
-        const int i = lane + 32 * u;
-        raw[u] = make_uint4(0, 0, 0, 0);
-        if (i < n_vec) {
-            const int r = i / vec_per_row, c = i % vec_per_row;
-            const uint16_t* src = r < n_old ? open + (size_t)r * g.D : in + (size_t)r * g.Hkv * g.D;
-            raw[u] = *reinterpret_cast<const uint4*>(src + c * 8);
-        }
+        const int r = r_lane + RPI * u;
+        const uint16_t* src = r < n_old ? open + (size_t)r * D : in + (size_t)r * in_stride;
+        raw[u] = *reinterpret_cast<const uint4*>(src);
     }
+    uint32_t mx = 0u;
 #pragma unroll
     for (int u = 0; u < VPL; u++) {
         mx = max16x2<BF16>(mx, abs16x2<BF16>(raw[u].x));
@@ -178,16 +182,14 @@ seal_warp_kernel(Geometry g, LayerPtrs lp, StepDev st, const uint16_t* __restric
     const float inv_scale = __fdiv_rn(1.0f, scale);
     if (lane == 0) lp.scales[((size_t)page * g.Hkv + kvh) * 2 + kv] = scale;
 
-    uint8_t* codes = (uint8_t*)lp.pool + tile_off(page, kvh, kv, g.Hkv, g.ps, g.D);
+    // vector i = lane + 32 u of the tile (row r, vector c of the row) is 8 codes at byte 8 i
+    uint8_t* codes = (uint8_t*)lp.pool + tile_off(page, kvh, kv, g.Hkv, PS, D) + (size_t)lane * 8;
 #pragma unroll
     for (int u = 0; u < VPL; u++) {
-        const int i = lane + 32 * u;
-        if (i < n_vec) {
-            uint2 out;
-            out.x = quant2<BF16>(raw[u].x, inv_scale) | (quant2<BF16>(raw[u].y, inv_scale) << 16);
-            out.y = quant2<BF16>(raw[u].z, inv_scale) | (quant2<BF16>(raw[u].w, inv_scale) << 16);
-            *reinterpret_cast<uint2*>(codes + (size_t)i * 8) = out;
-        }
+        uint2 out;
+        out.x = quant2<BF16>(raw[u].x, inv_scale) | (quant2<BF16>(raw[u].y, inv_scale) << 16);
+        out.y = quant2<BF16>(raw[u].z, inv_scale) | (quant2<BF16>(raw[u].w, inv_scale) << 16);
+        *reinterpret_cast<uint2*>(codes + (size_t)u * 256) = out;
     }
 }
 
@@ -240,12 +242,11 @@ seal_kernel(Geometry g, LayerPtrs lp, StepDev st, const uint16_t* __restrict__ k
 template <bool BF16>
 cudaError_t launch_seal(const Geometry& g, const LayerPtrs& lp, const StepDev& st, const uint16_t* k,
                         const uint16_t* v, cudaStream_t s) {
-    const int n_vec = g.ps * (g.D / 8);
     const long long tiles = (long long)st.n_seals * g.Hkv * 2;
     const unsigned grid = (unsigned)((tiles + 7) / 8);
-    if (n_vec <= 256)      seal_warp_kernel<BF16, 8><<<grid, 256, 0, s>>>(g, lp, st, k, v);
-    else if (n_vec <= 512) seal_warp_kernel<BF16, 16><<<grid, 256, 0, s>>>(g, lp, st, k, v);
-    else                   seal_kernel<BF16><<<dim3(st.n_seals, g.Hkv * 2), 256, 0, s>>>(g, lp, st, k, v);
+    if (g.ps == 16 && g.D == 128)     seal_warp_kernel<BF16, 128><<<grid, 256, 0, s>>>(g, lp, st, k, v);
+    else if (g.ps == 16 && g.D == 64) seal_warp_kernel<BF16, 64><<<grid, 256, 0, s>>>(g, lp, st, k, v);
+    else                              seal_kernel<BF16><<<dim3(st.n_seals, g.Hkv * 2), 256, 0, s>>>(g, lp, st, k, v);
     return cudaGetLastError();
 }
 

@@ -244,6 +244,9 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         }
     }
 
+    // every page tile has been fetched and used: a launch of another layer may start (see decode_mma.cu)
+    pdl_launch_dependents();
+
     // ---- merge the 4 warps through shared memory (stage memory is idle now) ----------
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
     __syncthreads();
@@ -258,6 +261,7 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
         if (j == 0) { red_at(warp, gr, kDv) = m0; red_at(warp, gr, kDv + 1) = l0; }
     }
     __syncthreads();
+    pdl_wait();                                             // split-KV rows, counters and `out` are shared with the launch before
     const int prow = st.chunk_base[b] + chunk;
     const int heads_per_row = MULTI ? g.H * st.nq_max : g.H;   // columns of a partial row
     for (int idx = threadIdx.x; idx < rows * (kDv + 2); idx += blockDim.x) {
@@ -332,7 +336,7 @@ cudaError_t make_mla_tensor_maps(const Geometry& g, void* layer_pool, CUtensorMa
 template <bool BF, bool MULTI>
 static cudaError_t launch_mla_cfg(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map, const CUtensorMap* v_map,
                                   const StepDev& st, const int32_t* page_table, const void* q, float* partials, int* status,
-                                  cudaStream_t s, const MergeOut& mo, const FuseAppend& fa) {
+                                  cudaStream_t s, const MergeOut& mo, const FuseAppend& fa, bool overlap_prev = false) {
     static bool attr_done[64] = {};                         // per instantiation and device
     int dev = 0;
     cudaGetDevice(&dev);
@@ -343,9 +347,19 @@ static cudaError_t launch_mla_cfg(const Geometry& g, const LayerPtrs& lp, const 
     }
     const int tpg = 8 / (g.H / g.Hkv);                      // multi-token attention: tokens per pass
     const dim3 grid(st.n_items, MULTI ? (st.nq_max + tpg - 1) / tpg : 1);
-    decode_mma_mla_kernel<BF, MULTI><<<grid, kWarps * 32, kMlaSmem, s>>>(*k_map, *v_map, g, lp, st, page_table,
-                                                                         (const uint16_t*)q, partials, status, mo, fa);
-    return cudaGetLastError();
+    if (!overlap_prev) {
+        decode_mma_mla_kernel<BF, MULTI><<<grid, kWarps * 32, kMlaSmem, s>>>(*k_map, *v_map, g, lp, st, page_table,
+                                                                             (const uint16_t*)q, partials, status, mo, fa);
+        return cudaGetLastError();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kWarps * 32); cfg.dynamicSmemBytes = kMlaSmem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, decode_mma_mla_kernel<BF, MULTI>, *k_map, *v_map, g, lp, st, page_table,
+                              (const uint16_t*)q, partials, status, mo, fa);
 }
 
 bool decode_mma_mla_multi_supported(const Geometry& g, int nq_max) {
@@ -368,13 +382,13 @@ cudaError_t launch_decode_mma_mla_multi(const Geometry& g, const LayerPtrs& lp, 
 cudaError_t launch_decode_mma_mla(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map,
                                   const CUtensorMap* v_map, const StepDev& st, const int32_t* page_table,
                                   const void* q, float* partials, int* status, cudaStream_t s,
-                                  const MergeOut* merge, const FuseAppend* fuse) {
+                                  const MergeOut* merge, const FuseAppend* fuse, bool overlap_prev) {
     if (st.n_items <= 0) return cudaSuccess;
     if (!decode_mma_mla_supported(g) || st.chunk_tokens > kPage * kWarps * 32) return cudaErrorNotSupported;
     const MergeOut mo = merge ? *merge : MergeOut{nullptr, nullptr, nullptr, 0};
     const FuseAppend fa = fuse ? *fuse : FuseAppend{nullptr, nullptr, nullptr};
-    return g.dtype == DT_BF16 ? launch_mla_cfg<true, false>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa)
-                              : launch_mla_cfg<false, false>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa);
+    return g.dtype == DT_BF16 ? launch_mla_cfg<true, false>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa, overlap_prev)
+                              : launch_mla_cfg<false, false>(g, lp, k_map, v_map, st, page_table, q, partials, status, s, mo, fa, overlap_prev);
 }
 
 }  // namespace tk

@@ -96,7 +96,7 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
         mbar_expect_tx(bar, C::STAGE_BYTES);
         const int row = (s_pages[i] * g.Hkv + kvh) * 32;
 #pragma unroll
-        for (int h = 0; h < C::NBOX; h++) tma_load_2d(dst + h * kBoxBytes, &tmap, h * 64, row, bar);
+        for (int h = 0; h < C::NBOX; h++) tma_load_2d_shared_tile(dst + h * kBoxBytes, &tmap, h * 64, row, bar);
     };
     if (threadIdx.x == 0)
         for (int i = 0; i < kPfStages && i < n_pages; i++) issue(i);
@@ -159,17 +159,24 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
             const int nv1 = v1 ? max(0, min(n_valid, lim1 - tok_base)) : 0;
 
             // ---- S = Q K^T over the page's 16 tokens ----
+            // (two accumulators per n-tile, even and odd k-steps: four independent MMA chains instead of two)
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
             {
+                float t0[4] = {0.f, 0.f, 0.f, 0.f}, t1[4] = {0.f, 0.f, 0.f, 0.f};
                 const int row = ((lane >> 4) << 3) + (lane & 7);
 #pragma unroll
-                for (int kk = 0; kk < KS; kk++) {
-                    const int cc = 2 * kk + ((lane >> 3) & 1);
-                    uint32_t b0, b1, b2, b3;
-                    ldsm_x4(stg_u + (cc >> 3) * kBoxBytes + swz(row, cc & 7), b0, b1, b2, b3);
-                    mma16816<BF>(s0, qa[kk], b0, b1);
-                    mma16816<BF>(s1, qa[kk], b2, b3);
+                for (int kk = 0; kk < KS; kk += 2) {
+                    const int ca = 2 * kk + ((lane >> 3) & 1), cb = ca + 2;
+                    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                    ldsm_x4(stg_u + (ca >> 3) * kBoxBytes + swz(row, ca & 7), a0, a1, a2, a3);
+                    ldsm_x4(stg_u + (cb >> 3) * kBoxBytes + swz(row, cb & 7), b0, b1, b2, b3);
+                    mma16816<BF>(s0, qa[kk], a0, a1);
+                    mma16816<BF>(s1, qa[kk], a2, a3);
+                    mma16816<BF>(t0, qa[kk + 1], b0, b1);
+                    mma16816<BF>(t1, qa[kk + 1], b2, b3);
                 }
+#pragma unroll
+                for (int e = 0; e < 4; e++) { s0[e] += t0[e]; s1[e] += t1[e]; }
             }
 
             // ---- online softmax: row r0 in [0],[1]; row r1 in [2],[3]; token columns 2j, 2j+1, 2j+8, 2j+9 ----

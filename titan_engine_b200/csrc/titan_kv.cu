@@ -853,19 +853,18 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
     if (mma) {
         // FP8: the 16-bit open pages are items of kind 1 of the same launch
         if (h->dev.n_items > 0) {
+            // A launch of ANOTHER layer that directly follows an attention launch of this handle on the same
+            // stream may overlap that launch's tail: its page tiles belong to a pool the earlier kernel does
+            // not touch, and it waits for the earlier kernel before it writes split-KV rows or `out`.
+            const bool overlap = h->cfg.launch_overlap == TK_OVERLAP_AUTO && !cold && !timed &&
+                                 h->chain_launches == h->launches && h->chain_stream == s && h->chain_layer != layer;
             if (h->mla_mma)
                 e = tk::launch_decode_mma_mla(h->geo, lp, &h->maps[layer], &h->maps_v[layer], h->dev, h->d_table, q,
-                                              h->d_partials, h->d_status, s, &mo, &fa);
-            else {
-                // A launch of ANOTHER layer that directly follows an attention launch of this handle on the same
-                // stream may overlap that launch's tail: its page tiles belong to a pool the earlier kernel does
-                // not touch, and it waits for the earlier kernel before it writes split-KV rows or `out`.
-                const bool overlap = h->cfg.launch_overlap == TK_OVERLAP_AUTO && !cold && !timed &&
-                                     h->chain_launches == h->launches && h->chain_stream == s && h->chain_layer != layer;
+                                              h->d_partials, h->d_status, s, &mo, &fa, overlap);
+            else
                 e = tk::launch_decode_mma(h->geo, lp, &h->maps[layer], cold ? &h->stage_maps[slot] : nullptr, h->dev,
                                           h->d_table, q, h->d_partials, h->d_status, s, &mo, &fa, overlap);
-                h->chain_launches = h->launches + 1; h->chain_layer = layer; h->chain_stream = s;
-            }
+            h->chain_launches = h->launches + 1; h->chain_layer = layer; h->chain_stream = s;
             h->launches++;
         }
         if (timed) { cudaEventRecord(h->prof_ev[h->prof_used + 1], s); h->prof_used += 2; }

@@ -167,7 +167,8 @@ cudaError_t make_mla_tensor_maps(const Geometry& g, void* layer_pool, CUtensorMa
 cudaError_t launch_decode_mma_mla(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* k_map,
                                   const CUtensorMap* v_map, const StepDev& st, const int32_t* page_table,
                                   const void* q, float* partials, int* status, cudaStream_t s,
-                                  const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr);
+                                  const MergeOut* merge = nullptr, const FuseAppend* fuse = nullptr,
+                                  bool overlap_prev = false);
 
 // ... and its multi-token form: 8/G tokens per pass, up to 8 token groups.
 bool        decode_mma_mla_multi_supported(const Geometry& g, int nq_max);
