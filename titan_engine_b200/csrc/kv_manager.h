@@ -60,7 +60,7 @@ struct StepPlan {
 
     // Prefill-sized multi-token steps (16-bit storage, some sequence appending more tokens than the decode
     // kernel's token groups hold).  Sequences whose (tokens x heads per kv head) rows fit one 16-row tile keep
-    // the decode kernel (pf_small_items, chunked by chunk_tokens); the others are cut into tiles of 64 rows
+    // the decode kernel (pf_small_items, chunked by chunk_tokens); the others are cut into tiles of kPrefillRows rows
     // and, where a sequence has too few tiles to fill the GPU, into split-KV chunks of pf_ct[b] tokens.
     bool pf_built = false;
     std::vector<WorkItem> pf_items;        // (b, chunk, kvh, tile)
@@ -74,7 +74,7 @@ struct StepPlan {
 };
 
 // Geometry of the prefill kernel's work list, shared by the planner and the kernel.
-constexpr int kPrefillRows = 64;           // (token, head) rows per tile
+constexpr int kPrefillRows = 128;          // (token, head) rows per tile
 constexpr int kPrefillMaxPages = 2048;     // pages per item: a split-KV chunk holds at most 32768 tokens
 constexpr int kDecodeTileRows = 16;        // rows of the decode kernel's tile
 constexpr int kDecodeMaxTokenGroups = 8;   // token groups per sequence the decode kernel's multi-token form takes
