@@ -155,6 +155,14 @@ int64_t  tk_kv_slot(const tk_kv* h, int32_t seq, int32_t pos);
 /* FNV-1a over (sequence lengths, page tables, free stack). */
 uint64_t tk_kv_state_digest(const tk_kv* h);
 int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out);
+/* Snapshot / restore of the allocator and page-table state (sequence lengths, page tables, free list,
+ * reference counts, cold ids) as a flat int32 image, for replaying a churn run from the step where it went
+ * wrong; the reference has no counterpart (its slots are whole-sequence, src/inference/batch.cpp:86-101).
+ * save: *n_out = image length; image may be NULL to ask for it.  load: a handle of the same geometry takes
+ * the state over (the K/V bytes of the pool are the caller's to restore); the device copy of the page table
+ * is rewritten by the next tk_kv_step_begin.  TK_INVALID_ARG for a foreign or damaged image. */
+int tk_kv_state_save(const tk_kv* h, int32_t* image, int64_t cap, int64_t* n_out);
+int tk_kv_state_load(tk_kv* h, const int32_t* image, int64_t n);
 
 /* ---- one decode/prefill step ---------------------------------------------------
  * tk_kv_step_begin reserves n_new[i] tokens for seq_ids[i] (all or nothing), lays

@@ -384,3 +384,43 @@ def test_prefill_work_list_covers_every_row_once(shape):
     # a step the decode kernel's token groups can hold does not build the list
     c.step_begin(seqs, [1, 1, 128 // G, 1, 1, 1, 1])
     assert len(c.step_prefill_plan()[0]) == 0
+
+
+def test_state_image_replays_a_churn_run_from_the_middle():
+    """Save the allocator + page-table state in the middle of a churn run, load it into a fresh handle and
+    continue both with the same calls: identical digests at every step, and a damaged image is refused."""
+    def make():
+        return host_cache(num_pages=600, max_seqs=16, mpps=64, max_step_tokens=4096)
+    a = make()
+    g = rng(12)
+    live = []
+    def churn(c, g, live, steps):
+        for _ in range(steps):
+            if live and g.random() < 0.4:
+                s = live.pop(int(g.integers(len(live)))); c.seq_free(s)
+            if len(live) < 12:
+                live.append(c.seq_alloc())
+            c.step_begin(sorted(live), [int(g.integers(1, 40)) for _ in live])
+            if live and g.random() < 0.3:
+                s = live[int(g.integers(len(live)))]
+                c.truncate(s, (c.seq_len(s) // 2 // 16) * 16)
+    churn(a, g, live, 40)
+    image = a.state_save()
+    b = make()
+    b.state_load(image)
+    assert b.digest() == a.digest() and b.num_free_pages == a.num_free_pages
+    for s in live:
+        np.testing.assert_array_equal(b.page_table(s), a.page_table(s))
+    state = g.bit_generator.state
+    live_b = list(live)
+    churn(a, g, live, 30)
+    g2 = rng(0); g2.bit_generator.state = state
+    churn(b, g2, live_b, 30)
+    assert a.digest() == b.digest() and live == live_b
+    bad = image.copy(); bad[0] ^= 1
+    with pytest.raises(KvError):
+        make().state_load(bad)
+    with pytest.raises(KvError):
+        make().state_load(image[:-3])
+    with pytest.raises(KvError):
+        host_cache(num_pages=601, max_seqs=16, mpps=64).state_load(image)

@@ -70,6 +70,8 @@ SIGNATURES = {
     "tk_kv_page_table": (C.c_int, [_P, C.c_int32, _I32P, C.c_int32, _I32P]),
     "tk_kv_slot": (C.c_int64, [_P, C.c_int32, C.c_int32]),
     "tk_kv_state_digest": (C.c_uint64, [_P]),
+    "tk_kv_state_save": (C.c_int, [_P, _I32P, C.c_int64, C.POINTER(C.c_int64)]),
+    "tk_kv_state_load": (C.c_int, [_P, _I32P, C.c_int64]),
     "tk_kv_get_stats": (C.c_int, [_P, C.POINTER(KvStats)]),
     "tk_kv_step_begin": (C.c_int, [_P, C.c_int32, _I32P, _I32P, _P]),
     "tk_kv_step_begin_capped": (C.c_int, [_P, C.c_int32, _I32P, _I32P, _I32P, _P]),

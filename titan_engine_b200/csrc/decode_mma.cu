@@ -330,6 +330,9 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         // ---- S = Q K^T over the page's 16 tokens ----
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
         if (KIND == K_FP8) {
+            // the kernel is close to its issue limit here, and a chain of eight dependent MMAs per accumulator
+            // leaves the warp waiting on fixed latencies: four accumulators (even / odd k-steps), summed at the end
+            float u0[4] = {0.f, 0.f, 0.f, 0.f}, u1[4] = {0.f, 0.f, 0.f, 0.f};
             const int row = ((lane >> 4) << 3) + (lane & 7);
 #pragma unroll
             for (int cp = 0; cp < D / 32; cp++) {
@@ -337,9 +340,11 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                 ldsm_x4(stg_u + swz(row, 2 * cp + ((lane >> 3) & 1)), r0, r1, r2, r3);
                 mma16816<BF>(s0, qa[2 * cp],     e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r0 >> 16));
                 mma16816<BF>(s1, qa[2 * cp],     e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r2 >> 16));
-                mma16816<BF>(s0, qa[2 * cp + 1], e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
-                mma16816<BF>(s1, qa[2 * cp + 1], e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
+                mma16816<BF>(u0, qa[2 * cp + 1], e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r1 >> 16));
+                mma16816<BF>(u1, qa[2 * cp + 1], e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r3 >> 16));
             }
+#pragma unroll
+            for (int e = 0; e < 4; e++) { s0[e] += u0[e]; s1[e] += u1[e]; }
         } else {
             const int row = ((lane >> 4) << 3) + (lane & 7);
 #pragma unroll

@@ -221,6 +221,60 @@ uint64_t PageManager::digest() const {
     return h;
 }
 
+namespace { constexpr int32_t kImageMagic = 0x544B5631; }      // "TKV1"
+
+std::vector<int32_t> PageManager::save() const {
+    std::vector<int32_t> im = {kImageMagic, num_pages_, max_seqs_, max_pages_per_seq_, page_size_, hot_window_,
+                               num_cold_pages_, cold_high_water_, (int32_t)free_stack_.size(), (int32_t)cold_stack_.size()};
+    im.insert(im.end(), seq_len_.begin(), seq_len_.end());
+    im.insert(im.end(), seq_pages_.begin(), seq_pages_.end());
+    im.insert(im.end(), seq_tail_.begin(), seq_tail_.end());
+    im.insert(im.end(), refcount_.begin(), refcount_.end());
+    im.insert(im.end(), free_stack_.begin(), free_stack_.end());
+    im.insert(im.end(), cold_stack_.begin(), cold_stack_.end());
+    for (int s = 0; s < max_seqs_; s++)                       // only the rows in use: live sequences, their pages
+        if (seq_len_[s] >= 0) im.insert(im.end(), row(s), row(s) + seq_pages_[s]);
+    return im;
+}
+
+int PageManager::load(const int32_t* im, size_t n) {
+    if (!im || n < 10 || im[0] != kImageMagic) return ST_INVALID_ARG;
+    if (im[1] != num_pages_ || im[2] != max_seqs_ || im[3] != max_pages_per_seq_ || im[4] != page_size_ ||
+        im[5] != hot_window_ || im[6] != num_cold_pages_) return ST_INVALID_ARG;
+    const int n_free = im[8], n_cold = im[9];
+    if (n_free < 0 || n_free > num_pages_ || n_cold < 0 || n_cold > num_cold_pages_) return ST_INVALID_ARG;
+    size_t at = 10;
+    const size_t fixed = at + 3 * (size_t)max_seqs_ + num_pages_ + n_free + n_cold;
+    if (n < fixed) return ST_INVALID_ARG;
+    const int32_t *len = im + at, *pages = len + max_seqs_, *tail = pages + max_seqs_, *ref = tail + max_seqs_;
+    const int32_t *fs = ref + num_pages_, *cs = fs + n_free, *rows = cs + n_cold;
+    size_t need = fixed;
+    for (int s = 0; s < max_seqs_; s++) {
+        if (len[s] < -1 || pages[s] < 0 || pages[s] > max_pages_per_seq_) return ST_INVALID_ARG;
+        if (len[s] >= 0 && ((int64_t)len[s] + page_size_ - 1) / page_size_ != pages[s]) return ST_INVALID_ARG;
+        if (len[s] >= 0) need += pages[s];
+    }
+    if (n != need) return ST_INVALID_ARG;
+    for (int i = 0; i < n_free; i++) if (fs[i] < 0 || fs[i] >= num_pages_) return ST_INVALID_ARG;
+    for (size_t i = fixed; i < need; i++) if (im[i] >= num_pages_ || im[i] < -2 - num_cold_pages_ || im[i] == -1) return ST_INVALID_ARG;
+    seq_len_.assign(len, len + max_seqs_);
+    seq_pages_.assign(pages, pages + max_seqs_);
+    seq_tail_.assign(tail, tail + max_seqs_);
+    refcount_.assign(ref, ref + num_pages_);
+    free_stack_.assign(fs, fs + n_free);
+    cold_stack_.assign(cs, cs + n_cold);
+    cold_high_water_ = im[7];
+    table_.assign(table_.size(), -1);
+    for (int s = 0; s < max_seqs_; s++) {
+        if (seq_len_[s] < 0) { seq_pages_[s] = 0; continue; }
+        std::copy(rows, rows + seq_pages_[s], table_.begin() + (size_t)s * max_pages_per_seq_);
+        rows += seq_pages_[s];
+    }
+    delta_.clear();
+    full_upload_ = true;
+    return ST_OK;
+}
+
 int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                            bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
                            int max_partial_rows, StepPlan* plan, const int32_t* len_cap, int heads_per_kv) {

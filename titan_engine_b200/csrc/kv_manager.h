@@ -137,6 +137,13 @@ public:
                   bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
                   int max_partial_rows, StepPlan* plan, const int32_t* len_cap = nullptr, int heads_per_kv = 0);
 
+    // Snapshot of the whole bookkeeping state (lengths, page tables, free lists, reference counts, cold ids)
+    // as a flat int32 image, and its restore into a manager of the same geometry: a failing churn run can be
+    // saved at step N and replayed from there.  load() marks every table entry as changed.
+    std::vector<int32_t> save() const;
+    int load(const int32_t* image, size_t n);              // status; ST_INVALID_ARG on a foreign or damaged image
+    bool take_full_upload() { const bool f = full_upload_; full_upload_ = false; return f; }
+
     struct Counters { int64_t page_allocs = 0, page_frees = 0, seq_allocs = 0, seq_frees = 0, evictions = 0; } counters;
 
 private:
@@ -153,6 +160,7 @@ private:
     std::vector<int32_t> cold_stack_;   // back() is the next cold id handed out
     std::vector<std::pair<int32_t, int32_t>> delta_;
     std::vector<uint32_t> delta_stamp_;  // per table index: generation of the last compaction that saw it
+    bool full_upload_ = false;           // the device copy of the table must be rewritten whole (after load())
     uint32_t delta_gen_ = 0;
 };
 

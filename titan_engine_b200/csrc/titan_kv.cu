@@ -623,6 +623,27 @@ int tk_kv_page_table(const tk_kv* h, int32_t seq, int32_t* out, int32_t cap, int
 }
 int64_t tk_kv_slot(const tk_kv* h, int32_t seq, int32_t pos) { return h ? h->mgr->slot(seq, pos) : -1; }
 uint64_t tk_kv_state_digest(const tk_kv* h) { return h ? h->mgr->digest() : 0; }
+int tk_kv_state_save(const tk_kv* h, int32_t* image, int64_t cap, int64_t* n_out) {
+    if (!h || !n_out) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(const_cast<tk_kv*>(h)->mgr_mu);
+    const std::vector<int32_t> im = h->mgr->save();
+    *n_out = (int64_t)im.size();
+    if (!image) return TK_OK;
+    if (cap < (int64_t)im.size()) return TK_INVALID_ARG;
+    memcpy(image, im.data(), im.size() * sizeof(int32_t));
+    return TK_OK;
+}
+int tk_kv_state_load(tk_kv* h, const int32_t* image, int64_t n) {
+    if (!h || !image || n <= 0) return TK_INVALID_ARG;
+    std::lock_guard<std::mutex> lock(h->mgr_mu);
+    if (h->mgr->cold_enabled() && !h->host_only)
+        return fail(h, TK_UNSUPPORTED, "state_load: a device handle with a cold tier cannot take an image (the host pool's contents are not part of it)");
+    const int st = h->mgr->load(image, (size_t)n);
+    if (st != TK_OK) return fail(h, st, "state_load: the image does not belong to a cache of this geometry, or is damaged");
+    h->have_step = false;
+    return TK_OK;
+}
+
 int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out) {
     if (!h || !out) return TK_INVALID_ARG;
     *out = h->stats;
@@ -674,7 +695,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     h->mgr->compact_delta();
     auto& delta = h->mgr->delta();
     int n_delta = (int)delta.size();
-    if (n_delta > kMaxDelta) {
+    if (n_delta > kMaxDelta || h->mgr->take_full_upload()) {
         // rare (bulk adopt / huge prefill): copy the whole table from pageable memory
         const size_t n_entries = (size_t)h->cfg.max_seqs * h->cfg.max_pages_per_seq;
         std::vector<int32_t> full(n_entries);

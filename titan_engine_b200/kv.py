@@ -162,6 +162,18 @@ class PagedKVCache:
     def digest(self) -> int:
         return self._lib.tk_kv_state_digest(self._h)
 
+    def state_save(self) -> np.ndarray:
+        """Allocator + page-table state as a flat int32 image (see tk_kv_state_save)."""
+        n = C.c_int64(0)
+        self._check(self._lib.tk_kv_state_save(self._h, None, 0, C.byref(n)))
+        image = np.zeros(n.value, dtype=np.int32)
+        self._check(self._lib.tk_kv_state_save(self._h, _ptr(image), n.value, C.byref(n)))
+        return image
+
+    def state_load(self, image: np.ndarray) -> None:
+        image = _i32(image)
+        self._check(self._lib.tk_kv_state_load(self._h, _ptr(image), len(image)))
+
     def stats(self) -> dict:
         s = L.KvStats()
         self._check(self._lib.tk_kv_get_stats(self._h, C.byref(s)))
