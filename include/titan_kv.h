@@ -186,7 +186,7 @@ int tk_kv_step_num_tokens(const tk_kv* h);
 int tk_kv_step_num_work_items(const tk_kv* h);
 int tk_kv_step_chunk_tokens(const tk_kv* h);
 /* Work list of the prefill attention kernel for the current step (inspection and tests): *n_items items of
- * four int32 (index into the step's sequences, split-KV chunk, kv head, tile of 128 (token, head) rows), the
+ * four int32 (index into the step's sequences, split-KV chunk, kv head, tile of 64 (token, head) rows), the
  * split-KV chunk in tokens of each of the step's sequences, and how many (sequence, chunk, kv head) items
  * stay with the decode kernel.  *n_items is 0 for a step that tk_kv_decode_multi serves without that kernel. */
 int tk_kv_step_prefill_plan(const tk_kv* h, int32_t cap, int32_t* items, int32_t* n_items, int32_t* chunk_tokens,
@@ -229,7 +229,7 @@ int tk_kv_decode_ex(tk_kv* h, int32_t layer, const void* q, int32_t q_dtype, voi
  * It is also the attention of a prefill chunk: the reference runs update + attention_decode once per
  * prompt token (src/inference/engine.cpp:182-193, src/inference/batch.cpp:169-198).  When a sequence
  * appends more than 128 / (num_heads / num_kv_heads) tokens, the sequences with many tokens go to a kernel
- * that works on tiles of 128 (token, head) rows sharing each K/V page tile; the others stay with the decode
+ * that works on tiles of 64 (token, head) rows sharing each K/V page tile; the others stay with the decode
  * kernel.  16-bit pools with the tensor-core kernels, every sequence of the step appending at least one
  * token, no cold pages; the MLA shape up to 64 / (num_heads / num_kv_heads) tokens per sequence;
  * TK_UNSUPPORTED otherwise. */

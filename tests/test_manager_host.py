@@ -353,7 +353,7 @@ def test_prefill_work_list_covers_every_row_once(shape):
     c.step_begin(seqs, n_new)
     items, ct, n_decode = c.step_prefill_plan()
     assert len(items) > 0
-    tpt = 128 // G
+    tpt = 64 // G
     small = [i for i, n in enumerate(n_new) if n * G <= 16]
     assert n_decode == sum(-(-(l + n) // c.step_chunk_tokens) * Hkv for i, (l, n) in enumerate(zip(lens0, n_new)) if i in small)
     seen = {}

@@ -74,7 +74,7 @@ struct StepPlan {
 };
 
 // Geometry of the prefill kernel's work list, shared by the planner and the kernel.
-constexpr int kPrefillRows = 128;          // (token, head) rows per tile
+constexpr int kPrefillRows = 64;           // (token, head) rows per tile
 constexpr int kPrefillMaxPages = 2048;     // pages per item: a split-KV chunk holds at most 32768 tokens
 constexpr int kDecodeTileRows = 16;        // rows of the decode kernel's tile
 constexpr int kDecodeMaxTokenGroups = 8;   // token groups per sequence the decode kernel's multi-token form takes

@@ -11,18 +11,23 @@
 // kv_head = head/(H/Hkv) — evaluated as an online softmax.
 //
 // Schedule.  The rows of a (sequence, kv head) are its (query token, head of the group) pairs:
-// T * G rows, G = H/Hkv.  One CTA takes a tile of 128 rows (128/G whole tokens) and a range of the
+// T * G rows, G = H/Hkv.  One CTA takes a tile of 64 rows (64/G whole tokens) and a range of the
 // context (the whole visible context, or one split-KV chunk of it when the sequence has too few
-// tiles to fill the GPU).  Its 4 warps own 32 rows each — two sets of the M rows of m16n8k16 MMAs,
-// so that every K/V fragment read from shared memory feeds two MMAs — and all consume the SAME K/V
-// page tiles: a CTA-wide ring of TMA stages (one elected thread issues cp.async.bulk.tensor.2d per
-// page tile; `full` mbarriers carry the byte count, `empty` mbarriers collect one arrival per
-// warp), so a page is fetched once per 128 rows instead of once per 16 as in the decode kernel's
-// multi-token form.  With T * G >= 128 this is a contraction in its own right (128 flop per K/V
-// byte at D = 128), bounded by the tensor pipe, not by HBM.
+// tiles to fill the GPU).  Its 4 warps own 16 rows each — the M rows of m16n8k16 MMAs — and all
+// consume the SAME K/V page tiles: a CTA-wide ring of TMA stages (one elected thread issues
+// cp.async.bulk.tensor.2d per page tile; `full` mbarriers carry the byte count, `empty`
+// mbarriers collect one arrival per warp), so a page is fetched once per 64 rows instead of once
+// per 16 as in the decode kernel's multi-token form.  With T * G >= 64 this is a contraction in
+// its own right (64 flop per K/V byte at D = 128), bounded by the tensor pipe, not by HBM.
 // Tiles that see the whole visible context write normalised outputs directly; split ones leave
 // (o, m, l) partials and the CTA that arrives last for the tile merges them (tk_merge.cuh).
 // Every wait is bounded; a wait that gives up sets the status word and nothing is written.
+//
+// Measured alternatives (16 fresh sequences growing by 1024 tokens per step, 8B head shape, B200): this form
+// 235 TFLOP/s; four instead of two accumulator chains in QK^T 214; 32 rows per warp (128-row tiles, every
+// shared-memory fragment feeding two MMAs, 255 registers, 2 CTAs/SM) 200; 6 instead of 4 stages and the L2
+// eviction hint of the tile loads: no difference.  ncu: tensor pipe 42 % active, issue slots 44 %: the
+// kernel sits at what the warp-level mma.sync path delivers on this part, not at a memory limit.
 #include "tk_kernels.cuh"
 #include "tk_merge.cuh"
 #include "tk_mma.cuh"
@@ -36,8 +41,6 @@ namespace tk {
 namespace {
 
 constexpr int kPfStages = 4;              // page tiles in flight per CTA
-constexpr int kMT = 2;                    // 16-row MMA tiles per warp: kPrefillRows = 4 warps x kMT x 16
-static_assert(kPrefillRows == kWarps * kMT * 16, "tile rows");
 
 template <int D>
 struct PfCfg {
@@ -52,7 +55,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 template <bool BF, int D>
-__global__ void __launch_bounds__(kWarps * 32, 2)
+__global__ void __launch_bounds__(kWarps * 32, 3)
 prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev st, PrefillDev pf,
                    const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q, void* __restrict__ out,
                    int out_dtype, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ status) {
@@ -104,46 +107,31 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
     if (threadIdx.x == 0)
         for (int i = 0; i < kPfStages && i < n_pages; i++) issue(i);
 
-    // ---- this warp's kMT x 16 rows: row r of the CTA tile is query token r / G of the tile, head r % G.
-    // Each B fragment (K or V page rows from shared memory) feeds kMT MMAs: half the shared-memory traffic
-    // per flop of a 16-row warp tile, which is what bounds a 16-row tile on this path.
-    int rr[kMT][2], lim[kMT][2];
-    bool vv[kMT][2];
-#pragma unroll
-    for (int mt = 0; mt < kMT; mt++)
-#pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-            rr[mt][hf] = kMT * 16 * warp + 16 * mt + gr + 8 * hf;
-            vv[mt][hf] = rr[mt][hf] / G < tok_cnt;
-            lim[mt][hf] = base_pos + tok_first + rr[mt][hf] / G + 1;      // positions the row attends to: [0, lim)
-        }
+    // ---- this warp's 16 rows: row r is query token (16*warp + r) / G of the tile, head (16*warp + r) % G
+    const int r0 = 16 * warp + gr, r1 = r0 + 8;
+    const bool v0 = r0 / G < tok_cnt, v1 = r1 / G < tok_cnt;
+    const int lim0 = base_pos + tok_first + r0 / G + 1;     // positions row r0 attends to: [0, lim0)
+    const int lim1 = base_pos + tok_first + r1 / G + 1;
     // last position any row of this warp sees (0: the warp has no row)
-    const int warp_lim = (kMT * 16 * warp) / G < tok_cnt
-                             ? base_pos + tok_first + min(tok_cnt - 1, (kMT * 16 * warp + kMT * 16 - 1) / G) + 1 : 0;
+    const int warp_lim = (16 * warp) / G < tok_cnt ? base_pos + tok_first + min(tok_cnt - 1, (16 * warp + 15) / G) + 1 : 0;
 
-    uint32_t qa[kMT][KS][4];
-#pragma unroll
-    for (int mt = 0; mt < kMT; mt++) {
-        const uint16_t* qrow0 = q + ((size_t)(st.q_base[b] + tok_first + rr[mt][0] / G) * g.H + (size_t)kvh * G + rr[mt][0] % G) * D;
-        const uint16_t* qrow1 = q + ((size_t)(st.q_base[b] + tok_first + rr[mt][1] / G) * g.H + (size_t)kvh * G + rr[mt][1] % G) * D;
+    uint32_t qa[KS][4];
+    {
+        const uint16_t* qrow0 = q + ((size_t)(st.q_base[b] + tok_first + r0 / G) * g.H + (size_t)kvh * G + r0 % G) * D;
+        const uint16_t* qrow1 = q + ((size_t)(st.q_base[b] + tok_first + r1 / G) * g.H + (size_t)kvh * G + r1 % G) * D;
 #pragma unroll
         for (int kk = 0; kk < KS; kk++) {
-            qa[mt][kk][0] = vv[mt][0] ? *reinterpret_cast<const uint32_t*>(qrow0 + 16 * kk + 2 * j) : 0u;
-            qa[mt][kk][2] = vv[mt][0] ? *reinterpret_cast<const uint32_t*>(qrow0 + 16 * kk + 8 + 2 * j) : 0u;
-            qa[mt][kk][1] = vv[mt][1] ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 2 * j) : 0u;
-            qa[mt][kk][3] = vv[mt][1] ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 8 + 2 * j) : 0u;
+            qa[kk][0] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + 16 * kk + 2 * j) : 0u;
+            qa[kk][2] = v0 ? *reinterpret_cast<const uint32_t*>(qrow0 + 16 * kk + 8 + 2 * j) : 0u;
+            qa[kk][1] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 2 * j) : 0u;
+            qa[kk][3] = v1 ? *reinterpret_cast<const uint32_t*>(qrow1 + 16 * kk + 8 + 2 * j) : 0u;
         }
     }
 
-    float o[kMT][NT][4];
-    float mrow[kMT][2], lrow[kMT][2];
+    float o[NT][4];
 #pragma unroll
-    for (int mt = 0; mt < kMT; mt++) {
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) { o[mt][nt][0] = o[mt][nt][1] = o[mt][nt][2] = o[mt][nt][3] = 0.0f; }
-        mrow[mt][0] = mrow[mt][1] = -1e30f;
-        lrow[mt][0] = lrow[mt][1] = 0.0f;
-    }
+    for (int nt = 0; nt < NT; nt++) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f; }
+    float m0 = -1e30f, m1 = -1e30f, l0 = 0.0f, l1 = 0.0f;  // rows r0 and r1
     const float sm_scale = 1.0f / sqrtf((float)D);
     bool alive = true;
 
@@ -173,13 +161,11 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
                 __syncwarp();
             }
             const int n_valid = min(kPage, t1 - tok_base);
+            const int nv0 = v0 ? max(0, min(n_valid, lim0 - tok_base)) : 0;
+            const int nv1 = v1 ? max(0, min(n_valid, lim1 - tok_base)) : 0;
 
-            // ---- S = Q K^T over the page's 16 tokens: s[mt][0] tokens 0-7, s[mt][1] tokens 8-15 ----
-            float sacc[kMT][2][4];
-#pragma unroll
-            for (int mt = 0; mt < kMT; mt++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) sacc[mt][0][e] = sacc[mt][1][e] = 0.0f;
+            // ---- S = Q K^T over the page's 16 tokens ----
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
             {
                 const int row = ((lane >> 4) << 3) + (lane & 7);
 #pragma unroll
@@ -187,56 +173,68 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
                     const int cc = 2 * kk + ((lane >> 3) & 1);
                     uint32_t b0, b1, b2, b3;
                     ldsm_x4(stg_u + (cc >> 3) * kBoxBytes + swz(row, cc & 7), b0, b1, b2, b3);
-#pragma unroll
-                    for (int mt = 0; mt < kMT; mt++) {
-                        mma16816<BF>(sacc[mt][0], qa[mt][kk], b0, b1);
-                        mma16816<BF>(sacc[mt][1], qa[mt][kk], b2, b3);
-                    }
+                    mma16816<BF>(s0, qa[kk], b0, b1);
+                    mma16816<BF>(s1, qa[kk], b2, b3);
                 }
             }
 
-            // ---- online softmax per row; a thread holds token columns 2j, 2j+1, 2j+8, 2j+9 of its rows ----
-            uint32_t pa[kMT][4];
+            // ---- online softmax: row r0 in [0],[1]; row r1 in [2],[3]; token columns 2j, 2j+1, 2j+8, 2j+9 ----
+            float p0[4], p1[4];
             const int c0 = 2 * j;
+            {
+                float a0 = s0[0] * sm_scale, a1 = s0[1] * sm_scale, a2 = s1[0] * sm_scale, a3 = s1[1] * sm_scale;
+                if (c0 >= nv0) a0 = -1e30f;
+                if (c0 + 1 >= nv0) a1 = -1e30f;
+                if (c0 + 8 >= nv0) a2 = -1e30f;
+                if (c0 + 9 >= nv0) a3 = -1e30f;
+                float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+                mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+                const float mn = fmaxf(m0, mx);
+                const float alpha = ex2((m0 - mn) * kLog2e);
+                const float nb = -mn * kLog2e;
+                // a row may see nothing of a page: exp(-1e30 + 1e30) is 1, not 0
+                p0[0] = c0 < nv0 ? ex2(fmaf(a0, kLog2e, nb)) : 0.0f;
+                p0[1] = c0 + 1 < nv0 ? ex2(fmaf(a1, kLog2e, nb)) : 0.0f;
+                p1[0] = c0 + 8 < nv0 ? ex2(fmaf(a2, kLog2e, nb)) : 0.0f;
+                p1[1] = c0 + 9 < nv0 ? ex2(fmaf(a3, kLog2e, nb)) : 0.0f;
+                l0 = l0 * alpha + (p0[0] + p0[1] + p1[0] + p1[1]);
+                if (!__all_sync(0xFFFFFFFFu, mn == m0)) {
 #pragma unroll
-            for (int mt = 0; mt < kMT; mt++) {
-                float p[2][4];                                  // [half][col]: cols 2j, 2j+1, 2j+8, 2j+9
-#pragma unroll
-                for (int hf = 0; hf < 2; hf++) {
-                    const int nv = vv[mt][hf] ? max(0, min(n_valid, lim[mt][hf] - tok_base)) : 0;
-                    float a0 = sacc[mt][0][2 * hf] * sm_scale, a1 = sacc[mt][0][2 * hf + 1] * sm_scale;
-                    float a2 = sacc[mt][1][2 * hf] * sm_scale, a3 = sacc[mt][1][2 * hf + 1] * sm_scale;
-                    if (c0 >= nv) a0 = -1e30f;
-                    if (c0 + 1 >= nv) a1 = -1e30f;
-                    if (c0 + 8 >= nv) a2 = -1e30f;
-                    if (c0 + 9 >= nv) a3 = -1e30f;
-                    float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
-                    mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
-                    const float mo_ = mrow[mt][hf];
-                    const float mn = fmaxf(mo_, mx);
-                    const float alpha = ex2((mo_ - mn) * kLog2e);
-                    const float nb = -mn * kLog2e;
-                    // a row may see nothing of a page: exp(-1e30 + 1e30) is 1, not 0
-                    p[hf][0] = c0 < nv ? ex2(fmaf(a0, kLog2e, nb)) : 0.0f;
-                    p[hf][1] = c0 + 1 < nv ? ex2(fmaf(a1, kLog2e, nb)) : 0.0f;
-                    p[hf][2] = c0 + 8 < nv ? ex2(fmaf(a2, kLog2e, nb)) : 0.0f;
-                    p[hf][3] = c0 + 9 < nv ? ex2(fmaf(a3, kLog2e, nb)) : 0.0f;
-                    lrow[mt][hf] = lrow[mt][hf] * alpha + (p[hf][0] + p[hf][1] + p[hf][2] + p[hf][3]);
-                    // the running maximum rarely moves after the first pages: skip the 2*NT multiplies then
-                    if (!__all_sync(0xFFFFFFFFu, mn == mo_)) {
-#pragma unroll
-                        for (int nt = 0; nt < NT; nt++) { o[mt][nt][2 * hf] *= alpha; o[mt][nt][2 * hf + 1] *= alpha; }
-                    }
-                    mrow[mt][hf] = mn;
+                    for (int nt = 0; nt < NT; nt++) { o[nt][0] *= alpha; o[nt][1] *= alpha; }
                 }
-                pa[mt][0] = pack2<BF>(p[0][0], p[0][1]);        // row gr,   tokens 2j, 2j+1
-                pa[mt][1] = pack2<BF>(p[1][0], p[1][1]);        // row gr+8, tokens 2j, 2j+1
-                pa[mt][2] = pack2<BF>(p[0][2], p[0][3]);        // row gr,   tokens 2j+8, 2j+9
-                pa[mt][3] = pack2<BF>(p[1][2], p[1][3]);        // row gr+8, tokens 2j+8, 2j+9
+                m0 = mn;
+            }
+            {
+                float a0 = s0[2] * sm_scale, a1 = s0[3] * sm_scale, a2 = s1[2] * sm_scale, a3 = s1[3] * sm_scale;
+                if (c0 >= nv1) a0 = -1e30f;
+                if (c0 + 1 >= nv1) a1 = -1e30f;
+                if (c0 + 8 >= nv1) a2 = -1e30f;
+                if (c0 + 9 >= nv1) a3 = -1e30f;
+                float mx = fmaxf(fmaxf(a0, a1), fmaxf(a2, a3));
+                mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, 2));
+                const float mn = fmaxf(m1, mx);
+                const float alpha = ex2((m1 - mn) * kLog2e);
+                const float nb = -mn * kLog2e;
+                p0[2] = c0 < nv1 ? ex2(fmaf(a0, kLog2e, nb)) : 0.0f;
+                p0[3] = c0 + 1 < nv1 ? ex2(fmaf(a1, kLog2e, nb)) : 0.0f;
+                p1[2] = c0 + 8 < nv1 ? ex2(fmaf(a2, kLog2e, nb)) : 0.0f;
+                p1[3] = c0 + 9 < nv1 ? ex2(fmaf(a3, kLog2e, nb)) : 0.0f;
+                l1 = l1 * alpha + (p0[2] + p0[3] + p1[2] + p1[3]);
+                if (!__all_sync(0xFFFFFFFFu, mn == m1)) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++) { o[nt][2] *= alpha; o[nt][3] *= alpha; }
+                }
+                m1 = mn;
             }
 
             // ---- O += P V ----
+            uint32_t pa[4];
+            pa[0] = pack2<BF>(p0[0], p0[1]);
+            pa[1] = pack2<BF>(p0[2], p0[3]);
+            pa[2] = pack2<BF>(p1[0], p1[1]);
+            pa[3] = pack2<BF>(p1[2], p1[3]);
             {
                 const int row = 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
 #pragma unroll
@@ -244,11 +242,8 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
                     const int cc = 2 * np + (lane >> 4);
                     uint32_t b0, b1, b2, b3;
                     ldsm_x4_t(stg_u + (cc >> 3) * kBoxBytes + swz(row, cc & 7), b0, b1, b2, b3);
-#pragma unroll
-                    for (int mt = 0; mt < kMT; mt++) {
-                        mma16816<BF>(o[mt][2 * np], pa[mt], b0, b1);
-                        mma16816<BF>(o[mt][2 * np + 1], pa[mt], b2, b3);
-                    }
+                    mma16816<BF>(o[2 * np], pa, b0, b1);
+                    mma16816<BF>(o[2 * np + 1], pa, b2, b3);
                 }
             }
         }
@@ -272,13 +267,8 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
     }
 
     // quad-reduce the row sums
-#pragma unroll
-    for (int mt = 0; mt < kMT; mt++)
-#pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-            lrow[mt][hf] += __shfl_xor_sync(0xFFFFFFFFu, lrow[mt][hf], 1);
-            lrow[mt][hf] += __shfl_xor_sync(0xFFFFFFFFu, lrow[mt][hf], 2);
-        }
+    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
     // fail closed: a wait that gave up (here or anywhere on this handle) means no output
     const bool poisoned = !alive || __ldcg(status) != 0;
 
@@ -286,20 +276,18 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
         // the tile saw its whole visible context: normalised rows straight to `out`
         if (poisoned) return;
 #pragma unroll
-        for (int mt = 0; mt < kMT; mt++)
+        for (int half = 0; half < 2; half++) {
+            if (!(half ? v1 : v0)) continue;
+            const int r = half ? r1 : r0;
+            const float inv = 1.0f / ((half ? l1 : l0) + 1e-8f);
+            const size_t base = ((size_t)(st.q_base[b] + tok_first + r / G) * g.H + (size_t)kvh * G + r % G) * D + 2 * j;
 #pragma unroll
-            for (int hf = 0; hf < 2; hf++) {
-                if (!vv[mt][hf]) continue;
-                const int r = rr[mt][hf];
-                const float inv = 1.0f / (lrow[mt][hf] + 1e-8f);
-                const size_t base = ((size_t)(st.q_base[b] + tok_first + r / G) * g.H + (size_t)kvh * G + r % G) * D + 2 * j;
-#pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    const float x = o[mt][nt][2 * hf] * inv, y = o[mt][nt][2 * hf + 1] * inv;
-                    if (out_dtype == DT_FP32) *reinterpret_cast<float2*>((float*)out + base + 8 * nt) = make_float2(x, y);
-                    else *reinterpret_cast<uint32_t*>((uint16_t*)out + base + 8 * nt) = pack2<BF>(x, y);
-                }
+            for (int nt = 0; nt < NT; nt++) {
+                const float x = o[nt][2 * half] * inv, y = o[nt][2 * half + 1] * inv;
+                if (out_dtype == DT_FP32) *reinterpret_cast<float2*>((float*)out + base + 8 * nt) = make_float2(x, y);
+                else *reinterpret_cast<uint32_t*>((uint16_t*)out + base + 8 * nt) = pack2<BF>(x, y);
             }
+        }
         return;
     }
 
@@ -308,17 +296,15 @@ prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev
     float* region = partials + (size_t)pf.poff[b] * g.H * (D + 2);
     const int HP = nq * g.H;
 #pragma unroll
-    for (int mt = 0; mt < kMT; mt++)
+    for (int half = 0; half < 2; half++) {
+        if (!(half ? v1 : v0)) continue;
+        const int r = half ? r1 : r0;
+        float* prow = region + partial_off(chunk, (tok_first + r / G) * g.H + kvh * G + r % G, HP, D);
 #pragma unroll
-        for (int hf = 0; hf < 2; hf++) {
-            if (!vv[mt][hf]) continue;
-            const int r = rr[mt][hf];
-            float* prow = region + partial_off(chunk, (tok_first + r / G) * g.H + kvh * G + r % G, HP, D);
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-                *reinterpret_cast<float2*>(prow + 8 * nt + 2 * j) = make_float2(o[mt][nt][2 * hf], o[mt][nt][2 * hf + 1]);
-            if (j == 0) *reinterpret_cast<float2*>(prow + D) = make_float2(mrow[mt][hf], lrow[mt][hf]);
-        }
+        for (int nt = 0; nt < NT; nt++)
+            *reinterpret_cast<float2*>(prow + 8 * nt + 2 * j) = make_float2(o[nt][2 * half], o[nt][2 * half + 1]);
+        if (j == 0) *reinterpret_cast<float2*>(prow + D) = make_float2(half ? m1 : m0, half ? l1 : l0);
+    }
     __syncthreads();                                        // the CTA's rows are complete ...
     if (threadIdx.x == 0) {
         __threadfence();                                    // ... and ordered before the ticket, device-wide
