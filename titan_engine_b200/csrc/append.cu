@@ -137,7 +137,7 @@ __device__ __forceinline__ uint32_t quant2(uint32_t w, float inv_scale) {
 // mask, which matters - the kernel issues a few hundred instructions per tile and is bound by issue slots,
 // not by HBM, when the addressing costs integer divisions.
 template <bool BF16, int D>
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 4)
 seal_warp_kernel(Geometry g, LayerPtrs lp, StepDev st, const uint16_t* __restrict__ k, const uint16_t* __restrict__ v) {
     constexpr int PS = 16;
     constexpr int VPR = D / 8;                  // 16-byte vectors per row
