@@ -52,6 +52,10 @@ enum { TK_MERGE_IN_KERNEL = 0, TK_MERGE_SEPARATE = 1 };
 /* back-to-back attention launches of different layers: the later one may start (programmatic dependent
  * launch) while the earlier one drains, or every launch waits for the one before it */
 enum { TK_OVERLAP_AUTO = 0, TK_OVERLAP_OFF = 1 };
+/* attention of prefill chunks (tk_kv_decode_multi with many tokens per sequence): the tcgen05 kernel (tiles of
+ * 128 rows, accumulators in tensor memory) where the shape allows it (16-bit pool, head_dim 128), or always the
+ * mma.sync kernel (tiles of 64 rows) */
+enum { TK_PREFILL_AUTO = 0, TK_PREFILL_MMA_SYNC = 1 };
 
 /* Stands in for the (L, Hkv, D, max_seq_len, dtype) argument list of
  * KVCache::initialize (src/inference/kv_cache.h:21-23) plus the fields of
@@ -83,7 +87,7 @@ typedef struct tk_kv_config {
                                    have head_dim, scale = 1/sqrtf(head_dim); 16-bit storage, generic kernel */
     int32_t merge_impl;         /* TK_MERGE_* */
     int32_t launch_overlap;     /* TK_OVERLAP_* */
-    int32_t reserved[1];
+    int32_t prefill_impl;       /* TK_PREFILL_* */
 } tk_kv_config;
 
 typedef struct tk_kv_stats {    /* in the style of CacheStats, src/memory/memory_manager.h:211-220 */

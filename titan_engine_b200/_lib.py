@@ -15,6 +15,7 @@ TK_FP32, TK_FP16, TK_BF16, TK_FP8_E4M3 = 0, 1, 2, 3
 TK_DECODE_AUTO, TK_DECODE_SIMT, TK_DECODE_MMA = 0, 1, 2
 TK_MERGE_IN_KERNEL, TK_MERGE_SEPARATE = 0, 1
 TK_OVERLAP_AUTO, TK_OVERLAP_OFF = 0, 1
+TK_PREFILL_AUTO, TK_PREFILL_MMA_SYNC = 0, 1
 TK_DEVICE_NONE = -2
 TK_PEER_HANDLE_BYTES = 64
 
@@ -23,7 +24,7 @@ class KvConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in (
         "num_layers", "num_heads", "num_kv_heads", "head_dim", "page_size", "dtype", "io_dtype",
         "num_pages", "max_seqs", "max_pages_per_seq", "max_step_tokens", "chunk_tokens",
-        "decode_impl", "device", "hot_window", "cold_pages", "v_head_dim", "merge_impl", "launch_overlap")] + [("reserved", C.c_int32 * 1)]
+        "decode_impl", "device", "hot_window", "cold_pages", "v_head_dim", "merge_impl", "launch_overlap", "prefill_impl")]
 
 
 class KvStats(C.Structure):

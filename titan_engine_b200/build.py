@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libtitan_kv.so")
-SOURCES = ["titan_kv.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_mma_mla.cu", "prefill_mma.cu",
+SOURCES = ["titan_kv.cu", "append.cu", "decode_simt.cu", "decode_mma.cu", "decode_mma_mla.cu", "prefill_mma.cu", "prefill_tc.cu",
            "decode_static.cu", "peer_exchange.cu", "rope_append.cu", "kv_manager.cpp", "kv_scheduler.cpp",
            "sched_abi.cpp", "compat/kv_cache_compat.cu"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",

@@ -628,8 +628,9 @@ bool decode_mma_supported(const Geometry& g) {
 }
 
 // The layer's pool as a 2-D tensor: rows = num_pages*Hkv*2*16 token rows of D elements.
-// Box = 32 rows (one tile: K rows then V rows) x 128 bytes, 128-byte swizzle.
-cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out) {
+// Box = box_rows rows x 128 bytes, 128-byte swizzle: 32 rows = one tile (K rows then V rows) for the
+// mma.sync kernels, 16 rows = the K or the V rows of a page for the tcgen05 prefill kernel.
+cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out, int box_rows) {
     static PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
     if (!encode) {
         void* fn = nullptr;
@@ -642,7 +643,7 @@ cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMa
     const int esize = g.dtype == DT_FP8 ? 1 : 2;
     cuuint64_t dims[2] = {(cuuint64_t)g.D, (cuuint64_t)g.num_pages * g.Hkv * 2 * g.ps};
     cuuint64_t strides[1] = {(cuuint64_t)g.D * esize};
-    cuuint32_t box[2] = {(cuuint32_t)(128 / esize), 32};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esize), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode(out, esize == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2,
                         layer_pool, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,

@@ -277,7 +277,8 @@ int PageManager::load(const int32_t* im, size_t n) {
 
 int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                            bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
-                           int max_partial_rows, StepPlan* plan, const int32_t* len_cap, int heads_per_kv) {
+                           int max_partial_rows, StepPlan* plan, const int32_t* len_cap, int heads_per_kv,
+                           int prefill_rows) {
     if (n_seqs < 0 || (n_seqs > 0 && !seqs) || !plan) return ST_INVALID_ARG;
     const int ps = page_size_;
     if (chunk_tokens < 0 || chunk_tokens % ps != 0) return ST_INVALID_ARG;
@@ -440,9 +441,10 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
     plan->pf_items.clear(); plan->pf_small_items.clear();
     plan->pf_small_nq_max = 0; plan->pf_partial_rows = 0; plan->pf_groups = 0;
     const int G = heads_per_kv;
-    if (!fp8 && !len_cap && G > 0 && G <= kDecodeTileRows && plan->nq_min >= 1 &&
+    if (!fp8 && !len_cap && G > 0 && G <= kDecodeTileRows && prefill_rows % G == 0 && plan->nq_min >= 1 &&
         (int64_t)plan->nq_max * G > (int64_t)kDecodeTileRows * kDecodeMaxTokenGroups) {
-        const int tpt = kPrefillRows / G;                      // query tokens per tile
+        const int tpt = prefill_rows / G;                      // query tokens per tile
+        plan->pf_rows = prefill_rows;
         const int max_ct = kPrefillMaxPages * ps;
         plan->pf_ct.assign(n_seqs, 0); plan->pf_poff.assign(n_seqs, 0); plan->pf_cbase.assign(n_seqs, 0);
         auto is_small = [&](int i) { return plan->nq[i] * G <= kDecodeTileRows; };

@@ -71,10 +71,12 @@ struct StepPlan {
     int32_t pf_small_nq_max = 0;           // most tokens a sequence of pf_small_items appends
     int32_t pf_partial_rows = 0;           // token rows the split regions take
     int32_t pf_groups = 0;                 // (sequence, kv head, tile) groups = arrival counters in use
+    int32_t pf_rows = 0;                   // (token, head) rows per tile the lists were laid out for
 };
 
 // Geometry of the prefill kernel's work list, shared by the planner and the kernel.
-constexpr int kPrefillRows = 64;           // (token, head) rows per tile
+constexpr int kPrefillRows = 64;           // (token, head) rows per tile of the mma.sync prefill kernel
+constexpr int kPrefillRowsTc = 128;        // ... of the tcgen05 prefill kernel
 constexpr int kPrefillMaxPages = 2048;     // pages per item: a split-KV chunk holds at most 32768 tokens
 constexpr int kDecodeTileRows = 16;        // rows of the decode kernel's tile
 constexpr int kDecodeMaxTokenGroups = 8;   // token groups per sequence the decode kernel's multi-token form takes
@@ -132,10 +134,11 @@ public:
     // chunk_tokens == 0 picks a chunk so that about `target_items` items exist.
     // len_cap (optional, 16-bit storage only) limits the attended prefix of each sequence.
     // heads_per_kv > 0 (16-bit storage): also lay out the prefill work lists when a sequence appends
-    // more tokens than the decode kernel's token groups hold.
+    // more tokens than the decode kernel's token groups hold, in tiles of prefill_rows (token, head) rows.
     int plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                   bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
-                  int max_partial_rows, StepPlan* plan, const int32_t* len_cap = nullptr, int heads_per_kv = 0);
+                  int max_partial_rows, StepPlan* plan, const int32_t* len_cap = nullptr, int heads_per_kv = 0,
+                  int prefill_rows = kPrefillRows);
 
     // Snapshot of the whole bookkeeping state (lengths, page tables, free lists, reference counts, cold ids)
     // as a flat int32 image, and its restore into a manager of the same geometry: a failing churn run can be

@@ -1,0 +1,425 @@
+// prefill_tc.cu — attention for every token of a prefill chunk on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory), head_dim 128, 16-bit pools.
+//
+// Same work and arithmetic contract as prefill_mma.cu (the reference runs its layer once per prompt token:
+// src/inference/engine.cpp:182-193; per token: attention_decode_kernel, src/compute/cuda/attention.cu:58-157),
+// same work list; what changes is the engine.  With T * G >= 128 (token, head) rows per kv head the tile
+// is a contraction the tcgen05 instruction takes whole: M = 128 rows = the 128 lanes of tensor memory.
+//
+// One CTA = one tile of 128 rows x a range of the context, 128 threads, thread t owns row t (TMEM lane t:
+// no shuffles in the softmax).  Per block of 64 context tokens (4 pages):
+//   TMA      K rows and V rows of the 4 pages land as [64 tokens][128 B] slabs per 64-dim half (128-byte
+//            swizzle): separate boxes of 16 rows, so that the K rows of consecutive pages are consecutive
+//   S = Q K^T  one thread issues 8 tcgen05.mma (M 128, N 64, K 16) with Q and K from shared memory (K-major
+//            descriptors), S in TMEM columns [0, 64); tcgen05.commit -> mbarrier
+//   softmax  every thread tcgen05.ld's its row of S, masks (causal limit of its token, end of the sequence),
+//            running max / sum, P = exp2(..) rounded to the 16-bit type, tcgen05.st into TMEM columns [64, 96);
+//            when a row's maximum moved, the warp rescales its rows of O in TMEM (ld, multiply, st)
+//   O += P V   4 tcgen05.mma (M 128, N 128, K 16) with P from TMEM and V from shared memory (MN-major
+//            descriptor: V rows are tokens), O in TMEM columns [128, 256)
+// Two CTAs share an SM (256 TMEM columns and 98 KB of shared memory each), so one CTA's softmax overlaps the
+// other's MMAs.  No cluster, no multicast, cta_group::1 only, this GPU's memory only.
+// Every mbarrier wait is bounded; on expiry the status word is set, nothing is written, and the CTA still
+// frees its tensor memory before it returns.
+#include "tk_kernels.cuh"
+#include "tk_merge.cuh"
+#include "tk_mma.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cudaTypedefs.h>
+
+namespace tk {
+
+namespace {
+
+constexpr int kTcRows = 128;                    // rows per tile = TMEM lanes
+constexpr int kTcBlock = 64;                    // context tokens per block (4 pages)
+constexpr int kTcD = 128;
+constexpr int kTcStages = 2;
+constexpr int kQBytes = 2 * kTcRows * 128;      // two 64-dim halves of [128 rows][128 B]
+constexpr int kSlabBytes = 2 * kTcBlock * 128;  // K (or V) of one block: two halves of [64 tokens][128 B]
+constexpr int kHalfBytes = kTcBlock * 128;      // one 64-dim half of a slab
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColP = 64, kColO = 128;
+constexpr int kTcSmem = kQBytes + 2 * kTcStages * kSlabBytes + 256 + kPrefillMaxPages * 4 + 1024;
+
+// ---- tcgen05 / TMEM primitives -------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void tc_mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: register i of thread t = column i of lane (warp's base lane + t)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr),
+          "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (sm_100 format:
+// address, leading and stride byte offsets in 16-byte units, descriptor version 1, layout type 2).
+//   K-major operand (Q, K: rows of 128 B hold 64 consecutive dims): lbo is not used by the swizzled form
+//   MN-major operand (V: rows are tokens, the MMA's N runs along the row): lbo = bytes between the two
+//   64-dim halves of the slab
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((1024u >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;                                 // descriptor version (Blackwell)
+    d |= (uint64_t)2 << 61;                                 // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor of kind::f16: F32 accumulate, A/B format (0 f16, 1 bf16), B major, N, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(bool bf16, bool b_mn_major, int n) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kTcRows >> 4) << 24);
+}
+
+template <bool BF>
+__global__ void __launch_bounds__(128, 2)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev st, PrefillDev pf,
+                  const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q, void* __restrict__ out,
+                  int out_dtype, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ status) {
+    constexpr int D = kTcD;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* s_q = smem;                                     // [2 halves][128 rows][128 B]
+    uint8_t* s_k = s_q + kQBytes;                            // [stages][2 halves][64 tokens][128 B]
+    uint8_t* s_v = s_k + kTcStages * kSlabBytes;
+    uint64_t* bars = (uint64_t*)(s_v + kTcStages * kSlabBytes);
+    uint64_t* kfull = bars;                                  // [stages]
+    uint64_t* vfull = bars + kTcStages;                      // [stages]
+    uint64_t* bar_s = bars + 2 * kTcStages;                  // S of a block is in TMEM
+    uint64_t* bar_o = bar_s + 1;                             // O += P V of a block is done
+    uint32_t* s_tmem = (uint32_t*)(bar_o + 1);               // TMEM base address from the allocator
+    int* s_flag = (int*)(s_tmem + 1);
+    int32_t* s_pages = (int32_t*)((uint8_t*)bars + 256);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int G = g.H / g.Hkv;
+    const int4 it = pf.items[blockIdx.x];
+    const int b = it.x, chunk = it.y, kvh = it.z, tile = it.w;
+    const int seq = st.seq[b], len = st.len[b], nq = st.nq[b];
+    const int ct = pf.ct[b];
+    const int tpt = kTcRows / G;                            // query tokens per tile
+    const int tok_first = tile * tpt;
+    const int tok_cnt = min(nq - tok_first, tpt);
+    const int base_pos = len - nq;
+    const int p_last = base_pos + tok_first + tok_cnt - 1;
+    const int t0 = chunk * ct;
+    const int t1 = min(t0 + ct, p_last + 1);
+    const int n_pages = (t1 - t0 + kPage - 1) / kPage;
+    const int n_blocks = (n_pages + 3) / 4;
+    const int lp0 = t0 / kPage;
+    const int n_chunks = p_last / ct + 1;
+
+    // this thread's row: query token tid / G of the tile, head tid % G of the group
+    const bool valid = tid / G < tok_cnt;
+    const int lim = base_pos + tok_first + tid / G + 1;     // positions the row attends to: [0, lim)
+    const size_t qo_row = (size_t)(st.q_base[b] + tok_first + tid / G) * g.H + (size_t)kvh * G + tid % G;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2 * kTcStages + 2; i++) mbar_init(smem_u32(&bars[i]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {                                        // one warp allocates the CTA's tensor memory
+        tmem_alloc(smem_u32(s_tmem), kTmemCols);
+        tmem_relinquish();
+    }
+    for (int i = tid; i < n_pages; i += blockDim.x)
+        s_pages[i] = page_table[(size_t)seq * g.max_pages_per_seq + lp0 + i];
+    // Q row -> shared memory in the 128-byte-swizzled K-major form the MMA reads (16-byte chunk c of a row
+    // sits at chunk c ^ (row & 7)); rows without a token are zero
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(q + qo_row * D);
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+            const uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(s_q + (c >> 3) * (kTcRows * 128) + tid * 128 + (((c & 7) ^ (tid & 7)) << 4)) = v;
+        }
+    }
+    // V slabs start as zeros: a block whose last pages do not exist must not feed stale bits to 0 * V
+    for (int i = tid; i < kTcStages * kSlabBytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(s_v)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes above -> visible to TMA / MMA
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;  // this warp's 32 TMEM lanes
+
+    // thread 0: K and V rows of block `blk` -> stage blk % 2 (a box of 16 rows x 128 B per page, half and K|V)
+    auto issue_block = [&](int blk) {
+        const int s = blk % kTcStages;
+        const int pages = min(4, n_pages - 4 * blk);
+        const uint32_t kb = smem_u32(&kfull[s]), vb = smem_u32(&vfull[s]);
+        mbar_expect_tx(kb, pages * 2 * 2048);
+        mbar_expect_tx(vb, pages * 2 * 2048);
+        for (int p = 0; p < pages; p++) {
+            const int row = (s_pages[4 * blk + p] * g.Hkv + kvh) * 32;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                tma_load_2d_shared_tile(smem_u32(s_k + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, kb);
+                tma_load_2d_shared_tile(smem_u32(s_v + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row + 16, vb);
+            }
+        }
+    };
+    constexpr uint32_t kIdescS = instr_desc(BF, false, kTcBlock);
+    constexpr uint32_t kIdescO = instr_desc(BF, true, D);
+    // thread 0: S = Q K^T of block `blk` (8 k-steps of 16 dims: 4 per 64-dim half, 32 bytes apart inside the swizzled row)
+    auto issue_s = [&](int blk) {
+        const int s = blk % kTcStages;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+            const uint32_t off = (ks >> 2) * (kTcRows * 128) + (ks & 3) * 32;
+            const uint32_t koff = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+            tc_mma_ss(tmem + kColS, smem_desc(smem_u32(s_q) + off, 16), smem_desc(smem_u32(s_k + s * kSlabBytes) + koff, 16),
+                      kIdescS, ks > 0);
+        }
+        tc_commit(smem_u32(bar_s));
+    };
+
+    float m_run = -1e30f, l_run = 0.0f;
+    const float sm_scale = 1.0f / sqrtf((float)D);
+    bool alive = true;
+
+    if (tid == 0) {
+        issue_block(0);
+        if (n_blocks > 1) issue_block(1);
+        if (mbar_wait_bounded(smem_u32(&kfull[0]), 0u, status)) issue_s(0);
+    }
+
+    for (int blk = 0; blk < n_blocks; blk++) {
+        const int s = blk % kTcStages;
+        const int tok_base = t0 + blk * kTcBlock;
+        // ---- S of this block ----
+        if (!__syncthreads_and(mbar_wait_bounded(smem_u32(bar_s), (uint32_t)(blk & 1), status))) { alive = false; break; }
+        tc_fence_after();
+        uint32_t sr[2][32];
+        tmem_ld32(tmem + lane_base + kColS, sr[0]);
+        tmem_ld32(tmem + lane_base + kColS + 32, sr[1]);
+        tc_wait_ld();
+
+        // ---- online softmax of the row (reference arithmetic: scale after the dot, max from -1e30) ----
+        const int nv = valid ? max(0, min(min(kTcBlock, t1 - tok_base), lim - tok_base)) : 0;
+        float mx = -1e30f;
+#pragma unroll
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+                float a = __uint_as_float(sr[h][c]) * sm_scale;
+                if (32 * h + c >= nv) a = -1e30f;
+                sr[h][c] = __float_as_uint(a);
+                mx = fmaxf(mx, a);
+            }
+        const float mn = fmaxf(m_run, mx);
+        const float alpha = ex2((m_run - mn) * kLog2e);
+        const float nb = -mn * kLog2e;
+        float sum = 0.0f;
+        uint32_t pr[32];                                     // P of the row: 64 values, two 16-bit per register
+#pragma unroll
+        for (int c = 0; c < 32; c++) {
+            // a row may see nothing of a block: exp(-1e30 + 1e30) is 1, not 0
+            const float p0 = 2 * c < nv ? ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), kLog2e, nb)) : 0.0f;
+            const float p1 = 2 * c + 1 < nv ? ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), kLog2e, nb)) : 0.0f;
+            sum += p0 + p1;
+            pr[c] = pack2<BF>(p0, p1);
+        }
+        l_run = l_run * alpha + sum;
+        const bool moved = mn != m_run;
+        m_run = mn;
+
+        // ---- O += P V of the previous block must be done before P is overwritten and O rescaled ----
+        if (blk > 0) {
+            if (!__syncthreads_and(mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) { alive = false; break; }
+            tc_fence_after();
+            if (tid == 0 && blk + 1 < n_blocks) issue_block(blk + 1);      // its stages were block blk-1's
+            if (__any_sync(0xFFFFFFFFu, moved)) {            // this warp's rows of O *= alpha
+#pragma unroll
+                for (int part = 0; part < 4; part++) {
+                    uint32_t orow[32];
+                    tmem_ld32(tmem + lane_base + kColO + 32 * part, orow);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+                    tmem_st32(tmem + lane_base + kColO + 32 * part, orow);
+                }
+            }
+        }
+        tmem_st32(tmem + lane_base + kColP, pr);
+        tc_wait_st();
+
+        // rows past the sequence's end hold whatever the page's last owner left: zero those V rows of the slab
+        const int n_live = len - tok_base;                   // tokens of the sequence in this block
+        if (n_live < kTcBlock && n_live < 16 * min(4, n_pages - 4 * blk)) {
+            if (!__syncthreads_and(mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status))) { alive = false; break; }
+            const int r0 = max(n_live, 0), n_rows = kTcBlock - r0;
+            for (int i = tid; i < n_rows * 16; i += blockDim.x) {
+                const int r = r0 + (i >> 4), c = i & 15;
+                *reinterpret_cast<uint4*>(s_v + s * kSlabBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        tc_fence_before();
+        __syncthreads();                                     // every row's P is in TMEM, S has been read
+
+        // ---- O += P V of this block, then S of the next ----
+        if (tid == 0) {
+            tc_fence_after();
+            bool ok = mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status);
+            if (ok) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++)               // 16 tokens per MMA: 8 TMEM columns of P, 16 rows of the V slab
+                    tc_mma_ts(tmem + kColO, tmem + kColP + 8 * ks, smem_desc(smem_u32(s_v + s * kSlabBytes) + ks * 2048, kHalfBytes),
+                              kIdescO, (blk > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(smem_u32(bar_o));
+                if (blk + 1 < n_blocks &&
+                    mbar_wait_bounded(smem_u32(&kfull[(blk + 1) % kTcStages]), (uint32_t)(((blk + 1) / kTcStages) & 1), status))
+                    issue_s(blk + 1);
+            }
+        }
+    }
+
+    // ---- the last block's O ----
+    if (alive && !__syncthreads_and(mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((n_blocks - 1) & 1), status))) alive = false;
+    tc_fence_after();
+    const bool poisoned = !alive || __ldcg(status) != 0;     // fail closed
+
+    if (!poisoned) {
+        float* prow = nullptr;
+        if (n_chunks > 1)                                    // split context: (o, m, l) of this chunk into the sequence's region
+            prow = partials + (size_t)pf.poff[b] * g.H * (D + 2) +
+                   partial_off(chunk, (tok_first + tid / G) * g.H + kvh * G + tid % G, nq * g.H, D);
+        const float inv = 1.0f / (l_run + 1e-8f);
+#pragma unroll
+        for (int part = 0; part < 4; part++) {
+            uint32_t orow[32];
+            tmem_ld32(tmem + lane_base + kColO + 32 * part, orow);
+            tc_wait_ld();
+            if (!valid) continue;
+            if (n_chunks > 1) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 2)
+                    *reinterpret_cast<float2*>(prow + 32 * part + c) = make_float2(__uint_as_float(orow[c]), __uint_as_float(orow[c + 1]));
+            } else if (out_dtype == DT_FP32) {
+#pragma unroll
+                for (int c = 0; c < 32; c += 4)
+                    *reinterpret_cast<float4*>((float*)out + qo_row * D + 32 * part + c) =
+                        make_float4(__uint_as_float(orow[c]) * inv, __uint_as_float(orow[c + 1]) * inv,
+                                    __uint_as_float(orow[c + 2]) * inv, __uint_as_float(orow[c + 3]) * inv);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; c += 8) {
+                    uint4 w;
+                    w.x = pack2<BF>(__uint_as_float(orow[c]) * inv, __uint_as_float(orow[c + 1]) * inv);
+                    w.y = pack2<BF>(__uint_as_float(orow[c + 2]) * inv, __uint_as_float(orow[c + 3]) * inv);
+                    w.z = pack2<BF>(__uint_as_float(orow[c + 4]) * inv, __uint_as_float(orow[c + 5]) * inv);
+                    w.w = pack2<BF>(__uint_as_float(orow[c + 6]) * inv, __uint_as_float(orow[c + 7]) * inv);
+                    *reinterpret_cast<uint4*>((uint16_t*)out + qo_row * D + 32 * part + c) = w;
+                }
+            }
+        }
+        if (n_chunks > 1 && valid) *reinterpret_cast<float2*>(prow + D) = make_float2(m_run, l_run);
+    }
+
+    // ---- tensor memory goes back on every path ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+    if (n_chunks == 1) return;
+
+    // the CTA that arrives last for the tile merges its chunks (nothing is written while the status word is set)
+    if (tid == 0) {
+        __threadfence();
+        const int tiles = (nq + tpt - 1) / tpt;
+        int* c = counters + pf.cbase[b] + kvh * tiles + tile;
+        const int ticket = atomicAdd(c, 1);
+        const int last = ticket == n_chunks - 1;
+        if (last) *c = 0;
+        *s_flag = last;
+    }
+    __syncthreads();
+    if (*s_flag) {
+        const MergeOut mo{nullptr, out, nullptr, out_dtype, nullptr, status};
+        merge_rows(g, mo, b, kvh, G, 0, n_chunks, partials + (size_t)pf.poff[b] * g.H * (D + 2),
+                   MergeMap{G * tok_cnt, nq * g.H, st.q_base[b] + tok_first, tok_first, 0});
+    }
+}
+
+}  // namespace
+
+// 128-row tiles on tcgen05: 16-bit pools, head_dim 128, page size 16, groups that divide 128.
+bool prefill_tc_supported(const Geometry& g) {
+    return decode_mma_supported(g) && g.dtype != DT_FP8 && g.D == kTcD && g.Hkv > 0 && kTcRows % (g.H / g.Hkv) == 0;
+}
+
+// `map16`: the layer's pool as rows of D elements with a box of 16 rows x 64 elements (make_pool_tensor_map
+// with box_rows = 16).  Work list, counters and split regions as for launch_prefill_mma, with tiles of 128 rows.
+cudaError_t launch_prefill_tc(const Geometry& g, const CUtensorMap* map16, const StepDev& st, const PrefillDev& pf,
+                              const int32_t* page_table, const void* q, void* out, int out_dtype, float* partials,
+                              int* counters, int* status, cudaStream_t s) {
+    if (pf.n_items <= 0) return cudaSuccess;
+    if (!prefill_tc_supported(g) || !counters || !status) return cudaErrorNotSupported;
+    if (out_dtype != DT_FP32 && out_dtype != g.io_dtype) return cudaErrorInvalidValue;
+    static bool attr_done[2][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int bf = g.dtype == DT_BF16;
+    if (dev < 0 || dev >= 64 || !attr_done[bf][dev]) {
+        cudaError_t e = bf ? cudaFuncSetAttribute(prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem)
+                           : cudaFuncSetAttribute(prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) attr_done[bf][dev] = true;
+    }
+    if (bf) prefill_tc_kernel<true><<<pf.n_items, 128, kTcSmem, s>>>(*map16, g, st, pf, page_table, (const uint16_t*)q, out,
+                                                                     out_dtype, partials, counters, status);
+    else    prefill_tc_kernel<false><<<pf.n_items, 128, kTcSmem, s>>>(*map16, g, st, pf, page_table, (const uint16_t*)q, out,
+                                                                      out_dtype, partials, counters, status);
+    return cudaGetLastError();
+}
+
+}  // namespace tk

@@ -74,6 +74,7 @@ const char* validate(const tk_kv_config& c) {
     if (c.decode_impl < TK_DECODE_AUTO || c.decode_impl > TK_DECODE_MMA) return "bad decode_impl";
     if (c.merge_impl != TK_MERGE_IN_KERNEL && c.merge_impl != TK_MERGE_SEPARATE) return "bad merge_impl";
     if (c.launch_overlap != TK_OVERLAP_AUTO && c.launch_overlap != TK_OVERLAP_OFF) return "bad launch_overlap";
+    if (c.prefill_impl != TK_PREFILL_AUTO && c.prefill_impl != TK_PREFILL_MMA_SYNC) return "bad prefill_impl";
     if (c.hot_window < 0 || c.cold_pages < 0) return "hot_window and cold_pages must not be negative";
     if (c.hot_window > 0) {
         if (c.hot_window < c.page_size) return "hot_window must cover at least one page";
@@ -135,6 +136,8 @@ struct tk_kv {
 
     std::vector<CUtensorMap> maps;       // one per layer (MMA path); MLA shape: the K-row view
     std::vector<CUtensorMap> maps_v;     // MLA shape: the V-row view
+    std::vector<CUtensorMap> maps16;     // boxes of 16 rows (the K or V rows of a page): tcgen05 prefill kernel
+    bool prefill_tc = false;             // prefill chunks go to the tcgen05 kernel (128-row tiles)
     float* d_xpartial = nullptr;         // this rank's merged partial rows for tk_kv_decode_exchange
     float* d_multi_partials = nullptr;   // split-KV rows of multi-token steps that outgrow d_partials
     size_t multi_partials_floats = 0;
@@ -277,7 +280,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     h->max_seals = c.max_step_tokens / c.page_size + c.max_seqs;
     {   // prefill work list: tiles of 64 rows per (sequence, kv head), times the split-KV chunks a tile may see
         const int G = c.num_heads / c.num_kv_heads;
-        const int64_t tiles = (int64_t)c.max_step_tokens * G / tk::kPrefillRows + c.max_seqs;
+        const int64_t tiles = (int64_t)c.max_step_tokens * G / tk::kPrefillRows + c.max_seqs;      // the smaller tile: the upper bound
         const int64_t long_chunks = ((int64_t)c.max_pages_per_seq + tk::kPrefillMaxPages - 1) / tk::kPrefillMaxPages;
         h->max_pf_groups = (int)std::min<int64_t>(tiles * c.num_kv_heads, 1 << 24);
         h->max_pf_items = (int)std::min<int64_t>(tiles * c.num_kv_heads * long_chunks + 128 * (int64_t)c.max_seqs, 1 << 24);
@@ -377,6 +380,12 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
         for (int l = 0; l < c.num_layers; l++) {
             if (h->mla_mma) CREATE_CUDA(tk::make_mla_tensor_maps(h->geo, h->layer(l).pool, &h->maps[l], &h->maps_v[l]));
             else CREATE_CUDA(tk::make_pool_tensor_map(h->geo, h->layer(l).pool, &h->maps[l]));
+        }
+        h->prefill_tc = !h->mla_mma && c.prefill_impl != TK_PREFILL_MMA_SYNC && c.hot_window == 0 && tk::prefill_tc_supported(h->geo);
+        if (h->prefill_tc) {
+            h->maps16.resize(c.num_layers);
+            for (int l = 0; l < c.num_layers; l++)
+                CREATE_CUDA(tk::make_pool_tensor_map(h->geo, h->layer(l).pool, &h->maps16[l], 16));
         }
     }
     if (c.hot_window > 0) {
@@ -670,7 +679,7 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     // the tensor-core kernel keeps one page id per lane per warp: chunk <= 16*4*32 tokens
     int st = h->mgr->plan_step(n_seqs, seq_ids, n_new, h->cfg.num_kv_heads, h->cfg.dtype == TK_FP8_E4M3,
                                chunk, target, h->cfg.max_step_tokens, h->max_partial_rows, &h->plan, len_cap,
-                               h->geo.H / h->geo.Hkv);
+                               h->geo.H / h->geo.Hkv, h->prefill_tc ? tk::kPrefillRowsTc : tk::kPrefillRows);
     if (st != TK_OK) return fail(h, st, "step_begin: %s", tk_status_str(st));
     tk::StepPlan& p = h->plan;
     if (chunk == 0 && p.chunk_tokens > 2048) {
@@ -1018,8 +1027,12 @@ static int decode_multi_impl(tk_kv* h, int32_t layer, const void* q, void* out, 
             if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "decode_multi launch: %s", cudaGetErrorString(e));
         }
         float* pf_partials = ws + small_rows * row_floats;
-        e = tk::launch_prefill_mma(h->geo, &h->maps[layer], h->dev, h->pf_dev, h->d_table, q, out, out_dtype, pf_partials,
-                                   h->d_pf_counters, h->d_status, (cudaStream_t)stream);
+        if (h->prefill_tc && p.pf_rows == tk::kPrefillRowsTc)
+            e = tk::launch_prefill_tc(h->geo, &h->maps16[layer], h->dev, h->pf_dev, h->d_table, q, out, out_dtype, pf_partials,
+                                      h->d_pf_counters, h->d_status, (cudaStream_t)stream);
+        else
+            e = tk::launch_prefill_mma(h->geo, &h->maps[layer], h->dev, h->pf_dev, h->d_table, q, out, out_dtype, pf_partials,
+                                       h->d_pf_counters, h->d_status, (cudaStream_t)stream);
         if (h->pf_dev.n_items > 0) h->launches++;
         if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, "prefill attention launch: %s", cudaGetErrorString(e));
         return TK_OK;

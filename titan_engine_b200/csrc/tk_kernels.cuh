@@ -140,7 +140,7 @@ cudaError_t launch_decode_simt(const Geometry& g, const LayerPtrs& lp, const Ste
 
 // TMA + mma.sync decode (16-bit and FP8 pools, page size 16, D in {64,128}).
 bool        decode_mma_supported(const Geometry& g);
-cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out);
+cudaError_t make_pool_tensor_map(const Geometry& g, void* layer_pool, CUtensorMap* out, int box_rows = 32);
 cudaError_t launch_decode_mma(const Geometry& g, const LayerPtrs& lp, const CUtensorMap* map,
                               const CUtensorMap* map_cold, const StepDev& st, const int32_t* page_table, const void* q,
                               float* partials, int* status, cudaStream_t s,
@@ -160,6 +160,13 @@ bool        prefill_mma_supported(const Geometry& g);
 cudaError_t launch_prefill_mma(const Geometry& g, const CUtensorMap* map, const StepDev& st, const PrefillDev& pf,
                                const int32_t* page_table, const void* q, void* out, int out_dtype, float* partials,
                                int* counters, int* status, cudaStream_t s);
+
+// The same on tcgen05 / tensor memory: tiles of 128 rows (pf.items laid out for 128-row tiles), head_dim 128;
+// `map16` is make_pool_tensor_map(..., box_rows = 16).
+bool        prefill_tc_supported(const Geometry& g);
+cudaError_t launch_prefill_tc(const Geometry& g, const CUtensorMap* map16, const StepDev& st, const PrefillDev& pf,
+                              const int32_t* page_table, const void* q, void* out, int out_dtype, float* partials,
+                              int* counters, int* status, cudaStream_t s);
 
 // The same for the MLA cache shape (K rows 192, V rows 128; 16-bit pools, groups of <= 8 heads).
 bool        decode_mma_mla_supported(const Geometry& g);

@@ -47,7 +47,7 @@ class PagedKVCache:
                  max_step_tokens: Optional[int] = None, chunk_tokens: int = 0,
                  decode_impl: str = "auto", device: Optional[int] = None, host_only: bool = False,
                  hot_window: int = 0, cold_pages: int = 0, v_head_dim: int = 0, separate_combine: bool = False,
-                 launch_overlap: bool = True):
+                 launch_overlap: bool = True, prefill_impl: str = "auto"):
         self._lib = L.lib()
         cfg = L.KvConfig()
         self._lib.tk_kv_config_default(C.byref(cfg))
@@ -60,6 +60,7 @@ class PagedKVCache:
         cfg.hot_window, cfg.cold_pages, cfg.v_head_dim = hot_window, cold_pages, v_head_dim
         cfg.merge_impl = L.TK_MERGE_SEPARATE if separate_combine else L.TK_MERGE_IN_KERNEL
         cfg.launch_overlap = L.TK_OVERLAP_AUTO if launch_overlap else L.TK_OVERLAP_OFF
+        cfg.prefill_impl = {"auto": L.TK_PREFILL_AUTO, "mma_sync": L.TK_PREFILL_MMA_SYNC}[prefill_impl]
         self._h = C.c_void_p()
         self.host_only = host_only
         self._arena = None
