@@ -807,7 +807,7 @@ def run_multi(args):
     """`--multi K`: K new tokens per sequence and step, each with its own causal attention output
     (tk_kv_append_decode_multi).  Small K on the workload's 64 long contexts is the verification step of a
     speculative decoder; K >= 256 is a prefill chunk: 16 fresh sequences that append K tokens per step (the
-    chunk attends to everything before it), which is where the 64-row tiles of the prefill kernel make the
+    chunk attends to everything before it), which is where the 128-row tiles of the prefill kernel make the
     work a contraction.  Prints one JSON line with the time per layer and per token-layer and, for prefill
     chunks, the achieved tensor throughput; not the headline metric."""
     import torch
@@ -822,7 +822,7 @@ def run_multi(args):
     reps = args.warmup + args.steps
     pages_end = (ctx + reps * K + ps - 1) // ps
     cache = PagedKVCache(L, s["H"], s["Hkv"], s["D"], int(pages_end.sum()) + 64, B, int(pages_end.max()) + 1, dtype="bf16",
-                         max_step_tokens=B * K)
+                         max_step_tokens=B * K, prefill_impl=args.prefill_impl)
     seqs, at = [], 0
     for b in range(B):
         sid = cache.seq_alloc()
@@ -889,7 +889,9 @@ def run_multi(args):
                                         "unit": "TFLOP/s", "frac": float(np.median(per_step)) / tf_peak,
                                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (cuBLAS)" if peaks else
                                                        "fallback 1.4 PFLOP/s",
-                                        "note": "mma.sync m16n8k16 tiles; flops count the causal half only"}}
+                                        "kernel": "prefill_mma_kernel (mma.sync m16n8k16, 64-row tiles)" if args.prefill_impl == "mma_sync"
+                                                  else "prefill_tc_kernel (tcgen05.mma, accumulators in tensor memory, 128-row tiles)",
+                                        "note": "flops count the causal half only"}}
     print(json.dumps(line), flush=True)
 
 
@@ -914,6 +916,8 @@ def main():
     ap.add_argument("--seqs", type=int, default=0, help="sequences per GPU instead of the workload's (reported in config)")
     ap.add_argument("--append-prefill", type=int, default=0, metavar="T",
                     help="measure the append kernels alone: one prefill step of T tokens per sequence and layer")
+    ap.add_argument("--prefill-impl", default="auto", choices=["auto", "mma_sync"],
+                    help="--multi: the prefill kernel (auto: tcgen05 at head_dim 128; mma_sync: the warp-level kernel)")
     ap.add_argument("--multi", type=int, default=0, metavar="K",
                     help="measure multi-token attention: K new tokens per sequence and step")
     args = ap.parse_args()

@@ -62,7 +62,8 @@ class Twin:
     """
 
     def __init__(self, L, H, Hkv, D, num_pages, max_seqs, mpps, dtype="bf16", impl="auto",
-                 chunk_tokens=0, max_step_tokens=4096, io=None, seed=0, hot_window=0, cold_pages=0, Dv=None):
+                 chunk_tokens=0, max_step_tokens=4096, io=None, seed=0, hot_window=0, cold_pages=0, Dv=None,
+                 prefill_impl="auto"):
         import torch
         from titan_engine_b200 import PagedKVCache
         self.torch = torch
@@ -72,7 +73,8 @@ class Twin:
         self.carrier = DT[io] if io else (O.BF16 if self.dt == O.FP8 else self.dt)
         self.gpu = PagedKVCache(L, H, Hkv, D, num_pages, max_seqs, mpps, dtype=dtype, io_dtype=io,
                                 decode_impl=impl, chunk_tokens=chunk_tokens, max_step_tokens=max_step_tokens,
-                                hot_window=hot_window, cold_pages=cold_pages, v_head_dim=self.Dv if self.Dv != D else 0)
+                                hot_window=hot_window, cold_pages=cold_pages, v_head_dim=self.Dv if self.Dv != D else 0,
+                                prefill_impl=prefill_impl)
         self.mgr = O.Manager(num_pages, max_seqs, mpps, 16)
         # With a cold tier the oracle keeps two managers: `mgr` follows the tiering rule (page/slot
         # state parity), `flat` holds the same logical data in one untiered pool (attention parity:

@@ -654,19 +654,24 @@ def test_decode_multi_tokens_causal(shape):
 
 
 @pytest.mark.parametrize("shape", [
-    # H, Hkv, D, dtype
-    (32, 8, 128, "bf16"),     # 8B head shape: 16 tokens per 64-row tile
-    (64, 8, 128, "fp16"),     # 70B head shape: 8 tokens per tile
-    (8, 2, 64, "fp16"),       # tiny config
-    (16, 16, 128, "bf16"),    # MHA: 64 tokens per tile
-    (16, 1, 64, "bf16"),      # 16 heads per kv head: 4 tokens per tile
+    # H, Hkv, D, dtype, prefill kernel
+    (32, 8, 128, "bf16", "auto"),      # 8B head shape on tcgen05: 32 tokens per 128-row tile
+    (32, 8, 128, "bf16", "mma_sync"),  # ... and on the mma.sync kernel: 16 tokens per 64-row tile
+    (64, 8, 128, "fp16", "auto"),      # 70B head shape
+    (64, 8, 128, "fp16", "mma_sync"),
+    (8, 2, 64, "fp16", "auto"),        # tiny config (head_dim 64: mma.sync kernel)
+    (16, 16, 128, "bf16", "auto"),     # MHA: 128 tokens per tile
+    (16, 16, 128, "fp16", "mma_sync"),
+    (16, 1, 128, "bf16", "auto"),      # 16 heads per kv head: 8 tokens per tile
+    (16, 1, 64, "bf16", "auto"),       # ... at head_dim 64: 4 tokens per 64-row tile
 ])
 def test_prefill_chunk_attention_every_token(shape):
     """Prefill chunks through tk_kv_append + tk_kv_decode_multi: a fresh prompt (the chunk is the whole
     context), a chunk on top of a long context (tiles split over the context and merged), short and
-    single-token rows in the same step (they stay with the decode kernel), ragged page boundaries."""
-    H, Hkv, D, dtype = shape
-    t = Twin(2, H, Hkv, D, 700, 6, 400, dtype=dtype, impl="mma", max_step_tokens=4096, seed=120)
+    single-token rows in the same step (they stay with the decode kernel), ragged page boundaries.  Both
+    prefill kernels: tcgen05 with accumulators in tensor memory (head_dim 128) and mma.sync."""
+    H, Hkv, D, dtype, pimpl = shape
+    t = Twin(2, H, Hkv, D, 700, 6, 400, dtype=dtype, impl="mma", max_step_tokens=4096, seed=120, prefill_impl=pimpl)
     a, b, c, d = (t.seq_alloc() for _ in range(4))
     t.step([a, b], [3000, 45], decode=False)                       # a long context and a short one
     t.step([a, b, c, d], [333, 1, 777, 2], every_token=True, check_pool=True)
@@ -678,10 +683,11 @@ def test_prefill_chunk_attention_every_token(shape):
     t.gpu.device_status()
 
 
-def test_prefill_chunk_long_context_split_and_merge():
+@pytest.mark.parametrize("pimpl", ["auto", "mma_sync"])
+def test_prefill_chunk_long_context_split_and_merge(pimpl):
     """A 40-token chunk on a 20000-token context at the 8B head shape: few tiles, so every tile is cut
     into split-KV chunks whose partial rows the last CTA merges; and a 2500-token fresh prompt beside it."""
-    t = Twin(1, 32, 8, 128, 1600, 2, 1400, dtype="bf16", impl="mma", max_step_tokens=4096, seed=121)
+    t = Twin(1, 32, 8, 128, 1600, 2, 1400, dtype="bf16", impl="mma", max_step_tokens=4096, seed=121, prefill_impl=pimpl)
     a, b = t.seq_alloc(), t.seq_alloc()
     t.step([a], [20000 - 4096 * 4], decode=False)
     for _ in range(4):
