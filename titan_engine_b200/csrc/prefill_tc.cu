@@ -11,10 +11,13 @@
 //   TMA      K rows and V rows of the 4 pages land as [64 tokens][128 B] slabs per 64-dim half (128-byte
 //            swizzle): separate boxes of 16 rows, so that the K rows of consecutive pages are consecutive
 //   S = Q K^T  one thread issues 8 tcgen05.mma (M 128, N 64, K 16) with Q and K from shared memory (K-major
-//            descriptors), S in TMEM columns [0, 64); tcgen05.commit -> mbarrier
+//            descriptors), S in one of two TMEM buffers (columns [0, 64) and [64, 128)); tcgen05.commit -> mbarrier.
+//            S of block i+2 is issued right behind P V of block i, S of block i+1 is already there: the tensor
+//            pipe works while the threads do the softmax of block i
 //   softmax  every thread tcgen05.ld's its row of S, masks (causal limit of its token, end of the sequence),
-//            running max / sum, P = exp2(..) rounded to the 16-bit type, tcgen05.st into TMEM columns [64, 96);
-//            when a row's maximum moved, the warp rescales its rows of O in TMEM (ld, multiply, st)
+//            sum and reference maximum in base-2 units, P = exp2(..) rounded to the 16-bit type, tcgen05.st over
+//            the first 32 columns of the S buffer it came from; the reference maximum moves only when a block
+//            exceeds it by 2^8, and only then the warp rescales its rows of O in TMEM (ld, multiply, st)
 //   O += P V   4 tcgen05.mma (M 128, N 128, K 16) with P from TMEM and V from shared memory (MN-major
 //            descriptor: V rows are tokens), O in TMEM columns [128, 256)
 // Two CTAs share an SM (256 TMEM columns and 98 KB of shared memory each), so one CTA's softmax overlaps the
@@ -41,7 +44,7 @@ constexpr int kQBytes = 2 * kTcRows * 128;      // two 64-dim halves of [128 row
 constexpr int kSlabBytes = 2 * kTcBlock * 128;  // K (or V) of one block: two halves of [64 tokens][128 B]
 constexpr int kHalfBytes = kTcBlock * 128;      // one 64-dim half of a slab
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColP = 64, kColO = 128;
+constexpr uint32_t kColS = 0, kColO = 128;       // S buffers at columns 0 and 64 (P over their first 32), O at 128
 constexpr int kTcSmem = kQBytes + 2 * kTcStages * kSlabBytes + 256 + kPrefillMaxPages * 4 + 1024;
 
 // ---- tcgen05 / TMEM primitives -------------------------------------------------------------------------
@@ -134,8 +137,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     uint64_t* bars = (uint64_t*)(s_v + kTcStages * kSlabBytes);
     uint64_t* kfull = bars;                                  // [stages]
     uint64_t* vfull = bars + kTcStages;                      // [stages]
-    uint64_t* bar_s = bars + 2 * kTcStages;                  // S of a block is in TMEM
-    uint64_t* bar_o = bar_s + 1;                             // O += P V of a block is done
+    uint64_t* bar_s = bars + 2 * kTcStages;                  // [2] S of a block is in TMEM (one barrier per S buffer)
+    uint64_t* bar_o = bar_s + 2;                             // O += P V of a block is done
     uint32_t* s_tmem = (uint32_t*)(bar_o + 1);               // TMEM base address from the allocator
     int* s_flag = (int*)(s_tmem + 1);
     int32_t* s_pages = (int32_t*)((uint8_t*)bars + 256);
@@ -164,7 +167,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     const size_t qo_row = (size_t)(st.q_base[b] + tok_first + tid / G) * g.H + (size_t)kvh * G + tid % G;
 
     if (tid == 0) {
-        for (int i = 0; i < 2 * kTcStages + 2; i++) mbar_init(smem_u32(&bars[i]), 1);
+        for (int i = 0; i < 2 * kTcStages + 3; i++) mbar_init(smem_u32(&bars[i]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {                                        // one warp allocates the CTA's tensor memory
@@ -192,20 +195,29 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     const uint32_t tmem = *s_tmem;
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;  // this warp's 32 TMEM lanes
 
-    // thread 0: K and V rows of block `blk` -> stage blk % 2 (a box of 16 rows x 128 B per page, half and K|V)
-    auto issue_block = [&](int blk) {
+    // thread 0: K rows (V rows) of block `blk` -> stage blk % 2: a box of 16 rows x 128 B per page and 64-dim half
+    auto issue_k = [&](int blk) {
         const int s = blk % kTcStages;
         const int pages = min(4, n_pages - 4 * blk);
-        const uint32_t kb = smem_u32(&kfull[s]), vb = smem_u32(&vfull[s]);
+        const uint32_t kb = smem_u32(&kfull[s]);
         mbar_expect_tx(kb, pages * 2 * 2048);
-        mbar_expect_tx(vb, pages * 2 * 2048);
         for (int p = 0; p < pages; p++) {
             const int row = (s_pages[4 * blk + p] * g.Hkv + kvh) * 32;
 #pragma unroll
-            for (int h = 0; h < 2; h++) {
+            for (int h = 0; h < 2; h++)
                 tma_load_2d_shared_tile(smem_u32(s_k + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, kb);
-                tma_load_2d_shared_tile(smem_u32(s_v + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row + 16, vb);
-            }
+        }
+    };
+    auto issue_v = [&](int blk) {
+        const int s = blk % kTcStages;
+        const int pages = min(4, n_pages - 4 * blk);
+        const uint32_t vb = smem_u32(&vfull[s]);
+        mbar_expect_tx(vb, pages * 2 * 2048);
+        for (int p = 0; p < pages; p++) {
+            const int row = (s_pages[4 * blk + p] * g.Hkv + kvh) * 32 + 16;
+#pragma unroll
+            for (int h = 0; h < 2; h++)
+                tma_load_2d_shared_tile(smem_u32(s_v + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, vb);
         }
     };
     constexpr uint32_t kIdescS = instr_desc(BF, false, kTcBlock);
@@ -217,67 +229,83 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
         for (int ks = 0; ks < 8; ks++) {
             const uint32_t off = (ks >> 2) * (kTcRows * 128) + (ks & 3) * 32;
             const uint32_t koff = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-            tc_mma_ss(tmem + kColS, smem_desc(smem_u32(s_q) + off, 16), smem_desc(smem_u32(s_k + s * kSlabBytes) + koff, 16),
-                      kIdescS, ks > 0);
+            tc_mma_ss(tmem + kColS + 64u * (blk & 1), smem_desc(smem_u32(s_q) + off, 16),
+                      smem_desc(smem_u32(s_k + s * kSlabBytes) + koff, 16), kIdescS, ks > 0);
         }
-        tc_commit(smem_u32(bar_s));
+        tc_commit(smem_u32(&bar_s[blk & 1]));
     };
 
-    float m_run = -1e30f, l_run = 0.0f;
-    const float sm_scale = 1.0f / sqrtf((float)D);
+    // Softmax state of this thread's row, in base-2 units: scores are s * (log2e / sqrt(D)), m2 is the reference
+    // maximum the probabilities are taken against.  The reference moves only when a block's maximum exceeds it by
+    // more than kLazy (then O is rescaled); until then probabilities may reach 2^kLazy, which the 16-bit P and
+    // the FP32 sums hold easily, and O / l is unchanged by the choice of reference.
+    constexpr float kLazy = 8.0f;
+    float m2 = -1e30f, l_run = 0.0f;
+    const float sc2 = kLog2e / sqrtf((float)D);
     bool alive = true;
 
     if (tid == 0) {
-        issue_block(0);
-        if (n_blocks > 1) issue_block(1);
+        issue_k(0); issue_v(0);
+        if (n_blocks > 1) { issue_k(1); issue_v(1); }
         if (mbar_wait_bounded(smem_u32(&kfull[0]), 0u, status)) issue_s(0);
+        if (n_blocks > 1 && mbar_wait_bounded(smem_u32(&kfull[1]), 0u, status)) issue_s(1);
     }
 
     for (int blk = 0; blk < n_blocks; blk++) {
-        const int s = blk % kTcStages;
+        const int s = blk % kTcStages, buf = blk & 1;
+        const uint32_t col_s = kColS + 64u * buf;            // S of this block; its first 32 columns become P
         const int tok_base = t0 + blk * kTcBlock;
-        // ---- S of this block ----
-        if (!__syncthreads_and(mbar_wait_bounded(smem_u32(bar_s), (uint32_t)(blk & 1), status))) { alive = false; break; }
+        // ---- S of this block (issued one block ahead: the tensor pipe worked on it during the last softmax) ----
+        if (!__syncthreads_and(mbar_wait_bounded(smem_u32(&bar_s[buf]), (uint32_t)((blk >> 1) & 1), status))) { alive = false; break; }
         tc_fence_after();
         uint32_t sr[2][32];
-        tmem_ld32(tmem + lane_base + kColS, sr[0]);
-        tmem_ld32(tmem + lane_base + kColS + 32, sr[1]);
+        tmem_ld32(tmem + lane_base + col_s, sr[0]);
+        tmem_ld32(tmem + lane_base + col_s + 32, sr[1]);
         tc_wait_ld();
+        if (tid == 0 && blk + 2 < n_blocks) issue_k(blk + 2);     // S(blk) is done with this K stage
 
-        // ---- online softmax of the row (reference arithmetic: scale after the dot, max from -1e30) ----
+        // ---- online softmax of the row ----
         const int nv = valid ? max(0, min(min(kTcBlock, t1 - tok_base), lim - tok_base)) : 0;
+        const bool full = __all_sync(0xFFFFFFFFu, nv == kTcBlock);      // no row of the warp is cut by the diagonal or the end
         float mx = -1e30f;
+        if (full) {
 #pragma unroll
-        for (int h = 0; h < 2; h++)
+            for (int c = 0; c < 32; c++) mx = fmaxf(mx, fmaxf(__uint_as_float(sr[0][c]), __uint_as_float(sr[1][c])));
+        } else {
 #pragma unroll
-            for (int c = 0; c < 32; c++) {
-                float a = __uint_as_float(sr[h][c]) * sm_scale;
-                if (32 * h + c >= nv) a = -1e30f;
-                sr[h][c] = __float_as_uint(a);
-                mx = fmaxf(mx, a);
-            }
-        const float mn = fmaxf(m_run, mx);
-        const float alpha = ex2((m_run - mn) * kLog2e);
-        const float nb = -mn * kLog2e;
-        float sum = 0.0f;
+            for (int h = 0; h < 2; h++)
+#pragma unroll
+                for (int c = 0; c < 32; c++) {
+                    if (32 * h + c >= nv) sr[h][c] = __float_as_uint(-1e30f / sc2);      // masked: far below any score
+                    mx = fmaxf(mx, __uint_as_float(sr[h][c]));
+                }
+        }
+        mx *= sc2;                                           // sc2 > 0: the maximum of the scaled scores
+        const bool moved = mx > m2 + kLazy;
+        const float m_new = moved ? mx : m2;
+        const float alpha = moved ? ex2(m2 - m_new) : 1.0f;  // first block: ex2(-1e30 - mx) = 0
+        const float nb = -m_new;
+        float sum0 = 0.0f, sum1 = 0.0f;
         uint32_t pr[32];                                     // P of the row: 64 values, two 16-bit per register
 #pragma unroll
         for (int c = 0; c < 32; c++) {
-            // a row may see nothing of a block: exp(-1e30 + 1e30) is 1, not 0
-            const float p0 = 2 * c < nv ? ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), kLog2e, nb)) : 0.0f;
-            const float p1 = 2 * c + 1 < nv ? ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), kLog2e, nb)) : 0.0f;
-            sum += p0 + p1;
+            float p0 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sc2, nb));
+            float p1 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sc2, nb));
+            if (!full) {                                     // a row that sees nothing: exp2(-1e30 + 1e30) is 1, not 0
+                if (2 * c >= nv) p0 = 0.0f;
+                if (2 * c + 1 >= nv) p1 = 0.0f;
+            }
+            sum0 += p0; sum1 += p1;
             pr[c] = pack2<BF>(p0, p1);
         }
-        l_run = l_run * alpha + sum;
-        const bool moved = mn != m_run;
-        m_run = mn;
+        l_run = l_run * alpha + (sum0 + sum1);
+        m2 = m_new;
 
-        // ---- O += P V of the previous block must be done before P is overwritten and O rescaled ----
+        // ---- O += P V of the previous block must be done before O is rescaled and its V stage refilled ----
         if (blk > 0) {
             if (!__syncthreads_and(mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) { alive = false; break; }
             tc_fence_after();
-            if (tid == 0 && blk + 1 < n_blocks) issue_block(blk + 1);      // its stages were block blk-1's
+            if (tid == 0 && blk + 1 < n_blocks) issue_v(blk + 1);          // its stage was block blk-1's
             if (__any_sync(0xFFFFFFFFu, moved)) {            // this warp's rows of O *= alpha
 #pragma unroll
                 for (int part = 0; part < 4; part++) {
@@ -290,7 +318,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                 }
             }
         }
-        tmem_st32(tmem + lane_base + kColP, pr);
+        tmem_st32(tmem + lane_base + col_s, pr);             // P over the columns S was read from
         tc_wait_st();
 
         // rows past the sequence's end hold whatever the page's last owner left: zero those V rows of the slab
@@ -305,24 +333,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
         tc_fence_before();
-        __syncthreads();                                     // every row's P is in TMEM, S has been read
+        __syncthreads();                                     // every row's P is in TMEM
 
-        // ---- O += P V of this block, then S of the next ----
+        // ---- O += P V of this block; then S of the block after next into the columns P occupies now ----
         if (tid == 0) {
             tc_fence_after();
-            bool ok = mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status);
-            if (ok) {
+            if (mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status)) {
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)               // 16 tokens per MMA: 8 TMEM columns of P, 16 rows of the V slab
-                    tc_mma_ts(tmem + kColO, tmem + kColP + 8 * ks, smem_desc(smem_u32(s_v + s * kSlabBytes) + ks * 2048, kHalfBytes),
+                    tc_mma_ts(tmem + kColO, tmem + col_s + 8 * ks, smem_desc(smem_u32(s_v + s * kSlabBytes) + ks * 2048, kHalfBytes),
                               kIdescO, (blk > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(smem_u32(bar_o));
-                if (blk + 1 < n_blocks &&
-                    mbar_wait_bounded(smem_u32(&kfull[(blk + 1) % kTcStages]), (uint32_t)(((blk + 1) / kTcStages) & 1), status))
-                    issue_s(blk + 1);
+                // the tensor pipe runs its MMAs in issue order: S(blk+2) overwrites these columns after P V has read them
+                if (blk + 2 < n_blocks &&
+                    mbar_wait_bounded(smem_u32(&kfull[s]), (uint32_t)(((blk + 2) / kTcStages) & 1), status))
+                    issue_s(blk + 2);
             }
         }
     }
+    const float m_run = m2 * 0.6931471805599453f;            // natural-log units, as the split-KV rows carry it
 
     // ---- the last block's O ----
     if (alive && !__syncthreads_and(mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((n_blocks - 1) & 1), status))) alive = false;
