@@ -50,10 +50,6 @@ struct PfCfg {
     static constexpr int SMEM_BYTES = kPfStages * STAGE_BYTES + BAR_BYTES + kPrefillMaxPages * 4 + 1024;
 };
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-
 template <bool BF, int D>
 __global__ void __launch_bounds__(kWarps * 32, 3)
 prefill_mma_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev st, PrefillDev pf,

@@ -6,8 +6,9 @@
 // same work list; what changes is the engine.  With T * G >= 128 (token, head) rows per kv head the tile
 // is a contraction the tcgen05 instruction takes whole: M = 128 rows = the 128 lanes of tensor memory.
 //
-// One CTA = one tile of 128 rows x a range of the context, 128 threads, thread t owns row t (TMEM lane t:
-// no shuffles in the softmax).  Per block of 64 context tokens (4 pages):
+// One CTA = one tile of 128 rows x a range of the context: 4 softmax warps, thread t owns row t (TMEM lane t:
+// no shuffles in the softmax), and a producer warp whose one elected thread issues every TMA load and every MMA;
+// the roles meet on mbarriers only (no CTA-wide barrier inside the loop).  Per block of 64 context tokens (4 pages):
 //   TMA      K rows and V rows of the 4 pages land as [64 tokens][128 B] slabs per 64-dim half (128-byte
 //            swizzle): separate boxes of 16 rows, so that the K rows of consecutive pages are consecutive
 //   S = Q K^T  one thread issues 8 tcgen05.mma (M 128, N 64, K 16) with Q and K from shared memory (K-major
@@ -40,6 +41,7 @@ constexpr int kTcRows = 128;                    // rows per tile = TMEM lanes
 constexpr int kTcBlock = 64;                    // context tokens per block (4 pages)
 constexpr int kTcD = 128;
 constexpr int kTcStages = 2;
+constexpr int kTcThreads = kTcRows + 32;      // 4 softmax warps (a row per thread) + the producer warp
 constexpr int kQBytes = 2 * kTcRows * 128;      // two 64-dim halves of [128 rows][128 B]
 constexpr int kSlabBytes = 2 * kTcBlock * 128;  // K (or V) of one block: two halves of [64 tokens][128 B]
 constexpr int kHalfBytes = kTcBlock * 128;      // one 64-dim half of a slab
@@ -124,7 +126,7 @@ __host__ __device__ constexpr uint32_t instr_desc(bool bf16, bool b_mn_major, in
 }
 
 template <bool BF>
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(kTcThreads, 2)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev st, PrefillDev pf,
                   const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q, void* __restrict__ out,
                   int out_dtype, float* __restrict__ partials, int* __restrict__ counters, int* __restrict__ status) {
@@ -139,11 +141,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     uint64_t* vfull = bars + kTcStages;                      // [stages]
     uint64_t* bar_s = bars + 2 * kTcStages;                  // [2] S of a block is in TMEM (one barrier per S buffer)
     uint64_t* bar_o = bar_s + 2;                             // O += P V of a block is done
-    uint32_t* s_tmem = (uint32_t*)(bar_o + 1);               // TMEM base address from the allocator
+    uint64_t* p_ready = bar_o + 1;                           // [2] all 128 rows of P of a block are in TMEM (one per S buffer)
+    uint32_t* s_tmem = (uint32_t*)(p_ready + 2);             // TMEM base address from the allocator
     int* s_flag = (int*)(s_tmem + 1);
     int32_t* s_pages = (int32_t*)((uint8_t*)bars + 256);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = g.H / g.Hkv;
     const int4 it = pf.items[blockIdx.x];
     const int b = it.x, chunk = it.y, kvh = it.z, tile = it.w;
@@ -162,15 +165,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     const int n_chunks = p_last / ct + 1;
 
     // this thread's row: query token tid / G of the tile, head tid % G of the group
-    const bool valid = tid / G < tok_cnt;
+    const bool valid = tid < kTcRows && tid / G < tok_cnt;
     const int lim = base_pos + tok_first + tid / G + 1;     // positions the row attends to: [0, lim)
     const size_t qo_row = (size_t)(st.q_base[b] + tok_first + tid / G) * g.H + (size_t)kvh * G + tid % G;
 
     if (tid == 0) {
         for (int i = 0; i < 2 * kTcStages + 3; i++) mbar_init(smem_u32(&bars[i]), 1);
+        mbar_init(smem_u32(&p_ready[0]), kTcRows);
+        mbar_init(smem_u32(&p_ready[1]), kTcRows);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) {                                        // one warp allocates the CTA's tensor memory
+    if (warp == kTcRows / 32) {                             // the producer warp allocates the CTA's tensor memory
         tmem_alloc(smem_u32(s_tmem), kTmemCols);
         tmem_relinquish();
     }
@@ -178,7 +183,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
         s_pages[i] = page_table[(size_t)seq * g.max_pages_per_seq + lp0 + i];
     // Q row -> shared memory in the 128-byte-swizzled K-major form the MMA reads (16-byte chunk c of a row
     // sits at chunk c ^ (row & 7)); rows without a token are zero
-    {
+    if (tid < kTcRows) {
         const uint4* src = reinterpret_cast<const uint4*>(q + qo_row * D);
 #pragma unroll
         for (int c = 0; c < 16; c++) {
@@ -193,7 +198,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;  // this warp's 32 TMEM lanes
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's 32 TMEM lanes
 
     // thread 0: K rows (V rows) of block `blk` -> stage blk % 2: a box of 16 rows x 128 B per page and 64-dim half
     auto issue_k = [&](int blk) {
@@ -244,121 +249,138 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     const float sc2 = kLog2e / sqrtf((float)D);
     bool alive = true;
 
-    if (tid == 0) {
-        issue_k(0); issue_v(0);
-        if (n_blocks > 1) { issue_k(1); issue_v(1); }
-        if (mbar_wait_bounded(smem_u32(&kfull[0]), 0u, status)) issue_s(0);
-        if (n_blocks > 1 && mbar_wait_bounded(smem_u32(&kfull[1]), 0u, status)) issue_s(1);
-    }
-
-    for (int blk = 0; blk < n_blocks; blk++) {
-        const int s = blk % kTcStages, buf = blk & 1;
-        const uint32_t col_s = kColS + 64u * buf;            // S of this block; its first 32 columns become P
-        const int tok_base = t0 + blk * kTcBlock;
-        // ---- S of this block (issued one block ahead: the tensor pipe worked on it during the last softmax) ----
-        if (!__syncthreads_and(mbar_wait_bounded(smem_u32(&bar_s[buf]), (uint32_t)((blk >> 1) & 1), status))) { alive = false; break; }
-        tc_fence_after();
-        uint32_t sr[2][32];
-        tmem_ld32(tmem + lane_base + col_s, sr[0]);
-        tmem_ld32(tmem + lane_base + col_s + 32, sr[1]);
-        tc_wait_ld();
-        if (tid == 0 && blk + 2 < n_blocks) issue_k(blk + 2);     // S(blk) is done with this K stage
-
-        // ---- online softmax of the row ----
-        const int nv = valid ? max(0, min(min(kTcBlock, t1 - tok_base), lim - tok_base)) : 0;
-        const bool full = __all_sync(0xFFFFFFFFu, nv == kTcBlock);      // no row of the warp is cut by the diagonal or the end
-        float mx = -1e30f;
-        if (full) {
-#pragma unroll
-            for (int c = 0; c < 32; c++) mx = fmaxf(mx, fmaxf(__uint_as_float(sr[0][c]), __uint_as_float(sr[1][c])));
-        } else {
-#pragma unroll
-            for (int h = 0; h < 2; h++)
-#pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    if (32 * h + c >= nv) sr[h][c] = __float_as_uint(-1e30f / sc2);      // masked: far below any score
-                    mx = fmaxf(mx, __uint_as_float(sr[h][c]));
+    if (warp == kTcRows / 32) {
+        // ===== producer warp: one thread feeds the TMA and the tensor pipe; nobody else waits for it =====
+        if (lane == 0) {
+            issue_k(0); issue_v(0);
+            if (n_blocks > 1) { issue_k(1); issue_v(1); }
+            bool ok = mbar_wait_bounded(smem_u32(&kfull[0]), 0u, status);
+            if (ok) issue_s(0);
+            if (ok && n_blocks > 1 && (ok = mbar_wait_bounded(smem_u32(&kfull[1]), 0u, status))) issue_s(1);
+            for (int blk = 0; blk < n_blocks && ok; blk++) {
+                const int s = blk % kTcStages, buf = blk & 1;
+                // S(blk) is done with its K stage: fetch K of the block after next into it
+                ok = mbar_wait_bounded(smem_u32(&bar_s[buf]), (uint32_t)((blk >> 1) & 1), status);
+                if (!ok) break;
+                if (blk + 2 < n_blocks) issue_k(blk + 2);
+                // P V (blk-1) is done with its V stage: fetch V of the next block into it
+                if (blk > 0) {
+                    ok = mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status);
+                    if (!ok) break;
+                    if (blk + 1 < n_blocks) issue_v(blk + 1);
                 }
-        }
-        mx *= sc2;                                           // sc2 > 0: the maximum of the scaled scores
-        const bool moved = mx > m2 + kLazy;
-        const float m_new = moved ? mx : m2;
-        const float alpha = moved ? ex2(m2 - m_new) : 1.0f;  // first block: ex2(-1e30 - mx) = 0
-        const float nb = -m_new;
-        float sum0 = 0.0f, sum1 = 0.0f;
-        uint32_t pr[32];                                     // P of the row: 64 values, two 16-bit per register
-#pragma unroll
-        for (int c = 0; c < 32; c++) {
-            float p0 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sc2, nb));
-            float p1 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sc2, nb));
-            if (!full) {                                     // a row that sees nothing: exp2(-1e30 + 1e30) is 1, not 0
-                if (2 * c >= nv) p0 = 0.0f;
-                if (2 * c + 1 >= nv) p1 = 0.0f;
-            }
-            sum0 += p0; sum1 += p1;
-            pr[c] = pack2<BF>(p0, p1);
-        }
-        l_run = l_run * alpha + (sum0 + sum1);
-        m2 = m_new;
-
-        // ---- O += P V of the previous block must be done before O is rescaled and its V stage refilled ----
-        if (blk > 0) {
-            if (!__syncthreads_and(mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) { alive = false; break; }
-            tc_fence_after();
-            if (tid == 0 && blk + 1 < n_blocks) issue_v(blk + 1);          // its stage was block blk-1's
-            if (__any_sync(0xFFFFFFFFu, moved)) {            // this warp's rows of O *= alpha
-#pragma unroll
-                for (int part = 0; part < 4; part++) {
-                    uint32_t orow[32];
-                    tmem_ld32(tmem + lane_base + kColO + 32 * part, orow);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 32; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
-                    tmem_st32(tmem + lane_base + kColO + 32 * part, orow);
-                }
-            }
-        }
-        tmem_st32(tmem + lane_base + col_s, pr);             // P over the columns S was read from
-        tc_wait_st();
-
-        // rows past the sequence's end hold whatever the page's last owner left: zero those V rows of the slab
-        const int n_live = len - tok_base;                   // tokens of the sequence in this block
-        if (n_live < kTcBlock && n_live < 16 * min(4, n_pages - 4 * blk)) {
-            if (!__syncthreads_and(mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status))) { alive = false; break; }
-            const int r0 = max(n_live, 0), n_rows = kTcBlock - r0;
-            for (int i = tid; i < n_rows * 16; i += blockDim.x) {
-                const int r = r0 + (i >> 4), c = i & 15;
-                *reinterpret_cast<uint4*>(s_v + s * kSlabBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        }
-        tc_fence_before();
-        __syncthreads();                                     // every row's P is in TMEM
-
-        // ---- O += P V of this block; then S of the block after next into the columns P occupies now ----
-        if (tid == 0) {
-            tc_fence_after();
-            if (mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status)) {
+                // every row's P of this block is in TMEM (and O rescaled): O += P V, then S of the block after next
+                ok = mbar_wait_bounded(smem_u32(&p_ready[buf]), (uint32_t)((blk >> 1) & 1), status) &&
+                     mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t col_p = kColS + 64u * buf;
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)               // 16 tokens per MMA: 8 TMEM columns of P, 16 rows of the V slab
-                    tc_mma_ts(tmem + kColO, tmem + col_s + 8 * ks, smem_desc(smem_u32(s_v + s * kSlabBytes) + ks * 2048, kHalfBytes),
+                    tc_mma_ts(tmem + kColO, tmem + col_p + 8 * ks, smem_desc(smem_u32(s_v + s * kSlabBytes) + ks * 2048, kHalfBytes),
                               kIdescO, (blk > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(smem_u32(bar_o));
                 // the tensor pipe runs its MMAs in issue order: S(blk+2) overwrites these columns after P V has read them
-                if (blk + 2 < n_blocks &&
-                    mbar_wait_bounded(smem_u32(&kfull[s]), (uint32_t)(((blk + 2) / kTcStages) & 1), status))
-                    issue_s(blk + 2);
+                if (blk + 2 < n_blocks) {
+                    ok = mbar_wait_bounded(smem_u32(&kfull[s]), (uint32_t)(((blk + 2) / kTcStages) & 1), status);
+                    if (ok) issue_s(blk + 2);
+                }
             }
         }
+        __syncwarp();
+    } else {
+        // ===== softmax warps: thread t owns row t =====
+        for (int blk = 0; blk < n_blocks; blk++) {
+            const int s = blk % kTcStages, buf = blk & 1;
+            const uint32_t col_s = kColS + 64u * buf;        // S of this block; its first 32 columns become P
+            const int tok_base = t0 + blk * kTcBlock;
+            // ---- S of this block (issued one block ahead: the tensor pipe worked on it during the last softmax) ----
+            if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&bar_s[buf]), (uint32_t)((blk >> 1) & 1), status))) { alive = false; break; }
+            tc_fence_after();
+            uint32_t sr[2][32];
+            tmem_ld32(tmem + lane_base + col_s, sr[0]);
+            tmem_ld32(tmem + lane_base + col_s + 32, sr[1]);
+            tc_wait_ld();
+
+            // ---- online softmax of the row ----
+            const int nv = valid ? max(0, min(min(kTcBlock, t1 - tok_base), lim - tok_base)) : 0;
+            const bool full = __all_sync(0xFFFFFFFFu, nv == kTcBlock);  // no row of the warp is cut by the diagonal or the end
+            float mx = -1e30f;
+            if (full) {
+#pragma unroll
+                for (int c = 0; c < 32; c++) mx = fmaxf(mx, fmaxf(__uint_as_float(sr[0][c]), __uint_as_float(sr[1][c])));
+            } else {
+#pragma unroll
+                for (int h = 0; h < 2; h++)
+#pragma unroll
+                    for (int c = 0; c < 32; c++) {
+                        if (32 * h + c >= nv) sr[h][c] = __float_as_uint(-1e30f / sc2);  // masked: far below any score
+                        mx = fmaxf(mx, __uint_as_float(sr[h][c]));
+                    }
+            }
+            mx *= sc2;                                       // sc2 > 0: the maximum of the scaled scores
+            const bool moved = mx > m2 + kLazy;
+            const float m_new = moved ? mx : m2;
+            const float alpha = moved ? ex2(m2 - m_new) : 1.0f;          // first block: ex2(-1e30 - mx) = 0
+            const float nb = -m_new;
+            float sum0 = 0.0f, sum1 = 0.0f;
+            uint32_t pr[32];                                 // P of the row: 64 values, two 16-bit per register
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+                float p0 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sc2, nb));
+                float p1 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sc2, nb));
+                if (!full) {                                 // a row that sees nothing: exp2(-1e30 + 1e30) is 1, not 0
+                    if (2 * c >= nv) p0 = 0.0f;
+                    if (2 * c + 1 >= nv) p1 = 0.0f;
+                }
+                sum0 += p0; sum1 += p1;
+                pr[c] = pack2<BF>(p0, p1);
+            }
+            l_run = l_run * alpha + (sum0 + sum1);
+            m2 = m_new;
+
+            // ---- O += P V of the previous block must be done before O is rescaled ----
+            if (blk > 0) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) { alive = false; break; }
+                tc_fence_after();
+                if (__any_sync(0xFFFFFFFFu, moved)) {        // this warp's rows of O *= alpha
+#pragma unroll
+                    for (int part = 0; part < 4; part++) {
+                        uint32_t orow[32];
+                        tmem_ld32(tmem + lane_base + kColO + 32 * part, orow);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
+                        tmem_st32(tmem + lane_base + kColO + 32 * part, orow);
+                    }
+                }
+            }
+            tmem_st32(tmem + lane_base + col_s, pr);         // P over the columns S was read from
+            tc_wait_st();
+
+            // rows past the sequence's end hold whatever the page's last owner left: zero those V rows of the slab
+            const int n_live = len - tok_base;               // tokens of the sequence in this block
+            if (n_live < kTcBlock && n_live < 16 * min(4, n_pages - 4 * blk)) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status))) { alive = false; break; }
+                const int r0 = max(n_live, 0), n_rows = kTcBlock - r0;
+                for (int i = tid; i < n_rows * 16; i += kTcRows) {
+                    const int r = r0 + (i >> 4), c = i & 15;
+                    *reinterpret_cast<uint4*>(s_v + s * kSlabBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&p_ready[buf]));            // this row's P (and O) are ready for the tensor pipe
+        }
+        // ---- the last block's O ----
+        if (alive && !__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((n_blocks - 1) & 1), status))) alive = false;
+        tc_fence_after();
     }
     const float m_run = m2 * 0.6931471805599453f;            // natural-log units, as the split-KV rows carry it
 
-    // ---- the last block's O ----
-    if (alive && !__syncthreads_and(mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((n_blocks - 1) & 1), status))) alive = false;
-    tc_fence_after();
-    const bool poisoned = !alive || __ldcg(status) != 0;     // fail closed
+    const bool poisoned = __any_sync(0xFFFFFFFFu, !alive || __ldcg(status) != 0);   // fail closed, whole warps at a time
 
-    if (!poisoned) {
+    if (!poisoned && warp < kTcRows / 32) {
         float* prow = nullptr;
         if (n_chunks > 1)                                    // split context: (o, m, l) of this chunk into the sequence's region
             prow = partials + (size_t)pf.poff[b] * g.H * (D + 2) +
@@ -398,7 +420,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     // ---- tensor memory goes back on every path ----
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+    if (warp == kTcRows / 32) tmem_dealloc(tmem, kTmemCols);
     if (n_chunks == 1) return;
 
     // the CTA that arrives last for the tile merges its chunks (nothing is written while the status word is set)
@@ -444,9 +466,9 @@ cudaError_t launch_prefill_tc(const Geometry& g, const CUtensorMap* map16, const
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) attr_done[bf][dev] = true;
     }
-    if (bf) prefill_tc_kernel<true><<<pf.n_items, 128, kTcSmem, s>>>(*map16, g, st, pf, page_table, (const uint16_t*)q, out,
+    if (bf) prefill_tc_kernel<true><<<pf.n_items, kTcThreads, kTcSmem, s>>>(*map16, g, st, pf, page_table, (const uint16_t*)q, out,
                                                                      out_dtype, partials, counters, status);
-    else    prefill_tc_kernel<false><<<pf.n_items, 128, kTcSmem, s>>>(*map16, g, st, pf, page_table, (const uint16_t*)q, out,
+    else    prefill_tc_kernel<false><<<pf.n_items, kTcThreads, kTcSmem, s>>>(*map16, g, st, pf, page_table, (const uint16_t*)q, out,
                                                                       out_dtype, partials, counters, status);
     return cudaGetLastError();
 }
