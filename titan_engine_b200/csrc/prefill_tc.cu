@@ -7,8 +7,10 @@
 // is a contraction the tcgen05 instruction takes whole: M = 128 rows = the 128 lanes of tensor memory.
 //
 // One CTA = one tile of 128 rows x a range of the context: 4 softmax warps, thread t owns row t (TMEM lane t:
-// no shuffles in the softmax), and a producer warp whose one elected thread issues every TMA load and every MMA;
-// the roles meet on mbarriers only (no CTA-wide barrier inside the loop).  Per block of 64 context tokens (4 pages):
+// no shuffles in the softmax), an MMA warp whose one elected thread issues every tcgen05.mma, and a loader warp
+// whose lanes issue the TMA copies; the roles meet on mbarriers only (no CTA-wide barrier inside the loop).
+// (Measured with clock64 around each phase: with one thread issuing both the 16 copies and the 12 MMAs of a
+// block, that thread was busy 80 % of the kernel and the softmax warps waited for it 60 % of theirs.)  Per block of 64 context tokens (4 pages):
 //   TMA      K rows and V rows of the 4 pages land as [64 tokens][128 B] slabs per 64-dim half (128-byte
 //            swizzle): separate boxes of 16 rows, so that the K rows of consecutive pages are consecutive
 //   S = Q K^T  one thread issues 8 tcgen05.mma (M 128, N 64, K 16) with Q and K from shared memory (K-major
@@ -41,7 +43,7 @@ constexpr int kTcRows = 128;                    // rows per tile = TMEM lanes
 constexpr int kTcBlock = 64;                    // context tokens per block (4 pages)
 constexpr int kTcD = 128;
 constexpr int kTcStages = 2;
-constexpr int kTcThreads = kTcRows + 32;      // 4 softmax warps (a row per thread) + the producer warp
+constexpr int kTcThreads = kTcRows + 64;        // 4 softmax warps (a row per thread), the MMA warp, the loader warp
 constexpr int kQBytes = 2 * kTcRows * 128;      // two 64-dim halves of [128 rows][128 B]
 constexpr int kSlabBytes = 2 * kTcBlock * 128;  // K (or V) of one block: two halves of [64 tokens][128 B]
 constexpr int kHalfBytes = kTcBlock * 128;      // one 64-dim half of a slab
@@ -141,7 +143,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     uint64_t* vfull = bars + kTcStages;                      // [stages]
     uint64_t* bar_s = bars + 2 * kTcStages;                  // [2] S of a block is in TMEM (one barrier per S buffer)
     uint64_t* bar_o = bar_s + 2;                             // O += P V of a block is done
-    uint64_t* p_ready = bar_o + 1;                           // [2] all 128 rows of P of a block are in TMEM (one per S buffer)
+    uint64_t* p_ready = bar_o + 1;                           // [2] all 128 rows of P of a block are in TMEM (one per S buffer); + the loader
     uint32_t* s_tmem = (uint32_t*)(p_ready + 2);             // TMEM base address from the allocator
     int* s_flag = (int*)(s_tmem + 1);
     int32_t* s_pages = (int32_t*)((uint8_t*)bars + 256);
@@ -171,11 +173,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
 
     if (tid == 0) {
         for (int i = 0; i < 2 * kTcStages + 3; i++) mbar_init(smem_u32(&bars[i]), 1);
-        mbar_init(smem_u32(&p_ready[0]), kTcRows);
-        mbar_init(smem_u32(&p_ready[1]), kTcRows);
+        mbar_init(smem_u32(&p_ready[0]), kTcRows + 1);
+        mbar_init(smem_u32(&p_ready[1]), kTcRows + 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == kTcRows / 32) {                             // the producer warp allocates the CTA's tensor memory
+    if (warp == kTcRows / 32) {                             // the MMA warp allocates the CTA's tensor memory
         tmem_alloc(smem_u32(s_tmem), kTmemCols);
         tmem_relinquish();
     }
@@ -200,43 +202,34 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     const uint32_t tmem = *s_tmem;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's 32 TMEM lanes
 
-    // thread 0: K rows (V rows) of block `blk` -> stage blk % 2: a box of 16 rows x 128 B per page and 64-dim half
-    auto issue_k = [&](int blk) {
+    // loader warp: K rows (V rows) of block `blk` -> stage blk % 2, a box of 16 rows x 128 B per page and 64-dim half;
+    // lane i < 8 issues box i (page i / 2, half i % 2), so the eight copies leave in one instruction
+    auto load_rows = [&](int blk, bool is_v) {
         const int s = blk % kTcStages;
         const int pages = min(4, n_pages - 4 * blk);
-        const uint32_t kb = smem_u32(&kfull[s]);
-        mbar_expect_tx(kb, pages * 2 * 2048);
-        for (int p = 0; p < pages; p++) {
-            const int row = (s_pages[4 * blk + p] * g.Hkv + kvh) * 32;
-#pragma unroll
-            for (int h = 0; h < 2; h++)
-                tma_load_2d_shared_tile(smem_u32(s_k + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, kb);
-        }
-    };
-    auto issue_v = [&](int blk) {
-        const int s = blk % kTcStages;
-        const int pages = min(4, n_pages - 4 * blk);
-        const uint32_t vb = smem_u32(&vfull[s]);
-        mbar_expect_tx(vb, pages * 2 * 2048);
-        for (int p = 0; p < pages; p++) {
-            const int row = (s_pages[4 * blk + p] * g.Hkv + kvh) * 32 + 16;
-#pragma unroll
-            for (int h = 0; h < 2; h++)
-                tma_load_2d_shared_tile(smem_u32(s_v + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, vb);
+        const uint32_t bar = smem_u32(is_v ? &vfull[s] : &kfull[s]);
+        if (lane == 0) mbar_expect_tx(bar, pages * 2 * 2048);
+        __syncwarp();
+        const int p = lane >> 1, h = lane & 1;
+        if (lane < 8 && p < pages) {
+            const int row = (s_pages[4 * blk + p] * g.Hkv + kvh) * 32 + (is_v ? 16 : 0);
+            tma_load_2d_shared_tile(smem_u32((is_v ? s_v : s_k) + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, bar);
         }
     };
     constexpr uint32_t kIdescS = instr_desc(BF, false, kTcBlock);
     constexpr uint32_t kIdescO = instr_desc(BF, true, D);
-    // thread 0: S = Q K^T of block `blk` (8 k-steps of 16 dims: 4 per 64-dim half, 32 bytes apart inside the swizzled row)
+    // MMA thread: the descriptors of a stage differ from those of stage 0 by the stage's byte offset / 16 in the
+    // address field (the field cannot carry: shared memory addresses stay below 2^18)
+    const uint64_t desc_q = smem_desc(smem_u32(s_q), 16), desc_k = smem_desc(smem_u32(s_k), 16),
+                   desc_v = smem_desc(smem_u32(s_v), kHalfBytes);
+    // S = Q K^T of block `blk` (8 k-steps of 16 dims: 4 per 64-dim half, 32 bytes apart inside the swizzled row)
     auto issue_s = [&](int blk) {
-        const int s = blk % kTcStages;
+        const uint64_t dk = desc_k + (uint64_t)((blk % kTcStages) * (kSlabBytes >> 4));
+        const uint32_t d_s = tmem + kColS + 64u * (blk & 1);
 #pragma unroll
-        for (int ks = 0; ks < 8; ks++) {
-            const uint32_t off = (ks >> 2) * (kTcRows * 128) + (ks & 3) * 32;
-            const uint32_t koff = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-            tc_mma_ss(tmem + kColS + 64u * (blk & 1), smem_desc(smem_u32(s_q) + off, 16),
-                      smem_desc(smem_u32(s_k + s * kSlabBytes) + koff, 16), kIdescS, ks > 0);
-        }
+        for (int ks = 0; ks < 8; ks++)
+            tc_mma_ss(d_s, desc_q + (uint64_t)(((ks >> 2) * (kTcRows * 128) + (ks & 3) * 32) >> 4),
+                      dk + (uint64_t)(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4), kIdescS, ks > 0);
         tc_commit(smem_u32(&bar_s[blk & 1]));
     };
 
@@ -250,35 +243,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     bool alive = true;
 
     if (warp == kTcRows / 32) {
-        // ===== producer warp: one thread feeds the TMA and the tensor pipe; nobody else waits for it =====
+        // ===== MMA warp: one thread feeds the tensor pipe; nobody else waits for its instruction stream =====
         if (lane == 0) {
-            issue_k(0); issue_v(0);
-            if (n_blocks > 1) { issue_k(1); issue_v(1); }
             bool ok = mbar_wait_bounded(smem_u32(&kfull[0]), 0u, status);
             if (ok) issue_s(0);
             if (ok && n_blocks > 1 && (ok = mbar_wait_bounded(smem_u32(&kfull[1]), 0u, status))) issue_s(1);
             for (int blk = 0; blk < n_blocks && ok; blk++) {
                 const int s = blk % kTcStages, buf = blk & 1;
-                // S(blk) is done with its K stage: fetch K of the block after next into it
-                ok = mbar_wait_bounded(smem_u32(&bar_s[buf]), (uint32_t)((blk >> 1) & 1), status);
-                if (!ok) break;
-                if (blk + 2 < n_blocks) issue_k(blk + 2);
-                // P V (blk-1) is done with its V stage: fetch V of the next block into it
-                if (blk > 0) {
-                    ok = mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status);
-                    if (!ok) break;
-                    if (blk + 1 < n_blocks) issue_v(blk + 1);
-                }
                 // every row's P of this block is in TMEM (and O rescaled): O += P V, then S of the block after next
                 ok = mbar_wait_bounded(smem_u32(&p_ready[buf]), (uint32_t)((blk >> 1) & 1), status) &&
                      mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t col_p = kColS + 64u * buf;
+                const uint32_t a_p = tmem + kColS + 64u * buf;
+                const uint64_t dv = desc_v + (uint64_t)(s * (kSlabBytes >> 4));
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)               // 16 tokens per MMA: 8 TMEM columns of P, 16 rows of the V slab
-                    tc_mma_ts(tmem + kColO, tmem + col_p + 8 * ks, smem_desc(smem_u32(s_v + s * kSlabBytes) + ks * 2048, kHalfBytes),
-                              kIdescO, (blk > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem + kColO, a_p + 8 * ks, dv + (uint64_t)((ks * 2048) >> 4), kIdescO, (blk > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(smem_u32(bar_o));
                 // the tensor pipe runs its MMAs in issue order: S(blk+2) overwrites these columns after P V has read them
                 if (blk + 2 < n_blocks) {
@@ -288,6 +269,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
             }
         }
         __syncwarp();
+    } else if (warp == kTcRows / 32 + 1) {
+        // ===== loader warp: keeps the two K stages and the two V stages full =====
+        load_rows(0, false); load_rows(0, true);
+        if (n_blocks > 1) { load_rows(1, false); load_rows(1, true); }
+        for (int blk = 0; blk < n_blocks; blk++) {
+            // S(blk) is done with its K stage: K of the block after next goes there
+            if (blk + 2 < n_blocks) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&bar_s[blk & 1]), (uint32_t)((blk >> 1) & 1), status))) break;
+                load_rows(blk + 2, false);
+            }
+            // P V (blk-1) is done with its V stage: V of the next block goes there
+            if (blk > 0 && blk + 1 < n_blocks) {
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) break;
+                load_rows(blk + 1, true);
+            }
+            // P V (blk) may not complete before this warp has seen P V (blk-1) complete (a parity wait cannot tell
+            // a phase that is two ahead from one that has not happened): the MMA thread waits for this arrival too
+            if (lane == 0) mbar_arrive(smem_u32(&p_ready[blk & 1]));
+        }
     } else {
         // ===== softmax warps: thread t owns row t =====
         for (int blk = 0; blk < n_blocks; blk++) {
