@@ -305,11 +305,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
             // ---- online softmax of the row ----
             const int nv = valid ? max(0, min(min(kTcBlock, t1 - tok_base), lim - tok_base)) : 0;
             const bool full = __all_sync(0xFFFFFFFFu, nv == kTcBlock);  // no row of the warp is cut by the diagonal or the end
-            float mx = -1e30f;
+            float alpha = 1.0f;
+            bool moved = false;
+            uint32_t pr[32];                                 // P of the row: 64 values, two 16-bit per register
+            bool settled = false;
             if (full) {
+                // Speculate that the reference maximum stays: maximum, probabilities and sum in ONE pass, so that the
+                // maximum's compare chain and the sum's add chain issue in the shadow of the exponentials (the
+                // special-function unit, 4 lanes per clock and scheduler, is the scarce pipe of this loop).
+                const float nb = -m2;
+                float mx = -1e30f, sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-                for (int c = 0; c < 32; c++) mx = fmaxf(mx, fmaxf(__uint_as_float(sr[0][c]), __uint_as_float(sr[1][c])));
-            } else {
+                for (int c = 0; c < 32; c++) {
+                    const float a0 = __uint_as_float(sr[c >> 4][(2 * c) & 31]), a1 = __uint_as_float(sr[c >> 4][(2 * c + 1) & 31]);
+                    mx = fmaxf(mx, fmaxf(a0, a1));
+                    const float p0 = ex2(fmaf(a0, sc2, nb)), p1 = ex2(fmaf(a1, sc2, nb));
+                    sum0 += p0; sum1 += p1;
+                    pr[c] = pack2<BF>(p0, p1);
+                }
+                moved = mx * sc2 > m2 + kLazy;               // always on a row's first block (m2 = -1e30)
+                if (!__any_sync(0xFFFFFFFFu, moved)) {
+                    l_run += sum0 + sum1;
+                    settled = true;
+                }
+            }
+            if (!settled) {
+                // the careful pass: masks, the new reference of every row that moved, and its probabilities again
+                float mx = -1e30f;
 #pragma unroll
                 for (int h = 0; h < 2; h++)
 #pragma unroll
@@ -317,33 +339,35 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                         if (32 * h + c >= nv) sr[h][c] = __float_as_uint(-1e30f / sc2);  // masked: far below any score
                         mx = fmaxf(mx, __uint_as_float(sr[h][c]));
                     }
-            }
-            mx *= sc2;                                       // sc2 > 0: the maximum of the scaled scores
-            const bool moved = mx > m2 + kLazy;
-            const float m_new = moved ? mx : m2;
-            const float alpha = moved ? ex2(m2 - m_new) : 1.0f;          // first block: ex2(-1e30 - mx) = 0
-            const float nb = -m_new;
-            float sum0 = 0.0f, sum1 = 0.0f;
-            uint32_t pr[32];                                 // P of the row: 64 values, two 16-bit per register
+                mx *= sc2;                                   // sc2 > 0: the maximum of the scaled scores
+                moved = mx > m2 + kLazy;
+                const float m_new = moved ? mx : m2;
+                alpha = moved ? ex2(m2 - m_new) : 1.0f;      // first block: ex2(-1e30 - mx) = 0
+                const float nb = -m_new;
+                float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 32; c++) {
-                float p0 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sc2, nb));
-                float p1 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sc2, nb));
-                if (!full) {                                 // a row that sees nothing: exp2(-1e30 + 1e30) is 1, not 0
-                    if (2 * c >= nv) p0 = 0.0f;
+                for (int c = 0; c < 32; c++) {
+                    float p0 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c) & 31]), sc2, nb));
+                    float p1 = ex2(fmaf(__uint_as_float(sr[c >> 4][(2 * c + 1) & 31]), sc2, nb));
+                    if (2 * c >= nv) p0 = 0.0f;              // a row that sees nothing: exp2(-1e30 + 1e30) is 1, not 0
                     if (2 * c + 1 >= nv) p1 = 0.0f;
+                    sum0 += p0; sum1 += p1;
+                    pr[c] = pack2<BF>(p0, p1);
                 }
-                sum0 += p0; sum1 += p1;
-                pr[c] = pack2<BF>(p0, p1);
+                l_run = l_run * alpha + (sum0 + sum1);
+                m2 = m_new;
             }
-            l_run = l_run * alpha + (sum0 + sum1);
-            m2 = m_new;
 
             // ---- O += P V of the previous block must be done before O is rescaled ----
-            if (blk > 0) {
+            // S of this block was committed behind P V of block blk-2, so the barrier's current phase is blk-1 or
+            // later and its parity cannot be mistaken for an older one; blocks that rescale nothing do not wait at all
+            // (the last block waits in any case: once its P is handed over, P V of it may complete at any time, and
+            // the wait for the last phase after the loop must not meet a barrier that is two phases ahead of it)
+            const bool rescale = __any_sync(0xFFFFFFFFu, moved);
+            if (blk > 0 && (rescale || blk == n_blocks - 1)) {
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) { alive = false; break; }
                 tc_fence_after();
-                if (__any_sync(0xFFFFFFFFu, moved)) {        // this warp's rows of O *= alpha
+                if (rescale) {                               // this warp's rows of O *= alpha
 #pragma unroll
                     for (int part = 0; part < 4; part++) {
                         uint32_t orow[32];
