@@ -148,8 +148,14 @@ struct Cfg {
 // token j, head gg of the group (G * nq <= 16), so the tokens share one pass over the pages: what a
 // speculative decoder's verification of nq drafted tokens needs (the reference runs the layer once per
 // token there: src/inference/speculative.cpp:262-272).
+// FP8 pools with a group of at most 8 query heads run the products transposed: S^T = K Q^T and
+// O^T = V^T P^T, tokens (dims) as the 16 rows of the MMA and the 8 heads as its 8 columns, so that no row of
+// a tile is padding: half the MMAs per page, half the accumulator registers (4 CTAs per SM instead of 3).
+template <int KIND, bool GHI, bool MULTI>
+constexpr bool kTransposed = KIND == K_FP8 && !GHI && !MULTI;
+
 template <int KIND, int D, bool IO_BF16, bool GHI, bool MULTI>
-__global__ void __launch_bounds__(kWarps * 32, kMinCtas)
+__global__ void __launch_bounds__(kWarps * 32, kTransposed<KIND, GHI, MULTI> ? kMinCtas + 1 : kMinCtas)
 decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_cold, Geometry g, LayerPtrs lp, StepDev st,
                   const int32_t* __restrict__ page_table, const uint16_t* __restrict__ q,
                   float* __restrict__ partials, int* __restrict__ status, MergeOut mo, FuseAppend fa) {
@@ -157,6 +163,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     constexpr int kStages = C::STAGES;
     constexpr bool BF = C::MMA_BF16;
     constexpr int KS = D / 16;                              // k-steps of QK^T
+    constexpr bool SWAP = kTransposed<KIND, GHI, MULTI>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + kWarps * kStages * C::STAGE_BYTES);
@@ -223,8 +230,25 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     for (int i = 0; i < kStages && i < n_w; i++) issue(i);
 
     // ---- Q fragments (A operand), rows >= G are zero -------------------------------
-    uint32_t qa[KS][4];
-    {
+    uint32_t qa[SWAP ? 1 : KS][4];
+    uint32_t qb[SWAP ? KS : 1][2];                          // transposed form: Q^T as the B operand, column gr = head gr
+    if constexpr (SWAP) {
+        // k index (2j,2j+1) <-> dims 16kk+4j,+1 ; (2j+8,2j+9) <-> dims 16kk+4j+2,+3 (the order the K codes arrive in)
+        const uint16_t* qrow = q + ((size_t)q_row0 * g.H + (size_t)kvh * G + gr) * D;
+#pragma unroll
+        for (int kk = 0; kk < KS; kk++) {
+            const uint2 x = gr < rows ? *reinterpret_cast<const uint2*>(qrow + 16 * kk + 4 * j) : make_uint2(0, 0);
+            uint32_t w[2] = {x.x, x.y};
+            if (IO_BF16) {                                  // bf16 -> fp16 (exact in fp16's normal range)
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);
+                    w[i] = pack2<false>(lo, hi);
+                }
+            }
+            qb[kk][0] = w[0]; qb[kk][1] = w[1];
+        }
+    } else {
         // row r of the tile: token r / G of the sequence, head r % G of the group
         const uint16_t* qrow0 = q + ((size_t)(q_row0 + (MULTI ? gr / G : 0)) * g.H + (size_t)kvh * G + (MULTI ? gr % G : gr)) * D;
         const uint16_t* qrow1 = MULTI ? q + ((size_t)(q_row0 + (gr + 8) / G) * g.H + (size_t)kvh * G + (gr + 8) % G) * D
@@ -268,7 +292,10 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     // ---- running state -------------------------------------------------------------
     // 16-bit: o[nt] is the C fragment of n-tile nt (dims 8nt..8nt+7).
     // FP8:    o[2c] / o[2c+1] are the even-dim / odd-dim tiles of 16-dim chunk c.
-    constexpr int NT = D / 8;
+    // Transposed (FP8, group <= 8): o[2c] / o[2c+1] hold the even / odd dims of 32-dim chunk c: element [0],[1] =
+    //         (dim 32c + 2gr (+1), heads 2j, 2j+1), [2],[3] = (dim 32c + 16 + 2gr (+1), heads 2j, 2j+1);
+    //         m0/l0 belong to head 2j, m1/l1 to head 2j+1, m in base-2 units, l summed over this lane's tokens only.
+    constexpr int NT = SWAP ? D / 16 : D / 8;
     float o[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f; }
@@ -327,6 +354,66 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
             __syncwarp();
         }
 
+        if constexpr (SWAP) {
+            // ---- S^T = K Q^T: rows = the page's 16 tokens, columns = heads ----
+            float sT[4] = {0.f, 0.f, 0.f, 0.f}, uT[4] = {0.f, 0.f, 0.f, 0.f};
+            const int mi = lane >> 3;                       // matrix this lane addresses: token half mi & 1, 16-dim chunk mi >> 1
+            {
+                const int row = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+                for (int cp = 0; cp < D / 32; cp++) {
+                    uint32_t r0, r1, r2, r3;                // (tokens 0-7 | 8-15) x (chunk 2cp | 2cp+1), 4 codes of one token each
+                    ldsm_x4(stg_u + swz(row, 2 * cp + (mi >> 1)), r0, r1, r2, r3);
+                    const uint32_t a0[4] = {e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r1 >> 16)};
+                    mma16816<false>(sT, a0, qb[2 * cp][0], qb[2 * cp][1]);
+                    const uint32_t a1[4] = {e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r3), e4m3x2_to_f16x2(r2 >> 16), e4m3x2_to_f16x2(r3 >> 16)};
+                    mma16816<false>(uT, a1, qb[2 * cp + 1][0], qb[2 * cp + 1][1]);
+                }
+            }
+            // ---- softmax down the columns: this lane has tokens gr, gr+8 of heads 2j ([0],[2]) and 2j+1 ([1],[3]) ----
+            // (sealed pages are always full, so nothing is masked).  The reference maximum of a head moves only when a
+            // score exceeds it by 2^4: one vote per page instead of a shuffle reduction; probabilities stay below 16.
+            const float k2 = sc_k * kLog2e;
+            const float a0 = (sT[0] + uT[0]) * k2, a1 = (sT[1] + uT[1]) * k2, a2 = (sT[2] + uT[2]) * k2, a3 = (sT[3] + uT[3]) * k2;
+            float xa = fmaxf(a0, a2), xb = fmaxf(a1, a3);
+            if (__any_sync(0xFFFFFFFFu, xa > m0 + 4.0f || xb > m1 + 4.0f)) {
+#pragma unroll
+                for (int off = 4; off < 32; off <<= 1) {
+                    xa = fmaxf(xa, __shfl_xor_sync(0xFFFFFFFFu, xa, off));
+                    xb = fmaxf(xb, __shfl_xor_sync(0xFFFFFFFFu, xb, off));
+                }
+                const float na = fmaxf(m0, xa), nb = fmaxf(m1, xb);
+                const float al0 = ex2(m0 - na), al1 = ex2(m1 - nb);
+                l0 *= al0; l1 *= al1;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) { o[nt][0] *= al0; o[nt][2] *= al0; o[nt][1] *= al1; o[nt][3] *= al1; }
+                m0 = na; m1 = nb;
+            }
+            const float p0 = ex2(a0 - m0), p1 = ex2(a1 - m1), p2 = ex2(a2 - m0), p3 = ex2(a3 - m1);
+            l0 += p0 + p2; l1 += p1 + p3;
+            // ---- O^T += V^T P^T: P^T (tokens x heads as the B operand) is the transpose of what this lane holds ----
+            uint32_t b0, b1;
+            {
+                const uint32_t t0 = pack2<false>(p0 * sc_v, p1 * sc_v), t1 = pack2<false>(p2 * sc_v, p3 * sc_v);
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(b0) : "r"(t0));
+                asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(b1) : "r"(t1));
+            }
+            {
+                const int row = 16 + ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+                for (int cp = 0; cp < D / 32; cp++) {
+                    uint32_t r0, r1, r2, r3;                // dims pair gr of (chunk 2cp | 2cp+1) for tokens (2j,2j+1 | 2j+8,2j+9)
+                    ldsm_x4_t(stg_u + swz(row, 2 * cp + (mi >> 1)), r0, r1, r2, r3);
+                    // bytes (even dim tok 2j, even dim tok 2j+1, odd dim tok 2j, odd dim tok 2j+1)
+                    r0 = __byte_perm(r0, 0, 0x3120); r1 = __byte_perm(r1, 0, 0x3120);
+                    r2 = __byte_perm(r2, 0, 0x3120); r3 = __byte_perm(r3, 0, 0x3120);
+                    const uint32_t ae[4] = {e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r1), e4m3x2_to_f16x2(r3)};
+                    mma16816<false>(o[2 * cp], ae, b0, b1);
+                    const uint32_t ao[4] = {e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r2 >> 16), e4m3x2_to_f16x2(r1 >> 16), e4m3x2_to_f16x2(r3 >> 16)};
+                    mma16816<false>(o[2 * cp + 1], ao, b0, b1);
+                }
+            }
+        } else {
         // ---- S = Q K^T over the page's 16 tokens ----
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
         if (KIND == K_FP8) {
@@ -450,6 +537,8 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
             }
         }
 
+        }
+
         // ---- refill this stage ----
         __syncwarp();
         if (i + kStages < n_w) {
@@ -466,11 +555,38 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     pdl_launch_dependents();
 
     // ---- merge the 4 warps through shared memory (stage memory is idle now) ----------
-    l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
-    l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+    if constexpr (SWAP) {
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, off);
+            l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, off);
+        }
+    } else {
+        l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);
+        l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 1); l1 += __shfl_xor_sync(0xFFFFFFFFu, l1, 2);
+    }
     __syncthreads();
     float* red = reinterpret_cast<float*>(smem);            // [kWarps][rows][D+2]
     auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * rows + row) * (D + 2) + d]; };
+    if constexpr (SWAP) {
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {                    // heads 2j and 2j+1
+            const int row = 2 * j + hh;
+            if (row < rows) {
+#pragma unroll
+                for (int c = 0; c < D / 32; c++) {
+                    red_at(warp, row, 32 * c + 2 * gr + 0) = o[2 * c][hh];
+                    red_at(warp, row, 32 * c + 2 * gr + 1) = o[2 * c + 1][hh];
+                    red_at(warp, row, 32 * c + 16 + 2 * gr + 0) = o[2 * c][2 + hh];
+                    red_at(warp, row, 32 * c + 16 + 2 * gr + 1) = o[2 * c + 1][2 + hh];
+                }
+                if (gr == 0) {                              // the merge below works in natural-log units
+                    red_at(warp, row, D) = (hh ? m1 : m0) * 0.6931471805599453f;
+                    red_at(warp, row, D + 1) = hh ? l1 : l0;
+                }
+            }
+        }
+    } else {
 #pragma unroll
     for (int half = 0; half < 2; half++) {
         const int row = gr + 8 * half;
@@ -495,6 +611,7 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                 red_at(warp, row, D + 1) = half ? l1 : l0;
             }
         }
+    }
     }
     __syncthreads();
     pdl_wait();
