@@ -25,6 +25,9 @@
 //            descriptor: V rows are tokens), O in TMEM columns [128, 256)
 // Two CTAs share an SM (256 TMEM columns and 98 KB of shared memory each), so one CTA's softmax overlaps the
 // other's MMAs.  No cluster, no multicast, cta_group::1 only, this GPU's memory only.
+// Measured and left out: computing a share of the exponentials as a cubic on the FMA pipe (0 / 12.5 / 25 / 50 % of
+// them: 916 / 887 / 856 / 793 TFLOP/s) - the softmax warps are short of issue slots and latency cover, not of
+// special-function throughput.
 // Every mbarrier wait is bounded; on expiry the status word is set, nothing is written, and the CTA still
 // frees its tensor memory before it returns.
 #include "tk_kernels.cuh"
@@ -93,6 +96,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
+}
+// The same wait with the 32 registers of a load as in/out operands: nothing that reads them can be scheduled above it.
+__device__ __forceinline__ void tc_wait_ld(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr),
+          "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -297,10 +319,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
             // ---- S of this block (issued one block ahead: the tensor pipe worked on it during the last softmax) ----
             if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&bar_s[buf]), (uint32_t)((blk >> 1) & 1), status))) { alive = false; break; }
             tc_fence_after();
-            uint32_t sr[2][32];
+            uint32_t sr[2][32];                              // the second half of the row arrives while the first is worked on
             tmem_ld32(tmem + lane_base + col_s, sr[0]);
+            tc_wait_ld(sr[0]);
             tmem_ld32(tmem + lane_base + col_s + 32, sr[1]);
-            tc_wait_ld();
 
             // ---- online softmax of the row ----
             const int nv = valid ? max(0, min(min(kTcBlock, t1 - tok_base), lim - tok_base)) : 0;
@@ -309,23 +331,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
             bool moved = false;
             uint32_t pr[32];                                 // P of the row: 64 values, two 16-bit per register
             bool settled = false;
+            // Speculate that the reference maximum stays: maximum, probabilities and sum in ONE pass, so that the
+            // maximum's compare chain and the sum's add chain issue in the shadow of the exponentials (the
+            // special-function unit, 4 lanes per clock and scheduler, is the scarce pipe of this loop).
+            float smx = -1e30f, ssum0 = 0.0f, ssum1 = 0.0f;
             if (full) {
-                // Speculate that the reference maximum stays: maximum, probabilities and sum in ONE pass, so that the
-                // maximum's compare chain and the sum's add chain issue in the shadow of the exponentials (the
-                // special-function unit, 4 lanes per clock and scheduler, is the scarce pipe of this loop).
                 const float nb = -m2;
-                float mx = -1e30f, sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    const float a0 = __uint_as_float(sr[c >> 4][(2 * c) & 31]), a1 = __uint_as_float(sr[c >> 4][(2 * c + 1) & 31]);
-                    mx = fmaxf(mx, fmaxf(a0, a1));
+                for (int c = 0; c < 16; c++) {
+                    const float a0 = __uint_as_float(sr[0][2 * c]), a1 = __uint_as_float(sr[0][2 * c + 1]);
+                    smx = fmaxf(smx, fmaxf(a0, a1));
                     const float p0 = ex2(fmaf(a0, sc2, nb)), p1 = ex2(fmaf(a1, sc2, nb));
-                    sum0 += p0; sum1 += p1;
+                    ssum0 += p0; ssum1 += p1;
                     pr[c] = pack2<BF>(p0, p1);
                 }
-                moved = mx * sc2 > m2 + kLazy;               // always on a row's first block (m2 = -1e30)
+                tmem_st16(tmem + lane_base + col_s, pr);     // these columns of S are in registers already
+            }
+            tc_wait_ld(sr[1]);
+            if (full) {
+                const float nb = -m2;
+#pragma unroll
+                for (int c = 16; c < 32; c++) {
+                    const float a0 = __uint_as_float(sr[1][2 * c - 32]), a1 = __uint_as_float(sr[1][2 * c - 31]);
+                    smx = fmaxf(smx, fmaxf(a0, a1));
+                    const float p0 = ex2(fmaf(a0, sc2, nb)), p1 = ex2(fmaf(a1, sc2, nb));
+                    ssum0 += p0; ssum1 += p1;
+                    pr[c] = pack2<BF>(p0, p1);
+                }
+                moved = smx * sc2 > m2 + kLazy;              // always on a row's first block (m2 = -1e30)
                 if (!__any_sync(0xFFFFFFFFu, moved)) {
-                    l_run += sum0 + sum1;
+                    l_run += ssum0 + ssum1;
+                    tmem_st16(tmem + lane_base + col_s + 16, pr + 16);
                     settled = true;
                 }
             }
@@ -357,6 +393,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                 l_run = l_run * alpha + (sum0 + sum1);
                 m2 = m_new;
             }
+            const bool p_stored = settled;
 
             // ---- O += P V of the previous block must be done before O is rescaled ----
             // S of this block was committed behind P V of block blk-2, so the barrier's current phase is blk-1 or
@@ -379,7 +416,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                     }
                 }
             }
-            tmem_st32(tmem + lane_base + col_s, pr);         // P over the columns S was read from
+            if (!p_stored) tmem_st32(tmem + lane_base + col_s, pr);   // P over the columns S was read from
             tc_wait_st();
 
             // rows past the sequence's end hold whatever the page's last owner left: zero those V rows of the slab
