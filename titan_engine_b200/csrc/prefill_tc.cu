@@ -27,7 +27,9 @@
 // other's MMAs.  No cluster, no multicast, cta_group::1 only, this GPU's memory only.
 // Measured and left out: computing a share of the exponentials as a cubic on the FMA pipe (0 / 12.5 / 25 / 50 % of
 // them: 916 / 887 / 856 / 793 TFLOP/s) - the softmax warps are short of issue slots and latency cover, not of
-// special-function throughput.
+// special-function throughput.  Nor did more softmax warps help: two threads per row (8 softmax warps per CTA, 32
+// columns each, the halves' maxima exchanged through shared memory on a named barrier per warp pair) ran at 771
+// against 930 TFLOP/s; nor the pass written out in batches of 16 exponentials with four chains each (895).
 // Every mbarrier wait is bounded; on expiry the status word is set, nothing is written, and the CTA still
 // frees its tensor memory before it returns.
 #include "tk_kernels.cuh"
@@ -127,6 +129,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
           "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
           "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
+}
+
+// Two FP32 lanes per instruction (sm_100): (a0, a1) * b + c and (s0, s1) += (p0, p1)
+__device__ __forceinline__ void fma2(float& r0, float& r1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}" : "=f"(r0), "=f"(r1) : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float& s0, float& s1, float p0, float p1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%0, %1};\n\tmov.b64 rb, {%2, %3};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}" : "+f"(s0), "+f"(s1) : "f"(p0), "f"(p1));
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, 8-row groups 1024 bytes apart (sm_100 format:
@@ -341,8 +353,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                 for (int c = 0; c < 16; c++) {
                     const float a0 = __uint_as_float(sr[0][2 * c]), a1 = __uint_as_float(sr[0][2 * c + 1]);
                     smx = fmaxf(smx, fmaxf(a0, a1));
-                    const float p0 = ex2(fmaf(a0, sc2, nb)), p1 = ex2(fmaf(a1, sc2, nb));
-                    ssum0 += p0; ssum1 += p1;
+                    float x0, x1;
+                    fma2(x0, x1, a0, a1, sc2, nb);
+                    const float p0 = ex2(x0), p1 = ex2(x1);
+                    add2(ssum0, ssum1, p0, p1);
                     pr[c] = pack2<BF>(p0, p1);
                 }
                 tmem_st16(tmem + lane_base + col_s, pr);     // these columns of S are in registers already
@@ -354,8 +368,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                 for (int c = 16; c < 32; c++) {
                     const float a0 = __uint_as_float(sr[1][2 * c - 32]), a1 = __uint_as_float(sr[1][2 * c - 31]);
                     smx = fmaxf(smx, fmaxf(a0, a1));
-                    const float p0 = ex2(fmaf(a0, sc2, nb)), p1 = ex2(fmaf(a1, sc2, nb));
-                    ssum0 += p0; ssum1 += p1;
+                    float x0, x1;
+                    fma2(x0, x1, a0, a1, sc2, nb);
+                    const float p0 = ex2(x0), p1 = ex2(x1);
+                    add2(ssum0, ssum1, p0, p1);
                     pr[c] = pack2<BF>(p0, p1);
                 }
                 moved = smx * sc2 > m2 + kLazy;              // always on a row's first block (m2 = -1e30)
