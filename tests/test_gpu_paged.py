@@ -111,6 +111,20 @@ def test_decode_fp8(impl, io):
     t.check_pool(1)
 
 
+@pytest.mark.parametrize("heads", [(8, 8), (16, 8), (32, 8), (64, 8), (64, 4)])
+def test_decode_fp8_group_sizes(heads):
+    """FP8 pools with a group of at most 8 query heads run both products transposed (the heads are the MMA's 8
+    columns; groups of 1, 2, 4 leave columns empty), larger groups keep the heads as rows.  Long enough for
+    several split-KV chunks per sequence; outliers move the reference maximum late in a sequence."""
+    H, Hkv = heads
+    t = Twin(1, H, Hkv, 128, 260, 3, 200, dtype="fp8", io="bf16", impl="mma", chunk_tokens=512, max_step_tokens=4096, seed=45)
+    seqs = [t.seq_alloc() for _ in range(3)]
+    t.step(seqs, [3000, 300, 17], check_pool=True, outlier_p=0.01)
+    for _ in range(3):
+        t.step(seqs, [1, 1, 1], outlier_p=0.01, f32_out=True)        # FP32 results: the stated tolerance with no slack
+    t.gpu.device_status()
+
+
 @pytest.mark.parametrize("shape", [(8, 2, 64, "fp16"), (32, 8, 128, "bf16"), (16, 1, 128, "fp16")])
 def test_fused_append_decode_single_launch(shape):
     """Decode steps through tk_kv_append_decode: the attention kernel writes the new token's rows
