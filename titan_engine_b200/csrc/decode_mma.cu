@@ -100,7 +100,6 @@ __device__ __forceinline__ void open_page_item(uint8_t* smem, const Geometry& g,
             }
         }
     }
-    pdl_launch_dependents();
     auto red_at = [&](int w, int row, int d) -> float& { return red[((size_t)w * G + row) * (D + 2) + d]; };
 #pragma unroll
     for (int gq = 0; gq < MAXG; gq++) {
@@ -173,6 +172,12 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     const int gr = lane >> 2, j = lane & 3;                 // fragment row / column-pair index
     const int G = g.H / g.Hkv;
 
+    // A launch of the next layer may begin as soon as every CTA of this one has STARTED (the hardware hands the
+    // dependent grid only the slots this grid no longer needs): its CTAs read what kernels of other layers leave
+    // alone - their own layer's pool, q, the step's metadata - write only their own layer's pool row, and wait
+    // (pdl_wait below) before they touch what is shared with this launch: split-KV rows, arrival counters, `out`.
+    // So the last, ragged wave of one layer runs beside the first wave of the next.
+    pdl_launch_dependents();
     const int4 it = st.items[blockIdx.x];
     if (KIND == K_FP8 && it.w == 1) {                       // the 16-bit open page of an FP8 cache
         open_page_item<IO_BF16, GHI ? 16 : 8>(smem, g, lp, st, it, q, partials, mo, fa, s_flag);
@@ -548,12 +553,6 @@ decode_mma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     }
     // a wait that gave up has set the status word: the merging CTA sees it and writes no output
     (void)alive;
-    // Every page tile of this CTA has been fetched and used.  Up to here the CTA has read only what kernels
-    // of other layers leave alone (its layer's pool, q, the step's metadata) and written only its own
-    // layer's pool row, so a launch of the next layer may start now; what follows (split-KV rows, arrival
-    // counters, `out`) is shared with the launch before and waits for it to finish.
-    pdl_launch_dependents();
-
     // ---- merge the 4 warps through shared memory (stage memory is idle now) ----------
     if constexpr (SWAP) {
 #pragma unroll

@@ -65,6 +65,7 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
     const int gr = lane >> 2, j = lane & 3;                 // fragment row / column-pair index
     const int G = g.H / g.Hkv;                              // <= 8: rows 8..15 of the M tile are padding
 
+    pdl_launch_dependents();                                // a launch of another layer may fill the slots this one leaves (see decode_mma.cu)
     const int4 it = st.items[blockIdx.x];
     const int b = it.x, chunk = it.y, kvh = it.z;
     const int seq = st.seq[b], len = st.len[b];
@@ -243,9 +244,6 @@ decode_mma_mla_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_c
             issue(i + kMlaStages);
         }
     }
-
-    // every page tile has been fetched and used: a launch of another layer may start (see decode_mma.cu)
-    pdl_launch_dependents();
 
     // ---- merge the 4 warps through shared memory (stage memory is idle now) ----------
     l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 1); l0 += __shfl_xor_sync(0xFFFFFFFFu, l0, 2);

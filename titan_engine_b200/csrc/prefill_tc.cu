@@ -68,7 +68,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -425,7 +424,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                     for (int part = 0; part < 4; part++) {
                         uint32_t orow[32];
                         tmem_ld32(tmem + lane_base + kColO + 32 * part, orow);
-                        tc_wait_ld();
+                        tc_wait_ld(orow);
 #pragma unroll
                         for (int c = 0; c < 32; c++) orow[c] = __float_as_uint(__uint_as_float(orow[c]) * alpha);
                         tmem_st32(tmem + lane_base + kColO + 32 * part, orow);
@@ -467,7 +466,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
         for (int part = 0; part < 4; part++) {
             uint32_t orow[32];
             tmem_ld32(tmem + lane_base + kColO + 32 * part, orow);
-            tc_wait_ld();
+            tc_wait_ld(orow);
             if (!valid) continue;
             if (n_chunks > 1) {
 #pragma unroll

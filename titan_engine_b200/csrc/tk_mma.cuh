@@ -139,7 +139,8 @@ __device__ __forceinline__ uint32_t rope_pair(uint32_t w, const float2* __restri
 // start while the kernel before it in the stream is still running, once every CTA of that kernel has
 // executed pdl_launch_dependents() or exited; it must call pdl_wait() - which returns when the earlier
 // kernel has finished and its writes are visible - before it touches anything that kernel reads or
-// writes.  Both are no-ops in a launch without the attribute.
+// writes.  Both are no-ops in a launch without the attribute.  The decode kernels signal as their first
+// instruction: the dependent grid then gets exactly the SM slots the earlier grid has stopped needing.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
