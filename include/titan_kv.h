@@ -299,11 +299,15 @@ int tk_kv_append_decode_host(tk_kv* h, int32_t layer, const void* k_host, const 
 /* Same without the final wait.  Copies run on the handle's own copy streams so that they
  * overlap the kernels of neighbouring calls; before reading out_host the caller calls
  * tk_kv_host_wait(h, stream) and synchronises `stream`.  The host buffers must be pinned and
- * stay untouched until then. */
+ * stay untouched until then.  The copy-in starts at the call; the kernel launches of up to four
+ * consecutive calls (decode-sized steps) are held back and issued together - by the fourth call,
+ * by tk_kv_host_wait, or by any other launching entry point of the handle - so that the launches
+ * of neighbouring layers sit next to each other in the stream and overlap. */
 int tk_kv_append_decode_host_async(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
                                    const void* q_host, void* out_host, void* stream);
 
-/* Makes `stream` wait for every device-to-host copy the *_host calls have queued. */
+/* Issues the launches the *_host_async calls still hold back and makes `stream` wait for every
+ * device-to-host copy the *_host calls have queued. */
 int tk_kv_host_wait(tk_kv* h, void* stream);
 
 /* Timing of the dominant decode kernel on its own stream: after enable(n), each of the next

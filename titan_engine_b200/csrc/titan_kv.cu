@@ -19,6 +19,7 @@
 namespace {
 
 constexpr int kRing = 4;                 // pinned staging buffers in rotation
+constexpr int kHostSetsMax = 8;          // device staging sets of the host-buffer entry points
 constexpr int kMaxDelta = 1 << 16;       // page-table patches per upload; more -> full table copy
 constexpr int TK_DEVICE_NONE = -2;       // bookkeeping only: no device memory, compute calls fail
 // Guard bytes behind every buffer that kernels write at host-computed rows (the pool arena, the split-KV
@@ -127,12 +128,19 @@ struct tk_kv {
     float2* d_rope_tab = nullptr;        // [max_seqs][D/2] (cos, sin) of each sequence's newest position
     int64_t rope_tab_step = -1;          // step the table was filled for, with which parameters
     float rope_tab_theta = 0, rope_tab_scaling = 0;
-    // the *_host entry points: two staging sets, so that the copies of one layer overlap the
-    // kernel of another on the copy engines (copy-in stream, caller's stream, copy-out stream)
-    void *hs_k[2] = {}, *hs_v[2] = {}, *hs_q[2] = {}, *hs_out[2] = {};
+    // the *_host entry points: staging sets in rotation, so that the copies of one layer overlap the
+    // kernel of another on the copy engines (copy-in stream, caller's stream, copy-out stream); the
+    // asynchronous form launches its kernels in groups (see append_decode_host_impl)
+    void *hs_k[kHostSetsMax] = {}, *hs_v[kHostSetsMax] = {}, *hs_q[kHostSetsMax] = {}, *hs_out[kHostSetsMax] = {};
     cudaStream_t st_in = nullptr, st_out = nullptr;
-    cudaEvent_t ev_in[2] = {}, ev_compute[2] = {}, ev_out[2] = {};
+    cudaEvent_t ev_in[kHostSetsMax] = {}, ev_free[kHostSetsMax] = {}, ev_group = nullptr, ev_out_all = nullptr;
     uint64_t host_calls = 0;
+    int host_calls_in_step = 0;          // groups start small so that a step's first kernel does not wait for four layers' copies
+    int host_sets = 2, host_group = 1;   // sets in rotation; calls whose kernels are launched back to back
+    struct HostPending { int layer, set; bool kv, q; void* out_host; size_t o_bytes; };
+    std::vector<HostPending> host_pending;
+    cudaStream_t host_pending_stream = nullptr;
+    bool host_flushing = false;
 
     std::vector<CUtensorMap> maps;       // one per layer (MMA path); MLA shape: the K-row view
     std::vector<CUtensorMap> maps_v;     // MLA shape: the V-row view
@@ -183,6 +191,10 @@ struct tk_kv {
     }
 };
 
+extern "C" {
+static int host_flush(tk_kv* h);       // launches what the host-buffer calls hold back (defined with them)
+}
+
 namespace {
 
 int fail(tk_kv* h, int status, const char* fmt, ...) {
@@ -219,15 +231,16 @@ void release(tk_kv* h) {
         if (h->d_rq) cudaFree(h->d_rq);
         if (h->d_rope_tab) cudaFree(h->d_rope_tab);
         if (h->d_rk) cudaFree(h->d_rk);
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < kHostSetsMax; i++) {
             if (h->hs_k[i]) cudaFree(h->hs_k[i]);
             if (h->hs_v[i]) cudaFree(h->hs_v[i]);
             if (h->hs_q[i]) cudaFree(h->hs_q[i]);
             if (h->hs_out[i]) cudaFree(h->hs_out[i]);
             if (h->ev_in[i]) cudaEventDestroy(h->ev_in[i]);
-            if (h->ev_compute[i]) cudaEventDestroy(h->ev_compute[i]);
-            if (h->ev_out[i]) cudaEventDestroy(h->ev_out[i]);
+            if (h->ev_free[i]) cudaEventDestroy(h->ev_free[i]);
         }
+        if (h->ev_group) cudaEventDestroy(h->ev_group);
+        if (h->ev_out_all) cudaEventDestroy(h->ev_out_all);
         if (h->st_in) cudaStreamDestroy(h->st_in);
         if (h->st_out) cudaStreamDestroy(h->st_out);
         for (int i = 0; i < kRing; i++) {
@@ -352,15 +365,19 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
     CREATE_CUDA(cudaMalloc(&h->d_rq, q_bytes));
     CREATE_CUDA(cudaMalloc((void**)&h->d_rope_tab, sizeof(float2) * (size_t)c.max_seqs * (c.head_dim / 2)));
     CREATE_CUDA(cudaMalloc(&h->d_rk, kv_bytes));
-    for (int i = 0; i < 2; i++) {
+    // decode-sized steps: 8 sets, kernels launched up to four calls at a time; prefill-sized steps keep two sets
+    h->host_group = 2 * (kv_bytes + q_bytes) * kHostSetsMax <= ((size_t)64 << 20) ? kHostSetsMax / 2 : 1;
+    h->host_sets = 2 * h->host_group;
+    for (int i = 0; i < h->host_sets; i++) {
         CREATE_CUDA(cudaMalloc(&h->hs_k[i], kv_bytes));
         CREATE_CUDA(cudaMalloc(&h->hs_v[i], kv_bytes));
         CREATE_CUDA(cudaMalloc(&h->hs_q[i], q_bytes));
         CREATE_CUDA(cudaMalloc(&h->hs_out[i], q_bytes));
         CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_in[i], cudaEventDisableTiming));
-        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_compute[i], cudaEventDisableTiming));
-        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_out[i], cudaEventDisableTiming));
+        CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_free[i], cudaEventDisableTiming));
     }
+    CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_group, cudaEventDisableTiming));
+    CREATE_CUDA(cudaEventCreateWithFlags(&h->ev_out_all, cudaEventDisableTiming));
     CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_in, cudaStreamNonBlocking));
     CREATE_CUDA(cudaStreamCreateWithFlags(&h->st_out, cudaStreamNonBlocking));
 
@@ -670,6 +687,8 @@ int tk_kv_get_stats(const tk_kv* h, tk_kv_stats* out) {
 static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_new,
                            const int32_t* len_cap, void* stream) {
     if (!h) return TK_INVALID_ARG;
+    if (const int fs = host_flush(h)) return fs;               // launches the host-buffer calls still hold back come first
+    h->host_calls_in_step = 0;
     if (len_cap && h->cfg.dtype == TK_FP8_E4M3)
         return fail(h, TK_UNSUPPORTED, "step_begin: an attended-length cap needs 16-bit storage");
     std::lock_guard<std::mutex> lock(h->mgr_mu);
@@ -828,6 +847,7 @@ int tk_kv_step_prefill_plan(const tk_kv* h, int32_t cap, int32_t* items, int32_t
 
 int tk_kv_append(tk_kv* h, int32_t layer, const void* k, const void* v, int64_t* slots_out, void* stream) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (const int fs = host_flush(h)) return fs;               // launches the host-buffer calls still hold back come first
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "append: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "append: no step in progress (call tk_kv_step_begin)");
     if (h->dev.n_tokens == 0) return TK_OK;
@@ -845,6 +865,7 @@ static int decode_impl(tk_kv* h, int layer, const void* q, void* out, float* par
                        const void* fuse_v = nullptr, const float* rope = nullptr,
                        const tk::PeerCtx* peer_ctx = nullptr) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (const int fs = host_flush(h)) return fs;               // launches the host-buffer calls still hold back come first
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode: no step in progress (call tk_kv_step_begin)");
     if (h->dev.n_seqs == 0) return TK_OK;
@@ -927,6 +948,7 @@ int tk_kv_decode(tk_kv* h, int32_t layer, const void* q, void* out, void* stream
 int tk_kv_append_decode(tk_kv* h, int32_t layer, const void* k, const void* v, const void* q, void* out,
                         void* stream) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (const int fs = host_flush(h)) return fs;               // launches the host-buffer calls still hold back come first
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "append_decode: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "append_decode: no step in progress (call tk_kv_step_begin)");
     // 16-bit storage: the new row goes into the page the kernel is about to read.  FP8 storage: it
@@ -997,6 +1019,7 @@ static float* multi_workspace(tk_kv* h, size_t floats, cudaStream_t stream) {
 // pass over the pages: what the verification of drafted tokens needs.
 static int decode_multi_impl(tk_kv* h, int32_t layer, const void* q, void* out, int out_dtype, void* stream) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
+    if (const int fs = host_flush(h)) return fs;               // launches the host-buffer calls still hold back come first
     if (out_dtype != TK_FP32 && out_dtype != h->cfg.io_dtype)
         return fail(h, TK_INVALID_ARG, "decode_multi: out dtype must be FP32 or the handle's io dtype");
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode_multi: handle has no device (bookkeeping only)");
@@ -1082,6 +1105,7 @@ int tk_kv_append_decode_multi(tk_kv* h, int32_t layer, const void* k, const void
 // same cells - so ranks that take different routes for the same layer still meet.
 int tk_kv_decode_exchange(tk_kv* h, int32_t layer, const void* q, tk_peer* peer, void* out, void* stream) {
     if (!h || !peer || !out) return TK_INVALID_ARG;
+    if (const int fs = host_flush(h)) return fs;               // launches the host-buffer calls still hold back come first
     if (h->host_only) return fail(h, TK_CUDA_ERROR, "decode_exchange: handle has no device (bookkeeping only)");
     if (!h->have_step) return fail(h, TK_INVALID_ARG, "decode_exchange: no step in progress (call tk_kv_step_begin)");
     const tk::PeerCtx* ctx = tk::peer_device_ctx(peer);
@@ -1120,12 +1144,47 @@ int tk_combine_partials(const float* parts, int32_t n_parts, int32_t n_rows, int
     return e == cudaSuccess ? TK_OK : TK_CUDA_ERROR;
 }
 
-// Host-buffer path.  Call n uses staging set n&1:
-//   copy-in stream : (wait: kernel of call n-2 done with this set)  H2D k, v, q
-//   caller's stream: (wait: H2D done, D2H of call n-2 done)         append + decode
-//   copy-out stream: (wait: kernel done)                            D2H out
-// so the copies of neighbouring layers ride the copy engines while a kernel runs.
-// tk_kv_host_wait() makes the caller's stream wait for the outstanding D2H copies.
+// Host-buffer path.  Call n uses staging set n % host_sets:
+//   copy-in stream : (wait: this set's last use is over)            H2D k, v, q        - at the call
+//   caller's stream: (wait: H2D of the group's last call done)      append + decode    - one group of calls at a time
+//   copy-out stream: (wait: the group's kernels done)               D2H out of each call of the group
+// so the copies of neighbouring layers ride the copy engines while a kernel runs.  The asynchronous form
+// holds its kernel launches back until host_group calls are in (or until tk_kv_host_wait, a new step, or any
+// other launching entry point): an event wait or record BETWEEN two attention launches keeps the later one
+// from starting while the earlier one drains (programmatic dependent launch needs them adjacent in the
+// stream), so the waits and records go around a group of launches, not around each.
+// tk_kv_host_wait() launches what is held back and makes the caller's stream wait for the outstanding D2H copies.
+static int host_flush(tk_kv* h) {
+    if (h->host_flushing || h->host_pending.empty()) return TK_OK;
+    h->host_flushing = true;
+    std::vector<tk_kv::HostPending> pend;
+    pend.swap(h->host_pending);
+    cudaStream_t s = h->host_pending_stream;
+    int st = TK_OK;
+    cudaError_t e = cudaStreamWaitEvent(s, h->ev_in[pend.back().set], 0);   // the copy-in stream is in order: all of them are in
+    for (size_t i = 0; i < pend.size() && st == TK_OK && e == cudaSuccess; i++) {
+        const auto& p = pend[i];
+        if (p.kv && p.q)  st = tk_kv_append_decode(h, p.layer, h->hs_k[p.set], h->hs_v[p.set], h->hs_q[p.set], h->hs_out[p.set], s);
+        else if (p.kv)    st = tk_kv_append(h, p.layer, h->hs_k[p.set], h->hs_v[p.set], nullptr, s);
+        else if (p.q)     st = tk_kv_decode(h, p.layer, h->hs_q[p.set], h->hs_out[p.set], s);
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_group, s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(h->st_out, h->ev_group, 0);
+    for (size_t i = 0; i < pend.size() && e == cudaSuccess; i++) {
+        const auto& p = pend[i];
+        if (p.q && st == TK_OK) {
+            e = cudaMemcpyAsync(p.out_host, h->hs_out[p.set], p.o_bytes, cudaMemcpyDeviceToHost, h->st_out);
+            h->stats.bytes_d2h += (int64_t)p.o_bytes;
+        }
+        if (e == cudaSuccess) e = cudaEventRecord(h->ev_free[p.set], h->st_out);
+    }
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_out_all, h->st_out);
+    h->host_flushing = false;
+    if (st != TK_OK) return st;
+    if (e != cudaSuccess) return fail(h, TK_CUDA_ERROR, cudaGetErrorString(e));
+    return TK_OK;
+}
+
 static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, const void* v_host,
                                    const void* q_host, void* out_host, void* stream, bool wait) {
     if (!h || layer < 0 || layer >= h->cfg.num_layers) return TK_INVALID_ARG;
@@ -1138,8 +1197,12 @@ static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, 
     const size_t o_bytes = (size_t)h->dev.n_seqs * h->cfg.num_heads * h->cfg.v_head_dim * 2;
     if (kv_bytes && (!k_host || !v_host)) return fail(h, TK_INVALID_ARG, "append_decode_host: null k/v");
     if (q_bytes && (!q_host || !out_host)) return fail(h, TK_INVALID_ARG, "append_decode_host: null q/out");
-    const int set = (int)(h->host_calls++ & 1);
-    TK_CUDA(h, cudaStreamWaitEvent(h->st_in, h->ev_compute[set], 0));
+    if (!h->host_pending.empty() && h->host_pending_stream != s) {      // one group, one stream
+        const int st = host_flush(h);
+        if (st != TK_OK) return st;
+    }
+    const int set = (int)(h->host_calls++ % (uint64_t)h->host_sets);
+    TK_CUDA(h, cudaStreamWaitEvent(h->st_in, h->ev_free[set], 0));
     if (kv_bytes) {
         TK_CUDA(h, cudaMemcpyAsync(h->hs_k[set], k_host, kv_bytes, cudaMemcpyHostToDevice, h->st_in));
         TK_CUDA(h, cudaMemcpyAsync(h->hs_v[set], v_host, vv_bytes, cudaMemcpyHostToDevice, h->st_in));
@@ -1150,19 +1213,13 @@ static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, 
         h->stats.bytes_h2d += (int64_t)q_bytes;
     }
     TK_CUDA(h, cudaEventRecord(h->ev_in[set], h->st_in));
-    TK_CUDA(h, cudaStreamWaitEvent(s, h->ev_in[set], 0));
-    TK_CUDA(h, cudaStreamWaitEvent(s, h->ev_out[set], 0));
-    int st = TK_OK;
-    if (kv_bytes && q_bytes)  st = tk_kv_append_decode(h, layer, h->hs_k[set], h->hs_v[set], h->hs_q[set], h->hs_out[set], stream);
-    else if (kv_bytes)        st = tk_kv_append(h, layer, h->hs_k[set], h->hs_v[set], nullptr, stream);
-    else if (q_bytes)         st = tk_kv_decode(h, layer, h->hs_q[set], h->hs_out[set], stream);
-    if (st != TK_OK) return st;
-    TK_CUDA(h, cudaEventRecord(h->ev_compute[set], s));
-    if (q_bytes) {
-        TK_CUDA(h, cudaStreamWaitEvent(h->st_out, h->ev_compute[set], 0));
-        TK_CUDA(h, cudaMemcpyAsync(out_host, h->hs_out[set], o_bytes, cudaMemcpyDeviceToHost, h->st_out));
-        TK_CUDA(h, cudaEventRecord(h->ev_out[set], h->st_out));
-        h->stats.bytes_d2h += (int64_t)o_bytes;
+    h->host_pending.push_back({layer, set, kv_bytes != 0, q_bytes != 0, out_host, o_bytes});
+    h->host_pending_stream = s;
+    const int c = h->host_calls_in_step++;
+    const int group = std::min(h->host_group, c < 2 ? 1 : (c < 6 ? 2 : 4));   // 1, 1, 2, 2, 4, 4, ...
+    if (wait || (int)h->host_pending.size() >= group) {
+        const int st = host_flush(h);
+        if (st != TK_OK) return st;
     }
     if (wait) {
         TK_CUDA(h, cudaStreamSynchronize(s));
@@ -1173,7 +1230,9 @@ static int append_decode_host_impl(tk_kv* h, int32_t layer, const void* k_host, 
 
 int tk_kv_host_wait(tk_kv* h, void* stream) {
     if (!h || h->host_only) return TK_INVALID_ARG;
-    for (int i = 0; i < 2; i++) TK_CUDA(h, cudaStreamWaitEvent((cudaStream_t)stream, h->ev_out[i], 0));
+    const int st = host_flush(h);
+    if (st != TK_OK) return st;
+    TK_CUDA(h, cudaStreamWaitEvent((cudaStream_t)stream, h->ev_out_all, 0));
     return TK_OK;
 }
 
@@ -1229,6 +1288,7 @@ int tk_kv_profile_read_each(tk_kv* h, float* ms_out, int32_t cap, int32_t* launc
 
 int tk_kv_device_status(tk_kv* h, void* stream) {
     if (!h || h->host_only) return TK_INVALID_ARG;
+    if (const int fs = host_flush(h)) return fs;               // launches the host-buffer calls still hold back come first
     int st = 0;
     TK_CUDA(h, cudaMemcpyAsync(&st, h->d_status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
     TK_CUDA(h, cudaStreamSynchronize((cudaStream_t)stream));
