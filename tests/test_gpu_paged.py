@@ -206,6 +206,48 @@ def test_host_buffer_entry_point():
     assert st["bytes_h2d"] > 0 and st["bytes_d2h"] > 0 and t.gpu.launch_count > 0
 
 
+def test_host_buffer_async_groups_equal_device_path():
+    """tk_kv_append_decode_host_async holds its kernel launches back and issues them in groups (1, 1, 2, 2, 4, ...):
+    eleven layers per step through it - so that groups of every size and a partly filled last group occur - against a
+    second cache driven through the device entry point with the same rows; a device call in the middle of a step and
+    the next step_begin both have to issue what is held back first.  Outputs and pools must be identical."""
+    from titan_engine_b200 import PagedKVCache
+    Lyr, H, Hkv, D, B = 11, 32, 8, 128, 5
+    dev = torch.device("cuda")
+    mk = lambda: PagedKVCache(Lyr, H, Hkv, D, 64, B, 12, dtype="bf16", max_step_tokens=256)
+    a, b = mk(), mk()
+    sa = [a.seq_alloc() for _ in range(B)]; sb = [b.seq_alloc() for _ in range(B)]
+    gen = torch.Generator(device="cpu"); gen.manual_seed(7)
+    for step, n_new in enumerate([[40, 3, 17, 1, 16], [1] * B, [1] * B, [1] * B]):
+        n_tok = sum(n_new)
+        hk = [torch.randn(n_tok, Hkv, D, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(Lyr)]
+        hv = [torch.randn(n_tok, Hkv, D, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(Lyr)]
+        hq = [torch.randn(B, H, D, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(Lyr)]
+        ho = [torch.zeros(B, H, D, dtype=torch.bfloat16).pin_memory() for _ in range(Lyr)]
+        a.step_begin(sa, n_new); b.step_begin(sb, n_new)
+        ref = [b.append_decode(l, hk[l].to(dev), hv[l].to(dev), hq[l].to(dev)) for l in range(Lyr)]
+        for l in range(Lyr):
+            if step == 2 and l == 7:                        # a device call between two held-back host calls
+                a.append_decode(l, hk[l].to(dev), hv[l].to(dev), hq[l].to(dev), out=(tmp := torch.empty(B, H, D, dtype=torch.bfloat16, device=dev)))
+                ho[l].copy_(tmp)
+            else:
+                a.append_decode_host_async(l, hk[l], hv[l], hq[l], ho[l])
+        if step != 1:                                        # step 1 leaves its last group to the next step_begin
+            a.host_wait()
+            torch.cuda.synchronize()
+            for l in range(Lyr):
+                assert torch.equal(ho[l], ref[l].cpu()), f"step {step} layer {l}"
+        else:
+            keep = (ho, ref)
+        if step == 2:                                        # by now step 1's copies have landed too
+            for l in range(Lyr):
+                assert torch.equal(keep[0][l], keep[1][l].cpu()), f"step 1 layer {l}"
+    torch.cuda.synchronize()
+    for l in range(Lyr):
+        assert torch.equal(a.layer_views(l)[0], b.layer_views(l)[0]), f"pool of layer {l}"
+    a.device_status(); b.device_status()
+
+
 def test_partials_and_cross_rank_combine():
     """Two 'ranks' each hold half of one sequence; merged partials equal single-cache attention."""
     from titan_engine_b200 import _lib as L
