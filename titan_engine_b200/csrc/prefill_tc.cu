@@ -10,20 +10,25 @@
 // no shuffles in the softmax), an MMA warp whose one elected thread issues every tcgen05.mma, and a loader warp
 // whose lanes issue the TMA copies; the roles meet on mbarriers only (no CTA-wide barrier inside the loop).
 // (Measured with clock64 around each phase: with one thread issuing both the 16 copies and the 12 MMAs of a
-// block, that thread was busy 80 % of the kernel and the softmax warps waited for it 60 % of theirs.)  Per block of 64 context tokens (4 pages):
+// block, that thread was busy 80 % of the kernel and the softmax warps waited for it 60 % of theirs.)
+// Per block of 64 context tokens (4 pages):
 //   TMA      K rows and V rows of the 4 pages land as [64 tokens][128 B] slabs per 64-dim half (128-byte
-//            swizzle): separate boxes of 16 rows, so that the K rows of consecutive pages are consecutive
+//            swizzle): separate boxes of 16 rows, so that the K rows of consecutive pages are consecutive;
+//            eight boxes leave in one instruction of the loader warp, two stages for K and two for V
 //   S = Q K^T  one thread issues 8 tcgen05.mma (M 128, N 64, K 16) with Q and K from shared memory (K-major
 //            descriptors), S in one of two TMEM buffers (columns [0, 64) and [64, 128)); tcgen05.commit -> mbarrier.
 //            S of block i+2 is issued right behind P V of block i, S of block i+1 is already there: the tensor
 //            pipe works while the threads do the softmax of block i
-//   softmax  every thread tcgen05.ld's its row of S, masks (causal limit of its token, end of the sequence),
-//            sum and reference maximum in base-2 units, P = exp2(..) rounded to the 16-bit type, tcgen05.st over
-//            the first 32 columns of the S buffer it came from; the reference maximum moves only when a block
-//            exceeds it by 2^8, and only then the warp rescales its rows of O in TMEM (ld, multiply, st)
+//   softmax  every thread tcgen05.ld's its row of S (the second half while it works on the first).  Blocks that no
+//            row of the warp sees cut (causal limit of its token, end of the sequence) take ONE pass: maximum,
+//            exp2 against the current reference maximum, sum, P rounded to the 16-bit type - speculating that the
+//            reference stays, which it does unless a score exceeds it by 2^8; only then (and on cut blocks) the
+//            careful pass recomputes against the new reference and the warp rescales its rows of O in TMEM (ld,
+//            multiply, st), for which alone it waits for the previous P V.  P goes over the first 32 columns of
+//            the S buffer it came from (tcgen05.st); an mbarrier with one arrival per row tells the MMA thread
 //   O += P V   4 tcgen05.mma (M 128, N 128, K 16) with P from TMEM and V from shared memory (MN-major
 //            descriptor: V rows are tokens), O in TMEM columns [128, 256)
-// Two CTAs share an SM (256 TMEM columns and 98 KB of shared memory each), so one CTA's softmax overlaps the
+// Two CTAs share an SM (256 TMEM columns and 108 KB of shared memory each), so one CTA's softmax overlaps the
 // other's MMAs.  No cluster, no multicast, cta_group::1 only, this GPU's memory only.
 // Measured and left out: computing a share of the exponentials as a cubic on the FMA pipe (0 / 12.5 / 25 / 50 % of
 // them: 916 / 887 / 856 / 793 TFLOP/s) - the softmax warps are short of issue slots and latency cover, not of
