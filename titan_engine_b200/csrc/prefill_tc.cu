@@ -210,7 +210,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     const size_t qo_row = (size_t)(st.q_base[b] + tok_first + tid / G) * g.H + (size_t)kvh * G + tid % G;
 
     if (tid == 0) {
-        for (int i = 0; i < 2 * kTcStages + 3; i++) mbar_init(smem_u32(&bars[i]), 1);
+        for (int i = 2 * kTcStages; i < 2 * kTcStages + 3; i++) mbar_init(smem_u32(&bars[i]), 1);
         mbar_init(smem_u32(&p_ready[0]), kTcRows + 1);
         mbar_init(smem_u32(&p_ready[1]), kTcRows + 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -219,8 +219,31 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
         tmem_alloc(smem_u32(s_tmem), kTmemCols);
         tmem_relinquish();
     }
-    for (int i = tid; i < n_pages; i += blockDim.x)
-        s_pages[i] = page_table[(size_t)seq * g.max_pages_per_seq + lp0 + i];
+    const int32_t* pt_row = page_table + (size_t)seq * g.max_pages_per_seq + lp0;
+    for (int i = tid; i < n_pages; i += blockDim.x) s_pages[i] = pt_row[i];
+    // The loader warp does not wait for the rest of the prologue: it sets up the K/V barriers itself and sends the
+    // copies of the first two blocks off with page ids read straight from the table.
+    auto load_rows = [&](int blk, bool is_v, const int32_t* pages_of) {
+        const int s = blk % kTcStages;
+        const int pages = min(4, n_pages - 4 * blk);
+        const uint32_t bar = smem_u32(is_v ? &vfull[s] : &kfull[s]);
+        if (lane == 0) mbar_expect_tx(bar, pages * 2 * 2048);
+        __syncwarp();
+        const int p = lane >> 1, h = lane & 1;
+        if (lane < 8 && p < pages) {
+            const int row = (pages_of[4 * blk + p] * g.Hkv + kvh) * 32 + (is_v ? 16 : 0);
+            tma_load_2d_shared_tile(smem_u32((is_v ? s_v : s_k) + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, bar);
+        }
+    };
+    if (warp == kTcRows / 32 + 1) {
+        if (lane == 0) {
+            for (int i = 0; i < 2 * kTcStages; i++) mbar_init(smem_u32(&bars[i]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+        load_rows(0, false, pt_row); load_rows(0, true, pt_row);
+        if (n_blocks > 1) { load_rows(1, false, pt_row); load_rows(1, true, pt_row); }
+    }
     // Q row -> shared memory in the 128-byte-swizzled K-major form the MMA reads (16-byte chunk c of a row
     // sits at chunk c ^ (row & 7)); rows without a token are zero
     if (tid < kTcRows) {
@@ -231,8 +254,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
             *reinterpret_cast<uint4*>(s_q + (c >> 3) * (kTcRows * 128) + tid * 128 + (((c & 7) ^ (tid & 7)) << 4)) = v;
         }
     }
-    // V slabs start as zeros: a block whose last pages do not exist must not feed stale bits to 0 * V
-    for (int i = tid; i < kTcStages * kSlabBytes / 16; i += blockDim.x) reinterpret_cast<uint4*>(s_v)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes above -> visible to TMA / MMA
     tc_fence_before();
     __syncthreads();
@@ -240,20 +261,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     const uint32_t tmem = *s_tmem;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's 32 TMEM lanes
 
-    // loader warp: K rows (V rows) of block `blk` -> stage blk % 2, a box of 16 rows x 128 B per page and 64-dim half;
-    // lane i < 8 issues box i (page i / 2, half i % 2), so the eight copies leave in one instruction
-    auto load_rows = [&](int blk, bool is_v) {
-        const int s = blk % kTcStages;
-        const int pages = min(4, n_pages - 4 * blk);
-        const uint32_t bar = smem_u32(is_v ? &vfull[s] : &kfull[s]);
-        if (lane == 0) mbar_expect_tx(bar, pages * 2 * 2048);
-        __syncwarp();
-        const int p = lane >> 1, h = lane & 1;
-        if (lane < 8 && p < pages) {
-            const int row = (s_pages[4 * blk + p] * g.Hkv + kvh) * 32 + (is_v ? 16 : 0);
-            tma_load_2d_shared_tile(smem_u32((is_v ? s_v : s_k) + s * kSlabBytes + h * kHalfBytes + p * 2048), &tmap, h * 64, row, bar);
-        }
-    };
     constexpr uint32_t kIdescS = instr_desc(BF, false, kTcBlock);
     constexpr uint32_t kIdescO = instr_desc(BF, true, D);
     // MMA thread: the descriptors of a stage differ from those of stage 0 by the stage's byte offset / 16 in the
@@ -309,18 +316,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
         __syncwarp();
     } else if (warp == kTcRows / 32 + 1) {
         // ===== loader warp: keeps the two K stages and the two V stages full =====
-        load_rows(0, false); load_rows(0, true);
-        if (n_blocks > 1) { load_rows(1, false); load_rows(1, true); }
+        // (the copies of blocks 0 and 1 left in the prologue)
         for (int blk = 0; blk < n_blocks; blk++) {
             // S(blk) is done with its K stage: K of the block after next goes there
             if (blk + 2 < n_blocks) {
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&bar_s[blk & 1]), (uint32_t)((blk >> 1) & 1), status))) break;
-                load_rows(blk + 2, false);
+                load_rows(blk + 2, false, s_pages);
             }
             // P V (blk-1) is done with its V stage: V of the next block goes there
             if (blk > 0 && blk + 1 < n_blocks) {
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) break;
-                load_rows(blk + 1, true);
+                load_rows(blk + 1, true, s_pages);
             }
             // P V (blk) may not complete before this warp has seen P V (blk-1) complete (a parity wait cannot tell
             // a phase that is two ahead from one that has not happened): the MMA thread waits for this arrival too
@@ -439,11 +445,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
             if (!p_stored) tmem_st32(tmem + lane_base + col_s, pr);   // P over the columns S was read from
             tc_wait_st();
 
-            // rows past the sequence's end hold whatever the page's last owner left: zero those V rows of the slab
-            const int n_live = len - tok_base;               // tokens of the sequence in this block
-            if (n_live < kTcBlock && n_live < 16 * min(4, n_pages - 4 * blk)) {
+            // V rows of the slab that no copy of this block wrote (pages this tile does not need: whatever the stage
+            // held before, at first whatever the SM's last CTA left) or that lie past the sequence's end (whatever the
+            // page's last owner left) meet P = 0, and 0 * NaN is NaN: zero them.  Last block(s) of a tile only.
+            const int n_good = min(len - tok_base, 16 * min(4, n_pages - 4 * blk));   // rows that hold tokens of the sequence
+            if (n_good < kTcBlock) {
                 if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status))) { alive = false; break; }
-                const int r0 = max(n_live, 0), n_rows = kTcBlock - r0;
+                const int r0 = max(n_good, 0), n_rows = kTcBlock - r0;
                 for (int i = tid; i < n_rows * 16; i += kTcRows) {
                     const int r = r0 + (i >> 4), c = i & 15;
                     *reinterpret_cast<uint4*>(s_v + s * kSlabBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
