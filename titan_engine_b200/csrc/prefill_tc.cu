@@ -35,6 +35,8 @@
 // special-function throughput.  Nor did more softmax warps help: two threads per row (8 softmax warps per CTA, 32
 // columns each, the halves' maxima exchanged through shared memory on a named barrier per warp pair) ran at 771
 // against 930 TFLOP/s; nor the pass written out in batches of 16 exponentials with four chains each (895).
+// Nor blocks of 128 tokens with ONE S buffer of 128 columns (8 + 8 MMAs per block, half the barrier traffic and
+// TMA instructions per token, but S of the next block cannot start before P V of this one): 857 against 935.
 // Every mbarrier wait is bounded; on expiry the status word is set, nothing is written, and the CTA still
 // frees its tensor memory before it returns.
 #include "tk_kernels.cuh"
