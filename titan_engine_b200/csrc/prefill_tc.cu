@@ -292,14 +292,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     if (warp == kTcRows / 32) {
         // ===== MMA warp: one thread feeds the tensor pipe; nobody else waits for its instruction stream =====
         if (lane == 0) {
-            bool ok = mbar_wait_bounded(smem_u32(&kfull[0]), 0u, status);
+            bool ok = mbar_wait_bounded_idle(smem_u32(&kfull[0]), 0u, status);
             if (ok) issue_s(0);
-            if (ok && n_blocks > 1 && (ok = mbar_wait_bounded(smem_u32(&kfull[1]), 0u, status))) issue_s(1);
+            if (ok && n_blocks > 1 && (ok = mbar_wait_bounded_idle(smem_u32(&kfull[1]), 0u, status))) issue_s(1);
             for (int blk = 0; blk < n_blocks && ok; blk++) {
                 const int s = blk % kTcStages, buf = blk & 1;
                 // every row's P of this block is in TMEM (and O rescaled): O += P V, then S of the block after next
-                ok = mbar_wait_bounded(smem_u32(&p_ready[buf]), (uint32_t)((blk >> 1) & 1), status) &&
-                     mbar_wait_bounded(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status);
+                ok = mbar_wait_bounded_idle(smem_u32(&p_ready[buf]), (uint32_t)((blk >> 1) & 1), status) &&
+                     mbar_wait_bounded_idle(smem_u32(&vfull[s]), (uint32_t)((blk / kTcStages) & 1), status);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t a_p = tmem + kColS + 64u * buf;
@@ -310,7 +310,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
                 tc_commit(smem_u32(bar_o));
                 // the tensor pipe runs its MMAs in issue order: S(blk+2) overwrites these columns after P V has read them
                 if (blk + 2 < n_blocks) {
-                    ok = mbar_wait_bounded(smem_u32(&kfull[s]), (uint32_t)(((blk + 2) / kTcStages) & 1), status);
+                    ok = mbar_wait_bounded_idle(smem_u32(&kfull[s]), (uint32_t)(((blk + 2) / kTcStages) & 1), status);
                     if (ok) issue_s(blk + 2);
                 }
             }
@@ -322,12 +322,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
         for (int blk = 0; blk < n_blocks; blk++) {
             // S(blk) is done with its K stage: K of the block after next goes there
             if (blk + 2 < n_blocks) {
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(&bar_s[blk & 1]), (uint32_t)((blk >> 1) & 1), status))) break;
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded_idle(smem_u32(&bar_s[blk & 1]), (uint32_t)((blk >> 1) & 1), status))) break;
                 load_rows(blk + 2, false, s_pages);
             }
             // P V (blk-1) is done with its V stage: V of the next block goes there
             if (blk > 0 && blk + 1 < n_blocks) {
-                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) break;
+                if (!__all_sync(0xFFFFFFFFu, mbar_wait_bounded_idle(smem_u32(bar_o), (uint32_t)((blk - 1) & 1), status))) break;
                 load_rows(blk + 1, true, s_pages);
             }
             // P V (blk) may not complete before this warp has seen P V (blk-1) complete (a parity wait cannot tell

@@ -41,6 +41,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same test, but the thread may stay suspended in hardware for up to `hint_ns` while the phase is not complete
+// (it is woken when it completes): a waiting thread then costs its scheduler almost no issue slots.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -52,6 +63,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     while (!mbar_try_wait(bar, parity)) {
+        if (globaltimer_ns() - t0 > limit_ns) {
+            if (status) atomicExch(status, 4 /* TK_TIMEOUT */);
+            return false;
+        }
+    }
+    return true;
+}
+// For threads that do nothing but wait (a producer role between two pieces of work): suspended waits.
+__device__ __forceinline__ bool mbar_wait_bounded_idle(uint32_t bar, uint32_t parity, int* status,
+                                                       unsigned long long limit_ns = kWaitLimitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    while (!mbar_try_wait_suspend(bar, parity, 100000u)) {
         if (globaltimer_ns() - t0 > limit_ns) {
             if (status) atomicExch(status, 4 /* TK_TIMEOUT */);
             return false;
