@@ -493,9 +493,35 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         }
         for (const WorkItem& w : plan->items)
             if (is_small(w.b)) plan->pf_small_items.push_back(w);     // already big-first
+        // Launch order: the tiles and chunks of one (sequence, kv head) walk the same K/V pages, so they go out
+        // together and the pages stay in L2 (with a plain big-first order every group of the step was in flight at
+        // once and each page came from DRAM ~9 times).  Groups by total work, big first, are cut into sets of about
+        // 48 MB of K/V; inside a set the items go big first, which keeps the load balance of the plain order when
+        // contexts are short.
         std::vector<int32_t> ord(plan->pf_items.size());
         for (size_t i = 0; i < ord.size(); i++) ord[i] = (int32_t)i;
-        std::stable_sort(ord.begin(), ord.end(), [&](int32_t a, int32_t b) { return weight[a] > weight[b]; });
+        const size_t n_groups = (size_t)n_seqs * num_kv_heads;
+        std::vector<int64_t> group_weight(n_groups, 0);
+        std::vector<int32_t> group_items(n_groups, 0), group_set(n_groups, 0), gord;
+        auto group_of = [&](int32_t k) { return (size_t)plan->pf_items[k].b * num_kv_heads + plan->pf_items[k].kvh; };
+        for (size_t k = 0; k < ord.size(); k++) { group_weight[group_of((int32_t)k)] += weight[k]; group_items[group_of((int32_t)k)]++; }
+        for (size_t gi = 0; gi < n_groups; gi++) if (group_items[gi]) gord.push_back((int32_t)gi);
+        std::stable_sort(gord.begin(), gord.end(), [&](int32_t a, int32_t b) { return group_weight[a] > group_weight[b]; });
+        {
+            constexpr int64_t kSetBytes = (int64_t)48 << 20;
+            int64_t bytes_in = 0;
+            int32_t set = 0;
+            for (int32_t gi : gord) {
+                const int64_t kv_bytes = (int64_t)plan->len[gi / num_kv_heads] * 512;   // K and V rows of 128 16-bit dims
+                if (bytes_in > 0 && bytes_in + kv_bytes > kSetBytes) { set++; bytes_in = 0; }
+                group_set[gi] = set;
+                bytes_in += kv_bytes;
+            }
+        }
+        std::stable_sort(ord.begin(), ord.end(), [&](int32_t a, int32_t b) {
+            const int32_t sa = group_set[group_of(a)], sb = group_set[group_of(b)];
+            return sa != sb ? sa < sb : weight[a] > weight[b];
+        });
         std::vector<WorkItem> pf_sorted(ord.size());
         for (size_t i = 0; i < ord.size(); i++) pf_sorted[i] = plan->pf_items[ord[i]];
         plan->pf_items.swap(pf_sorted);
