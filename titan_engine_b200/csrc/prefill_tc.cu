@@ -190,10 +190,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = g.H / g.Hkv;
-    const int4 it = pf.items[blockIdx.x];
+    // item and the facts about its sequence in three independent loads (not item -> sequence index -> facts)
+    const int4 it = pf.items[blockIdx.x], i0 = pf.info[2 * blockIdx.x], i1 = pf.info[2 * blockIdx.x + 1];
     const int b = it.x, chunk = it.y, kvh = it.z, tile = it.w;
-    const int seq = st.seq[b], len = st.len[b], nq = st.nq[b];
-    const int ct = pf.ct[b];
+    const int seq = i0.x, len = i0.y, nq = i0.z, ct = i0.w;
+    const int q_base = i1.x, poff = i1.y, cbase = i1.z;
     const int tpt = kTcRows / G;                            // query tokens per tile
     const int tok_first = tile * tpt;
     const int tok_cnt = min(nq - tok_first, tpt);
@@ -209,8 +210,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     // this thread's row: query token tid / G of the tile, head tid % G of the group
     const bool valid = tid < kTcRows && tid / G < tok_cnt;
     const int lim = base_pos + tok_first + tid / G + 1;     // positions the row attends to: [0, lim)
-    const size_t qo_row = (size_t)(st.q_base[b] + tok_first + tid / G) * g.H + (size_t)kvh * G + tid % G;
+    const size_t qo_row = (size_t)(q_base + tok_first + tid / G) * g.H + (size_t)kvh * G + tid % G;
 
+    // Q tile of the CTA: 128 rows of 256 B.  The loads go out first, so that their latency runs beside the rest of the
+    // prologue (barriers, tensor-memory allocation, page ids, the first K/V copies), and each warp instruction reads
+    // two whole rows: vector i of thread t is 16-byte chunk (i * 128 + t) % 16 of row (i * 128 + t) / 16.
+    uint4 qv[16];
+    if (tid < kTcRows) {
+        const int sh = __ffs(G) - 1;                        // G divides 128: a power of two
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int r = (i * kTcRows + tid) >> 4, c = tid & 15;
+            const bool ok = (r >> sh) < tok_cnt;
+            const size_t row = (size_t)(q_base + tok_first + (r >> sh)) * g.H + (size_t)kvh * G + (r & (G - 1));
+            qv[i] = ok ? __ldg(reinterpret_cast<const uint4*>(q + row * D) + c) : make_uint4(0, 0, 0, 0);
+        }
+    }
     if (tid == 0) {
         for (int i = 2 * kTcStages; i < 2 * kTcStages + 3; i++) mbar_init(smem_u32(&bars[i]), 1);
         mbar_init(smem_u32(&p_ready[0]), kTcRows + 1);
@@ -246,14 +261,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
         load_rows(0, false, pt_row); load_rows(0, true, pt_row);
         if (n_blocks > 1) { load_rows(1, false, pt_row); load_rows(1, true, pt_row); }
     }
-    // Q row -> shared memory in the 128-byte-swizzled K-major form the MMA reads (16-byte chunk c of a row
+    // Q rows -> shared memory in the 128-byte-swizzled K-major form the MMA reads (16-byte chunk c of a row
     // sits at chunk c ^ (row & 7)); rows without a token are zero
     if (tid < kTcRows) {
-        const uint4* src = reinterpret_cast<const uint4*>(q + qo_row * D);
 #pragma unroll
-        for (int c = 0; c < 16; c++) {
-            const uint4 v = valid ? src[c] : make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(s_q + (c >> 3) * (kTcRows * 128) + tid * 128 + (((c & 7) ^ (tid & 7)) << 4)) = v;
+        for (int i = 0; i < 16; i++) {
+            const int r = (i * kTcRows + tid) >> 4, c = tid & 15;
+            *reinterpret_cast<uint4*>(s_q + (c >> 3) * (kTcRows * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = qv[i];
         }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic writes above -> visible to TMA / MMA
@@ -474,7 +488,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     if (!poisoned && warp < kTcRows / 32) {
         float* prow = nullptr;
         if (n_chunks > 1)                                    // split context: (o, m, l) of this chunk into the sequence's region
-            prow = partials + (size_t)pf.poff[b] * g.H * (D + 2) +
+            prow = partials + (size_t)poff * g.H * (D + 2) +
                    partial_off(chunk, (tok_first + tid / G) * g.H + kvh * G + tid % G, nq * g.H, D);
         const float inv = 1.0f / (l_run + 1e-8f);
 #pragma unroll
@@ -518,7 +532,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     if (tid == 0) {
         __threadfence();
         const int tiles = (nq + tpt - 1) / tpt;
-        int* c = counters + pf.cbase[b] + kvh * tiles + tile;
+        int* c = counters + cbase + kvh * tiles + tile;
         const int ticket = atomicAdd(c, 1);
         const int last = ticket == n_chunks - 1;
         if (last) *c = 0;
@@ -527,8 +541,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
     __syncthreads();
     if (*s_flag) {
         const MergeOut mo{nullptr, out, nullptr, out_dtype, nullptr, status};
-        merge_rows(g, mo, b, kvh, G, 0, n_chunks, partials + (size_t)pf.poff[b] * g.H * (D + 2),
-                   MergeMap{G * tok_cnt, nq * g.H, st.q_base[b] + tok_first, tok_first, 0});
+        merge_rows(g, mo, b, kvh, G, 0, n_chunks, partials + (size_t)poff * g.H * (D + 2),
+                   MergeMap{G * tok_cnt, nq * g.H, q_base + tok_first, tok_first, 0});
     }
 }
 

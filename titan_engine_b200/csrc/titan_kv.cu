@@ -301,7 +301,7 @@ int create_impl(const tk_kv_config* cfg_in, void* arena, size_t arena_bytes, boo
 
     // one buffer holds every per-step array; sections are 16-byte aligned
     size_t ints = 9 * (size_t)c.max_seqs + 4 + 32 + 4 * (size_t)c.max_step_tokens + 16 +
-                  8 * (size_t)h->max_items + 4 * (size_t)h->max_pf_items + 4 * (size_t)h->max_seals +
+                  8 * (size_t)h->max_items + 12 * (size_t)h->max_pf_items + 4 * (size_t)h->max_seals +
                   2 * (size_t)kMaxDelta + 32;
     h->step_bytes = align_up(ints * 4, 256);
 
@@ -474,7 +474,7 @@ int prefetch_layer(tk_kv* h, int layer, bool ahead) {
 
 struct Sections {       // offsets (in int32 units) of the arrays inside a step buffer
     size_t seq, len, chunk_base, new_tok, q_base, nq, tok_b, tok_pos, tok_dst, tok_open, items, seals, delta,
-           pf_ct, pf_poff, pf_cbase, pf_items, pf_small, end;
+           pf_ct, pf_poff, pf_cbase, pf_items, pf_info, pf_small, end;
 };
 Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals, int n_delta, int n_pf, int n_pf_small) {
     auto a4 = [](size_t x) { return (x + 3) / 4 * 4; };
@@ -498,6 +498,7 @@ Sections sections(int n_seqs, int n_tokens, int n_open, int n_items, int n_seals
         s.pf_poff = o;  o = a4(o + n_seqs);
         s.pf_cbase = o; o = a4(o + n_seqs);
         s.pf_items = o; o = a4(o + 4 * (size_t)n_pf);
+        s.pf_info = o;  o = a4(o + 8 * (size_t)n_pf);
         s.pf_small = o; o = a4(o + 4 * (size_t)n_pf_small);
     }
     s.end = o;
@@ -771,6 +772,12 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
         memcpy(w + sec.pf_poff, p.pf_poff.data(), 4 * (size_t)n_seqs);
         memcpy(w + sec.pf_cbase, p.pf_cbase.data(), 4 * (size_t)n_seqs);
         if (n_pf) memcpy(w + sec.pf_items, p.pf_items.data(), 16 * (size_t)n_pf);
+        for (int i = 0; i < n_pf; i++) {                     // what the item's CTA needs of its sequence, next to the item:
+            const int b = p.pf_items[i].b;                   // one dependent load less before its first copy can go out
+            int32_t* o = w + sec.pf_info + 8 * (size_t)i;
+            o[0] = p.seq[b]; o[1] = p.len[b]; o[2] = p.nq[b]; o[3] = p.pf_ct[b];
+            o[4] = p.q_base[b]; o[5] = p.pf_poff[b]; o[6] = p.pf_cbase[b]; o[7] = 0;
+        }
         if (n_pf_small) memcpy(w + sec.pf_small, p.pf_small_items.data(), 16 * (size_t)n_pf_small);
     }
     TK_CUDA(h, cudaMemcpyAsync(h->d_step, w, sec.end * 4, cudaMemcpyHostToDevice, s));
@@ -788,7 +795,8 @@ static int step_begin_impl(tk_kv* h, int32_t n_seqs, const int32_t* seq_ids, con
     dv.chunk_tokens = p.chunk_tokens; dv.n_open = n_open;
     h->pf_dev = tk::PrefillDev{};
     if (p.pf_built) {
-        h->pf_dev = tk::PrefillDev{(const int4*)(d + sec.pf_items), d + sec.pf_ct, d + sec.pf_poff, d + sec.pf_cbase, n_pf};
+        h->pf_dev = tk::PrefillDev{(const int4*)(d + sec.pf_items), d + sec.pf_ct, d + sec.pf_poff, d + sec.pf_cbase, n_pf,
+                                   (const int4*)(d + sec.pf_info)};
         h->small_dev = dv;                                  // the decode kernel's share: the short sequences only
         h->small_dev.items = (const int4*)(d + sec.pf_small);
         h->small_dev.n_items = n_pf_small;

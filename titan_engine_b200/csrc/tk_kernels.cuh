@@ -72,6 +72,7 @@ struct PrefillDev {
     const int32_t* poff;        // [n_seqs] first token row of the sequence's split region in the workspace
     const int32_t* cbase;       // [n_seqs] first arrival counter of the sequence (+ kvh * tiles + tile)
     int n_items;
+    const int4*    info;        // [n_items][2]: (seq, len, nq, ct), (q_base, poff, cbase, 0) of the item's sequence
 };
 
 // partial row layout: [row][H][D+2] f32 = o[0..D) unnormalised, m at [D], l at [D+1]
