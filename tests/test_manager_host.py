@@ -330,6 +330,54 @@ def test_fork_shares_full_pages_and_counts_references():
     assert e.value.status == L.TK_OUT_OF_PAGES and t.digest() == dg
 
 
+def test_prefill_work_list_order_keeps_a_sequences_pages_together():
+    """Launch order of the prefill items: the tiles and chunks of one (sequence, kv head) read the same pages, so
+    they go out together - in sets of about 48 MB of K/V (512 B per token and kv head), the biggest (sequence, kv
+    head) groups first, and big items first inside a set."""
+    H, Hkv, G = 32, 8, 4
+    lens0 = [150_000, 60_000, 90_000, 20_000, 0]             # 77, 31, 46, 10 MB of K/V per kv head (+ the new tokens)
+    n_new = [512, 512, 512, 512, 512]
+    mpps = 9500
+    c = PagedKVCache(1, H, Hkv, 128, 21_000, len(lens0), mpps, dtype="bf16", host_only=True, max_step_tokens=4096)
+    seqs, at = [], 0
+    for n in lens0:
+        s = c.seq_alloc()
+        pages = (n + 15) // 16
+        c.adopt(s, np.arange(at, at + pages, dtype=np.int32), n)
+        at += pages
+        seqs.append(s)
+    c.step_begin(seqs, n_new)
+    items, ct, _ = c.step_prefill_plan()
+    items = items.tolist()
+    tpt = 64 // G
+    def weight(it):
+        b, chunk, kvh, tile = it
+        nq, ln = n_new[b], lens0[b] + n_new[b]
+        tok_cnt = min(nq - tile * tpt, tpt)
+        p_last = ln - nq + tile * tpt + tok_cnt - 1
+        return min(ct[b], p_last + 1 - chunk * ct[b]) * tok_cnt * G
+    # replay the rule: groups by total weight (ties: sequence, kv head), cut into sets by bytes
+    groups = {}
+    for it in items:
+        groups.setdefault((it[0], it[2]), 0)
+        groups[(it[0], it[2])] += weight(it)
+    order = sorted(groups, key=lambda k: (-groups[k], k))
+    set_of, cur, bytes_in = {}, 0, 0
+    for k in order:
+        kv = (lens0[k[0]] + n_new[k[0]]) * 512
+        if bytes_in > 0 and bytes_in + kv > 48 << 20:
+            cur, bytes_in = cur + 1, 0
+        set_of[k] = cur
+        bytes_in += kv
+    sets = [set_of[(it[0], it[2])] for it in items]
+    assert sets == sorted(sets) and sets[-1] >= 3            # the long sequences are alone in their sets
+    for a, b in zip(items, items[1:]):                       # big first inside a set
+        if set_of[(a[0], a[2])] == set_of[(b[0], b[2])]:
+            assert weight(a) >= weight(b)
+    first = [it for it, st in zip(items, sets) if st == 0]
+    assert {(it[0], it[2]) for it in first} == {(0, 0)}      # the heaviest group: sequence 0, kv head 0, by itself
+
+
 @pytest.mark.parametrize("shape", [(32, 8), (64, 8), (16, 16), (16, 1), (8, 4)])
 def test_prefill_work_list_covers_every_row_once(shape):
     """Index arithmetic of the prefill attention kernel, replayed on the host: the tiles of 64 (token, head)
