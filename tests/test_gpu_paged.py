@@ -774,6 +774,29 @@ def test_decode_multi_refusals():
         f.gpu.decode_multi(0, torch.zeros(2, 64, 128, device=f.dev, dtype=torch.bfloat16))
 
 
+@pytest.mark.parametrize("case", [(1, 32, 8, "bf16"), (2, 64, 8, "fp16"), (3, 16, 16, "bf16")])
+def test_prefill_chunks_random_steps(case):
+    """Random prefill chunks (1 .. 700 tokens, so tiles that end anywhere in a 128-row tile, blocks that end anywhere in
+    a page) on contexts that grow from step to step, sequences leaving and joining, one-token rows in the same
+    steps: every token of every step against the oracle's per-token decode, FP32 results at the stated tolerance."""
+    seed, H, Hkv, dtype = case
+    t = Twin(1, H, Hkv, 128, 700, 4, 260, dtype=dtype, impl="mma", max_step_tokens=2200, seed=300 + seed)
+    g = rng(400 + seed)
+    live = [t.seq_alloc() for _ in range(3)]
+    for it in range(7):
+        if it == 3:
+            t.seq_free(live.pop(1))
+            live.append(t.seq_alloc())
+        seqs = sorted(live)
+        n_new = []
+        for s in seqs:
+            room = 260 * 16 - t.gpu.seq_len(s)
+            n = int(g.integers(1, 701)) if g.random() < 0.75 else 1
+            n_new.append(max(1, min(n, room - 1)))
+        t.step(seqs, n_new, every_token=True, f32_out=(it % 2 == 0))
+    t.gpu.device_status()
+
+
 @pytest.mark.parametrize("seed", [1, 2])
 def test_decode_multi_random_steps(seed):
     """Random token counts per sequence and step (1 .. 2*16/G + 1), small chunks so that the new tokens keep
