@@ -364,7 +364,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, Geometry g, StepDev 
 
             // ---- online softmax of the row ----
             const int nv = valid ? max(0, min(min(kTcBlock, t1 - tok_base), lim - tok_base)) : 0;
-            const bool full = __all_sync(0xFFFFFFFFu, nv == kTcBlock);  // no row of the warp is cut by the diagonal or the end
+            // no row of the warp is cut by the diagonal or the end, and every row has a reference already (on its first
+            // block a row has none: speculating against -1e30 would be a pass thrown away)
+            const bool full = __all_sync(0xFFFFFFFFu, nv == kTcBlock && m2 > -1e29f);
             float alpha = 1.0f;
             bool moved = false;
             uint32_t pr[32];                                 // P of the row: 64 values, two 16-bit per register
