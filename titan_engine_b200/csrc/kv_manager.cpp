@@ -275,6 +275,20 @@ int PageManager::load(const int32_t* im, size_t n) {
     return ST_OK;
 }
 
+namespace {
+// One stable counting pass of an index permutation by 11 bits of a 32-bit key (LSD radix sort: call it for
+// the low digit first).  The step plans sort a few thousand to a few ten thousand items per step; a
+// comparison sort of that many took longer than everything else in the plan.
+void radix_pass(const std::vector<uint32_t>& key, std::vector<int32_t>& idx, std::vector<int32_t>& tmp, int shift) {
+    uint32_t count[2049] = {};
+    for (int32_t i : idx) count[((key[(size_t)i] >> shift) & 2047u) + 1]++;
+    for (int d = 0; d < 2048; d++) count[d + 1] += count[d];
+    tmp.resize(idx.size());
+    for (int32_t i : idx) tmp[count[(key[(size_t)i] >> shift) & 2047u]++] = i;
+    idx.swap(tmp);
+}
+}  // namespace
+
 int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new, int num_kv_heads,
                            bool fp8, int chunk_tokens, int target_items, int max_step_tokens,
                            int max_partial_rows, StepPlan* plan, const int32_t* len_cap, int heads_per_kv,
@@ -387,14 +401,25 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         if (add > 1) plan->one_token_steps = false;
         if (len == 0) plan->has_empty_seq = true;
         const int sealed_end = (full_len / ps) * ps;    // FP8: rows below it are in sealed pages after this step
-        for (int p = old_len; p < full_len; p++) {
-            plan->tok_b.push_back(i);
-            plan->tok_pos.push_back(p);
-            if (fp8) {
-                if (p >= sealed_end) plan->tok_open.push_back((int32_t)plan->tok_b.size() - 1);
-                plan->tok_dst.push_back(p < sealed_end ? -1 : s * ps + p % ps);
+        {   // the step's token list: (sequence index, position, destination row) - filled in place, page by page
+            const size_t at = plan->tok_b.size();
+            plan->tok_b.resize(at + add, i);
+            plan->tok_pos.resize(at + add);
+            plan->tok_dst.resize(at + add);
+            int32_t* pos = plan->tok_pos.data() + at;
+            int32_t* dst = plan->tok_dst.data() + at;
+            const int32_t* row_s = table_.data() + (size_t)s * max_pages_per_seq_;
+            for (int p = old_len; p < full_len;) {
+                const int r0 = p % ps, n = std::min(ps - r0, full_len - p);
+                const int32_t base = fp8 ? (p >= sealed_end ? s * ps : -1) : row_s[p / ps] * ps;
+                for (int r = 0; r < n; r++) {
+                    pos[p - old_len + r] = p + r;
+                    dst[p - old_len + r] = (fp8 && base < 0) ? -1 : base + r0 + r;
+                }
+                if (fp8 && base >= 0)
+                    for (int r = 0; r < n; r++) plan->tok_open.push_back((int32_t)(at + (p - old_len) + r));
+                p += n;
             }
-            else plan->tok_dst.push_back(table_[(size_t)s * max_pages_per_seq_ + p / ps] * ps + p % ps);
         }
         if (fp8)
             for (int lp = old_len / ps; (lp + 1) * ps <= full_len; lp++)
@@ -428,13 +453,16 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
         for (int i = 0; i < n_seqs; i++)
             if (evict_cold(seqs[i], old_lens[i], &plan->evictions) < 0) plan->evictions_refused++;
     // biggest items first, so the short tails fill the end of the schedule
-    std::vector<int32_t> order(plan->items.size());
-    for (size_t i = 0; i < order.size(); i++) order[i] = (int32_t)i;
-    std::stable_sort(order.begin(), order.end(),
-                     [&](int32_t a, int32_t b) { return item_tokens[a] > item_tokens[b]; });
-    std::vector<WorkItem> sorted(order.size());
-    for (size_t i = 0; i < order.size(); i++) sorted[i] = plan->items[order[i]];
-    plan->items.swap(sorted);
+    {
+        std::vector<uint32_t> key(plan->items.size());       // descending size: a chunk holds at most 2^22 tokens
+        std::vector<int32_t> order(key.size()), tmp;
+        for (size_t i = 0; i < key.size(); i++) { key[i] = 0x3FFFFFu - (uint32_t)std::min(item_tokens[i], 0x3FFFFF); order[i] = (int32_t)i; }
+        radix_pass(key, order, tmp, 0);
+        radix_pass(key, order, tmp, 11);
+        std::vector<WorkItem> sorted(order.size());
+        for (size_t i = 0; i < order.size(); i++) sorted[i] = plan->items[(size_t)order[i]];
+        plan->items.swap(sorted);
+    }
 
     // ---- prefill-sized steps: tiles of kPrefillRows rows for the sequences that append many tokens ----
     plan->pf_built = false;
@@ -475,6 +503,7 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
             if (small_rows + rows <= max_partial_rows || shrink > 8) { plan->pf_partial_rows = (int32_t)std::min<int64_t>(rows, INT32_MAX); break; }
         }
         std::vector<int64_t> weight;
+        weight.reserve(plan->pf_items.capacity());
         for (int i = 0; i < n_seqs; i++) {
             if (is_small(i)) continue;
             const int nq = plan->nq[i], len = plan->len[i], ct = plan->pf_ct[i];
@@ -518,10 +547,18 @@ int PageManager::plan_step(int n_seqs, const int32_t* seqs, const int32_t* n_new
                 bytes_in += kv_bytes;
             }
         }
-        std::stable_sort(ord.begin(), ord.end(), [&](int32_t a, int32_t b) {
-            const int32_t sa = group_set[group_of(a)], sb = group_set[group_of(b)];
-            return sa != sb ? sa < sb : weight[a] > weight[b];
-        });
+        {   // by set, inside a set by descending weight (at most 32768 tokens x 128 rows: 22 bits), then the order of
+            // generation: three stable passes, least significant first (sets beyond 2047 share the last one)
+            std::vector<uint32_t> kw(ord.size()), ks(ord.size());
+            std::vector<int32_t> tmp;
+            for (size_t k = 0; k < ord.size(); k++) {
+                kw[k] = 0x3FFFFFu - (uint32_t)std::min<int64_t>(weight[k], 0x3FFFFF);
+                ks[k] = (uint32_t)std::min(group_set[group_of((int32_t)k)], 2047);
+            }
+            radix_pass(kw, ord, tmp, 0);
+            radix_pass(kw, ord, tmp, 11);
+            radix_pass(ks, ord, tmp, 0);
+        }
         std::vector<WorkItem> pf_sorted(ord.size());
         for (size_t i = 0; i < ord.size(); i++) pf_sorted[i] = plan->pf_items[ord[i]];
         plan->pf_items.swap(pf_sorted);
